@@ -1,0 +1,111 @@
+"""ctypes bindings of the in-tree native libraries.
+
+``cuda()`` returns the handle of ``libaxonml_cuda.so`` (hand-written sm_100a kernels) and
+``host()`` the handle of ``libaxonml_host.so`` (C++ runtime: codecs, quantisers, CPU reference
+kernels).  Both are built on first use if the shared object is missing.  On a machine with a GPU
+a missing CUDA library is an error, never a silent fallback to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LOCK = threading.Lock()
+_CUDA = None
+_HOST = None
+_LIBDIR = Path(__file__).resolve().parent / "_lib"
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_int64 = ctypes.c_int64
+
+
+class NativeError(RuntimeError):
+    """Raised when a native launcher returns a non-zero code."""
+
+
+def _load(name: str, builder: str):
+    path = _LIBDIR / name
+    if not path.exists() or os.environ.get("AXONML_REBUILD") == "1":
+        from . import _build
+        getattr(_build, builder)(verbose=True)
+    return ctypes.CDLL(str(path))
+
+
+def cuda():
+    """Handle of the CUDA kernel library (built for sm_100a)."""
+    global _CUDA
+    if _CUDA is None:
+        with _LOCK:
+            if _CUDA is None:
+                _CUDA = _load("libaxonml_cuda.so", "build_cuda")
+    return _CUDA
+
+
+def host():
+    """Handle of the host C++ runtime library."""
+    global _HOST
+    if _HOST is None:
+        with _LOCK:
+            if _HOST is None:
+                _HOST = _load("libaxonml_host.so", "build_host")
+    return _HOST
+
+
+def have_gpu() -> bool:
+    return torch.cuda.is_available()
+
+
+def is_blackwell() -> bool:
+    if not torch.cuda.is_available():
+        return False
+    major, _ = torch.cuda.get_device_capability()
+    return major == 10
+
+
+def stream_ptr(stream=None) -> c_void_p:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return c_void_p(s.cuda_stream)
+
+
+def ptr(t) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    return c_void_p(t.data_ptr())
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{what} failed with code {rc}")
+
+
+_STATUS = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32[4] status word that kernels write when a bounded wait gives up."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.type, dev.index)
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=dev)
+        _STATUS[key] = t
+    return t
+
+
+class KernelTimeout(RuntimeError):
+    """A bounded device-side wait ran out (the kernel still finished and freed its resources)."""
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises ``KernelTimeout`` if any kernel recorded an error."""
+    t = status_word(device)
+    vals = t.tolist()
+    if vals[0] != 0:
+        t.zero_()
+        raise KernelTimeout(f"kernel status code={vals[0]} where={vals[1]} block={vals[2]}")

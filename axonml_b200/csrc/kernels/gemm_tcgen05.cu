@@ -1,0 +1,380 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// the accumulator in TMEM -> tcgen05.ld epilogue (bias, activation, optional second output) ->
+// TMA store.  One CTA per SM; the accumulator is double-buffered in TMEM so that the epilogue of
+// tile i overlaps the main loop of tile i+1.
+//
+//   C[M,N] = act(A[M,K] * B[K,N] + bias[N])
+//
+// Operand layouts ("major" = which logical dimension is contiguous in memory):
+//   A: K-major  = row-major [M,K]          MN-major = row-major [K,M]   (A given transposed)
+//   B: K-major  = row-major [N,K] (Linear) MN-major = row-major [K,N]
+// which covers forward (A K, B K), dgrad (A K, B MN) and wgrad (A MN, B MN) of a Linear layer
+// without materialising a transpose.
+//
+// Replaces the reference's CPU FusedLinear (crates/axonml-fusion/src/linear.rs:138-164), the
+// Linear forward (crates/axonml-nn/src/layers/linear.rs:104-140) and its cuBLAS sgemm island
+// (crates/axonml-core/src/backends/cuda.rs:413-451).
+#include "common.cuh"
+
+namespace {
+
+using namespace ax;
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int kEpiWarps = 4;
+constexpr int kStageBufBytes = 32 * 128;  // 32 rows x 64 bf16 staging tile for the TMA store
+
+struct GemmParams {
+  int M, N, K;
+  const void* bias;  // per output column
+  int bias_kind;     // 0 none, 1 fp32, 2 bf16
+  int act;           // ax::Act applied to C
+  int has_aux;       // also store the pre-activation (A*B + bias) through map_aux
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators
+  static constexpr int kSmem =
+      1024 /*alignment slack*/ + kStages * kStage + kEpiWarps * 2 * kStageBufBytes + 256;
+};
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_c,
+                 const __grid_constant__ CUtensorMap map_aux, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* epi_base = smem + C::kStages * C::kStage;
+  uint64_t* bars = (uint64_t*)(epi_base + kEpiWarps * 2 * kStageBufBytes);
+  uint64_t* full_bar = bars;                       // [kStages]
+  uint64_t* empty_bar = bars + C::kStages;         // [kStages]
+  uint64_t* tfull_bar = bars + 2 * C::kStages;     // [2]
+  uint64_t* tempty_bar = bars + 2 * C::kStages + 2;  // [2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::kStages + 4);
+  volatile int* dead = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], kEpiWarps);
+    }
+    mbar_fence_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    prefetch_tensormap(&map_c);
+  }
+  if (warp == 1) {
+    tmem_alloc<C::kTmemCols>(tmem_slot);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Tile order: groups of 8 M-blocks sweep all N-blocks, so that concurrently running CTAs
+  // share A and B tiles through L2.
+  auto tile_coords = [&](int t, int& mb, int& nb) {
+    constexpr int G = 8;
+    int per_group = G * num_n;
+    int g = t / per_group;
+    int first_m = g * G;
+    int gsz = min(G, num_m - first_m);
+    int r = t - g * per_group;
+    mb = first_m + r % gsz;
+    nb = r / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int mb, nb;
+        tile_coords(t, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, dead, p.status, 100)) break;
+          uint8_t* sa = stage_base + s * C::kStage;
+          uint8_t* sb = sa + C::kStageA;
+          mbar_expect_tx(&full_bar[s], C::kStage);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), &map_a, &full_bar[s], m0 + j * 64, k0);
+          } else {
+            tma_load_2d(sa, &map_a, &full_bar[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &map_b, &full_bar[s], n0 + j * 64, k0);
+          } else {
+            tma_load_2d(sb, &map_b, &full_bar[s], k0, n0);
+          }
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+        if (*dead) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, A_MN, B_MN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, dead, p.status, 200)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, dead, p.status, 201)) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * C::kStage);
+          const uint32_t sb = sa + C::kStageA;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da = A_MN ? umma_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024)
+                               : umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                               : umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        if (*dead) break;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int ew = warp - 2;           // staging-buffer owner index
+    uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
+    int buf = 0;
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(t, mb, nb);
+      const int m0 = mb * BM, n0 = nb * BN;
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      bool ok = mbar_wait(&tfull_bar[acc], acc_ph, dead, p.status, 300);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 64; ++ch) {
+        uint32_t r[64];
+        {
+          uint32_t(&r0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[0]);
+          uint32_t(&r1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[32]);
+          tmem_ld_32x32b_x32(t_row + ch * 64, r0);
+          tmem_ld_32x32b_x32(t_row + ch * 64 + 32, r1);
+          tc_wait_ld();
+        }
+        if (ch == BN / 64 - 1) {
+          // all of this warp's TMEM reads for the tile are done: hand the accumulator back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        const int ncol0 = n0 + ch * 64;
+        if (ncol0 >= p.N) continue;  // fully out-of-range chunk (warp-uniform)
+        if (p.bias_kind != 0) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            int n = ncol0 + j;
+            float b = 0.f;
+            if (n < p.N)
+              b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n)
+                                   : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
+            r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
+          }
+        }
+        const int passes = p.has_aux ? 2 : 1;
+        for (int pass = 0; pass < passes; ++pass) {
+          const bool is_aux = p.has_aux && pass == 0;
+          uint8_t* dst = stg + buf * kStageBufBytes;
+          // the bulk store that last read this buffer must have finished reading it
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float x = __uint_as_float(r[c * 8 + j]);
+              v[j] = is_aux ? x : apply_act(x, p.act);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]);
+            o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]);
+            o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(is_aux ? &map_aux : &map_c, dst, ncol0, m0 + q * 32);
+            tma_store_commit();
+          }
+          buf ^= 1;
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc<C::kTmemCols>(tmem_base);
+}
+
+// ------------------------------------------------------------------ host side
+struct MapKey {
+  const void* ptr;
+  uint64_t d0, d1, ld;
+  uint32_t b0, b1;
+};
+
+int make_map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                uint32_t box_inner, uint32_t box_outer) {
+  uint64_t dims[2] = {inner, outer};
+  uint64_t strides[1] = {ld_elems * 2};
+  uint32_t box[2] = {box_inner, box_outer};
+  return axh::encode_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <int BN, int A_MN, int B_MN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc,
+           const CUtensorMap& maux, const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
+  if (grid < 1) grid = 1;
+  kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mb, mc, maux, p);
+  return (int)cudaGetLastError();
+}
+
+template <int BN>
+int dispatch_major(int a_mn, int b_mn, const CUtensorMap& ma, const CUtensorMap& mb,
+                   const CUtensorMap& mc, const CUtensorMap& maux, const GemmParams& p,
+                   int max_ctas, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch<BN, 0, 0>(ma, mb, mc, maux, p, max_ctas, stream);
+  if (!a_mn && b_mn) return launch<BN, 0, 1>(ma, mb, mc, maux, p, max_ctas, stream);
+  if (a_mn && !b_mn) return launch<BN, 1, 0>(ma, mb, mc, maux, p, max_ctas, stream);
+  return launch<BN, 1, 1>(ma, mb, mc, maux, p, max_ctas, stream);
+}
+
+}  // namespace
+
+// C[M,N] (bf16, row stride ldc) = act(A*B + bias).  `a_mn` / `b_mn` select the operand layout
+// (see the file header); lda / ldb are the row strides, in elements, of the matrices as stored.
+// `aux` (may be null) receives the pre-activation.  `bn_hint` forces the N tile (0 = choose).
+// `max_ctas` limits the persistent grid (0 = one per SM), so that a concurrent kernel on another
+// stream keeps some SMs.  Returns a cudaError_t value, or -1 for an unsupported argument.
+AX_API int ax_gemm_bf16(const void* A, const void* B, void* Cout, void* aux, const void* bias,
+                        int bias_kind, int act, int M, int N, int K, int lda, int ldb, int ldc,
+                        int a_mn, int b_mn, int bn_hint, int max_ctas, int* status,
+                        cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8)) return -1;
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)Cout | (uintptr_t)aux) & 15) return -1;
+  int sms = axh::sm_count();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+
+  int BN = bn_hint;
+  if (BN != 64 && BN != 128 && BN != 256) {
+    if (N <= 64) {
+      BN = 64;
+    } else if (N <= 128) {
+      BN = 128;
+    } else {
+      // pick the tile with the lower estimated time: waves x per-tile cost
+      auto waves = [&](int bn) {
+        long tiles = (long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+        return (double)((tiles + max_ctas - 1) / max_ctas);
+      };
+      double c256 = waves(256) * 2.0, c128 = waves(128) * 1.45;
+      BN = c256 <= c128 ? 256 : 128;
+    }
+  }
+
+  CUtensorMap ma, mb, mc, maux;
+  int rc;
+  if (a_mn)
+    rc = make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+  else
+    rc = make_map_2d(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (rc) return 1000 + rc;
+  if (b_mn)
+    rc = make_map_2d(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  else
+    rc = make_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)BN);
+  if (rc) return 2000 + rc;
+  rc = make_map_2d(&mc, Cout, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32);
+  if (rc) return 3000 + rc;
+  if (aux) {
+    rc = make_map_2d(&maux, aux, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32);
+    if (rc) return 4000 + rc;
+  } else {
+    maux = mc;
+  }
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.bias = bias;
+  p.bias_kind = bias ? bias_kind : 0;
+  p.act = act;
+  p.has_aux = aux ? 1 : 0;
+  p.status = status;
+  switch (BN) {
+    case 256: return dispatch_major<256>(a_mn, b_mn, ma, mb, mc, maux, p, max_ctas, stream);
+    case 128: return dispatch_major<128>(a_mn, b_mn, ma, mb, mc, maux, p, max_ctas, stream);
+    default: return dispatch_major<64>(a_mn, b_mn, ma, mb, mc, maux, p, max_ctas, stream);
+  }
+}
