@@ -1,0 +1,281 @@
+// LayerNorm / RMSNorm forward and backward, bf16 or fp32 activations, fp32 statistics.
+// One warp per row; rows are read twice (the second read is served by L1/L2), so HBM traffic is
+// one read of x and one write of y.  The optional residual input fuses `h = x + r` (h is written
+// out as the new residual stream) with the normalisation of h.
+//
+// Backward: per-row dx in one pass; weight/bias gradients are accumulated per CTA in shared
+// memory, written as per-CTA partials to a scratch buffer [grid, 2, D] and summed by a second
+// kernel (deterministic, no global atomics).
+//
+// Parity: crates/axonml-nn/src/layers/norm.rs:447-482 (LayerNorm), crates/axonml-llm/src/llama.rs:158-187
+// (RMSNorm), and the WGSL layer-norm shader arithmetic (wgpu_backend.rs:1318-1361).
+#include "common.cuh"
+
+namespace {
+using namespace ax;
+
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
+           d = unpack_bf16x2(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+    u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <>
+struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+constexpr int kWarpsPerCta = 8;
+
+// x, res, y, hout: [rows, D] (row stride D); w, b: [D] of type WT; mean/rstd: [rows] fp32.
+template <typename T, typename WT, bool RMS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const WT* __restrict__ w,
+                const WT* __restrict__ b, T* __restrict__ y, T* __restrict__ hout,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int D,
+                float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (long row = (long)blockIdx.x * kWarpsPerCta + warp; row < rows;
+       row += (long)gridDim.x * kWarpsPerCta) {
+    const T* xr = x + row * D;
+    const T* rr = res ? res + row * D : nullptr;
+    T* hr = hout ? hout + row * D : nullptr;
+    float s = 0.f, ss = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+      float v[8];
+      Vec8<T>::load(xr + c, v);
+      if (rr) {
+        float r[8];
+        Vec8<T>::load(rr + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += r[j];
+        if (hr) {
+          // round to the storage type so that the statistics match what backward re-reads
+          Vec8<T>::store(hr + c, v);
+          Vec8<T>::load(hr + c, v);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[j]; ss += v[j] * v[j]; }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    float mean = RMS ? 0.f : s / D;
+    float var = RMS ? ss / D : fmaxf(ss / D - mean * mean, 0.f);
+    float rstd = rsqrtf(var + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    const T* src = (rr && hr) ? hr : xr;
+    T* yr = y + row * D;
+    for (int c = lane * 8; c < D; c += 256) {
+      float v[8], wv[8], bv[8];
+      Vec8<T>::load(src + c, v);
+      if (rr && !hr) {
+        float r[8];
+        Vec8<T>::load(rr + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += r[j];
+      }
+      Vec8<WT>::load(w + c, wv);
+      if (b) Vec8<WT>::load(b + c, bv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float o = (v[j] - mean) * rstd * wv[j];
+        v[j] = b ? o + bv[j] : o;
+      }
+      Vec8<T>::store(yr + c, v);
+    }
+  }
+}
+
+// dx per row; per-CTA partial sums of dw (and db) into `partial` [gridDim.x, 2, D].
+// If `dres_in` is given it is added to dx (gradient arriving through the residual stream).
+template <typename T, typename WT, bool RMS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* __restrict__ w,
+                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                const T* __restrict__ dres_in, T* __restrict__ dx, float* __restrict__ partial,
+                int rows, int D) {
+  // [2][Dp], Dp = D rounded up to 256.  Column (b*256 + l*8 + j) lives at b*256 + j*32 + l so
+  // that the 32 lanes of a warp always hit 32 different banks.
+  extern __shared__ float sacc[];
+  const int Dp = ((D + 255) / 256) * 256;
+  float* sdw = sacc;
+  float* sdb = sacc + Dp;
+  for (int i = threadIdx.x; i < 2 * Dp; i += blockDim.x) sacc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (long row = (long)blockIdx.x * kWarpsPerCta + warp; row < rows;
+       row += (long)gridDim.x * kWarpsPerCta) {
+    const T* xr = x + row * D;
+    const T* dyr = dy + row * D;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;  // sum(dy*w), sum(dy*w*xhat)
+    for (int c = lane * 8; c < D; c += 256) {
+      float xv[8], gv[8], wv[8];
+      Vec8<T>::load(xr + c, xv);
+      Vec8<T>::load(dyr + c, gv);
+      Vec8<WT>::load(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float xh = (xv[j] - mean) * rstd;
+        float gw = gv[j] * wv[j];
+        s1 += gw;
+        s2 += gw * xh;
+        const int slot = (c - lane * 8) + j * 32 + lane;
+        atomicAdd(&sdw[slot], gv[j] * xh);
+        if (!RMS) atomicAdd(&sdb[slot], gv[j]);
+      }
+    }
+    s1 = warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    if (RMS) s1 = 0.f;
+    T* dxr = dx + row * D;
+    const T* drr = dres_in ? dres_in + row * D : nullptr;
+    for (int c = lane * 8; c < D; c += 256) {
+      float xv[8], gv[8], wv[8], o[8];
+      Vec8<T>::load(xr + c, xv);
+      Vec8<T>::load(dyr + c, gv);
+      Vec8<WT>::load(w + c, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float xh = (xv[j] - mean) * rstd;
+        o[j] = rstd * (gv[j] * wv[j] - s1 - xh * s2);
+      }
+      if (drr) {
+        float r[8];
+        Vec8<T>::load(drr + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      Vec8<T>::store(dxr + c, o);
+    }
+  }
+  __syncthreads();
+  float* out = partial + (long)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * Dp; i += blockDim.x) {
+    const int which = i / Dp, pos = i - which * Dp;
+    const int rem = pos & 255;
+    const int col = (pos - rem) + (rem & 31) * 8 + (rem >> 5);
+    if (col < D) out[which * D + col] = sacc[i];
+  }
+}
+
+// dw[d] = sum_g partial[g,0,d]; db[d] = sum_g partial[g,1,d]
+template <typename WT>
+__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, WT* __restrict__ dw,
+                                       WT* __restrict__ db, int groups, int D) {
+  int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float a = 0.f, b = 0.f;
+  for (int g = 0; g < groups; ++g) {
+    a += partial[(long)g * 2 * D + d];
+    b += partial[(long)g * 2 * D + D + d];
+  }
+  if (dw) dw[d] = (WT)a;
+  if (db) db[d] = (WT)b;
+}
+
+template <typename T, typename WT>
+int launch_fwd(bool rms, const void* x, const void* res, const void* w, const void* b, void* y,
+               void* hout, float* mean, float* rstd, int rows, int D, float eps,
+               cudaStream_t stream) {
+  int grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  int cap = axh::sm_count() * 8;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  if (rms)
+    norm_fwd_kernel<T, WT, true><<<grid, kWarpsPerCta * 32, 0, stream>>>(
+        (const T*)x, (const T*)res, (const WT*)w, (const WT*)b, (T*)y, (T*)hout, mean, rstd, rows,
+        D, eps);
+  else
+    norm_fwd_kernel<T, WT, false><<<grid, kWarpsPerCta * 32, 0, stream>>>(
+        (const T*)x, (const T*)res, (const WT*)w, (const WT*)b, (T*)y, (T*)hout, mean, rstd, rows,
+        D, eps);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, typename WT>
+int launch_bwd(bool rms, const void* dy, const void* x, const void* w, const float* mean,
+               const float* rstd, const void* dres, void* dx, void* dw, void* db, float* scratch,
+               int groups, int rows, int D, cudaStream_t stream) {
+  size_t smem = (size_t)2 * (((D + 255) / 256) * 256) * sizeof(float);
+  if (rms) {
+    auto k = norm_bwd_kernel<T, WT, true>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<groups, kWarpsPerCta * 32, smem, stream>>>((const T*)dy, (const T*)x, (const WT*)w, mean,
+                                                   rstd, (const T*)dres, (T*)dx, scratch, rows, D);
+  } else {
+    auto k = norm_bwd_kernel<T, WT, false>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<groups, kWarpsPerCta * 32, smem, stream>>>((const T*)dy, (const T*)x, (const WT*)w, mean,
+                                                   rstd, (const T*)dres, (T*)dx, scratch, rows, D);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  norm_bwd_reduce_kernel<WT><<<(D + 255) / 256, 256, 0, stream>>>(scratch, (WT*)dw,
+                                                                   rms ? nullptr : (WT*)db, groups, D);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// dtype codes: 0 = fp32, 1 = bf16.  D must be a multiple of 8.
+AX_API int ax_norm_fwd(int rms, int act_dtype, int w_dtype, const void* x, const void* res,
+                       const void* w, const void* b, void* y, void* hout, float* mean, float* rstd,
+                       int rows, int D, float eps, cudaStream_t stream) {
+  if (D % 8 != 0 || rows <= 0) return -1;
+  if (act_dtype == 1 && w_dtype == 1)
+    return launch_fwd<__nv_bfloat16, __nv_bfloat16>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
+  if (act_dtype == 1 && w_dtype == 0)
+    return launch_fwd<__nv_bfloat16, float>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
+  if (act_dtype == 0 && w_dtype == 0)
+    return launch_fwd<float, float>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
+  return -1;
+}
+
+// Number of per-CTA partial slots the backward uses for `rows` rows; scratch must hold
+// groups * 2 * D floats.
+AX_API int ax_norm_bwd_groups(int rows) {
+  int g = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  int cap = axh::sm_count() * 2;
+  if (g > cap) g = cap;
+  return g < 1 ? 1 : g;
+}
+
+AX_API int ax_norm_bwd(int rms, int act_dtype, int w_dtype, const void* dy, const void* x,
+                       const void* w, const float* mean, const float* rstd, const void* dres,
+                       void* dx, void* dw, void* db, float* scratch, int groups, int rows, int D,
+                       cudaStream_t stream) {
+  if (D % 8 != 0 || rows <= 0 || groups <= 0) return -1;
+  if (act_dtype == 1 && w_dtype == 1)
+    return launch_bwd<__nv_bfloat16, __nv_bfloat16>(rms, dy, x, w, mean, rstd, dres, dx, dw, db, scratch, groups, rows, D, stream);
+  if (act_dtype == 1 && w_dtype == 0)
+    return launch_bwd<__nv_bfloat16, float>(rms, dy, x, w, mean, rstd, dres, dx, dw, db, scratch, groups, rows, D, stream);
+  if (act_dtype == 0 && w_dtype == 0)
+    return launch_bwd<float, float>(rms, dy, x, w, mean, rstd, dres, dx, dw, db, scratch, groups, rows, D, stream);
+  return -1;
+}

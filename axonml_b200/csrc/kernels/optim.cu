@@ -1,0 +1,244 @@
+// Multi-tensor fused optimizers.  One launch updates up to kMaxTensors tensors: the kernel
+// parameters carry a table of tensor pointers and a block -> (tensor, chunk) map, so that a whole
+// model is stepped in a handful of launches instead of several per parameter.
+//
+// Every update can (a) multiply the gradient by a device-resident 1/loss-scale, (b) skip itself
+// when a device-resident found-inf flag is set (GradScaler semantics without a host sync), and
+// (c) write a bf16 copy of the updated fp32 master parameter.
+//
+// Update rules follow the reference: SGD crates/axonml-optim/src/sgd.rs:132-198, Adam/AdamW
+// adam.rs:158-234 and :376-445, RMSprop rmsprop.rs:181-250, LAMB lamb.rs:200-280, gradient
+// clipping crates/axonml/src/trainer.rs:413-440, GradScaler unscale grad_scaler.rs:187-206.
+#include "common.cuh"
+
+namespace {
+using namespace ax;
+
+constexpr int kMaxTensors = 24;
+constexpr int kMaxBlocks = 320;
+constexpr int kChunk = 2048 * 32;  // elements per block
+
+struct TensorTable {
+  void* p[kMaxTensors];    // parameter (fp32 or bf16)
+  void* g[kMaxTensors];    // gradient (fp32 or bf16)
+  float* s1[kMaxTensors];  // state 1 (momentum / exp_avg / square_avg)
+  float* s2[kMaxTensors];  // state 2 (exp_avg_sq / momentum buffer)
+  float* s3[kMaxTensors];  // state 3 (amsgrad max / grad_avg / LAMB update)
+  __nv_bfloat16* lp[kMaxTensors];  // optional low-precision copy of p
+  long n[kMaxTensors];
+  int gidx[kMaxTensors];  // index of the tensor in the caller's list (for per-tensor norms)
+  int blk_tensor[kMaxBlocks];
+  int blk_chunk[kMaxBlocks];
+};
+
+struct Hyper {
+  float lr, beta1, beta2, eps, wd, bc1, bc2;  // bc = 1 - beta^t
+  float momentum, dampening, alpha;
+  int nesterov, first_step, adamw, amsgrad, centered;
+  const float* inv_scale;  // may be null
+  const int* found_inf;    // may be null: skip everything when *found_inf != 0
+  float* norms;            // LAMB: [tensor][2] sums of squares; grad-norm: [1]
+  const float* clip_coef;  // optional device scalar multiplied into the gradient
+};
+
+template <typename T> __device__ __forceinline__ float ld(const T* p, long i);
+template <> __device__ __forceinline__ float ld<float>(const float* p, long i) { return p[i]; }
+template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, long i) { return __bfloat162float(p[i]); }
+template <typename T> __device__ __forceinline__ void st(T* p, long i, float v);
+template <> __device__ __forceinline__ void st<float>(float* p, long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, long i, float v) { p[i] = __float2bfloat16(v); }
+
+enum Kind : int { K_SGD = 0, K_ADAM, K_RMSPROP, K_LAMB1, K_LAMB2, K_SUMSQ, K_SCALE, K_UNSCALE_CHECK };
+
+template <int KIND, typename PT, typename GT>
+__global__ void __launch_bounds__(512)
+mt_kernel(const TensorTable tt, const Hyper h) {
+  if (KIND != K_SUMSQ && KIND != K_UNSCALE_CHECK && h.found_inf && *h.found_inf) return;
+  const int t = tt.blk_tensor[blockIdx.x];
+  const long base = (long)tt.blk_chunk[blockIdx.x] * kChunk;
+  const long n = tt.n[t];
+  const long end = base + kChunk < n ? base + kChunk : n;
+  PT* p = (PT*)tt.p[t];
+  GT* g = (GT*)tt.g[t];
+  float* s1 = tt.s1[t];
+  float* s2 = tt.s2[t];
+  float* s3 = tt.s3[t];
+  __nv_bfloat16* lp = tt.lp[t];
+  float gmul = h.inv_scale ? *h.inv_scale : 1.f;
+  if (h.clip_coef) gmul *= *h.clip_coef;
+  float acc0 = 0.f, acc1 = 0.f;
+  int bad = 0;
+  float trust = 1.f;
+  if (KIND == K_LAMB2) {
+    float pn = sqrtf(h.norms[2 * tt.gidx[t]]), rn = sqrtf(h.norms[2 * tt.gidx[t] + 1]);
+    trust = (pn > 0.f && rn > 0.f) ? pn / rn : 1.f;
+  }
+  for (long i = base + threadIdx.x; i < end; i += blockDim.x) {
+    if (KIND == K_SGD) {
+      float w = ld(p, i), gr = ld(g, i) * gmul;
+      gr += h.wd * w;
+      if (h.momentum != 0.f) {
+        float b = h.first_step ? gr : h.momentum * s1[i] + (1.f - h.dampening) * gr;
+        s1[i] = b;
+        gr = h.nesterov ? gr + h.momentum * b : b;
+      }
+      w -= h.lr * gr;
+      st(p, i, w);
+      if (lp) lp[i] = __float2bfloat16(w);
+    } else if (KIND == K_ADAM) {
+      float w = ld(p, i), gr = ld(g, i) * gmul;
+      if (h.adamw) w *= 1.f - h.lr * h.wd; else gr += h.wd * w;
+      float m = h.beta1 * s1[i] + (1.f - h.beta1) * gr;
+      float v = h.beta2 * s2[i] + (1.f - h.beta2) * gr * gr;
+      s1[i] = m; s2[i] = v;
+      float vv = v;
+      if (h.amsgrad) { vv = fmaxf(s3[i], v); s3[i] = vv; }
+      float denom = sqrtf(vv / h.bc2) + h.eps;
+      w -= (h.lr / h.bc1) * m / denom;
+      st(p, i, w);
+      if (lp) lp[i] = __float2bfloat16(w);
+    } else if (KIND == K_RMSPROP) {
+      float w = ld(p, i), gr = ld(g, i) * gmul;
+      gr += h.wd * w;
+      float sq = h.alpha * s1[i] + (1.f - h.alpha) * gr * gr;
+      s1[i] = sq;
+      float avg;
+      if (h.centered) {
+        float ga = h.alpha * s3[i] + (1.f - h.alpha) * gr;
+        s3[i] = ga;
+        avg = sqrtf(fmaxf(sq - ga * ga, 0.f)) + h.eps;
+      } else {
+        avg = sqrtf(sq) + h.eps;
+      }
+      if (h.momentum > 0.f) {
+        float b = h.momentum * s2[i] + gr / avg;
+        s2[i] = b;
+        w -= h.lr * b;
+      } else {
+        w -= h.lr * gr / avg;
+      }
+      st(p, i, w);
+      if (lp) lp[i] = __float2bfloat16(w);
+    } else if (KIND == K_LAMB1) {
+      float w = ld(p, i), gr = ld(g, i) * gmul;
+      float m = h.beta1 * s1[i] + (1.f - h.beta1) * gr;
+      float v = h.beta2 * s2[i] + (1.f - h.beta2) * gr * gr;
+      s1[i] = m; s2[i] = v;
+      float r = (m / h.bc1) / (sqrtf(v / h.bc2) + h.eps) + h.wd * w;
+      s3[i] = r;
+      acc0 += w * w;
+      acc1 += r * r;
+    } else if (KIND == K_LAMB2) {
+      float w = ld(p, i) - h.lr * trust * s3[i];
+      st(p, i, w);
+      if (lp) lp[i] = __float2bfloat16(w);
+    } else if (KIND == K_SUMSQ) {
+      float gr = ld(g, i) * gmul;
+      acc0 += gr * gr;
+    } else if (KIND == K_SCALE) {
+      st(g, i, ld(g, i) * gmul);
+    } else if (KIND == K_UNSCALE_CHECK) {
+      float gr = ld(g, i) * gmul;
+      if (!isfinite(gr)) bad = 1;
+      st(g, i, gr);
+    }
+  }
+  if (KIND == K_LAMB1 || KIND == K_SUMSQ) {
+    __shared__ float r0[16], r1[16];
+    acc0 = warp_sum(acc0);
+    acc1 = warp_sum(acc1);
+    if ((threadIdx.x & 31) == 0) { r0[threadIdx.x >> 5] = acc0; r1[threadIdx.x >> 5] = acc1; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = 0.f, b = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { a += r0[w]; b += r1[w]; }
+      if (KIND == K_LAMB1) {
+        atomicAdd(&h.norms[2 * tt.gidx[t]], a);
+        atomicAdd(&h.norms[2 * tt.gidx[t] + 1], b);
+      } else {
+        atomicAdd(&h.norms[0], a);
+      }
+    }
+  }
+  if (KIND == K_UNSCALE_CHECK) {
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicExch((int*)h.norms, 1);
+  }
+}
+
+template <int KIND>
+int launch_typed(int p_bf16, int g_bf16, const TensorTable& tt, const Hyper& h, int blocks,
+                 cudaStream_t stream) {
+  if (!p_bf16 && !g_bf16) mt_kernel<KIND, float, float><<<blocks, 512, 0, stream>>>(tt, h);
+  else if (!p_bf16 && g_bf16) mt_kernel<KIND, float, __nv_bfloat16><<<blocks, 512, 0, stream>>>(tt, h);
+  else if (p_bf16 && g_bf16) mt_kernel<KIND, __nv_bfloat16, __nv_bfloat16><<<blocks, 512, 0, stream>>>(tt, h);
+  else mt_kernel<KIND, __nv_bfloat16, float><<<blocks, 512, 0, stream>>>(tt, h);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// Generic entry: `kind` selects the update (see Kind).  Pointer arrays have `nt` entries (entries
+// of unused state arrays may be null).  hyper: float[10] = lr, beta1, beta2, eps, wd, bc1, bc2,
+// momentum, dampening, alpha; flags: int[5] = nesterov, first_step, adamw, amsgrad, centered.
+AX_API int ax_multi_tensor(int kind, int p_bf16, int g_bf16, int nt, void** p, void** g, void** s1,
+                           void** s2, void** s3, void** lp, const long* n, const float* hyper,
+                           const int* flags, const float* inv_scale, const int* found_inf,
+                           float* norms, const float* clip_coef, cudaStream_t stream) {
+  Hyper h;
+  h.lr = hyper[0]; h.beta1 = hyper[1]; h.beta2 = hyper[2]; h.eps = hyper[3]; h.wd = hyper[4];
+  h.bc1 = hyper[5]; h.bc2 = hyper[6]; h.momentum = hyper[7]; h.dampening = hyper[8]; h.alpha = hyper[9];
+  h.nesterov = flags[0]; h.first_step = flags[1]; h.adamw = flags[2]; h.amsgrad = flags[3]; h.centered = flags[4];
+  h.inv_scale = inv_scale; h.found_inf = found_inf; h.norms = norms; h.clip_coef = clip_coef;
+
+  TensorTable tt;
+  int nt_in = 0, nb = 0, rc = 0;
+  auto flush = [&]() {
+    if (nb == 0) return 0;
+    int r;
+    switch (kind) {
+      case K_SGD: r = launch_typed<K_SGD>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_ADAM: r = launch_typed<K_ADAM>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_RMSPROP: r = launch_typed<K_RMSPROP>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_LAMB1: r = launch_typed<K_LAMB1>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_LAMB2: r = launch_typed<K_LAMB2>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_SUMSQ: r = launch_typed<K_SUMSQ>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_SCALE: r = launch_typed<K_SCALE>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      case K_UNSCALE_CHECK: r = launch_typed<K_UNSCALE_CHECK>(p_bf16, g_bf16, tt, h, nb, stream); break;
+      default: r = -1;
+    }
+    nb = 0;
+    return r;
+  };
+  for (int t = 0; t < nt; ++t) {
+    if (n[t] <= 0) continue;
+    const long chunks = (n[t] + kChunk - 1) / kChunk;
+    long c = 0;
+    while (c < chunks) {
+      if (nt_in == kMaxTensors || nb == kMaxBlocks) {
+        if ((rc = flush())) return rc;
+        nt_in = 0;
+      }
+      const int slot = nt_in++;
+      tt.p[slot] = p ? p[t] : nullptr;
+      tt.g[slot] = g ? g[t] : nullptr;
+      tt.s1[slot] = s1 ? (float*)s1[t] : nullptr;
+      tt.s2[slot] = s2 ? (float*)s2[t] : nullptr;
+      tt.s3[slot] = s3 ? (float*)s3[t] : nullptr;
+      tt.lp[slot] = lp ? (__nv_bfloat16*)lp[t] : nullptr;
+      tt.n[slot] = n[t];
+      tt.gidx[slot] = t;
+      while (c < chunks && nb < kMaxBlocks) {
+        tt.blk_tensor[nb] = slot;
+        tt.blk_chunk[nb] = (int)c;
+        ++nb;
+        ++c;
+      }
+    }
+  }
+  return flush();
+}
+
+AX_API int ax_multi_tensor_limits(int* max_tensors, int* max_blocks, int* chunk) {
+  *max_tensors = kMaxTensors; *max_blocks = kMaxBlocks; *chunk = kChunk;
+  return 0;
+}

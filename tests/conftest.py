@@ -1,0 +1,37 @@
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    config.addinivalue_line("markers", "multigpu: needs two or more CUDA devices")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _seed():
+    torch.manual_seed(1234)
+    yield
+
+
+@pytest.fixture
+def kernel_status():
+    """Checks after the test that no kernel recorded a bounded-wait timeout."""
+    yield
+    if torch.cuda.is_available():
+        from axonml_b200 import _native
+        torch.cuda.synchronize()
+        _native.check_status()

@@ -1,0 +1,304 @@
+"""Numerics of the hand-written sm_100a kernels against plain PyTorch fp32 references.
+
+Mirrors the reference's CPU-vs-GPU harness (crates/axonml-core/src/backends/gpu_tests.rs:221-367):
+deterministic inputs, a sweep of sizes that includes ragged tails, absolute + relative tolerance.
+"""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def close(a, b, atol, rtol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    lim = atol + rtol * b.abs()
+    assert bool((err <= lim).all()), f"max err {err.max().item():.4g} (limit {lim.max().item():.4g})"
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 136), (1024, 1024, 1024), (8, 8, 8),
+                                   (4096, 512, 2048)])
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+def test_gemm_layouts(M, N, K, ta, tb, kernel_status):
+    from axonml_b200.ops.gemm import gemm_bf16
+    a = torch.randn((K, M) if ta else (M, K), device=DEV).bfloat16()
+    b = torch.randn((N, K) if tb else (K, N), device=DEV).bfloat16()
+    c = gemm_bf16(a, b, trans_a=ta, trans_b=tb)
+    A = a.float().t() if ta else a.float()
+    B = b.float().t() if tb else b.float()
+    ref = A @ B
+    close(c, ref, atol=0.02 * (K ** 0.5), rtol=2e-2)
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "silu", "sigmoid", "tanh"])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_epilogue(act, bn, kernel_status):
+    from axonml_b200.ops.gemm import gemm_bf16
+    M, N, K = 384, 512, 256
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    y, z = gemm_bf16(a, w, bias=bias, act=act, want_aux=True, bn=bn)
+    zr = a.float() @ w.float().t() + bias
+    fn = {"none": lambda t: t, "relu": torch.relu, "gelu": lambda t: F.gelu(t, approximate="tanh"),
+          "silu": F.silu, "sigmoid": torch.sigmoid, "tanh": torch.tanh}[act]
+    close(z, zr, 2e-2, 2e-2)
+    close(y, fn(zr), 2e-2, 2e-2)
+
+
+def test_linear_autograd(kernel_status):
+    from axonml_b200.ops.linear import linear
+    x = torch.randn(4, 96, 256, device=DEV).bfloat16().requires_grad_()
+    w = (torch.randn(512, 256, device=DEV) / 16).bfloat16().requires_grad_()
+    b = torch.randn(512, device=DEV).bfloat16().requires_grad_()
+    y = linear(x, w, b, "gelu")
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = F.gelu(F.linear(xr, wr, br), approximate="tanh")
+    yr.backward(g.float())
+    close(y, yr, 3e-2, 3e-2)
+    close(x.grad, xr.grad, 5e-2, 5e-2)
+    close(w.grad, wr.grad, 0.3, 5e-2)
+    close(b.grad, br.grad, 0.3, 5e-2)
+
+
+# ------------------------------------------------------------------ norms
+@pytest.mark.parametrize("rows,D", [(1, 8), (7, 64), (33, 256), (512, 2048), (100, 4096), (64, 1000)])
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_fwd_bwd(rows, D, rms, dtype):
+    from axonml_b200.ops.norm import layer_norm, rms_norm
+    x = torch.randn(rows, D, device=DEV).to(dtype).requires_grad_()
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(dtype).requires_grad_()
+    b = (0.1 * torch.randn(D, device=DEV)).to(dtype).requires_grad_()
+    y = rms_norm(x, w, 1e-5) if rms else layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    if rms:
+        yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    else:
+        yr = F.layer_norm(xr, (D,), wr, br, 1e-5)
+    yr.backward(g.float())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    close(y, yr, tol, tol)
+    close(x.grad, xr.grad, tol, tol)
+    wt = 1e-3 if dtype == torch.float32 else 0.05 * rows ** 0.5
+    close(w.grad, wr.grad, wt, 2e-2)
+    if not rms:
+        close(b.grad, br.grad, wt, 2e-2)
+
+
+def test_norm_residual():
+    from axonml_b200.ops.norm import layer_norm
+    x = torch.randn(64, 512, device=DEV).bfloat16().requires_grad_()
+    r = torch.randn(64, 512, device=DEV).bfloat16().requires_grad_()
+    w = torch.ones(512, device=DEV).bfloat16().requires_grad_()
+    b = torch.zeros(512, device=DEV).bfloat16().requires_grad_()
+    y, h = layer_norm(x, w, b, 1e-5, residual=r)
+    (y.float().sum() + (h.float() ** 2).sum()).backward()
+    xr, rr = x.detach().float().requires_grad_(), r.detach().float().requires_grad_()
+    hr = (xr + rr)
+    yr = F.layer_norm(hr, (512,))
+    (yr.sum() + (hr ** 2).sum()).backward()
+    close(h, hr, 2e-2, 2e-2)
+    close(y, yr, 3e-2, 3e-2)
+    close(x.grad, xr.grad, 0.1, 5e-2)
+    close(r.grad, rr.grad, 0.1, 5e-2)
+
+
+# ------------------------------------------------------------------ softmax / CE
+@pytest.mark.parametrize("rows,V", [(1, 1), (7, 10), (16, 1000), (64, 50257), (4, 128256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cross_entropy(rows, V, dtype):
+    from axonml_b200.ops.loss import cross_entropy
+    Vpad = (V + 127) // 128 * 128
+    logits = (3 * torch.randn(rows, Vpad, device=DEV)).to(dtype).requires_grad_()
+    t = torch.randint(0, V, (rows,), device=DEV)
+    if rows > 4:
+        t[1] = -100
+    loss = cross_entropy(logits, t, valid_classes=V)
+    loss.backward()
+    lr = logits.detach().float().requires_grad_()
+    ref = F.cross_entropy(lr[:, :V], t, ignore_index=-100)
+    ref.backward()
+    tol = 1e-4 if dtype == torch.float32 else 1e-2
+    close(loss, ref, tol, tol)
+    close(logits.grad, lr.grad, tol / 10, tol)
+
+
+@pytest.mark.parametrize("log", [False, True])
+@pytest.mark.parametrize("shape,dim", [((4, 7), -1), ((3, 5, 64), 1), ((16, 4096), -1)])
+def test_softmax(shape, dim, log):
+    from axonml_b200.ops.loss import softmax
+    x = torch.randn(*shape, device=DEV).requires_grad_()
+    y = softmax(x, dim, log=log)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().clone().requires_grad_()
+    yr = F.log_softmax(xr, dim) if log else F.softmax(xr, dim)
+    yr.backward(g)
+    close(y, yr, 1e-5, 1e-4)
+    close(x.grad, xr.grad, 1e-5, 1e-3)
+
+
+# ------------------------------------------------------------------ elementwise set
+@pytest.mark.parametrize("n", [1, 7, 16, 64, 256, 1024, 4096, 100003])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_elementwise_set(n, dtype):
+    from axonml_b200.ops import elementwise as E
+    x = torch.randn(n, device=DEV).to(dtype)
+    y = torch.randn(n, device=DEV).to(dtype)
+    tol = dict(atol=1e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    approx = dict(atol=1e-3, rtol=1e-2) if dtype == torch.float32 else tol
+    for op in ("add", "sub", "mul", "max", "min"):
+        close(E.binary(x, y, op), E._binary_ref(x.float(), y.float(), op, 0.0), **tol)
+    close(E.binary(x, y.abs() + 0.5, "div"), x.float() / (y.float().abs() + 0.5), **approx)
+    for op, p0, p1 in (("neg", 0, 0), ("abs", 0, 0), ("relu", 0, 0), ("scale", 2.5, 0),
+                       ("add_scalar", -1.25, 0), ("clamp", -0.5, 0.5), ("square", 0, 0),
+                       ("leaky_relu", 0.01, 0)):
+        close(E.unary(x, op, p0, p1), E._UNARY_REF[op](x.float(), p0, p1), **tol)
+    for op, p0 in (("sigmoid", 0), ("tanh", 0), ("gelu", 0), ("silu", 0), ("elu", 1.0), ("exp", 0)):
+        close(E.unary(x, op, p0), E._UNARY_REF[op](x.float(), p0, 0), **approx)
+    xp = x.abs() + 0.1
+    for op in ("sqrt", "log", "rsqrt"):
+        close(E.unary(xp, op), E._UNARY_REF[op](xp.float(), 0, 0), **approx)
+    for act in ("relu", "gelu", "silu"):
+        close(E.act_backward(y, x, act), E._binary_ref(y.float(), x.float(), act + "_bwd", 0.0), **approx)
+
+
+def test_swiglu_and_colsum():
+    from axonml_b200.ops import elementwise as E
+    gu = torch.randn(37, 2 * 256, device=DEV).bfloat16().requires_grad_()
+    out = E.swiglu(gu)
+    g = torch.randn_like(out)
+    out.backward(g)
+    gr = gu.detach().float().requires_grad_()
+    a, b = gr.split(256, -1)
+    ref = F.silu(a) * b
+    ref.backward(g.float())
+    close(out, ref, 2e-2, 2e-2)
+    close(gu.grad, gr.grad, 3e-2, 3e-2)
+    x = torch.randn(3000, 520, device=DEV).bfloat16()
+    close(E.colsum(x), x.float().sum(0), 1e-2, 1e-3)
+
+
+def test_dropout():
+    from axonml_b200.ops import elementwise as E
+    x = torch.ones(1 << 20, device=DEV, requires_grad=True)
+    y = E.dropout(x, 0.25, True)
+    keep = (y != 0).float().mean().item()
+    assert abs(keep - 0.75) < 0.01
+    assert torch.allclose(y[y != 0], torch.full_like(y[y != 0], 1 / 0.75))
+    y.sum().backward()
+    assert torch.equal(x.grad != 0, y != 0)
+
+
+# ------------------------------------------------------------------ embedding / rope
+def test_embedding_and_rope():
+    from axonml_b200.ops import misc as Mi
+    V, D, B, S = 1000, 256, 3, 17
+    W = torch.randn(V, D, device=DEV).bfloat16().requires_grad_()
+    P = torch.randn(64, D, device=DEV).bfloat16().requires_grad_()
+    idx = torch.randint(0, V, (B, S), device=DEV)
+    out = Mi.embedding(idx, W, pos_weight=P, seq_len=S)
+    g = torch.randn_like(out)
+    out.backward(g)
+    Wr, Pr = W.detach().float().requires_grad_(), P.detach().float().requires_grad_()
+    ref = F.embedding(idx, Wr) + Pr[:S][None]
+    ref.backward(g.float())
+    close(out, ref, 2e-2, 2e-2)
+    close(W.grad, Wr.grad, 5e-2, 2e-2)
+    close(P.grad, Pr.grad, 5e-2, 2e-2)
+
+    H, hd = 4, 128
+    cos, sin = Mi.rope_tables(64, hd, 500000.0, device=DEV)
+    x = torch.randn(B, S, H, hd, device=DEV).bfloat16().requires_grad_()
+    y = Mi.rope(x, cos, sin, seq_len=S)
+    y.backward(torch.ones_like(y))
+    xr = x.detach().float().requires_grad_()
+    c, s = cos[:S].view(1, S, 1, hd // 2), sin[:S].view(1, S, 1, hd // 2)
+    a, b = xr[..., :hd // 2], xr[..., hd // 2:]
+    yr = torch.cat([a * c - b * s, b * c + a * s], -1)
+    yr.backward(torch.ones_like(yr))
+    close(y, yr, 2e-2, 2e-2)
+    close(x.grad, xr.grad, 2e-2, 2e-2)
+
+
+# ------------------------------------------------------------------ fused optimizers
+@pytest.mark.parametrize("kind", ["sgd", "adam", "adamw", "rmsprop", "lamb"])
+def test_multi_tensor_optimizers(kind):
+    from axonml_b200.ops import optim as O
+    shapes = [(5,), (33, 7), (70000,), (256, 300)] * 9  # > 24 tensors and > 1 chunk
+    ps = [torch.randn(s, device=DEV) for s in shapes]
+    gs = [torch.randn(s, device=DEV) for s in shapes]
+    ref_p = [p.clone().requires_grad_() for p in ps]
+    for p, g in zip(ref_p, gs):
+        p.grad = g.clone()
+    z = lambda: [torch.zeros_like(p) for p in ps]
+    if kind == "sgd":
+        opt = torch.optim.SGD(ref_p, lr=0.1, momentum=0.9, weight_decay=0.01, nesterov=True)
+        s1 = z()
+        for step in range(2):
+            opt.step()
+            O.multi_tensor("sgd", ps, gs, s1, lr=0.1, momentum=0.9, wd=0.01, nesterov=True,
+                           first_step=(step == 0))
+    elif kind in ("adam", "adamw"):
+        cls = torch.optim.AdamW if kind == "adamw" else torch.optim.Adam
+        opt = cls(ref_p, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+        s1, s2 = z(), z()
+        for step in range(1, 3):
+            opt.step()
+            O.multi_tensor("adam", ps, gs, s1, s2, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1,
+                           bc1=1 - 0.9 ** step, bc2=1 - 0.95 ** step, adamw=(kind == "adamw"))
+    elif kind == "rmsprop":
+        opt = torch.optim.RMSprop(ref_p, lr=1e-2, alpha=0.99, eps=1e-8, momentum=0.5, centered=True)
+        s1, s2, s3 = z(), z(), z()
+        for step in range(2):
+            opt.step()
+            O.multi_tensor("rmsprop", ps, gs, s1, s2, s3, lr=1e-2, alpha=0.99, eps=1e-8,
+                           momentum=0.5, centered=True)
+    else:
+        s1, s2, s3 = z(), z(), z()
+        m = [torch.zeros_like(p) for p in ps]
+        v = [torch.zeros_like(p) for p in ps]
+        for step in range(1, 3):
+            norms = torch.zeros(2 * len(ps), device=DEV)
+            hp = dict(lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-6, wd=0.01, bc1=1 - 0.9 ** step,
+                      bc2=1 - 0.999 ** step)
+            O.multi_tensor("lamb1", ps, gs, s1, s2, s3, norms=norms, **hp)
+            O.multi_tensor("lamb2", ps, gs, s1, s2, s3, norms=norms, **hp)
+            with torch.no_grad():
+                for i, (p, g) in enumerate(zip(ref_p, gs)):
+                    m[i] = 0.9 * m[i] + 0.1 * g
+                    v[i] = 0.999 * v[i] + 0.001 * g * g
+                    r = (m[i] / hp["bc1"]) / ((v[i] / hp["bc2"]).sqrt() + 1e-6) + 0.01 * p
+                    pn, rn = p.norm(), r.norm()
+                    trust = pn / rn if pn > 0 and rn > 0 else 1.0
+                    p -= 1e-2 * trust * r
+    for p, r in zip(ps, ref_p):
+        close(p, r.detach(), 1e-5, 1e-4)
+
+
+def test_grad_sumsq_and_unscale():
+    from axonml_b200.ops import optim as O
+    gs = [torch.randn(n, device=DEV).bfloat16() for n in (3, 1000, 70001)]
+    ss = O.grad_sumsq(gs)
+    ref = sum((g.float() ** 2).sum() for g in gs)
+    close(ss[0], ref, 1e-2, 1e-3)
+    inv = torch.tensor([0.5], device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    fg = [torch.randn(100, device=DEV), torch.randn(5, device=DEV)]
+    want = [g * 0.5 for g in fg]
+    O.multi_tensor("unscale_check", None, fg, inv_scale=inv, norms=flag)
+    assert flag.item() == 0
+    for a, b in zip(fg, want):
+        close(a, b, 1e-6, 1e-6)
+    fg[1][2] = float("inf")
+    O.multi_tensor("unscale_check", None, fg, inv_scale=inv, norms=flag)
+    assert flag.item() == 1
