@@ -1,0 +1,9 @@
+"""Autodiff facade over ``torch.autograd`` with the reference's names (crates/axonml-autograd):
+``Variable``, ``backward``, ``no_grad`` / ``enable_grad`` / ``inference_mode``, ``amp.autocast``,
+``checkpoint`` / ``checkpoint_sequential`` (real recomputation; the reference's version only runs
+under no_grad, checkpoint.rs:70-95), ``numerical_gradient`` / ``gradcheck``."""
+from .amp import AutocastGuard, AutocastPolicy, autocast, disable_autocast, is_autocast_enabled
+from .checkpoint import checkpoint, checkpoint_sequential
+from .grad_mode import (enable_grad, inference_mode, is_grad_enabled, is_inference_mode, no_grad,
+                        set_grad_enabled_context)
+from .variable import Variable, backward, gradcheck, numerical_gradient

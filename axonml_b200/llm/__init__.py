@@ -1,0 +1,7 @@
+"""Language models and generation (crates/axonml-llm)."""
+from .attention import FlashAttention, KVCache, LayerKVCache, scaled_dot_product_attention
+from .config import BertConfig, GPT2Config, LLaMAConfig, MistralConfig, PhiConfig
+from .generation import BeamSearch, GenerationConfig, TextGenerator
+from .gpt2 import GPT2, CausalSelfAttention, FeedForward, GPT2Embedding, GPT2LMHead, TransformerBlock
+from .llama import (LLaMA, LLaMAAttention, LLaMADecoderLayer, LLaMAForCausalLM, LLaMAMLP,
+                    RotaryEmbedding)

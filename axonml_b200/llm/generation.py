@@ -1,0 +1,134 @@
+"""Text generation (crates/axonml-llm/src/generation.rs:11-395): ``GenerationConfig`` with its
+presets, ``TextGenerator`` (repetition penalty -> temperature -> top-k -> top-p -> sample or
+argmax) and ``BeamSearch``.  Sampling is real (the reference's ``generate`` is always greedy)."""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+
+@dataclasses.dataclass
+class GenerationConfig:
+    max_new_tokens: int = 50
+    temperature: float = 1.0
+    top_k: int | None = None
+    top_p: float | None = None
+    repetition_penalty: float = 1.0
+    eos_token_ids: list = dataclasses.field(default_factory=list)
+    pad_token_id: int | None = None
+    do_sample: bool = True
+    num_beams: int = 1
+    length_penalty: float = 1.0
+    early_stopping: bool = False
+
+    @classmethod
+    def greedy(cls, max_new_tokens: int = 50): return cls(max_new_tokens=max_new_tokens, do_sample=False)
+    @classmethod
+    def sampling(cls, max_new_tokens: int = 50, temperature: float = 1.0):
+        return cls(max_new_tokens=max_new_tokens, temperature=temperature)
+    @classmethod
+    def top_k_sampling(cls, max_new_tokens: int, k: int, temperature: float = 1.0):
+        return cls(max_new_tokens=max_new_tokens, top_k=k, temperature=temperature)
+    @classmethod
+    def nucleus_sampling(cls, max_new_tokens: int, p: float, temperature: float = 1.0):
+        return cls(max_new_tokens=max_new_tokens, top_p=p, temperature=temperature)
+    @classmethod
+    def beam_search(cls, max_new_tokens: int, num_beams: int):
+        return cls(max_new_tokens=max_new_tokens, num_beams=num_beams, do_sample=False)
+
+
+class TextGenerator:
+    def __init__(self, config: GenerationConfig | None = None):
+        self.config = config or GenerationConfig()
+
+    @classmethod
+    def new(cls, config): return cls(config)
+
+    def process_logits(self, logits: torch.Tensor, generated: torch.Tensor | None = None) -> torch.Tensor:
+        """``logits [B, V]`` -> filtered logits (fp32)."""
+        c = self.config
+        logits = logits.float().clone()
+        if c.repetition_penalty != 1.0 and generated is not None and generated.numel():
+            score = torch.gather(logits, 1, generated)
+            score = torch.where(score > 0, score / c.repetition_penalty, score * c.repetition_penalty)
+            logits.scatter_(1, generated, score)
+        if c.temperature != 1.0 and c.temperature > 0:
+            logits = logits / c.temperature
+        if c.top_k is not None and 0 < c.top_k < logits.shape[-1]:
+            kth = torch.topk(logits, c.top_k, dim=-1).values[..., -1:]
+            logits = logits.masked_fill(logits < kth, float("-inf"))
+        if c.top_p is not None and 0.0 < c.top_p < 1.0:
+            sl, si = torch.sort(logits, descending=True, dim=-1)
+            cum = torch.softmax(sl, -1).cumsum(-1)
+            remove = cum - torch.softmax(sl, -1) > c.top_p
+            sl = sl.masked_fill(remove, float("-inf"))
+            logits = torch.full_like(logits, float("-inf")).scatter(1, si, sl)
+        return logits
+
+    def sample(self, logits: torch.Tensor, generated=None) -> torch.Tensor:
+        logits = self.process_logits(logits, generated)
+        if self.config.do_sample:
+            return torch.multinomial(torch.softmax(logits, -1), 1).squeeze(-1)
+        return logits.argmax(-1)
+
+    @torch.no_grad()
+    def generate(self, model, ids: torch.Tensor) -> torch.Tensor:
+        """Autoregressive decode with the model's KV cache when it offers one."""
+        c = self.config
+        if c.num_beams > 1:
+            return BeamSearch(c.num_beams, c.length_penalty, c.early_stopping).search(model, ids, c)
+        caches = model.create_kv_cache(ids.shape[0], ids.shape[1] + c.max_new_tokens) if hasattr(model, "create_kv_cache") else None
+        out = ids
+        done = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
+        step_in, pos0 = ids, 0
+        for _ in range(c.max_new_tokens):
+            if caches is not None:
+                logits = model(step_in, caches, pos0) if _takes_pos(model) else model(step_in, caches)
+                pos0 += step_in.shape[1]
+            else:
+                logits = model(out)
+            nxt = self.sample(logits[:, -1], out)
+            if c.eos_token_ids:
+                if c.pad_token_id is not None:
+                    nxt = torch.where(done, torch.full_like(nxt, c.pad_token_id), nxt)
+                done = done | torch.isin(nxt, torch.tensor(c.eos_token_ids, device=nxt.device))
+            out = torch.cat([out, nxt[:, None]], dim=1)
+            step_in = nxt[:, None]
+            if c.eos_token_ids and bool(done.all()):
+                break
+        return out
+
+
+def _takes_pos(model) -> bool:
+    import inspect
+    try:
+        return "pos0" in inspect.signature(model.forward).parameters
+    except (TypeError, ValueError):
+        return False
+
+
+class BeamSearch:
+    def __init__(self, num_beams: int, length_penalty: float = 1.0, early_stopping: bool = False):
+        self.num_beams, self.length_penalty, self.early_stopping = num_beams, length_penalty, early_stopping
+
+    @torch.no_grad()
+    def search(self, model, ids: torch.Tensor, config: GenerationConfig) -> torch.Tensor:
+        """Beam search for batch size 1 (as in the reference); returns the best sequence."""
+        beams = [(ids[:1], 0.0, False)]
+        eos = set(config.eos_token_ids)
+        for _ in range(config.max_new_tokens):
+            cand = []
+            for seq, score, fin in beams:
+                if fin:
+                    cand.append((seq, score, True))
+                    continue
+                lp = torch.log_softmax(model(seq)[:, -1].float(), -1)[0]
+                top = torch.topk(lp, self.num_beams)
+                for v, i in zip(top.values.tolist(), top.indices.tolist()):
+                    cand.append((torch.cat([seq, torch.tensor([[i]], device=seq.device)], 1), score + v, i in eos))
+            cand.sort(key=lambda c: c[1] / (c[0].shape[1] ** self.length_penalty), reverse=True)
+            beams = cand[: self.num_beams]
+            if all(b[2] for b in beams) or (self.early_stopping and beams[0][2]):
+                break
+        return beams[0][0]

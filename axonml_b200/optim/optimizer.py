@@ -1,0 +1,116 @@
+"""Optimizer base class.  Reference trait: crates/axonml-optim/src/optimizer.rs:17-39
+(``step, zero_grad, get_lr, set_lr, parameters, num_parameters``).  Unlike the reference the
+optimizers carry a ``state_dict`` so that checkpoints restore momentum / Adam moments.
+
+On CUDA every step is a multi-tensor fused kernel (``ops.optim``): parameters are grouped by
+(param dtype, grad dtype) and updated in a handful of launches, with the GradScaler's 1/scale and
+found-inf flag read from device memory.  On CPU the same formulas run as torch expressions."""
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+
+from ..ops import optim as O
+
+
+class Optimizer:
+    def __init__(self, params: Iterable[torch.Tensor], lr: float):
+        self.params = [p for p in params]
+        if not self.params:
+            raise ValueError("optimizer got an empty parameter list")
+        self.lr = float(lr)
+        self.state: dict[int, dict] = {}
+        self._step_count = 0
+        # set by GradScaler.step(): device tensors read by the fused kernels
+        self._inv_scale = None
+        self._found_inf = None
+
+    # ---- reference trait
+    def step(self) -> None:  # pragma: no cover - abstract
+        raise NotImplementedError
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.params:
+            if p.grad is not None:
+                if set_to_none:
+                    p.grad = None
+                else:
+                    p.grad.zero_()
+
+    def get_lr(self) -> float:
+        return self.lr
+
+    def set_lr(self, lr: float) -> None:
+        self.lr = float(lr)
+
+    def parameters(self):
+        return self.params
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.params)
+
+    # torch-style view used by the schedulers
+    @property
+    def param_groups(self):
+        return [{"params": self.params, "lr": self.lr}]
+
+    # ---- helpers
+    def _state(self, p, names):
+        st = self.state.get(id(p))
+        if st is None:
+            st = {n: torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+                  for n in names}
+            self.state[id(p)] = st
+        else:
+            for n in names:
+                if n not in st:
+                    st[n] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
+        return st
+
+    def _active(self):
+        return [p for p in self.params if p.grad is not None]
+
+    def _groups(self, ps):
+        """Splits into lists the fused kernel can take plus a remainder for the torch path."""
+        fused: dict[tuple, list] = {}
+        rest = []
+        for p in ps:
+            g = p.grad
+            if (p.is_cuda and O.supported([p], [g]) and not g.is_sparse):
+                fused.setdefault((p.dtype, g.dtype, p.device), []).append(p)
+            else:
+                rest.append(p)
+        return list(fused.values()), rest
+
+    def _skip(self) -> bool:
+        """CPU-side found-inf check for the torch path."""
+        return self._found_inf is not None and bool(self._found_inf.item())
+
+    def _grad(self, p):
+        g = p.grad.float()
+        if self._inv_scale is not None:
+            g = g * self._inv_scale.to(g.device)
+        return g
+
+    # ---- state dict
+    def state_dict(self) -> dict:
+        out = {"lr": self.lr, "step": self._step_count, "state": {}, "hyper": self._hyper()}
+        for i, p in enumerate(self.params):
+            st = self.state.get(id(p))
+            if st:
+                out["state"][i] = {k: v.detach().clone() if torch.is_tensor(v) else v for k, v in st.items()}
+        return out
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.lr = float(sd.get("lr", self.lr))
+        self._step_count = int(sd.get("step", 0))
+        for i, st in sd.get("state", {}).items():
+            p = self.params[int(i)]
+            self.state[id(p)] = {k: (v.to(p.device) if torch.is_tensor(v) else v) for k, v in st.items()}
+        for k, v in sd.get("hyper", {}).items():
+            if hasattr(self, k):
+                setattr(self, k, v)
+
+    def _hyper(self) -> dict:
+        return {}
