@@ -37,14 +37,44 @@ def _load(name: str, builder: str):
     return ctypes.CDLL(str(path))
 
 
+class _CountingLib:
+    """Forwards attribute access to the ctypes library and counts calls of the kernel launchers
+    (every ``ax_*`` entry that takes a stream launches at least one kernel)."""
+
+    _NO_LAUNCH = {"ax_version", "ax_sm_count", "ax_norm_bwd_groups", "ax_multi_tensor_limits"}
+
+    def __init__(self, lib):
+        self._lib = lib
+        self._cache = {}
+        self.launches = 0
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._lib, name)
+            if name in self._NO_LAUNCH:
+                fn = raw
+            else:
+                def fn(*args, _raw=raw):
+                    self.launches += 1
+                    return _raw(*args)
+            self._cache[name] = fn
+        return fn
+
+
 def cuda():
     """Handle of the CUDA kernel library (built for sm_100a)."""
     global _CUDA
     if _CUDA is None:
         with _LOCK:
             if _CUDA is None:
-                _CUDA = _load("libaxonml_cuda.so", "build_cuda")
+                _CUDA = _CountingLib(_load("libaxonml_cuda.so", "build_cuda"))
     return _CUDA
+
+
+def launch_count() -> int:
+    """Number of native launcher calls made so far in this process."""
+    return _CUDA.launches if _CUDA is not None else 0
 
 
 def host():

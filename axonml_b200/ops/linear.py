@@ -37,7 +37,8 @@ def _use_kernel(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, b, act):
+    def forward(ctx, x, w, b, act, sink=None):
+        ctx.sink = sink
         x2 = x.reshape(-1, x.shape[-1])
         need_z = act != "none" and (x.requires_grad or w.requires_grad)
         if need_z:
@@ -65,10 +66,19 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm_bf16(dz, w, trans_b=False).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm_bf16(dz, x2, trans_a=True, trans_b=False)
+            sink = ctx.sink
+            if sink is not None and sink.target().dtype == torch.bfloat16:
+                # write the weight gradient straight into the sharded engine's flat buffer
+                if sink.first_write():
+                    gemm_bf16(dz, x2, trans_a=True, trans_b=False, out=sink.target())
+                else:
+                    sink.target().add_(gemm_bf16(dz, x2, trans_a=True, trans_b=False))
+                sink.done()
+            else:
+                dw = gemm_bf16(dz, x2, trans_a=True, trans_b=False)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = E.colsum(dz).to(ctx.bias_dtype)
-        return dx, dw, db, None
+        return dx, dw, db, None, None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
@@ -78,7 +88,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     if _use_kernel(x, weight):
         if bias is not None and bias.dtype not in (torch.float32, torch.bfloat16):
             bias = bias.float()
-        return _LinearFn.apply(x, weight, bias, act)
+        return _LinearFn.apply(x, weight, bias, act, getattr(weight, "_axon_grad_sink", None))
     if x.is_cuda and N.is_blackwell() and torch.is_autocast_enabled():
         # autocast region with fp32 parameters: cast once, then take the kernel path
         dt = torch.get_autocast_dtype("cuda")

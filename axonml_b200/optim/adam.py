@@ -53,10 +53,10 @@ class Adam(Optimizer):
         fused, rest = self._groups(self._active())
         for grp in fused:
             sts = [self._state(p, names) for p in grp]
-            O.multi_tensor("adam", grp, [p.grad for p in grp], [s["exp_avg"] for s in sts],
+            O.multi_tensor("adam", grp, [self._g(p) for p in grp], [s["exp_avg"] for s in sts],
                            [s["exp_avg_sq"] for s in sts],
                            [s["max_exp_avg_sq"] for s in sts] if self._amsgrad else None,
-                           lr=self.lr, beta1=b1, beta2=b2, eps=self._eps, wd=self._weight_decay,
+                           lp=self._lp(grp), lr=self.lr, beta1=b1, beta2=b2, eps=self._eps, wd=self._weight_decay,
                            bc1=bc1, bc2=bc2, adamw=self._DECOUPLED, amsgrad=self._amsgrad,
                            inv_scale=self._inv_scale, found_inf=self._found_inf)
         if rest and self._skip():
@@ -78,7 +78,7 @@ class Adam(Optimizer):
                 torch.maximum(st["max_exp_avg_sq"], v, out=st["max_exp_avg_sq"])
                 vv = st["max_exp_avg_sq"]
             denom = (vv / bc2).sqrt() + self._eps
-            p.copy_((pf - (self.lr / bc1) * m / denom).to(p.dtype))
+            self._write(p, (pf - (self.lr / bc1) * m / denom).to(p.dtype))
 
 
 class AdamW(Adam):

@@ -46,9 +46,9 @@ class LAMB(Optimizer):
         for grp in fused:
             sts = [self._state(p, names) for p in grp]
             norms = torch.zeros(2 * len(grp), dtype=torch.float32, device=grp[0].device)
-            hp = dict(lr=self.lr, beta1=b1, beta2=b2, eps=self._eps, wd=self._weight_decay, bc1=bc1,
+            hp = dict(lp=self._lp(grp), lr=self.lr, beta1=b1, beta2=b2, eps=self._eps, wd=self._weight_decay, bc1=bc1,
                       bc2=bc2, inv_scale=self._inv_scale, found_inf=self._found_inf, norms=norms)
-            args = (grp, [p.grad for p in grp], [s["exp_avg"] for s in sts],
+            args = (grp, [self._g(p) for p in grp], [s["exp_avg"] for s in sts],
                     [s["exp_avg_sq"] for s in sts], [s["update"] for s in sts])
             O.multi_tensor("lamb1", *args, **hp)
             O.multi_tensor("lamb2", *args, **hp)
@@ -65,4 +65,4 @@ class LAMB(Optimizer):
             r = (m / bc1) / ((v / bc2).sqrt() + self._eps) + self._weight_decay * pf
             pn, rn = pf.norm(), r.norm()
             trust = (pn / rn).item() if pn > 0 and rn > 0 else 1.0
-            p.copy_((pf - self.lr * trust * r).to(p.dtype))
+            self._write(p, (pf - self.lr * trust * r).to(p.dtype))

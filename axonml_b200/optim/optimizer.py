@@ -32,6 +32,8 @@ class Optimizer:
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         for p in self.params:
+            if getattr(p, "_axon_grad", None) is not None:
+                p._axon_grad = None
             if p.grad is not None:
                 if set_to_none:
                     p.grad = None
@@ -68,17 +70,37 @@ class Optimizer:
                     st[n] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.contiguous_format)
         return st
 
+    @staticmethod
+    def _g(p):
+        """Gradient of ``p``: a sharded engine may attach it as ``_axon_grad`` (it can have a
+        different dtype than the master parameter, which ``.grad`` does not allow)."""
+        g = getattr(p, "_axon_grad", None)
+        return g if g is not None else p.grad
+
+    @staticmethod
+    def _lp(grp):
+        """Low-precision mirrors the kernel refreshes together with the fp32 parameters."""
+        lps = [getattr(p, "_axon_lp", None) for p in grp]
+        return lps if any(l is not None for l in lps) else None
+
+    @staticmethod
+    def _write(p, new) -> None:
+        p.copy_(new)
+        lp = getattr(p, "_axon_lp", None)
+        if lp is not None:
+            lp.copy_(p)
+
     def _active(self):
-        return [p for p in self.params if p.grad is not None]
+        return [p for p in self.params if self._g(p) is not None]
 
     def _groups(self, ps):
         """Splits into lists the fused kernel can take plus a remainder for the torch path."""
         fused: dict[tuple, list] = {}
         rest = []
         for p in ps:
-            g = p.grad
+            g = self._g(p)
             if (p.is_cuda and O.supported([p], [g]) and not g.is_sparse):
-                fused.setdefault((p.dtype, g.dtype, p.device), []).append(p)
+                fused.setdefault((p.dtype, g.dtype, p.device, getattr(p, '_axon_lp', None) is not None), []).append(p)
             else:
                 rest.append(p)
         return list(fused.values()), rest
@@ -88,7 +110,7 @@ class Optimizer:
         return self._found_inf is not None and bool(self._found_inf.item())
 
     def _grad(self, p):
-        g = p.grad.float()
+        g = self._g(p).float()
         if self._inv_scale is not None:
             g = g * self._inv_scale.to(g.device)
         return g

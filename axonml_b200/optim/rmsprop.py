@@ -41,9 +41,9 @@ class RMSprop(Optimizer):
         fused, rest = self._groups(self._active())
         for grp in fused:
             sts = [self._state(p, names) for p in grp]
-            O.multi_tensor("rmsprop", grp, [p.grad for p in grp], [s["square_avg"] for s in sts],
+            O.multi_tensor("rmsprop", grp, [self._g(p) for p in grp], [s["square_avg"] for s in sts],
                            [s["momentum_buffer"] for s in sts], [s["grad_avg"] for s in sts],
-                           lr=self.lr, alpha=self._alpha, eps=self._eps, wd=self._weight_decay,
+                           lp=self._lp(grp), lr=self.lr, alpha=self._alpha, eps=self._eps, wd=self._weight_decay,
                            momentum=self._momentum, centered=self._centered,
                            inv_scale=self._inv_scale, found_inf=self._found_inf)
         if rest and not self._skip():
@@ -67,5 +67,5 @@ class RMSprop(Optimizer):
                     pf = pf - self.lr * buf
                 else:
                     pf = pf - self.lr * g / avg
-                p.copy_(pf.to(p.dtype))
+                self._write(p, pf.to(p.dtype))
         self._step_count += 1

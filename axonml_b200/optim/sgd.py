@@ -53,7 +53,7 @@ class SGD(Optimizer):
                 bufs = None
                 if self._momentum != 0.0:
                     bufs = [self._state(p, ("momentum_buffer",))["momentum_buffer"] for p in sub]
-                O.multi_tensor("sgd", sub, [p.grad for p in sub], bufs, lr=self.lr,
+                O.multi_tensor("sgd", sub, [self._g(p) for p in sub], bufs, lp=self._lp(sub), lr=self.lr,
                                momentum=self._momentum, wd=self._weight_decay,
                                dampening=self._dampening, nesterov=self._nesterov,
                                first_step=first, inv_scale=self._inv_scale,
@@ -77,5 +77,5 @@ class SGD(Optimizer):
                     else:
                         buf.mul_(self._momentum).add_(g, alpha=1 - self._dampening)
                     g = g + self._momentum * buf if self._nesterov else buf
-                p.copy_((pf - self.lr * g).to(p.dtype))
+                self._write(p, (pf - self.lr * g).to(p.dtype))
         self._step_count += 1

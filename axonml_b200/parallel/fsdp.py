@@ -1,0 +1,456 @@
+"""FullyShardedDataParallel: ZeRO-2 / ZeRO-3 over flat-parameter units.
+
+API of the reference (crates/axonml-distributed/src/fsdp.rs:33-354): ``ShardingStrategy``
+{FullShard (ZeRO-3, default), ShardGradOp (ZeRO-2), NoShard, HybridShard}, ``CPUOffload``,
+builders ``sharding_strategy / cpu_offload / mixed_precision``, ``gather_parameters``,
+``reshard_parameters``, ``sync_gradients``, ``clip_grad_norm``, ``memory_estimate``; alias
+``FSDP``.  The reference shards every parameter separately, never gathers in ``forward`` and drops
+the result of its reduce-scatter (fsdp.rs:259-268, :350-354); here the engine is real:
+
+* one flat unit per transformer block (plus a root unit for what is left), see ``flat_param``;
+* forward / recompute / backward gather a unit's parameters just in time on a communication
+  stream and prefetch the next unit while the current one computes;
+* ZeRO-3 with more than one rank rotates three full-size buffers between the block units (a
+  unit's parameters always view the same buffer, so no pointer is ever re-bound); ZeRO-2, NoShard
+  and single-rank runs keep one resident buffer per unit;
+* when the last gradient of a unit has arrived its flat gradient is reduce-scattered (mean) on the
+  communication stream while backward continues;
+* the optimizer steps fp32 master shards (``parameters()``), and its fused kernel writes the bf16
+  shard in the same pass.
+"""
+from __future__ import annotations
+
+import contextlib
+import dataclasses
+import enum
+
+import torch
+import torch.distributed as dist
+
+from ..nn.module import Module
+from .backend import ReduceOp
+from .flat_param import FlatUnit
+from .process_group import ProcessGroup
+
+
+class ShardingStrategy(enum.Enum):
+    FullShard = "full_shard"        # ZeRO-3
+    ShardGradOp = "shard_grad_op"   # ZeRO-2
+    NoShard = "no_shard"            # DDP-like
+    HybridShard = "hybrid_shard"    # shard inside a node, replicate across (single node: = FullShard)
+
+
+class CPUOffload(enum.Enum):
+    None_ = "none"
+    Params = "params"
+    Full = "full"
+
+
+@dataclasses.dataclass
+class FSDPMemoryStats:
+    total_params: int
+    total_param_memory: int
+    local_params: int
+    local_param_memory: int
+    local_optimizer_memory: int
+    savings_factor: float
+
+
+class _Buffer:
+    def __init__(self, numel, dtype, device):
+        self.data = torch.zeros(numel, dtype=dtype, device=device)
+        self.owner = None
+        self.free_event = None
+
+
+class FullyShardedDataParallel(Module):
+    def __init__(self, module: torch.nn.Module, process_group: ProcessGroup | None = None, *,
+                 units: list | None = None, param_dtype: torch.dtype | None = None,
+                 strategy: ShardingStrategy = ShardingStrategy.FullShard, device=None):
+        super().__init__()
+        self.module = module
+        self.pg = process_group or ProcessGroup.mock()
+        self.world, self.rank = self.pg.world_size(), self.pg.rank()
+        self._strategy = strategy
+        self._cpu_offload = CPUOffload.None_
+        self._mixed_precision = True
+        first = next(module.parameters())
+        self.device = torch.device(device) if device is not None else first.device
+        self.param_dtype = param_dtype or first.dtype
+        self._group = getattr(self.pg.backend(), "group", lambda: None)()
+        self._use_dist = self.world > 1 and dist.is_initialized()
+        self._unit_modules = units
+        self._built = False
+        self._phase = "idle"
+        self._sync = True
+        self._build()
+
+    # ------------------------------------------------------------------ reference builders
+    @classmethod
+    def new(cls, module, process_group): return cls(module, process_group)
+
+    def sharding_strategy(self, strategy: ShardingStrategy):
+        if strategy is not self._strategy:
+            raise ValueError("pass strategy= at construction; units are laid out for one strategy")
+        return self
+
+    def cpu_offload(self, offload: CPUOffload):
+        self._cpu_offload = offload
+        return self
+
+    def mixed_precision(self, flag: bool):
+        self._mixed_precision = flag
+        return self
+
+    def strategy(self) -> ShardingStrategy: return self._strategy
+
+    # ------------------------------------------------------------------ construction
+    def _auto_units(self):
+        mods = []
+        for m in self.module.modules():
+            if isinstance(m, torch.nn.ModuleList) and len(m) > 1 and all(
+                    any(True for _ in c.parameters()) for c in m):
+                mods.extend(list(m))
+        return mods
+
+    def _build(self):
+        unit_mods = self._unit_modules if self._unit_modules is not None else self._auto_units()
+        seen = set()
+        self.units: list[FlatUnit] = []
+        self._unit_of_module = {}
+        shard_params = self._strategy is not ShardingStrategy.NoShard
+        w = self.world if shard_params else 1
+        r = self.rank if shard_params else 0
+        for i, m in enumerate(unit_mods):
+            ps = [p for p in m.parameters() if id(p) not in seen and p.requires_grad]
+            for p in ps:
+                seen.add(id(p))
+            if not ps:
+                continue
+            u = FlatUnit(f"unit{i}", ps, w, r, self.device, self.param_dtype)
+            u.module, u.is_root, u.index = m, False, len(self.units)
+            self.units.append(u)
+            self._unit_of_module[id(m)] = u
+        rest = [p for p in self.module.parameters() if id(p) not in seen and p.requires_grad]
+        self.root = None
+        if rest:
+            u = FlatUnit("root", rest, w, r, self.device, self.param_dtype)
+            u.module, u.is_root, u.index = self.module, True, -1
+            self.root = u
+        self.block_units = list(self.units)
+        if self.root is not None:
+            self.units.append(self.root)
+
+        rotate = (self._strategy in (ShardingStrategy.FullShard, ShardingStrategy.HybridShard)
+                  and self.world > 1 and len(self.block_units) > 3)
+        self._rotate = rotate
+        if rotate:
+            size = max(u.padded for u in self.block_units)
+            self._pool = [_Buffer(size, self.param_dtype, self.device) for _ in range(3)]
+        for u in self.units:
+            if rotate and not u.is_root:
+                u.buffer = self._pool[u.index % 3]
+            else:
+                u.buffer = _Buffer(u.padded, self.param_dtype, self.device)
+                u.buffer.owner = u
+            u.bind_full(u.buffer.data[:u.padded])
+            if u.world == 1:
+                # the shard is the whole buffer: the optimizer writes the parameters directly
+                u.full.copy_(u._init_full)
+                u._init_full = None
+                u.lp_shard = u.full
+                u.gathered = True
+            u.bind_grad(torch.zeros(u.padded, dtype=self.param_dtype, device=self.device))
+            u.grad_shard = u.grad_flat if u.world == 1 else torch.zeros(
+                u.shard, dtype=self.param_dtype, device=self.device)
+            u.master._axon_lp = u.lp_shard
+            u.master._axon_grad = None
+        self._comm = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+
+        for u in self.block_units:
+            u.module.register_forward_pre_hook(lambda m, a, u=u: self._pre_forward(u))
+            u.module.register_forward_hook(lambda m, a, o, u=u: self._post_forward(u))
+            u.module.register_full_backward_pre_hook(lambda m, g, u=u: self._pre_backward(u))
+        for u in self.units:
+            for idx, p in enumerate(u.params):
+                p.register_post_accumulate_grad_hook(lambda p, u=u, idx=idx: self._on_grad(u, idx, p))
+                if not u.is_root and p.dim() == 2:
+                    p._axon_grad_sink = _GradSink(self, u, idx)
+        self._built = True
+
+    # ------------------------------------------------------------------ gather / release
+    def _stream_ctx(self):
+        return torch.cuda.stream(self._comm) if self._comm is not None else contextlib.nullcontext()
+
+    def _gather(self, u: FlatUnit) -> None:
+        if u.gathered or u.world == 1:
+            return
+        buf = u.buffer
+        with self._stream_ctx():
+            if self._comm is not None:
+                if buf.free_event is not None:
+                    self._comm.wait_event(buf.free_event)
+            with torch.autograd._unsafe_preserve_version_counter(buf.data):
+                if self._use_dist:
+                    dist.all_gather_into_tensor(u.full, u.lp_shard, group=self._group)
+                else:
+                    self.pg.backend().all_gather(u.lp_shard, u.full)
+            if self._comm is not None:
+                u.gather_event = torch.cuda.Event()
+                u.gather_event.record(self._comm)
+        if buf.owner is not None and buf.owner is not u:
+            buf.owner.gathered = False
+        buf.owner = u
+        u.gathered = True
+
+    def _wait(self, u: FlatUnit) -> None:
+        if u.gather_event is not None:
+            torch.cuda.current_stream().wait_event(u.gather_event)
+            u.gather_event = None
+
+    def _mark_free(self, u: FlatUnit) -> None:
+        if self._comm is not None and u.world > 1:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            u.buffer.free_event = ev
+
+    def _neighbor(self, u: FlatUnit, step: int):
+        j = u.index + step
+        return self.block_units[j] if 0 <= j < len(self.block_units) else None
+
+    def _pre_forward(self, u: FlatUnit) -> None:
+        self._gather(u)
+        self._wait(u)
+        nxt = self._neighbor(u, -1 if self._phase == "bwd" else 1)
+        if nxt is not None:
+            self._gather(nxt)
+
+    def _post_forward(self, u: FlatUnit) -> None:
+        self._mark_free(u)
+
+    def _pre_backward(self, u: FlatUnit) -> None:
+        self._enter_backward()
+        self._gather(u)
+        self._wait(u)
+        prv = self._neighbor(u, -1)
+        if prv is not None:
+            self._gather(prv)
+
+    # ------------------------------------------------------------------ gradients
+    def _enter_backward(self) -> None:
+        if self._phase == "bwd":
+            return
+        self._phase = "bwd"
+        for u in self.units:
+            u.pending = len(u.params)
+        torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)
+
+    def _on_grad(self, u: FlatUnit, idx: int, p) -> None:
+        g = p.grad
+        if g is None:
+            return
+        self._enter_backward()
+        dst = u.grad_views[idx]
+        if u.grad_written[idx]:
+            dst.add_(g)
+        else:
+            dst.copy_(g)
+            u.grad_written[idx] = True
+        p.grad = None
+        if not u.is_root:
+            self._arrived(u)
+
+    def _arrived(self, u: FlatUnit) -> None:
+        u.pending -= 1
+        if u.pending == 0:
+            self._mark_free(u)
+            if self._sync:
+                self._reduce(u)
+
+    def _reduce(self, u: FlatUnit) -> None:
+        """Mean over ranks of the unit's flat gradient; this rank keeps its shard."""
+        if self.world == 1:
+            u.master._axon_grad = u.grad_shard
+        else:
+            with self._stream_ctx():
+                if self._comm is not None:
+                    self._comm.wait_stream(torch.cuda.current_stream())
+                if u.world == 1:   # NoShard: all-reduce the whole flat gradient
+                    self.pg.backend().all_reduce(u.grad_flat, ReduceOp.Average)
+                elif self._use_dist:
+                    dist.reduce_scatter_tensor(u.grad_shard, u.grad_flat, op=dist.ReduceOp.AVG,
+                                               group=self._group)
+                else:
+                    self.pg.backend().reduce_scatter(u.grad_flat, u.grad_shard, ReduceOp.Average)
+            u.master._axon_grad = u.grad_shard
+        u.grad_written = [False] * len(u.params)
+        u.reduced = True
+
+    def _finish_backward(self) -> None:
+        if self._sync:
+            for u in self.units:
+                if not getattr(u, "reduced", False) and any(u.grad_written):
+                    self._reduce(u)
+            if self._comm is not None:
+                torch.cuda.current_stream().wait_stream(self._comm)
+        for u in self.units:
+            u.reduced = False
+        self._phase = "idle"
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Accumulates gradients locally; the next backward outside the context reduces them."""
+        old, self._sync = self._sync, False
+        try:
+            yield
+        finally:
+            self._sync = old
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, *args, **kwargs):
+        return self._run(self.module, *args, **kwargs)
+
+    def call(self, method: str, *args, **kwargs):
+        """Runs ``module.<method>(*args)`` (e.g. ``forward_with_loss``) under the engine."""
+        return self._run(getattr(self.module, method), *args, **kwargs)
+
+    def _run(self, fn, *args, **kwargs):
+        self._phase = "fwd"
+        if self._comm is not None:
+            # shards written by the optimizer on the compute stream must be visible to the gathers
+            self._comm.wait_stream(torch.cuda.current_stream())
+        if self.world > 1:
+            for u in self.units:
+                if u.world > 1:
+                    u.gathered = False
+                    if u.buffer.owner is u and self._rotate and not u.is_root:
+                        u.buffer.owner = None
+        if self.root is not None:
+            self._gather(self.root)
+            self._wait(self.root)
+        if self.block_units:
+            self._gather(self.block_units[0])
+        out = fn(*args, **kwargs)
+        for t in (out if isinstance(out, (tuple, list)) else (out,)):
+            if torch.is_tensor(t) and t.requires_grad:
+                t.register_hook(lambda g: (self._enter_backward(), g)[1])
+        return out
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(super().__getattr__("module"), name)
+
+    # ------------------------------------------------------------------ reference methods
+    def parameters(self, recurse: bool = True):
+        """The tensors an optimizer must step: one fp32 master shard per unit."""
+        return iter([u.master for u in self.units])
+
+    def named_parameters(self, prefix: str = "", recurse: bool = True, remove_duplicate: bool = True):
+        return iter([(f"{prefix}{u.name}.flat_shard", u.master) for u in self.units])
+
+    def model_parameters(self):
+        return self.module.parameters()
+
+    def gather_parameters(self) -> None:
+        for u in self.units:
+            if not (self._rotate and not u.is_root):
+                self._gather(u)
+                self._wait(u)
+
+    def reshard_parameters(self) -> None:
+        for u in self.units:
+            if u.world > 1:
+                u.gathered = False
+
+    def sync_gradients(self) -> None:
+        for u in self.units:
+            if any(u.grad_written):
+                self._reduce(u)
+        if self._comm is not None:
+            torch.cuda.current_stream().wait_stream(self._comm)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for u in self.units:
+            u.master._axon_grad = None
+            u.grad_written = [False] * len(u.params)
+        for p in self.module.parameters():
+            p.grad = None
+
+    def clip_grad_norm(self, max_norm: float) -> torch.Tensor:
+        """Global L2 norm over all shards (local sum of squares -> all-reduce -> scale;
+        fsdp.rs:284-314)."""
+        from ..ops import optim as O
+        grads = [u.master._axon_grad for u in self.units if u.master._axon_grad is not None]
+        if not grads:
+            return torch.zeros((), device=self.device)
+        ss = O.grad_sumsq(grads)
+        if self.world > 1 and self._strategy is not ShardingStrategy.NoShard:
+            self.pg.backend().all_reduce(ss, ReduceOp.Sum)
+        norm = ss.sqrt()
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        if O.supported(grads, grads):
+            O.multi_tensor("scale", None, grads, clip_coef=coef)
+        else:
+            for g in grads:
+                g.mul_(coef.to(g.dtype)[0])
+        return norm[0]
+
+    def memory_estimate(self) -> FSDPMemoryStats:
+        total = sum(u.param_numel() for u in self.units)
+        local = sum(u.shard for u in self.units)
+        bpe = torch.empty((), dtype=self.param_dtype).element_size()
+        return FSDPMemoryStats(total, total * bpe, local, local * (bpe + 4), local * 8,
+                               total / max(local, 1))
+
+    # ------------------------------------------------------------------ state (sharded checkpoints)
+    def full_state_dict(self) -> dict:
+        """Full-precision state dict of the wrapped module, gathered from the master shards."""
+        out = {}
+        names = {id(p): n for n, p in self.module.named_parameters()}
+        for u in self.units:
+            if u.world > 1:
+                full = torch.empty(u.padded, dtype=torch.float32, device=self.device)
+                self.pg.backend().all_gather(u.master.detach(), full)
+            else:
+                full = u.master.detach()
+            for p, o in zip(u.params, u.offsets):
+                out[names[id(p)]] = full[o:o + p.numel()].view(p.shape).clone()
+        for n, b in self.module.named_buffers():
+            out[n] = b.detach().clone()
+        return out
+
+    def load_full_state_dict(self, sd: dict) -> None:
+        names = {id(p): n for n, p in self.module.named_parameters()}
+        for u in self.units:
+            flat = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
+            for p, o in zip(u.params, u.offsets):
+                flat[o:o + p.numel()].copy_(torch.as_tensor(sd[names[id(p)]]).reshape(-1))
+            lo = u.rank * u.shard
+            with torch.no_grad():
+                u.master.copy_(flat[lo:lo + u.shard])
+                u.lp_shard.copy_(flat[lo:lo + u.shard].to(self.param_dtype))
+            if u.world > 1:
+                u.gathered = False
+
+
+class _GradSink:
+    """Lets a GEMM write a weight gradient straight into the unit's flat gradient buffer."""
+
+    def __init__(self, engine: FullyShardedDataParallel, unit: FlatUnit, idx: int):
+        self.engine, self.unit, self.idx = engine, unit, idx
+
+    def target(self) -> torch.Tensor:
+        return self.unit.grad_views[self.idx]
+
+    def first_write(self) -> bool:
+        return not self.unit.grad_written[self.idx]
+
+    def done(self) -> None:
+        self.engine._enter_backward()
+        self.unit.grad_written[self.idx] = True
+        self.engine._arrived(self.unit)
+
+
+FSDP = FullyShardedDataParallel
