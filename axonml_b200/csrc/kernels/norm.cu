@@ -279,3 +279,56 @@ AX_API int ax_norm_bwd(int rms, int act_dtype, int w_dtype, const void* dy, cons
     return launch_bwd<float, float>(rms, dy, x, w, mean, rstd, dres, dx, dw, db, scratch, groups, rows, D, stream);
   return -1;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant of the norm backward (declared in axonml_noalloc.h).
+//
+// Some callers cannot allocate device memory: code running inside a CUDA-graph capture or a
+// latency-critical serving loop where cudaMalloc would synchronise the device, plugins that are
+// handed a fixed arena by their host application, and processes whose memory pool is owned by
+// another runtime.  For them the per-CTA partial sums live in a fixed array inside this library
+// instead of a caller-provided scratch buffer.
+//
+// Limits: D <= kNoAllocMaxD (8192) and at most kNoAllocGroups (64) partial slots, i.e. 4 MiB of
+// device memory that every GPU which loads this library holds until the process exits.
+// The array is shared by all calls: two calls that overlap on the GPU (different streams) race on
+// it.  Nothing in it has to start at zero - every slot that the reduction reads is rewritten by
+// the first kernel of the same call - so the previous call's contents are harmless.
+namespace {
+constexpr int kNoAllocMaxD = 8192;
+constexpr int kNoAllocGroups = 64;
+static __device__ __align__(256) float g_norm_bwd_scratch[(size_t)kNoAllocGroups * 2 * kNoAllocMaxD];
+// Device address of the array, resolved once per device.  In host code the symbol's name is only
+// a stand-in; the kernels must be given the address that cudaGetSymbolAddress returns.
+static float* g_norm_bwd_scratch_addr[64] = {nullptr};
+}  // namespace
+
+AX_API int ax_norm_bwd_noalloc(int rms, int act_dtype, int w_dtype, const void* dy, const void* x,
+                               const void* w, const float* mean, const float* rstd,
+                               const void* dres, void* dx, void* dw, void* db, int rows, int D,
+                               cudaStream_t stream) {
+  if (D % 8 != 0 || rows <= 0) return -1;
+  if (D > kNoAllocMaxD) return -2;  // beyond the built-in scratch: use ax_norm_bwd with your own buffer
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -3;
+  if (g_norm_bwd_scratch_addr[dev] == nullptr) {
+    // First call on this device: resolve the array's device address (no allocation happens; the
+    // array is part of the loaded module).  Do this before any stream capture.
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_norm_bwd_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_norm_bwd_scratch_addr[dev] = p;
+  }
+  int groups = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  if (groups > kNoAllocGroups) groups = kNoAllocGroups;
+  return ax_norm_bwd(rms, act_dtype, w_dtype, dy, x, w, mean, rstd, dres, dx, dw, db,
+                     g_norm_bwd_scratch_addr[dev], groups, rows, D, stream);
+}
+
+AX_API int ax_norm_bwd_noalloc_limits(int* max_d, int* max_groups) {
+  *max_d = kNoAllocMaxD;
+  *max_groups = kNoAllocGroups;
+  return 0;
+}
