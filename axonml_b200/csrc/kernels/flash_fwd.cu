@@ -1,0 +1,320 @@
+// Flash-attention forward for sm_100a: bf16, head_dim 128, causal or full, grouped-query heads,
+// token-major [B, S, H, D] operands (views into a fused QKV tensor are fine).
+//
+// One CTA per (batch, query head, 128-query block).  Warp 0 streams K/V blocks of 128 keys with
+// TMA (two stages), warp 1 issues tcgen05.mma: S = Q K^T into one of two TMEM buffers and
+// O += P V into a TMEM accumulator, warps 2..5 (one thread per query row) read S from TMEM, keep
+// the running max / sum, write P as bf16 into shared memory for the second MMA, and rescale O in
+// TMEM only when a row's max has grown by more than 2^8 (the deferred-rescale trick keeps the
+// result exact because the final normalisation uses the same reference max).  S(j+1) is issued
+// before P(j) V(j), so the tensor pipe works on the next block while softmax(j) runs.
+//
+// Parity: FlashAttention forward crates/axonml-llm/src/attention.rs:836-943 (CPU, block 64) and
+// the attention inside LLaMA / GPT-2 (llama.rs:429-441).
+#include "flash_common.cuh"
+
+namespace {
+using namespace ax;
+using namespace fa;
+
+constexpr int BQ = 128;
+constexpr int BKV = 128;
+constexpr int kThreads = 192;
+constexpr int kTile = BQ * HD * 2;           // 32 KB: one [128 x 128] bf16 tile
+constexpr int kSmem = 1024 + kTile /*Q*/ + 2 * kTile /*K*/ + 2 * kTile /*V*/ + kTile /*P*/ + 256;
+constexpr int kTmemCols = 512;               // S0 | S1 | O | (unused)
+constexpr float kRescaleThreshold = 8.0f;    // log2 units
+
+struct FwdParams {
+  void* out;          // [B, Sq, Hq, D] bf16
+  long o_row_stride, o_batch_stride;
+  float* lse;         // [B, Hq, Sq] natural-log log-sum-exp
+  int B, Hq, Hkv, Sq, Skv;
+  int causal;
+  float scale_log2;   // softmax scale * log2(e)
+  int* status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTile;
+  uint8_t* sV = sK + 2 * kTile;
+  uint8_t* sP = sV + 2 * kTile;
+  uint64_t* bars = (uint64_t*)(sP + kTile);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* s_empty = bars + 11;    // 2
+  uint64_t* p_full = bars + 13;     // 1
+  uint64_t* pv_done = bars + 14;    // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+  volatile int* dead = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // longest (last) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qb * BQ;
+  const int offset = p.Skv - p.Sq;                        // causal: row i sees keys <= i + offset
+  int kv_end = p.Skv;
+  if (p.causal) kv_end = min(p.Skv, q0 + BQ + offset);
+  const int nblk = kv_end > 0 ? (kv_end + BKV - 1) / BKV : 0;
+
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    mbar_fence_init();
+    prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) { tmem_alloc<kTmemCols>(tmem_slot); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS0 = tmem_base, tO = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0 && nblk > 0) {
+      mbar_expect_tx(q_full, kTile);
+      tma_load_4d(sQ, &map_q, q_full, 0, h, q0, b);
+      tma_load_4d(sQ + slab_bytes(BQ), &map_q, q_full, 64, h, q0, b);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int kv0 = j * BKV;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, dead, p.status, 400)) break;
+        mbar_expect_tx(&k_full[s], kTile);
+        tma_load_4d(sK + s * kTile, &map_k, &k_full[s], 0, hk, kv0, b);
+        tma_load_4d(sK + s * kTile + slab_bytes(BKV), &map_k, &k_full[s], 64, hk, kv0, b);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, dead, p.status, 401)) break;
+        mbar_expect_tx(&v_full[s], kTile);
+        tma_load_4d(sV + s * kTile, &map_v, &v_full[s], 0, hk, kv0, b);
+        tma_load_4d(sV + s * kTile + slab_bytes(BKV), &map_v, &v_full[s], 64, hk, kv0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_s = umma_idesc_f16(1, 128, 128, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc_f16(1, 128, 128, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, dead, p.status, 410);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, dead, p.status, 411)) return false;
+        if (!mbar_wait(&s_empty[s], ph ^ 1, dead, p.status, 412)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + s * kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_f16_ss(tS0 + s * 128, desc_kmajor(aQ, BQ, k), desc_kmajor(aK, BKV, k), idesc_s, k != 0);
+        umma_commit(&k_empty[s]);
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < nblk; ++j) {
+        if (j + 1 < nblk) ok = issue_s(j + 1);
+        if (!ok) break;
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(p_full, j & 1, dead, p.status, 413)) break;
+        if (!mbar_wait(&v_full[s], ph, dead, p.status, 414)) break;
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + s * kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_f16_ss(tO, desc_kmajor(aP, BQ, k), desc_mnmajor(aV, BKV, k), idesc_o, (j | k) != 0);
+        umma_commit(&v_empty[s]);
+        umma_commit(pv_done);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                 // row inside the tile == TMEM lane
+    const int qi = q0 + r;                       // query index
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const int kv0 = j * BKV;
+      ok = mbar_wait(&s_full[s], ph, dead, p.status, 420);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tS = tS0 + s * 128 + lane_addr;
+      const int limit = p.causal ? min(p.Skv - 1, qi + offset) : p.Skv - 1;   // last visible key
+      const bool need_mask = __any_sync(0xffffffffu, kv0 + BKV - 1 > limit);
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tS + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(v[i]);
+          if (need_mask && kv0 + c * 32 + i > limit) x = -INFINITY;
+          mx = fmaxf(mx, x);
+        }
+      }
+      float m_new = fmaxf(m, mx * p.scale_log2);
+      if (m_new == -INFINITY) m_new = 0.f;
+      // O and the P buffer are free once P(j-1) V(j-1) has retired
+      if (j > 0) {
+        ok = mbar_wait(pv_done, (j - 1) & 1, dead, p.status, 421);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const bool grow = m_new > m + kRescaleThreshold;
+      if (j == 0) {
+        m = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = grow ? exp2f(m - m_new) : 1.f;
+        if (grow) { l *= alpha; m = m_new; }
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t v[16];
+          tmem_ld_32x32b_x16(tO + lane_addr + c * 16, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32b_x16(tO + lane_addr + c * 16, v);
+        }
+        tc_wait_st();
+      }
+      // pass 2: probabilities -> shared memory (bf16), row sum
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tS + c * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float pv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c * 32 + g * 8 + i;
+            float x = __uint_as_float(v[g * 8 + i]) * p.scale_log2 - m;
+            float e = exp2f(x);
+            if (need_mask && kv0 + col > limit) e = 0.f;
+            pv[i] = e;
+            rs += e;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(pv[0], pv[1]); o.y = pack_bf16x2(pv[2], pv[3]);
+          o.z = pack_bf16x2(pv[4], pv[5]); o.w = pack_bf16x2(pv[6], pv[7]);
+          store_tile_chunk(sP, BQ, r, c * 4 + g, o);
+        }
+      }
+      l += rs;
+      // hand S[s] back, publish P
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&s_empty[s]); mbar_arrive(p_full); }
+    }
+    // epilogue: O / l -> global, lse
+    if (ok && nblk > 0) {
+      ok = mbar_wait(pv_done, (nblk - 1) & 1, dead, p.status, 422);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool valid = qi < p.Sq;
+      __nv_bfloat16* orow = (__nv_bfloat16*)p.out + (long)b * p.o_batch_stride + (long)qi * p.o_row_stride + (long)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        if (nblk > 0) {
+          tmem_ld_32x32b_x32(tO + lane_addr + c * 32, v);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+          }
+        }
+      }
+      if (valid && p.lse)
+        p.lse[((long)b * p.Hq + h) * p.Sq + qi] = l > 0.f ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc<kTmemCols>(tmem_base);
+}
+
+}  // namespace
+
+namespace axh {
+int make_bshd_map(CUtensorMap* m, const void* ptr, int D, int H, int S, int B, long row_stride,
+                  long batch_stride, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)row_stride * 2, (uint64_t)batch_stride * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return encode_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptr, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+}
+}  // namespace axh
+
+// q [B,Sq,Hq,128], k/v [B,Skv,Hkv,128], out [B,Sq,Hq,128] (bf16, token-major; strides in elements),
+// lse [B,Hq,Sq] fp32.  Returns a cudaError_t value or a negative code for unsupported arguments.
+AX_API int ax_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                        int Sq, int Skv, int Hq, int Hkv, int D, long q_row, long q_batch, long k_row,
+                        long k_batch, long v_row, long v_batch, long o_row, long o_batch, int causal,
+                        float scale, int* status, cudaStream_t stream) {
+  if (D != fa::HD || Hq % Hkv != 0) return -1;
+  if ((q_row | k_row | v_row | o_row | q_batch | k_batch | v_batch) % 8) return -1;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return -1;
+  if (B <= 0 || Sq <= 0 || Skv <= 0) return 0;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = axh::make_bshd_map(&mq, q, D, Hq, Sq, B, q_row, q_batch, BQ))) return 1000 + rc;
+  if ((rc = axh::make_bshd_map(&mk, k, D, Hkv, Skv, B, k_row, k_batch, BKV))) return 2000 + rc;
+  if ((rc = axh::make_bshd_map(&mv, v, D, Hkv, Skv, B, v_row, v_batch, BKV))) return 3000 + rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  FwdParams p;
+  p.out = out; p.o_row_stride = o_row; p.o_batch_stride = o_batch; p.lse = lse;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv; p.causal = causal;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
+  flash_fwd_kernel<<<grid, kThreads, kSmem, stream>>>(mq, mk, mv, p);
+  return (int)cudaGetLastError();
+}
