@@ -16,7 +16,7 @@ from .. import nn
 from ..autograd.checkpoint import checkpoint
 from ..ops import loss as L
 from ..ops import misc as Mi
-from ..ops.attention import sdpa
+from ..ops.attention import sdpa, sdpa_packed
 from ..ops.linear import linear
 from .config import GPT2Config
 
@@ -53,11 +53,15 @@ class CausalSelfAttention(nn.Module):
 
     def forward(self, x, kv_cache=None):
         B, S, E = x.shape
-        qkv = self.c_attn(x).view(B, S, 3, self.n_head, self.head_dim)
-        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
-        if kv_cache is not None:
+        drop = self.attn_dropout if self.training else 0.0
+        if kv_cache is None:
+            qkv = self.c_attn(x).view(B, S, 3 * self.n_head, self.head_dim)
+            o = sdpa_packed(qkv, self.n_head, self.n_head, causal=True, dropout_p=drop)
+        else:
+            qkv = self.c_attn(x).view(B, S, 3, self.n_head, self.head_dim)
+            q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
             k, v = kv_cache.update(k, v)
-        o = sdpa(q, k, v, causal=True, dropout_p=self.attn_dropout if self.training else 0.0)
+            o = sdpa(q, k, v, causal=True, dropout_p=drop)
         return self.resid_drop(self.c_proj(o.reshape(B, S, E)))
 
 

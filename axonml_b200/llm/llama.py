@@ -19,7 +19,7 @@ from ..autograd.checkpoint import checkpoint
 from ..ops import elementwise as E
 from ..ops import loss as L
 from ..ops import misc as Mi
-from ..ops.attention import sdpa
+from ..ops.attention import sdpa, sdpa_packed
 from ..ops.linear import linear
 from .attention import LayerKVCache
 from .config import LLaMAConfig
@@ -61,6 +61,12 @@ class LLaMAAttention(nn.Module):
         B, S, _ = x.shape
         w = _cat_rows(self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
         qkv = linear(x, w)
+        if kv_cache is None and self.sliding_window is None:
+            packed = qkv.view(B, S, self.nh + 2 * self.nkv, self.hd)
+            packed = Mi.rope(packed, self.rotary.cos_cached.to(x.device), self.rotary.sin_cached.to(x.device),
+                             seq_len=S, pos0=pos0, rot_heads=self.nh + self.nkv)
+            o = sdpa_packed(packed, self.nh, self.nkv, causal=True)
+            return self.o_proj(o.reshape(B, S, self.nh * self.hd))
         nq, nk = self.nh * self.hd, self.nkv * self.hd
         q = qkv[..., :nq].reshape(B, S, self.nh, self.hd)
         k = qkv[..., nq:nq + nk].reshape(B, S, self.nkv, self.hd)

@@ -65,3 +65,15 @@ def sdpa(q, k, v, mask=None, causal: bool = False, scale: float | None = None,
     if dropout_p > 0:
         o = F.dropout(o, dropout_p)
     return o
+
+
+def sdpa_packed(qkv, Hq: int, Hkv: int, causal: bool = True, scale: float | None = None,
+                dropout_p: float = 0.0):
+    """Self-attention on a packed ``[B, S, Hq + 2*Hkv, D]`` tensor laid out q heads | k heads |
+    v heads (what a fused QKV projection produces).  On a B200 the flash kernels read the three
+    parts in place and the backward writes one packed gradient."""
+    from . import flash
+    if dropout_p == 0.0 and flash.packed_supported(qkv):
+        return flash.flash_attention_packed(qkv, Hq, Hkv, causal, scale)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    return sdpa(q, k, v, causal=causal, scale=scale, dropout_p=dropout_p)

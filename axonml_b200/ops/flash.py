@@ -52,3 +52,81 @@ _HAVE_BWD = False
 
 def flash_attention(q, k, v, causal: bool = False, scale: float | None = None):
     return flash_fwd(q, k, v, causal, scale)[0]
+
+
+def flash_bwd(q, k, v, out, dout, lse, causal, scale, dq, dk, dv):
+    """Writes dq/dk/dv (token-major views, any row/batch strides)."""
+    B, Sq, Hq, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    dout, dor, dob = _strides(dout)
+    delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
+    assert dk.stride(1) == dv.stride(1) and dk.stride(0) == dv.stride(0)
+    L = N.c_int64
+    rc = N.cuda().ax_flash_bwd(
+        N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(dout), N.ptr(lse), N.ptr(delta), N.ptr(dq),
+        N.ptr(dk), N.ptr(dv), B, Sq, Skv, Hq, Hkv, D, L(q.stride(1)), L(q.stride(0)), L(k.stride(1)),
+        L(k.stride(0)), L(v.stride(1)), L(v.stride(0)), L(out.stride(1)), L(out.stride(0)), L(dor),
+        L(dob), L(dq.stride(1)), L(dq.stride(0)), L(dk.stride(1)), L(dk.stride(0)), int(causal),
+        N.c_float(scale), N.ptr(N.status_word(q.device)), N.stream_ptr())
+    N.check(rc, "ax_flash_bwd")
+
+
+class _FlashFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        out, lse, (q, k, v) = flash_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        flash_bwd(q, k, v, out, dout, lse, ctx.causal, ctx.scale, dq, dk, dv)
+        return dq, dk, dv, None, None
+
+
+class _FlashPackedFn(torch.autograd.Function):
+    """Attention on a packed ``[B, S, Hq + 2*Hkv, D]`` tensor (q heads | k heads | v heads): the
+    backward writes dq, dk, dv straight into one packed gradient tensor."""
+
+    @staticmethod
+    def forward(ctx, qkv, Hq, Hkv, causal, scale):
+        scale = scale if scale is not None else 1.0 / math.sqrt(qkv.shape[-1])
+        if not qkv.is_contiguous():
+            qkv = qkv.contiguous()
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        out, lse, _ = flash_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (Hq, Hkv, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        Hq, Hkv, causal, scale = ctx.meta
+        d = torch.empty_like(qkv)
+        q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+        flash_bwd(q, k, v, out, dout, lse, causal, scale, d[:, :, :Hq], d[:, :, Hq:Hq + Hkv],
+                  d[:, :, Hq + Hkv:])
+        return d, None, None, None, None
+
+
+_HAVE_BWD = True
+
+
+def flash_attention(q, k, v, causal: bool = False, scale: float | None = None):  # noqa: F811
+    return _FlashFn.apply(q, k, v, causal, scale)
+
+
+def flash_attention_packed(qkv, Hq: int, Hkv: int, causal: bool = True, scale: float | None = None):
+    return _FlashPackedFn.apply(qkv, Hq, Hkv, causal, scale)
+
+
+def packed_supported(qkv) -> bool:
+    return (N.is_blackwell() and qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 4
+            and qkv.shape[-1] == 128)

@@ -67,19 +67,19 @@ def rope_tables(max_pos: int, head_dim: int, theta: float = 10000.0, device=None
 
 class _RopeFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, cos, sin, seq_len, pos0):
-        out = _rope_launch(x, cos, sin, seq_len, pos0, 1.0)
+    def forward(ctx, x, cos, sin, seq_len, pos0, rot_heads=-1):
+        out = _rope_launch(x, cos, sin, seq_len, pos0, 1.0, rot_heads)
         ctx.save_for_backward(cos, sin)
-        ctx.meta = (seq_len, pos0)
+        ctx.meta = (seq_len, pos0, rot_heads)
         return out
 
     @staticmethod
     def backward(ctx, dy):
         cos, sin = ctx.saved_tensors
-        return _rope_launch(dy, cos, sin, ctx.meta[0], ctx.meta[1], -1.0), None, None, None, None
+        return _rope_launch(dy, cos, sin, ctx.meta[0], ctx.meta[1], -1.0, ctx.meta[2]), None, None, None, None, None
 
 
-def _rope_launch(x, cos, sin, seq_len, pos0, sign):
+def _rope_launch(x, cos, sin, seq_len, pos0, sign, rot_heads=-1):
     # x: [..., heads, head_dim] with token-major leading dims
     heads, hd = x.shape[-2], x.shape[-1]
     x3 = x.reshape(-1, heads, hd)
@@ -89,15 +89,19 @@ def _rope_launch(x, cos, sin, seq_len, pos0, sign):
     N.check(N.cuda().ax_rope(_dt(x3), N.ptr(x3), N.ptr(out), N.ptr(cos), N.ptr(sin),
                              N.c_int64(x3.shape[0]), heads, hd, N.c_int64(x3.stride(0)),
                              N.c_int64(out.stride(0)), seq_len, pos0, N.c_float(sign),
-                             N.stream_ptr()), "ax_rope")
+                             heads if rot_heads < 0 else rot_heads, N.stream_ptr()), "ax_rope")
     return out.view(x.shape)
 
 
-def rope(x, cos, sin, *, seq_len: int, pos0: int = 0):
+def rope(x, cos, sin, *, seq_len: int, pos0: int = 0, rot_heads: int = -1):
     """Rotary embedding (half-split) of ``x[B*S or B,S, heads, head_dim]``; token t of the
-    flattened leading dims has position ``pos0 + t % seq_len``."""
+    flattened leading dims has position ``pos0 + t % seq_len``.  With ``rot_heads >= 0`` only the
+    first ``rot_heads`` heads are rotated and the rest are copied (packed q|k|v tensors)."""
     if _ok(x):
-        return _RopeFn.apply(x, cos, sin, seq_len, pos0)
+        return _RopeFn.apply(x, cos, sin, seq_len, pos0, rot_heads)
+    if rot_heads >= 0 and rot_heads < x.shape[-2]:
+        a = rope(x[..., :rot_heads, :], cos, sin, seq_len=seq_len, pos0=pos0)
+        return torch.cat([a, x[..., rot_heads:, :]], dim=-2)
     hd = x.shape[-1]
     half = hd // 2
     lead = x.shape[:-2]
