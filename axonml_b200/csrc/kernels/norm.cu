@@ -184,19 +184,31 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* __r
   }
 }
 
-// dw[d] = sum_g partial[g,0,d]; db[d] = sum_g partial[g,1,d]
+// dw[d] = sum_g partial[g,0,d]; db[d] = sum_g partial[g,1,d].  Block = 32 columns x 32 group
+// lanes: each thread sums groups g = ty, ty+32, ..., then the 32 partials of a column are combined
+// through shared memory.
 template <typename WT>
 __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, WT* __restrict__ dw,
                                        WT* __restrict__ db, int groups, int D) {
-  int d = blockIdx.x * blockDim.x + threadIdx.x;
-  if (d >= D) return;
+  __shared__ float sa[32][33], sb[32][33];
+  const int d = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f, b = 0.f;
-  for (int g = 0; g < groups; ++g) {
-    a += partial[(long)g * 2 * D + d];
-    b += partial[(long)g * 2 * D + D + d];
+  if (d < D) {
+    for (int g = threadIdx.y; g < groups; g += 32) {
+      a += partial[(long)g * 2 * D + d];
+      if (db) b += partial[(long)g * 2 * D + D + d];
+    }
   }
-  if (dw) dw[d] = (WT)a;
-  if (db) db[d] = (WT)b;
+  sa[threadIdx.y][threadIdx.x] = a;
+  sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && d < D) {
+    float ta = 0.f, tb = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { ta += sa[j][threadIdx.x]; tb += sb[j][threadIdx.x]; }
+    if (dw) dw[d] = (WT)ta;
+    if (db) db[d] = (WT)tb;
+  }
 }
 
 template <typename T, typename WT>
@@ -236,7 +248,7 @@ int launch_bwd(bool rms, const void* dy, const void* x, const void* w, const flo
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  norm_bwd_reduce_kernel<WT><<<(D + 255) / 256, 256, 0, stream>>>(scratch, (WT*)dw,
+  norm_bwd_reduce_kernel<WT><<<(D + 31) / 32, dim3(32, 32), 0, stream>>>(scratch, (WT*)dw,
                                                                    rms ? nullptr : (WT*)db, groups, D);
   return (int)cudaGetLastError();
 }

@@ -48,6 +48,24 @@ template <typename T> __device__ __forceinline__ void st(T* p, long i, float v);
 template <> __device__ __forceinline__ void st<float>(float* p, long i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, long i, float v) { p[i] = __float2bfloat16(v); }
 
+__device__ __forceinline__ void ld4(const float* p, long i, float (&v)[4]) {
+  float4 t = *reinterpret_cast<const float4*>(p + i);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, long i, float (&v)[4]) {
+  uint2 t = *reinterpret_cast<const uint2*>(p + i);
+  float2 a = unpack_bf16x2(t.x), b = unpack_bf16x2(t.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void st4(float* p, long i, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, long i, const float (&v)[4]) {
+  uint2 t;
+  t.x = pack_bf16x2(v[0], v[1]); t.y = pack_bf16x2(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p + i) = t;
+}
+
 enum Kind : int { K_SGD = 0, K_ADAM, K_RMSPROP, K_LAMB1, K_LAMB2, K_SUMSQ, K_SCALE, K_UNSCALE_CHECK };
 
 template <int KIND, typename PT, typename GT>
@@ -73,75 +91,99 @@ mt_kernel(const TensorTable tt, const Hyper h) {
     float pn = sqrtf(h.norms[2 * tt.gidx[t]]), rn = sqrtf(h.norms[2 * tt.gidx[t] + 1]);
     trust = (pn > 0.f && rn > 0.f) ? pn / rn : 1.f;
   }
-  for (long i = base + threadIdx.x; i < end; i += blockDim.x) {
+  // One element of the update.  w: parameter, gr: raw gradient, a/b/c: optimizer states.
+  auto elem = [&](float& w, float& gr, float& a, float& b, float& c) {
     if (KIND == K_SGD) {
-      float w = ld(p, i), gr = ld(g, i) * gmul;
-      gr += h.wd * w;
+      gr = gr * gmul + h.wd * w;
       if (h.momentum != 0.f) {
-        float b = h.first_step ? gr : h.momentum * s1[i] + (1.f - h.dampening) * gr;
-        s1[i] = b;
-        gr = h.nesterov ? gr + h.momentum * b : b;
+        a = h.first_step ? gr : h.momentum * a + (1.f - h.dampening) * gr;
+        gr = h.nesterov ? gr + h.momentum * a : a;
       }
       w -= h.lr * gr;
-      st(p, i, w);
-      if (lp) lp[i] = __float2bfloat16(w);
     } else if (KIND == K_ADAM) {
-      float w = ld(p, i), gr = ld(g, i) * gmul;
+      gr *= gmul;
       if (h.adamw) w *= 1.f - h.lr * h.wd; else gr += h.wd * w;
-      float m = h.beta1 * s1[i] + (1.f - h.beta1) * gr;
-      float v = h.beta2 * s2[i] + (1.f - h.beta2) * gr * gr;
-      s1[i] = m; s2[i] = v;
-      float vv = v;
-      if (h.amsgrad) { vv = fmaxf(s3[i], v); s3[i] = vv; }
-      float denom = sqrtf(vv / h.bc2) + h.eps;
-      w -= (h.lr / h.bc1) * m / denom;
-      st(p, i, w);
-      if (lp) lp[i] = __float2bfloat16(w);
+      a = h.beta1 * a + (1.f - h.beta1) * gr;
+      b = h.beta2 * b + (1.f - h.beta2) * gr * gr;
+      float vv = b;
+      if (h.amsgrad) { vv = fmaxf(c, b); c = vv; }
+      w -= (h.lr / h.bc1) * a / (sqrtf(vv / h.bc2) + h.eps);
     } else if (KIND == K_RMSPROP) {
-      float w = ld(p, i), gr = ld(g, i) * gmul;
-      gr += h.wd * w;
-      float sq = h.alpha * s1[i] + (1.f - h.alpha) * gr * gr;
-      s1[i] = sq;
+      gr = gr * gmul + h.wd * w;
+      a = h.alpha * a + (1.f - h.alpha) * gr * gr;
       float avg;
       if (h.centered) {
-        float ga = h.alpha * s3[i] + (1.f - h.alpha) * gr;
-        s3[i] = ga;
-        avg = sqrtf(fmaxf(sq - ga * ga, 0.f)) + h.eps;
+        c = h.alpha * c + (1.f - h.alpha) * gr;
+        avg = sqrtf(fmaxf(a - c * c, 0.f)) + h.eps;
       } else {
-        avg = sqrtf(sq) + h.eps;
+        avg = sqrtf(a) + h.eps;
       }
       if (h.momentum > 0.f) {
-        float b = h.momentum * s2[i] + gr / avg;
-        s2[i] = b;
+        b = h.momentum * b + gr / avg;
         w -= h.lr * b;
       } else {
         w -= h.lr * gr / avg;
       }
-      st(p, i, w);
-      if (lp) lp[i] = __float2bfloat16(w);
     } else if (KIND == K_LAMB1) {
-      float w = ld(p, i), gr = ld(g, i) * gmul;
-      float m = h.beta1 * s1[i] + (1.f - h.beta1) * gr;
-      float v = h.beta2 * s2[i] + (1.f - h.beta2) * gr * gr;
-      s1[i] = m; s2[i] = v;
-      float r = (m / h.bc1) / (sqrtf(v / h.bc2) + h.eps) + h.wd * w;
-      s3[i] = r;
+      gr *= gmul;
+      a = h.beta1 * a + (1.f - h.beta1) * gr;
+      b = h.beta2 * b + (1.f - h.beta2) * gr * gr;
+      c = (a / h.bc1) / (sqrtf(b / h.bc2) + h.eps) + h.wd * w;
       acc0 += w * w;
-      acc1 += r * r;
+      acc1 += c * c;
     } else if (KIND == K_LAMB2) {
-      float w = ld(p, i) - h.lr * trust * s3[i];
-      st(p, i, w);
-      if (lp) lp[i] = __float2bfloat16(w);
+      w -= h.lr * trust * c;
     } else if (KIND == K_SUMSQ) {
-      float gr = ld(g, i) * gmul;
+      gr *= gmul;
       acc0 += gr * gr;
     } else if (KIND == K_SCALE) {
-      st(g, i, ld(g, i) * gmul);
+      gr *= gmul;
     } else if (KIND == K_UNSCALE_CHECK) {
-      float gr = ld(g, i) * gmul;
+      gr *= gmul;
       if (!isfinite(gr)) bad = 1;
-      st(g, i, gr);
     }
+  };
+  constexpr bool kUsesP = KIND == K_SGD || KIND == K_ADAM || KIND == K_RMSPROP || KIND == K_LAMB1 || KIND == K_LAMB2;
+  constexpr bool kWritesP = KIND == K_SGD || KIND == K_ADAM || KIND == K_RMSPROP || KIND == K_LAMB2;
+  constexpr bool kUsesG = KIND != K_LAMB2;
+  constexpr bool kWritesG = KIND == K_SCALE || KIND == K_UNSCALE_CHECK;
+  constexpr bool kS1 = KIND == K_SGD || KIND == K_ADAM || KIND == K_RMSPROP || KIND == K_LAMB1;
+  constexpr bool kS2 = KIND == K_ADAM || KIND == K_RMSPROP || KIND == K_LAMB1;
+  constexpr bool kS3R = KIND == K_ADAM || KIND == K_RMSPROP || KIND == K_LAMB2;
+  constexpr bool kS3W = KIND == K_ADAM || KIND == K_RMSPROP || KIND == K_LAMB1;
+  const bool use_s1 = kS1 && s1 != nullptr && !(KIND == K_SGD && h.momentum == 0.f);
+  const bool use_s2 = kS2 && s2 != nullptr && !(KIND == K_RMSPROP && h.momentum <= 0.f);
+  const bool use_s3 = s3 != nullptr && ((KIND == K_ADAM && h.amsgrad) || (KIND == K_RMSPROP && h.centered) ||
+                                        KIND == K_LAMB1 || KIND == K_LAMB2);
+  // vector path: 4 elements per thread per iteration when every pointer is 16-byte aligned
+  const uintptr_t al = (kUsesP ? (uintptr_t)p : 0) | (kUsesG ? (uintptr_t)g : 0) | (use_s1 ? (uintptr_t)s1 : 0) |
+                       (use_s2 ? (uintptr_t)s2 : 0) | (use_s3 ? (uintptr_t)s3 : 0) | (uintptr_t)lp;
+  const bool vec = (al & 15) == 0;
+  const long vend = vec ? base + ((end - base) & ~3L) : base;
+  for (long i = base + threadIdx.x * 4L; i < vend; i += blockDim.x * 4L) {
+    float w[4] = {0, 0, 0, 0}, gr[4] = {0, 0, 0, 0}, a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0}, c[4] = {0, 0, 0, 0};
+    if (kUsesP) ld4(p, i, w);
+    if (kUsesG) ld4(g, i, gr);
+    if (use_s1) ld4(s1, i, a);
+    if (use_s2) ld4(s2, i, b);
+    if (use_s3 && kS3R) ld4(s3, i, c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) elem(w[j], gr[j], a[j], b[j], c[j]);
+    if (kWritesP) { st4(p, i, w); if (lp) st4(lp, i, w); }
+    if (kWritesG) st4(g, i, gr);
+    if (use_s1) st4(s1, i, a);
+    if (use_s2) st4(s2, i, b);
+    if (use_s3 && kS3W) st4(s3, i, c);
+  }
+  for (long i = vend + threadIdx.x; i < end; i += blockDim.x) {
+    float w = kUsesP ? ld(p, i) : 0.f, gr = kUsesG ? ld(g, i) : 0.f;
+    float a = use_s1 ? s1[i] : 0.f, b = use_s2 ? s2[i] : 0.f, c = (use_s3 && kS3R) ? s3[i] : 0.f;
+    elem(w, gr, a, b, c);
+    if (kWritesP) { st(p, i, w); if (lp) lp[i] = __float2bfloat16(w); }
+    if (kWritesG) st(g, i, gr);
+    if (use_s1) s1[i] = a;
+    if (use_s2) s2[i] = b;
+    if (use_s3 && kS3W) s3[i] = c;
   }
   if (KIND == K_LAMB1 || KIND == K_SUMSQ) {
     __shared__ float r0[16], r1[16];

@@ -7,5 +7,7 @@ from .comm import (all_gather, all_reduce_max, all_reduce_mean, all_reduce_min, 
                    all_reduce_sum, barrier, broadcast, broadcast_from, gather_tensor,
                    is_main_process, rank, reduce_scatter_mean, reduce_scatter_sum, ring_all_reduce,
                    scatter_tensor, sync_gradient, sync_gradients, world_size)
+from .ddp import (DDP, DistributedDataParallel, GradientBucket, GradientSynchronizer,
+                  GradSyncStrategy)
 from .fsdp import (FSDP, CPUOffload, FSDPMemoryStats, FullyShardedDataParallel, ShardingStrategy)
 from .process_group import ProcessGroup, World

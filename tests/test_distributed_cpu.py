@@ -1,0 +1,217 @@
+"""Multi-rank behaviour on CPU: in-process mock ranks (threads) and real gloo ranks (processes).
+
+The reference only ever drives rank 0 of a mock world (crates/axonml-distributed/src/backend.rs:471-498);
+here every collective is checked numerically across ranks, DDP and FSDP are compared with
+single-process training, and failures are produced on the host only (a rank that never joins, a
+dropped message)."""
+import threading
+
+import pytest
+import torch
+
+from tests._mp import run_ranks
+
+
+# ------------------------------------------------------------------ mock backend (threads)
+def _run_threads(n, fn):
+    from axonml_b200.parallel import MockBackend
+    world = MockBackend.create_world(n, timeout_s=5.0)
+    out, errs = [None] * n, []
+
+    def go(r):
+        try:
+            out[r] = fn(r, world[r])
+        except Exception as e:  # noqa: BLE001
+            errs.append(e)
+    ts = [threading.Thread(target=go, args=(r,)) for r in range(n)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    if errs:
+        raise errs[0]
+    return out
+
+
+def test_mock_collectives():
+    from axonml_b200.parallel import ReduceOp
+
+    def fn(r, be):
+        t = torch.tensor([1.0 + r, 2.0])
+        be.all_reduce(t, ReduceOp.Sum)
+        g = torch.empty(6)
+        be.all_gather(torch.tensor([float(r), 10.0 * r]), g)
+        rs = torch.empty(1)
+        be.reduce_scatter(torch.arange(3.0) + r, rs, ReduceOp.Average)
+        b = torch.tensor([float(r)])
+        be.broadcast(b, 2)
+        be.barrier()
+        if r == 0:
+            be.send(torch.tensor([42.0]), 1, tag=7)
+        got = torch.zeros(1)
+        if r == 1:
+            be.recv(got, 0, tag=7)
+        return t, g, rs, b, got
+    out = _run_threads(3, fn)
+    for r, (t, g, rs, b, got) in enumerate(out):
+        assert t.tolist() == [6.0, 6.0]
+        assert g.tolist() == [0, 0, 1, 10, 2, 20]
+        assert rs.item() == pytest.approx(r + 1.0)
+        assert b.item() == 2.0
+    assert out[1][4].item() == 42.0
+
+
+def test_mock_missing_rank_times_out():
+    from axonml_b200.parallel import CommTimeout, MockBackend
+    world = MockBackend.create_world(2, timeout_s=0.3)
+    with pytest.raises(CommTimeout):
+        world[0].all_reduce(torch.ones(2))       # rank 1 never calls
+    with pytest.raises(CommTimeout):
+        world[0].recv(torch.zeros(1), 1)          # nothing was sent
+
+
+def test_mock_dropped_message_is_detected():
+    from axonml_b200.parallel import CommTimeout, MockBackend
+    world = MockBackend.create_world(2, timeout_s=0.3)
+    world[0].drop_next_message(0, 1, 0)
+    world[0].send(torch.ones(1), 1)
+    with pytest.raises(CommTimeout):
+        world[1].recv(torch.zeros(1), 0)
+
+
+def test_process_group_shapes():
+    from axonml_b200.parallel import ProcessGroup, World, comm
+    pg = ProcessGroup.mock()
+    t = torch.arange(6.0).view(2, 3)
+    assert pg.all_gather_tensor(t).shape == (1, 2, 3)
+    assert pg.reduce_scatter_tensor(t).shape == (2, 3)
+    assert torch.equal(comm.all_reduce_mean(t.clone(), pg), t)
+    w = World.mock()
+    assert w.is_main() and w.world_size() == 1 and w.default_group().rank() == 0
+    assert comm.gather_tensor(t, pg).shape == (2, 3)
+
+
+# ------------------------------------------------------------------ gloo ranks (processes)
+def _collectives(rank, world, be):
+    from axonml_b200.parallel import ProcessGroup, ReduceOp
+    pg = ProcessGroup(be)
+    t = torch.full((4,), float(rank + 1))
+    pg.all_reduce_tensor(t, ReduceOp.Average)
+    g = pg.all_gather_tensor(torch.tensor([float(rank)]))
+    rs = pg.reduce_scatter_tensor(torch.arange(4.0) * (rank + 1), ReduceOp.Sum)
+    sub = pg.backend().new_group([0, 1])
+    return t.tolist(), g.flatten().tolist(), rs.tolist(), sub.world_size()
+
+
+def test_gloo_collectives():
+    res = run_ranks(_collectives, 2)
+    for r in (0, 1):
+        t, g, rs, sw = res[r][1]
+        assert t == [1.5] * 4 and g == [0.0, 1.0] and sw == 2
+        assert rs == [0.0 * 3, 1.0 * 3] if r == 0 else rs == [2.0 * 3, 3.0 * 3]
+
+
+def _lenet_ddp(rank, world, be):
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import DDP, ProcessGroup
+    from axonml_b200.vision import LeNet
+    torch.manual_seed(0)
+    model = LeNet.new()
+    ddp = DDP(model, ProcessGroup(be), bucket_bytes=64 * 1024)
+    opt = optim.SGD(model.parameters(), 0.01).momentum(0.9)
+    g = torch.Generator().manual_seed(7)
+    X = torch.randn(8, 64, 1, 28, 28, generator=g)
+    Y = torch.randint(0, 10, (8, 64), generator=g)
+    lossf = nn.CrossEntropyLoss()
+    for it in range(8):
+        xs, ys = X[it].chunk(world)[rank], Y[it].chunk(world)[rank]
+        opt.zero_grad()
+        loss = lossf(ddp(xs), ys)
+        loss.backward()
+        opt.step()
+    return [p.detach().clone() for p in model.parameters()], ddp.num_buckets()
+
+
+def test_lenet_ddp_matches_single_process():
+    from axonml_b200 import nn, optim
+    from axonml_b200.vision import LeNet
+    res = run_ranks(_lenet_ddp, 2)
+    torch.manual_seed(0)
+    ref = LeNet.new()
+    opt = optim.SGD(ref.parameters(), 0.01).momentum(0.9)
+    g = torch.Generator().manual_seed(7)
+    X = torch.randn(8, 64, 1, 28, 28, generator=g)
+    Y = torch.randint(0, 10, (8, 64), generator=g)
+    for it in range(8):
+        opt.zero_grad()
+        nn.CrossEntropyLoss()(ref(X[it]), Y[it]).backward()
+        opt.step()
+    assert res[0][1][1] > 1
+    for a, b, c in zip(res[0][1][0], res[1][1][0], ref.parameters()):
+        assert torch.allclose(a, b, atol=1e-6)
+        assert torch.allclose(a, c.detach(), atol=2e-5)
+
+
+def _gpt_fsdp(rank, world, be, strategy_name):
+    from axonml_b200 import optim
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    from axonml_b200.parallel import FSDP, ProcessGroup, ShardingStrategy
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=200, n_ctx=32, n_embd=32, n_layer=5, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    m = GPT2LMHead(cfg).gradient_checkpointing_enable(True)
+    m.train()
+    f = FSDP(m, ProcessGroup(be), strategy=ShardingStrategy[strategy_name])
+    opt = optim.AdamW(f.parameters(), 1e-2)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 200, (4, 4, 32), generator=g)
+    losses = []
+    for it in range(4):
+        loss, _ = f.call("forward_with_loss", ids[it].chunk(world)[rank])
+        loss.backward()
+        f.clip_grad_norm(1.0)
+        opt.step()
+        f.zero_grad()
+        losses.append(loss.item())
+    sd = f.full_state_dict()
+    return losses, {k: v for k, v in sd.items()}
+
+
+@pytest.mark.parametrize("strategy", ["FullShard", "ShardGradOp", "NoShard"])
+def test_fsdp_matches_single_process(strategy):
+    from axonml_b200 import optim
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    res = run_ranks(_gpt_fsdp, 2, args=(strategy,))
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=200, n_ctx=32, n_embd=32, n_layer=5, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    ref = GPT2LMHead(cfg)
+    opt = torch.optim.AdamW(ref.parameters(), 1e-2, weight_decay=0.01)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 200, (4, 4, 32), generator=g)
+    for it in range(4):
+        # mean over the two ranks' half-batches == mean of per-half losses
+        l = sum(ref.forward_with_loss(h)[0] for h in ids[it].chunk(2)) / 2
+        l.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad()
+    sd0, sd1 = res[0][1][1], res[1][1][1]
+    for k, v in ref.named_parameters():
+        assert torch.allclose(sd0[k], sd1[k], atol=1e-6), k
+        assert torch.allclose(sd0[k], v.detach(), atol=5e-4), (k, (sd0[k] - v).abs().max())
+
+
+def _waits_for_absent_rank(rank, world, be):
+    from axonml_b200.parallel import CommTimeout
+    try:
+        be.all_reduce(torch.ones(2))
+    except CommTimeout as e:
+        return "timeout: " + str(e)[:40]
+    return "completed"
+
+
+def test_rank_that_never_joins_is_reported():
+    """Rank 1 is never started: rank 0's rendezvous or first collective must fail in bounded time
+    instead of hanging (host-side failure detection)."""
+    res = run_ranks(_waits_for_absent_rank, 2, timeout_s=4.0, expect_all_ok=False, skip_ranks=(1,))
+    st, val = res[0]
+    assert st == "err" or "timeout" in val
