@@ -128,7 +128,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// ---------------------------------------------------------------- TMA (local memory, no multicast)
+// ---------------------------------------------------------------- TMA (plain per-CTA loads and stores)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
                                             int x, int y) {
   asm volatile(
