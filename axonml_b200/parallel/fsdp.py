@@ -66,7 +66,8 @@ class _Buffer:
 class FullyShardedDataParallel(Module):
     def __init__(self, module: torch.nn.Module, process_group: ProcessGroup | None = None, *,
                  units: list | None = None, param_dtype: torch.dtype | None = None,
-                 strategy: ShardingStrategy = ShardingStrategy.FullShard, device=None):
+                 strategy: ShardingStrategy = ShardingStrategy.FullShard, device=None,
+                 fused_adamw: dict | None = None):
         super().__init__()
         self.module = module
         self.pg = process_group or ProcessGroup.mock()
@@ -83,6 +84,9 @@ class FullyShardedDataParallel(Module):
         self._built = False
         self._phase = "idle"
         self._sync = True
+        self._fused_hp = dict(fused_adamw) if fused_adamw else None
+        self._fused = None
+        self._fused_step = 0
         self._build()
 
     # ------------------------------------------------------------------ reference builders
@@ -160,7 +164,7 @@ class FullyShardedDataParallel(Module):
                 u._init_full = None
                 u.lp_shard = u.full
                 u.gathered = True
-            u.bind_grad(torch.zeros(u.padded, dtype=self.param_dtype, device=self.device))
+            u.bind_grad(self._grad_storage(u))
             u.grad_shard = u.grad_flat if u.world == 1 else torch.zeros(
                 u.shard, dtype=self.param_dtype, device=self.device)
             u.master._axon_lp = u.lp_shard
@@ -177,6 +181,32 @@ class FullyShardedDataParallel(Module):
                 if not u.is_root and p.dim() == 2:
                     p._axon_grad_sink = _GradSink(self, u, idx)
         self._built = True
+
+    def _grad_storage(self, u: FlatUnit) -> torch.Tensor:
+        """Flat gradient of a unit: a slice of the symmetric arena when the fused reduce-scatter +
+        AdamW kernel is in use, an ordinary tensor otherwise."""
+        if self._fused_hp is not None and self._fused is None and self.world > 1 and u.world > 1:
+            from . import fused as F
+            from .symm import SymmetricHeap, available
+            if available(self.pg) and self.param_dtype == torch.bfloat16:
+                total = sum(x.padded for x in self.units)
+                self._fused = F.FusedShardedAdamW(SymmetricHeap(self.pg), total)
+                self._arena_off = 0
+                for x in self.units:
+                    x.m1 = torch.zeros(x.shard, dtype=torch.float32, device=self.device)
+                    x.m2 = torch.zeros(x.shard, dtype=torch.float32, device=self.device)
+            else:
+                self._fused_hp = None
+        if self._fused is not None:
+            u.grad_off = self._arena_off
+            self._arena_off += u.padded
+            return self._fused.arena.local[u.grad_off:u.grad_off + u.padded]
+        return torch.zeros(u.padded, dtype=self.param_dtype, device=self.device)
+
+    def fused_optimizer(self):
+        """Handle with the optimizer API for the in-backward fused AdamW (``step`` only advances
+        the step counter: the update itself runs inside backward, fused with the reduce-scatter)."""
+        return _FusedOptimizerHandle(self)
 
     # ------------------------------------------------------------------ gather / release
     def _stream_ctx(self):
@@ -271,6 +301,15 @@ class FullyShardedDataParallel(Module):
         """Mean over ranks of the unit's flat gradient; this rank keeps its shard."""
         if self.world == 1:
             u.master._axon_grad = u.grad_shard
+        elif self._fused is not None and u.world > 1:
+            hp = self._fused_hp
+            with self._stream_ctx():
+                if self._comm is not None:
+                    self._comm.wait_stream(torch.cuda.current_stream())
+                b1, b2 = hp.get("betas", (0.9, 0.999))
+                self._fused.step_unit(u.grad_off, u.shard, u.master.data, u.m1, u.m2, u.lp_shard,
+                                      lr=hp["lr"], beta1=b1, beta2=b2, eps=hp.get("eps", 1e-8),
+                                      wd=hp.get("weight_decay", 0.01), step=self._fused_step + 1)
         else:
             with self._stream_ctx():
                 if self._comm is not None:
@@ -433,6 +472,20 @@ class FullyShardedDataParallel(Module):
                 u.lp_shard.copy_(flat[lo:lo + u.shard].to(self.param_dtype))
             if u.world > 1:
                 u.gathered = False
+
+
+class _FusedOptimizerHandle:
+    def __init__(self, engine: FullyShardedDataParallel):
+        self.engine = engine
+
+    def step(self) -> None:
+        self.engine._fused_step += 1
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.engine.zero_grad()
+
+    def get_lr(self) -> float: return self.engine._fused_hp["lr"]
+    def set_lr(self, lr: float) -> None: self.engine._fused_hp["lr"] = float(lr)
 
 
 class _GradSink:

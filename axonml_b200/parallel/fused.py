@@ -1,0 +1,88 @@
+"""Python drivers of the fused compute+collective kernels (``csrc/kernels/comm.cu``).
+
+* ``FusedAllReduce``    - DDP bucket mean all-reduce + GradScaler unscale + found-inf, one kernel.
+* ``FusedShardedAdamW`` - FSDP reduce-scatter + sharded AdamW (+ push of the updated bf16 shard
+  into every rank's resident parameter buffer), one kernel per flat unit.
+
+Both stage their operands in symmetric memory: DDP copies a bucket into a symmetric staging
+buffer (the bucket itself when it was allocated there), FSDP allocates its flat gradient arena
+symmetrically.  The NCCL path (``all_reduce`` / ``reduce_scatter_tensor``) remains the fallback and
+the baseline that the fused path is measured against.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as N
+from .symm import Communicator, SymmetricHeap, available
+
+
+class FusedAllReduce:
+    def __init__(self, heap: SymmetricHeap, max_numel: int, dtype: torch.dtype, grid_blocks: int = 32):
+        self.heap = heap
+        self.comm = Communicator(heap, grid_blocks)
+        self.dtype = dtype
+        align = 8 * heap.world * 16
+        self.capacity = (max_numel + align - 1) // align * align
+        self.stage = heap.allocate(self.capacity, dtype)
+
+    @classmethod
+    def try_create(cls, pg, max_numel: int, dtype: torch.dtype):
+        if not available(pg) or dtype not in (torch.float32, torch.bfloat16):
+            return None
+        return cls(SymmetricHeap(pg), max_numel, dtype)
+
+    def all_reduce_mean_(self, flat: torch.Tensor, inv_scale=None, found_inf=None) -> None:
+        """In-place mean over ranks of ``flat`` (optionally times ``inv_scale``); sets
+        ``found_inf`` (int32[1]) when any reduced value is not finite."""
+        n = flat.numel()
+        if n > self.capacity or flat.dtype != self.dtype:
+            raise ValueError("bucket does not fit the fused all-reduce staging buffer")
+        esz = flat.element_size()
+        unit = 16 * self.heap.world // esz
+        n_pad = (n + unit - 1) // unit * unit
+        stage = self.stage.local
+        in_place = flat.data_ptr() == stage.data_ptr()
+        if not in_place:
+            stage[:n].copy_(flat)
+            if n_pad > n:
+                stage[n:n_pad].zero_()
+        rc = N.cuda().ax_fused_allreduce(
+            1 if self.dtype == torch.bfloat16 else 0, self.stage.ptr_array(),
+            self.comm.signals.ptr_array(), self.stage.mc(), self.heap.rank, self.heap.world,
+            ctypes.c_long(0), ctypes.c_long(n_pad), N.ptr(inv_scale), N.ptr(found_inf),
+            ctypes.c_uint(self.comm.next_epoch()), self.comm.grid, N.ptr(N.status_word(flat.device)),
+            N.stream_ptr())
+        N.check(rc, "ax_fused_allreduce")
+        if not in_place:
+            flat.copy_(stage[:n])
+
+
+class FusedShardedAdamW:
+    """Owns the symmetric gradient arena of a sharded engine and steps one unit per call."""
+
+    def __init__(self, heap: SymmetricHeap, arena_numel: int, grid_blocks: int = 32):
+        self.heap = heap
+        self.comm = Communicator(heap, grid_blocks)
+        self.arena = heap.allocate(arena_numel, torch.bfloat16)
+        self.params = None          # optional symmetric arena of resident full parameter buffers
+
+    def attach_param_arena(self, numel: int):
+        self.params = self.heap.allocate(numel, torch.bfloat16)
+        return self.params
+
+    def step_unit(self, grad_off_elems: int, shard: int, master, m1, m2, lp, *, lr, beta1, beta2, eps,
+                  wd, step: int, push_off_elems: int | None = None, skip_flag=None) -> None:
+        hyper = (ctypes.c_float * 7)(lr, beta1, beta2, eps, wd, 1 - beta1 ** step, 1 - beta2 ** step)
+        push = self.params if (push_off_elems is not None and self.params is not None) else None
+        rc = N.cuda().ax_fused_rs_adamw(
+            self.arena.ptr_array(), self.comm.signals.ptr_array(), self.arena.mc(), self.heap.rank,
+            self.heap.world, ctypes.c_long(grad_off_elems * 2), ctypes.c_long(shard), N.ptr(master),
+            N.ptr(m1), N.ptr(m2), N.ptr(lp), push.ptr_array() if push else None,
+            push.mc() if push else ctypes.c_void_p(0),
+            ctypes.c_long((push_off_elems or 0) * 2), hyper, N.ptr(skip_flag),
+            ctypes.c_uint(self.comm.next_epoch()), self.comm.grid, N.ptr(N.status_word(master.device)),
+            N.stream_ptr())
+        N.check(rc, "ax_fused_rs_adamw")

@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=4)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
+    ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"],
+                    help="gradient path at N>1: NCCL reduce-scatter + optimizer, or the fused kernel")
     return ap.parse_args()
 
 
@@ -128,8 +130,16 @@ def main():
     model = GPT2LMHead(cfg, device=dev, dtype=torch.bfloat16)
     model.gradient_checkpointing_enable(True)
     model.train()
-    engine = FSDP(model, pg)
-    opt = optim.AdamW(engine.parameters(), 3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    hp = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    use_fused = world > 1 and args.comm in ("auto", "fused")
+    engine = FSDP(model, pg, fused_adamw=hp if use_fused else None)
+    if engine._fused is not None:
+        opt = engine.fused_optimizer()
+        comm_path = "fused reduce-scatter+AdamW kernel (peer memory / NVLS)"
+    else:
+        opt = optim.AdamW(engine.parameters(), hp["lr"], betas=hp["betas"], eps=hp["eps"],
+                          weight_decay=hp["weight_decay"])
+        comm_path = "nccl" if world > 1 else "none (1 GPU)"
 
     B, S = args.micro_batch, args.seq_len
     gen = torch.Generator(device="cpu").manual_seed(99 + rank)
@@ -208,7 +218,7 @@ def main():
             "config": {"model": "gpt-1.3b (24L d2048 16h ffn8192 vocab50257)",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"fsdp{world}-zero3",
                        "optimizer": "AdamW lr3e-4 b(0.9,0.95) wd0.1", "grad_checkpointing": True,
-                       "layers": cfg.n_layer,
+                       "layers": cfg.n_layer, "grad_comm": comm_path,
                        "l2_policy": "per-step working set (weights+optimizer state > 20 GB) far exceeds the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",

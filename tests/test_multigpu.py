@@ -1,0 +1,145 @@
+"""Fused compute+collective kernels on 2+ GPUs against NCCL / single-process references.
+Each case runs as one child process per GPU; the NVLS (multimem) path and the plain peer
+load/store path are both exercised (``AXONML_NVLS=0`` selects the latter)."""
+import pytest
+import torch
+
+from tests._mp_gpu import run_gpu_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu,
+              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
+
+WORLD = 2 if torch.cuda.device_count() < 4 else min(4, torch.cuda.device_count())
+
+
+def _fused_allreduce(rank, world, be, dtype_name):
+    from axonml_b200 import _native
+    from axonml_b200.parallel import ProcessGroup
+    from axonml_b200.parallel.fused import FusedAllReduce
+    dtype = getattr(torch, dtype_name)
+    pg = ProcessGroup(be)
+    far = FusedAllReduce.try_create(pg, 3_000_000, dtype)
+    assert far is not None
+    out = {}
+    for n in (1000, 65536 + 24, 2_500_000):
+        torch.manual_seed(100 + rank)
+        x = torch.randn(n, device="cuda").to(dtype)
+        ref = x.clone().float()
+        torch.distributed.all_reduce(ref)
+        ref = ref / world * 0.5
+        inv = torch.tensor([0.5], device="cuda")
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        far.all_reduce_mean_(x, inv_scale=inv, found_inf=flag)
+        torch.cuda.synchronize()
+        _native.check_status()
+        out[n] = ((x.float() - ref).abs().max().item(), int(flag.item()))
+    # overflow on one rank only must raise the flag on every rank
+    x = torch.ones(4096, device="cuda").to(dtype)
+    if rank == world - 1:
+        x[4000] = float("inf")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    far.all_reduce_mean_(x, found_inf=flag)
+    torch.cuda.synchronize()
+    out["inf"] = int(flag.item())
+    out["mc"] = bool(far.stage.mc_ptr)
+    return out
+
+
+@pytest.mark.parametrize("nvls", ["1", "0"])
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_fused_allreduce(dtype, nvls):
+    res = run_gpu_ranks(_fused_allreduce, WORLD, args=(dtype,), env={"AXONML_NVLS": nvls})
+    tol = 2e-2 if dtype == "bfloat16" else 1e-5
+    for r in range(WORLD):
+        out = res[r][1]
+        for n in (1000, 65536 + 24, 2_500_000):
+            err, flag = out[n]
+            assert err < tol and flag == 0, (n, err, flag)
+        assert out["inf"] == 1
+
+
+def _fsdp_fused_vs_nccl(rank, world, be):
+    import copy
+    from axonml_b200 import _native, optim
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    from axonml_b200.parallel import FSDP, ProcessGroup
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=512, n_ctx=128, n_embd=256, n_layer=4, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    base = GPT2LMHead(cfg, device="cuda", dtype=torch.bfloat16)
+    m1, m2 = copy.deepcopy(base), copy.deepcopy(base)
+    pg = ProcessGroup(be)
+    hp = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    f1 = FSDP(m1, pg)
+    o1 = optim.AdamW(f1.parameters(), hp["lr"], betas=hp["betas"], eps=hp["eps"], weight_decay=hp["weight_decay"])
+    f2 = FSDP(m2, pg, fused_adamw=hp)
+    assert f2._fused is not None
+    o2 = f2.fused_optimizer()
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 512, (3, 2 * world, 128), generator=g).cuda()
+    l1s, l2s = [], []
+    for it in range(3):
+        x = ids[it].chunk(world)[rank]
+        for f, o, ls in ((f1, o1, l1s), (f2, o2, l2s)):
+            loss, _ = f.call("forward_with_loss", x)
+            loss.backward()
+            o.step()
+            f.zero_grad()
+            ls.append(loss.item())
+    torch.cuda.synchronize()
+    _native.check_status()
+    sd1, sd2 = f1.full_state_dict(), f2.full_state_dict()
+    diff = max((sd1[k] - sd2[k]).abs().max().item() for k in sd1)
+    return l1s, l2s, diff
+
+
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fsdp_fused_rs_adamw_matches_nccl_path(nvls):
+    res = run_gpu_ranks(_fsdp_fused_vs_nccl, WORLD, env={"AXONML_NVLS": nvls})
+    for r in range(WORLD):
+        l1, l2, diff = res[r][1]
+        assert abs(l1[-1] - l2[-1]) < 5e-2, (l1, l2)
+        assert diff < 2e-3, diff
+
+
+def _ddp_fused(rank, world, be):
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import DDP, ProcessGroup
+    from axonml_b200.vision import LeNet
+    torch.manual_seed(0)
+    model = LeNet.new().cuda()
+    ddp = DDP(model, ProcessGroup(be), bucket_bytes=64 * 1024)
+    fused = ddp._fused is not None
+    opt = optim.SGD(model.parameters(), 0.01).momentum(0.9)
+    scaler = optim.GradScaler.with_scale(1024.0)
+    ddp.attach_scaler(scaler)
+    g = torch.Generator().manual_seed(7)
+    X = torch.randn(4, 64, 1, 28, 28, generator=g).cuda()
+    Y = torch.randint(0, 10, (4, 64), generator=g).cuda()
+    for it in range(4):
+        xs, ys = X[it].chunk(world)[rank], Y[it].chunk(world)[rank]
+        opt.zero_grad()
+        loss = nn.CrossEntropyLoss()(ddp(xs), ys)
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+    return [p.detach().float().cpu() for p in model.parameters()], fused
+
+
+def test_ddp_fused_allreduce_with_scaler_matches_single_process():
+    from axonml_b200 import nn, optim
+    from axonml_b200.vision import LeNet
+    res = run_gpu_ranks(_ddp_fused, WORLD)
+    assert res[0][1][1], "fused all-reduce was not used"
+    torch.manual_seed(0)
+    ref = LeNet.new()
+    opt = optim.SGD(ref.parameters(), 0.01).momentum(0.9)
+    g = torch.Generator().manual_seed(7)
+    X = torch.randn(4, 64, 1, 28, 28, generator=g)
+    Y = torch.randint(0, 10, (4, 64), generator=g)
+    for it in range(4):
+        opt.zero_grad()
+        nn.CrossEntropyLoss()(ref(X[it]), Y[it]).backward()
+        opt.step()
+    for a, c in zip(res[0][1][0], ref.parameters()):
+        assert torch.allclose(a, c.detach(), atol=2e-3), (a - c).abs().max()
