@@ -25,7 +25,8 @@ def available(pg) -> bool:
     if not (torch.cuda.is_available() and dist.is_initialized() and pg.world_size() > 1):
         return False
     try:
-        import torch.distributed._symmetric_memory  # noqa: F401
+        import importlib
+        importlib.import_module("torch.distributed._symmetric_memory")
         return True
     except Exception:
         return False
@@ -71,10 +72,6 @@ class SymmetricHeap:
         self.group = grp if grp is not None else dist.group.WORLD
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.use_mc = os.environ.get("AXONML_NVLS", "1") != "0"
-        try:
-            symm_mem.enable_symm_mem_for_group(self.group.group_name)
-        except Exception:
-            pass
         self.rank, self.world = pg.rank(), pg.world_size()
 
     def allocate(self, numel: int, dtype: torch.dtype) -> SymmetricBuffer:

@@ -89,17 +89,21 @@ def _fsdp_fused_vs_nccl(rank, world, be):
     torch.cuda.synchronize()
     _native.check_status()
     sd1, sd2 = f1.full_state_dict(), f2.full_state_dict()
+    # Adam moves every element by about lr per step, so single elements whose tiny gradients round
+    # differently (bf16 NCCL reduction vs fp32 in-kernel reduction) may differ by a few lr; the
+    # mean difference must stay far below that.
     diff = max((sd1[k] - sd2[k]).abs().max().item() for k in sd1)
-    return l1s, l2s, diff
+    mean = max((sd1[k] - sd2[k]).abs().mean().item() for k in sd1)
+    return l1s, l2s, diff, mean
 
 
 @pytest.mark.parametrize("nvls", ["1", "0"])
 def test_fsdp_fused_rs_adamw_matches_nccl_path(nvls):
     res = run_gpu_ranks(_fsdp_fused_vs_nccl, WORLD, env={"AXONML_NVLS": nvls})
     for r in range(WORLD):
-        l1, l2, diff = res[r][1]
+        l1, l2, diff, mean = res[r][1]
         assert abs(l1[-1] - l2[-1]) < 5e-2, (l1, l2)
-        assert diff < 2e-3, diff
+        assert diff < 1e-2 and mean < 1e-3, (diff, mean)
 
 
 def _ddp_fused(rank, world, be):
