@@ -1,0 +1,94 @@
+"""Quantisation types (crates/axonml-quant/src/types.rs:17-340): ``QuantType`` with block size,
+bytes per block, bits per value and compression ratio; ``QuantizedTensor`` holding the packed
+blocks.  Q5_0 / Q5_1 are real codecs and Q4_K is added (the reference maps Q5 to Q4_0 and has no
+K-quants)."""
+from __future__ import annotations
+
+import dataclasses
+import enum
+
+import torch
+
+
+class QuantError(Exception):
+    pass
+
+
+class QuantType(enum.Enum):
+    Q8_0 = "q8_0"
+    Q4_0 = "q4_0"
+    Q4_1 = "q4_1"
+    Q5_0 = "q5_0"
+    Q5_1 = "q5_1"
+    Q4_K = "q4_k"
+    F16 = "f16"
+    BF16 = "bf16"
+    F32 = "f32"
+
+    def block_size(self) -> int:
+        return {QuantType.Q4_K: 256, QuantType.F16: 1, QuantType.BF16: 1, QuantType.F32: 1}.get(self, 32)
+
+    def bytes_per_block(self) -> int:
+        return {QuantType.Q8_0: 34, QuantType.Q4_0: 18, QuantType.Q4_1: 20, QuantType.Q5_0: 22,
+                QuantType.Q5_1: 24, QuantType.Q4_K: 144, QuantType.F16: 2, QuantType.BF16: 2,
+                QuantType.F32: 4}[self]
+
+    def bits_per_value(self) -> float:
+        return 8.0 * self.bytes_per_block() / self.block_size()
+
+    def nominal_bits(self) -> int:
+        return {QuantType.Q8_0: 8, QuantType.Q4_0: 4, QuantType.Q4_1: 4, QuantType.Q5_0: 5, QuantType.Q5_1: 5,
+                QuantType.Q4_K: 4, QuantType.F16: 16, QuantType.BF16: 16, QuantType.F32: 32}[self]
+
+    def compression_ratio(self) -> float:
+        return 32.0 / self.nominal_bits()
+
+    def is_block_quantized(self) -> bool:
+        return self not in (QuantType.F16, QuantType.BF16, QuantType.F32)
+
+    def codec_id(self) -> int:
+        return {QuantType.Q8_0: 0, QuantType.Q4_0: 1, QuantType.Q4_1: 2, QuantType.Q5_0: 3,
+                QuantType.Q5_1: 4, QuantType.Q4_K: 5}[self]
+
+    def ggml_type(self) -> int:
+        return {QuantType.F32: 0, QuantType.F16: 1, QuantType.Q4_0: 2, QuantType.Q4_1: 3, QuantType.Q5_0: 6,
+                QuantType.Q5_1: 7, QuantType.Q8_0: 8, QuantType.Q4_K: 12, QuantType.BF16: 30}[self]
+
+    @staticmethod
+    def from_ggml_type(t: int) -> "QuantType":
+        for q in QuantType:
+            if q.ggml_type() == t:
+                return q
+        raise QuantError(f"unsupported GGML tensor type {t}")
+
+    @staticmethod
+    def from_str(s: str):
+        s = s.strip().lower().replace("-", "_")
+        alias = {"q8": "q8_0", "int8": "q8_0", "q4": "q4_0", "int4": "q4_0", "q5": "q5_0", "fp16": "f16",
+                 "half": "f16", "fp32": "f32", "float": "f32", "q4k": "q4_k", "q4_k_m": "q4_k"}
+        s = alias.get(s, s)
+        for q in QuantType:
+            if q.value == s:
+                return q
+        return None
+
+
+@dataclasses.dataclass
+class QuantizedTensor:
+    shape: list
+    quant_type: QuantType
+    data: torch.Tensor            # uint8, packed blocks in row order
+    layout: str = "ggml"          # "ggml" or "adjacent" (the reference's nibble order, Q4 only)
+
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def size_bytes(self) -> int: return self.data.numel()
+    def num_blocks(self) -> int: return self.data.numel() // self.quant_type.bytes_per_block()
+    def compression_ratio(self) -> float: return 4.0 * self.numel() / max(1, self.size_bytes())
+
+    def to(self, device) -> "QuantizedTensor":
+        return QuantizedTensor(self.shape, self.quant_type, self.data.to(device), self.layout)

@@ -1,0 +1,75 @@
+"""Key converters between naming schemes (crates/axonml-serialize/src/convert.rs:20-263):
+PyTorch <-> AxonML names, ``transpose_linear_weights``, ``OnnxOpType``."""
+from __future__ import annotations
+
+import enum
+
+from .state_dict import StateDict, StateDictEntry, TensorData
+
+
+def convert_from_pytorch_key(key: str) -> str:
+    """``module.`` (DataParallel) and ``_orig_mod.`` (compiled) prefixes are dropped; BatchNorm
+    bookkeeping keeps its name."""
+    for p in ("module.", "_orig_mod."):
+        if key.startswith(p):
+            key = key[len(p):]
+    return key
+
+
+def convert_to_pytorch_key(key: str) -> str:
+    return key
+
+
+def from_pytorch_state_dict(tensors: dict) -> StateDict:
+    sd = StateDict()
+    for k, v in tensors.items():
+        if k.endswith("num_batches_tracked"):
+            continue
+        sd.insert(convert_from_pytorch_key(k), TensorData.from_tensor(v))
+    sd.set_metadata("source", "pytorch")
+    return sd
+
+
+def to_pytorch_state_dict(sd: StateDict) -> dict:
+    return {convert_to_pytorch_key(k): e.data.to_tensor() for k, e in sd.entries()}
+
+
+def pytorch_layer_mapping() -> dict:
+    return {"Linear": "Linear", "Conv2d": "Conv2d", "BatchNorm2d": "BatchNorm2d", "LayerNorm": "LayerNorm",
+            "Embedding": "Embedding", "LSTM": "LSTM", "GRU": "GRU", "MultiheadAttention": "MultiHeadAttention"}
+
+
+def transpose_linear_weights(sd: StateDict) -> StateDict:
+    """Transposes every 2-D ``*.weight`` (for frameworks that store Linear as [in, out])."""
+    out = StateDict()
+    for k, e in sd.entries():
+        if k.endswith("weight") and len(e.data.shape) == 2:
+            t = e.data.to_tensor().t().contiguous()
+            out.insert_entry(k, StateDictEntry(TensorData.from_tensor(t), e.requires_grad, dict(e.metadata)))
+        else:
+            out.insert_entry(k, e)
+    out.metadata = dict(sd.metadata)
+    return out
+
+
+class OnnxOpType(enum.Enum):
+    Gemm = "Gemm"
+    MatMul = "MatMul"
+    Conv = "Conv"
+    Relu = "Relu"
+    Sigmoid = "Sigmoid"
+    Tanh = "Tanh"
+    Softmax = "Softmax"
+    BatchNormalization = "BatchNormalization"
+    MaxPool = "MaxPool"
+    AveragePool = "AveragePool"
+    Flatten = "Flatten"
+    Add = "Add"
+    Dropout = "Dropout"
+
+    @staticmethod
+    def from_layer(name: str):
+        return {"Linear": OnnxOpType.Gemm, "Conv2d": OnnxOpType.Conv, "ReLU": OnnxOpType.Relu,
+                "Sigmoid": OnnxOpType.Sigmoid, "Tanh": OnnxOpType.Tanh, "Softmax": OnnxOpType.Softmax,
+                "BatchNorm2d": OnnxOpType.BatchNormalization, "MaxPool2d": OnnxOpType.MaxPool,
+                "AvgPool2d": OnnxOpType.AveragePool, "Dropout": OnnxOpType.Dropout}.get(name)
