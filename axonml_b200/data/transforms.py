@@ -1,0 +1,82 @@
+"""Tensor transforms (crates/axonml-data/src/transforms.rs:16-550)."""
+from __future__ import annotations
+
+import torch
+
+
+class Transform:
+    def apply(self, x): raise NotImplementedError
+    def __call__(self, x): return self.apply(x)
+
+
+class Compose(Transform):
+    def __init__(self, transforms): self.transforms = list(transforms)
+    @classmethod
+    def new(cls, transforms): return cls(transforms)
+    def add(self, t): self.transforms.append(t); return self
+    def apply(self, x):
+        for t in self.transforms:
+            x = t(x)
+        return x
+
+
+class ToTensor(Transform):
+    def apply(self, x): return torch.as_tensor(x, dtype=torch.float32)
+
+
+class Normalize(Transform):
+    def __init__(self, mean, std): self.mean, self.std = mean, std
+    @classmethod
+    def new(cls, mean, std): return cls(mean, std)
+    @classmethod
+    def standard(cls): return cls(0.0, 1.0)
+    def apply(self, x): return (x - self.mean) / self.std
+
+
+class RandomNoise(Transform):
+    def __init__(self, std: float): self.std = std
+    def apply(self, x): return x + torch.randn_like(x) * self.std
+
+
+class RandomCrop(Transform):
+    def __init__(self, size): self.size = (size, size) if isinstance(size, int) else tuple(size)
+    def apply(self, x):
+        h, w = x.shape[-2:]
+        th, tw = self.size
+        i = int(torch.randint(0, h - th + 1, ())) if h > th else 0
+        j = int(torch.randint(0, w - tw + 1, ())) if w > tw else 0
+        return x[..., i:i + th, j:j + tw]
+
+
+class RandomFlip(Transform):
+    def __init__(self, dim: int = -1, p: float = 0.5): self.dim, self.p = dim, p
+    def apply(self, x): return x.flip(self.dim) if float(torch.rand(())) < self.p else x
+
+
+class Scale(Transform):
+    def __init__(self, factor: float): self.factor = factor
+    def apply(self, x): return x * self.factor
+
+
+class Clamp(Transform):
+    def __init__(self, lo: float, hi: float): self.lo, self.hi = lo, hi
+    def apply(self, x): return x.clamp(self.lo, self.hi)
+
+
+class Flatten(Transform):
+    def apply(self, x): return x.flatten()
+
+
+class Reshape(Transform):
+    def __init__(self, shape): self.shape = tuple(shape)
+    def apply(self, x): return x.reshape(self.shape)
+
+
+class DropoutTransform(Transform):
+    def __init__(self, p: float): self.p = p
+    def apply(self, x): return torch.nn.functional.dropout(x, self.p, True)
+
+
+class Lambda(Transform):
+    def __init__(self, fn): self.fn = fn
+    def apply(self, x): return self.fn(x)

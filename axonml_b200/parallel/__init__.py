@@ -11,3 +11,6 @@ from .ddp import (DDP, DistributedDataParallel, GradientBucket, GradientSynchron
                   GradSyncStrategy)
 from .fsdp import (FSDP, CPUOffload, FSDPMemoryStats, FullyShardedDataParallel, ShardingStrategy)
 from .process_group import ProcessGroup, World
+from .pipeline import Pipeline, PipelineMemoryStats, PipelineSchedule, PipelineStage
+from .tensor_parallel import (ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding,
+                              vocab_parallel_cross_entropy)

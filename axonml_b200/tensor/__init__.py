@@ -1,0 +1,10 @@
+"""Tensor facade (crates/axonml-tensor): ``Tensor`` is ``torch.Tensor``; creation functions, views,
+operations and sparse formats keep the reference's names."""
+import torch
+
+from . import ops, sparse, view
+from .creation import (arange, diag, empty, eye, from_vec, full, full_like, linspace, logspace, normal,
+                       ones, ones_like, rand, randint, randn, scalar, uniform, zeros, zeros_like)
+from .sparse import SparseCOO, SparseCSR
+
+Tensor = torch.Tensor

@@ -215,3 +215,67 @@ def test_rank_that_never_joins_is_reported():
     res = run_ranks(_waits_for_absent_rank, 2, timeout_s=4.0, expect_all_ok=False, skip_ranks=(1,))
     st, val = res[0]
     assert st == "err" or "timeout" in val
+
+
+# ------------------------------------------------------------------ tensor / pipeline parallel
+def _tp_block(rank, world, be):
+    from axonml_b200.parallel import ColumnParallelLinear, ProcessGroup, RowParallelLinear
+    pg = ProcessGroup(be)
+    torch.manual_seed(0)
+    Wc, Wr = torch.randn(16, 8) * 0.3, torch.randn(8, 16) * 0.3
+    x = torch.randn(6 * world, 8)
+    col = ColumnParallelLinear(8, 16, True, pg, sequence_parallel=True, activation="gelu")
+    row = RowParallelLinear(16, 8, True, pg, sequence_parallel=True)
+    n = 16 // world
+    with torch.no_grad():
+        col.weight.copy_(Wc[rank * n:(rank + 1) * n])
+        row.weight.copy_(Wr[:, rank * n:(rank + 1) * n])
+    xl = x.chunk(world)[rank].clone().requires_grad_(True)
+    y = row(col(xl))
+    y.sum().backward()
+    return y.detach(), xl.grad, col.weight.grad, row.weight.grad
+
+
+def test_tensor_parallel_sequence_parallel_block():
+    res = run_ranks(_tp_block, 2)
+    torch.manual_seed(0)
+    Wc, Wr = (torch.randn(16, 8) * 0.3).requires_grad_(), (torch.randn(8, 16) * 0.3).requires_grad_()
+    x = torch.randn(12, 8, requires_grad=True)
+    y = torch.nn.functional.gelu(x @ Wc.t(), approximate="tanh") @ Wr.t()
+    y.sum().backward()
+    for r in (0, 1):
+        yl, xg, cg, rg = res[r][1]
+        assert torch.allclose(yl, y.detach().chunk(2)[r], atol=1e-5)
+        assert torch.allclose(xg, x.grad.chunk(2)[r], atol=1e-5)
+        assert torch.allclose(cg, Wc.grad[r * 8:(r + 1) * 8], atol=1e-5)
+        assert torch.allclose(rg, Wr.grad[:, r * 8:(r + 1) * 8], atol=1e-5)
+
+
+def _pipeline(rank, world, be, schedule):
+    from axonml_b200 import nn
+    from axonml_b200.parallel import Pipeline, PipelineSchedule, ProcessGroup
+    torch.manual_seed(0)
+    mods = [nn.Sequential(nn.Linear(4, 8), nn.Tanh()), nn.Sequential(nn.Linear(8, 3))]
+    pipe = Pipeline.from_modules(mods, ProcessGroup(be)).schedule(PipelineSchedule[schedule]).num_microbatches(4)
+    g = torch.Generator().manual_seed(1)
+    x, t = torch.randn(8, 4, generator=g), torch.randn(8, 3, generator=g)
+    loss = pipe.train_step(x if rank == 0 else None, t if rank == world - 1 else None,
+                           lambda y, tt: ((y - tt) ** 2).mean())
+    grads = [p.grad.clone() for p in mods[rank].parameters()]
+    return (loss if loss is not None else torch.zeros(())), grads
+
+
+@pytest.mark.parametrize("schedule", ["GPipe", "OneFOneBSchedule"])
+def test_pipeline_schedules_match_single_process(schedule):
+    from axonml_b200 import nn
+    res = run_ranks(_pipeline, 2, args=(schedule,))
+    torch.manual_seed(0)
+    mods = [nn.Sequential(nn.Linear(4, 8), nn.Tanh()), nn.Sequential(nn.Linear(8, 3))]
+    g = torch.Generator().manual_seed(1)
+    x, t = torch.randn(8, 4, generator=g), torch.randn(8, 3, generator=g)
+    loss = sum(((mods[1](mods[0](xm)) - tm) ** 2).mean() / 4 for xm, tm in zip(x.chunk(4), t.chunk(4)))
+    loss.backward()
+    assert abs(res[1][1][0].item() - loss.item()) < 1e-5
+    for r in (0, 1):
+        for a, p in zip(res[r][1][1], mods[r].parameters()):
+            assert torch.allclose(a, p.grad, atol=1e-5)

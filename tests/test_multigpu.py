@@ -93,7 +93,9 @@ def _fsdp_fused_vs_nccl(rank, world, be):
     # differently (bf16 NCCL reduction vs fp32 in-kernel reduction) may differ by a few lr; the
     # mean difference must stay far below that.
     diff = max((sd1[k] - sd2[k]).abs().max().item() for k in sd1)
-    mean = max((sd1[k] - sd2[k]).abs().mean().item() for k in sd1)
+    # global mean: the key-bias third of c_attn.bias has a mathematically zero gradient (softmax is
+    # shift invariant), so Adam turns pure rounding noise into +-lr steps there on both paths
+    mean = sum((sd1[k] - sd2[k]).abs().sum().item() for k in sd1) / sum(v.numel() for v in sd1.values())
     return l1s, l2s, diff, mean
 
 
@@ -103,7 +105,7 @@ def test_fsdp_fused_rs_adamw_matches_nccl_path(nvls):
     for r in range(WORLD):
         l1, l2, diff, mean = res[r][1]
         assert abs(l1[-1] - l2[-1]) < 5e-2, (l1, l2)
-        assert diff < 1e-2 and mean < 1e-3, (diff, mean)
+        assert diff < 1e-2 and mean < 1e-4, (diff, mean)
 
 
 def _ddp_fused(rank, world, be):
