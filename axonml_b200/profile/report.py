@@ -1,0 +1,77 @@
+"""Profile reports in text / JSON / Markdown / HTML (crates/axonml-profile/src/report.rs:17-359)."""
+from __future__ import annotations
+
+import dataclasses
+import enum
+import json
+
+from .bottleneck import BottleneckAnalyzer
+
+
+class ReportFormat(enum.Enum):
+    Text = "text"
+    Json = "json"
+    Markdown = "markdown"
+    Html = "html"
+
+
+@dataclasses.dataclass
+class ProfileReport:
+    operations: list
+    total_time_ms: float
+    peak_memory: int
+    current_memory: int
+    bottlenecks: list
+    device_memory: dict
+
+    @classmethod
+    def generate(cls, profiler) -> "ProfileReport":
+        ops = profiler.compute.top(1000)
+        return cls([dataclasses.asdict(s) | {"avg_ns": s.avg_ns(), "gflops": s.gflops(), "gbps": s.gbps()} for s in ops],
+                   profiler.compute.total_time_ns() / 1e6, profiler.memory.peak, profiler.memory.current,
+                   [dataclasses.asdict(b) | {"kind": b.kind.value} for b in BottleneckAnalyzer().analyze(profiler)],
+                   profiler.memory.device_stats())
+
+    def format(self, fmt: ReportFormat) -> str:
+        return {ReportFormat.Text: self.to_text, ReportFormat.Json: self.to_json,
+                ReportFormat.Markdown: self.to_markdown, ReportFormat.Html: self.to_html}[fmt]()
+
+    def _rows(self):
+        for o in self.operations:
+            yield (o["name"], o["count"], o["total_ns"] / 1e6, o["avg_ns"] / 1e3, o["gflops"], o["gbps"])
+
+    def to_text(self) -> str:
+        lines = [f"=== Profile: {self.total_time_ms:.3f} ms total, peak memory {self.peak_memory} B ===",
+                 f"{'operation':32s} {'calls':>8s} {'total ms':>10s} {'avg us':>10s} {'GFLOPS':>9s} {'GB/s':>8s}"]
+        for n, c, t, a, g, b in self._rows():
+            lines.append(f"{n[:32]:32s} {c:8d} {t:10.3f} {a:10.2f} {g:9.2f} {b:8.2f}")
+        for b in self.bottlenecks:
+            lines.append(f"[{b['kind']}] {b['description']} -> {b['suggestion']}")
+        return "\n".join(lines)
+
+    def to_json(self) -> str: return json.dumps(dataclasses.asdict(self), indent=2, default=str)
+
+    def to_markdown(self) -> str:
+        lines = [f"# Profile report\n\nTotal {self.total_time_ms:.3f} ms, peak memory {self.peak_memory} bytes\n",
+                 "| operation | calls | total ms | avg us | GFLOPS | GB/s |", "|---|---|---|---|---|---|"]
+        for n, c, t, a, g, b in self._rows():
+            lines.append(f"| {n} | {c} | {t:.3f} | {a:.2f} | {g:.2f} | {b:.2f} |")
+        if self.bottlenecks:
+            lines.append("\n## Bottlenecks\n")
+            lines += [f"- **{b['kind']}** {b['description']} — {b['suggestion']}" for b in self.bottlenecks]
+        return "\n".join(lines)
+
+    def to_html(self) -> str:
+        rows = "".join(f"<tr><td>{n}</td><td>{c}</td><td>{t:.3f}</td><td>{a:.2f}</td><td>{g:.2f}</td><td>{b:.2f}</td></tr>"
+                       for n, c, t, a, g, b in self._rows())
+        return ("<html><body><h1>Profile report</h1>"
+                f"<p>Total {self.total_time_ms:.3f} ms, peak memory {self.peak_memory} bytes</p>"
+                "<table border=1><tr><th>operation</th><th>calls</th><th>total ms</th><th>avg us</th>"
+                f"<th>GFLOPS</th><th>GB/s</th></tr>{rows}</table></body></html>")
+
+    def save(self, path, fmt: ReportFormat | None = None) -> None:
+        if fmt is None:
+            ext = str(path).rsplit(".", 1)[-1].lower()
+            fmt = {"json": ReportFormat.Json, "md": ReportFormat.Markdown, "html": ReportFormat.Html}.get(ext, ReportFormat.Text)
+        with open(path, "w") as f:
+            f.write(self.format(fmt))
