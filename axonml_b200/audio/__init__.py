@@ -1,0 +1,4 @@
+"""Audio processing (crates/axonml-audio)."""
+from .datasets import SyntheticCommandDataset, SyntheticMusicDataset, SyntheticSpeakerDataset
+from .transforms import (MFCC, AddNoise, MelSpectrogram, NormalizeAudio, PitchShift, Resample, TimeStretch,
+                         TrimSilence, mel_filterbank)

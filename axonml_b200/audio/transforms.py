@@ -1,0 +1,107 @@
+"""Audio transforms (crates/axonml-audio/src/transforms.rs:18-517): Resample, MelSpectrogram
+(STFT via torch.fft instead of the reference's own DFT loop), MFCC, TimeStretch, PitchShift,
+AddNoise, NormalizeAudio, TrimSilence."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from ..data.transforms import Transform
+
+
+class Resample(Transform):
+    def __init__(self, orig_freq: int, new_freq: int): self.orig, self.new = orig_freq, new_freq
+    @classmethod
+    def new(cls, orig_freq, new_freq): return cls(orig_freq, new_freq)
+    def apply(self, x):
+        if self.orig == self.new:
+            return x
+        n = int(round(x.shape[-1] * self.new / self.orig))
+        return F.interpolate(x.reshape(1, 1, -1).float(), size=n, mode="linear", align_corners=False).reshape(*x.shape[:-1], n)
+
+
+def _hz_to_mel(f): return 2595.0 * math.log10(1.0 + f / 700.0)
+def _mel_to_hz(m): return 700.0 * (10 ** (m / 2595.0) - 1.0)
+
+
+def mel_filterbank(n_mels: int, n_fft: int, sample_rate: int, f_min: float = 0.0, f_max: float | None = None):
+    f_max = f_max or sample_rate / 2
+    pts = torch.linspace(_hz_to_mel(f_min), _hz_to_mel(f_max), n_mels + 2)
+    hz = torch.tensor([_mel_to_hz(float(m)) for m in pts])
+    bins = torch.floor((n_fft + 1) * hz / sample_rate).long()
+    fb = torch.zeros(n_mels, n_fft // 2 + 1)
+    for m in range(1, n_mels + 1):
+        l, c, r = int(bins[m - 1]), int(bins[m]), int(bins[m + 1])
+        for k in range(l, c):
+            fb[m - 1, k] = (k - l) / max(c - l, 1)
+        for k in range(c, r):
+            fb[m - 1, k] = (r - k) / max(r - c, 1)
+    return fb
+
+
+class MelSpectrogram(Transform):
+    def __init__(self, sample_rate: int = 16000, n_fft: int = 400, hop_length: int = 160, n_mels: int = 40):
+        self.sr, self.n_fft, self.hop, self.n_mels = sample_rate, n_fft, hop_length, n_mels
+        self.fb = mel_filterbank(n_mels, n_fft, sample_rate)
+
+    @classmethod
+    def new(cls, sample_rate=16000): return cls(sample_rate)
+    @classmethod
+    def with_params(cls, sample_rate, n_fft, hop_length, n_mels): return cls(sample_rate, n_fft, hop_length, n_mels)
+
+    def apply(self, x):
+        x = x.float()
+        spec = torch.stft(x, self.n_fft, self.hop, window=torch.hann_window(self.n_fft, device=x.device),
+                          return_complex=True, center=True).abs() ** 2
+        return self.fb.to(x.device) @ spec
+
+
+class MFCC(Transform):
+    def __init__(self, sample_rate: int = 16000, n_mfcc: int = 13, n_mels: int = 40):
+        self.mel, self.n_mfcc = MelSpectrogram(sample_rate, n_mels=n_mels), n_mfcc
+        n = n_mels
+        k = torch.arange(n_mfcc).unsqueeze(1)
+        i = torch.arange(n).unsqueeze(0)
+        self.dct = torch.cos(math.pi / n * (i + 0.5) * k) * math.sqrt(2.0 / n)
+
+    @classmethod
+    def new(cls, sample_rate=16000, n_mfcc=13): return cls(sample_rate, n_mfcc)
+    def apply(self, x): return self.dct.to(x.device) @ torch.log(self.mel(x) + 1e-6)
+
+
+class TimeStretch(Transform):
+    def __init__(self, rate: float): self.rate = rate
+    def apply(self, x):
+        n = max(1, int(round(x.shape[-1] / self.rate)))
+        return F.interpolate(x.reshape(1, 1, -1).float(), size=n, mode="linear", align_corners=False).reshape(*x.shape[:-1], n)
+
+
+class PitchShift(Transform):
+    def __init__(self, semitones: float): self.semitones = semitones
+    def apply(self, x):
+        rate = 2.0 ** (self.semitones / 12.0)
+        y = TimeStretch(rate)(x)                       # changes pitch and duration ...
+        return F.interpolate(y.reshape(1, 1, -1), size=x.shape[-1], mode="linear", align_corners=False).reshape(x.shape)
+
+
+class AddNoise(Transform):
+    def __init__(self, snr_db: float = 20.0): self.snr_db = snr_db
+    def apply(self, x):
+        p = x.float().pow(2).mean().clamp_min(1e-12)
+        return x + torch.randn_like(x.float()) * torch.sqrt(p / (10 ** (self.snr_db / 10)))
+
+
+class NormalizeAudio(Transform):
+    def __init__(self, peak: float = 1.0): self.peak = peak
+    def apply(self, x): return x * (self.peak / x.abs().max().clamp_min(1e-12))
+
+
+class TrimSilence(Transform):
+    def __init__(self, threshold_db: float = -40.0): self.thr = 10 ** (threshold_db / 20.0)
+    def apply(self, x):
+        idx = (x.abs() > self.thr * x.abs().max().clamp_min(1e-12)).nonzero()
+        if idx.numel() == 0:
+            return x
+        return x[..., int(idx[:, -1].min()): int(idx[:, -1].max()) + 1]
