@@ -64,7 +64,7 @@ def run_ranks(fn, world: int = 2, args=(), timeout_s: float = 60.0, expect_all_o
     for r in range(world):
         if r in skip_ranks:
             continue
-        p = ctx.Process(target=_entry, args=(r, world, port, fn, args, q, timeout_s))
+        p = ctx.Process(target=_entry, args=(r, world, port, fn, args, q, timeout_s), daemon=True)
         p.start()
         procs.append(p)
     res = {}

@@ -32,16 +32,20 @@ def run_gpu_ranks(fn, world: int = 2, args=(), env=None, timeout_s: float = 180.
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, dict(env or {}))) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, dict(env or {})), daemon=True)
+             for r in range(world)]
     [p.start() for p in procs]
     res = {}
-    for _ in procs:
-        r, st, val = q.get(timeout=timeout_s)
-        res[r] = (st, _unplain(val))
-    for p in procs:
-        p.join(30)
-        if p.is_alive():
-            p.kill()
+    try:
+        for _ in procs:
+            r, st, val = q.get(timeout=timeout_s)
+            res[r] = (st, _unplain(val))
+    finally:
+        # a rank that is stuck must not keep the test process alive
+        for p in procs:
+            p.join(10 if len(res) == len(procs) else 0.1)
+            if p.is_alive():
+                p.kill()
     for r, (st, val) in res.items():
         assert st == "ok", f"rank {r}: {val}"
     return res
