@@ -5,3 +5,7 @@ from .generation import BeamSearch, GenerationConfig, TextGenerator
 from .gpt2 import GPT2, CausalSelfAttention, FeedForward, GPT2Embedding, GPT2LMHead, TransformerBlock
 from .llama import (LLaMA, LLaMAAttention, LLaMADecoderLayer, LLaMAForCausalLM, LLaMAMLP,
                     RotaryEmbedding)
+from .bert import Bert, BertForMaskedLM, BertForSequenceClassification
+from .hf_loader import (HFLoader, HFTokenizer, LoadStateDict, map_gpt2_weights, map_llama_weights,
+                        map_llama_weights_alt)
+from .mistral_phi import Mistral, MistralForCausalLM, Phi, PhiForCausalLM

@@ -1,0 +1,106 @@
+"""Vision datasets (crates/axonml-vision/src/datasets): MNIST / FashionMNIST from IDX files,
+CIFAR-10/100 from the binary batches, and deterministic synthetic stand-ins.  Targets are class
+indices (the reference returns one-hot rows that its own CrossEntropyLoss cannot consume)."""
+from __future__ import annotations
+
+import gzip
+import os
+import struct
+
+import numpy as np
+import torch
+
+from ..data.dataset import Dataset
+
+
+def read_idx(path) -> np.ndarray:
+    op = gzip.open if str(path).endswith(".gz") else open
+    with op(path, "rb") as f:
+        zero, dtype, nd = struct.unpack(">HBB", f.read(4))
+        shape = struct.unpack(">" + "I" * nd, f.read(4 * nd))
+        dt = {8: np.uint8, 9: np.int8, 11: ">i2", 12: ">i4", 13: ">f4", 14: ">f8"}[dtype]
+        return np.frombuffer(f.read(), dtype=dt).reshape(shape)
+
+
+class MNIST(Dataset):
+    FILES = {True: ("train-images-idx3-ubyte", "train-labels-idx1-ubyte"), False: ("t10k-images-idx3-ubyte", "t10k-labels-idx1-ubyte")}
+
+    def __init__(self, root: str, train: bool = True):
+        img, lab = self.FILES[train]
+        def find(n):
+            for c in (n, n + ".gz"):
+                if os.path.exists(os.path.join(root, c)):
+                    return os.path.join(root, c)
+            raise FileNotFoundError(os.path.join(root, n))
+        self.images = torch.from_numpy(read_idx(find(img)).copy()).float().div_(255.0).unsqueeze(1)
+        self.labels = torch.from_numpy(read_idx(find(lab)).copy()).long()
+
+    @classmethod
+    def new(cls, root, train=True): return cls(root, train)
+    def len(self) -> int: return self.images.shape[0]
+    def get(self, i): return self.images[i], self.labels[i]
+
+
+class FashionMNIST(MNIST):
+    CLASSES = ["T-shirt/top", "Trouser", "Pullover", "Dress", "Coat", "Sandal", "Shirt", "Sneaker", "Bag", "Ankle boot"]
+
+
+class CIFAR10(Dataset):
+    NUM_FINE, REC = 10, 3073
+
+    def __init__(self, root: str, train: bool = True):
+        files = [f"data_batch_{i}.bin" for i in range(1, 6)] if train else ["test_batch.bin"]
+        raw = np.concatenate([np.fromfile(os.path.join(root, f), dtype=np.uint8) for f in files]).reshape(-1, self.REC)
+        self.labels = torch.from_numpy(raw[:, self.REC - 3073].astype(np.int64))
+        self.images = torch.from_numpy(raw[:, -3072:].copy()).float().div_(255.0).view(-1, 3, 32, 32)
+
+    def len(self) -> int: return self.images.shape[0]
+    def get(self, i): return self.images[i], self.labels[i]
+
+
+class CIFAR100(CIFAR10):
+    NUM_FINE, REC = 100, 3074
+
+    def __init__(self, root: str, train: bool = True):
+        raw = np.fromfile(os.path.join(root, "train.bin" if train else "test.bin"), dtype=np.uint8).reshape(-1, self.REC)
+        self.labels = torch.from_numpy(raw[:, 1].astype(np.int64))
+        self.images = torch.from_numpy(raw[:, 2:].copy()).float().div_(255.0).view(-1, 3, 32, 32)
+
+
+class _SyntheticImages(Dataset):
+    def __init__(self, n, shape, classes, seed):
+        self.n, self.shape, self.classes, self.seed = n, shape, classes, seed
+
+    def len(self) -> int: return self.n
+    def num_classes(self) -> int: return self.classes
+
+    def get(self, i):
+        g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
+        label = i % self.classes
+        img = torch.rand(self.shape, generator=g) * 0.3
+        c, h, w = self.shape
+        r = (label * 2 + 2) % (h - 4)
+        img[:, r:r + 4, :] += 0.6           # a class-dependent bright band makes the task learnable
+        return img.clamp_(0, 1), torch.tensor(label, dtype=torch.long)
+
+
+class SyntheticMNIST(_SyntheticImages):
+    def __init__(self, num_samples: int = 1000, seed: int = 42): super().__init__(num_samples, (1, 28, 28), 10, seed)
+    @classmethod
+    def new(cls, num_samples=1000): return cls(num_samples)
+
+
+class SyntheticCIFAR(_SyntheticImages):
+    def __init__(self, num_samples: int = 1000, num_classes: int = 10, seed: int = 42): super().__init__(num_samples, (3, 32, 32), num_classes, seed)
+    @classmethod
+    def new(cls, num_samples=1000): return cls(num_samples)
+
+
+class SyntheticImageNet(_SyntheticImages):
+    """N(0,1) 3x224x224 images with uniform random labels in [0, 1000) (benchmark input shape)."""
+
+    def __init__(self, num_samples: int = 1024, seed: int = 0): super().__init__(num_samples, (3, 224, 224), 1000, seed)
+
+    def get(self, i):
+        g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
+        return torch.randn(self.shape, generator=g), torch.randint(0, 1000, (), generator=g)

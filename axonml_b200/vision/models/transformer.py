@@ -1,0 +1,117 @@
+"""Transformer encoder / decoder and VisionTransformer tiny/small/base/large
+(crates/axonml-vision/src/models/transformer.rs)."""
+from __future__ import annotations
+
+import torch
+
+from ... import nn
+from ...ops.attention import sdpa
+
+
+class _MHA(nn.Module):
+    def __init__(self, d_model: int, nhead: int, dropout: float = 0.0):
+        super().__init__()
+        self.h, self.hd = nhead, d_model // nhead
+        self.q_proj, self.k_proj = nn.Linear(d_model, d_model), nn.Linear(d_model, d_model)
+        self.v_proj, self.out_proj = nn.Linear(d_model, d_model), nn.Linear(d_model, d_model)
+
+    def forward(self, q, k, v, causal=False):
+        B, Sq, E = q.shape
+        Sk = k.shape[1]
+        o = sdpa(self.q_proj(q).view(B, Sq, self.h, self.hd), self.k_proj(k).view(B, Sk, self.h, self.hd),
+                 self.v_proj(v).view(B, Sk, self.h, self.hd), causal=causal)
+        return self.out_proj(o.reshape(B, Sq, E))
+
+
+class TransformerEncoderLayer(nn.Module):
+    def __init__(self, d_model: int, nhead: int, dim_feedforward: int = 2048, dropout: float = 0.1, activation: str = "gelu"):
+        super().__init__()
+        self.attn = _MHA(d_model, nhead, dropout)
+        self.norm1, self.norm2 = nn.LayerNorm(d_model), nn.LayerNorm(d_model)
+        self.fc1 = nn.Linear(d_model, dim_feedforward, activation=activation)
+        self.fc2 = nn.Linear(dim_feedforward, d_model)
+        self.drop = nn.Dropout(dropout)
+
+    def forward(self, x):
+        h = self.norm1(x)
+        x = x + self.drop(self.attn(h, h, h))
+        return x + self.drop(self.fc2(self.fc1(self.norm2(x))))
+
+
+class TransformerDecoderLayer(nn.Module):
+    def __init__(self, d_model: int, nhead: int, dim_feedforward: int = 2048, dropout: float = 0.1):
+        super().__init__()
+        self.self_attn, self.cross_attn = _MHA(d_model, nhead), _MHA(d_model, nhead)
+        self.norm1, self.norm2, self.norm3 = nn.LayerNorm(d_model), nn.LayerNorm(d_model), nn.LayerNorm(d_model)
+        self.fc1 = nn.Linear(d_model, dim_feedforward, activation="gelu")
+        self.fc2 = nn.Linear(dim_feedforward, d_model)
+        self.drop = nn.Dropout(dropout)
+
+    def forward(self, x, memory):
+        h = self.norm1(x)
+        x = x + self.drop(self.self_attn(h, h, h, causal=True))
+        x = x + self.drop(self.cross_attn(self.norm2(x), memory, memory))
+        return x + self.drop(self.fc2(self.fc1(self.norm3(x))))
+
+
+class TransformerEncoder(nn.Module):
+    def __init__(self, d_model, nhead, num_layers, dim_feedforward=2048, dropout=0.1):
+        super().__init__()
+        self.layers = nn.ModuleList([TransformerEncoderLayer(d_model, nhead, dim_feedforward, dropout) for _ in range(num_layers)])
+        self.norm = nn.LayerNorm(d_model)
+
+    def forward(self, x):
+        for l in self.layers:
+            x = l(x)
+        return self.norm(x)
+
+
+class TransformerDecoder(nn.Module):
+    def __init__(self, d_model, nhead, num_layers, dim_feedforward=2048, dropout=0.1):
+        super().__init__()
+        self.layers = nn.ModuleList([TransformerDecoderLayer(d_model, nhead, dim_feedforward, dropout) for _ in range(num_layers)])
+        self.norm = nn.LayerNorm(d_model)
+
+    def forward(self, x, memory):
+        for l in self.layers:
+            x = l(x, memory)
+        return self.norm(x)
+
+
+class Transformer(nn.Module):
+    def __init__(self, d_model=512, nhead=8, num_encoder_layers=6, num_decoder_layers=6, dim_feedforward=2048, dropout=0.1):
+        super().__init__()
+        self.encoder = TransformerEncoder(d_model, nhead, num_encoder_layers, dim_feedforward, dropout)
+        self.decoder = TransformerDecoder(d_model, nhead, num_decoder_layers, dim_feedforward, dropout)
+
+    def forward(self, src, tgt): return self.decoder(tgt, self.encoder(src))
+
+
+class VisionTransformer(nn.Module):
+    def __init__(self, image_size=224, patch_size=16, in_channels=3, num_classes=1000, d_model=768, depth=12,
+                 nhead=12, mlp_ratio=4.0, dropout=0.0):
+        super().__init__()
+        self.patch_size = patch_size
+        n = (image_size // patch_size) ** 2
+        self.patch_embed = nn.Linear(in_channels * patch_size * patch_size, d_model)
+        self.cls_token = nn.Parameter(torch.zeros(1, 1, d_model))
+        self.pos_embed = nn.Parameter(torch.randn(1, n + 1, d_model) * 0.02)
+        self.encoder = TransformerEncoder(d_model, nhead, depth, int(d_model * mlp_ratio), dropout)
+        self.head = nn.Linear(d_model, num_classes)
+
+    @classmethod
+    def vit_tiny(cls, image_size=224, num_classes=1000): return cls(image_size, 16, 3, num_classes, 192, 12, 3)
+    @classmethod
+    def vit_small(cls, image_size=224, num_classes=1000): return cls(image_size, 16, 3, num_classes, 384, 12, 6)
+    @classmethod
+    def vit_base(cls, image_size=224, num_classes=1000): return cls(image_size, 16, 3, num_classes, 768, 12, 12)
+    @classmethod
+    def vit_large(cls, image_size=224, num_classes=1000): return cls(image_size, 16, 3, num_classes, 1024, 24, 16)
+
+    def forward(self, x):
+        B, C, H, W = x.shape
+        p = self.patch_size
+        patches = x.unfold(2, p, p).unfold(3, p, p).permute(0, 2, 3, 1, 4, 5).reshape(B, -1, C * p * p)
+        h = self.patch_embed(patches)
+        h = torch.cat([self.cls_token.to(h.dtype).expand(B, -1, -1), h], 1) + self.pos_embed.to(h.dtype)
+        return self.head(self.encoder(h)[:, 0])
