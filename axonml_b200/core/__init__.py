@@ -4,3 +4,6 @@ from .device import (Device, DeviceCapabilities, as_torch_device, cuda_device_co
 from .dtype import DType, as_torch_dtype
 from .error import *  # noqa: F401,F403
 from .error import AxonmlError, Error
+from .backends import (Backend, CpuBackend, CudaBackend, MetalBackend, VulkanBackend, WgpuBackend,
+                       best_available_backend)
+from .storage import Allocator, CachingDeviceAllocator, DefaultAllocator, Storage

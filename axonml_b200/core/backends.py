@@ -1,0 +1,206 @@
+"""Compute backends (crates/axonml-core/src/backends): ``CpuBackend`` = the C++/OpenMP reference
+kernels of ``csrc/host/cpu_kernels.cpp`` (static methods on fp32 tensors, cpu.rs:137-731);
+``CudaBackend`` = the hand-written sm_100a kernels behind the same method names (the reference's
+CUDA island offers add/mul/scale/relu/sigmoid/tanh through sm_50 PTX and cuBLAS sgemm,
+cuda.rs:413-629); the graphics-API backends exist as names whose ``is_available()`` is False."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as N
+from .device import Device
+
+_BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+_UN = {"neg": 0, "abs": 1, "relu": 2, "sigmoid": 3, "tanh": 4, "exp": 5, "ln": 6, "sqrt": 7, "square": 8,
+       "gelu": 9, "silu": 10, "add_scalar": 11, "mul_scalar": 12, "leaky_relu": 13, "elu": 14}
+_RED = {"sum": 0, "prod": 1, "max": 2, "min": 3, "mean": 4, "argmax": 5, "argmin": 6}
+
+
+def _p(t): return ctypes.c_void_p(t.data_ptr())
+def _f(t): return t.detach().to("cpu", torch.float32).contiguous()
+
+
+class Backend:
+    """alloc / copy / sync surface of the reference's ``Backend`` trait (backends/mod.rs:73-100)."""
+    def name(self) -> str: raise NotImplementedError
+    def is_available(self) -> bool: return False
+    def device(self) -> Device: raise NotImplementedError
+    def allocate(self, count: int, dtype=torch.float32): return torch.empty(count, dtype=dtype, device=self.device().to_torch())
+    def copy_to_device(self, host: torch.Tensor): return host.to(self.device().to_torch())
+    def copy_to_host(self, dev: torch.Tensor): return dev.cpu()
+    def synchronize(self) -> None: pass
+
+
+class CpuBackend(Backend):
+    def name(self) -> str: return "cpu"
+    def is_available(self) -> bool: return True
+    def device(self) -> Device: return Device.Cpu()
+
+    @staticmethod
+    def _binary(op, a, b):
+        a, b = _f(a), _f(b)
+        y = torch.empty_like(a)
+        N.host().ax_cpu_binary(_BIN[op], _p(a), _p(b), _p(y), ctypes.c_int64(a.numel()))
+        return y
+
+    @staticmethod
+    def _unary(op, x, p=0.0):
+        x = _f(x)
+        y = torch.empty_like(x)
+        N.host().ax_cpu_unary(_UN[op], _p(x), _p(y), ctypes.c_int64(x.numel()), ctypes.c_float(p))
+        return y
+
+    @staticmethod
+    def _reduce(op, x):
+        x = _f(x)
+        fn = N.host().ax_cpu_reduce
+        fn.restype = ctypes.c_double
+        return fn(_RED[op], _p(x), ctypes.c_int64(x.numel()))
+
+    add = staticmethod(lambda a, b: CpuBackend._binary("add", a, b))
+    sub = staticmethod(lambda a, b: CpuBackend._binary("sub", a, b))
+    mul = staticmethod(lambda a, b: CpuBackend._binary("mul", a, b))
+    div = staticmethod(lambda a, b: CpuBackend._binary("div", a, b))
+    add_scalar = staticmethod(lambda x, s: CpuBackend._unary("add_scalar", x, s))
+    mul_scalar = staticmethod(lambda x, s: CpuBackend._unary("mul_scalar", x, s))
+    neg = staticmethod(lambda x: CpuBackend._unary("neg", x))
+    abs = staticmethod(lambda x: CpuBackend._unary("abs", x))
+    relu = staticmethod(lambda x: CpuBackend._unary("relu", x))
+    sigmoid = staticmethod(lambda x: CpuBackend._unary("sigmoid", x))
+    tanh = staticmethod(lambda x: CpuBackend._unary("tanh", x))
+    exp = staticmethod(lambda x: CpuBackend._unary("exp", x))
+    ln = staticmethod(lambda x: CpuBackend._unary("ln", x))
+    sqrt = staticmethod(lambda x: CpuBackend._unary("sqrt", x))
+    square = staticmethod(lambda x: CpuBackend._unary("square", x))
+    gelu = staticmethod(lambda x: CpuBackend._unary("gelu", x))
+    silu = staticmethod(lambda x: CpuBackend._unary("silu", x))
+    sum = staticmethod(lambda x: CpuBackend._reduce("sum", x))
+    prod = staticmethod(lambda x: CpuBackend._reduce("prod", x))
+    max = staticmethod(lambda x: CpuBackend._reduce("max", x))
+    min = staticmethod(lambda x: CpuBackend._reduce("min", x))
+    mean = staticmethod(lambda x: CpuBackend._reduce("mean", x))
+    argmax = staticmethod(lambda x: int(CpuBackend._reduce("argmax", x)))
+    argmin = staticmethod(lambda x: int(CpuBackend._reduce("argmin", x)))
+
+    @staticmethod
+    def matmul(a, b):
+        a, b = _f(a), _f(b)
+        M, K = a.shape
+        K2, Nn = b.shape
+        c = torch.empty(M, Nn)
+        N.host().ax_cpu_matmul(_p(a), _p(b), _p(c), ctypes.c_int64(M), ctypes.c_int64(Nn), ctypes.c_int64(K))
+        return c
+
+    @staticmethod
+    def transpose(x):
+        x = _f(x)
+        y = torch.empty(x.shape[1], x.shape[0])
+        N.host().ax_cpu_transpose(_p(x), _p(y), ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]))
+        return y
+
+    @staticmethod
+    def dot(a, b):
+        a, b = _f(a), _f(b)
+        fn = N.host().ax_cpu_dot
+        fn.restype = ctypes.c_double
+        return fn(_p(a), _p(b), ctypes.c_int64(a.numel()))
+
+    @staticmethod
+    def _cmp(op, a, b):
+        a, b = _f(a), _f(b)
+        y = torch.empty_like(a)
+        N.host().ax_cpu_compare(op, _p(a), _p(b), _p(y), ctypes.c_int64(a.numel()))
+        return y
+
+    eq = staticmethod(lambda a, b: CpuBackend._cmp(0, a, b))
+    lt = staticmethod(lambda a, b: CpuBackend._cmp(1, a, b))
+    gt = staticmethod(lambda a, b: CpuBackend._cmp(2, a, b))
+
+    @staticmethod
+    def conv2d(x, w, bias=None, stride=1, padding=0):
+        x, w = _f(x), _f(w)
+        Nb, C, H, W = x.shape
+        O, _, KH, KW = w.shape
+        OH, OW = (H + 2 * padding - KH) // stride + 1, (W + 2 * padding - KW) // stride + 1
+        y = torch.empty(Nb, O, OH, OW)
+        b = _f(bias) if bias is not None else None
+        N.host().ax_cpu_conv2d(_p(x), _p(w), _p(b) if b is not None else ctypes.c_void_p(0), _p(y), Nb, C, H, W, O, KH, KW,
+                               stride, stride, padding, padding)
+        return y
+
+    @staticmethod
+    def softmax_rows(x, log: bool = False):
+        x = _f(x)
+        y = torch.empty_like(x)
+        N.host().ax_cpu_softmax_rows(_p(x), _p(y), ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]), int(log))
+        return y
+
+    @staticmethod
+    def layer_norm(x, w=None, b=None, eps=1e-5, rms=False):
+        x = _f(x)
+        y = torch.empty_like(x)
+        wf, bf = (_f(w) if w is not None else None), (_f(b) if b is not None else None)
+        N.host().ax_cpu_layer_norm(_p(x), _p(wf) if wf is not None else ctypes.c_void_p(0),
+                                   _p(bf) if bf is not None else ctypes.c_void_p(0), _p(y),
+                                   ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]), ctypes.c_float(eps), int(rms))
+        return y
+
+    @staticmethod
+    def flash_attention(q, k, v, causal=False, scale=None, block=64):
+        q, k, v = _f(q), _f(k), _f(v)
+        BH, Sq, D = q.shape
+        o = torch.empty_like(q)
+        N.host().ax_cpu_flash_attention(_p(q), _p(k), _p(v), _p(o), BH, Sq, k.shape[1], D,
+                                        ctypes.c_float(scale if scale is not None else D ** -0.5), int(causal), block)
+        return o
+
+
+class CudaBackend(Backend):
+    def __init__(self, index: int = 0): self.index = index
+    def name(self) -> str: return "cuda"
+    def is_available(self) -> bool: return torch.cuda.is_available() and self.index < torch.cuda.device_count()
+    def device(self) -> Device: return Device.Cuda(self.index)
+    def synchronize(self) -> None: torch.cuda.synchronize(self.index)
+    def stream_synchronize(self) -> None: torch.cuda.current_stream(self.index).synchronize()
+    def mem_get_info(self): return torch.cuda.mem_get_info(self.index)
+
+    def _e(self):
+        from ..ops import elementwise
+        return elementwise
+
+    def add_f32(self, a, b): return self._e().binary(a, b, "add")
+    def sub_f32(self, a, b): return self._e().binary(a, b, "sub")
+    def mul_f32(self, a, b): return self._e().binary(a, b, "mul")
+    def div_f32(self, a, b): return self._e().binary(a, b, "div")
+    def scale_f32(self, x, alpha): return self._e().unary(x, "scale", alpha, out=x)
+    def relu_f32(self, x): return self._e().unary(x, "relu")
+    def sigmoid_f32(self, x): return self._e().unary(x, "sigmoid")
+    def tanh_f32(self, x): return self._e().unary(x, "tanh")
+    def gelu_f32(self, x): return self._e().unary(x, "gelu")
+    def silu_f32(self, x): return self._e().unary(x, "silu")
+
+    def gemm_f32(self, a, b):
+        """C = A B for fp32 inputs: operands are rounded to bf16 and multiplied on the tcgen05
+        kernel with fp32 accumulation (tolerance of the reference's GEMM test: 1e-3 / 1e-2)."""
+        from ..ops.gemm import gemm_bf16
+        return gemm_bf16(a.bfloat16(), b.bfloat16(), trans_b=False).float()
+
+    def gemm_batched_f32(self, a, b): return torch.stack([self.gemm_f32(x, y) for x, y in zip(a, b)])
+
+
+class _Unavailable(Backend):
+    NAME = "none"
+    def name(self) -> str: return self.NAME
+    def is_available(self) -> bool: return False
+    def device(self) -> Device: return Device(self.NAME, 0)
+
+
+class VulkanBackend(_Unavailable): NAME = "vulkan"
+class MetalBackend(_Unavailable): NAME = "metal"
+class WgpuBackend(_Unavailable): NAME = "wgpu"
+
+
+def best_available_backend() -> Backend:
+    return CudaBackend(torch.cuda.current_device()) if torch.cuda.is_available() else CpuBackend()
