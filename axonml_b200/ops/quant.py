@@ -1,0 +1,73 @@
+"""GPU block quantisation, dequantisation and the dequantising matmul
+(``csrc/kernels/quant.cu``, ``qgemm.cu``)."""
+from __future__ import annotations
+
+import torch
+
+from .. import _native as N
+
+
+def quantize_cuda(x: torch.Tensor, quant_type) -> torch.Tensor:
+    """fp32/bf16 CUDA tensor -> packed uint8 blocks (GGML layout).  Q8_0 and Q4_K run on the GPU;
+    the other formats round-trip through the CPU codec."""
+    from ..quant.types import QuantType
+    n = x.numel()
+    nbytes = n // quant_type.block_size() * quant_type.bytes_per_block()
+    if quant_type in (QuantType.Q8_0, QuantType.Q4_K) and x.dtype in (torch.float32, torch.bfloat16):
+        xc = x.contiguous()
+        out = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        rc = N.cuda().ax_quantize_cuda(quant_type.codec_id(), int(xc.dtype == torch.bfloat16), N.ptr(xc), N.ptr(out),
+                                       N.c_int64(n), N.stream_ptr())
+        N.check(rc, "ax_quantize_cuda")
+        return out
+    from ..quant.quantize import quantize_tensor
+    return quantize_tensor(x.detach().float().cpu(), quant_type).data.to(x.device)
+
+
+def dequantize_cuda(data: torch.Tensor, quant_type, numel: int, dtype=torch.float32) -> torch.Tensor:
+    out_dt = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    y = torch.empty(numel, dtype=out_dt, device=data.device)
+    rc = N.cuda().ax_dequantize_cuda(quant_type.codec_id(), int(out_dt == torch.bfloat16), N.ptr(data), N.ptr(y),
+                                     N.c_int64(numel), N.stream_ptr())
+    N.check(rc, "ax_dequantize_cuda")
+    return y if out_dt == dtype else y.to(dtype)
+
+
+def qgemm_supported(x: torch.Tensor, qweight) -> bool:
+    from ..quant.types import QuantType
+    return (N.is_blackwell() and x.is_cuda and x.dtype == torch.bfloat16 and qweight.data.is_cuda
+            and qweight.quant_type in (QuantType.Q4_K, QuantType.Q8_0) and len(qweight.shape) == 2
+            and qweight.shape[1] % 256 == 0 and qweight.layout == "ggml")
+
+
+def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int = 0) -> torch.Tensor:
+    """``x[B, K]`` (bf16, B <= 64 per launch) times the quantised ``W[N, K]``^T -> fp32 ``[B, N]``.
+    Larger batches are processed in slices of 64 rows."""
+    Nn, K = qweight.shape
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    B = x2.shape[0]
+    if out is None:
+        out = torch.zeros((B, Nn), dtype=torch.float32, device=x.device)
+    for b0 in range(0, B, 64):
+        xs = x2[b0:b0 + 64]
+        rc = N.cuda().ax_qgemm(qweight.quant_type.codec_id(), N.ptr(qweight.data), N.ptr(xs), N.ptr(out[b0:b0 + 64]),
+                               xs.shape[0], Nn, K, xs.stride(0), splits, N.ptr(N.status_word(x.device)), N.stream_ptr())
+        N.check(rc, "ax_qgemm")
+    return out.view(*x.shape[:-1], Nn)
+
+
+def qlinear(x: torch.Tensor, qweight, bias=None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Linear layer on a quantised weight: the fused dequant-matmul for up to a few hundred rows,
+    dequantise + tcgen05 GEMM beyond that (compute-bound prefill)."""
+    rows = x.numel() // x.shape[-1]
+    if qgemm_supported(x, qweight) and rows <= 256:
+        y = qgemm(x, qweight)
+        if bias is not None:
+            y = y + bias.float()
+        return y.to(out_dtype)
+    from ..quant.quantize import dequantize_tensor
+    from .linear import linear
+    w = dequantize_tensor(qweight, x.dtype if x.is_floating_point() else torch.float32)
+    return linear(x, w, bias).to(out_dtype)
