@@ -57,7 +57,8 @@ __global__ void embedding_bwd_kernel(const long* __restrict__ idx, const T* __re
 template <typename T>
 __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ cs,
                             const float* __restrict__ sn, long tokens, int heads, int hd,
-                            long in_stride, long out_stride, int S, int pos0, float sign, int rot_heads) {
+                            long in_stride, long out_stride, int S, int pos0, float sign, int rot_heads,
+                            const int* __restrict__ positions) {
   const int half = hd / 2;
   const long total = tokens * heads * half;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -66,7 +67,7 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const fl
     const long th = i / half;
     const int hh = (int)(th % heads);
     const long t = th / heads;
-    const long pos = pos0 + (t % S);
+    const long pos = positions ? (long)positions[t] : pos0 + (t % S);   // per-token positions (serving)
     const bool rot = hh < rot_heads;   // heads >= rot_heads are copied through unchanged
     const float c = rot ? cs[pos * half + j] : 1.f, s = rot ? sn[pos * half + j] * sign : 0.f;
     const T* xi = x + t * in_stride + (long)hh * hd;
@@ -140,18 +141,18 @@ AX_API int ax_embedding_bwd(int dtype, const long* idx, const void* dout, float*
 
 AX_API int ax_rope(int dtype, const void* x, void* y, const float* cs, const float* sn, long tokens,
                    int heads, int hd, long in_stride, long out_stride, int S, int pos0, float sign,
-                   int rot_heads, cudaStream_t stream) {
+                   int rot_heads, const int* positions, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (hd % 2) return -1;
   long total = tokens * heads * (hd / 2);
   if (dtype == 1)
     rope_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>(
         (const __nv_bfloat16*)x, (__nv_bfloat16*)y, cs, sn, tokens, heads, hd, in_stride,
-        out_stride, S < 1 ? 1 : S, pos0, sign, rot_heads);
+        out_stride, S < 1 ? 1 : S, pos0, sign, rot_heads, positions);
   else
     rope_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>(
         (const float*)x, (float*)y, cs, sn, tokens, heads, hd, in_stride, out_stride,
-        S < 1 ? 1 : S, pos0, sign, rot_heads);
+        S < 1 ? 1 : S, pos0, sign, rot_heads, positions);
   return (int)cudaGetLastError();
 }
 

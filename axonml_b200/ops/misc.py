@@ -79,7 +79,7 @@ class _RopeFn(torch.autograd.Function):
         return _rope_launch(dy, cos, sin, ctx.meta[0], ctx.meta[1], -1.0, ctx.meta[2]), None, None, None, None, None
 
 
-def _rope_launch(x, cos, sin, seq_len, pos0, sign, rot_heads=-1):
+def _rope_launch(x, cos, sin, seq_len, pos0, sign, rot_heads=-1, positions=None):
     # x: [..., heads, head_dim] with token-major leading dims
     heads, hd = x.shape[-2], x.shape[-1]
     x3 = x.reshape(-1, heads, hd)
@@ -89,7 +89,7 @@ def _rope_launch(x, cos, sin, seq_len, pos0, sign, rot_heads=-1):
     N.check(N.cuda().ax_rope(_dt(x3), N.ptr(x3), N.ptr(out), N.ptr(cos), N.ptr(sin),
                              N.c_int64(x3.shape[0]), heads, hd, N.c_int64(x3.stride(0)),
                              N.c_int64(out.stride(0)), seq_len, pos0, N.c_float(sign),
-                             heads if rot_heads < 0 else rot_heads, N.stream_ptr()), "ax_rope")
+                             heads if rot_heads < 0 else rot_heads, N.ptr(positions), N.stream_ptr()), "ax_rope")
     return out.view(x.shape)
 
 
@@ -113,6 +113,21 @@ def rope(x, cos, sin, *, seq_len: int, pos0: int = 0, rot_heads: int = -1):
     s = sin[pos].view(*lead, 1, half).to(torch.float32)
     a, b = x[..., :half].float(), x[..., half:].float()
     return torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(x.dtype)
+
+
+def rope_positions(x, cos, sin, positions, rot_heads: int = -1):
+    """Rotary embedding with an explicit int32 position per token (decode batches where every
+    sequence is at a different position).  ``x``: ``[T, heads, head_dim]``; inference only."""
+    if _ok(x):
+        return _rope_launch(x, cos, sin, 1, 0, 1.0, rot_heads, positions.to(torch.int32))
+    hd = x.shape[-1]
+    half = hd // 2
+    nrot = x.shape[-2] if rot_heads < 0 else rot_heads
+    c = cos[positions.long()].view(-1, 1, half).float()
+    s = sin[positions.long()].view(-1, 1, half).float()
+    a, b = x[:, :nrot, :half].float(), x[:, :nrot, half:].float()
+    rot = torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(x.dtype)
+    return torch.cat([rot, x[:, nrot:]], dim=1)
 
 
 def cast(x: torch.Tensor, dtype: torch.dtype, scale: float = 1.0) -> torch.Tensor:

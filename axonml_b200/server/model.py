@@ -1,0 +1,245 @@
+"""Quantised LLaMA for serving: Q4_K projection weights, Q8_0 embedding and output head, bf16
+paged KV cache, tensor parallel over the process group (heads and FFN columns split across ranks,
+vocabulary-parallel head).  Weights come from a GGUF file or are drawn N(0, 0.02) and quantised on
+the GPU (``from_random``).
+
+Every projection is the fused dequantising matmul (``ops.quant.qlinear``); prefill attention is
+the flash kernel, decode attention reads the paged cache; the two all-reduces per layer use the
+fused peer-memory all-reduce kernel when symmetric memory is available, NCCL otherwise."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..llm.config import LLaMAConfig
+from ..ops import elementwise as E
+from ..ops import misc as Mi
+from ..ops import norm as Nm
+from ..ops import paged
+from ..ops.attention import sdpa
+from ..ops.quant import qlinear
+from ..quant.quantize import dequantize_tensor, quantize_tensor
+from ..quant.types import QuantizedTensor, QuantType
+
+
+class _Layer:
+    __slots__ = ("attn_norm", "wqkv", "wo", "ffn_norm", "wgu", "wdown")
+
+
+class QuantizedLlama:
+    def __init__(self, cfg: LLaMAConfig, pg=None, device="cuda"):
+        self.cfg, self.pg, self.device = cfg, pg, torch.device(device)
+        self.tp = pg.world_size() if pg is not None else 1
+        self.rank = pg.rank() if pg is not None else 0
+        if cfg.num_attention_heads % self.tp or cfg.num_key_value_heads % self.tp or cfg.intermediate_size % self.tp:
+            raise ValueError("heads / kv heads / FFN width must be divisible by the tensor-parallel size")
+        self.hq, self.hkv, self.hd = cfg.num_attention_heads // self.tp, cfg.num_key_value_heads // self.tp, cfg.head_dim()
+        self.ffn = cfg.intermediate_size // self.tp
+        self.vocab_local = (cfg.vocab_size + self.tp - 1) // self.tp
+        self.layers: list[_Layer] = []
+        self.embed = None
+        self.head = None
+        self.final_norm = None
+        cos, sin = Mi.rope_tables(cfg.max_position_embeddings, self.hd, cfg.rope_theta, device=self.device)
+        self.cos, self.sin = cos, sin
+        self._ar = None
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_random(cls, cfg: LLaMAConfig, pg=None, device="cuda", seed: int = 0, std: float = 0.02,
+                    proj_type: QuantType = QuantType.Q4_K):
+        m = cls(cfg, pg, device)
+        g = torch.Generator(device=m.device).manual_seed(seed + 1000 * m.rank)
+        H = cfg.hidden_size
+
+        def rnd(rows, cols, qt):
+            w = torch.empty(rows, cols, device=m.device, dtype=torch.float32).normal_(0.0, std, generator=g)
+            return quantize_tensor(w, qt)
+        for _ in range(cfg.num_hidden_layers):
+            L = _Layer()
+            L.attn_norm = torch.ones(H, device=m.device, dtype=torch.bfloat16)
+            L.ffn_norm = torch.ones(H, device=m.device, dtype=torch.bfloat16)
+            L.wqkv = rnd((m.hq + 2 * m.hkv) * m.hd, H, proj_type)
+            L.wo = rnd(H, m.hq * m.hd, proj_type)
+            L.wgu = rnd(2 * m.ffn, H, proj_type)
+            L.wdown = rnd(H, m.ffn, proj_type)
+            m.layers.append(L)
+        m.embed = rnd(cfg.vocab_size, H, QuantType.Q8_0)
+        m.head = rnd(m.vocab_local, H, QuantType.Q8_0)
+        m.final_norm = torch.ones(H, device=m.device, dtype=torch.bfloat16)
+        return m
+
+    @classmethod
+    def from_gguf(cls, path, pg=None, device="cuda"):
+        from ..quant.gguf import read_gguf
+        g = read_gguf(path)
+        md = g.metadata
+        a = md.get("general.architecture", "llama")
+        cfg = LLaMAConfig(vocab_size=int(md.get(f"{a}.vocab_size", g.tensors["token_embd.weight"][0][0])),
+                          hidden_size=int(md[f"{a}.embedding_length"]), intermediate_size=int(md[f"{a}.feed_forward_length"]),
+                          num_hidden_layers=int(md[f"{a}.block_count"]), num_attention_heads=int(md[f"{a}.attention.head_count"]),
+                          num_key_value_heads=int(md.get(f"{a}.attention.head_count_kv", md[f"{a}.attention.head_count"])),
+                          max_position_embeddings=int(md.get(f"{a}.context_length", 4096)),
+                          rms_norm_eps=float(md.get(f"{a}.attention.layer_norm_rms_epsilon", 1e-5)),
+                          rope_theta=float(md.get(f"{a}.rope.freq_base", 10000.0)))
+        m = cls(cfg, pg, device)
+        tp, r, hd = m.tp, m.rank, m.hd
+
+        def rows(name, lo, hi, qt_fallback=QuantType.Q4_K):
+            """Rows [lo, hi) of a 2-D GGUF tensor, kept quantised when its blocks do not straddle rows."""
+            shape, qt, _, _ = g.tensors[name]
+            q = g.quantized(name)
+            if qt.is_block_quantized() and shape[1] % qt.block_size() == 0:
+                rb = shape[1] // qt.block_size() * qt.bytes_per_block()
+                return QuantizedTensor([hi - lo, shape[1]], qt, q.data[lo * rb:hi * rb].to(m.device))
+            w = dequantize_tensor(q)[lo:hi].to(m.device)
+            return quantize_tensor(w, qt_fallback if w.shape[1] % 256 == 0 else QuantType.Q8_0)
+
+        def cols(name, lo, hi):
+            w = g.tensor(name)[:, lo:hi].contiguous().to(m.device)
+            return quantize_tensor(w, QuantType.Q4_K if w.shape[1] % 256 == 0 else QuantType.Q8_0)
+
+        def cat(parts):
+            return QuantizedTensor([sum(p.shape[0] for p in parts), parts[0].shape[1]], parts[0].quant_type,
+                                   torch.cat([p.data for p in parts]))
+        for i in range(cfg.num_hidden_layers):
+            L, p = _Layer(), f"blk.{i}."
+            L.attn_norm = g.tensor(p + "attn_norm.weight").to(m.device, torch.bfloat16)
+            L.ffn_norm = g.tensor(p + "ffn_norm.weight").to(m.device, torch.bfloat16)
+            nq, nk = m.hq * hd, m.hkv * hd
+            parts = [rows(p + "attn_q.weight", r * nq, (r + 1) * nq), rows(p + "attn_k.weight", r * nk, (r + 1) * nk),
+                     rows(p + "attn_v.weight", r * nk, (r + 1) * nk)]
+            if len({x.quant_type for x in parts}) > 1:
+                parts = [quantize_tensor(dequantize_tensor(x), QuantType.Q4_K) for x in parts]
+            L.wqkv = cat(parts)
+            L.wo = cols(p + "attn_output.weight", r * nq, (r + 1) * nq) if tp > 1 else rows(p + "attn_output.weight", 0, cfg.hidden_size)
+            gu = [rows(p + "ffn_gate.weight", r * m.ffn, (r + 1) * m.ffn), rows(p + "ffn_up.weight", r * m.ffn, (r + 1) * m.ffn)]
+            if gu[0].quant_type != gu[1].quant_type:
+                gu = [quantize_tensor(dequantize_tensor(x), QuantType.Q4_K) for x in gu]
+            L.wgu = cat(gu)
+            L.wdown = cols(p + "ffn_down.weight", r * m.ffn, (r + 1) * m.ffn) if tp > 1 else rows(p + "ffn_down.weight", 0, cfg.hidden_size)
+            m.layers.append(L)
+        m.embed = rows("token_embd.weight", 0, cfg.vocab_size, QuantType.Q8_0)
+        hn = "output.weight" if "output.weight" in g.tensors else "token_embd.weight"
+        lo = r * m.vocab_local
+        m.head = rows(hn, lo, min(cfg.vocab_size, lo + m.vocab_local), QuantType.Q8_0)
+        m.final_norm = g.tensor("output_norm.weight").to(m.device, torch.bfloat16)
+        g.close()
+        return m
+
+    def to_gguf(self, path) -> None:
+        """Writes this rank's weights as a GGUF file (single-rank models are complete checkpoints)."""
+        from ..quant.gguf import write_gguf
+        c, hd = self.cfg, self.hd
+        t, nq, nk = {}, self.hq * hd, self.hkv * hd
+
+        def part(q: QuantizedTensor, lo, hi):
+            rb = q.shape[1] // q.quant_type.block_size() * q.quant_type.bytes_per_block()
+            return QuantizedTensor([hi - lo, q.shape[1]], q.quant_type, q.data[lo * rb:hi * rb])
+        for i, L in enumerate(self.layers):
+            p = f"blk.{i}."
+            t[p + "attn_norm.weight"], t[p + "ffn_norm.weight"] = L.attn_norm.float(), L.ffn_norm.float()
+            t[p + "attn_q.weight"], t[p + "attn_k.weight"] = part(L.wqkv, 0, nq), part(L.wqkv, nq, nq + nk)
+            t[p + "attn_v.weight"], t[p + "attn_output.weight"] = part(L.wqkv, nq + nk, nq + 2 * nk), L.wo
+            t[p + "ffn_gate.weight"], t[p + "ffn_up.weight"] = part(L.wgu, 0, self.ffn), part(L.wgu, self.ffn, 2 * self.ffn)
+            t[p + "ffn_down.weight"] = L.wdown
+        t["token_embd.weight"], t["output.weight"], t["output_norm.weight"] = self.embed, self.head, self.final_norm.float()
+        md = {"general.architecture": "llama", "general.name": "axonml-llama", "llama.vocab_size": c.vocab_size,
+              "llama.embedding_length": c.hidden_size, "llama.feed_forward_length": c.intermediate_size,
+              "llama.block_count": c.num_hidden_layers, "llama.attention.head_count": c.num_attention_heads,
+              "llama.attention.head_count_kv": c.num_key_value_heads, "llama.context_length": c.max_position_embeddings,
+              "llama.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps), "llama.rope.freq_base": float(c.rope_theta)}
+        write_gguf(path, t, md)
+
+    def weight_bytes(self) -> int:
+        n = self.embed.size_bytes() + self.head.size_bytes()
+        for L in self.layers:
+            n += L.wqkv.size_bytes() + L.wo.size_bytes() + L.wgu.size_bytes() + L.wdown.size_bytes()
+        return n
+
+    # ------------------------------------------------------------------ forward
+    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp == 1:
+            return x
+        if self._ar is None:
+            from ..parallel.fused import FusedAllReduce
+            self._ar = FusedAllReduce.try_create(self.pg, 64 * 512 * self.cfg.hidden_size, torch.bfloat16) or False
+        if self._ar:
+            flat = x.reshape(-1)
+            self._ar.all_reduce_mean_(flat)
+            return x.mul_(self.tp)
+        from ..parallel.backend import ReduceOp
+        self.pg.backend().all_reduce(x, ReduceOp.Sum)
+        return x
+
+    def _embed(self, ids: torch.Tensor) -> torch.Tensor:
+        rb = self.cfg.hidden_size // 32 * 34
+        rows = self.embed.data.view(-1, rb)[ids.reshape(-1).long()]
+        q = QuantizedTensor([rows.shape[0], self.cfg.hidden_size], self.embed.quant_type, rows.reshape(-1))
+        if q.quant_type is not QuantType.Q8_0:
+            raise ValueError("token embedding must be Q8_0")
+        return dequantize_tensor(q, torch.bfloat16)
+
+    def _logits(self, h: torch.Tensor) -> torch.Tensor:
+        return qlinear(Nm.rms_norm(h, self.final_norm, self.cfg.rms_norm_eps), self.head, out_dtype=torch.float32)
+
+    def greedy(self, h: torch.Tensor) -> torch.Tensor:
+        """Next token per row of ``h`` with the vocabulary split over ranks: local arg-max, then one
+        tiny all-gather of (value, index) pairs."""
+        lg = self._logits(h)
+        val, idx = lg.max(dim=-1)
+        idx = idx + self.rank * self.vocab_local
+        if self.tp == 1:
+            return idx
+        pair = torch.stack([val, idx.float()], dim=-1).contiguous()
+        out = torch.empty((self.tp,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
+        self.pg.backend().all_gather(pair, out)
+        best = out[..., 0].argmax(dim=0)
+        return out[..., 1].gather(0, best.unsqueeze(0)).squeeze(0).long()
+
+    def prefill(self, ids: torch.Tensor, cache, slots, layer_write=True) -> torch.Tensor:
+        """``ids`` [B, S] (equal-length prompts); writes K/V of every token into the pages of
+        ``slots`` and returns the hidden state of the last token of each prompt, [B, H]."""
+        B, S = ids.shape
+        x = self._embed(ids).view(B * S, -1)
+        seq = torch.tensor(slots, dtype=torch.int32, device=self.device).repeat_interleave(S)
+        pos = torch.arange(S, dtype=torch.int32, device=self.device).repeat(B)
+        nq, nk = self.hq * self.hd, self.hkv * self.hd
+        for li, L in enumerate(self.layers):
+            h = Nm.rms_norm(x, L.attn_norm, self.cfg.rms_norm_eps)
+            qkv = qlinear(h, L.wqkv).view(B * S, self.hq + 2 * self.hkv, self.hd)
+            qkv = Mi.rope_positions(qkv, self.cos, self.sin, pos, rot_heads=self.hq + self.hkv)
+            q, k, v = qkv[:, :self.hq], qkv[:, self.hq:self.hq + self.hkv], qkv[:, self.hq + self.hkv:]
+            paged.kv_write(k, v, cache.k[li], cache.v[li], cache.block_table, seq, pos, cache.page_size)
+            a = sdpa(q.reshape(B, S, self.hq, self.hd), k.reshape(B, S, self.hkv, self.hd),
+                     v.reshape(B, S, self.hkv, self.hd), causal=True)
+            o = self._all_reduce(qlinear(a.reshape(B * S, nq), L.wo))
+            x = x + o
+            h = Nm.rms_norm(x, L.ffn_norm, self.cfg.rms_norm_eps)
+            d = self._all_reduce(qlinear(E.swiglu(qlinear(h, L.wgu)), L.wdown))
+            x = x + d
+        return x.view(B, S, -1)[:, -1]
+
+    def decode(self, tokens: torch.Tensor, cache, slots_t: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """One token per running sequence.  ``tokens`` [B], ``slots_t`` [B] int32 cache slots,
+        ``positions`` [B] int32 position of the new token.  Returns the hidden state [B, H]."""
+        B = tokens.shape[0]
+        x = self._embed(tokens)
+        ctx = positions + 1
+        table = cache.block_table[slots_t.long()]
+        seq_local = torch.arange(B, dtype=torch.int32, device=self.device)
+        nq = self.hq * self.hd
+        for li, L in enumerate(self.layers):
+            h = Nm.rms_norm(x, L.attn_norm, self.cfg.rms_norm_eps)
+            qkv = qlinear(h, L.wqkv).view(B, self.hq + 2 * self.hkv, self.hd)
+            qkv = Mi.rope_positions(qkv, self.cos, self.sin, positions, rot_heads=self.hq + self.hkv)
+            q, k, v = qkv[:, :self.hq], qkv[:, self.hq:self.hq + self.hkv], qkv[:, self.hq + self.hkv:]
+            paged.kv_write(k, v, cache.k[li], cache.v[li], table, seq_local, positions, cache.page_size)
+            a = paged.decode_attention(q.contiguous(), cache.k[li], cache.v[li], table, ctx, cache.page_size)
+            o = self._all_reduce(qlinear(a.reshape(B, nq), L.wo))
+            x = x + o
+            h = Nm.rms_norm(x, L.ffn_norm, self.cfg.rms_norm_eps)
+            d = self._all_reduce(qlinear(E.swiglu(qlinear(h, L.wgu)), L.wdown))
+            x = x + d
+        return x
