@@ -41,8 +41,9 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 
 struct QParams {
-  const uint8_t* wq;     // [N][row_bytes]
+  const uint8_t* wq;     // row layout: [N][row_bytes]; tiled layout: [N/128][K/256][128][stage row bytes]
   long row_bytes;        // bytes of one full weight row (K/256*144 or K/32*34)
+  int tiled;             // 1: the 128 rows of a tile are contiguous per 256-wide k block (one bulk copy)
   float* out;            // [B][N] fp32, accumulated with reductions
   int N, K, B;
   int k_per_split;       // multiple of 256
@@ -100,6 +101,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_x, const QParams p) {
       if (!ok) break;
       const int k0 = k_begin + s * KS;
       const long koff = (long)(k0 / KS) * C::kRowBytes;
+      if (p.tiled) {
+        // 128 rows x one k block are contiguous: a single bulk copy instead of 128 small ones
+        if (lane == 0)
+          bulk_load(sQ + st * kQStage, p.wq + ((long)blockIdx.x * (p.K / KS) + k0 / KS) * kQStage, kQStage, &full[st]);
+      } else
 #pragma unroll
       for (int i = 0; i < BN / 32; ++i) {
         const int r = i * 32 + lane;
@@ -242,10 +248,12 @@ int launch_q(const CUtensorMap& mx, const QParams& p, int splits, cudaStream_t s
 }  // namespace
 
 // out[B,N] (fp32, must be zeroed or hold a value to accumulate onto) += x[B,K] (bf16) * Wq[N,K]^T.
+// tiled = 1: Wq was repacked so that each (128-row tile, 256-wide k block) is contiguous, rows
+// padded to a multiple of 128 (see ops/quant.py: tile_weight).
 // qtype: 5 = Q4_K, 0 = Q8_0.  K must be a multiple of 256, B <= 64.  `splits` = 0 picks a split-K
 // factor that fills the GPU.
 AX_API int ax_qgemm(int qtype, const void* wq, const void* x, float* out, int B, int N, int K, int ldx,
-                    int splits, int* status, cudaStream_t stream) {
+                    int splits, int tiled, int* status, cudaStream_t stream) {
   if (B <= 0 || N <= 0 || K <= 0) return 0;
   if (B > BB || K % KS || ldx % 8 || (qtype != 5 && qtype != 0)) return -1;
   CUtensorMap mx;
@@ -267,6 +275,7 @@ AX_API int ax_qgemm(int qtype, const void* wq, const void* x, float* out, int B,
   QParams p;
   p.wq = (const uint8_t*)wq;
   p.row_bytes = qtype == 5 ? (long)(K / 256) * 144 : (long)(K / 32) * 34;
+  p.tiled = tiled;
   p.out = out; p.N = N; p.K = K; p.B = B; p.k_per_split = per * KS; p.status = status;
   return qtype == 5 ? launch_q<5>(mx, p, splits, stream) : launch_q<0>(mx, p, splits, stream);
 }

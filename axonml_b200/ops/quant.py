@@ -33,11 +33,39 @@ def dequantize_cuda(data: torch.Tensor, quant_type, numel: int, dtype=torch.floa
     return y if out_dt == dtype else y.to(dtype)
 
 
+def tile_weight(qweight):
+    """Repacks a row-major quantised ``[N, K]`` weight (Q4_K / Q8_0, K % 256 == 0) so that the 128
+    rows of a tile are contiguous for every 256-wide k block: ``[N/128][K/256][128][bytes]``.  The
+    dequantising matmul then fetches a whole stage with one bulk copy instead of 128 small ones.
+    Rows are padded to a multiple of 128 with zero blocks."""
+    from ..quant.types import QuantizedTensor
+    Nn, K = qweight.shape
+    qt = qweight.quant_type
+    sb = 256 // qt.block_size() * qt.bytes_per_block()          # bytes of one row within a k block
+    kb = K // 256
+    d = qweight.data.view(Nn, kb, sb)
+    pad = (-Nn) % 128
+    if pad:
+        d = torch.cat([d, torch.zeros((pad, kb, sb), dtype=torch.uint8, device=d.device)], 0)
+    d = d.view(-1, 128, kb, sb).permute(0, 2, 1, 3).contiguous()
+    return QuantizedTensor([Nn, K], qt, d.view(-1), "tile128")
+
+
+def untile_weight(qweight):
+    from ..quant.types import QuantizedTensor
+    Nn, K = qweight.shape
+    qt = qweight.quant_type
+    sb = 256 // qt.block_size() * qt.bytes_per_block()
+    kb = K // 256
+    d = qweight.data.view(-1, kb, 128, sb).permute(0, 2, 1, 3).reshape(-1, kb * sb)[:Nn].contiguous()
+    return QuantizedTensor([Nn, K], qt, d.view(-1), "ggml")
+
+
 def qgemm_supported(x: torch.Tensor, qweight) -> bool:
     from ..quant.types import QuantType
     return (N.is_blackwell() and x.is_cuda and x.dtype == torch.bfloat16 and qweight.data.is_cuda
             and qweight.quant_type in (QuantType.Q4_K, QuantType.Q8_0) and len(qweight.shape) == 2
-            and qweight.shape[1] % 256 == 0 and qweight.layout == "ggml")
+            and qweight.shape[1] % 256 == 0 and qweight.layout in ("ggml", "tile128"))
 
 
 def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int = 0) -> torch.Tensor:
@@ -53,7 +81,8 @@ def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int
     for b0 in range(0, B, 64):
         xs = x2[b0:b0 + 64]
         rc = N.cuda().ax_qgemm(qweight.quant_type.codec_id(), N.ptr(qweight.data), N.ptr(xs), N.ptr(out[b0:b0 + 64]),
-                               xs.shape[0], Nn, K, xs.stride(0), splits, N.ptr(N.status_word(x.device)), N.stream_ptr())
+                               xs.shape[0], Nn, K, xs.stride(0), splits, int(qweight.layout == "tile128"),
+                               N.ptr(N.status_word(x.device)), N.stream_ptr())
         N.check(rc, "ax_qgemm")
     return out.view(*x.shape[:-1], Nn)
 
@@ -69,5 +98,7 @@ def qlinear(x: torch.Tensor, qweight, bias=None, out_dtype=torch.bfloat16) -> to
         return y.to(out_dtype)
     from ..quant.quantize import dequantize_tensor
     from .linear import linear
+    if qweight.layout == "tile128":
+        qweight = untile_weight(qweight)
     w = dequantize_tensor(qweight, x.dtype if x.is_floating_point() else torch.float32)
     return linear(x, w, bias).to(out_dtype)

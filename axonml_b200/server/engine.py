@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import dataclasses
 import itertools
+import os
 import time
 
 import torch
@@ -31,6 +32,8 @@ class LLMEngine:
     def __init__(self, model, max_batch: int = 64, max_context: int = 1024, page_size: int = 16,
                  num_pages: int | None = None):
         self.model, self.max_batch = model, max_batch
+        if hasattr(model, "optimize_layout"):
+            model.optimize_layout()
         cfg = model.cfg
         pages_per_seq = (max_context + page_size - 1) // page_size
         num_pages = num_pages or max_batch * pages_per_seq
@@ -40,6 +43,17 @@ class LLMEngine:
         self.running: list[Request] = []
         self.finished: list[Request] = []
         self._ids = itertools.count()
+        # CUDA-graph decode: one captured graph per batch size, fed through static input buffers
+        self.use_graphs = model.device.type == "cuda" and os.environ.get("AXONML_DECODE_GRAPHS", "1") != "0"
+        self._graphs: dict = {}
+        if self.use_graphs:
+            dev = model.device
+            if model.tp > 1:
+                model.comm_mode = "nccl"
+            self._g_tokens = torch.zeros(max_batch, dtype=torch.long, device=dev)
+            self._g_slots = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+            self._g_pos = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+            self._g_next = torch.zeros(max_batch, dtype=torch.long, device=dev)
         self.decode_steps = 0
         self.decode_time = 0.0
         self.decode_tokens = 0
@@ -108,8 +122,7 @@ class LLMEngine:
         tokens = torch.tensor([r.output[-1] for r in reqs], dtype=torch.long, device=dev)
         slots = torch.tensor([r.slot for r in reqs], dtype=torch.int32, device=dev)
         positions = torch.tensor(pos, dtype=torch.int32, device=dev)
-        h = self.model.decode(tokens, self.cache, slots, positions)
-        nxt = self.model.greedy(h).tolist()
+        nxt = self._decode_step(tokens, slots, positions).tolist()
         now = self._now()
         self.decode_time += now - t0
         self.decode_steps += 1
@@ -118,6 +131,36 @@ class LLMEngine:
             r.output.append(int(t))
             if len(r.output) >= r.max_new_tokens or t == r.eos_token_id:
                 self._finish(r, now)
+
+    def _decode_step(self, tokens, slots, positions) -> torch.Tensor:
+        """Eager decode, or replay of the CUDA graph captured for this batch size (the whole step -
+        embedding gather, 32 layers, head, arg-max - is one graph launch, which removes the
+        per-kernel launch overhead that dominates small-batch decoding)."""
+        B = tokens.shape[0]
+        if not self.use_graphs:
+            return self.model.greedy(self.model.decode(tokens, self.cache, slots, positions))
+        self._g_tokens[:B].copy_(tokens)
+        self._g_slots[:B].copy_(slots)
+        self._g_pos[:B].copy_(positions)
+        g = self._graphs.get(B)
+        if g is None:
+            def run():
+                h = self.model.decode(self._g_tokens[:B], self.cache, self._g_slots[:B], self._g_pos[:B])
+                self._g_next[:B].copy_(self.model.greedy(h))
+            side = torch.cuda.Stream(self.model.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):        # warm-up outside capture (lazy initialisation, attributes)
+                run()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                run()
+            self._graphs[B] = g
+            # the warm-up and the capture both ran the step on real inputs; replaying once more
+            # rewrites the same K/V rows, so the result is unchanged
+        g.replay()
+        return self._g_next[:B].clone()
 
     def run_until_done(self) -> None:
         while self.waiting or self.running:

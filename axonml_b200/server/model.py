@@ -152,6 +152,22 @@ class QuantizedLlama:
               "llama.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps), "llama.rope.freq_base": float(c.rope_theta)}
         write_gguf(path, t, md)
 
+    def optimize_layout(self) -> "QuantizedLlama":
+        """Repacks the projection weights and the head into the tile layout of the dequantising
+        matmul (GPU only).  Prefill of long prompts dequantises from the same data."""
+        if self.device.type != "cuda":
+            return self
+        from ..ops.quant import tile_weight
+        ok = lambda q: q.layout == "ggml" and q.quant_type in (QuantType.Q4_K, QuantType.Q8_0) and q.shape[1] % 256 == 0
+        for L in self.layers:
+            for name in ("wqkv", "wo", "wgu", "wdown"):
+                q = getattr(L, name)
+                if ok(q):
+                    setattr(L, name, tile_weight(q))
+        if ok(self.head):
+            self.head = tile_weight(self.head)
+        return self
+
     def weight_bytes(self) -> int:
         n = self.embed.size_bytes() + self.head.size_bytes()
         for L in self.layers:
@@ -162,6 +178,8 @@ class QuantizedLlama:
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp == 1:
             return x
+        if self._ar is None and getattr(self, "comm_mode", "fused") == "nccl":
+            self._ar = False        # decode graphs replay fixed kernel arguments: use NCCL, which is capturable
         if self._ar is None:
             from ..parallel.fused import FusedAllReduce
             self._ar = FusedAllReduce.try_create(self.pg, 64 * 512 * self.cfg.hidden_size, torch.bfloat16) or False

@@ -98,12 +98,69 @@ def reference_arm(args):
                       "offline): pip install of /root/reference fails, nothing to run"}))
 
 
+def bench_q4k_decode(args):
+    """GGUF-style Q4_K serving of the Llama-3-8B architecture: p50 time-to-first-token and decode
+    tokens/s at concurrent batch 1/8/32/64 (512-token random prompts, greedy decoding)."""
+    import torch
+    import torch.distributed as dist
+    from axonml_b200 import _native
+    from axonml_b200.llm import LLaMAConfig
+    from axonml_b200.parallel import NcclBackend, ProcessGroup
+    from axonml_b200.server import LLMEngine, QuantizedLlama
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    pg = ProcessGroup(NcclBackend.init(timeout_s=600)) if world > 1 else None
+    cfg = LLaMAConfig.llama3_8b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    model = QuantizedLlama.from_random(cfg, pg, device=f"cuda:{local}")
+    prompt_len, new_tokens = args.seq_len if args.seq_len != 2048 else 512, max(2, args.steps if args.steps > 8 else 256)
+    gen = torch.Generator().manual_seed(7)
+    results = {}
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _native.launch_count()
+    for conc in (1, 8, 32, 64):
+        eng = LLMEngine(model, max_batch=64, max_context=prompt_len + new_tokens + 16, page_size=16)
+        prompts = torch.randint(0, cfg.vocab_size, (conc, prompt_len), generator=gen).tolist()
+        if conc == 1:      # warm-up pass (kernel attributes, allocator)
+            LLMEngine(model, 64, prompt_len + 32, 16).generate(prompts, 4)
+        eng.generate(prompts, new_tokens)
+        st = eng.stats()
+        results[conc] = {"ttft_p50_ms": round(st["ttft_p50_s"] * 1e3, 2), "decode_tok_s": round(st["decode_tokens_per_s"], 1),
+                         "decode_ms_per_step": round(st["decode_time_s"] / max(st["decode_steps"], 1) * 1e3, 3)}
+    launches = _native.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    torch.cuda.synchronize()
+    _native.check_status()
+    if rank == 0:
+        print(json.dumps({"metric": "Q4_K decode tok/s (Llama-3-8B architecture, GGUF Q4_K weights, Q8_0 embeddings/head)",
+                          "value": results[64]["decode_tok_s"], "unit": "tokens/s", "n_gpus": world, "steps": new_tokens,
+                          "warmup": 4, "ms_per_step": results[64]["decode_ms_per_step"], "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "q4_k weights, bf16 activations/KV",
+                          "data": "synthetic", "impl": "axonml_b200",
+                          "config": {"model": f"llama-3-8b arch ({cfg.num_hidden_layers}L)", "parallelism": f"tp{world}",
+                                     "prompt_len": prompt_len, "new_tokens": new_tokens, "weight_bytes_per_rank": model.weight_bytes(),
+                                     "by_concurrency": results, "timing": "host clock around device synchronisation per scheduler step"},
+                          "clocks": clocks, "gpu_launches": launches}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
             reference_arm(args)
         return 0
+    if args.config == "q4k_decode":
+        return bench_q4k_decode(args)
 
     import torch
     import torch.distributed as dist

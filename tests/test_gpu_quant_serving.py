@@ -41,10 +41,14 @@ def test_qgemm(qt, B, N, K, kernel_status):
     w = torch.randn(N, K) * 0.05
     q = quantize_tensor(w, QuantType[qt]).to("cuda")
     x = torch.randn(B, K, device="cuda").bfloat16()
+    from axonml_b200.ops.quant import tile_weight, untile_weight
     y = qgemm(x, q)
     ref = x.float() @ dequantize_tensor(q).float().t()
     err = (y - ref).abs().max().item()
     assert err < 0.02 * (K ** 0.5) * 0.05 * 4 + 1e-2, err
+    qt_ = tile_weight(q)
+    assert torch.equal(untile_weight(qt_).data, q.data)
+    assert (qgemm(x, qt_) - y).abs().max().item() < 1e-3
 
 
 def test_paged_kv_and_decode_attention():
