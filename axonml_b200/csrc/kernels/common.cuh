@@ -95,6 +95,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Upper bound (ns) the hardware may keep a waiting thread suspended inside one try_wait; the thread
+// wakes as soon as the phase completes, so a long hint costs no latency and frees issue slots that
+// a tight polling loop would take from the warps doing the work.
+constexpr uint32_t kSuspendHintNs = 20000;
+
 // Bounded wait.  `dead` is a shared-memory flag of the CTA: once any wait of the CTA has
 // given up, all later waits return at once so that the CTA drains quickly.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* dead,
@@ -106,14 +111,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     asm volatile(
         "{\n\t"
         ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, P;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     if (ok) return true;
-    if (++spins >= 64) {
+    if (++spins >= 16) {
       if (*dead) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {

@@ -30,6 +30,10 @@ struct Vec8<__nv_bfloat16> {
     u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
     *reinterpret_cast<uint4*>(p) = u;
   }
+  static __device__ __forceinline__ void round_trip(float (&v)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+  }
 };
 template <>
 struct Vec8<float> {
@@ -41,6 +45,7 @@ struct Vec8<float> {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
   }
+  static __device__ __forceinline__ void round_trip(float (&)[8]) {}
 };
 
 constexpr int kWarpsPerCta = 8;
@@ -105,6 +110,75 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const WT* __
         v[j] = b ? o + bv[j] : o;
       }
       Vec8<T>::store(yr + c, v);
+    }
+  }
+}
+
+// Few rows (decode steps, small batches): one CTA per row, the row held in registers between
+// the statistics and the normalisation, so the row is read once and all its loads are in flight
+// together.  D <= kWarpsPerCta * 32 * 8 * kBlockVecs.
+constexpr int kBlockVecs = 8;
+template <typename T, typename WT, bool RMS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+norm_fwd_block_kernel(const T* __restrict__ x, const T* __restrict__ res, const WT* __restrict__ w,
+                      const WT* __restrict__ b, T* __restrict__ y, T* __restrict__ hout,
+                      float* __restrict__ mean_out, float* __restrict__ rstd_out, int D, float eps) {
+  constexpr int kStep = kWarpsPerCta * 32 * 8;
+  __shared__ float red[2][kWarpsPerCta];
+  const long row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* xr = x + row * D;
+  const T* rr = res ? res + row * D : nullptr;
+  T* hr = hout ? hout + row * D : nullptr;
+  float v[kBlockVecs][8];
+  float s = 0.f, ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kBlockVecs; ++i) {
+    const int c = threadIdx.x * 8 + i * kStep;
+    if (c < D) {
+      Vec8<T>::load(xr + c, v[i]);
+      if (rr) {
+        float r[8];
+        Vec8<T>::load(rr + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+        if (hr) {
+          Vec8<T>::store(hr + c, v[i]);
+          Vec8<T>::round_trip(v[i]);      // statistics of the stored (rounded) values
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s += v[i][j]; ss += v[i][j] * v[i][j]; }
+    }
+  }
+  s = warp_sum(s);
+  ss = warp_sum(ss);
+  if (lane == 0) { red[0][warp] = s; red[1][warp] = ss; }
+  __syncthreads();
+  s = 0.f; ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kWarpsPerCta; ++i) { s += red[0][i]; ss += red[1][i]; }
+  const float mean = RMS ? 0.f : s / D;
+  const float var = RMS ? ss / D : fmaxf(ss / D - mean * mean, 0.f);
+  const float rstd = rsqrtf(var + eps);
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  T* yr = y + row * D;
+#pragma unroll
+  for (int i = 0; i < kBlockVecs; ++i) {
+    const int c = threadIdx.x * 8 + i * kStep;
+    if (c < D) {
+      float wv[8], bv[8];
+      Vec8<WT>::load(w + c, wv);
+      if (b) Vec8<WT>::load(b + c, bv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float o = (v[i][j] - mean) * rstd * wv[j];
+        v[i][j] = b ? o + bv[j] : o;
+      }
+      Vec8<T>::store(yr + c, v[i]);
     }
   }
 }
@@ -215,6 +289,15 @@ template <typename T, typename WT>
 int launch_fwd(bool rms, const void* x, const void* res, const void* w, const void* b, void* y,
                void* hout, float* mean, float* rstd, int rows, int D, float eps,
                cudaStream_t stream) {
+  if (rows <= axh::sm_count() * 4 && D >= 1024 && D <= kWarpsPerCta * 32 * 8 * kBlockVecs) {
+    if (rms)
+      norm_fwd_block_kernel<T, WT, true><<<rows, kWarpsPerCta * 32, 0, stream>>>(
+          (const T*)x, (const T*)res, (const WT*)w, (const WT*)b, (T*)y, (T*)hout, mean, rstd, D, eps);
+    else
+      norm_fwd_block_kernel<T, WT, false><<<rows, kWarpsPerCta * 32, 0, stream>>>(
+          (const T*)x, (const T*)res, (const WT*)w, (const WT*)b, (T*)y, (T*)hout, mean, rstd, D, eps);
+    return (int)cudaGetLastError();
+  }
   int grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
   int cap = axh::sm_count() * 8;
   if (grid > cap) grid = cap;

@@ -4,9 +4,10 @@
 // Cache layout: k_cache / v_cache [num_pages, page_size, Hkv, D] bf16; block_table [B, max_pages]
 // int32; context_lens [B] int32.  Grouped-query attention: the G = Hq/Hkv query heads that share
 // a KV head are processed by the same CTA, so each K/V row is read once for all of them.
-// One CTA per (sequence, kv head); 4 lanes cooperate on a token (each holds D/4 of the row), so a
-// warp covers 8 tokens per iteration with 16-byte loads; every 4-lane group keeps its own online
-// softmax state, groups are merged through shared memory at the end.
+// One CTA per (sequence, kv head, split of the context); 8 lanes cooperate on a token (each holds
+// 16 elements of the row), so a warp covers 4 tokens per iteration with 16-byte loads; every
+// 8-lane group keeps its own online softmax state; groups are merged with shuffles, warps through
+// shared memory, context splits by a small second kernel.
 //
 // Replaces the reference's concat-and-grow KVCache (crates/axonml-llm/src/attention.rs:46-70) and
 // the full score-matrix attention of crates/axonml-llm/src/llama.rs:429-441 for the decode step.
@@ -15,10 +16,13 @@
 namespace {
 using namespace ax;
 
-constexpr int kWarps = 4;
-constexpr int kGroups = kWarps * 8;     // 4-lane groups per CTA
+constexpr int kWarps = 8;
+constexpr int kLanesPerTok = 8;                       // lanes that share one cached token
+constexpr int kTokPerWarp = 32 / kLanesPerTok;
+constexpr int kTokPerIter = kWarps * kTokPerWarp;     // tokens a CTA covers per iteration
 constexpr int D = 128;
-constexpr int kMaxG = 8;                // query heads per KV head handled in one pass
+constexpr int kEl = D / kLanesPerTok;                 // 16 elements of a row per lane
+constexpr int kMaxG = 8;                              // query heads per KV head handled in one pass
 
 __global__ void paged_kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                                       __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
@@ -36,102 +40,138 @@ __global__ void paged_kv_write_kernel(const __nv_bfloat16* __restrict__ k, const
   }
 }
 
+// Unpacks 8 bf16 (one 16-byte load) into floats.
+__device__ __forceinline__ void unpack8(const uint4 u, float* d) {
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), e = unpack_bf16x2(u.w);
+  d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y; d[4] = c.x; d[5] = c.y; d[6] = e.x; d[7] = e.y;
+}
+
+// Grid (B, Hkv, S): split s of sequence b covers an equal share of the sequence's tokens (rounded
+// up to the 32 tokens a CTA handles per iteration), so one query token still fills the GPU.  With
+// S == 1 the result goes straight to `out`; otherwise un-normalised partial sums and (max, sum)
+// go to `part` [B, Hq, S, D + 2] fp32 and paged_merge_kernel finishes.
 template <int G>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                     const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
-                    const int* __restrict__ block_table, const int* __restrict__ ctx_lens, int Hq, int Hkv,
-                    int page_size, int max_pages, float scale_log2, long q_stride, long o_stride) {
-  const int b = blockIdx.x, hk = blockIdx.y;
+                    float* __restrict__ part, const int* __restrict__ block_table,
+                    const int* __restrict__ ctx_lens, int Hq, int Hkv, int page_size, int max_pages,
+                    float scale_log2, long q_stride, long o_stride) {
+  const int b = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z, S = gridDim.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane & 3;                      // which quarter of the row this lane holds
-  const int grp = warp * 8 + (lane >> 2);        // token slot of this 4-lane group
+  const int sub = lane & (kLanesPerTok - 1);     // which 16 elements of the row this lane holds
+  const int slot = warp * kTokPerWarp + lane / kLanesPerTok;
   const int ctx = ctx_lens[b];
-  const int h0 = hk * (Hq / Hkv);
-  // query: every lane keeps its 32-element quarter of each of the G heads
-  float qv[G][32];
+  const int chunk = (((ctx + S - 1) / S) + kTokPerIter - 1) / kTokPerIter * kTokPerIter;
+  const int t_begin = sp * chunk;
+  const int t_end = min(ctx, t_begin + chunk);
+  const int h0 = hk * G;
+  float qv[G][kEl];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + (long)b * q_stride + (long)(h0 + g) * D + sub * 32;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint4 u = *reinterpret_cast<const uint4*>(qp + c * 8);
-      const float2 a = unpack_bf16x2(u.x), bb = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), dd = unpack_bf16x2(u.w);
-      float* d = &qv[g][c * 8];
-      d[0] = a.x; d[1] = a.y; d[2] = bb.x; d[3] = bb.y; d[4] = cc.x; d[5] = cc.y; d[6] = dd.x; d[7] = dd.y;
-    }
+    const __nv_bfloat16* qp = q + (long)b * q_stride + (long)(h0 + g) * D + sub * kEl;
+    unpack8(*reinterpret_cast<const uint4*>(qp), &qv[g][0]);
+    unpack8(*reinterpret_cast<const uint4*>(qp + 8), &qv[g][8]);
   }
-  float m[G], l[G], acc[G][32];
+  float m[G], l[G], acc[G][kEl];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[g][i] = 0.f;
+    for (int i = 0; i < kEl; ++i) acc[g][i] = 0.f;
   }
   const long row = (long)Hkv * D;
-  for (int t0 = 0; t0 < ctx; t0 += kGroups) {
-    const int t = t0 + grp;
-    const bool valid = t < ctx;
-    float kf[32], vf[32];
+  for (int t0 = t_begin; t0 < t_end; t0 += kTokPerIter) {
+    const int t = t0 + slot;
+    const bool valid = t < t_end;
+    float kf[kEl], vf[kEl];
     if (valid) {
       const int page = block_table[b * max_pages + t / page_size];
-      const long off = ((long)page * page_size + t % page_size) * row + (long)hk * D + sub * 32;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint4 uk = *reinterpret_cast<const uint4*>(kc + off + c * 8);
-        const uint4 uv = *reinterpret_cast<const uint4*>(vc + off + c * 8);
-        float2 a = unpack_bf16x2(uk.x), bb = unpack_bf16x2(uk.y), cc = unpack_bf16x2(uk.z), dd = unpack_bf16x2(uk.w);
-        float* d = &kf[c * 8];
-        d[0] = a.x; d[1] = a.y; d[2] = bb.x; d[3] = bb.y; d[4] = cc.x; d[5] = cc.y; d[6] = dd.x; d[7] = dd.y;
-        a = unpack_bf16x2(uv.x); bb = unpack_bf16x2(uv.y); cc = unpack_bf16x2(uv.z); dd = unpack_bf16x2(uv.w);
-        d = &vf[c * 8];
-        d[0] = a.x; d[1] = a.y; d[2] = bb.x; d[3] = bb.y; d[4] = cc.x; d[5] = cc.y; d[6] = dd.x; d[7] = dd.y;
-      }
+      const long off = ((long)page * page_size + t % page_size) * row + (long)hk * D + sub * kEl;
+      const uint4 k0 = *reinterpret_cast<const uint4*>(kc + off), k1 = *reinterpret_cast<const uint4*>(kc + off + 8);
+      const uint4 v0 = *reinterpret_cast<const uint4*>(vc + off), v1 = *reinterpret_cast<const uint4*>(vc + off + 8);
+      unpack8(k0, kf); unpack8(k1, kf + 8);
+      unpack8(v0, vf); unpack8(v1, vf + 8);
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float s = 0.f;
       if (valid) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s += qv[g][i] * kf[i];
+        for (int i = 0; i < kEl; ++i) s += qv[g][i] * kf[i];
       }
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
       if (valid) {
         s *= scale_log2;
         const float mn = fmaxf(m[g], s);
         const float alpha = exp2f(m[g] - mn), pe = exp2f(s - mn);
         l[g] = l[g] * alpha + pe;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[g][i] = acc[g][i] * alpha + pe * vf[i];
+        for (int i = 0; i < kEl; ++i) acc[g][i] = acc[g][i] * alpha + pe * vf[i];
         m[g] = mn;
       }
     }
   }
-  // merge the kGroups partial states: shared memory [G][kGroups] for (m, l), then a second pass
-  __shared__ float sm[kMaxG][kGroups], sl[kMaxG][kGroups];
-  __shared__ float so[kMaxG][D];
-  for (int i = threadIdx.x; i < kMaxG * D; i += blockDim.x) (&so[0][0])[i] = 0.f;
-  if (sub == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) { sm[g][grp] = m[g]; sl[g][grp] = l[g]; }
-  }
-  __syncthreads();
+  // merge the token slots of a warp with shuffles, then the warps through shared memory
+  __shared__ float sM[kMaxG][kWarps], sL[kMaxG][kWarps];
+  __shared__ float sO[kWarps][G][D];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    float M = -INFINITY;
-    for (int j = 0; j < kGroups; ++j) M = fmaxf(M, sm[g][j]);
-    float L = 0.f;
-    for (int j = 0; j < kGroups; ++j) L += sl[g][j] * (sm[g][j] == -INFINITY ? 0.f : exp2f(sm[g][j] - M));
-    const float w = (m[g] == -INFINITY || L <= 0.f) ? 0.f : exp2f(m[g] - M) / L;
+    float M = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], 8));
+    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+    const float w = m[g] == -INFINITY ? 0.f : exp2f(m[g] - M);
+    float L = l[g] * w;
+    L += __shfl_xor_sync(0xffffffffu, L, 8);
+    L += __shfl_xor_sync(0xffffffffu, L, 16);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) atomicAdd(&so[g][sub * 32 + i], acc[g][i] * w);
+    for (int i = 0; i < kEl; ++i) {
+      float a = acc[g][i] * w;
+      a += __shfl_xor_sync(0xffffffffu, a, 8);
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      if (lane < kLanesPerTok) sO[warp][g][sub * kEl + i] = a;
+    }
+    if (lane == 0) { sM[g][warp] = M; sL[g][warp] = L; }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int g = i / D, d = i % D;
-    out[(long)b * o_stride + (long)(h0 + g) * D + d] = __float2bfloat16(so[g][d]);
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, sM[g][w]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float f = sM[g][w] == -INFINITY ? 0.f : exp2f(sM[g][w] - M);
+      L += sL[g][w] * f;
+      O += sO[w][g][d] * f;
+    }
+    if (S == 1) {
+      out[(long)b * o_stride + (long)(h0 + g) * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+    } else {
+      float* pp = part + (((long)b * Hq + h0 + g) * S + sp) * (D + 2);
+      pp[d] = O;
+      if (d == 0) { pp[D] = M; pp[D + 1] = L; }
+    }
   }
+}
+
+// One CTA of D threads per (sequence, query head): combines the S partial results.
+__global__ void __launch_bounds__(D)
+paged_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int Hq, int S, long o_stride) {
+  const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const float* pp = part + ((long)b * Hq + h) * S * (D + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, pp[s * (D + 2) + D]);
+  float L = 0.f, O = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float ms = pp[s * (D + 2) + D];
+    const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    L += pp[s * (D + 2) + D + 1] * f;
+    O += pp[s * (D + 2) + d] * f;
+  }
+  out[(long)b * o_stride + (long)h * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
 }
 
 }  // namespace
@@ -150,25 +190,33 @@ AX_API int ax_paged_kv_write(const void* k, const void* v, void* kc, void* vc, c
 }
 
 // q [B, Hq, 128], out [B, Hq, 128] bf16 (row strides in elements); Hq/Hkv in {1, 2, 4, 8}.
+// splits > 1 needs `workspace` of B * Hq * splits * 130 floats.
 AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* vc, void* out,
                                      const int* block_table, const int* ctx_lens, int B, int Hq, int Hkv,
                                      int Dh, int page_size, int max_pages, float scale, long q_stride,
-                                     long o_stride, cudaStream_t stream) {
+                                     long o_stride, int splits, float* workspace, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (Dh != D || Hq % Hkv) return -1;
+  if (Dh != D || Hq % Hkv || splits < 1 || (splits > 1 && !workspace)) return -1;
   const int G = Hq / Hkv;
-  dim3 grid(B, Hkv);
+  dim3 grid(B, Hkv, splits);
   const float sl2 = scale * 1.4426950408889634f;
 #define AX_LAUNCH(GG)                                                                                         \
   paged_decode_kernel<GG><<<grid, kWarps * 32, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, \
-      (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, block_table, ctx_lens, Hq, Hkv, page_size, max_pages, sl2, \
-      q_stride, o_stride)
+      (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, workspace, block_table, ctx_lens, Hq, Hkv, page_size,     \
+      max_pages, sl2, q_stride, o_stride)
   switch (G) {
     case 1: AX_LAUNCH(1); break;
     case 2: AX_LAUNCH(2); break;
     case 4: AX_LAUNCH(4); break;
+    case 8: AX_LAUNCH(8); break;
     default: return -2;
   }
 #undef AX_LAUNCH
-  return (int)cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (splits > 1) {
+    paged_merge_kernel<<<dim3(B, Hq), D, 0, stream>>>(workspace, (__nv_bfloat16*)out, Hq, splits, o_stride);
+    e = cudaGetLastError();
+  }
+  return (int)e;
 }

@@ -34,13 +34,17 @@ def decode_attention(q, k_cache, v_cache, block_table, ctx_lens, page_size: int,
     B, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if q.is_cuda and N.have_gpu() and q.dtype == torch.bfloat16 and D == 128 and Hq // Hkv in (1, 2, 4):
+    if q.is_cuda and N.have_gpu() and q.dtype == torch.bfloat16 and D == 128 and Hq // Hkv in (1, 2, 4, 8):
         q = q.contiguous()
         out = torch.empty_like(q)
+        # context splits: enough CTAs for two per SM, at most one split per 32 tokens of capacity
+        capacity = block_table.shape[1] * page_size
+        splits = max(1, min(296 // max(B * Hkv, 1), (capacity + 31) // 32, 64))
+        ws = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
         rc = N.cuda().ax_paged_decode_attention(N.ptr(q), N.ptr(k_cache), N.ptr(v_cache), N.ptr(out), N.ptr(block_table),
                                                 N.ptr(ctx_lens), B, Hq, Hkv, D, page_size, block_table.shape[1],
                                                 N.c_float(scale), N.c_int64(q.stride(0)), N.c_int64(out.stride(0)),
-                                                N.stream_ptr())
+                                                splits, N.ptr(ws) if ws is not None else None, N.stream_ptr())
         N.check(rc, "ax_paged_decode_attention")
         return out
     outs = []

@@ -162,6 +162,26 @@ class LLMEngine:
         g.replay()
         return self._g_next[:B].clone()
 
+    def warmup(self, batch_sizes=None) -> None:
+        """Captures the decode graphs ahead of the first request (server start-up), so no request
+        pays for a capture.  Uses scratch sequences of one token that are freed afterwards."""
+        if not self.use_graphs or self.running or self.waiting:
+            return
+        sizes = sorted(set(batch_sizes or [1, 2, 4, 8, 16, 32, self.max_batch]))
+        dev = self.model.device
+        for B in sizes:
+            if B in self._graphs or B > self.max_batch:
+                continue
+            slots = [self.cache.allocate_seq() for _ in range(B)]
+            for sl in slots:
+                self.cache.reserve(sl, 1)
+            self._decode_step(torch.zeros(B, dtype=torch.long, device=dev),
+                              torch.tensor(slots, dtype=torch.int32, device=dev),
+                              torch.zeros(B, dtype=torch.int32, device=dev))
+            for sl in slots:
+                self.cache.free_seq(sl)
+        torch.cuda.synchronize(dev)
+
     def run_until_done(self) -> None:
         while self.waiting or self.running:
             self.step()

@@ -248,16 +248,18 @@ class QuantizedLlama:
         table = cache.block_table[slots_t.long()]
         seq_local = torch.arange(B, dtype=torch.int32, device=self.device)
         nq = self.hq * self.hd
+        h = Nm.rms_norm(x, self.layers[0].attn_norm, self.cfg.rms_norm_eps)
         for li, L in enumerate(self.layers):
-            h = Nm.rms_norm(x, L.attn_norm, self.cfg.rms_norm_eps)
             qkv = qlinear(h, L.wqkv).view(B, self.hq + 2 * self.hkv, self.hd)
             qkv = Mi.rope_positions(qkv, self.cos, self.sin, positions, rot_heads=self.hq + self.hkv)
             q, k, v = qkv[:, :self.hq], qkv[:, self.hq:self.hq + self.hkv], qkv[:, self.hq + self.hkv:]
             paged.kv_write(k, v, cache.k[li], cache.v[li], table, seq_local, positions, cache.page_size)
             a = paged.decode_attention(q.contiguous(), cache.k[li], cache.v[li], table, ctx, cache.page_size)
             o = self._all_reduce(qlinear(a.reshape(B, nq), L.wo))
-            x = x + o
-            h = Nm.rms_norm(x, L.ffn_norm, self.cfg.rms_norm_eps)
+            h, x = Nm.rms_norm(o, L.ffn_norm, self.cfg.rms_norm_eps, residual=x)     # x += o, fused
             d = self._all_reduce(qlinear(E.swiglu(qlinear(h, L.wgu)), L.wdown))
-            x = x + d
+            if li + 1 < len(self.layers):
+                h, x = Nm.rms_norm(d, self.layers[li + 1].attn_norm, self.cfg.rms_norm_eps, residual=x)
+            else:
+                x = x + d
         return x

@@ -129,6 +129,7 @@ def bench_q4k_decode(args):
         prompts = torch.randint(0, cfg.vocab_size, (conc, prompt_len), generator=gen).tolist()
         if conc == 1:      # warm-up pass (kernel attributes, allocator)
             LLMEngine(model, 64, prompt_len + 32, 16).generate(prompts, 4)
+        eng.warmup([conc])          # decode-graph capture is server start-up, not request time
         eng.generate(prompts, new_tokens)
         st = eng.stats()
         results[conc] = {"ttft_p50_ms": round(st["ttft_p50_s"] * 1e3, 2), "decode_tok_s": round(st["decode_tokens_per_s"], 1),
