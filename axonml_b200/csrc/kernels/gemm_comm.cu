@@ -3,9 +3,8 @@
 //  MODE_AG  all-gather -> GEMM (column-parallel Linear with sequence-parallel input):
 //           C[W*Tl, N] = act(concat_r(X_r)[W*Tl, K] * B[N, K]^T + bias).
 //           A few "pusher" CTAs copy this rank's shard X_rank, 128 rows at a time, into slot `rank`
-//           of every peer's gathered buffer (one NVSwitch multimem store per 16 bytes when a
-//           multicast mapping exists, else one peer store per peer) and raise a per-chunk flag in
-//           the peer's memory.  The GEMM CTAs start on the local shard at once and take the other
+//           of every peer's gathered buffer (bulk loads into shared memory, bulk stores to the
+//           peers' memory) and raise a per-chunk flag in the peer's memory.  The GEMM CTAs start on the local shard at once and take the other
 //           shards in ring order; the TMA producer of a tile waits for the flag of the chunk it
 //           is about to read, so the transfer overlaps the math chunk by chunk.  TMA reads only
 //           this GPU's own memory.
@@ -13,11 +12,11 @@
 //  MODE_RS  GEMM -> reduce-scatter (row-parallel Linear with sequence-parallel output):
 //           out[Tl, N] = act(sum_r (X_r[W*Tl, Kl] * B_r[N, Kl]^T)[rows of this rank] + bias).
 //           Every rank computes its partial product tile by tile, the destination shard after
-//           its own first and its own shard last, and the epilogue stores each finished tile
-//           (bf16) straight from TMEM into the destination rank's staging slot for this source,
-//           then raises a per-tile flag there.  When a CTA has finished its GEMM tiles it reduces
-//           tiles of the local shard: waits for the W flags of a tile, sums the W staged copies
-//           in fp32 and writes the result.  Deterministic (no floating-point atomics).
+//           its own first and its own shard last, and the epilogue sends each finished tile
+//           (bf16, TMEM -> shared memory -> tensor bulk store) into the destination rank's staging
+//           slot for this source, then raises a per-tile flag there.  The tiles of the rank's own
+//           rows come last: their epilogue waits for the peers' flags, adds the W-1 staged copies
+//           to the fp32 accumulator and writes the result.  Deterministic (no floating-point atomics).
 //
 // Flags hold the call's epoch and only grow; a rank tells its peers "call e consumed" at the end
 // of the kernel, and the next call waits for that before it overwrites peer memory.  Every wait
@@ -91,34 +90,143 @@ struct TileMap {
 };
 
 // This rank's shard -> slot `rank` of every peer's gathered buffer, one 128-row chunk at a time.
-__device__ void push_shard(const CommParams& p, int pusher, int npushers) {
+// One thread runs the whole copy as an asynchronous pipeline: bulk loads bring 16 KB pieces of the
+// local rows into shared memory, bulk stores send each piece to every peer (per-thread stores to a
+// peer are limited by the few outstanding writes an SM tracks; the bulk engine is not).  When the
+// stores of a chunk have completed, the chunk's flag is raised in every peer's memory.
+constexpr int kPushPiece = 16384;
+constexpr int kPushStages = 12;      // 192 KB of shared memory
+constexpr int kPushAhead = 4;        // loads in flight; the other stages hold pieces being sent
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)),
+               "r"(bytes)
+               : "memory");
+}
+
+// NVSwitch variant for more than two ranks: one multimem store delivers 16 bytes to every rank, so
+// the shard leaves this GPU once instead of W-1 times.  Thread 0 keeps the bulk loads running, all
+// threads forward from shared memory.
+__device__ void push_shard_multimem(const CommParams& p, int pusher, int npushers, uint8_t* buf, uint64_t* full,
+                                    volatile int* dead) {
   const int chunks = p.Tl / BM;
   const long row_bytes = (long)p.K * 2;
   const long chunk_bytes = (long)BM * row_bytes;
+  const int pieces = (int)(chunk_bytes / kPushPiece);
   __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    *dead = 0;
+    for (int i = 0; i < kPushStages; ++i) mbar_init(&full[i], 1);
+    mbar_fence_init();
+  }
   __syncthreads();
-  // the peers must have finished reading what the previous call put there
   if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank)
-    if (!wait_ge<true>(p.sig[p.rank] + kSigDone + threadIdx.x, p.epoch - 1, p.status, 800)) s_ok = 0;
+    if (!wait_ge<true>(p.sig[p.rank] + kSigDone + threadIdx.x, p.epoch - 1, p.status, 802)) s_ok = 0;
   __syncthreads();
   if (!s_ok) return;
-  for (int c = pusher; c < chunks; c += npushers) {
-    const uint8_t* src = p.x_local + (long)c * chunk_bytes;
-    const long dst_off = ((long)p.rank * p.Tl + (long)c * BM) * row_bytes;
-    for (long o = (long)threadIdx.x * 16; o < chunk_bytes; o += (long)blockDim.x * 16) {
-      const uint4 v = *reinterpret_cast<const uint4*>(src + o);
-      if (p.sym_mc != nullptr) {
-        multimem_st_b32x4(p.sym_mc + dst_off + o, v);
-      } else {
-        for (int q = 1; q < p.world; ++q) st_peer_v4(p.sym[(p.rank + q) % p.world] + dst_off + o, v);
+  int my_chunks = 0;
+  for (int c = pusher; c < chunks; c += npushers) ++my_chunks;
+  const long total = (long)my_chunks * pieces;
+  auto piece_src = [&](long i) {
+    const int c = pusher + (int)(i / pieces) * npushers;
+    return p.x_local + (long)c * chunk_bytes + (i % pieces) * (long)kPushPiece;
+  };
+  if (threadIdx.x == 0) {
+    for (long i = 0; i < kPushStages - 1 && i < total; ++i) {
+      mbar_expect_tx(&full[i % kPushStages], kPushPiece);
+      bulk_load_1d(buf + (i % kPushStages) * kPushPiece, piece_src(i), kPushPiece, &full[i % kPushStages]);
+    }
+  }
+  for (long i = 0; i < total; ++i) {
+    const int st = (int)(i % kPushStages);
+    if (threadIdx.x == 0) {
+      const long nx = i + kPushStages - 1;      // its stage was drained before the last barrier
+      if (nx < total) {
+        mbar_expect_tx(&full[nx % kPushStages], kPushPiece);
+        bulk_load_1d(buf + (nx % kPushStages) * kPushPiece, piece_src(nx), kPushPiece, &full[nx % kPushStages]);
       }
     }
-    __threadfence_system();
+    const bool ok = mbar_wait(&full[st], (uint32_t)((i / kPushStages) & 1), dead, p.status, 803);
+    if (!__syncthreads_and(ok)) return;
+    const int c = pusher + (int)(i / pieces) * npushers;
+    const long dst_off = ((long)p.rank * p.Tl + (long)c * BM) * row_bytes + (i % pieces) * (long)kPushPiece;
+    const uint32_t sbase = smem_u32(buf + st * kPushPiece);
+#pragma unroll 4
+    for (int j = threadIdx.x; j < kPushPiece / 16; j += kThreads) {
+      uint4 v;
+      asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sbase + j * 16));
+      multimem_st_b32x4(p.sym_mc + dst_off + (long)j * 16, v);
+    }
+    const bool chunk_done = (i % pieces) == pieces - 1;
+    if (chunk_done) __threadfence_system();
     __syncthreads();
-    if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank)
+    if (chunk_done && (int)threadIdx.x < p.world && (int)threadIdx.x != p.rank)
       st_release_sys(p.sig[threadIdx.x] + kSigFlags + (p.rank * p.max_tiles + c) * kFlagsPerTile, p.epoch);
   }
+}
+
+__device__ void push_shard(const CommParams& p, int pusher, int npushers, uint8_t* smem) {
+  const int chunks = p.Tl / BM;
+  const long row_bytes = (long)p.K * 2;
+  const long chunk_bytes = (long)BM * row_bytes;            // a multiple of 16 KB (K % 64 == 0)
+  const int pieces = (int)(chunk_bytes / kPushPiece);
+  uint8_t* buf = smem;                                                       // [stages][piece]
+  uint64_t* full = (uint64_t*)(smem + kPushStages * kPushPiece);             // [stages]
+  volatile int* dead = (volatile int*)(full + kPushStages);
+  if (p.sym_mc != nullptr && p.world > 2) {
+    push_shard_multimem(p, pusher, npushers, buf, full, dead);
+    return;
+  }
+  if (threadIdx.x != 0) return;
+  *dead = 0;
+  for (int i = 0; i < kPushStages; ++i) mbar_init(&full[i], 1);
+  mbar_fence_init();
+  // the peers must have finished reading what the previous call put there
+  for (int q = 0; q < p.world; ++q)
+    if (q != p.rank && !wait_ge<true>(p.sig[p.rank] + kSigDone + q, p.epoch - 1, p.status, 800)) return;
+  int my_chunks = 0;
+  for (int c = pusher; c < chunks; c += npushers) ++my_chunks;
+  const long total = (long)my_chunks * pieces;               // pieces this CTA forwards, in order
+  auto piece_src = [&](long i) {
+    const int c = pusher + (int)(i / pieces) * npushers;
+    return p.x_local + (long)c * chunk_bytes + (i % pieces) * (long)kPushPiece;
+  };
+  for (long i = 0; i < kPushAhead && i < total; ++i) {
+    mbar_expect_tx(&full[i % kPushStages], kPushPiece);
+    bulk_load_1d(buf + (i % kPushStages) * kPushPiece, piece_src(i), kPushPiece, &full[i % kPushStages]);
+  }
+  for (long i = 0; i < total; ++i) {
+    const int st = (int)(i % kPushStages);
+    if (!mbar_wait(&full[st], (uint32_t)((i / kPushStages) & 1), dead, p.status, 801)) break;
+    const int c = pusher + (int)(i / pieces) * npushers;
+    const long dst_off = ((long)p.rank * p.Tl + (long)c * BM) * row_bytes + (i % pieces) * (long)kPushPiece;
+    for (int q = 1; q < p.world; ++q)
+      bulk_store_1d(p.sym[(p.rank + q) % p.world] + dst_off, buf + st * kPushPiece, kPushPiece);
+    tma_store_commit();
+    // the stage that piece i + kPushAhead will use was last read by the stores of piece
+    // i + kPushAhead - kPushStages: allow the more recent groups to stay in flight
+    tma_store_wait_read<kPushStages - kPushAhead>();
+    const long nx = i + kPushAhead;
+    if (nx < total) {
+      mbar_expect_tx(&full[nx % kPushStages], kPushPiece);
+      bulk_load_1d(buf + (nx % kPushStages) * kPushPiece, piece_src(nx), kPushPiece, &full[nx % kPushStages]);
+    }
+    if ((i % pieces) == pieces - 1) {
+      tma_store_wait<0>();                 // the chunk has landed on every peer
+      fence_proxy_async_global();
+      __threadfence_system();
+      for (int q = 0; q < p.world; ++q)
+        if (q != p.rank) st_release_sys(p.sig[q] + kSigFlags + (p.rank * p.max_tiles + c) * kFlagsPerTile, p.epoch);
+    }
+  }
+  tma_store_wait<0>();
 }
 
 // Last CTA of the launch tells every peer that this rank has consumed the call.
@@ -135,19 +243,21 @@ __device__ __forceinline__ void finish_call(const CommParams& p) {
   }
 }
 
+struct DstMaps { CUtensorMap m[kMaxRanks]; };     // RS: every rank's staging buffer as [world*Tl, N]
+
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_local,
                  const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
-                 const CommParams p) {
+                 const __grid_constant__ DstMaps dst_maps, const CommParams p) {
   using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   if (MODE == MODE_AG && (int)blockIdx.x < p.pushers) {
-    push_shard(p, blockIdx.x, p.pushers);
+    push_shard(p, blockIdx.x, p.pushers, smem);
     finish_call(p);
     return;
   }
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
   uint8_t* epi_base = smem + C::kStages * C::kStage;
   uint64_t* bars = (uint64_t*)(epi_base + kEpiWarps * 2 * kStageBufBytes);
@@ -251,10 +361,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;
     const int ew = warp - 2;
-    const int et = ew * 32 + lane;            // 0..127 inside the epilogue group
     uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
     int buf = 0, it = 0;
     bool ok = true;
+    uint32_t* prev_flag = nullptr;      // lane 0: flag of the tile whose stores are still in flight
     if (MODE == MODE_RS) {
       // peers must have consumed the previous call before their staging slots are overwritten
       // (every warp checks for itself: no barrier that a timed-out warp could leave hanging)
@@ -320,9 +430,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tma_store_commit();
           }
           buf ^= 1;
-        } else {
-          // partial tile -> staging slot `rank` on the rank that owns these rows
-          uint8_t* dst = p.sym[shard] + (((long)p.rank * p.Tl + mb * BM + q * 32 + lane) * p.N + ncol0) * 2;
+        } else if (shard != p.rank) {
+          // partial tile -> staging slot `rank` on the rank that owns these rows: the warp's
+          // 32 x 64 sub-tile is staged in shared memory and sent with one tensor bulk store.
+          uint8_t* dst = stg + buf * kStageBufBytes;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             uint4 o;
@@ -330,58 +443,110 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
             o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
             o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
-            if (ncol0 + c * 8 < p.N) st_peer_v4(dst + c * 16, o);
+            *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
           }
-        }
-      }
-      if (MODE == MODE_RS) {
-        // this warp's quarter of the tile is on its way: one flag per epilogue warp
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0)
-          st_release_sys(p.sig[shard] + kSigFlags + ((p.rank * p.max_tiles + mb * tm.num_n + nb) * kFlagsPerTile + ew), p.epoch);
-      }
-    }
-    if (MODE == MODE_AG) {
-      if (lane == 0) tma_store_wait<0>();
-    } else if (ok) {
-      // -------------------------------------------------------- reduce the local shard's tiles
-      const int work = tm.mbs * tm.num_n;
-      const long row_bytes = (long)p.N * 2;
-      for (int w = cta; w < work && ok; w += ncta) {
-        const int mb = w / tm.num_n, nb = w - mb * tm.num_n;
-        bool w_ok = true;       // lane l: source rank l / 4, epilogue warp l % 4
-        if (lane < p.world * kFlagsPerTile)
-          w_ok = wait_ge<true>(my_flags + ((lane / kFlagsPerTile) * p.max_tiles + w) * kFlagsPerTile + (lane % kFlagsPerTile),
-                               p.epoch, p.status, 840);
-        ok = __all_sync(0xffffffffu, w_ok);
-        if (!ok) break;
-        const int cols = min(BN, p.N - nb * BN);
-        const int vec_per_row = cols / 8;
-        for (int v = et; v < BM * vec_per_row; v += 128) {
-          const int row = v / vec_per_row, cv = v - row * vec_per_row;
-          const long off = ((long)(mb * BM + row)) * row_bytes + ((long)nb * BN + cv * 8) * 2;
-          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int src = 0; src < p.world; ++src) {
-            const uint4 u = ld_peer_v4(p.sym[p.rank] + (long)src * p.Tl * row_bytes + off);
-            const float2 x0 = unpack_bf16x2(u.x), x1 = unpack_bf16x2(u.y), x2 = unpack_bf16x2(u.z), x3 = unpack_bf16x2(u.w);
-            a[0] += x0.x; a[1] += x0.y; a[2] += x1.x; a[3] += x1.y; a[4] += x2.x; a[5] += x2.y; a[6] += x3.x; a[7] += x3.y;
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&dst_maps.m[shard], dst, ncol0, p.rank * p.Tl + mb * BM + q * 32);
+            tma_store_commit();
           }
-          const int n = nb * BN + cv * 8;
+          buf ^= 1;
+        } else {
+          // a tile of this rank's own rows (scheduled last): add the peers' staged partial tiles
+          // to the fp32 accumulator and write the finished output; nothing is staged locally
+          if (ch == 0) {
+            // the flag still owed for the last remote tile must go out first: the peers' own-row
+            // tiles wait for it exactly as this one waits for theirs
+            if (lane == 0 && prev_flag != nullptr) {
+              tma_store_wait<0>();
+              fence_proxy_async_global();
+              __threadfence_system();
+              st_release_sys(prev_flag, p.epoch);
+              prev_flag = nullptr;
+            }
+            __syncwarp();
+            bool w_ok = true;       // lane l: the same quarter of this tile as sent by rank l
+            if (lane < p.world && lane != p.rank)
+              w_ok = wait_ge<true>(my_flags + ((lane * p.max_tiles + mb * tm.num_n + nb) * kFlagsPerTile + ew), p.epoch,
+                                   p.status, 840);
+            ok = __all_sync(0xffffffffu, w_ok);
+          }
+          if (ok) {
+            const long row_off = ((long)(mb * BM + q * 32 + lane) * p.N + ncol0) * 2;
+            for (int src = 0; src < p.world; ++src) {
+              if (src == p.rank) continue;
+              const uint8_t* sp = p.sym[p.rank] + (long)src * p.Tl * p.N * 2 + row_off;
+              uint4 u[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float b = 0.f;
-            if (p.bias_kind == 1) b = __ldg((const float*)p.bias + n + j);
-            else if (p.bias_kind == 2) b = __bfloat162float(((const __nv_bfloat16*)p.bias)[n + j]);
-            a[j] = apply_act(a[j] + b, p.act);
+              for (int c = 0; c < 8; ++c) u[c] = ld_peer_v4(sp + c * 16);
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                const float2 x0 = unpack_bf16x2(u[c].x), x1 = unpack_bf16x2(u[c].y), x2 = unpack_bf16x2(u[c].z),
+                             x3 = unpack_bf16x2(u[c].w);
+                r[c * 8 + 0] = __float_as_uint(__uint_as_float(r[c * 8 + 0]) + x0.x);
+                r[c * 8 + 1] = __float_as_uint(__uint_as_float(r[c * 8 + 1]) + x0.y);
+                r[c * 8 + 2] = __float_as_uint(__uint_as_float(r[c * 8 + 2]) + x1.x);
+                r[c * 8 + 3] = __float_as_uint(__uint_as_float(r[c * 8 + 3]) + x1.y);
+                r[c * 8 + 4] = __float_as_uint(__uint_as_float(r[c * 8 + 4]) + x2.x);
+                r[c * 8 + 5] = __float_as_uint(__uint_as_float(r[c * 8 + 5]) + x2.y);
+                r[c * 8 + 6] = __float_as_uint(__uint_as_float(r[c * 8 + 6]) + x3.x);
+                r[c * 8 + 7] = __float_as_uint(__uint_as_float(r[c * 8 + 7]) + x3.y);
+              }
+            }
+            if (p.bias_kind != 0) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                const int n = ncol0 + j;
+                const float b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n) : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
+                r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
+              }
+            }
+            uint8_t* dst = stg + buf * kStageBufBytes;
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              uint4 o;
+              o.x = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 0]), p.act), apply_act(__uint_as_float(r[c * 8 + 1]), p.act));
+              o.y = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 2]), p.act), apply_act(__uint_as_float(r[c * 8 + 3]), p.act));
+              o.z = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 4]), p.act), apply_act(__uint_as_float(r[c * 8 + 5]), p.act));
+              o.w = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 6]), p.act), apply_act(__uint_as_float(r[c * 8 + 7]), p.act));
+              *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_c, dst, ncol0, mb * BM + q * 32);
+              tma_store_commit();
+            }
+            buf ^= 1;
           }
-          uint4 o;
-          o.x = pack_bf16x2(a[0], a[1]); o.y = pack_bf16x2(a[2], a[3]);
-          o.z = pack_bf16x2(a[4], a[5]); o.w = pack_bf16x2(a[6], a[7]);
-          *reinterpret_cast<uint4*>(p.out + off) = o;
         }
       }
+      if (MODE == MODE_RS && shard != p.rank) {
+        // Flags are one tile late: waiting for the previous tile's stores to complete (a round
+        // trip over NVLink) then overlaps this tile's work instead of stalling after every tile.
+        if (lane == 0) {
+          if (prev_flag != nullptr) {
+            tma_store_wait<BN / 64>();          // all but this tile's groups have completed
+            fence_proxy_async_global();
+            __threadfence_system();
+            st_release_sys(prev_flag, p.epoch);
+          }
+          prev_flag = p.sig[shard] + kSigFlags + ((p.rank * p.max_tiles + mb * tm.num_n + nb) * kFlagsPerTile + ew);
+        }
+        __syncwarp();
+      }
     }
+    if (MODE == MODE_RS && lane == 0 && prev_flag != nullptr) {
+      tma_store_wait<0>();
+      fence_proxy_async_global();
+      __threadfence_system();
+      st_release_sys(prev_flag, p.epoch);
+    }
+    __syncwarp();
+    if (lane == 0) tma_store_wait<0>();
   }
 
   tc_fence_before();
@@ -402,7 +567,7 @@ int make_map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer,
 
 template <int BN, int MODE>
 int launch(const CUtensorMap& ma, const CUtensorMap& mal, const CUtensorMap& mb, const CUtensorMap& mc,
-           const CommParams& p, int grid, cudaStream_t stream) {
+           const DstMaps& dm, const CommParams& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kern = gemm_comm_kernel<BN, MODE>;
   static bool configured = false;
@@ -411,7 +576,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mal, const CUtensorMap& mb,
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mal, mb, mc, p);
+  kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mal, mb, mc, dm, p);
   return (int)cudaGetLastError();
 }
 
@@ -462,13 +627,22 @@ AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out,
     rc = make_map_2d(&ma, x_local, (uint64_t)K, (uint64_t)world * Tl, (uint64_t)K, BK, BM);
     if (rc) return 1000 + rc;
     mal = ma;
-    mc = ma;
+    rc = make_map_2d(&mc, out, (uint64_t)N, (uint64_t)Tl, (uint64_t)N, 64, 32);
+    if (rc) return 3000 + rc;
+  }
+  DstMaps dm;
+  for (int i = 0; i < kMaxRanks; ++i) dm.m[i] = ma;
+  if (mode == MODE_RS) {
+    for (int i = 0; i < world; ++i) {
+      rc = make_map_2d(&dm.m[i], sym[i], (uint64_t)N, (uint64_t)world * Tl, (uint64_t)N, 64, 32);
+      if (rc) return 4000 + rc;
+    }
   }
   rc = make_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, (uint32_t)BN);
   if (rc) return 2000 + rc;
   if (BN == 256)
-    return mode == MODE_AG ? launch<256, MODE_AG>(ma, mal, mb, mc, p, grid, stream)
-                           : launch<256, MODE_RS>(ma, mal, mb, mc, p, grid, stream);
-  return mode == MODE_AG ? launch<128, MODE_AG>(ma, mal, mb, mc, p, grid, stream)
-                         : launch<128, MODE_RS>(ma, mal, mb, mc, p, grid, stream);
+    return mode == MODE_AG ? launch<256, MODE_AG>(ma, mal, mb, mc, dm, p, grid, stream)
+                           : launch<256, MODE_RS>(ma, mal, mb, mc, dm, p, grid, stream);
+  return mode == MODE_AG ? launch<128, MODE_AG>(ma, mal, mb, mc, dm, p, grid, stream)
+                         : launch<128, MODE_RS>(ma, mal, mb, mc, dm, p, grid, stream);
 }

@@ -50,7 +50,9 @@ def embedding(idx, weight, *, pos_weight=None, seq_len: int = 1, pos0: int = 0,
         return _EmbeddingFn.apply(idx, weight.contiguous(),
                                   None if pos_weight is None else pos_weight.contiguous(),
                                   seq_len, pos0, padding_idx)
-    out = F.embedding(idx.long(), weight, padding_idx=None if padding_idx < 0 else padding_idx)
+    neg = idx < 0                     # negative ids give zero rows (vocabulary-parallel tables)
+    out = F.embedding(idx.long().clamp_min(0), weight, padding_idx=None if padding_idx < 0 else padding_idx)
+    out = out.masked_fill(neg.unsqueeze(-1), 0)
     if pos_weight is not None:
         pos = (torch.arange(idx.numel(), device=idx.device) % seq_len + pos0).view(idx.shape)
         out = out + F.embedding(pos, pos_weight)

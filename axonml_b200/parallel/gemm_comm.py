@@ -26,7 +26,16 @@ from ..ops import elementwise as E
 from .symm import SymmetricHeap, available
 
 _MAX_TILES = 4096
-_PUSHERS = 8
+_PUSHER_GBS = 17.0        # bytes one copy CTA moves per second towards the peers (measured, GB/s)
+
+
+def _pushers(tl: int, k: int, n: int, world: int, grid: int, multimem: bool) -> int:
+    """Copy CTAs for the all-gather: enough that the shard is out before the GEMM has finished the
+    local shard's tiles, no more (every copy CTA is one SM less for the math)."""
+    local_gemm_s = 2.0 * tl * k * n / 1.4e15
+    copies = 1 if (multimem and world > 2) else world - 1
+    need = tl * k * 2 * copies / (_PUSHER_GBS * 1e9) / max(0.7 * local_gemm_s, 1e-6)
+    return int(min(max(need + 0.999, 4), 24, grid // 4))
 
 
 class _Channel:
@@ -93,7 +102,8 @@ class FusedGemmComm:
         rc = N.cuda().ax_gemm_comm(
             mode, N.ptr(x), N.ptr(weight), N.ptr(out), ch.data.ptr_array(), ch.data.mc(), ch.sig.ptr_array(),
             N.ptr(bias), bias_kind, ACT[act], tl, n, k, self.rank, self.world, ctypes.c_uint(ch.epoch),
-            _MAX_TILES, _PUSHERS, self.grid, N.ptr(N.status_word(x.device)), N.stream_ptr())
+            _MAX_TILES, _pushers(tl, k, n, self.world, self.grid, bool(ch.data.mc_ptr)), self.grid,
+            N.ptr(N.status_word(x.device)), N.stream_ptr())
         N.check(rc, "ax_gemm_comm")
 
     def ag_gemm(self, x_local, weight, bias=None, act="none"):

@@ -215,22 +215,70 @@ class VocabParallelEmbedding(Module):
         return reduce_from_tensor_parallel(out, self.pg)
 
 
+class _VocabParallelCE(torch.autograd.Function):
+    """Mean cross-entropy from a vocabulary slice of the logits.  Rows are processed in chunks so
+    that the fp32 temporaries stay small next to the (large) bf16 logits."""
+
+    CHUNK = 4096
+
+    @staticmethod
+    def forward(ctx, logits, target, pg, vocab_start, ignore_index, valid_vocab):
+        T, V = logits.shape
+        dev = logits.device
+        n_valid_cols = V if valid_vocab is None else max(0, min(V, valid_vocab - vocab_start))
+        m = torch.empty(T, dtype=torch.float32, device=dev)
+        for i in range(0, T, _VocabParallelCE.CHUNK):
+            blk = logits[i:i + _VocabParallelCE.CHUNK, :n_valid_cols]
+            m[i:i + blk.shape[0]] = blk.max(dim=-1).values.float() if n_valid_cols else float("-inf")
+        if pg.world_size() > 1:
+            pg.backend().all_reduce(m, ReduceOp.Max)
+        s = torch.empty(T, dtype=torch.float32, device=dev)
+        picked = torch.zeros(T, dtype=torch.float32, device=dev)
+        local_t = target - vocab_start
+        mine = (local_t >= 0) & (local_t < n_valid_cols)
+        for i in range(0, T, _VocabParallelCE.CHUNK):
+            blk = logits[i:i + _VocabParallelCE.CHUNK, :n_valid_cols].float()
+            j = i + blk.shape[0]
+            s[i:j] = (blk - m[i:j, None]).exp().sum(-1)
+            idx = local_t[i:j].clamp(0, max(n_valid_cols - 1, 0)).unsqueeze(-1)
+            if n_valid_cols:
+                picked[i:j] = torch.where(mine[i:j], torch.gather(blk, -1, idx).squeeze(-1), picked[i:j])
+        both = torch.stack([s, picked])
+        if pg.world_size() > 1:
+            pg.backend().all_reduce(both, ReduceOp.Sum)
+        s, picked = both[0], both[1]
+        lse = m + s.log()
+        valid = target != ignore_index
+        count = valid.sum().clamp_min(1).float()
+        loss = torch.where(valid, lse - picked, torch.zeros_like(lse)).sum() / count
+        ctx.save_for_backward(logits, lse, local_t, mine & valid, valid, count)
+        ctx.n_valid_cols = n_valid_cols
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, lse, local_t, hit, valid, count = ctx.saved_tensors
+        T, V = logits.shape
+        nv = ctx.n_valid_cols
+        grad = torch.zeros_like(logits)
+        scale = (g / count).float()
+        for i in range(0, T, _VocabParallelCE.CHUNK):
+            blk = logits[i:i + _VocabParallelCE.CHUNK, :nv].float()
+            j = i + blk.shape[0]
+            p = (blk - lse[i:j, None]).exp()
+            rows = torch.nonzero(hit[i:j]).squeeze(-1)
+            if rows.numel():
+                p[rows, local_t[i:j][rows]] -= 1.0
+            p *= (valid[i:j].float() * scale)[:, None]
+            grad[i:j, :nv] = p.to(logits.dtype)
+        return grad, None, None, None, None, None
+
+
 def vocab_parallel_cross_entropy(local_logits: torch.Tensor, target: torch.Tensor, pg: ProcessGroup,
-                                 vocab_start: int, ignore_index: int = -100) -> torch.Tensor:
-    """Mean cross-entropy over logits whose class dim is split across ranks: local max and
-    sum-exp are combined with two small all-reduces, so the full logits are never gathered."""
-    lf = local_logits.float()
-    m = lf.max(dim=-1).values.detach()
-    if pg.world_size() > 1:
-        pg.backend().all_reduce(m, ReduceOp.Max)
-    e = (lf - m.unsqueeze(-1)).exp()
-    s = reduce_from_tensor_parallel(e.sum(-1), pg)
-    lse = m + s.log()
-    V = lf.shape[-1]
-    local_t = target - vocab_start
-    mine = (local_t >= 0) & (local_t < V)
-    picked = torch.gather(lf, -1, local_t.clamp(0, V - 1).unsqueeze(-1)).squeeze(-1)
-    picked = reduce_from_tensor_parallel(torch.where(mine, picked, torch.zeros_like(picked)), pg)
-    valid = target != ignore_index
-    loss = torch.where(valid, lse - picked, torch.zeros_like(lse))
-    return loss.sum() / valid.sum().clamp_min(1)
+                                 vocab_start: int, ignore_index: int = -100,
+                                 valid_vocab: int | None = None) -> torch.Tensor:
+    """Mean cross-entropy over logits whose class dim is split across ranks: the row maxima and
+    the sum-exp / target-logit pairs are combined with two small all-reduces, so the full logits
+    are never gathered.  ``valid_vocab``: size of the real vocabulary when the split one was
+    padded (columns beyond it are ignored)."""
+    return _VocabParallelCE.apply(local_logits, target, pg, vocab_start, ignore_index, valid_vocab)

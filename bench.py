@@ -154,32 +154,79 @@ def bench_q4k_decode(args):
     return 0
 
 
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
-            reference_arm(args)
-        return 0
-    if args.config == "q4k_decode":
-        return bench_q4k_decode(args)
-
+def _dist_setup():
     import torch
-    import torch.distributed as dist
-
-    from axonml_b200 import _native, optim
-    from axonml_b200.llm import GPT2Config, GPT2LMHead
-    from axonml_b200.parallel import FSDP, NcclBackend, ProcessGroup
-
+    from axonml_b200.parallel import NcclBackend, ProcessGroup
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        pg = ProcessGroup(NcclBackend.init(timeout_s=600))
-    else:
-        pg = ProcessGroup.mock()
+    pg = ProcessGroup(NcclBackend.init(timeout_s=600)) if world > 1 else ProcessGroup.mock()
+    return world, rank, local, dev, pg
 
+
+def timed_training(args, world, rank, local, dev, step_device, step_e2e):
+    """Warm-up, K device-timed steps (CUDA events, max over ranks), then K end-to-end steps timed
+    on the host around synchronisations.  Returns the measurements of this run."""
+    import torch
+    import torch.distributed as dist
+    from axonml_b200 import _native
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step_device(i)
+    sync_all()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for i in range(args.steps):
+        loss = step_device(i)
+    e1.record()
+    sync_all()
+    ms_total = e0.elapsed_time(e1)
+    launches = _native.launch_count() - launches0
+    last_loss = float(loss.item())
+    sync_all()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        l_host = step_e2e(i)
+    sync_all()
+    e2e_ms = (time.perf_counter() - t0) * 1000.0
+    clocks = sampler.stop() if rank == 0 else None
+    _native.check_status()
+    if world > 1:
+        t = torch.tensor([ms_total, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, e2e_ms = t.tolist()
+    return {"ms_per_step": ms_total / args.steps, "e2e_ms_per_step": e2e_ms / args.steps, "launches": launches,
+            "clocks": clocks, "last_loss": last_loss, "e2e_last_loss": l_host}
+
+
+def _finish(world):
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def bench_gpt_fsdp(args):
+    import torch
+    from axonml_b200 import optim
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    from axonml_b200.parallel import FSDP
+
+    world, rank, local, dev, pg = _dist_setup()
     torch.manual_seed(1234 + rank)
     cfg = GPT2Config.gpt_1_3b()
     if args.layers:
@@ -205,91 +252,132 @@ def main():
     host_ids = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(n_host)]
     dev_ids = [t.to(dev) for t in host_ids[:4]]
 
-    def step_device(i):
-        loss, _ = engine.call("forward_with_loss", dev_ids[i % 4])
+    def run(ids):
+        loss, _ = engine.call("forward_with_loss", ids)
         loss.backward()
         opt.step()
         engine.zero_grad()
         return loss
 
+    def step_device(i):
+        return run(dev_ids[i % 4])
+
     def step_e2e(i):
         ids = host_ids[i % n_host].to(dev, non_blocking=True)       # H2D from pinned memory
-        loss, _ = engine.call("forward_with_loss", ids)
-        loss.backward()
-        opt.step()
-        engine.zero_grad()
-        return float(loss.item())                                     # D2H of the step's result
+        return float(run(ids).item())                                 # D2H of the step's result
 
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        step_device(i)
-    sync_all()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = _native.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    for i in range(args.steps):
-        loss = step_device(i)
-    e1.record()
-    sync_all()
-    ms_total = e0.elapsed_time(e1)
-    launches = _native.launch_count() - launches0
-    last_loss = float(loss.item())
-
-    # end-to-end loop (host inputs + loss read-back every step), timed on the host around syncs
-    sync_all()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        l_host = step_e2e(i)
-    sync_all()
-    e2e_s = time.perf_counter() - t0
-    clocks = sampler.stop() if rank == 0 else None
-    _native.check_status()
-
-    if world > 1:
-        t = torch.tensor([ms_total, e2e_s * 1000.0], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, e2e_ms = t.tolist()
-    else:
-        e2e_ms = e2e_s * 1000.0
-
+    m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
     tokens_per_step = B * S * world
-    ms_per_step = ms_total / args.steps
-    value = tokens_per_step / (ms_per_step / 1000.0)
-    e2e_value = tokens_per_step / (e2e_ms / args.steps / 1000.0)
     if rank == 0:
         out = {
             "metric": "tokens/s 1.3B-FSDP (GPT 1.3B, FSDP ZeRO-3, training)",
-            "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "value": round(tokens_per_step / (m["ms_per_step"] / 1000.0), 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms_per_step"], 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "axonml_b200",
             "config": {"model": "gpt-1.3b (24L d2048 16h ffn8192 vocab50257)",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"fsdp{world}-zero3",
                        "optimizer": "AdamW lr3e-4 b(0.9,0.95) wd0.1", "grad_checkpointing": True,
                        "layers": cfg.n_layer, "grad_comm": comm_path,
                        "l2_policy": "per-step working set (weights+optimizer state > 20 GB) far exceeds the 126 MB L2"},
-            "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
+            "clocks": m["clocks"],
+            "e2e": {"value": round(tokens_per_step / (m["e2e_ms_per_step"] / 1000.0), 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4,
-                    "ms_per_step": round(e2e_ms / args.steps, 3)},
-            "gpu_launches": launches,
-            "final_loss": round(last_loss, 4), "e2e_final_loss": round(l_host, 4),
+                    "ms_per_step": round(m["e2e_ms_per_step"], 3)},
+            "gpu_launches": m["launches"],
+            "final_loss": round(m["last_loss"], 4), "e2e_final_loss": round(m["e2e_last_loss"], 4),
         }
         print(json.dumps(out), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    return 0
+    return _finish(world)
+
+
+def bench_llama_tp(args):
+    """Llama-style 8B, tensor parallel over all GPUs of the job (sequence-parallel residual stream,
+    fused all-gather->GEMM / GEMM->reduce-scatter kernels), AdamW with fp32 master weights.  One
+    optimizer step = 8 sequences of 4096 tokens (strong scaling); a rank group of N GPUs runs them
+    as 8/N micro-batches of N sequences, so every rank always holds 4096 tokens of the residual
+    stream and the activation memory per GPU does not depend on N."""
+    import torch
+    from axonml_b200 import optim
+    from axonml_b200.llm import LLaMAConfig
+    from axonml_b200.llm.llama_tp import TPLLaMAForCausalLM
+    from axonml_b200.optim.mixed import MasterParams
+    from axonml_b200.parallel import fused_gemm
+
+    world, rank, local, dev, pg = _dist_setup()
+    cfg = LLaMAConfig.llama3_8b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    S = args.seq_len if args.seq_len != 2048 else 4096
+    global_batch = 8
+    micro = min(global_batch, world) if args.micro_batch == 4 else args.micro_batch
+    n_micro = global_batch // micro
+    if args.comm == "nccl":
+        fused_gemm._ENGINES[id(pg.backend())] = None         # composed baseline: NCCL + plain GEMM
+    torch.manual_seed(4321 + rank)
+    model = TPLLaMAForCausalLM(cfg, pg, device=dev, dtype=torch.bfloat16)
+    model.train()
+    mp = MasterParams(model.parameters())
+    opt = optim.AdamW(mp.parameters(), 3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    gen = torch.Generator(device="cpu").manual_seed(77)       # the same ids on every rank
+    n_host = max(args.steps, 2)
+    host_ids = [torch.randint(0, cfg.vocab_size, (global_batch, S), generator=gen).pin_memory() for _ in range(n_host)]
+    dev_ids = [t.to(dev) for t in host_ids[:2]]
+
+    def run(ids):
+        total = None
+        for j in range(n_micro):
+            loss = model.forward_with_loss(ids[j * micro:(j + 1) * micro]) / n_micro
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        model.sync_replicated_grads()
+        mp.attach_grads()
+        opt.step()
+        mp.zero_grad()
+        return total
+
+    def step_device(i):
+        return run(dev_ids[i % 2])
+
+    def step_e2e(i):
+        return float(run(host_ids[i % n_host].to(dev, non_blocking=True)).item())
+
+    m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
+    tokens = global_batch * S
+    fused = fused_gemm._ENGINES.get(id(pg.backend())) is not None
+    if rank == 0:
+        print(json.dumps({
+            "metric": "tokens/s 8B-TP8 (Llama-style 8B, tensor parallel, training)",
+            "value": round(tokens / (m["ms_per_step"] / 1000.0), 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms_per_step"], 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "axonml_b200",
+            "config": {"model": f"llama-8b ({cfg.num_hidden_layers}L d4096 32q/8kv ffn14336 vocab128256)",
+                       "global_batch": global_batch, "seq_len": S, "parallelism": f"tp{world} (sequence-parallel)",
+                       "micro_batches": n_micro, "optimizer": "AdamW lr3e-4 b(0.9,0.95) wd0.1, fp32 master weights",
+                       "tp_collectives": "fused all-gather->GEMM / GEMM->reduce-scatter kernels" if fused else
+                                         ("nccl + GEMM" if world > 1 else "none (1 GPU)"),
+                       "l2_policy": "per-step working set (>= 14 GB of weights and optimizer state per GPU) exceeds the 126 MB L2"},
+            "clocks": m["clocks"],
+            "e2e": {"value": round(tokens / (m["e2e_ms_per_step"] / 1000.0), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": global_batch * S * 8, "d2h_bytes_per_step": 4,
+                    "ms_per_step": round(m["e2e_ms_per_step"], 3)},
+            "gpu_launches": m["launches"],
+            "final_loss": round(m["last_loss"], 4), "e2e_final_loss": round(m["e2e_last_loss"], 4)}), flush=True)
+    return _finish(world)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            reference_arm(args)
+        return 0
+    if args.config == "q4k_decode":
+        return bench_q4k_decode(args)
+    if args.config == "llama8b_tp":
+        return bench_llama_tp(args)
+    return bench_gpt_fsdp(args)
 
 
 if __name__ == "__main__":
