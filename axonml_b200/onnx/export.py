@@ -111,6 +111,10 @@ def export_module(module, input_shape, name: str = "model") -> OnnxExporter:
     ex.add_input("input", ["batch"] + list(input_shape[1:]))
     cur, k = "input", 0
     act = {nn.ReLU: "Relu", nn.Sigmoid: "Sigmoid", nn.Tanh: "Tanh", nn.GELU: "Gelu", nn.Identity: "Identity"}
+    if not isinstance(module, nn.Sequential):
+        # a wrapper whose only child is the layer stack (MLP), or whose children run in order
+        subs = list(module.children())
+        module = subs[0] if len(subs) == 1 and isinstance(subs[0], nn.Sequential) else subs
     for layer in module:
         out = f"t{k}"
         k += 1
