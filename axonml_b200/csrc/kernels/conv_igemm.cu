@@ -1,0 +1,336 @@
+// Implicit-GEMM 2-D convolution (stride 1, NHWC bf16, fp32 accumulation) on tcgen05:
+//
+//     y[n, ho, wo, co] = act(bias[co] + sum_{r,s,ci} x[n, ho + r - ph, wo + s - pw, ci] * w[co, r, s, ci])
+//
+// No im2col matrix is materialised.  A GEMM row is an output pixel; a tile of 128 rows is a
+// TN x TH x TW box of pixels, so for filter tap (r, s) and a block of 64 input channels the A
+// operand of the tile is simply the same box of the INPUT shifted by (r - ph, s - pw): one 4-D
+// tiled TMA load, whose out-of-range coordinates (the zero padding, ragged edges) are filled with
+// zeros by the TMA unit.  Shared memory then holds [pixel][64 channels] rows of 128 bytes in the
+// 128-byte swizzle: exactly the K-major operand tcgen05.mma wants.  The filter matrix
+// [Cout, kh*kw*Cin] is the K-major B operand, loaded as in the plain GEMM.  The K loop runs over
+// taps x channel blocks.  The epilogue (bias, optional ReLU) stores each warp's 32 pixels x 64
+// channels with one 4-D TMA store, which also clips ragged tiles.
+//
+// The data gradient of a stride-1 convolution is the same kernel on the output gradient with the
+// filter flipped and its channel dims exchanged and padding k-1-p.
+//
+// Replaces the reference's 7-deep scalar loop (crates/axonml-nn/src/layers/conv.rs:256-337) and
+// its WGSL direct-convolution shader (crates/axonml-core/src/backends/wgpu_backend.rs:1364-1427).
+#include "common.cuh"
+
+namespace {
+using namespace ax;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int kEpiWarps = 4;
+constexpr int kStageBufBytes = 32 * 128;
+
+struct ConvParams {
+  int N, H, W, Cin, Cout, Ho, Wo;
+  int kh, kw, ph, pw;
+  int TN, TH, TW;          // pixel box of a tile, TN*TH*TW == 128
+  int bw, bh, bn;          // pixel box of one epilogue warp, bw*bh*bn == 32
+  const void* bias;
+  int bias_kind;           // 0 none, 1 fp32, 2 bf16
+  int act;
+  int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmem = 1024 + kStages * kStage + kEpiWarps * 2 * kStageBufBytes + 256;
+};
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int x, int y, int z,
+                                             int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               :
+               : "l"((uint64_t)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                  const __grid_constant__ CUtensorMap map_y, const ConvParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* epi_base = smem + C::kStages * C::kStage;
+  uint64_t* bars = (uint64_t*)(epi_base + kEpiWarps * 2 * kStageBufBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::kStages;
+  uint64_t* tfull_bar = bars + 2 * C::kStages;
+  uint64_t* tempty_bar = bars + 2 * C::kStages + 2;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * C::kStages + 4);
+  volatile int* dead = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_w = (p.Wo + p.TW - 1) / p.TW;
+  const int tiles_h = (p.Ho + p.TH - 1) / p.TH;
+  const int tiles_n = (p.N + p.TN - 1) / p.TN;
+  const int tiles_c = (p.Cout + BN - 1) / BN;
+  const int num_tiles = tiles_w * tiles_h * tiles_n * tiles_c;
+  const int cblocks = p.Cin / BK;
+  const int num_kb = p.kh * p.kw * cblocks;
+
+  // consecutive tiles share the pixel box (the A operand) and differ in the output-channel block
+  auto tile_coords = [&](int t, int& n0, int& h0, int& w0, int& c0) {
+    const int cb = t % tiles_c;
+    int r = t / tiles_c;
+    const int tw = r % tiles_w; r /= tiles_w;
+    const int th = r % tiles_h; r /= tiles_h;
+    n0 = r * p.TN; h0 = th * p.TH; w0 = tw * p.TW; c0 = cb * BN;
+  };
+
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    for (int i = 0; i < C::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], kEpiWarps); }
+    mbar_fence_init();
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_y);
+  }
+  if (warp == 1) { tmem_alloc<C::kTmemCols>(tmem_slot); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int n0, h0, w0, c0;
+        tile_coords(t, n0, h0, w0, c0);
+        int kb = 0;
+        for (int r = 0; r < p.kh && !*dead; ++r) {
+          for (int sx = 0; sx < p.kw; ++sx) {
+            for (int cb = 0; cb < cblocks; ++cb, ++kb) {
+              if (!mbar_wait(&empty_bar[s], ph ^ 1, dead, p.status, 900)) break;
+              uint8_t* sa = stage_base + s * C::kStage;
+              mbar_expect_tx(&full_bar[s], C::kStage);
+              // the tile's pixel box of the input, shifted by the tap; padding comes back as zeros
+              tma_load_4d(sa, &map_x, &full_bar[s], cb * BK, w0 + sx - p.pw, h0 + r - p.ph, n0);
+              tma_load_2d(sa + C::kStageA, &map_w, &full_bar[s], (r * p.kw + sx) * p.Cin + cb * BK, c0);
+              if (++s == C::kStages) { s = 0; ph ^= 1; }
+            }
+          }
+        }
+        if (*dead) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, 0, 0);
+      int s = 0, it = 0;
+      uint32_t ph = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        if (!mbar_wait(&tempty_bar[acc], ((it >> 1) & 1) ^ 1, dead, p.status, 910)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, dead, p.status, 911)) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * C::kStage);
+          const uint32_t sb = sa + C::kStageA;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16_ss(d_tmem, umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024),
+                        umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+        umma_commit(&tfull_bar[acc]);
+        if (*dead) break;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;
+    const int ew = warp - 2;
+    uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
+    // pixel offset of this warp's 32 rows inside the tile box
+    const int idx0 = q * 32;
+    const int w_off = idx0 % p.TW, h_off = (idx0 / p.TW) % p.TH, n_off = idx0 / (p.TW * p.TH);
+    int buf = 0, it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int n0, h0, w0, c0;
+      tile_coords(t, n0, h0, w0, c0);
+      const int acc = it & 1;
+      bool ok = mbar_wait(&tfull_bar[acc], (it >> 1) & 1, dead, p.status, 920);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 64; ++ch) {
+        uint32_t r[64];
+        {
+          uint32_t(&r0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[0]);
+          uint32_t(&r1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r[32]);
+          tmem_ld_32x32b_x32(t_row + ch * 64, r0);
+          tmem_ld_32x32b_x32(t_row + ch * 64 + 32, r1);
+          tc_wait_ld();
+        }
+        if (ch == BN / 64 - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        const int co0 = c0 + ch * 64;
+        if (co0 >= p.Cout) continue;
+        if (p.bias_kind != 0) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const int n = co0 + j;
+            float b = 0.f;
+            if (n < p.Cout)
+              b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n) : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
+            r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
+          }
+        }
+        uint8_t* dst = stg + buf * kStageBufBytes;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 o;
+          o.x = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 0]), p.act), apply_act(__uint_as_float(r[c * 8 + 1]), p.act));
+          o.y = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 2]), p.act), apply_act(__uint_as_float(r[c * 8 + 3]), p.act));
+          o.z = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 4]), p.act), apply_act(__uint_as_float(r[c * 8 + 5]), p.act));
+          o.w = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 6]), p.act), apply_act(__uint_as_float(r[c * 8 + 7]), p.act));
+          *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        // a warp box that starts outside the output (ragged tile) is skipped: TMA stores must not
+        // start at an out-of-range coordinate; boxes that start inside are clipped by the unit
+        if (lane == 0 && w0 + w_off < p.Wo && h0 + h_off < p.Ho && n0 + n_off < p.N) {
+          tma_store_4d(&map_y, dst, co0, w0 + w_off, h0 + h_off, n0 + n_off);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc<C::kTmemCols>(tmem_base);
+}
+
+template <int BN>
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const ConvParams& p, int max_ctas,
+           cudaStream_t stream) {
+  using C = Cfg<BN>;
+  auto kern = conv_fprop_kernel<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const long tiles = (long)((p.Wo + p.TW - 1) / p.TW) * ((p.Ho + p.TH - 1) / p.TH) * ((p.N + p.TN - 1) / p.TN) *
+                     ((p.Cout + BN - 1) / BN);
+  int grid = tiles < max_ctas ? (int)tiles : max_ctas;
+  if (grid < 1) grid = 1;
+  kern<<<grid, kThreads, C::kSmem, stream>>>(mx, mw, my, p);
+  return (int)cudaGetLastError();
+}
+
+int pow2_floor(int v) { int r = 1; while (r * 2 <= v) r *= 2; return r; }
+
+}  // namespace
+
+// x [N, H, W, Cin] bf16 (NHWC), w [Cout, kh, kw, Cin] bf16, y [N, Ho, Wo, Cout] bf16 with
+// Ho = H + 2*ph - kh + 1, Wo = W + 2*pw - kw + 1 (stride 1).  Cin and Cout multiples of 64.
+// Returns a cudaError_t value, -1 for an unsupported argument.
+AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bias, int bias_kind, int act, int N,
+                           int H, int W, int Cin, int Cout, int kh, int kw, int ph, int pw, int max_ctas,
+                           int* status, cudaStream_t stream) {
+  const int Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
+  if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
+  if (Cin % 64 || Cout % 64 || kh < 1 || kw < 1) return -1;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return -1;
+  int sms = axh::sm_count();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+
+  // pixel box of a tile: the TW x TH x TN split of 128 that wastes the fewest rows on ragged edges
+  int TW = 1, TH = 1, TN = 128;
+  double best = -1.0;
+  for (int tw = 1; tw <= 128; tw *= 2)
+    for (int th = 1; tw * th <= 128; th *= 2) {
+      const int tn = 128 / (tw * th);
+      const double eff = (double)Wo / (((Wo + tw - 1) / tw) * tw) * ((double)Ho / (((Ho + th - 1) / th) * th)) *
+                         ((double)N / (((N + tn - 1) / tn) * tn));
+      if (eff > best + 1e-9 || (eff > best - 1e-9 && tw > TW)) { best = eff; TW = tw; TH = th; TN = tn; }
+    }
+  ConvParams p;
+  p.N = N; p.H = H; p.W = W; p.Cin = Cin; p.Cout = Cout; p.Ho = Ho; p.Wo = Wo;
+  p.kh = kh; p.kw = kw; p.ph = ph; p.pw = pw;
+  p.TN = TN; p.TH = TH; p.TW = TW;
+  // the 32 pixels of one epilogue warp, in (n, h, w) order with w fastest
+  if (TW >= 32) { p.bw = 32; p.bh = 1; p.bn = 1; }
+  else if (TW * TH >= 32) { p.bw = TW; p.bh = 32 / TW; p.bn = 1; }
+  else { p.bw = TW; p.bh = TH; p.bn = 32 / (TW * TH); }
+  p.bias = bias; p.bias_kind = bias ? bias_kind : 0; p.act = act; p.status = status;
+
+  int BN = Cout % 256 == 0 ? 256 : (Cout % 128 == 0 ? 128 : 64);
+  // small problems: prefer more tiles over wide tiles
+  {
+    const long pix_tiles = (long)((Wo + TW - 1) / TW) * ((Ho + TH - 1) / TH) * ((N + TN - 1) / TN);
+    while (BN > 64 && pix_tiles * (Cout / BN) < max_ctas) BN /= 2;
+  }
+  (void)pow2_floor;
+
+  CUtensorMap mx, mw, my;
+  {
+    uint64_t dims[4] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)N};
+    uint64_t strides[3] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2};
+    uint32_t box[4] = {64, (uint32_t)TW, (uint32_t)TH, (uint32_t)TN};
+    int rc = axh::encode_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 1000 + rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)kh * kw * Cin, (uint64_t)Cout};
+    uint64_t strides[1] = {(uint64_t)kh * kw * Cin * 2};
+    uint32_t box[2] = {64, (uint32_t)BN};
+    int rc = axh::encode_tensor_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 2000 + rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)Cout, (uint64_t)Wo, (uint64_t)Ho, (uint64_t)N};
+    uint64_t strides[3] = {(uint64_t)Cout * 2, (uint64_t)Wo * Cout * 2, (uint64_t)Ho * Wo * Cout * 2};
+    uint32_t box[4] = {64, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
+    int rc = axh::encode_tensor_map(&my, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, y, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 3000 + rc;
+  }
+  switch (BN) {
+    case 256: return launch<256>(mx, mw, my, p, max_ctas, stream);
+    case 128: return launch<128>(mx, mw, my, p, max_ctas, stream);
+    default: return launch<64>(mx, mw, my, p, max_ctas, stream);
+  }
+}

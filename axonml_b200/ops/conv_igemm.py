@@ -1,16 +1,93 @@
-"""Implicit-GEMM convolution on the tcgen05 GEMM: NHWC bf16 activations are gathered into the
-[N*Ho*Wo, kh*kw*Cin] operand by a hand-written im2col kernel (1x1 stride-1 convolutions need no
-gather) and multiplied with the [Cout, kh*kw*Cin] filter matrix; dgrad and wgrad reuse the GEMM's
-MN-major operand modes.
+"""Implicit-GEMM convolution on tcgen05 (``csrc/kernels/conv_igemm.cu``).
+
+Forward and data gradient of stride-1 convolutions run without an im2col matrix: the kernel's TMA
+producer loads, per filter tap, the tile's box of NHWC input pixels shifted by the tap (zero
+padding is the TMA out-of-range fill).  The data gradient is the same kernel applied to the output
+gradient with the filter rotated by 180 degrees and its channel dims exchanged.  The weight
+gradient currently goes through the framework's convolution-backward fallback.
+
+Layout contract: activations are bf16 in channels-last memory format (NCHW shape, NHWC storage),
+weights ``[cout, cin, kh, kw]`` in any float dtype (converted to ``[cout, kh, kw, cin]`` bf16).
 
 Parity: Conv2d forward crates/axonml-nn/src/layers/conv.rs:256-337 and the WGSL direct-conv
-shader (wgpu_backend.rs:1364-1427)."""
+shader (wgpu_backend.rs:1364-1427); the reference has no convolution backward."""
 from __future__ import annotations
 
 import torch
 
 from .. import _native as N
+from .gemm import ACT
 
 
-def supported(x, weight, stride, padding) -> bool:
-    return False
+def supported(x, weight, stride, padding, dilation=(1, 1), groups: int = 1) -> bool:
+    if not (N.is_blackwell() and x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16):
+        return False
+    if tuple(stride) != (1, 1) or tuple(dilation) != (1, 1) or groups != 1:
+        return False
+    cout, cin, kh, kw = weight.shape
+    if cin % 64 or cout % 64:
+        return False
+    if not x.is_contiguous(memory_format=torch.channels_last):
+        return False
+    n, _, h, w = x.shape
+    ho, wo = h + 2 * padding[0] - kh + 1, w + 2 * padding[1] - kw + 1
+    return ho > 0 and wo > 0 and n * ho * wo >= 128
+
+
+def _ohwi(weight: torch.Tensor) -> torch.Tensor:
+    """[cout, cin, kh, kw] -> contiguous [cout, kh, kw, cin] bf16."""
+    return weight.detach().permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()
+
+
+def fprop(x, w_ohwi, bias, padding, act: str = "none"):
+    """x: NCHW-shaped channels-last bf16; w_ohwi: [cout, kh, kw, cin] bf16.  Returns the
+    channels-last result."""
+    n, cin, h, w = x.shape
+    cout, kh, kw, _ = w_ohwi.shape
+    ho, wo = h + 2 * padding[0] - kh + 1, w + 2 * padding[1] - kw + 1
+    y = torch.empty((n, cout, ho, wo), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+    bias_kind = 0
+    if bias is not None:
+        bias = bias.detach().contiguous()
+        bias_kind = 1 if bias.dtype == torch.float32 else 2
+        if bias.dtype not in (torch.float32, torch.bfloat16):
+            bias, bias_kind = bias.float(), 1
+    rc = N.cuda().ax_conv2d_fprop(N.ptr(x), N.ptr(w_ohwi), N.ptr(y), N.ptr(bias), bias_kind, ACT[act], n, h, w, cin,
+                                  cout, kh, kw, padding[0], padding[1], 0, N.ptr(N.status_word(x.device)),
+                                  N.stream_ptr())
+    N.check(rc, "ax_conv2d_fprop")
+    return y
+
+
+class _ConvFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, padding):
+        ctx.padding = tuple(padding)
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return fprop(x, _ohwi(weight), bias, padding)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        ph, pw = ctx.padding
+        cout, cin, kh, kw = weight.shape
+        if not dy.is_contiguous(memory_format=torch.channels_last):
+            dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            # rotate the filter by 180 degrees and swap its channel roles: [cin, kh, kw, cout]
+            w_t = weight.detach().flip(2, 3).permute(1, 2, 3, 0).to(torch.bfloat16).contiguous()
+            dx = fprop(dy, w_t, None, (kh - 1 - ph, kw - 1 - pw))
+        if ctx.needs_input_grad[1]:
+            _, dw, _ = torch.ops.aten.convolution_backward(
+                dy, x, weight.to(dy.dtype), None, [1, 1], [ph, pw], [1, 1], False, [0, 0], 1, [False, True, False])
+            dw = dw.to(weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy.float().sum(dim=(0, 2, 3)).to(ctx.bias_dtype)
+        return dx, dw, db, None
+
+
+def conv2d(x, weight, bias, stride, padding):
+    return _ConvFn.apply(x, weight, bias, tuple(padding))
