@@ -30,7 +30,13 @@ class Normalize(Transform):
     def new(cls, mean, std): return cls(mean, std)
     @classmethod
     def standard(cls): return cls(0.0, 1.0)
-    def apply(self, x): return (x - self.mean) / self.std
+    def apply(self, x):
+        m, s = self.mean, self.std
+        if isinstance(m, (list, tuple)):        # per-channel statistics: broadcast over [C, H, W]
+            shape = [-1] + [1] * max(x.dim() - 1, 0) if len(m) > 1 else [1]
+            m = torch.tensor(m, dtype=x.dtype, device=x.device).view(shape)
+            s = torch.tensor(s, dtype=x.dtype, device=x.device).view(shape)
+        return (x - m) / s
 
 
 class RandomNoise(Transform):

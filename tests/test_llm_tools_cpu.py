@@ -1,0 +1,230 @@
+"""LLM families (GPT-2, LLaMA, BERT, Mistral, Phi) on tiny configurations, KV-cache generation,
+JIT tracing / optimisation / interpretation, fusion, profiler, text and audio utilities, hub, the
+serving stack on the CPU (paged KV cache, continuous batching, HTTP endpoints) and the trainer."""
+import json
+import threading
+import urllib.request
+
+import pytest
+import torch
+
+from axonml_b200 import audio, fusion, hub, jit, llm, nn, optim, profile, server, text, trainer, vision
+from axonml_b200.quant import QuantType
+
+
+def test_gpt2_and_llama_tiny_train_step_reduces_loss():
+    torch.manual_seed(0)
+    for model in (llm.GPT2LMHead(llm.GPT2Config.tiny()), llm.LLaMAForCausalLM(llm.LLaMAConfig.tiny())):
+        ids = torch.randint(0, 100, (2, 16))
+        opt = optim.AdamW(list(model.parameters()), 3e-3)
+        first = None
+        for _ in range(8):
+            opt.zero_grad()
+            loss, logits = model.forward_with_loss(ids)
+            loss.backward()
+            opt.step()
+            first = first if first is not None else float(loss)
+        assert logits.shape[:2] == (2, 16)
+        assert float(loss) < first
+
+
+def test_llama_kv_cache_generation_matches_full_forward():
+    torch.manual_seed(0)
+    model = llm.LLaMAForCausalLM(llm.LLaMAConfig.tiny()).eval()
+    ids = torch.randint(0, 100, (1, 6))
+    out = model.generate(ids, max_new_tokens=5)
+    out = out if torch.is_tensor(out) else torch.tensor(out)
+    assert out.shape[-1] == 11
+    # greedy continuation token by token without a cache
+    cur = ids.clone()
+    with torch.no_grad():
+        for _ in range(5):
+            nxt = model(cur)[:, -1].argmax(-1, keepdim=True)
+            cur = torch.cat([cur, nxt], 1)
+    assert torch.equal(out.view(-1), cur.view(-1))
+
+
+def test_bert_mistral_phi_forward_shapes():
+    torch.manual_seed(0)
+    b = llm.BertForSequenceClassification(llm.BertConfig.tiny(), 3).eval()
+    ids = torch.randint(0, 100, (2, 10))
+    out = b(ids)
+    out = out[0] if isinstance(out, tuple) else out
+    assert out.shape == (2, 3)
+    for cls, cfg in ((llm.MistralForCausalLM, llm.MistralConfig.tiny() if hasattr(llm.MistralConfig, "tiny") else None),
+                     (llm.PhiForCausalLM, llm.PhiConfig.tiny())):
+        if cfg is None:
+            continue
+        m = cls(cfg).eval()
+        y = m(torch.randint(0, 100, (1, 8)))
+        y = y[0] if isinstance(y, tuple) else y
+        assert y.shape[:2] == (1, 8)
+
+
+def test_hf_weight_mapping_names():
+    sd = {"wte.weight": torch.zeros(2, 2), "h.0.attn.c_attn.weight": torch.zeros(2, 6)}
+    mapped = llm.map_gpt2_weights(sd)
+    assert len(mapped) == 2
+
+
+def test_jit_trace_optimize_interpret_and_codegen():
+    def f(tr):
+        a, b = tr.input("a", [4]), tr.input("b", [4])
+        y = a.add(b).mul_scalar(2.0).relu()
+        return tr.output("y", y)
+    g = jit.trace(f)
+    assert len(g.input_names()) == 2 and not g.is_empty()
+    a, b = torch.tensor([1.0, -2.0, 3.0, 0.5]), torch.tensor([1.0, 1.0, -5.0, 0.5])
+    out = jit.interpret(g, {"a": a, "b": b})
+    assert torch.allclose(out["y"], ((a + b) * 2).relu())
+    cm = jit.compile_graph(g)
+    got = cm.run_tensors({"a": a, "b": b})
+    assert torch.allclose(got["y"], ((a + b) * 2).relu())
+    src = jit.generate_cuda(g)
+    src = src if isinstance(src, str) else src[0]
+    assert "__global__" in src
+
+
+def test_fusion_linear_and_elementwise_and_conv_bn_fold():
+    torch.manual_seed(0)
+    w, b = torch.randn(3, 4), torch.randn(3)
+    fl = fusion.fuse_linear(w, b, fusion.Activation.ReLU if hasattr(fusion.Activation, "ReLU") else list(fusion.Activation)[1])
+    x = torch.randn(2, 4)
+    assert fl.execute(x).shape == (2, 3)
+    fe = fusion.FusedElementwiseBuilder().mul(2.0).add(1.0).relu().build()
+    assert torch.allclose(fe.execute(torch.tensor([-3.0, 1.0])), torch.tensor([0.0, 3.0]))
+    assert fe.num_ops() == 3
+    conv, bn = nn.Conv2d(2, 3, 3, padding=1), nn.BatchNorm2d(3)
+    bn.eval()
+    with torch.no_grad():
+        bn.running_mean.uniform_(-1, 1); bn.running_var.uniform_(0.5, 2.0)
+        bn.weight.uniform_(0.5, 1.5); bn.bias.uniform_(-1, 1)
+    fw, fb = fusion.fold_conv_bn(conv, bn)         # folded (weight, bias)
+    xx = torch.randn(1, 2, 5, 5)
+    assert torch.allclose(torch.nn.functional.conv2d(xx, fw, fb, 1, 1), bn(conv(xx)), atol=1e-5)
+
+
+def test_profiler_report_and_chrome_trace(tmp_path):
+    p = profile.Profiler()
+    p.enable()
+    with p.scope("matmul"):
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    with p.scope("matmul"):
+        torch.randn(64, 64) @ torch.randn(64, 64)
+    rep = p.report()
+    ops = {(o["name"] if isinstance(o, dict) else o.name): o for o in rep.operations}
+    assert "matmul" in ops
+    assert "matmul" in rep.to_markdown() and "matmul" in rep.to_json()
+    tl = profile.TimelineProfiler()
+    tl.begin("step"); tl.end("step")
+    out = tmp_path / "trace.json"
+    tl.export_chrome_trace(str(out))
+    ev = json.load(open(out))
+    ev = ev["traceEvents"] if isinstance(ev, dict) else ev
+    assert any(e.get("name") == "step" for e in ev)
+
+
+def test_text_and_audio_utilities():
+    tok = text.BasicBPETokenizer()
+    tok.train("low lower lowest low low", 20) if "num_merges" not in str(tok.train.__code__.co_varnames) else tok.train("low lower lowest", 20)
+    assert len(tok.tokenize("lower")) >= 1
+    v = text.Vocab.from_text("the cat sat on the mat")
+    ids = v.encode(["the", "cat"]) if not isinstance(v.encode("the cat"), list) or len(v.encode("the cat")) != 2 else v.encode("the cat")
+    dec = v.decode(ids)
+    assert (dec.split() if isinstance(dec, str) else list(dec)) == ["the", "cat"]
+    assert text.CharTokenizer().tokenize("ab c") == ["a", "b", " ", "c"]
+    ds = text.LanguageModelDataset(list(range(50)), 8)
+    x, y = ds.get(0)
+    assert torch.equal(x[1:], y[:-1])
+    wave = torch.sin(torch.linspace(0, 200.0, 16000))
+    mel = audio.MelSpectrogram(16000, 400, 160, 40).apply(wave)
+    assert mel.shape[0] == 40 or mel.shape[-2] == 40 or mel.shape[-1] == 40
+    assert audio.MFCC(16000, 13, 40).apply(wave).numel() > 0
+    assert abs(audio.Resample(16000, 8000).apply(wave).numel() - 8000) <= 2
+    a, lab = audio.SyntheticCommandDataset(4).get(0)
+    assert a.numel() == 16000
+
+
+def test_hub_registry():
+    names = [m.name for m in hub.list_all_models()]
+    assert "resnet18" in names
+    info = hub.get_model_info("resnet18")
+    assert 11_000_000 < info.num_parameters < 12_500_000
+    assert any("gpt" in m.name.lower() for m in hub.search_models("gpt"))
+
+
+def test_vision_models_forward():
+    assert vision.LeNet.new()(torch.randn(2, 1, 28, 28)).shape == (2, 10)
+    r = vision.ResNet.resnet18(10).eval()
+    assert r(torch.randn(1, 3, 64, 64)).shape == (1, 10)
+    assert sum(p.numel() for p in vision.ResNet.resnet18(1000).parameters()) == 11_689_512
+
+
+def test_paged_kv_cache_bookkeeping():
+    c = server.PagedKVCache(2, 8, 4, 1, 8, 4, 4, "cpu", torch.float32)
+    s0, s1 = c.allocate_seq(), c.allocate_seq()
+    c.reserve(s0, 9)                      # 3 pages
+    c.reserve(s1, 4)                      # 1 page
+    assert c.pages_free() == 4 and abs(c.occupancy() - 0.5) < 1e-9
+    assert not c.can_admit(17) and c.can_admit(16)
+    with pytest.raises(server.OutOfPages):
+        c.reserve(s1, 4 * 6)
+    c.free_seq(s0)
+    assert c.pages_free() == 7
+
+
+def test_engine_continuous_batching_matches_sequential_decode_cpu():
+    torch.manual_seed(0)
+    cfg = llm.LLaMAConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                          num_attention_heads=2, num_key_value_heads=1, max_position_embeddings=128)
+    model = server.QuantizedLlama.from_random(cfg, None, device="cpu", std=0.2, proj_type=QuantType.Q8_0)
+    prompts = [[1, 2, 3, 4], [9, 8, 7, 6], [5, 5, 5, 5]]
+    together = server.LLMEngine(model, max_batch=4, max_context=32, page_size=4).generate(prompts, 5)
+    alone = [server.LLMEngine(model, max_batch=4, max_context=32, page_size=4).generate([p], 5)[0] for p in prompts]
+    assert together == alone
+    st = server.LLMEngine(model, max_batch=4, max_context=32, page_size=4)
+    st.generate(prompts, 3)
+    s = st.stats()
+    assert s["requests"] == 3 and s["kv_page_occupancy"] == 0.0 and s["ttft_p50_s"] is not None
+
+
+def test_http_server_endpoints():
+    from axonml_b200.serialize.state_dict import StateDict
+    torch.manual_seed(0)
+    m = nn.Sequential().add(nn.Linear(4, 8)).add(nn.ReLU()).add(nn.Linear(8, 2))
+    inf = server.InferenceServer()
+    inf.register("mlp", server.build_model_from_state_dict(StateDict.from_module(m)))
+    srv = server.AxonmlHTTPServer("127.0.0.1", 0, inf).start()
+    try:
+        port = srv.port if hasattr(srv, "port") else srv.httpd.server_address[1]
+        base = f"http://127.0.0.1:{port}"
+        assert json.load(urllib.request.urlopen(base + "/health"))["status"] == "healthy"
+        req = urllib.request.Request(base + "/batch", method="POST", headers={"Content-Type": "application/json"},
+                                     data=json.dumps({"model": "mlp", "inputs": [[1.0, 2.0, 3.0, 4.0]]}).encode())
+        body = json.load(urllib.request.urlopen(req))
+        got = torch.tensor(body["outputs"])
+        req = urllib.request.Request(base + "/api/inference/predict/mlp", method="POST",
+                                     data=json.dumps({"input": [1.0, 2.0, 3.0, 4.0]}).encode())
+        one = json.load(urllib.request.urlopen(req))
+        assert torch.allclose(torch.tensor(one["output"]).view(-1), got.view(-1), atol=1e-6) and one["latency_ms"] >= 0
+        assert torch.allclose(got.view(-1), m(torch.tensor([[1.0, 2.0, 3.0, 4.0]])).view(-1), atol=1e-5)
+        prom = urllib.request.urlopen(base + "/metrics").read().decode()
+        assert "axonml" in prom
+    finally:
+        srv.stop()
+
+
+def test_trainer_fit_with_early_stopping():
+    torch.manual_seed(0)
+    from axonml_b200 import data
+    X = torch.randn(128, 4)
+    Y = (X.sum(-1) > 0).long()
+    loader = data.DataLoader(data.TensorDataset(X, Y), 32)
+    model = nn.Sequential().add(nn.Linear(4, 16)).add(nn.ReLU()).add(nn.Linear(16, 2))
+    cfg = trainer.TrainingConfig.new().epochs(15).learning_rate(0.01)
+    t = trainer.Trainer(model, optim.Adam(list(model.parameters()), 0.01), nn.CrossEntropyLoss(), cfg,
+                        callbacks=[trainer.EarlyStopping(3)])
+    hist = t.fit(loader, loader)
+    metrics = t.evaluate(loader)
+    acc = metrics.accuracy if hasattr(metrics, "accuracy") else metrics["accuracy"]
+    assert acc > 0.85
