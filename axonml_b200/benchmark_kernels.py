@@ -1,0 +1,156 @@
+"""Stand-alone timing of the hand-written kernels on one GPU, with the achieved fraction of the
+measured roofline (copy bandwidth / cuBLAS bf16 throughput from ``MEASURED_PEAKS.json`` when that
+file is present in the working directory, else the stated fallback figures).
+
+    python -m axonml_b200.benchmark_kernels gemm flash_fwd rmsnorm      # chosen workloads
+    python -m axonml_b200.benchmark_kernels all --iters 20
+    python -m axonml_b200.benchmark_kernels gemm --small                # a few launches on a small case
+                                                                        # (what a profiler capture uses)
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, operands rotated through more
+memory than the 126 MB L2 between launches.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _peaks():
+    hbm, tflops, src = 6650.0, 1590.0, "fallback"
+    p = os.path.join(os.getcwd(), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            hbm, tflops, src = float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return hbm, tflops, src
+
+
+def _time(fn, iters):
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3          # us
+
+
+def w_gemm(small):
+    from .ops.gemm import gemm_bf16
+    n = 2048 if small else 8192
+    nb = 2 if small else 3
+    a = [torch.randn(n, n, device="cuda").bfloat16() for _ in range(nb)]
+    b = [torch.randn(n, n, device="cuda").bfloat16() for _ in range(nb)]
+    return (lambda i: gemm_bf16(a[i % nb], b[i % nb])), 2.0 * n ** 3, 3 * n * n * 2, f"bf16 GEMM {n}^3"
+
+
+def w_flash_fwd(small, bwd=False):
+    from .ops import flash
+    B, H, S, D = (2, 8, 1024, 128) if small else (4, 16, 2048, 128)
+    nb = 2 if small else 4
+    qs = [[torch.randn(B, S, H, D, device="cuda").bfloat16().requires_grad_(bwd) for _ in range(3)] for _ in range(nb)]
+    flops = 4.0 * B * H * S * S * D / 2 * (3.5 if bwd else 1.0)
+    if not bwd:
+        return (lambda i: flash.flash_attention(*qs[i % nb], causal=True)), flops, 4 * B * S * H * D * 2, f"flash fwd B{B} H{H} S{S} D{D} causal"
+    g = torch.randn(B, S, H, D, device="cuda").bfloat16()
+
+    def run(i):
+        q, k, v = qs[i % nb]
+        q.grad = k.grad = v.grad = None
+        flash.flash_attention(q, k, v, causal=True).backward(g)
+    return run, flops, 8 * B * S * H * D * 2, f"flash fwd+bwd B{B} H{H} S{S} D{D} causal"
+
+
+def w_rmsnorm(small):
+    from .ops import norm
+    rows, D = (8192, 4096) if small else (65536, 4096)
+    nb = 2 if small else 3
+    xs = [torch.randn(rows, D, device="cuda").bfloat16() for _ in range(nb)]
+    w = torch.ones(D, device="cuda").bfloat16()
+    return (lambda i: norm.rms_norm(xs[i % nb], w, 1e-5)), 0.0, 2 * rows * D * 2, f"RMSNorm fwd [{rows}, {D}] bf16"
+
+
+def w_adamw(small):
+    from .ops import optim as O
+    n = (8 if small else 64) * 1024 * 1024
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda").bfloat16()
+    m, v, lp = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda").bfloat16()
+
+    def run(i):
+        O.multi_tensor("adam", [p], [g], [m], [v], None, lp=[lp], lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1,
+                       bc1=0.1, bc2=0.05, adamw=True, amsgrad=False, inv_scale=None, found_inf=None)
+    return run, 0.0, n * (4 + 2 + 4 + 4) + n * (4 + 4 + 4 + 2), f"fused AdamW step, {n >> 20} Mi parameters (fp32 master, bf16 grad + mirror)"
+
+
+def w_conv(small):
+    from .ops import conv_igemm as CI
+    n, c, h = (32, 128, 28) if small else (256, 128, 28)
+    x = torch.randn(n, c, h, h, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w = CI._ohwi(torch.randn(c, c, 3, 3, device="cuda") * 0.05)
+    return (lambda i: CI.fprop(x, w, None, (1, 1))), 2.0 * n * h * h * c * c * 9, 2 * n * h * h * c * 2, f"conv3x3 s1 fprop N{n} C{c} {h}x{h} NHWC bf16"
+
+
+def w_qgemm(small):
+    from .ops.quant import qgemm, tile_weight
+    from .quant.quantize import quantize_tensor
+    from .quant.types import QuantType
+    Nn, K = (4096, 4096) if small else (28672, 4096)
+    nb = 2 if small else 4
+    ws = [tile_weight(quantize_tensor(torch.randn(Nn, K, device="cuda") * 0.02, QuantType.Q4_K)) for _ in range(nb)]
+    x = torch.randn(1, K, device="cuda").bfloat16()
+    return (lambda i: qgemm(x, ws[i % nb])), 0.0, Nn * K * 0.5625, f"Q4_K dequantising matmul batch 1, [{Nn}, {K}]"
+
+
+def w_paged(small):
+    from .ops import paged
+    B, ctx, Hq, Hkv, D, page = (8, 512, 32, 8, 128, 16) if small else (64, 768, 32, 8, 128, 16)
+    pages = B * (ctx // page)
+    kc = torch.randn(pages, page, Hkv, D, device="cuda").bfloat16()
+    vc = torch.randn(pages, page, Hkv, D, device="cuda").bfloat16()
+    table = torch.arange(pages, device="cuda", dtype=torch.int32).view(B, -1)
+    lens = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    return (lambda i: paged.decode_attention(q, kc, vc, table, lens, page)), 0.0, 2 * B * ctx * Hkv * D * 2, f"paged decode attention B{B} ctx{ctx} GQA {Hq}/{Hkv}"
+
+
+WORKLOADS = {"gemm": w_gemm, "flash_fwd": w_flash_fwd, "flash_bwd": lambda s: w_flash_fwd(s, True), "rmsnorm": w_rmsnorm,
+             "adamw": w_adamw, "conv": w_conv, "qgemm": w_qgemm, "paged_decode": w_paged}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("names", nargs="+")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--small", action="store_true", help="small case, three launches (for a profiler capture)")
+    a = ap.parse_args()
+    from . import _native
+    names = list(WORKLOADS) if a.names == ["all"] else a.names
+    hbm, tflops, src = _peaks()
+    print(f"roofline denominators ({src}): {hbm:.0f} GB/s copy, {tflops:.0f} TFLOP/s bf16")
+    for n in names:
+        fn, flops, nbytes, desc = WORKLOADS[n](a.small)
+        if a.small:
+            for i in range(3):
+                fn(i)
+            torch.cuda.synchronize()
+            print(f"{n}: {desc}: 3 launches done")
+            continue
+        us = _time(fn, a.iters)
+        _native.check_status()
+        roof = max(flops / (tflops * 1e12), nbytes / (hbm * 1e9)) * 1e6
+        kind = "compute" if flops / (tflops * 1e12) > nbytes / (hbm * 1e9) else "memory"
+        rate = f"{flops / us / 1e6:.0f} TFLOP/s" if kind == "compute" else f"{nbytes / us / 1e3:.0f} GB/s"
+        print(f"{n}: {desc}: {us:.1f} us, {rate}, {roof / us:.2f} of {src} {kind} roofline")
+
+
+if __name__ == "__main__":
+    main()
