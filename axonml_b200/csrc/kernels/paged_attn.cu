@@ -81,15 +81,27 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int i = 0; i < kEl; ++i) acc[g][i] = 0.f;
   }
   const long row = (long)Hkv * D;
-  for (int t0 = t_begin; t0 < t_end; t0 += kTokPerIter) {
+  // The K/V rows of the next 32 tokens are requested before the current ones are used, so that
+  // two iterations of loads are in flight per thread.
+  uint4 nk0, nk1, nv0, nv1;
+  bool nvalid = false;
+  auto issue = [&](int t0) {
     const int t = t0 + slot;
-    const bool valid = t < t_end;
-    float kf[kEl], vf[kEl];
-    if (valid) {
+    nvalid = t < t_end;
+    if (nvalid) {
       const int page = block_table[b * max_pages + t / page_size];
       const long off = ((long)page * page_size + t % page_size) * row + (long)hk * D + sub * kEl;
-      const uint4 k0 = *reinterpret_cast<const uint4*>(kc + off), k1 = *reinterpret_cast<const uint4*>(kc + off + 8);
-      const uint4 v0 = *reinterpret_cast<const uint4*>(vc + off), v1 = *reinterpret_cast<const uint4*>(vc + off + 8);
+      nk0 = *reinterpret_cast<const uint4*>(kc + off); nk1 = *reinterpret_cast<const uint4*>(kc + off + 8);
+      nv0 = *reinterpret_cast<const uint4*>(vc + off); nv1 = *reinterpret_cast<const uint4*>(vc + off + 8);
+    }
+  };
+  if (t_begin < t_end) issue(t_begin);
+  for (int t0 = t_begin; t0 < t_end; t0 += kTokPerIter) {
+    const bool valid = nvalid;
+    const uint4 k0 = nk0, k1 = nk1, v0 = nv0, v1 = nv1;
+    if (t0 + kTokPerIter < t_end) issue(t0 + kTokPerIter);
+    float kf[kEl], vf[kEl];
+    if (valid) {
       unpack8(k0, kf); unpack8(k1, kf + 8);
       unpack8(v0, vf); unpack8(v1, vf + 8);
     }
