@@ -258,6 +258,180 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, 
   return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ weight gradient
+//   dw[co, r, s, ci] = sum_{n, ho, wo} dy[n, ho, wo, co] * x[n, ho + r - ph, wo + s - pw, ci]
+// as a GEMM whose reduction dimension is the pixels: for one filter tap, M = 128 output channels,
+// N = BNC input channels, K = boxes of 64 pixels.  Both operands are "MN-major" (the channel is the
+// contiguous dimension in memory): the A slabs are 4-D TMA boxes of dy, the B slabs the same pixel
+// box of x shifted by the tap (zero fill = padding).  The pixel range is split over CTAs; partial
+// sums are added to an fp32 buffer with global reductions.
+constexpr int WBK = 64;          // pixels per k block
+
+struct WgradParams {
+  int N, H, W, Cin, Cout, Ho, Wo;
+  int kh, kw, ph, pw;
+  int TN, TH, TW;          // pixel box of a k block, TN*TH*TW == 64
+  int splits;              // pixel-range splits per (tap, co block, ci block)
+  float* dw;               // [Cout, kh, kw, Cin] fp32, zero-initialised by the caller
+  int* status;
+};
+
+template <int BNC>
+struct WCfg {
+  static constexpr int kStageA = 2 * WBK * 128;             // two 64-channel slabs of dy
+  static constexpr int kStageB = (BNC / 64) * WBK * 128;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = BNC == 128 ? 6 : 8;
+  static constexpr int kSmem = 1024 + kStages * kStage + 256;
+};
+
+template <int BNC>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x,
+                  const WgradParams p) {
+  using C = WCfg<BNC>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint64_t* bars = (uint64_t*)(smem + C::kStages * C::kStage);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::kStages;
+  uint64_t* tfull_bar = bars + 2 * C::kStages;       // accumulator complete
+  uint64_t* tempty_bar = tfull_bar + 1;              // accumulator drained by the epilogue
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 1);
+  volatile int* dead = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_w = (p.Wo + p.TW - 1) / p.TW, tiles_h = (p.Ho + p.TH - 1) / p.TH, tiles_n = (p.N + p.TN - 1) / p.TN;
+  const int nboxes = tiles_w * tiles_h * tiles_n;
+  const int co_blocks = (p.Cout + 127) / 128, ci_blocks = p.Cin / BNC;
+  const int taps = p.kh * p.kw;
+  const int items = taps * co_blocks * ci_blocks * p.splits;
+  const int per_split = (nboxes + p.splits - 1) / p.splits;
+
+  auto item_coords = [&](int it, int& tap, int& cob, int& cib, int& b0, int& b1) {
+    const int sp = it % p.splits; it /= p.splits;
+    cib = it % ci_blocks; it /= ci_blocks;
+    cob = it % co_blocks; it /= co_blocks;
+    tap = it;
+    b0 = sp * per_split;
+    b1 = min(nboxes, b0 + per_split);
+  };
+
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    for (int i = 0; i < C::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, kEpiWarps);
+    mbar_fence_init();
+    prefetch_tensormap(&map_dy);
+    prefetch_tensormap(&map_x);
+  }
+  if (warp == 1) { tmem_alloc<BNC>(tmem_slot); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int it = blockIdx.x; it < items && !*dead; it += gridDim.x) {
+        int tap, cob, cib, b0, b1;
+        item_coords(it, tap, cob, cib, b0, b1);
+        const int r = tap / p.kw, sx = tap % p.kw;
+        for (int b = b0; b < b1; ++b) {
+          const int tw = b % tiles_w, th = (b / tiles_w) % tiles_h, tn = b / (tiles_w * tiles_h);
+          const int w0 = tw * p.TW, h0 = th * p.TH, n0 = tn * p.TN;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, dead, p.status, 930)) break;
+          uint8_t* sa = stage_base + s * C::kStage;
+          mbar_expect_tx(&full_bar[s], C::kStage);
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            tma_load_4d(sa + j * (WBK * 128), &map_dy, &full_bar[s], cob * 128 + j * 64, w0, h0, n0);
+#pragma unroll
+          for (int j = 0; j < BNC / 64; ++j)
+            tma_load_4d(sa + C::kStageA + j * (WBK * 128), &map_x, &full_bar[s], cib * BNC + j * 64, w0 + sx - p.pw,
+                        h0 + r - p.ph, n0);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(1, 128, BNC, 1, 1);
+      int s = 0, n_it = 0;
+      uint32_t ph = 0;
+      for (int it = blockIdx.x; it < items; it += gridDim.x, ++n_it) {
+        int tap, cob, cib, b0, b1;
+        item_coords(it, tap, cob, cib, b0, b1);
+        if (!mbar_wait(tempty_bar, (n_it & 1) ^ 1, dead, p.status, 940)) break;
+        tc_fence_after();
+        for (int b = b0; b < b1; ++b) {
+          if (!mbar_wait(&full_bar[s], ph, dead, p.status, 941)) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * C::kStage);
+          const uint32_t sb = sa + C::kStageA;
+#pragma unroll
+          for (int k = 0; k < WBK / UMMA_K; ++k)
+            umma_f16_ss(tmem_base, umma_desc_sw128(sa + k * (UMMA_K * 128), WBK * 128, 1024),
+                        umma_desc_sw128(sb + k * (UMMA_K * 128), WBK * 128, 1024), idesc, (b > b0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+          if (++s == C::kStages) { s = 0; ph ^= 1; }
+        }
+        umma_commit(tfull_bar);
+        if (*dead) break;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int n_it = 0;
+    const long row_stride = (long)p.kh * p.kw * p.Cin;
+    for (int it = blockIdx.x; it < items; it += gridDim.x, ++n_it) {
+      int tap, cob, cib, b0, b1;
+      item_coords(it, tap, cob, cib, b0, b1);
+      bool ok = mbar_wait(tfull_bar, n_it & 1, dead, p.status, 950);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int co = cob * 128 + q * 32 + lane;
+      float* drow = p.dw + (long)co * row_stride + (long)tap * p.Cin + cib * BNC;
+#pragma unroll 1
+      for (int ch = 0; ch < BNC / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32, v);
+        tc_wait_ld();
+        if (b1 > b0 && co < p.Cout) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) atomicAdd(drow + ch * 32 + j, __uint_as_float(v[j]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc<BNC>(tmem_base);
+}
+
+template <int BNC>
+int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const WgradParams& p, int grid, cudaStream_t stream) {
+  using C = WCfg<BNC>;
+  auto kern = conv_wgrad_kernel<BNC>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, kThreads, C::kSmem, stream>>>(mdy, mx, p);
+  return (int)cudaGetLastError();
+}
+
 int pow2_floor(int v) { int r = 1; while (r * 2 <= v) r *= 2; return r; }
 
 }  // namespace
@@ -333,4 +507,56 @@ AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bi
     case 128: return launch<128>(mx, mw, my, p, max_ctas, stream);
     default: return launch<64>(mx, mw, my, p, max_ctas, stream);
   }
+}
+
+// dy [N, Ho, Wo, Cout] bf16, x [N, H, W, Cin] bf16 (NHWC), dw [Cout, kh, kw, Cin] fp32 which must be
+// zero on entry (partial sums are added).  Stride 1; Cin and Cout multiples of 64.
+AX_API int ax_conv2d_wgrad(const void* dy, const void* x, float* dw, int N, int H, int W, int Cin, int Cout, int kh,
+                           int kw, int ph, int pw, int max_ctas, int* status, cudaStream_t stream) {
+  const int Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
+  if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
+  if (Cin % 64 || Cout % 64) return -1;
+  if (((uintptr_t)dy | (uintptr_t)x | (uintptr_t)dw) & 15) return -1;
+  int sms = axh::sm_count();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+  int TW = 1, TH = 1, TN = 64;
+  double best = -1.0;
+  for (int tw = 1; tw <= 64; tw *= 2)
+    for (int th = 1; tw * th <= 64; th *= 2) {
+      const int tn = 64 / (tw * th);
+      const double eff = (double)Wo / (((Wo + tw - 1) / tw) * tw) * ((double)Ho / (((Ho + th - 1) / th) * th)) *
+                         ((double)N / (((N + tn - 1) / tn) * tn));
+      if (eff > best + 1e-9 || (eff > best - 1e-9 && tw > TW)) { best = eff; TW = tw; TH = th; TN = tn; }
+    }
+  const int BNC = Cin % 128 == 0 ? 128 : 64;
+  WgradParams p;
+  p.N = N; p.H = H; p.W = W; p.Cin = Cin; p.Cout = Cout; p.Ho = Ho; p.Wo = Wo;
+  p.kh = kh; p.kw = kw; p.ph = ph; p.pw = pw; p.TN = TN; p.TH = TH; p.TW = TW;
+  p.dw = dw; p.status = status;
+  const int nboxes = ((Wo + TW - 1) / TW) * ((Ho + TH - 1) / TH) * ((N + TN - 1) / TN);
+  const int base_items = kh * kw * ((Cout + 127) / 128) * (Cin / BNC);
+  int splits = (2 * max_ctas + base_items - 1) / base_items;
+  if (splits > nboxes) splits = nboxes;
+  if (splits < 1) splits = 1;
+  p.splits = splits;
+  const long items = (long)base_items * splits;
+  const int grid = items < max_ctas ? (int)items : max_ctas;
+  CUtensorMap mdy, mx;
+  {
+    uint64_t dims[4] = {(uint64_t)Cout, (uint64_t)Wo, (uint64_t)Ho, (uint64_t)N};
+    uint64_t strides[3] = {(uint64_t)Cout * 2, (uint64_t)Wo * Cout * 2, (uint64_t)Ho * Wo * Cout * 2};
+    uint32_t box[4] = {64, (uint32_t)TW, (uint32_t)TH, (uint32_t)TN};
+    int rc = axh::encode_tensor_map(&mdy, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, dy, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 1000 + rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)N};
+    uint64_t strides[3] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2};
+    uint32_t box[4] = {64, (uint32_t)TW, (uint32_t)TH, (uint32_t)TN};
+    int rc = axh::encode_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return 2000 + rc;
+  }
+  return BNC == 128 ? launch_wgrad<128>(mdy, mx, p, grid, stream) : launch_wgrad<64>(mdy, mx, p, grid, stream);
 }

@@ -222,3 +222,52 @@ class TPLLaMAForCausalLM(nn.Module):
             sd["model.norm.weight"] = self.norm.weight.detach().clone()
             sd["lm_head.weight"] = torch.cat(gather(self.lm_head), 0)[:cfg.vocab_size]
         return sd
+
+
+class TPPipelineStage(nn.Module):
+    """One pipeline stage of the tensor-parallel model as a plain module: the first stage maps token
+    ids to the packed ``[2, T/W, H]`` pair (delta, residual) of this rank's token shard, later
+    stages map such a pair to the next one.  Ranks with the same tensor-parallel index in
+    consecutive stages exchange exactly this tensor, so nothing is sent twice."""
+
+    def __init__(self, model: TPLLaMAForCausalLM, seq_len: int):
+        super().__init__()
+        self.model, self.seq_len = model, seq_len
+
+    def forward(self, x):
+        m = self.model
+        if m.first_stage:
+            B, S = x.shape
+            delta, residual = m.run_layers(m.embed_tokens(x), B, S)
+        else:
+            tl = x.shape[1]
+            B = tl * m.pg.world_size() // self.seq_len
+            delta, residual = m.run_layers(x[0], B, self.seq_len, residual=x[1])
+        return torch.stack([delta, residual])
+
+    def loss(self, y, labels):
+        return self.model.loss_from_hidden(y[0], y[1], labels)
+
+
+def build_tp_pp(cfg: LLaMAConfig, world, tp: int, pp: int, seq_len: int, device=None, dtype=torch.bfloat16,
+                num_microbatches: int = 8):
+    """Lays ``tp * pp`` ranks out as ``pp`` consecutive tensor-parallel groups (stage s = ranks
+    ``[s*tp, (s+1)*tp)``) and returns ``(pipeline, stage_module, tp_group)`` for the calling rank.
+    ``world``: a ``parallel.World``.  Every rank creates every sub-group (required by the
+    process-group rendezvous) and keeps the ones it belongs to."""
+    from ..parallel.pipeline import Pipeline, PipelineSchedule, PipelineStage
+    rank = world.rank()
+    if world.world_size() != tp * pp:
+        raise ValueError("world size must be tp * pp")
+    my_stage, my_tp = rank // tp, rank % tp
+    tp_groups = [world.new_group(list(range(s * tp, (s + 1) * tp))) for s in range(pp)]
+    pp_groups = [world.new_group([s * tp + t for s in range(pp)]) for t in range(tp)]
+    tp_pg, pp_pg = tp_groups[my_stage], pp_groups[my_tp]
+    per = cfg.num_hidden_layers // pp
+    layers = range(my_stage * per, cfg.num_hidden_layers if my_stage == pp - 1 else (my_stage + 1) * per)
+    model = TPLLaMAForCausalLM(cfg, tp_pg, device=device, dtype=dtype, layers=layers,
+                               first_stage=my_stage == 0, last_stage=my_stage == pp - 1)
+    stage = TPPipelineStage(model, seq_len)
+    stages = [PipelineStage(stage if s == my_stage else None, s, s) for s in range(pp)]
+    pipe = Pipeline(stages, pp_pg, PipelineSchedule.OneFOneBSchedule, num_microbatches)
+    return pipe, stage, tp_pg

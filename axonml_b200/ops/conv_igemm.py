@@ -4,7 +4,7 @@ Forward and data gradient of stride-1 convolutions run without an im2col matrix:
 producer loads, per filter tap, the tile's box of NHWC input pixels shifted by the tap (zero
 padding is the TMA out-of-range fill).  The data gradient is the same kernel applied to the output
 gradient with the filter rotated by 180 degrees and its channel dims exchanged.  The weight
-gradient currently goes through the framework's convolution-backward fallback.
+gradient is a second implicit GEMM whose reduction dimension is the pixels.
 
 Layout contract: activations are bf16 in channels-last memory format (NCHW shape, NHWC storage),
 weights ``[cout, cin, kh, kw]`` in any float dtype (converted to ``[cout, kh, kw, cin]`` bf16).
@@ -59,6 +59,20 @@ def fprop(x, w_ohwi, bias, padding, act: str = "none"):
     return y
 
 
+def wgrad(dy, x, kernel_size, padding):
+    """Weight gradient ``[cout, cin, kh, kw]`` (fp32) of a stride-1 convolution from the channels-last
+    bf16 output gradient and input: pixels are the reduction dim of an implicit GEMM, split over
+    CTAs with fp32 global reductions."""
+    n, cin, h, w = x.shape
+    cout = dy.shape[1]
+    kh, kw = kernel_size
+    dw = torch.zeros((cout, kh, kw, cin), dtype=torch.float32, device=x.device)
+    rc = N.cuda().ax_conv2d_wgrad(N.ptr(dy), N.ptr(x), N.ptr(dw), n, h, w, cin, cout, kh, kw, padding[0], padding[1], 0,
+                                  N.ptr(N.status_word(x.device)), N.stream_ptr())
+    N.check(rc, "ax_conv2d_wgrad")
+    return dw.permute(0, 3, 1, 2).contiguous()
+
+
 class _ConvFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, padding):
@@ -81,9 +95,7 @@ class _ConvFn(torch.autograd.Function):
             w_t = weight.detach().flip(2, 3).permute(1, 2, 3, 0).to(torch.bfloat16).contiguous()
             dx = fprop(dy, w_t, None, (kh - 1 - ph, kw - 1 - pw))
         if ctx.needs_input_grad[1]:
-            _, dw, _ = torch.ops.aten.convolution_backward(
-                dy, x, weight.to(dy.dtype), None, [1, 1], [ph, pw], [1, 1], False, [0, 0], 1, [False, True, False])
-            dw = dw.to(weight.dtype)
+            dw = wgrad(dy, x, (kh, kw), (ph, pw)).to(weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy.float().sum(dim=(0, 2, 3)).to(ctx.bias_dtype)
         return dx, dw, db, None

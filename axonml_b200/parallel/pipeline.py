@@ -47,7 +47,8 @@ class Pipeline(Module):
         self.stages = list(stages)
         self.pg = process_group
         self._schedule, self._m = schedule, num_microbatches
-        self.local = torch.nn.ModuleList([s.module for s in self.stages if s.device_rank == self.pg.rank()])
+        self.local = torch.nn.ModuleList([s.module for s in self.stages
+                                          if s.device_rank == self.pg.rank() and s.module is not None])
         self._shape_cache = {}
         self._pending = []
 

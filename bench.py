@@ -482,6 +482,78 @@ def bench_lenet_cpu(args):
     return 0
 
 
+def bench_llama_tp_pp(args):
+    """Llama-style 8B as TP = N/2 x PP = 2 (stage s = ranks [s*TP, (s+1)*TP)), 1F1B over 8 microbatches
+    of one 4096-token sequence, AdamW with fp32 master weights.  Activations between the stages are
+    the sequence-parallel token shards, sent rank-to-rank over NCCL p2p."""
+    import torch
+    from axonml_b200 import optim
+    from axonml_b200.llm import LLaMAConfig
+    from axonml_b200.llm.llama_tp import build_tp_pp
+    from axonml_b200.optim.mixed import MasterParams
+    from axonml_b200.parallel import World, fused_gemm
+
+    world, rank, local, dev, pg = _dist_setup()
+    if world < 2 or world % 2:
+        raise SystemExit("llama8b_tp_pp needs an even number of GPUs (TP = N/2, PP = 2)")
+    cfg = LLaMAConfig.llama3_8b()
+    if args.layers:
+        cfg.num_hidden_layers = args.layers
+    S = args.seq_len if args.seq_len != 2048 else 4096
+    global_batch, n_micro = 8, 8
+    torch.manual_seed(4321 + rank)
+    w = World.init(pg.backend())
+    pipe, stage, tp_pg = build_tp_pp(cfg, w, world // 2, 2, S, device=dev, dtype=torch.bfloat16, num_microbatches=n_micro)
+    if args.comm == "nccl":
+        fused_gemm._ENGINES[id(tp_pg.backend())] = None
+    stage.train()
+    mp = MasterParams(stage.parameters())
+    opt = optim.AdamW(mp.parameters(), 3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    gen = torch.Generator(device="cpu").manual_seed(77)
+    n_host = max(args.steps, 2)
+    host_ids = [torch.randint(0, cfg.vocab_size, (global_batch, S), generator=gen).pin_memory() for _ in range(n_host)]
+    dev_ids = [t.to(dev) for t in host_ids[:2]]
+    last_stage = stage.model.last_stage
+
+    def run(ids):
+        loss = pipe.train_step(ids, ids, stage.loss, act_dtype=torch.bfloat16)
+        stage.model.sync_replicated_grads()
+        mp.attach_grads()
+        opt.step()
+        mp.zero_grad()
+        return loss if loss is not None else torch.zeros((), device=dev)
+
+    def step_device(i):
+        return run(dev_ids[i % 2])
+
+    def step_e2e(i):
+        return float(run(host_ids[i % n_host].to(dev, non_blocking=True)).item())
+
+    m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
+    # the loss lives on the last stage: fetch it for the report
+    import torch.distributed as dist
+    t = torch.tensor([m["last_loss"] if last_stage else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tokens = global_batch * S
+    if rank == 0:
+        print(json.dumps({
+            "metric": "tokens/s 8B TP x PP (Llama-style 8B, tensor + pipeline parallel, training)",
+            "value": round(tokens / (m["ms_per_step"] / 1000.0), 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms_per_step"], 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "axonml_b200",
+            "config": {"model": f"llama-8b ({cfg.num_hidden_layers}L d4096 32q/8kv ffn14336 vocab128256)",
+                       "global_batch": global_batch, "seq_len": S, "parallelism": f"tp{world // 2} x pp2 (1F1B, {n_micro} microbatches)",
+                       "optimizer": "AdamW lr3e-4 b(0.9,0.95) wd0.1, fp32 master weights",
+                       "l2_policy": "per-step working set (>= 14 GB per GPU) exceeds the 126 MB L2"},
+            "clocks": m["clocks"],
+            "e2e": {"value": round(tokens / (m["e2e_ms_per_step"] / 1000.0), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": global_batch * S * 8, "d2h_bytes_per_step": 4,
+                    "ms_per_step": round(m["e2e_ms_per_step"], 3)},
+            "gpu_launches": m["launches"], "final_loss": round(float(t.item()), 4)}), flush=True)
+    return _finish(world)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -492,6 +564,8 @@ def main():
         return bench_q4k_decode(args)
     if args.config == "llama8b_tp":
         return bench_llama_tp(args)
+    if args.config == "llama8b_tp_pp":
+        return bench_llama_tp_pp(args)
     if args.config == "resnet18_ddp":
         return bench_resnet_ddp(args)
     if args.config == "lenet_cpu":

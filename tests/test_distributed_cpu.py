@@ -323,3 +323,43 @@ def test_tensor_parallel_llama_matches_unsharded():
         assert abs(loss - loss_ref) < 1e-4, (loss, loss_ref)
         assert max(errs) < 1e-3, errs
         assert rt == 0.0
+
+
+def _tp_pp_llama(rank, world, be):
+    """TP=2 x PP=2 (1F1B, 2 microbatches) of the tiny LLaMA against the unsharded model: loss and
+    the gradient of one weight of each stage."""
+    from axonml_b200.llm import LLaMAConfig, LLaMAForCausalLM
+    from axonml_b200.llm.llama_tp import build_tp_pp
+    from axonml_b200.parallel import World
+    cfg = LLaMAConfig.tiny()
+    torch.manual_seed(11)
+    ref = LLaMAForCausalLM(cfg)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    S = 32
+    pipe, stage, tp_pg = build_tp_pp(cfg, World.init(be), 2, 2, S, dtype=torch.float32, num_microbatches=2)
+    stage.model.load_full_state_dict(sd)
+    torch.manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (2, S))
+    loss_ref, _ = ref.forward_with_loss(ids)
+    loss_ref.backward()
+    loss = pipe.train_step(ids, ids, stage.loss, act_dtype=torch.float32)
+    stage.model.sync_replicated_grads()
+    with torch.no_grad():
+        for p in stage.model.parameters():
+            p.copy_(p.grad)
+    g = stage.model.full_state_dict()
+    gref = dict(ref.named_parameters())
+    # per-microbatch losses are means over the microbatch's tokens; their mean equals the batch mean
+    # because both sequences have the same number of valid positions
+    errs = {n: float((g[n] - gref[n].grad).abs().max() / (gref[n].grad.abs().max() + 1e-12))
+            for n in g if n in gref and ("q_proj" in n or "down_proj" in n or n == "lm_head.weight")}
+    return (float(loss) if loss is not None else None), float(loss_ref), errs
+
+
+def test_tensor_plus_pipeline_parallel_llama_matches_unsharded():
+    res = run_ranks(_tp_pp_llama, 4)
+    for r in range(4):
+        loss, loss_ref, errs = res[r][1]
+        if r >= 2:
+            assert abs(loss - loss_ref) < 1e-4, (loss, loss_ref)
+        assert errs and max(errs.values()) < 1e-3, errs
