@@ -33,8 +33,19 @@ class _BatchNorm(Module):
     @classmethod
     def with_options(cls, num_features, eps, momentum, affine=True): return cls(num_features, eps, momentum, affine)
 
-    def forward(self, x):
+    def forward(self, x, relu: bool = False, residual=None):
+        """``relu`` / ``residual`` fuse the block's activation and skip connection into the
+        normalisation pass (one kernel on channels-last bf16 inputs)."""
         use_batch = self.training or not self.track_running_stats
+        if x.dim() == 4:
+            from ...ops import batchnorm as BN
+            if use_batch and self.track_running_stats:
+                with torch.no_grad():
+                    self.num_batches_tracked += 1
+            return BN.batch_norm(x, self.weight, self.bias,
+                                 self.running_mean if self.track_running_stats else None,
+                                 self.running_var if self.track_running_stats else None,
+                                 use_batch, self.momentum, self.eps, relu, residual)
         if use_batch and self.track_running_stats:
             # the reference updates running_var with the biased batch variance
             with torch.no_grad():
@@ -45,9 +56,13 @@ class _BatchNorm(Module):
                 self.running_mean.mul_(1 - self.momentum).add_(mean, alpha=self.momentum)
                 self.running_var.mul_(1 - self.momentum).add_(var, alpha=self.momentum)
                 self.num_batches_tracked += 1
-            return F.batch_norm(x, None, None, self.weight, self.bias, True, 0.0, self.eps)
-        return F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias,
-                            use_batch, 0.0, self.eps)
+            y = F.batch_norm(x, None, None, self.weight, self.bias, True, 0.0, self.eps)
+        else:
+            y = F.batch_norm(x, self.running_mean, self.running_var, self.weight, self.bias,
+                             use_batch, 0.0, self.eps)
+        if residual is not None:
+            y = y + residual
+        return torch.relu(y) if relu else y
 
 
 class BatchNorm1d(_BatchNorm):

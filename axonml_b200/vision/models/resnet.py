@@ -26,9 +26,8 @@ class BasicBlock(nn.Module):
 
     def forward(self, x):
         idt = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
-        return self.relu(out + idt)
+        out = self.bn1(self.conv1(x), relu=True)
+        return self.bn2(self.conv2(out), relu=True, residual=idt)       # relu(bn(conv) + identity), one pass
 
 
 class Bottleneck(nn.Module):
@@ -92,7 +91,7 @@ class ResNet(nn.Module):
     def resnet50(cls, num_classes: int = 1000): return cls(Bottleneck, [3, 4, 6, 3], num_classes)
 
     def forward(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = self.maxpool(self.bn1(self.conv1(x), relu=True))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(self.avgpool(x).flatten(1))
 

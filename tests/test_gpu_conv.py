@@ -64,3 +64,61 @@ def test_resnet_block_uses_the_kernel(kernel_status):
     assert _native.launch_count() > before
     ref = F.conv2d(x.float(), conv.weight.bfloat16().float(), None, 1, 1)
     assert (y.float() - ref).abs().max().item() < 0.03 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("shape,relu,res", [((8, 64, 56, 56), True, False), ((4, 128, 28, 28), True, True),
+                                              ((16, 512, 7, 7), False, False), ((2, 192, 9, 11), True, True)])
+def test_batchnorm_train_fwd_bwd_matches_fp32_reference(shape, relu, res, kernel_status):
+    from axonml_b200.ops import batchnorm as BN
+    torch.manual_seed(0)
+    n, c, h, w = shape
+    x = (torch.randn(shape, device="cuda") * 2 + 0.5).bfloat16().contiguous(memory_format=torch.channels_last)
+    r = torch.randn(shape, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last) if res else None
+    g = torch.randn(shape, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    wt, b = torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda")
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    x1, w1, b1 = x.clone().requires_grad_(True), wt.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    r1 = r.clone().requires_grad_(True) if res else None
+    y = BN.batch_norm(x1, w1, b1, rm, rv, True, 0.1, 1e-5, relu, r1)
+    y.backward(g)
+    # fp32 reference
+    x2, w2, b2 = x.float().requires_grad_(True), wt.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    r2 = r.float().requires_grad_(True) if res else None
+    rm2, rv2 = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    z = torch.nn.functional.batch_norm(x2, None, None, w2, b2, True, 0.0, 1e-5)
+    if res:
+        z = z + r2
+    if relu:
+        z = torch.relu(z)
+    z.backward(g.float())
+    xf = x.float()
+    rm2.mul_(0.9).add_(xf.mean((0, 2, 3)), alpha=0.1)
+    rv2.mul_(0.9).add_(xf.var((0, 2, 3), unbiased=False), alpha=0.1)
+    assert (y.float() - z).abs().max().item() < 0.05
+    assert (rm - rm2).abs().max().item() < 1e-3 and (rv - rv2).abs().max().item() < 1e-2
+    assert (x1.grad.float() - x2.grad).abs().max().item() < 0.05 * max(x2.grad.abs().max().item(), 1e-3) + 2e-3
+    assert (w1.grad - w2.grad).abs().max().item() < 0.02 * w2.grad.abs().max().item() + 0.05
+    assert (b1.grad - b2.grad).abs().max().item() < 0.02 * b2.grad.abs().max().item() + 0.05
+    if res:
+        assert (r1.grad.float() - r2.grad).abs().max().item() < 0.02
+
+
+def test_batchnorm_eval_and_maxpool(kernel_status):
+    from axonml_b200.ops import batchnorm as BN
+    torch.manual_seed(1)
+    x = torch.randn(4, 64, 20, 20, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    wt, b = torch.rand(64, device="cuda") + 0.5, torch.randn(64, device="cuda")
+    rm, rv = torch.randn(64, device="cuda") * 0.1, torch.rand(64, device="cuda") + 0.5
+    y = BN.batch_norm(x, wt, b, rm, rv, False, 0.1, 1e-5, True, None)
+    ref = torch.relu(torch.nn.functional.batch_norm(x.float(), rm, rv, wt, b, False, 0.0, 1e-5))
+    assert (y.float() - ref).abs().max().item() < 0.05
+    for (k, s, p) in ((3, 2, 1), (2, 2, 0)):
+        x1 = x.clone().requires_grad_(True)
+        o = BN.max_pool2d(x1, k, s, p)
+        g = torch.randn_like(o)
+        o.backward(g)
+        x2 = x.float().requires_grad_(True)
+        o2 = torch.nn.functional.max_pool2d(x2, k, s, p)
+        o2.backward(g.float())
+        assert torch.equal(o.float(), o2)
+        assert (x1.grad.float() - x2.grad).abs().max().item() < 0.02

@@ -302,3 +302,23 @@ def test_grad_sumsq_and_unscale():
     fg[1][2] = float("inf")
     O.multi_tensor("unscale_check", None, fg, inv_scale=inv, norms=flag)
     assert flag.item() == 1
+
+
+def test_jit_nvrtc_fused_elementwise_matches_interpreter(kernel_status):
+    """A traced elementwise graph compiled with NVRTC for this GPU and launched through the driver
+    API gives what the CPU interpreter gives."""
+    from axonml_b200 import jit
+    from axonml_b200.jit import nvrtc
+    if not nvrtc.available():
+        pytest.skip("cuda-python bindings not importable")
+
+    def f(tr):
+        a, b = tr.input("a", [4096]), tr.input("b", [4096])
+        y = a.mul(b).add_scalar(0.5).tanh().mul_scalar(2.0).relu()
+        return tr.output("y", y)
+    g = jit.trace(f)
+    a, b = torch.randn(4096, device="cuda"), torch.randn(4096, device="cuda")
+    ref = jit.interpret(g, {"a": a.cpu(), "b": b.cpu()})["y"]
+    out = jit.compile_graph(g).run_tensors({"a": a, "b": b})["y"]
+    assert out.is_cuda
+    assert (out.cpu() - ref).abs().max().item() < 2e-3
