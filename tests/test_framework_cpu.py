@@ -176,3 +176,13 @@ def test_data_pipeline():
     assert e0 != e1
     t = data.Compose([data.Normalize([0.5], [0.5]), data.Clamp(-1.0, 1.0)])
     assert float(t(torch.tensor([1.0]))) == 1.0
+
+
+def test_axonml_alias_package_and_prelude():
+    import axonml
+    from axonml import nn as nn2
+    from axonml.distributed import DistributedDataParallel
+    import axonml_b200.parallel as P
+    assert nn2.Linear is nn.Linear and DistributedDataParallel is P.DistributedDataParallel
+    pre = axonml.prelude()
+    assert {"Tensor", "Variable", "Linear", "Adam", "DataLoader", "Trainer"} <= set(pre)
