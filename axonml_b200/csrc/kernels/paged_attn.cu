@@ -169,6 +169,178 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode attention with the K/V pages staged through shared memory by TMA (page size 16).
+// The register-resident variant above keeps only two iterations of loads in flight per thread; here
+// one thread runs a ring of kTStages page loads (8 KB each: 16 tokens x 128 dims of K and of V for
+// one KV head, one 2-D box per operand), so a CTA has up to 48 KB on its way and three CTAs fit
+// on an SM.  Four warps consume a page together: warp w owns tokens 4w..4w+3, eight lanes per
+// token; lane `sub` holds dims [8*sub, 8*sub+8) and [64+8*sub, 64+8*sub+8), so a quarter-warp reads
+// 128 contiguous bytes of a row (no bank conflicts).  Splits and the final merge are as above.
+constexpr int kTWarps = 4;
+constexpr int kTPage = 16;
+constexpr int kTStages = 6;
+constexpr int kTStageBytes = 2 * kTPage * D * 2;      // K page + V page
+
+template <int G>
+__global__ void __launch_bounds__(kTWarps * 32)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, float* __restrict__ part,
+                        const int* __restrict__ block_table, const int* __restrict__ ctx_lens, int Hq, int Hkv,
+                        int max_pages, float scale_log2, long q_stride, long o_stride, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  uint64_t* full = (uint64_t*)(smem + kTStages * kTStageBytes);
+  uint64_t* empty = full + kTStages;
+  volatile int* dead = (volatile int*)(empty + kTStages);
+  float* sM = (float*)(dead + 2);                       // [G][warps]
+  float* sL = sM + kMaxG * kTWarps;
+  float* sO = sL + kMaxG * kTWarps;                     // [warps][G][D]
+
+  const int b = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z, S = gridDim.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7;
+  const int tok = warp * 4 + (lane >> 3);               // token of the page this lane group owns
+  const int ctx = ctx_lens[b];
+  const int pages = (ctx + kTPage - 1) / kTPage;
+  const int per = (pages + S - 1) / S;
+  const int p_begin = sp * per, p_end = min(pages, p_begin + per);
+  const int h0 = hk * G;
+
+  if (threadIdx.x == 0) {
+    *dead = 0;
+    for (int i = 0; i < kTStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], kTWarps); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](int pg) {       // thread 0 only
+    const int st = (pg - p_begin) % kTStages;
+    const int page = block_table[b * max_pages + pg];
+    uint8_t* dst = smem + st * kTStageBytes;
+    mbar_expect_tx(&full[st], kTStageBytes);
+    tma_load_2d(dst, &map_k, &full[st], hk * D, page * kTPage);
+    tma_load_2d(dst + kTPage * D * 2, &map_v, &full[st], hk * D, page * kTPage);
+  };
+  if (threadIdx.x == 0)
+    for (int pg = p_begin; pg < p_end && pg < p_begin + kTStages; ++pg) issue(pg);
+
+  float qv[G][16];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = q + (long)b * q_stride + (long)(h0 + g) * D;
+    unpack8(*reinterpret_cast<const uint4*>(qp + sub * 8), &qv[g][0]);
+    unpack8(*reinterpret_cast<const uint4*>(qp + 64 + sub * 8), &qv[g][8]);
+  }
+  float m[G], l[G], acc[G][16];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
+  }
+
+  bool ok = true;
+  for (int pg = p_begin; pg < p_end; ++pg) {
+    const int it = pg - p_begin;
+    const int st = it % kTStages;
+    ok = mbar_wait(&full[st], (uint32_t)((it / kTStages) & 1), dead, status, 960);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const uint32_t kbase = smem_u32(smem + st * kTStageBytes) + tok * (D * 2) + sub * 16;
+    const uint32_t vbase = kbase + kTPage * D * 2;
+    uint4 k0, k1, v0, v1;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k0.x), "=r"(k0.y), "=r"(k0.z), "=r"(k0.w) : "r"(kbase));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k1.x), "=r"(k1.y), "=r"(k1.z), "=r"(k1.w) : "r"(kbase + 128));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0.x), "=r"(v0.y), "=r"(v0.z), "=r"(v0.w) : "r"(vbase));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1.x), "=r"(v1.y), "=r"(v1.z), "=r"(v1.w) : "r"(vbase + 128));
+    // the stage can be refilled as soon as every warp has its registers
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
+    if (threadIdx.x == 0 && pg + kTStages < p_end) {
+      if (mbar_wait(&empty[st], (uint32_t)((it / kTStages) & 1), dead, status, 961)) issue(pg + kTStages);
+    }
+    const bool valid = pg * kTPage + tok < ctx;
+    float kf[16], vf[16];
+    unpack8(k0, kf); unpack8(k1, kf + 8);
+    unpack8(v0, vf); unpack8(v1, vf + 8);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float sc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) sc += qv[g][i] * kf[i];
+      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+      if (valid) {
+        sc *= scale_log2;
+        const float mn = fmaxf(m[g], sc);
+        const float alpha = exp2f(m[g] - mn), pe = exp2f(sc - mn);
+        l[g] = l[g] * alpha + pe;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[g][i] = acc[g][i] * alpha + pe * vf[i];
+        m[g] = mn;
+      }
+    }
+  }
+  // merge: the four token groups of a warp with shuffles, the warps through shared memory
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float M = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], 8));
+    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+    const float w = m[g] == -INFINITY ? 0.f : exp2f(m[g] - M);
+    float L = l[g] * w;
+    L += __shfl_xor_sync(0xffffffffu, L, 8);
+    L += __shfl_xor_sync(0xffffffffu, L, 16);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a = acc[g][i] * w;
+      a += __shfl_xor_sync(0xffffffffu, a, 8);
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      if (lane < 8) sO[(warp * G + g) * D + (i < 8 ? sub * 8 + i : 64 + sub * 8 + (i - 8))] = a;
+    }
+    if (lane == 0) { sM[g * kTWarps + warp] = M; sL[g * kTWarps + warp] = L; }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kTWarps; ++w) M = fmaxf(M, sM[g * kTWarps + w]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kTWarps; ++w) {
+      const float f = sM[g * kTWarps + w] == -INFINITY ? 0.f : exp2f(sM[g * kTWarps + w] - M);
+      L += sL[g * kTWarps + w] * f;
+      O += sO[(w * G + g) * D + d] * f;
+    }
+    if (S == 1) {
+      out[(long)b * o_stride + (long)(h0 + g) * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+    } else {
+      float* pp = part + (((long)b * Hq + h0 + g) * S + sp) * (D + 2);
+      pp[d] = O;
+      if (d == 0) { pp[D] = M; pp[D + 1] = L; }
+    }
+  }
+}
+
+template <int G>
+int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, void* out, float* ws, const int* block_table,
+               const int* ctx_lens, dim3 grid, int Hq, int Hkv, int max_pages, float sl2, long q_stride, long o_stride,
+               int* status, cudaStream_t stream) {
+  const int smem = 128 + kTStages * kTStageBytes + 2 * kTStages * 8 + 16 + (2 * kMaxG * kTWarps + kTWarps * G * D) * 4;
+  auto k = paged_decode_tma_kernel<G>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  k<<<grid, kTWarps * 32, smem, stream>>>(mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, ws, block_table, ctx_lens, Hq,
+                                          Hkv, max_pages, sl2, q_stride, o_stride, status);
+  return (int)cudaGetLastError();
+}
+
 // One CTA of D threads per (sequence, query head): combines the S partial results.
 __global__ void __launch_bounds__(D)
 paged_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int Hq, int S, long o_stride) {
@@ -202,16 +374,44 @@ AX_API int ax_paged_kv_write(const void* k, const void* v, void* kc, void* vc, c
 }
 
 // q [B, Hq, 128], out [B, Hq, 128] bf16 (row strides in elements); Hq/Hkv in {1, 2, 4, 8}.
-// splits > 1 needs `workspace` of B * Hq * splits * 130 floats.
+// splits > 1 needs `workspace` of B * Hq * splits * 130 floats.  With page_size 16, `num_pages` (pages in the
+// cache tensors) and a status word given, the TMA-staged kernel runs; otherwise the register-resident one.
 AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* vc, void* out,
                                      const int* block_table, const int* ctx_lens, int B, int Hq, int Hkv,
                                      int Dh, int page_size, int max_pages, float scale, long q_stride,
-                                     long o_stride, int splits, float* workspace, cudaStream_t stream) {
+                                     long o_stride, int splits, float* workspace, int num_pages, int* status,
+                                     cudaStream_t stream) {
   if (B <= 0) return 0;
   if (Dh != D || Hq % Hkv || splits < 1 || (splits > 1 && !workspace)) return -1;
   const int G = Hq / Hkv;
   dim3 grid(B, Hkv, splits);
   const float sl2 = scale * 1.4426950408889634f;
+  if (page_size == kTPage && num_pages > 0 && status != nullptr) {
+    CUtensorMap mk, mv;
+    uint64_t dims[2] = {(uint64_t)Hkv * D, (uint64_t)num_pages * page_size};
+    uint64_t strides[1] = {(uint64_t)Hkv * D * 2};
+    uint32_t box[2] = {(uint32_t)D, (uint32_t)kTPage};
+    int rc = axh::encode_tensor_map(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kc, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return 1000 + rc;
+    rc = axh::encode_tensor_map(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, vc, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return 1100 + rc;
+    int e;
+    switch (G) {
+      case 1: e = launch_tma<1>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 2: e = launch_tma<2>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 4: e = launch_tma<4>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 8: e = launch_tma<8>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      default: return -2;
+    }
+    if (e) return e;
+    if (splits > 1) {
+      paged_merge_kernel<<<dim3(B, Hq), D, 0, stream>>>(workspace, (__nv_bfloat16*)out, Hq, splits, o_stride);
+      return (int)cudaGetLastError();
+    }
+    return 0;
+  }
 #define AX_LAUNCH(GG)                                                                                         \
   paged_decode_kernel<GG><<<grid, kWarps * 32, 0, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc, \
       (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, workspace, block_table, ctx_lens, Hq, Hkv, page_size,     \

@@ -14,3 +14,5 @@ from .process_group import ProcessGroup, World
 from .pipeline import Pipeline, PipelineMemoryStats, PipelineSchedule, PipelineStage
 from .tensor_parallel import (ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding,
                               vocab_parallel_cross_entropy)
+from .mesh import DeviceMesh
+from .checkpoint import load_sharded, save_sharded

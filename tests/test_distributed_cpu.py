@@ -410,3 +410,21 @@ def test_sharded_checkpoint_resumes_at_other_world_sizes(tmp_path):
     other = run_ranks(_fsdp_train, 4, args=(d, "resume"))[0][1]
     for k in base:
         assert torch.allclose(base[k], other[k], atol=2e-4), (k, (base[k] - other[k]).abs().max())
+
+
+def _mesh(rank, world, be):
+    from axonml_b200.parallel import DeviceMesh, ReduceOp, World
+    mesh = DeviceMesh(World.init(be), {"pp": 2, "tp": 2})
+    t = torch.tensor([float(rank)])
+    mesh.group("tp").backend().all_reduce(t, ReduceOp.Sum)
+    p = torch.tensor([float(rank)])
+    mesh.group("pp").backend().all_reduce(p, ReduceOp.Sum)
+    return mesh.coords(), mesh.ranks("tp"), mesh.ranks("pp"), float(t), float(p)
+
+
+def test_device_mesh_groups():
+    res = run_ranks(_mesh, 4)
+    expect = {0: ({"pp": 0, "tp": 0}, [0, 1], [0, 2], 1.0, 2.0), 1: ({"pp": 0, "tp": 1}, [0, 1], [1, 3], 1.0, 4.0),
+              2: ({"pp": 1, "tp": 0}, [2, 3], [0, 2], 5.0, 2.0), 3: ({"pp": 1, "tp": 1}, [2, 3], [1, 3], 5.0, 4.0)}
+    for r in range(4):
+        assert tuple(res[r][1]) == expect[r], (r, res[r][1])
