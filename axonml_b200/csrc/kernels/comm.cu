@@ -152,7 +152,11 @@ __device__ __forceinline__ void bcast16(const Peers& P, long off, uint4 v) {
 template <bool BF16, bool MC>
 __global__ void __launch_bounds__(kThreads)
 fused_allreduce_kernel(const Peers P, long base_off, long n, float mul, const float* inv_scale,
-                       int* found_inf, uint32_t epoch, int* status) {
+                       int* found_inf, uint32_t epoch, uint32_t* epoch_dev, int* status) {
+  // With a device-side call counter the launch carries no per-call argument, so it can be
+  // captured in a CUDA graph and replayed: every block reads the counter at entry, block 0
+  // advances it after all blocks of this launch have finished.
+  if (epoch_dev != nullptr) epoch = *(volatile uint32_t*)epoch_dev + 1;
   const bool ok = collective_begin(P, epoch, status);
   int bad = 0;
   if (ok) {
@@ -181,6 +185,7 @@ fused_allreduce_kernel(const Peers P, long base_off, long n, float mul, const fl
   bad = __syncthreads_or(bad);
   const int any = collective_end(P, epoch, bad, status);
   if (blockIdx.x == 0 && threadIdx.x == 0 && any && found_inf) *found_inf = 1;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && epoch_dev != nullptr) *(volatile uint32_t*)epoch_dev = epoch;
 }
 
 struct AdamW {
@@ -268,9 +273,11 @@ AX_API int ax_comm_signal_slots() { return 2 * axc::kMaxRanks + 4; }
 // In-place mean all-reduce of `n` elements (dtype: 0 fp32, 1 bf16) located at byte offset
 // `base_off` of every rank's symmetric buffer.  n * elsize must be a multiple of 16 * world.
 // `epoch` must increase by one per call on this communicator (all ranks use the same value).
+// `epoch_dev` (optional): device word that replaces `epoch` (see the kernel); a communicator must use one
+// of the two consistently.
 AX_API int ax_fused_allreduce(int dtype, void* const* bufs, void* const* sigs, void* mc_buf, int rank,
                               int world, long base_off, long n, const float* inv_scale, int* found_inf,
-                              unsigned epoch, int grid_blocks, int* status, cudaStream_t stream) {
+                              unsigned epoch, unsigned* epoch_dev, int grid_blocks, int* status, cudaStream_t stream) {
   if (world < 1 || world > axc::kMaxRanks) return -1;
   const int esz = dtype == 1 ? 2 : 4;
   if ((n * esz) % (16L * world) || (base_off % 16)) return -1;
@@ -278,11 +285,11 @@ AX_API int ax_fused_allreduce(int dtype, void* const* bufs, void* const* sigs, v
   const int grid = checked_grid(grid_blocks);
   const float mul = 1.f / world;
   if (dtype == 1) {
-    if (mc_buf) fused_allreduce_kernel<true, true><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, status);
-    else fused_allreduce_kernel<true, false><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, status);
+    if (mc_buf) fused_allreduce_kernel<true, true><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, epoch_dev, status);
+    else fused_allreduce_kernel<true, false><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, epoch_dev, status);
   } else {
-    if (mc_buf) fused_allreduce_kernel<false, true><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, status);
-    else fused_allreduce_kernel<false, false><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, status);
+    if (mc_buf) fused_allreduce_kernel<false, true><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, epoch_dev, status);
+    else fused_allreduce_kernel<false, false><<<grid, kThreads, 0, stream>>>(P, base_off, n, mul, inv_scale, found_inf, epoch, epoch_dev, status);
   }
   return (int)cudaGetLastError();
 }

@@ -20,19 +20,24 @@ from .symm import Communicator, SymmetricHeap, available
 
 
 class FusedAllReduce:
-    def __init__(self, heap: SymmetricHeap, max_numel: int, dtype: torch.dtype, grid_blocks: int = 32):
+    def __init__(self, heap: SymmetricHeap, max_numel: int, dtype: torch.dtype, grid_blocks: int = 32,
+                 device_epoch: bool = False):
+        """``device_epoch``: keep the call counter in device memory so that calls can be captured
+        in CUDA graphs (serving decode steps); such an instance must not be mixed with host-counted
+        calls."""
         self.heap = heap
         self.comm = Communicator(heap, grid_blocks)
         self.dtype = dtype
+        self._epoch_dev = torch.zeros(1, dtype=torch.int32, device=heap.device) if device_epoch else None
         align = 8 * heap.world * 16
         self.capacity = (max_numel + align - 1) // align * align
         self.stage = heap.allocate(self.capacity, dtype)
 
     @classmethod
-    def try_create(cls, pg, max_numel: int, dtype: torch.dtype):
+    def try_create(cls, pg, max_numel: int, dtype: torch.dtype, grid_blocks: int = 32, device_epoch: bool = False):
         if not available(pg) or dtype not in (torch.float32, torch.bfloat16):
             return None
-        return cls(SymmetricHeap(pg), max_numel, dtype)
+        return cls(SymmetricHeap(pg), max_numel, dtype, grid_blocks, device_epoch)
 
     def all_reduce_mean_(self, flat: torch.Tensor, inv_scale=None, found_inf=None) -> None:
         """In-place mean over ranks of ``flat`` (optionally times ``inv_scale``); sets
@@ -53,8 +58,8 @@ class FusedAllReduce:
             1 if self.dtype == torch.bfloat16 else 0, self.stage.ptr_array(),
             self.comm.signals.ptr_array(), self.stage.mc(), self.heap.rank, self.heap.world,
             ctypes.c_long(0), ctypes.c_long(n_pad), N.ptr(inv_scale), N.ptr(found_inf),
-            ctypes.c_uint(self.comm.next_epoch()), self.comm.grid, N.ptr(N.status_word(flat.device)),
-            N.stream_ptr())
+            ctypes.c_uint(0 if self._epoch_dev is not None else self.comm.next_epoch()), N.ptr(self._epoch_dev),
+            self.comm.grid, N.ptr(N.status_word(flat.device)), N.stream_ptr())
         N.check(rc, "ax_fused_allreduce")
         if not in_place:
             flat.copy_(stage[:n])

@@ -48,8 +48,17 @@ class LLMEngine:
         self._graphs: dict = {}
         if self.use_graphs:
             dev = model.device
-            if model.tp > 1:
+            if model.tp > 1 and os.environ.get("AXONML_TP_COMM", "fused") == "nccl":
+                # NCCL collectives are not captured here (a capture that stalls would stall every
+                # rank until the process-group timeout): the NCCL variant decodes eagerly
                 model.comm_mode = "nccl"
+                self.use_graphs = False
+            elif model.tp > 1:
+                # create the peer-memory all-reduce now (a collective allocation, outside any capture);
+                # without it the step would contain process-group calls, which are not captured
+                model._all_reduce(torch.zeros(16, dtype=torch.bfloat16, device=dev))
+                if not model._ar:
+                    self.use_graphs = False
             self._g_tokens = torch.zeros(max_batch, dtype=torch.long, device=dev)
             self._g_slots = torch.zeros(max_batch, dtype=torch.int32, device=dev)
             self._g_pos = torch.zeros(max_batch, dtype=torch.int32, device=dev)

@@ -97,6 +97,15 @@ class QuantizedLlama:
             return quantize_tensor(w, qt_fallback if w.shape[1] % 256 == 0 else QuantType.Q8_0)
 
         def cols(name, lo, hi):
+            """Columns [lo, hi) of a 2-D GGUF tensor.  Blocks run along the columns, so a slice on
+            block boundaries is a byte slice of every row: the quantised values are kept exactly."""
+            shape, qt, _, _ = g.tensors[name]
+            if qt.is_block_quantized() and shape[1] % qt.block_size() == 0 and lo % qt.block_size() == 0 \
+                    and hi % qt.block_size() == 0:
+                q = g.quantized(name)
+                bs, bb = qt.block_size(), qt.bytes_per_block()
+                d = q.data.view(shape[0], shape[1] // bs, bb)[:, lo // bs:hi // bs].contiguous()
+                return QuantizedTensor([shape[0], hi - lo], qt, d.view(-1).to(m.device))
             w = g.tensor(name)[:, lo:hi].contiguous().to(m.device)
             return quantize_tensor(w, QuantType.Q4_K if w.shape[1] % 256 == 0 else QuantType.Q8_0)
 
@@ -176,14 +185,20 @@ class QuantizedLlama:
 
     # ------------------------------------------------------------------ forward
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over the tensor-parallel ranks.  On GPUs this is the one-launch all-reduce kernel over
+        peer memory with its call counter on the device, so decode steps that contain it can be
+        captured in CUDA graphs; elsewhere (CPU ranks, no symmetric memory) the process group's
+        all-reduce."""
         if self.tp == 1:
             return x
-        if self._ar is None and getattr(self, "comm_mode", "fused") == "nccl":
-            self._ar = False        # decode graphs replay fixed kernel arguments: use NCCL, which is capturable
         if self._ar is None:
-            from ..parallel.fused import FusedAllReduce
-            self._ar = FusedAllReduce.try_create(self.pg, 64 * 512 * self.cfg.hidden_size, torch.bfloat16) or False
-        if self._ar:
+            self._ar = False
+            if x.is_cuda and getattr(self, "comm_mode", "fused") != "nccl":
+                from ..parallel.fused import FusedAllReduce
+                self._ar = FusedAllReduce.try_create(self.pg, 64 * 512 * self.cfg.hidden_size, torch.bfloat16,
+                                                     device_epoch=True) or False
+                self._ar32 = FusedAllReduce.try_create(self.pg, 4096, torch.float32, device_epoch=True) if self._ar else None
+        if self._ar and x.dtype == torch.bfloat16 and x.numel() <= self._ar.capacity:
             flat = x.reshape(-1)
             self._ar.all_reduce_mean_(flat)
             return x.mul_(self.tp)
@@ -211,10 +226,19 @@ class QuantizedLlama:
         if self.tp == 1:
             return idx
         pair = torch.stack([val, idx.float()], dim=-1).contiguous()
-        out = torch.empty((self.tp,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
-        self.pg.backend().all_gather(pair, out)
+        ar32 = getattr(self, "_ar32", None) if self._ar else None
+        if ar32 is not None and self.tp * pair.numel() <= ar32.capacity:
+            # every rank writes its pairs into its own slot of a zero buffer; the sum is the gather
+            # (graph-capturable, unlike the process group's all-gather)
+            out = torch.zeros((self.tp,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
+            out[self.rank] = pair
+            ar32.all_reduce_mean_(out.view(-1))
+            out = out * self.tp
+        else:
+            out = torch.empty((self.tp,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
+            self.pg.backend().all_gather(pair, out)
         best = out[..., 0].argmax(dim=0)
-        return out[..., 1].gather(0, best.unsqueeze(0)).squeeze(0).long()
+        return out[..., 1].gather(0, best.unsqueeze(0)).squeeze(0).round().long()
 
     def prefill(self, ids: torch.Tensor, cache, slots, layer_write=True) -> torch.Tensor:
         """``ids`` [B, S] (equal-length prompts); writes K/V of every token into the pages of

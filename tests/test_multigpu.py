@@ -232,3 +232,37 @@ def test_sequence_parallel_block_fused_matches_composed():
     for r in range(WORLD):
         for rel in res[r][1]:
             assert rel < 3e-2, res[r][1]
+
+
+def _tp_serving_gpu(rank, world, be):
+    """Tensor-parallel quantised LLaMA decode: CUDA-graph steps with the peer-memory all-reduce
+    against eager steps, same weights, same prompts."""
+    import os
+    from axonml_b200 import _native
+    from axonml_b200.llm import LLaMAConfig
+    from axonml_b200.parallel import ProcessGroup
+    from axonml_b200.quant import QuantType
+    from axonml_b200.server import LLMEngine, QuantizedLlama
+    cfg = LLaMAConfig(vocab_size=4096, hidden_size=1024, intermediate_size=2048, num_hidden_layers=3,
+                      num_attention_heads=8, num_key_value_heads=8 if world > 4 else 4, max_position_embeddings=256)
+    model = QuantizedLlama.from_random(cfg, ProcessGroup(be), device="cuda", std=0.05, proj_type=QuantType.Q4_K)
+    prompts = [[(7 * i + j) % 4000 for j in range(24)] for i in range(5)]
+    eng = LLMEngine(model, max_batch=8, max_context=64, page_size=16)
+    graphs = eng.use_graphs
+    eng.warmup([5])
+    a = eng.generate(prompts, 6)
+    os.environ["AXONML_DECODE_GRAPHS"] = "0"
+    b = LLMEngine(model, max_batch=8, max_context=64, page_size=16).generate(prompts, 6)
+    torch.cuda.synchronize()
+    _native.check_status()
+    return a, b, graphs, bool(model._ar)
+
+
+def test_tensor_parallel_serving_graph_decode_matches_eager():
+    res = run_gpu_ranks(_tp_serving_gpu, WORLD)
+    a0, b0, graphs, fused = res[0][1]
+    assert graphs and fused
+    for r in range(WORLD):
+        a, b, _, _ = res[r][1]
+        assert a == a0 and b == b0          # all ranks agree
+    assert a0 == b0
