@@ -169,38 +169,54 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 }
 
+constexpr int kTPage = 16;        // page size of the tensor-core decode path
+
 // ---------------------------------------------------------------------------------------------
-// Decode attention with the K/V pages staged through shared memory by TMA (page size 16).
-// The register-resident variant above keeps only two iterations of loads in flight per thread; here
-// one thread runs a ring of kTStages page loads (8 KB each: 16 tokens x 128 dims of K and of V for
-// one KV head, one 2-D box per operand), so a CTA has up to 48 KB on its way and three CTAs fit
-// on an SM.  Four warps consume a page together: warp w owns tokens 4w..4w+3, eight lanes per
-// token; lane `sub` holds dims [8*sub, 8*sub+8) and [64+8*sub, 64+8*sub+8), so a quarter-warp reads
-// 128 contiguous bytes of a row (no bank conflicts).  Splits and the final merge are as above.
-constexpr int kTWarps = 4;
-constexpr int kTPage = 16;
-constexpr int kTStages = 6;
-constexpr int kTStageBytes = 2 * kTPage * D * 2;      // K page + V page
+// Decode attention on the warp-level tensor-core path (mma.sync m16n8k16, bf16 in, fp32 out).
+// With grouped-query attention the G query heads that share a KV head form the rows of a small
+// matrix: S[G x 16] = Q[G x 128] K_page^T and O[G x 128] += P[G x 16] V_page per 16-token page.
+// On CUDA cores those products cost 2 FMAs per byte of KV cache, which caps the kernel near a
+// quarter of HBM speed; as MMAs (rows padded to 16) they are a handful of instructions per page.
+// A producer warp keeps kMStages pages in flight with TMA (per page: K and V, each as two
+// 64-dim halves in the 128-byte swizzle so that ldmatrix is conflict-free); four consumer warps
+// take pages round-robin, each with its own online-softmax state, and merge at the end.
+constexpr int kMWarps = 4;
+constexpr int kMStages = 8;
+constexpr int kMHalf = kTPage * 64 * 2;            // 2 KB: 16 tokens x 64 dims
+constexpr int kMStageBytes = 4 * kMHalf;           // K lo, K hi, V lo, V hi
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 template <int G>
-__global__ void __launch_bounds__(kTWarps * 32)
-paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+__global__ void __launch_bounds__((kMWarps + 1) * 32)
+paged_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, float* __restrict__ part,
                         const int* __restrict__ block_table, const int* __restrict__ ctx_lens, int Hq, int Hkv,
                         int max_pages, float scale_log2, long q_stride, long o_stride, int* status) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
-  uint64_t* full = (uint64_t*)(smem + kTStages * kTStageBytes);
-  uint64_t* empty = full + kTStages;
-  volatile int* dead = (volatile int*)(empty + kTStages);
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + kMStages * kMStageBytes);
+  uint64_t* empty = full + kMStages;
+  volatile int* dead = (volatile int*)(empty + kMStages);
   float* sM = (float*)(dead + 2);                       // [G][warps]
-  float* sL = sM + kMaxG * kTWarps;
-  float* sO = sL + kMaxG * kTWarps;                     // [warps][G][D]
+  float* sL = sM + kMaxG * kMWarps;
+  float* sO = sL + kMaxG * kMWarps;                     // [warps][G][D]
 
   const int b = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z, S = gridDim.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane & 7;
-  const int tok = warp * 4 + (lane >> 3);               // token of the page this lane group owns
   const int ctx = ctx_lens[b];
   const int pages = (ctx + kTPage - 1) / kTPage;
   const int per = (pages + S - 1) / S;
@@ -209,109 +225,128 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
   if (threadIdx.x == 0) {
     *dead = 0;
-    for (int i = 0; i < kTStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], kTWarps); }
+    for (int i = 0; i < kMStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     mbar_fence_init();
   }
   __syncthreads();
 
-  auto issue = [&](int pg) {       // thread 0 only
-    const int st = (pg - p_begin) % kTStages;
-    const int page = block_table[b * max_pages + pg];
-    uint8_t* dst = smem + st * kTStageBytes;
-    mbar_expect_tx(&full[st], kTStageBytes);
-    tma_load_2d(dst, &map_k, &full[st], hk * D, page * kTPage);
-    tma_load_2d(dst + kTPage * D * 2, &map_v, &full[st], hk * D, page * kTPage);
-  };
-  if (threadIdx.x == 0)
-    for (int pg = p_begin; pg < p_end && pg < p_begin + kTStages; ++pg) issue(pg);
+  const int grow = lane >> 2;             // row of the 16 x N fragments this lane holds = query head
+  const int qcol = (lane & 3) * 2;        // first of its two columns inside an 8-wide tile
+  float m_run = -INFINITY, l_run = 0.f;
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
-  float qv[G][16];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + (long)b * q_stride + (long)(h0 + g) * D;
-    unpack8(*reinterpret_cast<const uint4*>(qp + sub * 8), &qv[g][0]);
-    unpack8(*reinterpret_cast<const uint4*>(qp + 64 + sub * 8), &qv[g][8]);
-  }
-  float m[G], l[G], acc[G][16];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
-  }
-
-  bool ok = true;
-  for (int pg = p_begin; pg < p_end; ++pg) {
-    const int it = pg - p_begin;
-    const int st = it % kTStages;
-    ok = mbar_wait(&full[st], (uint32_t)((it / kTStages) & 1), dead, status, 960);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) break;
-    const uint32_t kbase = smem_u32(smem + st * kTStageBytes) + tok * (D * 2) + sub * 16;
-    const uint32_t vbase = kbase + kTPage * D * 2;
-    uint4 k0, k1, v0, v1;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k0.x), "=r"(k0.y), "=r"(k0.z), "=r"(k0.w) : "r"(kbase));
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(k1.x), "=r"(k1.y), "=r"(k1.z), "=r"(k1.w) : "r"(kbase + 128));
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0.x), "=r"(v0.y), "=r"(v0.z), "=r"(v0.w) : "r"(vbase));
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1.x), "=r"(v1.y), "=r"(v1.z), "=r"(v1.w) : "r"(vbase + 128));
-    // the stage can be refilled as soon as every warp has its registers
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);
-    if (threadIdx.x == 0 && pg + kTStages < p_end) {
-      if (mbar_wait(&empty[st], (uint32_t)((it / kTStages) & 1), dead, status, 961)) issue(pg + kTStages);
-    }
-    const bool valid = pg * kTPage + tok < ctx;
-    float kf[16], vf[16];
-    unpack8(k0, kf); unpack8(k1, kf + 8);
-    unpack8(v0, vf); unpack8(v1, vf + 8);
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float sc = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) sc += qv[g][i] * kf[i];
-      sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-      sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-      sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-      if (valid) {
-        sc *= scale_log2;
-        const float mn = fmaxf(m[g], sc);
-        const float alpha = exp2f(m[g] - mn), pe = exp2f(sc - mn);
-        l[g] = l[g] * alpha + pe;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[g][i] = acc[g][i] * alpha + pe * vf[i];
-        m[g] = mn;
+  if (warp == kMWarps) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (int pg = p_begin; pg < p_end; ++pg) {
+        const int it = pg - p_begin, st = it % kMStages;
+        if (!mbar_wait(&empty[st], (uint32_t)(((it / kMStages) & 1) ^ 1), dead, status, 970)) break;
+        const int page = block_table[b * max_pages + pg];
+        uint8_t* dst = smem + st * kMStageBytes;
+        mbar_expect_tx(&full[st], kMStageBytes);
+        tma_load_2d(dst, &map_k, &full[st], hk * D, page * kTPage);
+        tma_load_2d(dst + kMHalf, &map_k, &full[st], hk * D + 64, page * kTPage);
+        tma_load_2d(dst + 2 * kMHalf, &map_v, &full[st], hk * D, page * kTPage);
+        tma_load_2d(dst + 3 * kMHalf, &map_v, &full[st], hk * D + 64, page * kTPage);
       }
     }
-  }
-  // merge: the four token groups of a warp with shuffles, the warps through shared memory
+  } else {
+    // ---------------------------------------------------------------- consumers
+    // Q as the A operand: rows = heads (rows >= G are zero), 8 k-steps of 16 dims
+    uint32_t qa[8][2];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float M = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], 8));
-    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
-    const float w = m[g] == -INFINITY ? 0.f : exp2f(m[g] - M);
-    float L = l[g] * w;
-    L += __shfl_xor_sync(0xffffffffu, L, 8);
-    L += __shfl_xor_sync(0xffffffffu, L, 16);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float a = acc[g][i] * w;
-      a += __shfl_xor_sync(0xffffffffu, a, 8);
-      a += __shfl_xor_sync(0xffffffffu, a, 16);
-      if (lane < 8) sO[(warp * G + g) * D + (i < 8 ? sub * 8 + i : 64 + sub * 8 + (i - 8))] = a;
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = qa[ks][1] = 0u;
+      if (grow < G) {
+        const __nv_bfloat16* qp = q + (long)b * q_stride + (long)(h0 + grow) * D + ks * 16 + qcol;
+        qa[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+        qa[ks][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
     }
-    if (lane == 0) { sM[g * kTWarps + warp] = M; sL[g * kTWarps + warp] = L; }
+    const int lm = lane >> 3, lr = lane & 7;      // ldmatrix: this lane addresses row lr of matrix lm
+    bool ok = true;
+    for (int pg = p_begin + warp; pg < p_end; pg += kMWarps) {
+      const int it = pg - p_begin, st = it % kMStages;
+      ok = mbar_wait(&full[st], (uint32_t)((it / kMStages) & 1), dead, status, 971);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const uint32_t sK = smem_u32(smem + st * kMStageBytes);
+      const uint32_t sV = sK + 2 * kMHalf;
+      // ---- S = Q K^T : two 8-token tiles
+      float sc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        const int tok = nt * 8 + lr;
+#pragma unroll
+        for (int kp = 0; kp < 4; ++kp) {            // two k-steps per ldmatrix.x4
+          const int c = kp * 4 + lm;                // 16-byte chunk (8 dims) of the 128-dim row
+          const uint32_t addr = sK + (c >> 3) * kMHalf + tok * 128 + (((c & 7) ^ (tok & 7)) << 4);
+          uint32_t kb[4];
+          ldmatrix_x4(addr, kb);
+          mma_bf16_16816(sc[nt], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, kb[0], kb[1]);
+          mma_bf16_16816(sc[nt], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, kb[2], kb[3]);
+        }
+      }
+      // ---- online softmax of row `grow` (its 16 scores live in the four lanes of a quad)
+      float sv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = pg * kTPage + (j >> 1) * 8 + qcol + (j & 1);
+        sv[j] = t < ctx ? sc[j >> 1][j & 1] * scale_log2 : -INFINITY;
+      }
+      float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_new);
+      float pv[4], ps = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { pv[j] = m_new == -INFINITY ? 0.f : exp2f(sv[j] - m_new); ps += pv[j]; }
+      ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+      l_run = l_run * alpha + ps;
+      m_run = m_new;
+      const uint32_t pa0 = pack_bf16x2(pv[0], pv[1]), pa2 = pack_bf16x2(pv[2], pv[3]);
+      // ---- O = alpha * O + P V : sixteen 8-dim tiles, two per ldmatrix.x4.trans
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        o[2 * np][0] *= alpha; o[2 * np][1] *= alpha;
+        o[2 * np + 1][0] *= alpha; o[2 * np + 1][1] *= alpha;
+        const int tok = (lm & 1) * 8 + lr;
+        const int c = np * 2 + (lm >> 1);
+        const uint32_t addr = sV + (c >> 3) * kMHalf + tok * 128 + (((c & 7) ^ (tok & 7)) << 4);
+        uint32_t vb[4];
+        ldmatrix_x4_trans(addr, vb);
+        mma_bf16_16816(o[2 * np], pa0, 0u, pa2, 0u, vb[0], vb[1]);
+        mma_bf16_16816(o[2 * np + 1], pa0, 0u, pa2, 0u, vb[2], vb[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+    }
+    // per-warp state to shared memory: row grow < G; lane holds dims nt*8 + qcol + {0,1}
+    if (grow < G) {
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        sO[(warp * G + grow) * D + nt * 8 + qcol] = o[nt][0];
+        sO[(warp * G + grow) * D + nt * 8 + qcol + 1] = o[nt][1];
+      }
+      if ((lane & 3) == 0) { sM[grow * kMWarps + warp] = m_run; sL[grow * kMWarps + warp] = l_run; }
+    }
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, d = idx % D;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kTWarps; ++w) M = fmaxf(M, sM[g * kTWarps + w]);
+    for (int w = 0; w < kMWarps; ++w) M = fmaxf(M, sM[g * kMWarps + w]);
     float L = 0.f, O = 0.f;
 #pragma unroll
-    for (int w = 0; w < kTWarps; ++w) {
-      const float f = sM[g * kTWarps + w] == -INFINITY ? 0.f : exp2f(sM[g * kTWarps + w] - M);
-      L += sL[g * kTWarps + w] * f;
+    for (int w = 0; w < kMWarps; ++w) {
+      const float f = sM[g * kMWarps + w] == -INFINITY ? 0.f : exp2f(sM[g * kMWarps + w] - M);
+      L += sL[g * kMWarps + w] * f;
       O += sO[(w * G + g) * D + d] * f;
     }
     if (S == 1) {
@@ -325,19 +360,19 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 }
 
 template <int G>
-int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, void* out, float* ws, const int* block_table,
+int launch_mma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, void* out, float* ws, const int* block_table,
                const int* ctx_lens, dim3 grid, int Hq, int Hkv, int max_pages, float sl2, long q_stride, long o_stride,
                int* status, cudaStream_t stream) {
-  const int smem = 128 + kTStages * kTStageBytes + 2 * kTStages * 8 + 16 + (2 * kMaxG * kTWarps + kTWarps * G * D) * 4;
-  auto k = paged_decode_tma_kernel<G>;
+  const int smem = 1024 + kMStages * kMStageBytes + 2 * kMStages * 8 + 16 + (2 * kMaxG * kMWarps + kMWarps * G * D) * 4;
+  auto k = paged_decode_mma_kernel<G>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  k<<<grid, kTWarps * 32, smem, stream>>>(mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, ws, block_table, ctx_lens, Hq,
-                                          Hkv, max_pages, sl2, q_stride, o_stride, status);
+  k<<<grid, (kMWarps + 1) * 32, smem, stream>>>(mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, ws, block_table,
+                                                ctx_lens, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status);
   return (int)cudaGetLastError();
 }
 
@@ -375,7 +410,7 @@ AX_API int ax_paged_kv_write(const void* k, const void* v, void* kc, void* vc, c
 
 // q [B, Hq, 128], out [B, Hq, 128] bf16 (row strides in elements); Hq/Hkv in {1, 2, 4, 8}.
 // splits > 1 needs `workspace` of B * Hq * splits * 130 floats.  With page_size 16, `num_pages` (pages in the
-// cache tensors) and a status word given, the TMA-staged kernel runs; otherwise the register-resident one.
+// cache tensors) and a status word given, the tensor-core kernel runs; otherwise the register-resident one.
 AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* vc, void* out,
                                      const int* block_table, const int* ctx_lens, int B, int Hq, int Hkv,
                                      int Dh, int page_size, int max_pages, float scale, long q_stride,
@@ -390,19 +425,19 @@ AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* 
     CUtensorMap mk, mv;
     uint64_t dims[2] = {(uint64_t)Hkv * D, (uint64_t)num_pages * page_size};
     uint64_t strides[1] = {(uint64_t)Hkv * D * 2};
-    uint32_t box[2] = {(uint32_t)D, (uint32_t)kTPage};
+    uint32_t box[2] = {64, (uint32_t)kTPage};
     int rc = axh::encode_tensor_map(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kc, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return 1000 + rc;
     rc = axh::encode_tensor_map(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, vc, dims, strides, box,
-                                CU_TENSOR_MAP_SWIZZLE_NONE);
+                                CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return 1100 + rc;
     int e;
     switch (G) {
-      case 1: e = launch_tma<1>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
-      case 2: e = launch_tma<2>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
-      case 4: e = launch_tma<4>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
-      case 8: e = launch_tma<8>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 1: e = launch_mma<1>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 2: e = launch_mma<2>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 4: e = launch_mma<4>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
+      case 8: e = launch_mma<8>(mk, mv, q, out, workspace, block_table, ctx_lens, grid, Hq, Hkv, max_pages, sl2, q_stride, o_stride, status, stream); break;
       default: return -2;
     }
     if (e) return e;
