@@ -139,6 +139,9 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, 0, 0);
+      // descriptors of stage 0, advanced per stage and k step (keeps the issuing thread short)
+      const uint64_t da0 = umma_desc_sw128(smem_u32(stage_base), 16, 1024);
+      const uint64_t db0 = umma_desc_sw128(smem_u32(stage_base) + C::kStageA, 16, 1024);
       int s = 0, it = 0;
       uint32_t ph = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
@@ -149,12 +152,11 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, dead, p.status, 911)) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(stage_base + s * C::kStage);
-          const uint32_t sb = sa + C::kStageA;
+          const uint64_t soff = (uint64_t)((uint32_t)(s * C::kStage) >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_f16_ss(d_tmem, umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024),
-                        umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, da0 + soff + (uint64_t)(k * ((UMMA_K * 2) >> 4)), db0 + soff + (uint64_t)(k * ((UMMA_K * 2) >> 4)),
+                        idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }

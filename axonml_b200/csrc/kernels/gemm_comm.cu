@@ -243,6 +243,13 @@ __device__ __forceinline__ void finish_call(const CommParams& p) {
   }
 }
 
+// RS staging buffer of a rank: [source rank][128-row block][64-column chunk][epilogue warp] pieces
+// of 4 KB, each the shared-memory image (128-byte swizzle) of a 32 x 64 bf16 sub-tile.
+__device__ __forceinline__ long stage_off(const CommParams& p, const TileMap& tm, int src, int mb, int chunk, int ew) {
+  const int nchunks = (p.N + 63) >> 6;
+  return ((((long)src * tm.mbs + mb) * nchunks + chunk) * kEpiWarps + ew) * (long)kStageBufBytes;
+}
+
 struct DstMaps { CUtensorMap m[kMaxRanks]; };     // RS: every rank's staging buffer as [world*Tl, N]
 
 template <int BN, int MODE>
@@ -334,6 +341,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, 0, 0);
+      // descriptors of stage 0, advanced per stage and k step (keeps the issuing thread short)
+      const uint64_t da0 = umma_desc_sw128(smem_u32(stage_base), 16, 1024);
+      const uint64_t db0 = umma_desc_sw128(smem_u32(stage_base) + C::kStageA, 16, 1024);
       int s = 0, it = 0;
       uint32_t ph = 0;
       for (int t = cta; t < num_tiles; t += ncta, ++it) {
@@ -344,12 +354,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, dead, p.status, 821)) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(stage_base + s * C::kStage);
-          const uint32_t sb = sa + C::kStageA;
+          const uint64_t soff = (uint64_t)((uint32_t)(s * C::kStage) >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_f16_ss(d_tmem, umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024),
-                        umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, da0 + soff + (uint64_t)(k * ((UMMA_K * 2) >> 4)), db0 + soff + (uint64_t)(k * ((UMMA_K * 2) >> 4)),
+                        idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
@@ -432,7 +441,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           buf ^= 1;
         } else if (shard != p.rank) {
           // partial tile -> staging slot `rank` on the rank that owns these rows: the warp's
-          // 32 x 64 sub-tile is staged in shared memory and sent with one tensor bulk store.
+          // 32 x 64 sub-tile is staged in shared memory and sent as one contiguous 4 KB bulk
+          // store (the staging buffer is tile-ordered; row-strided 128-byte writes over NVLink
+          // ran at a third of the rate)
           uint8_t* dst = stg + buf * kStageBufBytes;
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
@@ -448,7 +459,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&dst_maps.m[shard], dst, ncol0, p.rank * p.Tl + mb * BM + q * 32);
+            bulk_store_1d(p.sym[shard] + stage_off(p, tm, p.rank, mb, ncol0 >> 6, ew), dst, kStageBufBytes);
             tma_store_commit();
           }
           buf ^= 1;
@@ -473,13 +484,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ok = __all_sync(0xffffffffu, w_ok);
           }
           if (ok) {
-            const long row_off = ((long)(mb * BM + q * 32 + lane) * p.N + ncol0) * 2;
             for (int src = 0; src < p.world; ++src) {
               if (src == p.rank) continue;
-              const uint8_t* sp = p.sym[p.rank] + (long)src * p.Tl * p.N * 2 + row_off;
+              // the staged piece keeps the shared-memory image: row `lane`, 16-byte chunks swizzled
+              const uint8_t* sp = p.sym[p.rank] + stage_off(p, tm, src, mb, ncol0 >> 6, ew) + lane * 128;
               uint4 u[8];
 #pragma unroll
-              for (int c = 0; c < 8; ++c) u[c] = ld_peer_v4(sp + c * 16);
+              for (int c = 0; c < 8; ++c) u[c] = ld_peer_v4(sp + ((c ^ (lane & 7)) << 4));
 #pragma unroll
               for (int c = 0; c < 8; ++c) {
                 const float2 x0 = unpack_bf16x2(u[c].x), x1 = unpack_bf16x2(u[c].y), x2 = unpack_bf16x2(u[c].z),

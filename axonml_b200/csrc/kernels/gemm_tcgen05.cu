@@ -147,7 +147,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // One thread feeds the tensor core, so its instruction stream sits on the critical path:
+      // the shared-memory descriptors of stage 0 are built once and every MMA only adds the
+      // (16-byte-unit) offset of its stage and k step to them.
       constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, A_MN, B_MN);
+      const uint32_t sa0 = smem_u32(stage_base);
+      const uint64_t da0 = A_MN ? umma_desc_sw128(sa0, BK * 128, 1024) : umma_desc_sw128(sa0, 16, 1024);
+      const uint64_t db0 = B_MN ? umma_desc_sw128(sa0 + C::kStageA, BK * 128, 1024)
+                                : umma_desc_sw128(sa0 + C::kStageA, 16, 1024);
+      constexpr uint32_t kStepA = (A_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
+      constexpr uint32_t kStepB = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -157,18 +166,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, dead, p.status, 200)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accum = 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, dead, p.status, 201)) break;
           tc_fence_after();
-          const uint32_t sa = smem_u32(stage_base + s * C::kStage);
-          const uint32_t sb = sa + C::kStageA;
+          const uint64_t soff = (uint64_t)((uint32_t)(s * C::kStage) >> 4);
+          const uint64_t da = da0 + soff, db = db0 + soff;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t da = A_MN ? umma_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024)
-                               : umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
-            uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
-                               : umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
-            umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, da + (uint64_t)(k * kStepA), db + (uint64_t)(k * kStepB), idesc, accum);
+            accum = 1;
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
           if (++s == C::kStages) { s = 0; ph ^= 1; }
