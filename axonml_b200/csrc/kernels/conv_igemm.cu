@@ -199,26 +199,18 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         const int co0 = c0 + ch * 64;
         if (co0 >= p.Cout) continue;
-        if (p.bias_kind != 0) {
-#pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const int n = co0 + j;
-            float b = 0.f;
-            if (n < p.Cout)
-              b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n) : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
-            r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
-          }
-        }
+        add_bias_chunk(r, p.bias, p.bias_kind, co0, p.Cout);
+        apply_act_chunk(r, p.act);
         uint8_t* dst = stg + buf * kStageBufBytes;
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 o;
-          o.x = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 0]), p.act), apply_act(__uint_as_float(r[c * 8 + 1]), p.act));
-          o.y = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 2]), p.act), apply_act(__uint_as_float(r[c * 8 + 3]), p.act));
-          o.z = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 4]), p.act), apply_act(__uint_as_float(r[c * 8 + 5]), p.act));
-          o.w = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 6]), p.act), apply_act(__uint_as_float(r[c * 8 + 7]), p.act));
+          o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
+          o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+          o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+          o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
           *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
         }
         fence_proxy_async_smem();

@@ -60,7 +60,15 @@ struct CommParams {
   int pushers;               // AG: CTAs that only copy
   int max_tiles;             // flags per source rank
   int* status;
+  unsigned long long* trace; // optional timeline [grid][kTraceSlots] of globaltimer stamps, or null
 };
+
+// Timeline slots per CTA: 0 kernel start, 1 start-of-call wait done, then four per tile
+// (accumulator ready, peers' flags seen, epilogue done, MMA issued), 62 epilogue loop done, 63 end.
+constexpr int kTraceSlots = 64;
+__device__ __forceinline__ void trace_at(const CommParams& p, int slot) {
+  if (p.trace != nullptr && slot < kTraceSlots) p.trace[(long)blockIdx.x * kTraceSlots + slot] = globaltimer_ns();
+}
 
 template <int BN>
 struct Cfg {
@@ -292,6 +300,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t* my_flags = p.sig[p.rank] + kSigFlags;
 
   if (threadIdx.x == 0) {
+    trace_at(p, 0);
     *dead = 0;
     for (int i = 0; i < C::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], kEpiWarps); }
@@ -363,6 +372,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
         umma_commit(&tfull_bar[acc]);
+        trace_at(p, 2 + 4 * it + 3);
         if (*dead) break;
       }
     }
@@ -373,7 +383,20 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
     int buf = 0, it = 0;
     bool ok = true;
-    uint32_t* prev_flag = nullptr;      // lane 0: flag of the tile whose stores are still in flight
+    // lane 0: remote tiles [pend_first, pend_first + pend_n * ncta) of ring phase `pend_shard` whose
+    // flags are still owed.  A completion wait on stores to a peer costs a round trip under load,
+    // so flags go out once per ring phase (the owner needs them only for its own rows, which it
+    // computes last), one tile into the next phase so that the wait overlaps that tile's work.
+    int pend_first = 0, pend_n = 0, pend_shard = -1;
+    auto release_flags = [&](int first, int n) {
+      fence_proxy_async_global();
+      __threadfence_system();
+      for (int i = 0; i < n; ++i) {
+        int rp, sh, mb2, nb2;
+        tm.coords(first + i * ncta, rp, sh, mb2, nb2);
+        st_release_sys(p.sig[sh] + kSigFlags + ((p.rank * p.max_tiles + mb2 * tm.num_n + nb2) * kFlagsPerTile + ew), p.epoch);
+      }
+    };
     if (MODE == MODE_RS) {
       // peers must have consumed the previous call before their staging slots are overwritten
       // (every warp checks for itself: no barrier that a timed-out warp could leave hanging)
@@ -382,6 +405,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       ok = __all_sync(0xffffffffu, w_ok);
       if (!ok) *dead = 1;      // the producer and MMA warps stop at their next wait
     }
+    if (ew == 0 && lane == 0) trace_at(p, 1);
     for (int t = cta; t < num_tiles && ok; t += ncta, ++it) {
       int ring_pos, shard, mb, nb;
       tm.coords(t, ring_pos, shard, mb, nb);
@@ -391,6 +415,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (ew == 0 && lane == 0) trace_at(p, 2 + 4 * it);
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 64; ++ch) {
@@ -410,26 +435,18 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int ncol0 = n0 + ch * 64;
         if (ncol0 >= p.N) continue;
         if (MODE == MODE_AG) {
-          if (p.bias_kind != 0) {
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              const int n = ncol0 + j;
-              float b = 0.f;
-              if (n < p.N)
-                b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n) : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
-              r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
-            }
-          }
+          add_bias_chunk(r, p.bias, p.bias_kind, ncol0, p.N);
+          apply_act_chunk(r, p.act);
           uint8_t* dst = stg + buf * kStageBufBytes;
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             uint4 o;
-            o.x = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 0]), p.act), apply_act(__uint_as_float(r[c * 8 + 1]), p.act));
-            o.y = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 2]), p.act), apply_act(__uint_as_float(r[c * 8 + 3]), p.act));
-            o.z = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 4]), p.act), apply_act(__uint_as_float(r[c * 8 + 5]), p.act));
-            o.w = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 6]), p.act), apply_act(__uint_as_float(r[c * 8 + 7]), p.act));
+            o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
             *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
           }
           fence_proxy_async_smem();
@@ -469,12 +486,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (ch == 0) {
             // the flag still owed for the last remote tile must go out first: the peers' own-row
             // tiles wait for it exactly as this one waits for theirs
-            if (lane == 0 && prev_flag != nullptr) {
+            if (lane == 0 && pend_n > 0) {
               tma_store_wait<0>();
-              fence_proxy_async_global();
-              __threadfence_system();
-              st_release_sys(prev_flag, p.epoch);
-              prev_flag = nullptr;
+              release_flags(pend_first, pend_n);
+              pend_n = 0;
             }
             __syncwarp();
             bool w_ok = true;       // lane l: the same quarter of this tile as sent by rank l
@@ -482,47 +497,56 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               w_ok = wait_ge<true>(my_flags + ((lane * p.max_tiles + mb * tm.num_n + nb) * kFlagsPerTile + ew), p.epoch,
                                    p.status, 840);
             ok = __all_sync(0xffffffffu, w_ok);
+            if (ew == 0 && lane == 0) trace_at(p, 2 + 4 * it + 1);
           }
           if (ok) {
-            for (int src = 0; src < p.world; ++src) {
-              if (src == p.rank) continue;
+            // two peers' pieces per round: sixteen 16-byte loads in flight per lane, so the W-1
+            // dependent round trips to memory become (W-1)/2
+            for (int j = 1; j < p.world; j += 2) {
+              const int s0 = (p.rank + j) % p.world;
+              const bool two = j + 1 < p.world;
+              const int s1 = two ? (p.rank + j + 1) % p.world : s0;
               // the staged piece keeps the shared-memory image: row `lane`, 16-byte chunks swizzled
-              const uint8_t* sp = p.sym[p.rank] + stage_off(p, tm, src, mb, ncol0 >> 6, ew) + lane * 128;
-              uint4 u[8];
+              const uint8_t* sp0 = p.sym[p.rank] + stage_off(p, tm, s0, mb, ncol0 >> 6, ew) + lane * 128;
+              const uint8_t* sp1 = p.sym[p.rank] + stage_off(p, tm, s1, mb, ncol0 >> 6, ew) + lane * 128;
+              uint4 u[8], v[8];
 #pragma unroll
-              for (int c = 0; c < 8; ++c) u[c] = ld_peer_v4(sp + ((c ^ (lane & 7)) << 4));
+              for (int c = 0; c < 8; ++c) u[c] = ld_peer_v4(sp0 + ((c ^ (lane & 7)) << 4));
+              if (two) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = ld_peer_v4(sp1 + ((c ^ (lane & 7)) << 4));
+              } else {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = make_uint4(0u, 0u, 0u, 0u);
+              }
 #pragma unroll
               for (int c = 0; c < 8; ++c) {
                 const float2 x0 = unpack_bf16x2(u[c].x), x1 = unpack_bf16x2(u[c].y), x2 = unpack_bf16x2(u[c].z),
                              x3 = unpack_bf16x2(u[c].w);
-                r[c * 8 + 0] = __float_as_uint(__uint_as_float(r[c * 8 + 0]) + x0.x);
-                r[c * 8 + 1] = __float_as_uint(__uint_as_float(r[c * 8 + 1]) + x0.y);
-                r[c * 8 + 2] = __float_as_uint(__uint_as_float(r[c * 8 + 2]) + x1.x);
-                r[c * 8 + 3] = __float_as_uint(__uint_as_float(r[c * 8 + 3]) + x1.y);
-                r[c * 8 + 4] = __float_as_uint(__uint_as_float(r[c * 8 + 4]) + x2.x);
-                r[c * 8 + 5] = __float_as_uint(__uint_as_float(r[c * 8 + 5]) + x2.y);
-                r[c * 8 + 6] = __float_as_uint(__uint_as_float(r[c * 8 + 6]) + x3.x);
-                r[c * 8 + 7] = __float_as_uint(__uint_as_float(r[c * 8 + 7]) + x3.y);
+                const float2 y0 = unpack_bf16x2(v[c].x), y1 = unpack_bf16x2(v[c].y), y2 = unpack_bf16x2(v[c].z),
+                             y3 = unpack_bf16x2(v[c].w);
+                r[c * 8 + 0] = __float_as_uint(__uint_as_float(r[c * 8 + 0]) + (x0.x + y0.x));
+                r[c * 8 + 1] = __float_as_uint(__uint_as_float(r[c * 8 + 1]) + (x0.y + y0.y));
+                r[c * 8 + 2] = __float_as_uint(__uint_as_float(r[c * 8 + 2]) + (x1.x + y1.x));
+                r[c * 8 + 3] = __float_as_uint(__uint_as_float(r[c * 8 + 3]) + (x1.y + y1.y));
+                r[c * 8 + 4] = __float_as_uint(__uint_as_float(r[c * 8 + 4]) + (x2.x + y2.x));
+                r[c * 8 + 5] = __float_as_uint(__uint_as_float(r[c * 8 + 5]) + (x2.y + y2.y));
+                r[c * 8 + 6] = __float_as_uint(__uint_as_float(r[c * 8 + 6]) + (x3.x + y3.x));
+                r[c * 8 + 7] = __float_as_uint(__uint_as_float(r[c * 8 + 7]) + (x3.y + y3.y));
               }
             }
-            if (p.bias_kind != 0) {
-#pragma unroll
-              for (int j = 0; j < 64; ++j) {
-                const int n = ncol0 + j;
-                const float b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n) : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
-                r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
-              }
-            }
+            add_bias_chunk(r, p.bias, p.bias_kind, ncol0, p.N);
+            apply_act_chunk(r, p.act);
             uint8_t* dst = stg + buf * kStageBufBytes;
             if (lane == 0) tma_store_wait_read<1>();
             __syncwarp();
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
               uint4 o;
-              o.x = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 0]), p.act), apply_act(__uint_as_float(r[c * 8 + 1]), p.act));
-              o.y = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 2]), p.act), apply_act(__uint_as_float(r[c * 8 + 3]), p.act));
-              o.z = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 4]), p.act), apply_act(__uint_as_float(r[c * 8 + 5]), p.act));
-              o.w = pack_bf16x2(apply_act(__uint_as_float(r[c * 8 + 6]), p.act), apply_act(__uint_as_float(r[c * 8 + 7]), p.act));
+              o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
               *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
             }
             fence_proxy_async_smem();
@@ -535,28 +559,26 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
       }
+      if (ew == 0 && lane == 0) trace_at(p, 2 + 4 * it + 2);
       if (MODE == MODE_RS && shard != p.rank) {
-        // Flags are one tile late: waiting for the previous tile's stores to complete (a round
-        // trip over NVLink) then overlaps this tile's work instead of stalling after every tile.
         if (lane == 0) {
-          if (prev_flag != nullptr) {
-            tma_store_wait<BN / 64>();          // all but this tile's groups have completed
-            fence_proxy_async_global();
-            __threadfence_system();
-            st_release_sys(prev_flag, p.epoch);
+          if (pend_n > 0 && pend_shard != shard) {
+            tma_store_wait<BN / 64>();          // all but this tile's groups: the last phase has landed
+            release_flags(pend_first, pend_n);
+            pend_n = 0;
           }
-          prev_flag = p.sig[shard] + kSigFlags + ((p.rank * p.max_tiles + mb * tm.num_n + nb) * kFlagsPerTile + ew);
+          if (pend_n == 0) { pend_first = t; pend_shard = shard; }
+          ++pend_n;
         }
         __syncwarp();
       }
     }
-    if (MODE == MODE_RS && lane == 0 && prev_flag != nullptr) {
+    if (MODE == MODE_RS && lane == 0 && pend_n > 0) {
       tma_store_wait<0>();
-      fence_proxy_async_global();
-      __threadfence_system();
-      st_release_sys(prev_flag, p.epoch);
+      release_flags(pend_first, pend_n);
     }
     __syncwarp();
+    if (ew == 0 && lane == 0) trace_at(p, 62);
     if (lane == 0) tma_store_wait<0>();
   }
 
@@ -564,6 +586,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc<C::kTmemCols>(tmem_base);
+  if (threadIdx.x == 0) trace_at(p, 63);
   finish_call(p);
 }
 
@@ -602,6 +625,11 @@ AX_API int ax_gemm_comm_signal_slots(int max_tiles) { return kSigFlags + kMaxRan
 //         `x_local` = x.
 // `grid` must be the same for every call on one communicator (the end-of-call counter relies on it)
 // and must not exceed the SM count.  Requires Tl % 128 == 0, K % 64 == 0, N % 64 == 0.
+// Diagnostic timeline: the launches that follow write globaltimer stamps of their phases into
+// `buf` ([grid][64] 64-bit slots, zero-filled by the caller); null turns it off again.
+static unsigned long long* g_trace_buf = nullptr;
+AX_API void ax_gemm_comm_set_trace(void* buf) { g_trace_buf = (unsigned long long*)buf; }
+
 AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out, void* const* sym, void* sym_mc,
                         void* const* sig, const void* bias, int bias_kind, int act, int Tl, int N, int K,
                         int rank, int world, unsigned epoch, int max_tiles, int pushers, int grid, int* status,
@@ -625,6 +653,7 @@ AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out,
   p.pushers = mode == MODE_AG ? pushers : 0;
   p.max_tiles = max_tiles;
   p.status = status;
+  p.trace = g_trace_buf;
   CUtensorMap ma, mal, mb, mc;
   int rc;
   if (mode == MODE_AG) {

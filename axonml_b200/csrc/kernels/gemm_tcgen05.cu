@@ -220,37 +220,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         const int ncol0 = n0 + ch * 64;
         if (ncol0 >= p.N) continue;  // fully out-of-range chunk (warp-uniform)
-        if (p.bias_kind != 0) {
-#pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            int n = ncol0 + j;
-            float b = 0.f;
-            if (n < p.N)
-              b = p.bias_kind == 1 ? __ldg((const float*)p.bias + n)
-                                   : __bfloat162float(((const __nv_bfloat16*)p.bias)[n]);
-            r[j] = __float_as_uint(__uint_as_float(r[j]) + b);
-          }
-        }
+        add_bias_chunk(r, p.bias, p.bias_kind, ncol0, p.N);
         const int passes = p.has_aux ? 2 : 1;
         for (int pass = 0; pass < passes; ++pass) {
           const bool is_aux = p.has_aux && pass == 0;
+          if (!is_aux) apply_act_chunk(r, p.act);      // the aux output keeps the pre-activation values
           uint8_t* dst = stg + buf * kStageBufBytes;
           // the bulk store that last read this buffer must have finished reading it
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float x = __uint_as_float(r[c * 8 + j]);
-              v[j] = is_aux ? x : apply_act(x, p.act);
-            }
             uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]);
-            o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]);
-            o.w = pack_bf16x2(v[6], v[7]);
+            o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
             *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
           }
           fence_proxy_async_smem();

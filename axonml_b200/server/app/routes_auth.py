@@ -1,0 +1,180 @@
+"""Authentication and administration routes (crates/axonml-server/src/api/auth.rs; route table
+api/mod.rs:111-146, 342-350): register, login (with the MFA hand-off token), logout, refresh, me,
+TOTP setup / enable / verify, recovery codes, MFA disable, user administration, admin query."""
+from __future__ import annotations
+
+from . import auth as A
+from .api import ADMIN, PUBLIC, USER, HttpError
+from .store import now_iso
+
+
+def register(app) -> None:
+    r = app.router
+
+    def _login_response(u: dict, mfa_verified: bool) -> dict:
+        app.users.update(u["id"], {"last_login": now_iso()})
+        pair = app.jwt.create_token_pair(u["id"], u["email"], u["role"], mfa_verified)
+        return {**pair, "user": app.public_user(u), "requires_mfa": False}
+
+    def auth_register(req):
+        if not app.allow_registration:
+            raise HttpError(403, "registration is disabled")
+        email, name, password = req.need("email", "name", "password")
+        if "@" not in email or len(password) < 8:
+            raise HttpError(400, "a valid e-mail address and a password of at least 8 characters are required")
+        role = "admin" if app.users.count() == 0 else "user"      # the first account administers the server
+        u = app.create_user(email, name, password, role)
+        return 201, {"user": app.public_user(u), "message": "registered"}
+
+    def auth_login(req):
+        email, password = req.need("email", "password")
+        u = app.users.find_one(email=email.lower())
+        if u is None or not A.verify_password(password, u["password_hash"]):
+            raise HttpError(401, "invalid e-mail or password")
+        if not u.get("approved", True):
+            raise HttpError(403, "account not approved yet")
+        if u.get("mfa_enabled"):
+            return {"requires_mfa": True, "mfa_methods": ["totp", "recovery"], **app.jwt.create_mfa_token(u["id"], u["email"])}
+        return _login_response(u, False)
+
+    def _mfa_user(req) -> dict:
+        (tok,) = req.need("mfa_token")
+        c = app.jwt.validate_mfa_token(tok)
+        return app.users.get(c.sub)
+
+    def mfa_totp_verify(req):
+        u = _mfa_user(req)
+        (code,) = req.need("code")
+        if not u.get("totp_secret") or not app.totp.verify(u["totp_secret"], str(code)):
+            raise HttpError(401, "invalid code")
+        return _login_response(u, True)
+
+    def mfa_recovery_use(req):
+        u = _mfa_user(req)
+        (code,) = req.need("code")
+        i = A.RecoveryAuth.verify_code(str(code), u.get("recovery_codes") or [])
+        if i is None:
+            raise HttpError(401, "invalid recovery code")
+        left = list(u["recovery_codes"])
+        del left[i]                                  # a recovery code works once
+        app.users.update(u["id"], {"recovery_codes": left})
+        out = _login_response(u, True)
+        out["recovery_codes_left"] = len(left)
+        return out
+
+    def auth_logout(req):
+        tok = A.JwtAuth.extract_from_header(req.headers.get("Authorization"))
+        if tok:
+            app.revoked.add(tok)
+        return {"message": "logged out"}
+
+    def auth_refresh(req):
+        (tok,) = req.need("refresh_token")
+        c = app.jwt.validate_refresh_token(tok)
+        u = app.users.get(c.sub)                     # a deleted user cannot refresh
+        return app.jwt.create_token_pair(u["id"], u["email"], u["role"])
+
+    def auth_me(req):
+        return app.public_user(app.users.get(req.user_id))
+
+    def totp_setup(req):
+        u = app.users.get(req.user_id)
+        s = app.totp.setup(u["email"])
+        app.users.update(u["id"], {"pending_totp_secret": s["secret"]})
+        return s
+
+    def totp_enable(req):
+        u = app.users.get(req.user_id)
+        (code,) = req.need("code")
+        secret = u.get("pending_totp_secret")
+        if not secret or not app.totp.verify(secret, str(code)):
+            raise HttpError(400, "code does not match the pending secret")
+        rc = A.RecoveryAuth.generate_codes(10)
+        app.users.update(u["id"], {"totp_secret": secret, "pending_totp_secret": None, "mfa_enabled": True,
+                                   "recovery_codes": rc["hashed_codes"]})
+        return {"mfa_enabled": True, "recovery_codes": rc["codes"]}
+
+    def recovery_generate(req):
+        rc = A.RecoveryAuth.generate_codes(10)
+        app.users.update(req.user_id, {"recovery_codes": rc["hashed_codes"]})
+        return {"recovery_codes": rc["codes"]}
+
+    def recovery_status(req):
+        return {"remaining": len(app.users.get(req.user_id).get("recovery_codes") or [])}
+
+    def mfa_disable(req):
+        u = app.users.get(req.user_id)
+        (password,) = req.need("password")
+        if not A.verify_password(password, u["password_hash"]):
+            raise HttpError(401, "wrong password")
+        app.users.update(u["id"], {"mfa_enabled": False, "totp_secret": None, "pending_totp_secret": None,
+                                   "recovery_codes": []})
+        return {"mfa_enabled": False}
+
+    def webauthn_unavailable(req):
+        raise HttpError(501, "WebAuthn needs a browser authenticator; use TOTP")
+
+    r.add("POST", "/api/auth/register", auth_register, PUBLIC)
+    r.add("POST", "/api/auth/login", auth_login, PUBLIC)
+    r.add("POST", "/api/auth/mfa/totp/verify", mfa_totp_verify, PUBLIC)
+    r.add("POST", "/api/auth/mfa/recovery", mfa_recovery_use, PUBLIC)
+    r.add("POST", "/api/auth/mfa/webauthn/authenticate/start", webauthn_unavailable, PUBLIC)
+    r.add("POST", "/api/auth/mfa/webauthn/authenticate/finish", webauthn_unavailable, PUBLIC)
+    r.add("POST", "/api/auth/logout", auth_logout)
+    r.add("POST", "/api/auth/refresh", auth_refresh, PUBLIC)
+    r.add("GET", "/api/auth/me", auth_me)
+    r.add("POST", "/api/auth/mfa/totp/setup", totp_setup)
+    r.add("POST", "/api/auth/mfa/totp/enable", totp_enable)
+    r.add("POST", "/api/auth/mfa/webauthn/register/start", webauthn_unavailable)
+    r.add("POST", "/api/auth/mfa/webauthn/register/finish", webauthn_unavailable)
+    r.add("POST", "/api/auth/mfa/recovery/generate", recovery_generate)
+    r.add("GET", "/api/auth/mfa/recovery/status", recovery_status)
+    r.add("POST", "/api/auth/mfa/disable", mfa_disable)
+
+    # ------------------------------------------------------------------ administration
+    def admin_list_users(req):
+        return [app.public_user(u) for u in app.users.find(limit=req.q("limit", None, int), offset=req.q("offset", 0, int),
+                                                           sort="created_at")]
+
+    def admin_create_user(req):
+        email, name, password = req.need("email", "name", "password")
+        return 201, app.public_user(app.create_user(email, name, password, req.json.get("role", "user")))
+
+    def admin_get_user(req):
+        return app.public_user(app.users.get(req.params["id"]))
+
+    def admin_update_user(req):
+        ch = {k: v for k, v in req.json.items() if k in ("name", "role", "approved", "email_verified")}
+        if "role" in ch and ch["role"] not in A.ROLES:
+            raise HttpError(400, f"role must be one of {A.ROLES}")
+        if "password" in req.json:
+            ch["password_hash"] = A.hash_password(req.json["password"])
+        return app.public_user(app.users.update(req.params["id"], ch))
+
+    def admin_delete_user(req):
+        if req.params["id"] == req.user_id:
+            raise HttpError(400, "an administrator cannot delete their own account")
+        app.users.delete(req.params["id"])
+        return {"deleted": True}
+
+    def admin_stats(req):
+        return {"users": app.users.count(), "runs": app.runs.runs.count(), "runs_running": app.runs.count_running(),
+                "models": app.registry.models.count(), "datasets": app.datasets.col.count(),
+                "endpoints": app.endpoints.col.count(), "endpoints_running": app.endpoints.count_running(),
+                "notebooks": app.notebooks.col.count(), "database": app.store.health()}
+
+    def admin_query(req):
+        (collection,) = req.need("collection")
+        if collection == "users":
+            raise HttpError(403, "the users collection is not exposed through the query endpoint")
+        return app.store.query(collection, req.json.get("filter"), limit=req.json.get("limit"),
+                               sort=req.json.get("sort"), descending=bool(req.json.get("descending")))
+
+    r.add("GET", "/api/admin/users", admin_list_users, ADMIN)
+    r.add("POST", "/api/admin/users", admin_create_user, ADMIN)
+    r.add("GET", "/api/admin/users/:id", admin_get_user, ADMIN)
+    r.add("PUT", "/api/admin/users/:id", admin_update_user, ADMIN)
+    r.add("DELETE", "/api/admin/users/:id", admin_delete_user, ADMIN)
+    r.add("GET", "/api/admin/stats", admin_stats, ADMIN)
+    r.add("POST", "/api/admin/query", admin_query, ADMIN)
+    _ = USER
