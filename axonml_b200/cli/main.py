@@ -198,6 +198,11 @@ def cmd_train(a, resume_from: str | None = None):
         state = ck.training_state
         start_epoch = state.epoch
         print(f"resumed from {resume_from} (epoch {start_epoch}, step {state.global_step})")
+    from ..integrations.wandb import WandbConfig, init_training_run
+    wb = init_training_run(WandbConfig.load(), cfg.project.name, {"epochs": t.epochs, "batch_size": t.batch_size,
+                                                                  "learning_rate": t.learning_rate, "optimizer": t.optimizer.name,
+                                                                  "architecture": cfg.model.architecture},
+                           directory=os.path.join(t.output_dir, "wandb"))
     for epoch in range(start_epoch, t.epochs):
         t0, losses = time.time(), []
         for b in loader:
@@ -215,11 +220,15 @@ def cmd_train(a, resume_from: str | None = None):
         mean = sum(losses) / max(len(losses), 1)
         acc = _accuracy(model, val_loader, dev) if val_loader is not None else float("nan")
         print(f"epoch {epoch + 1}/{t.epochs}  loss {mean:.4f}  val_acc {acc:.4f}  {time.time() - t0:.1f}s", flush=True)
+        if wb is not None:
+            wb.log_at_step(epoch + 1, {"train_loss": mean, **({} if acc != acc else {"val_accuracy": acc})})
         if t.checkpoint_frequency and (epoch + 1) % t.checkpoint_frequency == 0:
             ck = (Checkpoint.builder().model_state(StateDict.from_module(model))
                   .optimizer_state(optimizer_to_state_dict(opt)).training_state(state)
                   .config("architecture", cfg.model.architecture).config("val_acc", acc).build())
             save_checkpoint(ck, _checkpoint_path(t.output_dir, epoch + 1))
+    if wb is not None:
+        print(f"W&B offline run: {wb.finish()}")
     print(f"done: {t.output_dir}")
 
 
@@ -523,6 +532,9 @@ def build_parser() -> argparse.ArgumentParser:
     p = sub.add_parser("launch"); p.add_argument("--nproc", type=int, default=0); p.add_argument("--port", type=int, default=29500)
     p.add_argument("script"); p.add_argument("script_args", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_launch)
     p = sub.add_parser("report"); p.add_argument("dir"); p.set_defaults(fn=cmd_report)
+    from . import services, workspace
+    workspace.add_parsers(sub)
+    services.add_parsers(sub)
     return ap
 
 

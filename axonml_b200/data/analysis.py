@@ -175,10 +175,20 @@ def _analyze_text(path: str, max_samples: int) -> dict:
 def _analyze_idx(path: str) -> dict:
     files = [path] if os.path.isfile(path) else [os.path.join(path, f) for f in sorted(os.listdir(path)) if "idx" in f.lower()]
     heads = {os.path.basename(f): _idx_header(f) for f in files}
-    images = next((h for h in heads.values() if len(h["shape"]) >= 3), None)
+    image_sets = [h for h in heads.values() if len(h["shape"]) >= 3]
+    images = max(image_sets, key=lambda h: h["shape"][0]) if image_sets else None
+    counts = {}
+    label_files = [f for f in files if len(heads[os.path.basename(f)]["shape"]) == 1]
+    if label_files:
+        import gzip
+        lf = max(label_files, key=lambda f: heads[os.path.basename(f)]["shape"][0])
+        with (gzip.open if lf.endswith(".gz") else open)(lf, "rb") as f:
+            f.read(8)
+            for b in f.read(1 << 22):
+                counts[str(b)] = counts.get(str(b), 0) + 1
     return {"num_samples": images["shape"][0] if images else None, "files": heads, "task": "classification",
-            "image_shape": [1] + images["shape"][1:] if images else None, "class_counts": {}, "num_features": None,
-            "missing_values": 0}
+            "image_shape": ([1] + images["shape"][1:] if len(images["shape"]) == 3 else images["shape"][1:]) if images else None,
+            "class_counts": counts, "num_features": None, "missing_values": 0}
 
 
 def analyze_dataset(path: str, dataset_type: str | None = None, max_samples: int = 10_000) -> dict:

@@ -104,3 +104,33 @@ class SyntheticImageNet(_SyntheticImages):
     def get(self, i):
         g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
         return torch.randn(self.shape, generator=g), torch.randint(0, 1000, (), generator=g)
+
+
+def write_idx(path, array: np.ndarray) -> None:
+    """Writes a uint8 array in IDX format (the inverse of ``read_idx``)."""
+    a = np.ascontiguousarray(array, dtype=np.uint8)
+    with open(path, "wb") as f:
+        f.write(struct.pack(">HBB", 0, 8, a.ndim))
+        f.write(struct.pack(">" + "I" * a.ndim, *a.shape))
+        f.write(a.tobytes())
+
+
+def write_synthetic_idx(root: str, shape, classes: int, samples: int = 2048, seed: int = 42) -> int:
+    """A stand-in for MNIST-style data in the original file layout (train and t10k image/label IDX
+    files), generated from the synthetic dataset, so that ``MNIST(root)`` reads it.  Only
+    single-channel shapes have an IDX layout; others are written channel-first as 4-D IDX."""
+    os.makedirs(root, exist_ok=True)
+    c, h, w = shape
+    ds = _SyntheticImages(samples, (c, h, w), classes, seed)
+    imgs = np.zeros((samples, h, w) if c == 1 else (samples, c, h, w), dtype=np.uint8)
+    labels = np.zeros((samples,), dtype=np.uint8)
+    for i in range(samples):
+        x, y = ds.get(i)
+        imgs[i] = (x[0] if c == 1 else x).mul(255).round().to(torch.uint8).numpy()
+        labels[i] = int(y)
+    n_test = max(samples // 8, 1)
+    write_idx(os.path.join(root, "train-images-idx3-ubyte"), imgs[:-n_test])
+    write_idx(os.path.join(root, "train-labels-idx1-ubyte"), labels[:-n_test])
+    write_idx(os.path.join(root, "t10k-images-idx3-ubyte"), imgs[-n_test:])
+    write_idx(os.path.join(root, "t10k-labels-idx1-ubyte"), labels[-n_test:])
+    return samples
