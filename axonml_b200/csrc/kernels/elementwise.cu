@@ -1,5 +1,6 @@
-// Elementwise / activation kernel set: vectorised (16-byte) grid-stride kernels selected by an
-// opcode.  Covers the reference's CUDA island (cuda_kernels/elementwise.cu, activations.cu:
+// Elementwise / activation kernel set: vectorised (16-byte) grid-stride kernels, one
+// instantiation per opcode (a switch per element costs more instructions than the memory system
+// leaves room for at HBM speed).  Covers the reference's CUDA island (cuda_kernels/elementwise.cu, activations.cu:
 // add, sub, mul, div, scale, add_scalar, neg, abs, sqrt, pow, pow_scalar, clamp, relu, sigmoid,
 // tanh, leaky_relu, exp, log, gelu, silu, elu and the three *_backward kernels) and the
 // arithmetic of its WGSL/MSL compute shaders (wgpu_backend.rs:1003-1267, metal.rs:527-700),
@@ -96,8 +97,8 @@ template <> struct IO<__nv_bfloat16> {
   static __device__ __forceinline__ void st1(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
 };
 
-template <typename T>
-__global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n, int op, float p0,
+template <typename T, int op>
+__global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n, float p0,
                              float p1, int aligned) {
   constexpr int V = IO<T>::V;
   const long stride = (long)gridDim.x * blockDim.x;
@@ -113,9 +114,9 @@ __global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n,
   for (long i = nv * V + tid; i < n; i += stride) IO<T>::st1(y + i, unary(IO<T>::ld1(x + i), op, p0, p1));
 }
 
-template <typename T>
+template <typename T, int op>
 __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y,
-                              long n, int op, float p0, int aligned) {
+                              long n, float p0, int aligned) {
   constexpr int V = IO<T>::V;
   const long stride = (long)gridDim.x * blockDim.x;
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -245,6 +246,49 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
   }
 }
 
+// Vectorised column sums: a thread owns V adjacent columns (one 16-byte load per row), a warp 32*V
+// adjacent columns, the 8 warps of a block (and gridDim.y blocks) split the rows.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_vec_kernel(const T* __restrict__ x, float* __restrict__ out, long rows,
+                                                        int N, long ld) {
+  constexpr int V = IO<T>::V;
+  __shared__ float sm[8][32 * V + 1];
+  const int col = (blockIdx.x * 32 + threadIdx.x) * V;
+  float acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = 0.f;
+  if (col < N) {
+    long r = (long)blockIdx.y * 8 + threadIdx.y;
+    const long step = (long)gridDim.y * 8;
+    // two rows in flight per thread
+    for (; r + step < rows; r += 2 * step) {
+      float a[V], b[V];
+      IO<T>::load(x + r * ld + col, a);
+      IO<T>::load(x + (r + step) * ld + col, b);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += a[j] + b[j];
+    }
+    for (; r < rows; r += step) {
+      float a[V];
+      IO<T>::load(x + r * ld + col, a);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += a[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) sm[threadIdx.y][threadIdx.x * V + j] = acc[j];
+  __syncthreads();
+  for (int c = threadIdx.y * 32 + threadIdx.x; c < 32 * V; c += 256) {
+    const int gc = blockIdx.x * 32 * V + c;
+    if (gc < N) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += sm[w][c];
+      atomicAdd(out + gc, t);
+    }
+  }
+}
+
 inline int grid_for(long work, int block) {
   long g = (work + block - 1) / block;
   long cap = (long)axh::sm_count() * 16;
@@ -258,29 +302,52 @@ inline bool aligned16(const void* a, const void* b, const void* c) {
 
 }  // namespace
 
+template <int OP>
+static void launch_unary(int dtype, const void* x, void* y, long n, float p0, float p1, int al, cudaStream_t stream) {
+  if (dtype == 1)
+    unary_kernel<__nv_bfloat16, OP><<<grid_for(n / 8 + 1, 256), 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+                                                                                  n, p0, p1, al);
+  else
+    unary_kernel<float, OP><<<grid_for(n / 4 + 1, 256), 256, 0, stream>>>((const float*)x, (float*)y, n, p0, p1, al);
+}
+
 AX_API int ax_unary(int dtype, int op, const void* x, void* y, long n, float p0, float p1,
                     cudaStream_t stream) {
   if (n <= 0) return 0;
-  int al = aligned16(x, y, nullptr);
-  if (dtype == 1)
-    unary_kernel<__nv_bfloat16><<<grid_for(n / 8 + 1, 256), 256, 0, stream>>>(
-        (const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, op, p0, p1, al);
-  else
-    unary_kernel<float><<<grid_for(n / 4 + 1, 256), 256, 0, stream>>>((const float*)x, (float*)y, n,
-                                                                     op, p0, p1, al);
+  const int al = aligned16(x, y, nullptr);
+#define AX_U(OP) case OP: launch_unary<OP>(dtype, x, y, n, p0, p1, al, stream); break;
+  switch (op) {
+    AX_U(U_NEG) AX_U(U_ABS) AX_U(U_SQRT) AX_U(U_EXP) AX_U(U_LOG) AX_U(U_RELU) AX_U(U_SIGMOID) AX_U(U_TANH)
+    AX_U(U_GELU) AX_U(U_SILU) AX_U(U_ELU) AX_U(U_LEAKY_RELU) AX_U(U_SCALE) AX_U(U_ADD_SCALAR) AX_U(U_POW_SCALAR)
+    AX_U(U_CLAMP) AX_U(U_SQUARE) AX_U(U_RSQRT) AX_U(U_COPY)
+    default: return -1;
+  }
+#undef AX_U
   return (int)cudaGetLastError();
+}
+
+template <int OP>
+static void launch_binary(int dtype, const void* a, const void* b, void* y, long n, float p0, int al, cudaStream_t stream) {
+  if (dtype == 1)
+    binary_kernel<__nv_bfloat16, OP><<<grid_for(n / 8 + 1, 256), 256, 0, stream>>>(
+        (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, p0, al);
+  else
+    binary_kernel<float, OP><<<grid_for(n / 4 + 1, 256), 256, 0, stream>>>((const float*)a, (const float*)b, (float*)y, n,
+                                                                           p0, al);
 }
 
 AX_API int ax_binary(int dtype, int op, const void* a, const void* b, void* y, long n, float p0,
                      cudaStream_t stream) {
   if (n <= 0) return 0;
-  int al = aligned16(a, b, y);
-  if (dtype == 1)
-    binary_kernel<__nv_bfloat16><<<grid_for(n / 8 + 1, 256), 256, 0, stream>>>(
-        (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)y, n, op, p0, al);
-  else
-    binary_kernel<float><<<grid_for(n / 4 + 1, 256), 256, 0, stream>>>(
-        (const float*)a, (const float*)b, (float*)y, n, op, p0, al);
+  const int al = aligned16(a, b, y);
+#define AX_B(OP) case OP: launch_binary<OP>(dtype, a, b, y, n, p0, al, stream); break;
+  switch (op) {
+    AX_B(B_ADD) AX_B(B_SUB) AX_B(B_MUL) AX_B(B_DIV) AX_B(B_POW) AX_B(B_MAX) AX_B(B_MIN) AX_B(B_RELU_BWD)
+    AX_B(B_SIGMOID_BWD) AX_B(B_TANH_BWD) AX_B(B_GELU_BWD) AX_B(B_SILU_BWD) AX_B(B_ELU_BWD) AX_B(B_LEAKY_RELU_BWD)
+    AX_B(B_AXPY)
+    default: return -1;
+  }
+#undef AX_B
   return (int)cudaGetLastError();
 }
 
@@ -342,6 +409,20 @@ AX_API int ax_dropout_bwd(int dtype, const void* dy, const uint8_t* mask, void* 
 AX_API int ax_colsum(int dtype, const void* x, float* out, long rows, int N, long ld,
                      cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
+  const int V = dtype == 1 ? 8 : 4;
+  if (N % V == 0 && ld % V == 0 && (((uintptr_t)x) & 15) == 0) {
+    dim3 block(32, 8);
+    const int gx = (N + 32 * V - 1) / (32 * V);
+    long gy = (long)axh::sm_count() * 8 / gx;            // about eight blocks per SM
+    if (gy > (rows + 15) / 16) gy = (rows + 15) / 16;
+    if (gy < 1) gy = 1;
+    dim3 grid(gx, (unsigned)gy);
+    if (dtype == 1)
+      colsum_vec_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>((const __nv_bfloat16*)x, out, rows, N, ld);
+    else
+      colsum_vec_kernel<float><<<grid, block, 0, stream>>>((const float*)x, out, rows, N, ld);
+    return (int)cudaGetLastError();
+  }
   dim3 block(32, 32);
   int gy = (int)((rows + 1023) / 1024);
   if (gy > 64) gy = 64;
