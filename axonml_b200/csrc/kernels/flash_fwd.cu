@@ -4,7 +4,8 @@
 // One CTA per (batch, query head, 128-query block).  Warp 0 streams K/V blocks of 128 keys with
 // TMA (two stages), warp 1 issues tcgen05.mma: S = Q K^T into one of two TMEM buffers and
 // O += P V into a TMEM accumulator, warps 2..5 (one thread per query row) read S from TMEM, keep
-// the running max / sum, write P as bf16 into shared memory for the second MMA, and rescale O in
+// the running max / sum, write P as bf16 into one of two shared-memory buffers for the second MMA
+// (so softmax(j+1) does not wait for P(j) V(j)), and rescale O in
 // TMEM only when a row's max has grown by more than 2^8 (the deferred-rescale trick keeps the
 // result exact because the final normalisation uses the same reference max).  S(j+1) is issued
 // before P(j) V(j), so the tensor pipe works on the next block while softmax(j) runs.
@@ -21,7 +22,7 @@ constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr int kThreads = 192;
 constexpr int kTile = BQ * HD * 2;           // 32 KB: one [128 x 128] bf16 tile
-constexpr int kSmem = 1024 + kTile /*Q*/ + 2 * kTile /*K*/ + 2 * kTile /*V*/ + kTile /*P*/ + 256;
+constexpr int kSmem = 1024 + kTile /*Q*/ + 2 * kTile /*K*/ + 2 * kTile /*V*/ + 2 * kTile /*P*/ + 256;
 constexpr int kTmemCols = 512;               // S0 | S1 | O | (unused)
 constexpr float kRescaleThreshold = 8.0f;    // log2 units
 
@@ -33,7 +34,12 @@ struct FwdParams {
   int causal;
   float scale_log2;   // softmax scale * log2(e)
   int* status;
+  unsigned long long* trace;   // optional timeline of two CTAs ([2][kTraceSlots] globaltimer stamps), or null
 };
+
+// Timeline: slot 0 kernel start, then per KV block five stamps (scores ready, scores in registers,
+// max / rescale done, P buffer free, P published), last slot epilogue done.
+constexpr int kTraceSlots = 128;
 
 __global__ void __launch_bounds__(kThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -44,7 +50,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint8_t* sK = sQ + kTile;
   uint8_t* sV = sK + 2 * kTile;
   uint8_t* sP = sV + 2 * kTile;
-  uint64_t* bars = (uint64_t*)(sP + kTile);
+  uint64_t* bars = (uint64_t*)(sP + 2 * kTile);
   uint64_t* q_full = bars;          // 1
   uint64_t* k_full = bars + 1;      // 2
   uint64_t* k_empty = bars + 3;     // 2
@@ -52,9 +58,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   uint64_t* v_empty = bars + 7;     // 2
   uint64_t* s_full = bars + 9;      // 2
   uint64_t* s_empty = bars + 11;    // 2
-  uint64_t* p_full = bars + 13;     // 1
-  uint64_t* pv_done = bars + 14;    // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+  uint64_t* p_full = bars + 13;     // 2 (one per P buffer)
+  uint64_t* pv_done = bars + 15;    // 2 (P V of even / odd blocks)
+  uint32_t* tmem_slot = (uint32_t*)(bars + 17);
   volatile int* dead = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -75,8 +81,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&p_full[i], 4); mbar_init(&pv_done[i], 1); }
     mbar_fence_init();
     prefetch_tensormap(&map_q); prefetch_tensormap(&map_k); prefetch_tensormap(&map_v);
   }
@@ -132,15 +137,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (!ok) break;
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(p_full, j & 1, dead, p.status, 413)) break;
+        if (!mbar_wait(&p_full[s], ph, dead, p.status, 413)) break;
         if (!mbar_wait(&v_full[s], ph, dead, p.status, 414)) break;
         tc_fence_after();
         const uint32_t aV = smem_u32(sV + s * kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_f16_ss(tO, desc_kmajor(aP, BQ, k), desc_mnmajor(aV, BKV, k), idesc_o, (j | k) != 0);
+          umma_f16_ss(tO, desc_kmajor(aP + s * kTile, BQ, k), desc_mnmajor(aV, BKV, k), idesc_o, (j | k) != 0);
         umma_commit(&v_empty[s]);
-        umma_commit(pv_done);
+        umma_commit(&pv_done[s]);
       }
     }
   } else {
@@ -148,6 +153,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int r = q * 32 + lane;                 // row inside the tile == TMEM lane
     const int qi = q0 + r;                       // query index
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t sP_u32 = smem_u32(sP);
+    unsigned long long* tr = nullptr;
+    if (p.trace != nullptr && warp == 2 && lane == 0 && blockIdx.x == 0 &&
+        ((blockIdx.y == 0 && blockIdx.z == 0) || (blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1)))
+      tr = p.trace + (blockIdx.z == 0 ? 0 : kTraceSlots);
+    auto stamp = [&](int slot) { if (tr != nullptr && slot < kTraceSlots) tr[slot] = globaltimer_ns(); };
+    stamp(0);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk && ok; ++j) {
@@ -158,84 +170,93 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tS0 + s * 128 + lane_addr;
-      const int limit = p.causal ? min(p.Skv - 1, qi + offset) : p.Skv - 1;   // last visible key
-      const bool need_mask = __any_sync(0xffffffffu, kv0 + BKV - 1 > limit);
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tS + c * 32, v);
+      stamp(1 + 5 * j);
+      // the row's 128 scores, read once: four loads in flight, one wait
+      uint32_t v[128];
+      {
+        const uint32_t tS = tS0 + s * 128 + lane_addr;
+        tmem_ld_32x32b_x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld_32x32b_x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        tmem_ld_32x32b_x32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
+        tmem_ld_32x32b_x32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
         tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
-          if (need_mask && kv0 + c * 32 + i > limit) x = -INFINITY;
-          mx = fmaxf(mx, x);
-        }
       }
+      // S[s] lives in registers now: hand the TMEM buffer back so that S(j+2) can be issued
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+      stamp(2 + 5 * j);
+      const int limit = p.causal ? min(p.Skv - 1, qi + offset) : p.Skv - 1;   // last visible key
+      if (__any_sync(0xffffffffu, kv0 + BKV - 1 > limit)) {
+        // only blocks that touch the diagonal or the end of the keys pay for the comparison;
+        // a masked score becomes -inf, whose probability below is exactly 0
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (kv0 + i > limit) v[i] = 0xff800000u;
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
       float m_new = fmaxf(m, mx * p.scale_log2);
       if (m_new == -INFINITY) m_new = 0.f;
-      // O and the P buffer are free once P(j-1) V(j-1) has retired
-      if (j > 0) {
-        ok = mbar_wait(pv_done, (j - 1) & 1, dead, p.status, 421);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-      }
       const bool grow = m_new > m + kRescaleThreshold;
       if (j == 0) {
         m = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
+        // O may only be touched once every P V issued so far has retired
+        ok = mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, dead, p.status, 421);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
         const float alpha = grow ? exp2f(m - m_new) : 1.f;
         if (grow) { l *= alpha; m = m_new; }
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
-          uint32_t v[16];
-          tmem_ld_32x32b_x16(tO + lane_addr + c * 16, v);
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(tO + lane_addr + c * 16, o);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32b_x16(tO + lane_addr + c * 16, v);
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x16(tO + lane_addr + c * 16, o);
         }
         tc_wait_st();
+        tc_fence_before();
       }
-      // pass 2: probabilities -> shared memory (bf16), row sum
+      if (tr != nullptr) { asm volatile("" ::"f"(m), "f"(mx) : "memory"); }
+      stamp(3 + 5 * j);
+      // P buffer s was last read by P V of block j-2
+      if (j >= 2) {
+        ok = mbar_wait(&pv_done[s], ((j - 2) >> 1) & 1, dead, p.status, 423);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      stamp(4 + 5 * j);
+      // probabilities -> shared memory (bf16, the swizzled K-major operand of P V), row sum
+      const uint32_t sp_row = sP_u32 + s * kTile + r * 128;
+      const float neg_m = -m;
       float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tS + c * 32, v);
-        tc_wait_ld();
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float pv[8];
+      for (int c = 0; c < 16; ++c) {
+        float e[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int col = c * 32 + g * 8 + i;
-            float x = __uint_as_float(v[g * 8 + i]) * p.scale_log2 - m;
-            float e = exp2f(x);
-            if (need_mask && kv0 + col > limit) e = 0.f;
-            pv[i] = e;
-            rs += e;
-          }
-          uint4 o;
-          o.x = pack_bf16x2(pv[0], pv[1]); o.y = pack_bf16x2(pv[2], pv[3]);
-          o.z = pack_bf16x2(pv[4], pv[5]); o.w = pack_bf16x2(pv[6], pv[7]);
-          store_tile_chunk(sP, BQ, r, c * 4 + g, o);
+        for (int i = 0; i < 8; ++i) {
+          e[i] = exp2f(fmaf(__uint_as_float(v[c * 8 + i]), p.scale_log2, neg_m));
+          rs += e[i];
         }
+        const uint32_t addr = sp_row + (c >> 3) * slab_bytes(BQ) + (((c & 7) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(e[0], e[1])),
+                     "r"(pack_bf16x2(e[2], e[3])), "r"(pack_bf16x2(e[4], e[5])), "r"(pack_bf16x2(e[6], e[7]))
+                     : "memory");
       }
       l += rs;
-      // hand S[s] back, publish P
-      tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) { mbar_arrive(&s_empty[s]); mbar_arrive(p_full); }
+      if (lane == 0) mbar_arrive(&p_full[s]);
+      stamp(5 + 5 * j);
     }
     // epilogue: O / l -> global, lse
     if (ok && nblk > 0) {
-      ok = mbar_wait(pv_done, (nblk - 1) & 1, dead, p.status, 422);
+      ok = mbar_wait(&pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, dead, p.status, 422);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -267,6 +288,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       if (valid && p.lse)
         p.lse[((long)b * p.Hq + h) * p.Sq + qi] = l > 0.f ? (m * 0.6931471805599453f + logf(l)) : -INFINITY;
+      stamp(kTraceSlots - 1);
     }
   }
   tc_fence_before();
@@ -287,6 +309,11 @@ int make_bshd_map(CUtensorMap* m, const void* ptr, int D, int H, int S, int B, l
                            CU_TENSOR_MAP_SWIZZLE_128B);
 }
 }  // namespace axh
+
+// Diagnostic timeline: the launches that follow stamp the softmax stage of two CTAs into `buf`
+// ([2][128] 64-bit slots, zero-filled by the caller); null turns it off.
+static unsigned long long* g_flash_trace = nullptr;
+AX_API void ax_flash_fwd_set_trace(void* buf) { g_flash_trace = (unsigned long long*)buf; }
 
 // q [B,Sq,Hq,128], k/v [B,Skv,Hkv,128], out [B,Sq,Hq,128] (bf16, token-major; strides in elements),
 // lse [B,Hq,Sq] fp32.  Returns a cudaError_t value or a negative code for unsupported arguments.
@@ -314,6 +341,7 @@ AX_API int ax_flash_fwd(const void* q, const void* k, const void* v, void* out, 
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv; p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.trace = g_flash_trace;
   dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
   flash_fwd_kernel<<<grid, kThreads, kSmem, stream>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();
