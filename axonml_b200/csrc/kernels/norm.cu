@@ -259,6 +259,91 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* __r
   }
 }
 
+// Same contract as norm_bwd_kernel for D == ITERS * 256: the weight- and bias-gradient partial sums
+// of the columns a lane owns stay in registers over all rows of its warp (no shared-memory atomics
+// in the row loop) and the warps of a CTA are combined once at the end.
+template <typename T, typename WT, bool RMS, int ITERS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+norm_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const WT* __restrict__ w,
+                    const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                    const T* __restrict__ dres_in, T* __restrict__ dx, float* __restrict__ partial, int rows) {
+  constexpr int D = ITERS * 256;
+  extern __shared__ float sacc[];            // [RMS ? 1 : 2][D]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float aw[ITERS][8];
+  float ab[RMS ? 1 : ITERS][8];
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { aw[i][j] = 0.f; if (!RMS) ab[i][j] = 0.f; }
+  for (long row = (long)blockIdx.x * kWarpsPerCta + warp; row < rows; row += (long)gridDim.x * kWarpsPerCta) {
+    const T* xr = x + row * D;
+    const T* dyr = dy + row * D;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      float xv[8], gv[8], wv[8];
+      Vec8<T>::load(xr + i * 256 + lane * 8, xv);
+      Vec8<T>::load(dyr + i * 256 + lane * 8, gv);
+      Vec8<WT>::load(w + i * 256 + lane * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = (xv[j] - mean) * rstd;
+        const float gw = gv[j] * wv[j];
+        s1 += gw;
+        s2 += gw * xh;
+        aw[i][j] += gv[j] * xh;
+        if (!RMS) ab[i][j] += gv[j];
+      }
+    }
+    s1 = warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    if (RMS) s1 = 0.f;
+    T* dxr = dx + row * D;
+    const T* drr = dres_in ? dres_in + row * D : nullptr;
+    // second pass over the row (4-16 KB, still in L1): the accumulators own the registers
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      float xv[8], gv[8], wv[8], o[8];
+      Vec8<T>::load(xr + i * 256 + lane * 8, xv);
+      Vec8<T>::load(dyr + i * 256 + lane * 8, gv);
+      Vec8<WT>::load(w + i * 256 + lane * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * (gv[j] * wv[j] - s1 - (xv[j] - mean) * rstd * s2);
+      if (drr) {
+        float r[8];
+        Vec8<T>::load(drr + i * 256 + lane * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      Vec8<T>::store(dxr + i * 256 + lane * 8, o);
+    }
+  }
+  for (int wi = 0; wi < kWarpsPerCta; ++wi) {
+    if (warp == wi) {
+#pragma unroll
+      for (int i = 0; i < ITERS; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int d = i * 256 + j * 32 + lane;        // conflict-free slot of column i*256 + lane*8 + j
+          if (wi == 0) { sacc[d] = aw[i][j]; if (!RMS) sacc[D + d] = ab[i][j]; }
+          else { sacc[d] += aw[i][j]; if (!RMS) sacc[D + d] += ab[i][j]; }
+        }
+    }
+    __syncthreads();
+  }
+  float* out = partial + (long)blockIdx.x * 2 * D;
+  for (int t = threadIdx.x; t < D; t += blockDim.x) {
+    const int rem = t & 255;
+    const int col = (t - rem) + (rem & 31) * 8 + (rem >> 5);
+    out[col] = sacc[t];
+    if (!RMS) out[D + col] = sacc[D + t];
+  }
+}
+
 // dw[d] = sum_g partial[g,0,d]; db[d] = sum_g partial[g,1,d].  Block = 32 columns x 32 group
 // lanes: each thread sums groups g = ty, ty+32, ..., then the 32 partials of a column are combined
 // through shared memory.
@@ -318,6 +403,25 @@ template <typename T, typename WT>
 int launch_bwd(bool rms, const void* dy, const void* x, const void* w, const float* mean,
                const float* rstd, const void* dres, void* dx, void* dw, void* db, float* scratch,
                int groups, int rows, int D, cudaStream_t stream) {
+  // register-accumulating variant for the common widths (accumulators must fit the register file)
+  bool done = false;
+#define AX_NORM_BWD_REG(RMSV, IT)                                                                              \
+  if (!done && rms == RMSV && D == IT * 256) {                                                                 \
+    norm_bwd_reg_kernel<T, WT, RMSV, IT><<<groups, kWarpsPerCta * 32, (RMSV ? 1 : 2) * D * sizeof(float), stream>>>( \
+        (const T*)dy, (const T*)x, (const WT*)w, mean, rstd, (const T*)dres, (T*)dx, scratch, rows);           \
+    done = true;                                                                                               \
+  }
+  AX_NORM_BWD_REG(false, 1) AX_NORM_BWD_REG(false, 2) AX_NORM_BWD_REG(false, 3) AX_NORM_BWD_REG(false, 4)
+  AX_NORM_BWD_REG(false, 8)
+  AX_NORM_BWD_REG(true, 1) AX_NORM_BWD_REG(true, 2) AX_NORM_BWD_REG(true, 4) AX_NORM_BWD_REG(true, 8)
+#undef AX_NORM_BWD_REG
+  if (done) {
+    cudaError_t e0 = cudaGetLastError();
+    if (e0 != cudaSuccess) return (int)e0;
+    norm_bwd_reduce_kernel<WT><<<(D + 31) / 32, dim3(32, 32), 0, stream>>>(scratch, (WT*)dw, rms ? nullptr : (WT*)db,
+                                                                     groups, D);
+    return (int)cudaGetLastError();
+  }
   size_t smem = (size_t)2 * (((D + 255) / 256) * 256) * sizeof(float);
   if (rms) {
     auto k = norm_bwd_kernel<T, WT, true>;

@@ -32,6 +32,26 @@ __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, long i, flo
 
 constexpr int kThreads = 512;
 
+// one 16-byte chunk of a row as floats
+__device__ __forceinline__ void load_chunk(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load_chunk(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void store_chunk(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store_chunk(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+  u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
 __device__ __forceinline__ void online_combine(float& m, float& s, float m2, float s2) {
   float mn = fmaxf(m, m2);
   if (mn == -INFINITY) { m = mn; s = 0.f; return; }
@@ -44,7 +64,23 @@ template <typename T>
 __device__ __forceinline__ void row_max_sum(const T* row, int V, float& m_out, float& s_out) {
   __shared__ float sm[kThreads / 32], ss[kThreads / 32];
   float m = -INFINITY, s = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  // 16-byte chunks first (8 bf16 / 4 fp32): one running-max update per chunk instead of a
+  // data-dependent branch per element
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const int nvec = (((uintptr_t)row & 15) == 0) ? V / kVec : 0;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float v[kVec];
+    load_chunk(row + (long)i * kVec, v);
+    float mx = v[0];
+#pragma unroll
+    for (int j = 1; j < kVec; ++j) mx = fmaxf(mx, v[j]);
+    if (mx > m) { s *= __expf(m - mx); m = mx; }
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) s += __expf(v[j] - m);
+    }
+  }
+  for (int i = nvec * kVec + threadIdx.x; i < V; i += blockDim.x) {
     float v = ldf(row, i);
     if (v > m) { s = s * __expf(m - v) + 1.f; m = v; }
     else s += __expf(v - m);
@@ -145,7 +181,28 @@ ce_bwd_kernel(const T* __restrict__ logits, const long* __restrict__ target,
   const bool ignored = (t == ignore_index || t < 0 || t >= V);
   const float g = ignored ? 0.f : gmul * (gscale ? gscale[gscale_per_row ? blockIdx.x : 0] : 1.f);
   const float l = lse[blockIdx.x];
-  for (int i = threadIdx.x; i < Vpad; i += blockDim.x) {
+  constexpr int kVec = 16 / (int)sizeof(T);
+  const bool vec_ok = ((((uintptr_t)row) | ((uintptr_t)out)) & 15) == 0;
+  const int nvec = vec_ok ? V / kVec : 0;          // chunks that lie entirely inside the vocabulary
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float v[kVec];
+    if (ignored) {
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) v[j] = 0.f;
+    } else {
+      load_chunk(row + (long)i * kVec, v);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) v[j] = __expf(v[j] - l) * g;
+      const long rel = t - (long)i * kVec;
+      if (rel >= 0 && rel < kVec) {
+#pragma unroll
+        for (int j = 0; j < kVec; ++j)
+          if (j == (int)rel) v[j] -= g;
+      }
+    }
+    store_chunk(out + (long)i * kVec, v);
+  }
+  for (int i = nvec * kVec + threadIdx.x; i < Vpad; i += blockDim.x) {
     float v = 0.f;
     if (i < V && !ignored) {
       v = __expf(ldf(row, i) - l);
