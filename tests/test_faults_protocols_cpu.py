@@ -1,0 +1,139 @@
+"""Host-side fault injection, heartbeat failure detection, recovery from a sharded checkpoint and
+the randomised-interleaving models of the peer-signal protocols (CPU only; no GPU is faulted)."""
+import threading
+import time
+
+import pytest
+import torch
+
+from axonml_b200.parallel import CommTimeout, MockBackend
+from axonml_b200.parallel.faults import (CorruptPayload, FailureDetector, FaultPlan, FaultyBackend, Heartbeat, RankKilled,
+                                         run_with_recovery)
+from axonml_b200.parallel.protocol_model import AllReduceModel, ProtocolError, ReduceScatterModel, check_all
+
+
+def _threads(n, fn):
+    out, errs = [None] * n, [None] * n
+
+    def run(r):
+        try:
+            out[r] = fn(r)
+        except BaseException as e:  # noqa: BLE001 - collected for the assertions
+            errs[r] = e
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(n)]
+    [t.start() for t in ts]
+    [t.join(30) for t in ts]
+    return out, errs
+
+
+def test_dropped_and_corrupted_messages_are_detected():
+    plan = FaultPlan().drop_message(0, 1, tag=0, nth=1).corrupt_message(0, 1, tag=7, nth=0)
+    world = [FaultyBackend(b, plan, verify=True) for b in MockBackend.create_world(2, timeout_s=0.4)]
+
+    def body(r):
+        if r == 0:
+            world[0].send(torch.arange(4.0), 1)            # arrives
+            world[0].send(torch.arange(4.0), 1)            # dropped by the plan
+            world[0].send(torch.ones(3), 1, tag=7)         # corrupted by the plan
+            return None
+        got = torch.zeros(4)
+        world[1].recv(got, 0)
+        assert got.tolist() == [0.0, 1.0, 2.0, 3.0]
+        with pytest.raises(CommTimeout):
+            world[1].recv(torch.zeros(4), 0)
+        with pytest.raises(CorruptPayload):
+            world[1].recv(torch.zeros(3), 0, tag=7)
+        return "checked"
+    out, errs = _threads(2, body)
+    assert errs == [None, None] and out[1] == "checked"
+
+
+def test_delay_within_timeout_passes_and_beyond_it_fails():
+    ok_plan = FaultPlan().delay_rank(1, "all_reduce", 0, 0.1)
+    world = [FaultyBackend(b, ok_plan) for b in MockBackend.create_world(2, timeout_s=1.0)]
+    out, errs = _threads(2, lambda r: (lambda t: (world[r].all_reduce(t), t.item())[1])(torch.tensor([r + 1.0])))
+    assert errs == [None, None] and out == [3.0, 3.0]
+    late = FaultPlan().delay_rank(1, "all_reduce", 0, 0.8)
+    world = [FaultyBackend(b, late) for b in MockBackend.create_world(2, timeout_s=0.2)]
+    out, errs = _threads(2, lambda r: world[r].all_reduce(torch.ones(1)))
+    assert isinstance(errs[0], CommTimeout)
+
+
+def test_killed_rank_is_named_by_the_failure_detector_and_training_recovers(tmp_path):
+    """Rank 2 of 3 dies before its second all-reduce.  The survivors' collective times out, the
+    detector names rank 2 from its stopped heartbeat, and the job restarts on two ranks from the
+    last checkpoint."""
+    hb_dir = str(tmp_path / "hb")
+    plan = FaultPlan().kill_rank(2, "all_reduce", nth=1)
+    state = {"world": 3, "resumed_from": None, "ckpt": None}
+
+    def job():
+        n = state["world"]
+        backends = MockBackend.create_world(n, timeout_s=0.5)
+        world = [FaultyBackend(b, plan) for b in backends] if state["resumed_from"] is None else backends
+        det = FailureDetector(hb_dir, n, timeout_s=0.4)
+        start = state["ckpt"] or 0
+
+        def rank_body(r):
+            hb = Heartbeat(hb_dir, r, interval_s=0.05)
+            try:
+                acc = float(start)
+                for step in range(start, 4):
+                    t = torch.tensor([1.0])
+                    world[r].all_reduce(t)
+                    acc += t.item() / n
+                    if r == 0:
+                        state["ckpt"] = step + 1          # "checkpoint" after every completed step
+                return acc
+            finally:
+                hb.stop()
+        out, errs = _threads(n, rank_body)
+        if any(errs):
+            assert isinstance(errs[2], RankKilled)
+            assert all(isinstance(e, CommTimeout) for e in errs[:2])
+            time.sleep(0.5)
+            assert det.dead_ranks() == [2] or set(det.dead_ranks()) >= {2}
+            raise errs[0]
+        return out
+
+    def rebuild(attempt, err):
+        state["world"] = 2                                # the survivors
+        state["resumed_from"] = state["ckpt"]
+    out = run_with_recovery(job, rebuild)
+    assert state["resumed_from"] == 1                      # one step had completed before the failure
+    assert out == [4.0, 4.0]                               # every step counted exactly once
+
+
+def test_heartbeat_detector_sees_a_stopped_rank(tmp_path):
+    d = str(tmp_path)
+    hbs = [Heartbeat(d, r, interval_s=0.05) for r in range(3)]
+    det = FailureDetector(d, 3, timeout_s=0.3)
+    time.sleep(0.15)
+    assert det.dead_ranks() == []
+    det.check()
+    hbs[1].stop()
+    time.sleep(0.5)
+    assert det.dead_ranks() == [1]
+    with pytest.raises(CommTimeout, match=r"\[1\]"):
+        det.check()
+    [h.stop() for h in hbs]
+
+
+def test_signal_protocols_hold_under_random_interleavings():
+    res = check_all(seeds=60)
+    assert res["runs"] == 60 * 7
+
+
+def test_protocol_models_catch_the_known_bugs():
+    # flags owed for the last remote phase must go out before a rank waits on its own rows
+    with pytest.raises(ProtocolError, match="deadlock"):
+        for seed in range(50):
+            ReduceScatterModel(2, 2, 3, calls=1, flush_before_own=False).run(seed)
+    # without the "peer consumed the previous call" wait a fast rank overwrites unread partial tiles
+    with pytest.raises(ProtocolError, match="overwrites|reads"):
+        for seed in range(200):
+            ReduceScatterModel(3, 2, 3, calls=3, wait_done=False).run(seed)
+    # without the closing barrier a fast rank reuses its buffer while a peer still reads it
+    with pytest.raises(ProtocolError, match="reads peer"):
+        for seed in range(200):
+            AllReduceModel(3, 2, calls=3, skip_second_barrier=True).run(seed)
