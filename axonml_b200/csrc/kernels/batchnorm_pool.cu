@@ -184,9 +184,13 @@ bn_bwd_apply_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
 }
 
 // ---------------------------------------------------------------------------- max pooling
+// KT / ST: compile-time window and stride (0 = take the run-time values): with constants the window
+// loops unroll and all loads of a window are in flight together.
+template <int KT, int ST>
 __global__ void __launch_bounds__(kThreads)
 maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, uint8_t* __restrict__ idx,
-                   int N, int H, int W, int C, int Ho, int Wo, int k, int s, int p) {
+                   int N, int H, int W, int C, int Ho, int Wo, int k_rt, int s_rt, int p) {
+  const int k = KT ? KT : k_rt, s = ST ? ST : s_rt;
   const int cv = C / 8;
   const long total = (long)N * Ho * Wo * cv;
   for (long i = (long)blockIdx.x * kThreads + threadIdx.x; i < total; i += (long)gridDim.x * kThreads) {
@@ -199,12 +203,13 @@ maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
     int bi[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; bi[j] = 0; }
+#pragma unroll
     for (int dh = 0; dh < k; ++dh) {
       const int h = ho * s - p + dh;
-      if (h < 0 || h >= H) continue;
+#pragma unroll
       for (int dw = 0; dw < k; ++dw) {
         const int w = wo * s - p + dw;
-        if (w < 0 || w >= W) continue;
+        if (h < 0 || h >= H || w < 0 || w >= W) continue;
         float t[8];
         load8(x + (((long)n * H + h) * W + w) * C + v * 8, t);
 #pragma unroll
@@ -222,9 +227,13 @@ maxpool_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
   }
 }
 
+template <int KT, int ST>
 __global__ void __launch_bounds__(kThreads)
 maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restrict__ idx, __nv_bfloat16* __restrict__ dx,
-                   int N, int H, int W, int C, int Ho, int Wo, int k, int s, int p) {
+                   int N, int H, int W, int C, int Ho, int Wo, int k_rt, int s_rt, int p) {
+  const int k = KT ? KT : k_rt, s = ST ? ST : s_rt;
+  // a pixel lies in at most ceil(k/s) windows per axis
+  constexpr int kMaxWin = (KT && ST) ? (KT + ST - 1) / ST : 0;
   const int cv = C / 8;
   const long total = (long)N * H * W * cv;
   for (long i = (long)blockIdx.x * kThreads + threadIdx.x; i < total; i += (long)gridDim.x * kThreads) {
@@ -239,10 +248,16 @@ maxpool_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const uint8_t* __restri
     // output windows that contain (h, w): ho*s - p <= h < ho*s - p + k
     const int ho_lo = max(0, (h + p - k + s) / s), ho_hi = min(Ho - 1, (h + p) / s);
     const int wo_lo = max(0, (w + p - k + s) / s), wo_hi = min(Wo - 1, (w + p) / s);
-    for (int ho = ho_lo; ho <= ho_hi; ++ho) {
+#pragma unroll
+    for (int a = 0; a < (kMaxWin ? kMaxWin : 1 << 30); ++a) {
+      const int ho = ho_lo + a;
+      if (ho > ho_hi) break;
       const int dh = h - (ho * s - p);
       if (dh < 0 || dh >= k) continue;
-      for (int wo = wo_lo; wo <= wo_hi; ++wo) {
+#pragma unroll
+      for (int b = 0; b < (kMaxWin ? kMaxWin : 1 << 30); ++b) {
+        const int wo = wo_lo + b;
+        if (wo > wo_hi) break;
         const int dw = w - (wo * s - p);
         if (dw < 0 || dw >= k) continue;
         const long o = ((((long)n * Ho + ho) * Wo + wo) * cv + v) * 8;
@@ -339,8 +354,15 @@ AX_API int ax_maxpool2d_fwd(const void* x, void* y, void* idx, int N, int H, int
   const int Ho = (H + 2 * p - k) / s + 1, Wo = (W + 2 * p - k) / s + 1;
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
   const long total = (long)N * Ho * Wo * (C / 8);
-  maxpool_fwd_kernel<<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)idx, N, H,
-                                                               W, C, Ho, Wo, k, s, p);
+  if (k == 3 && s == 2)
+    maxpool_fwd_kernel<3, 2><<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+                                                                       (uint8_t*)idx, N, H, W, C, Ho, Wo, k, s, p);
+  else if (k == 2 && s == 2)
+    maxpool_fwd_kernel<2, 2><<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+                                                                       (uint8_t*)idx, N, H, W, C, Ho, Wo, k, s, p);
+  else
+    maxpool_fwd_kernel<0, 0><<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y,
+                                                                       (uint8_t*)idx, N, H, W, C, Ho, Wo, k, s, p);
   return (int)cudaGetLastError();
 }
 
@@ -350,7 +372,14 @@ AX_API int ax_maxpool2d_bwd(const void* dy, const void* idx, void* dx, int N, in
   const int Ho = (H + 2 * p - k) / s + 1, Wo = (W + 2 * p - k) / s + 1;
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
   const long total = (long)N * H * W * (C / 8);
-  maxpool_bwd_kernel<<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)dy, (const uint8_t*)idx, (__nv_bfloat16*)dx,
-                                                               N, H, W, C, Ho, Wo, k, s, p);
+  if (k == 3 && s == 2)
+    maxpool_bwd_kernel<3, 2><<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)dy, (const uint8_t*)idx,
+                                                                       (__nv_bfloat16*)dx, N, H, W, C, Ho, Wo, k, s, p);
+  else if (k == 2 && s == 2)
+    maxpool_bwd_kernel<2, 2><<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)dy, (const uint8_t*)idx,
+                                                                       (__nv_bfloat16*)dx, N, H, W, C, Ho, Wo, k, s, p);
+  else
+    maxpool_bwd_kernel<0, 0><<<grid_for(total), kThreads, 0, stream>>>((const __nv_bfloat16*)dy, (const uint8_t*)idx,
+                                                                       (__nv_bfloat16*)dx, N, H, W, C, Ho, Wo, k, s, p);
   return (int)cudaGetLastError();
 }
