@@ -9,7 +9,7 @@ __version__ = "0.1.0"
 
 _SUBPACKAGES = ("core", "tensor", "autograd", "nn", "optim", "data", "vision", "text", "audio", "llm", "parallel",
                 "serialize", "quant", "fusion", "jit", "profile", "onnx", "hub", "server", "cli", "trainer", "benchmark",
-                "ops")
+                "ops", "integrations", "utils")
 _ALIASES = {"distributed": "parallel"}           # the reference's crate name
 
 

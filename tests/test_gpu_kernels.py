@@ -322,3 +322,59 @@ def test_jit_nvrtc_fused_elementwise_matches_interpreter(kernel_status):
     out = jit.compile_graph(g).run_tensors({"a": a, "b": b})["y"]
     assert out.is_cuda
     assert (out.cpu() - ref).abs().max().item() < 2e-3
+
+
+def test_kernels_do_not_write_outside_their_outputs(kernel_status):
+    """Outputs carved out of canary-padded allocations (a stand-in for a memory checker): ragged
+    sizes for the elementwise kernels, non-multiple-of-tile GEMM shapes, padded vocabulary columns
+    in the cross-entropy backward, pooling with a window that hangs over the border."""
+    from axonml_b200 import _native as N
+    from axonml_b200.ops.gemm import gemm_bf16
+    from axonml_b200.utils.canary import guarded
+    L, st = N.cuda(), N.stream_ptr()
+    torch.manual_seed(0)
+    for n in (1, 7, 33, 1000, 4097):
+        x = torch.randn(n, device="cuda").bfloat16()
+        y = guarded((n,), torch.bfloat16)
+        assert L.ax_unary(1, 8, N.ptr(x), N.ptr(y.tensor), N.c_int64(n), N.c_float(0.0), N.c_float(0.0), st) == 0      # GELU
+        z = guarded((n,), torch.bfloat16)
+        assert L.ax_binary(1, 2, N.ptr(x), N.ptr(x), N.ptr(z.tensor), N.c_int64(n), N.c_float(0.0), st) == 0            # mul
+        torch.cuda.synchronize()
+        y.check(f"unary n={n}"); z.check(f"binary n={n}")
+        assert torch.allclose(z.tensor.float(), (x.float() ** 2).bfloat16().float(), atol=1e-2, rtol=1e-2)
+    for (m, nn_, k) in ((128, 128, 64), (200, 136, 72), (1, 8, 8), (384, 520, 264)):
+        a = torch.randn(m, k, device="cuda").bfloat16()
+        b = torch.randn(nn_, k, device="cuda").bfloat16()
+        out = guarded((m, nn_), torch.bfloat16)
+        gemm_bf16(a, b, out=out.tensor)
+        torch.cuda.synchronize()
+        out.check(f"gemm {m}x{nn_}x{k}")
+        assert torch.allclose(out.tensor.float(), a.float() @ b.float().t(), atol=0.5, rtol=5e-2)
+    rows, D = 37, 1024
+    x = torch.randn(rows, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    y = guarded((rows, D), torch.bfloat16)
+    mean, rstd = guarded((rows,), torch.float32), guarded((rows,), torch.float32)
+    assert L.ax_norm_fwd(0, 1, 1, N.ptr(x), N.ptr(None), N.ptr(w), N.ptr(w), N.ptr(y.tensor), N.ptr(None), N.ptr(mean.tensor),
+                         N.ptr(rstd.tensor), rows, D, N.c_float(1e-5), st) == 0
+    rows, V, stride = 5, 1003, 1024
+    logits = torch.randn(rows, stride, device="cuda").bfloat16()
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    lse = torch.logsumexp(logits[:, :V].float(), -1)
+    dl = guarded((rows, stride), torch.bfloat16)
+    assert L.ax_ce_bwd(1, N.ptr(logits), N.ptr(tgt), N.ptr(lse), N.ptr(None), 0, N.c_float(1.0), N.ptr(dl.tensor), rows, V,
+                       stride, N.c_int64(stride), N.c_int64(-100), st) == 0
+    n_, h, w_, c = 2, 7, 9, 16
+    xp = torch.randn(n_, h, w_, c, device="cuda").bfloat16()
+    ho, wo = (h + 2 - 3) // 2 + 1, (w_ + 2 - 3) // 2 + 1
+    yp, ip = guarded((n_, ho, wo, c), torch.bfloat16), guarded((n_, ho, wo, c), torch.uint8)
+    assert L.ax_maxpool2d_fwd(N.ptr(xp), N.ptr(yp.tensor), N.ptr(ip.tensor), n_, h, w_, c, 3, 2, 1, st) == 0
+    dxp = guarded((n_, h, w_, c), torch.bfloat16)
+    assert L.ax_maxpool2d_bwd(N.ptr(yp.tensor), N.ptr(ip.tensor), N.ptr(dxp.tensor), n_, h, w_, c, 3, 2, 1, st) == 0
+    torch.cuda.synchronize()
+    for g, what in ((y, "norm y"), (mean, "norm mean"), (rstd, "norm rstd"), (dl, "ce dlogits"), (yp, "pool y"),
+                    (ip, "pool idx"), (dxp, "pool dx")):
+        g.check(what)
+    assert float(dl.tensor[:, V:].abs().max()) == 0.0
+    ref = torch.nn.functional.max_pool2d(xp.permute(0, 3, 1, 2).float(), 3, 2, 1).permute(0, 2, 3, 1)
+    assert torch.equal(yp.tensor.float(), ref)
