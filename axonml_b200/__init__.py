@@ -22,6 +22,24 @@ def __getattr__(name):
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
+def version() -> str:
+    return __version__
+
+
+def features() -> str:
+    """Comma-separated list of what this installation can use (the reference prints its cargo
+    features, crates/axonml/src/lib.rs)."""
+    import torch
+    f = ["core", "nn", "optim", "data", "vision", "text", "audio", "llm", "distributed", "serialize", "onnx", "quant",
+         "fusion", "jit", "profile", "server", "cli"]
+    if torch.cuda.is_available():
+        f.append("cuda")
+        from . import _native
+        if _native.is_blackwell():
+            f.append("sm_100a-kernels")
+    return ", ".join(f)
+
+
 def prelude() -> dict:
     """Names of the reference's prelude: tensor constructors, Variable, layers, losses,
     optimizers, data loading and the trainer helpers."""

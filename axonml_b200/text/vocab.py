@@ -35,6 +35,10 @@ class Vocab:
 
     @classmethod
     def from_text(cls, text: str, tokenizer=None, min_freq: int = 1):
+        """``from_text(corpus, 1)`` (the reference's ``Vocab::from_text(text, min_freq)``) or
+        ``from_text(corpus, tokenizer, min_freq)``."""
+        if isinstance(tokenizer, int):
+            tokenizer, min_freq = None, tokenizer
         toks = tokenizer(text) if tokenizer else text.split()
         return cls.from_tokens(toks, min_freq)
 
