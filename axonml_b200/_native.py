@@ -41,7 +41,8 @@ class _CountingLib:
     """Forwards attribute access to the ctypes library and counts calls of the kernel launchers
     (every ``ax_*`` entry that takes a stream launches at least one kernel)."""
 
-    _NO_LAUNCH = {"ax_version", "ax_sm_count", "ax_norm_bwd_groups", "ax_multi_tensor_limits"}
+    _NO_LAUNCH = {"ax_version", "ax_sm_count", "ax_norm_bwd_groups", "ax_multi_tensor_limits", "ax_gemm_comm_set_trace",
+                  "ax_flash_fwd_set_trace", "ax_gemm_comm_signal_slots", "ax_norm_bwd_noalloc_limits"}
 
     def __init__(self, lib):
         self._lib = lib
