@@ -554,3 +554,61 @@ AX_API int ax_conv2d_wgrad(const void* dy, const void* x, float* dw, int N, int 
   }
   return BNC == 128 ? launch_wgrad<128>(mdy, mx, p, grid, stream) : launch_wgrad<64>(mdy, mx, p, grid, stream);
 }
+
+// ---------------------------------------------------------------------------- im2col for thin inputs
+// Convolutions whose input has fewer than 64 channels (an RGB stem) cannot use the tap-wise TMA
+// path (its boxes are 64 channels wide).  Their patches are gathered into a matrix col[N*Ho*Wo, Kp]
+// which the tcgen05 GEMM multiplies by the [Cout, Kp] filter matrix; the product is the NHWC output.
+// One filter row of a patch is KW*C contiguous input values; it is stored padded to RP (a multiple
+// of 8) values, k = kh*RP + kw*C + c, so every 16-byte chunk of `col` comes from one contiguous run
+// of the input and no index needs a division by C.  Columns past KH*RP are zero.
+namespace {
+__global__ void __launch_bounds__(256)
+im2col_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ col, int Nimg, int H, int W, int C,
+                   int Ho, int Wo, int KH, int KW, int stride, int pad_h, int pad_w, int RP, int Kp) {
+  const int cpr = RP / 8;                     // chunks per filter row
+  const int chunks = Kp / 8;                  // chunks per output pixel
+  const long total = (long)Nimg * Ho * Wo * chunks;
+  const int row_run = KW * C;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int cc = (int)(i % chunks);
+    long r = i / chunks;
+    const int wo = (int)(r % Wo); r /= Wo;
+    const int ho = (int)(r % Ho);
+    const int n = (int)(r / Ho);
+    const int kh = cc / cpr, c8 = cc - kh * cpr;
+    const int h = ho * stride - pad_h + kh;
+    const int w0 = wo * stride - pad_w;
+    __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = zero;
+    if (kh < KH && h >= 0 && h < H) {
+      const __nv_bfloat16* src = x + (((long)n * H + h) * W + w0) * C;     // run start (may lie left of the row)
+      const int lo = -w0 * C, hi = (W - w0) * C;                           // valid offsets inside the image row
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int t = c8 * 8 + j;
+        if (t < row_run && t >= lo && t < hi) v[j] = src[t];
+      }
+    }
+    *reinterpret_cast<uint4*>(col + i * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+}  // namespace
+
+// x: NHWC bf16 [N, H, W, C]; col: [N*Ho*Wo, Kp] bf16; RP = KW*C rounded up to a multiple of 8,
+// Kp a multiple of 8 with Kp >= KH*RP.
+AX_API int ax_im2col_nhwc(const void* x, void* col, int N, int H, int W, int C, int KH, int KW, int stride, int pad_h,
+                          int pad_w, int RP, int Kp, cudaStream_t stream) {
+  if (N <= 0 || C <= 0 || KH <= 0 || KW <= 0 || stride <= 0 || RP % 8 || RP < KW * C || Kp % 8 || Kp < KH * RP) return -1;
+  const int Ho = (H + 2 * pad_h - KH) / stride + 1, Wo = (W + 2 * pad_w - KW) / stride + 1;
+  if (Ho <= 0 || Wo <= 0) return -1;
+  const long total = (long)N * Ho * Wo * (Kp / 8);
+  long grid = (total + 255) / 256;
+  const long cap = (long)axh::sm_count() * 16;
+  if (grid > cap) grid = cap;
+  im2col_nhwc_kernel<<<(int)grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)col, N, H, W, C, Ho, Wo, KH, KW,
+                                                    stride, pad_h, pad_w, RP, Kp);
+  return (int)cudaGetLastError();
+}

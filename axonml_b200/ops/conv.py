@@ -7,7 +7,7 @@ import torch
 
 def conv2d_supported(x, weight, stride, padding) -> bool:
     from . import conv_igemm
-    return conv_igemm.supported(x, weight, stride, padding)
+    return conv_igemm.supported(x, weight, stride, padding) or conv_igemm.thin_supported(x, weight, stride, padding)
 
 
 def conv2d(x, weight, bias, stride, padding):

@@ -102,4 +102,71 @@ class _ConvFn(torch.autograd.Function):
 
 
 def conv2d(x, weight, bias, stride, padding):
+    if weight.shape[1] < 64:
+        return _ThinConvFn.apply(x, weight, bias, tuple(stride), tuple(padding))
     return _ConvFn.apply(x, weight, bias, tuple(padding))
+
+
+# ------------------------------------------------------------------------------ thin inputs (RGB stem)
+def thin_supported(x, weight, stride, padding) -> bool:
+    """Convolutions with fewer than 64 input channels (any stride): patches are gathered by the
+    im2col kernel and multiplied by the tcgen05 GEMM."""
+    if not (N.is_blackwell() and x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16):
+        return False
+    cout, cin, kh, kw = weight.shape
+    if cin >= 64 or cout % 8 or kh * ((kw * cin + 7) // 8 * 8) > 1024 or stride[0] != stride[1]:
+        return False
+    if not x.is_contiguous(memory_format=torch.channels_last):
+        return False
+    n, _, h, w = x.shape
+    ho = (h + 2 * padding[0] - kh) // stride[0] + 1
+    wo = (w + 2 * padding[1] - kw) // stride[1] + 1
+    return ho > 0 and wo > 0 and n * ho * wo >= 128
+
+
+def thin_fprop(x, weight, bias, stride, padding):
+    from .gemm import gemm_bf16
+    n, cin, h, w = x.shape
+    cout, _, kh, kw = weight.shape
+    ho = (h + 2 * padding[0] - kh) // stride[0] + 1
+    wo = (w + 2 * padding[1] - kw) // stride[1] + 1
+    rp = (kw * cin + 7) // 8 * 8                      # one filter row of a patch, padded to 16-byte chunks
+    kp = (kh * rp + 63) // 64 * 64
+    col = torch.empty((n * ho * wo, kp), dtype=torch.bfloat16, device=x.device)
+    rc = N.cuda().ax_im2col_nhwc(N.ptr(x), N.ptr(col), n, h, w, cin, kh, kw, stride[0], padding[0], padding[1], rp, kp,
+                                 N.stream_ptr())
+    N.check(rc, "ax_im2col_nhwc")
+    w_rows = torch.zeros((cout, kh, rp), dtype=torch.bfloat16, device=x.device)
+    w_rows[:, :, :kw * cin] = weight.detach().permute(0, 2, 3, 1).reshape(cout, kh, kw * cin)   # (kh | kw, cin) as the patches
+    w2d = torch.zeros((cout, kp), dtype=torch.bfloat16, device=x.device)
+    w2d[:, :kh * rp] = w_rows.reshape(cout, kh * rp)
+    y = torch.empty((n, cout, ho, wo), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+    out2d = y.permute(0, 2, 3, 1).reshape(n * ho * wo, cout)                      # a view: NHWC storage
+    if bias is not None and bias.dtype not in (torch.float32, torch.bfloat16):
+        bias = bias.float()
+    gemm_bf16(col, w2d, bias=None if bias is None else bias.detach(), out=out2d)
+    return y
+
+
+class _ThinConvFn(torch.autograd.Function):
+    """Forward on this package's kernels; the gradients of this one layer (usually only the weight
+    gradient: the network input needs none) come from the library convolution backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, padding):
+        ctx.stride, ctx.padding = stride, padding
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return thin_fprop(x, weight, bias, stride, padding)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        if not dy.is_contiguous(memory_format=torch.channels_last):
+            dy = dy.contiguous(memory_format=torch.channels_last)
+        mask = (ctx.needs_input_grad[0], ctx.needs_input_grad[1], False)
+        dx, dw, _ = torch.ops.aten.convolution_backward(dy, x, weight.detach().to(torch.bfloat16), None, list(ctx.stride),
+                                                        list(ctx.padding), [1, 1], False, [0, 0], 1, list(mask))
+        db = dy.float().sum(dim=(0, 2, 3)).to(ctx.bias_dtype) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        return dx, (dw.to(weight.dtype) if dw is not None else None), db, None, None

@@ -122,3 +122,27 @@ def test_batchnorm_eval_and_maxpool(kernel_status):
         o2.backward(g.float())
         assert torch.equal(o.float(), o2)
         assert (x1.grad.float() - x2.grad).abs().max().item() < 0.02
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,hw", [(3, 64, 7, 2, 3, 64), (3, 32, 3, 1, 1, 33), (1, 16, 5, 2, 2, 28), (4, 64, 7, 2, 3, 224)])
+def test_thin_input_convolution_im2col_gemm(cin, cout, k, stride, pad, hw, kernel_status):
+    """The RGB-stem path (im2col kernel + tcgen05 GEMM) against the fp32 convolution, with the
+    gradients of weight and bias."""
+    from axonml_b200.ops import conv_igemm as CI
+    torch.manual_seed(0)
+    n = 4
+    x = torch.randn(n, cin, hw, hw, device="cuda").bfloat16().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(cout, cin, k, k, device="cuda") * 0.1).requires_grad_()
+    b = torch.randn(cout, device="cuda").requires_grad_()
+    assert CI.thin_supported(x, w, (stride, stride), (pad, pad))
+    y = CI.conv2d(x, w, b, (stride, stride), (pad, pad))
+    assert y.is_contiguous(memory_format=torch.channels_last)
+    wr, br = w.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    ref = F.conv2d(x.float(), wr.bfloat16().float(), br, stride, pad)
+    assert y.shape == ref.shape
+    assert (y.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 0.05
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float())
+    assert (w.grad - wr.grad).abs().max().item() < 0.03 * wr.grad.abs().max().item() + 1e-2
+    assert (b.grad - br.grad).abs().max().item() < 0.02 * br.grad.abs().max().item() + 1e-2
