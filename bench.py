@@ -554,6 +554,94 @@ def bench_llama_tp_pp(args):
     return _finish(world)
 
 
+def bench_published_micro(args):
+    """The four operations of the reference's published table (docs/index.md:128-133: MatMul
+    1024x1024 f32 2.1 ms, Conv2d 224x224 4.3 ms, LSTM seq 128 8.2 ms, Adam step 0.8 ms, one CPU
+    thread of a Ryzen 9 5900X) timed here on one CPU thread of this host and, when a GPU is present,
+    on this package's kernels.  The table does not state the convolution's channels, the LSTM's
+    width or the Adam parameter count; the shapes used are given in `config`."""
+    import torch
+    from axonml_b200 import nn, optim
+    published = {"matmul_1024_f32": 2.1, "conv2d_224": 4.3, "lstm_seq128": 8.2, "adam_step": 0.8}
+    iters = args.steps if args.steps != 8 else 20
+
+    def cpu_ms(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        return (time.perf_counter() - t0) / iters * 1e3
+
+    def gpu_ms(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def build(dev, dt):
+        torch.manual_seed(0)
+        a, b = torch.randn(1024, 1024, device=dev, dtype=dt), torch.randn(1024, 1024, device=dev, dtype=dt)
+        conv = nn.Conv2d(3, 16, 3, 1, 1).to(dev, dt)
+        x = torch.randn(1, 3, 224, 224, device=dev, dtype=dt)
+        if dev == "cuda":
+            x = x.contiguous(memory_format=torch.channels_last)
+        lstm = nn.LSTM(128, 128, 1).to(dev, dt)
+        seq = torch.randn(1, 128, 128, device=dev, dtype=dt)
+        lin = nn.Linear(1000, 1000).to(dev)
+        opt = optim.Adam(list(lin.parameters()), 1e-3)
+        for p in lin.parameters():
+            p.grad = torch.randn_like(p)
+        with torch.no_grad():
+            ops = {"matmul_1024_f32": lambda: a @ b, "conv2d_224": lambda: conv(x), "lstm_seq128": lambda: lstm(seq)}
+        ops["adam_step"] = opt.step
+        return ops
+
+    torch.set_num_threads(1)
+    cpu_ops = build("cpu", torch.float32)
+    res = {}
+    with torch.no_grad():
+        for k in ("matmul_1024_f32", "conv2d_224", "lstm_seq128"):
+            res[k] = {"cpu_ms": round(cpu_ms(cpu_ops[k]), 3)}
+    res["adam_step"] = {"cpu_ms": round(cpu_ms(cpu_ops["adam_step"]), 3)}
+    launches = 0
+    if torch.cuda.is_available():
+        from axonml_b200 import _native
+        gpu_ops = build("cuda", torch.bfloat16)
+        n0 = _native.cuda().launches
+        with torch.no_grad():
+            for k in ("matmul_1024_f32", "conv2d_224", "lstm_seq128"):
+                res[k]["gpu_ms"] = round(gpu_ms(gpu_ops[k]), 4)
+        res["adam_step"]["gpu_ms"] = round(gpu_ms(gpu_ops["adam_step"]), 4)
+        launches = _native.cuda().launches - n0
+    on_gpu = torch.cuda.is_available()
+    geo = 1.0
+    for k, v in res.items():
+        v["published_ms"] = published[k]
+        v["published_over_cpu"] = round(published[k] / v["cpu_ms"], 2)
+        if on_gpu:
+            v["published_over_gpu"] = round(published[k] / v["gpu_ms"], 1)
+        geo *= published[k] / (v["gpu_ms"] if on_gpu else v["cpu_ms"])
+    geo **= 0.25
+    where = "one B200, this package's kernels" if on_gpu else "1 CPU thread of this host"
+    print(json.dumps({"metric": "published CPU micro-table (matmul 1024^2, conv2d 224^2, LSTM seq 128, Adam step)",
+                      "value": round(geo, 3), "unit": f"x the published speed (geometric mean of published ms / ours; {where})",
+                      "n_gpus": 1 if torch.cuda.is_available() else 0, "steps": iters, "warmup": max(args.warmup, 3),
+                      "ms_per_step": None, "higher_is_better": True, "scaling": "strong", "vs_baseline": round(geo, 3),
+                      "dtype": "fp32 on the CPU, bf16 on the GPU", "data": "synthetic", "impl": "axonml_b200",
+                      "config": {"matmul": "1024x1024x1024", "conv2d": "1x3x224x224, 16 filters 3x3 pad 1",
+                                 "lstm": "1 layer, 128 -> 128, sequence 128, batch 1", "adam": "1000x1000 weight + bias",
+                                 "l2_policy": "operands fit in cache, as in the published table"},
+                      "ops": res, "gpu_launches": launches}), flush=True)
+    return 0
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -570,6 +658,8 @@ def main():
         return bench_resnet_ddp(args)
     if args.config == "lenet_cpu":
         return bench_lenet_cpu(args)
+    if args.config == "published_micro":
+        return bench_published_micro(args)
     return bench_gpt_fsdp(args)
 
 
