@@ -64,21 +64,28 @@ class Adam(Optimizer):
             return
         for p in rest:
             st = self._state(p, names)
-            g = self._grad(p)
-            pf = p.float()
-            if self._DECOUPLED:
-                pf = pf * (1 - self.lr * self._weight_decay)
-            elif self._weight_decay:
-                g = g + self._weight_decay * pf
+            g = self._grad(p)                              # may alias p.grad: never modified in place
             m, v = st["exp_avg"], st["exp_avg_sq"]
-            m.mul_(b1).add_(g, alpha=1 - b1)
-            v.mul_(b2).addcmul_(g, g, value=1 - b2)
-            vv = v
-            if self._amsgrad:
-                torch.maximum(st["max_exp_avg_sq"], v, out=st["max_exp_avg_sq"])
-                vv = st["max_exp_avg_sq"]
-            denom = (vv / bc2).sqrt() + self._eps
-            self._write(p, (pf - (self.lr / bc1) * m / denom).to(p.dtype))
+            with torch.no_grad():
+                w = p if p.dtype == torch.float32 else p.float()      # fp32 parameters are updated in place
+                if self._DECOUPLED:
+                    if self._weight_decay:
+                        w.mul_(1 - self.lr * self._weight_decay)
+                elif self._weight_decay:
+                    g = g + self._weight_decay * w
+                m.mul_(b1).add_(g, alpha=1 - b1)
+                v.mul_(b2).addcmul_(g, g, value=1 - b2)
+                vv = v
+                if self._amsgrad:
+                    torch.maximum(st["max_exp_avg_sq"], v, out=st["max_exp_avg_sq"])
+                    vv = st["max_exp_avg_sq"]
+                denom = vv.sqrt().div_(bc2 ** 0.5).add_(self._eps)      # sqrt(v / bc2) + eps, one temporary
+                w.addcdiv_(m, denom, value=-(self.lr / bc1))
+                if w is not p:
+                    p.copy_(w)
+                lp = getattr(p, "_axon_lp", None)
+                if lp is not None:
+                    lp.copy_(p)
 
 
 class AdamW(Adam):
