@@ -595,6 +595,44 @@ im2col_nhwc_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
     *reinterpret_cast<uint4*>(col + i * 8) = *reinterpret_cast<const uint4*>(v);
   }
 }
+// Same result, one CTA per output row (n, ho): the KH input rows the row needs are brought into
+// shared memory with 16-byte loads (rows outside the image as zeros), and every 16-byte chunk of
+// `col` is assembled from shared memory.  Needs W*C % 8 == 0 (16-byte rows) and KH rows to fit.
+__global__ void __launch_bounds__(256)
+im2col_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ col, int H, int W, int C, int Ho,
+                   int Wo, int KH, int KW, int stride, int pad_h, int pad_w, int RP, int Kp) {
+  extern __shared__ __align__(16) __nv_bfloat16 rows[];          // [KH][W*C]
+  const int n = blockIdx.x / Ho, ho = blockIdx.x - n * Ho;
+  const int rowlen = W * C, vec_per_row = rowlen / 8;
+  for (int i = threadIdx.x; i < KH * vec_per_row; i += blockDim.x) {
+    const int kh = i / vec_per_row, v = i - kh * vec_per_row;
+    const int h = ho * stride - pad_h + kh;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (h >= 0 && h < H) val = *reinterpret_cast<const uint4*>(x + ((long)n * H + h) * rowlen + v * 8);
+    *reinterpret_cast<uint4*>(rows + kh * rowlen + v * 8) = val;
+  }
+  __syncthreads();
+  const int cpr = RP / 8, chunks = Kp / 8, row_run = KW * C;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
+  __nv_bfloat16* out = col + ((long)n * Ho + ho) * Wo * Kp;
+  for (int i = threadIdx.x; i < Wo * chunks; i += blockDim.x) {
+    const int wo = i / chunks, cc = i - wo * chunks;
+    const int kh = cc / cpr, c8 = cc - kh * cpr;
+    __nv_bfloat16 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = zero;
+    if (kh < KH) {
+      const int start = (wo * stride - pad_w) * C;                 // offset of the run inside the image row
+      const __nv_bfloat16* src = rows + kh * rowlen;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int t = c8 * 8 + j, o = start + t;
+        if (t < row_run && o >= 0 && o < rowlen) v[j] = src[o];
+      }
+    }
+    *reinterpret_cast<uint4*>(out + (long)i * 8) = *reinterpret_cast<const uint4*>(v);
+  }
+}
 }  // namespace
 
 // x: NHWC bf16 [N, H, W, C]; col: [N*Ho*Wo, Kp] bf16; RP = KW*C rounded up to a multiple of 8,
@@ -604,6 +642,12 @@ AX_API int ax_im2col_nhwc(const void* x, void* col, int N, int H, int W, int C, 
   if (N <= 0 || C <= 0 || KH <= 0 || KW <= 0 || stride <= 0 || RP % 8 || RP < KW * C || Kp % 8 || Kp < KH * RP) return -1;
   const int Ho = (H + 2 * pad_h - KH) / stride + 1, Wo = (W + 2 * pad_w - KW) / stride + 1;
   if (Ho <= 0 || Wo <= 0) return -1;
+  const size_t row_smem = (size_t)KH * W * C * sizeof(__nv_bfloat16);
+  if ((W * C) % 8 == 0 && row_smem <= 48 * 1024 && (((uintptr_t)x) & 15) == 0 && Wo * (Kp / 8) >= 256) {
+    im2col_rows_kernel<<<N * Ho, 256, row_smem, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)col, H, W, C, Ho, Wo, KH,
+                                                          KW, stride, pad_h, pad_w, RP, Kp);
+    return (int)cudaGetLastError();
+  }
   const long total = (long)N * Ho * Wo * (Kp / 8);
   long grid = (total + 255) / 256;
   const long cap = (long)axh::sm_count() * 16;
