@@ -93,9 +93,49 @@ class _Recurrent(Module):
         h = cell(x, state)
         return h, h
 
+    SEQ_KIND = 0          # 4 = LSTM, 3 = GRU: cell types the whole-sequence kernel implements
+
+    def _fused_sequence(self, x, state):
+        """Inference on a B200 with H <= 128: one GEMM for all input projections of a layer, then
+        one kernel for the whole sequence (csrc/kernels/rnn_seq.cu).  Returns None when the
+        step-by-step path has to run (training, other devices, larger H, fp32 modules)."""
+        from ... import _native as N
+        if (self.SEQ_KIND == 0 or torch.is_grad_enabled() or not x.is_cuda or x.dtype != torch.bfloat16
+                or self.hidden_size > 128 or not N.is_blackwell() or x.shape[1] == 0):
+            return None
+        if any(c.weight_hh.dtype != torch.bfloat16 for c in self.cells):
+            return None
+        B, T, _ = x.shape
+        H, G = self.hidden_size, self.SEQ_KIND
+        inp = x.contiguous()
+        states = []
+        for li, cell in enumerate(self.cells):
+            xproj = _linear(inp.reshape(B * T, -1), cell.weight_ih, cell.bias_ih).float().contiguous()
+            st = state[li] if state is not None else None
+            h0 = c0 = None
+            if st is not None:
+                h0, c0 = (st if G == 4 else (st, None))
+                h0 = h0.float().contiguous()
+                c0 = c0.float().contiguous() if c0 is not None else None
+            out = torch.empty((B, T, H), dtype=torch.bfloat16, device=x.device)
+            h_last = torch.empty((B, H), dtype=torch.float32, device=x.device)
+            c_last = torch.empty((B, H), dtype=torch.float32, device=x.device) if G == 4 else None
+            rc = N.cuda().ax_rnn_seq_fwd(G, N.ptr(xproj), N.ptr(cell.weight_hh.detach().contiguous()),
+                                         N.ptr(cell.bias_hh.detach().float().contiguous()), N.ptr(h0), N.ptr(c0), N.ptr(out), 1,
+                                         N.ptr(h_last), N.ptr(c_last), B, T, H, N.stream_ptr())
+            N.check(rc, "ax_rnn_seq_fwd")
+            hl = h_last.to(x.dtype)
+            states.append((hl, c_last.to(x.dtype)) if G == 4 else hl)
+            inp = out
+        self.last_state = states
+        return inp
+
     def forward(self, x, state=None):
         if not self.batch_first:
             x = x.transpose(0, 1)
+        fused = self._fused_sequence(x, state)
+        if fused is not None:
+            return fused if self.batch_first else fused.transpose(0, 1)
         B, T, _ = x.shape
         states = list(state) if state is not None else [None] * self.num_layers
         outs = []
@@ -123,10 +163,12 @@ class RNN(_Recurrent):
 
 class GRU(_Recurrent):
     CELL = GRUCell
+    SEQ_KIND = 3
 
 
 class LSTM(_Recurrent):
     CELL = LSTMCell
+    SEQ_KIND = 4
 
     def _step(self, cell, x, state):
         h, c = cell(x, state)

@@ -378,3 +378,31 @@ def test_kernels_do_not_write_outside_their_outputs(kernel_status):
     assert float(dl.tensor[:, V:].abs().max()) == 0.0
     ref = torch.nn.functional.max_pool2d(xp.permute(0, 3, 1, 2).float(), 3, 2, 1).permute(0, 2, 3, 1)
     assert torch.equal(yp.tensor.float(), ref)
+
+
+@pytest.mark.parametrize("kind,hidden,layers,batch,steps", [("lstm", 128, 1, 1, 128), ("lstm", 48, 2, 3, 17), ("gru", 128, 2, 4, 60),
+                                                           ("gru", 20, 1, 2, 9)])
+def test_whole_sequence_rnn_kernel_matches_the_step_by_step_path(kind, hidden, layers, batch, steps, kernel_status):
+    """LSTM / GRU inference through the one-kernel-per-layer path against the same module evaluated
+    step by step in fp32."""
+    from axonml_b200 import nn
+    torch.manual_seed(0)
+    cls = nn.LSTM if kind == "lstm" else nn.GRU
+    ref = cls(24, hidden, layers)
+    for c in ref.cells:                                  # non-zero biases exercise both bias paths
+        c.bias_ih.data.uniform_(-0.2, 0.2)
+        c.bias_hh.data.uniform_(-0.2, 0.2)
+    import copy
+    m = copy.deepcopy(ref).to("cuda", torch.bfloat16)
+    for cr, cm in zip(ref.cells, m.cells):               # compare at the weights the GPU module really holds
+        for n in ("weight_ih", "weight_hh", "bias_ih", "bias_hh"):
+            getattr(cr, n).data.copy_(getattr(cm, n).data.float().cpu())
+    x = torch.randn(batch, steps, 24)
+    with torch.no_grad():
+        want = ref(x)
+        got = m(x.to("cuda", torch.bfloat16))
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    assert (got.float().cpu() - want).abs().max().item() < 4e-2
+    last = m.last_state[-1]
+    h_last = last[0] if kind == "lstm" else last
+    assert (h_last.float().cpu() - want[:, -1]).abs().max().item() < 4e-2
