@@ -1,0 +1,173 @@
+// Q4_K matrix-vector products for decode batches of 1..8 rows.
+//
+// The tensor-core dequantising matmul (qgemm.cu) expands every weight tile through shared memory;
+// at batch 1 that work is wasted and the kernel sits at 0.18 of the HBM roofline.  Here a warp
+// owns one output row: each lane loads 16 bytes of packed nibbles straight from global memory
+// (32 weights), splits them into low / high nibbles with two logic ops per word and multiplies
+// them against the int8-quantised activations with dp4a (0.5 instructions per weight).  The
+// activations are quantised once per call into 32-wide blocks (scale and block sum, as llama.cpp's
+// Q8_1 does), so that
+//     sum_i (d*sc*q_i - dmin*m) * (dx*q8_i) = d*sc*dx * dot(q, q8) - dmin*m * (dx * sum q8).
+//
+// Weight layouts: GGML row-major super-blocks, or the tile-contiguous layout of qgemm.cu
+// ([N/128][K/256][128 rows][144 bytes]).  Super-block: half d, half dmin, 12 bytes of 6-bit
+// scales/mins, 128 bytes of nibbles (byte l of group g: low nibble = weight 64g+l, high nibble =
+// weight 64g+32+l) - the GGUF Q4_K format the reference's quantiser family extends
+// (crates/axonml-quant/src/types.rs:57-67).
+#include "common.cuh"
+
+namespace {
+using namespace ax;
+
+constexpr int kSB = 144;                   // bytes of one Q4_K super-block (256 weights)
+
+// activations: one warp per 32-wide block
+__global__ void __launch_bounds__(256)
+q8_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long ldx, int8_t* __restrict__ x8, float* __restrict__ dx,
+                        float* __restrict__ sx, int B, int K) {
+  const int lane = threadIdx.x & 31;
+  const long blk = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int per_row = K / 32;
+  if (blk >= (long)B * per_row) return;
+  const int b = (int)(blk / per_row), i = (int)(blk - (long)b * per_row);
+  const float v = __bfloat162float(x[(long)b * ldx + i * 32 + lane]);
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float d = amax / 127.f;
+  const int q = d > 0.f ? __float2int_rn(v / d) : 0;
+  int s = q;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  x8[(long)b * K + i * 32 + lane] = (int8_t)q;
+  if (lane == 0) { dx[blk] = d; sx[blk] = d * (float)s; }
+}
+
+// 6-bit scales and mins of sub-blocks 2g and 2g+1 from the 12 packed bytes (hdr.y, hdr.z, hdr.w):
+// bytes 0-3 hold scales 0-3 (low 6 bits) and the top bits of scales 4-7, bytes 4-7 the same for the
+// mins, bytes 8-11 the low nibbles of scales / mins 4-7.
+__device__ __forceinline__ void scales_of_group(const uint4& hdr, int g, float& sc_lo, float& sc_hi, float& m_lo,
+                                                float& m_hi) {
+  const int sh = (g & 1) * 16;
+  const uint32_t a = (hdr.y >> sh) & 0xffffu, b = (hdr.z >> sh) & 0xffffu, c = (hdr.w >> sh) & 0xffffu;
+  uint32_t s0, s1, m0, m1;
+  if (g < 2) {
+    s0 = a & 63u; s1 = (a >> 8) & 63u;
+    m0 = b & 63u; m1 = (b >> 8) & 63u;
+  } else {
+    s0 = (c & 0xFu) | (((a >> 6) & 3u) << 4);
+    s1 = ((c >> 8) & 0xFu) | (((a >> 14) & 3u) << 4);
+    m0 = ((c >> 4) & 0xFu) | (((b >> 6) & 3u) << 4);
+    m1 = ((c >> 12) & 0xFu) | (((b >> 14) & 3u) << 4);
+  }
+  sc_lo = (float)s0; sc_hi = (float)s1; m_lo = (float)m0; m_hi = (float)m1;
+}
+
+// A lane owns one 64-weight group (32 bytes of nibbles = sub-blocks 2g and 2g+1) of a super-block,
+// four lanes a super-block, a warp eight super-blocks per iteration - for R consecutive rows at
+// once: the int8 activations of the group (64 bytes per batch row) are loaded into registers once
+// and multiplied against R rows, which divides the L1 traffic per weight by R (with one row per
+// warp the kernel ran at 86 % of the L1 pipe and 2.2 TB/s).
+template <int NB, int R>
+__global__ void __launch_bounds__(256)
+q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, const float* __restrict__ dx,
+                const float* __restrict__ sx, float* __restrict__ out, int N, int K, int tiled) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nsb = K / 256, per_row32 = K / 32;
+  const int sbi = lane >> 2, g = lane & 3;
+  const long sb_stride = tiled ? 128L * kSB : kSB;
+  for (int row0 = (blockIdx.x * 8 + warp) * R; row0 < N; row0 += gridDim.x * 8 * R) {
+    const uint8_t* base[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = min(row0 + r, N - 1);                 // rows past the end repeat the last one (not stored)
+      base[r] = tiled ? W + ((long)(row >> 7) * nsb) * (128L * kSB) + (long)(row & 127) * kSB : W + (long)row * nsb * kSB;
+    }
+    float acc[R][NB];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
+    for (int sb0 = 0; sb0 < nsb; sb0 += 8) {
+      const int sb = sb0 + sbi;
+      if (sb < nsb) {
+        const int i32 = sb * 8 + 2 * g;
+        const long xo = (long)sb * 256 + g * 64;
+        int xl[NB][8], xh[NB][8];
+        float2 dd[NB], ss[NB];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          const int4* xp = reinterpret_cast<const int4*>(x8 + (long)b * K + xo);
+          const int4 xa = __ldg(xp), xb = __ldg(xp + 1), xc = __ldg(xp + 2), xd = __ldg(xp + 3);
+          xl[b][0] = xa.x; xl[b][1] = xa.y; xl[b][2] = xa.z; xl[b][3] = xa.w;
+          xl[b][4] = xb.x; xl[b][5] = xb.y; xl[b][6] = xb.z; xl[b][7] = xb.w;
+          xh[b][0] = xc.x; xh[b][1] = xc.y; xh[b][2] = xc.z; xh[b][3] = xc.w;
+          xh[b][4] = xd.x; xh[b][5] = xd.y; xh[b][6] = xd.z; xh[b][7] = xd.w;
+          dd[b] = __ldg(reinterpret_cast<const float2*>(dx + (long)b * per_row32 + i32));
+          ss[b] = __ldg(reinterpret_cast<const float2*>(sx + (long)b * per_row32 + i32));
+        }
+        uint4 hdr[R], q0[R], q1[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {                         // all weight loads of the R rows in flight together
+          const uint8_t* blk = base[r] + sb * sb_stride;
+          hdr[r] = __ldg(reinterpret_cast<const uint4*>(blk));
+          q0[r] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + g * 32));
+          q1[r] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + g * 32));
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const __half2 dm = *reinterpret_cast<const __half2*>(&hdr[r].x);
+          const float d = __low2float(dm), dmin = __high2float(dm);
+          float sc_lo, sc_hi, m_lo, m_hi;
+          scales_of_group(hdr[r], g, sc_lo, sc_hi, m_lo, m_hi);
+          const uint32_t qw[8] = {q0[r].x, q0[r].y, q0[r].z, q0[r].w, q1[r].x, q1[r].y, q1[r].z, q1[r].w};
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            int lo = 0, hi = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              lo = __dp4a((int)(qw[k] & 0x0F0F0F0Fu), xl[b][k], lo);
+              hi = __dp4a((int)((qw[k] >> 4) & 0x0F0F0F0Fu), xh[b][k], hi);
+            }
+            acc[r][b] += d * (sc_lo * dd[b].x * (float)lo + sc_hi * dd[b].y * (float)hi) - dmin * (m_lo * ss[b].x + m_hi * ss[b].y);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float v = acc[r][b];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && row0 + r < N) out[(long)b * N + row0 + r] = v;
+      }
+  }
+}
+
+}  // namespace
+
+// x [B, K] bf16 (row stride ldx) times Q4_K W[N, K]^T -> out [B, N] fp32, 1 <= B <= 8, K % 256 == 0.
+// Scratch (caller-provided): x8 [B*K] int8, dx and sx [B*K/32] fp32.
+AX_API int ax_q4k_gemv(const void* W, int tiled, const void* x, long ldx, void* x8, float* dx, float* sx, float* out, int B,
+                       int N, int K, cudaStream_t stream) {
+  if (B < 1 || B > 8 || N <= 0 || K <= 0 || K % 256) return -1;
+  if ((((uintptr_t)W) | ((uintptr_t)x8)) & 15) return -1;
+  if ((((uintptr_t)dx) | ((uintptr_t)sx)) & 7) return -1;
+  const long blocks32 = (long)B * (K / 32);
+  q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8, dx,
+                                                                                 sx, B, K);
+  const int R = B <= 2 ? 4 : 2;                              // rows per warp
+  int grid = (N + 8 * R - 1) / (8 * R);
+  const int cap = axh::sm_count() * 8;
+  if (grid > cap) grid = cap;
+  const auto* w = (const uint8_t*)W;
+  const auto* q8 = (const int8_t*)x8;
+#define AX_GEMV(NB, RR) case NB: q4k_gemv_kernel<NB, RR><<<grid, 256, 0, stream>>>(w, q8, dx, sx, out, N, K, tiled); break;
+  switch (B) {
+    AX_GEMV(1, 4) AX_GEMV(2, 4) AX_GEMV(3, 2) AX_GEMV(4, 2) AX_GEMV(5, 2) AX_GEMV(6, 2) AX_GEMV(7, 2) AX_GEMV(8, 2)
+  }
+#undef AX_GEMV
+  return (int)cudaGetLastError();
+}

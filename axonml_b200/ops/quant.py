@@ -2,6 +2,8 @@
 (``csrc/kernels/quant.cu``, ``qgemm.cu``)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native as N
@@ -76,6 +78,17 @@ def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int
     if x2.stride(1) != 1 or x2.stride(0) % 8:
         x2 = x2.contiguous()
     B = x2.shape[0]
+    from ..quant.types import QuantType
+    if B <= 4 and qweight.quant_type is QuantType.Q4_K and os.environ.get("AXONML_QGEMV", "1") != "0":
+        # decode-sized batches: matrix-vector kernel (dp4a on int8 activations, weights read once from HBM)
+        if out is None:
+            out = torch.empty((B, Nn), dtype=torch.float32, device=x.device)
+        x8 = torch.empty(B * K, dtype=torch.int8, device=x.device)
+        dxs = torch.empty(2 * B * (K // 32), dtype=torch.float32, device=x.device)
+        rc = N.cuda().ax_q4k_gemv(N.ptr(qweight.data), int(qweight.layout == "tile128"), N.ptr(x2), N.c_int64(x2.stride(0)),
+                                  N.ptr(x8), N.ptr(dxs), N.ptr(dxs[B * (K // 32):]), N.ptr(out), B, Nn, K, N.stream_ptr())
+        N.check(rc, "ax_q4k_gemv")
+        return out.view(*x.shape[:-1], Nn)
     if out is None:
         out = torch.zeros((B, Nn), dtype=torch.float32, device=x.device)
     for b0 in range(0, B, 64):

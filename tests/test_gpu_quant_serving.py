@@ -51,6 +51,29 @@ def test_qgemm(qt, B, N, K, kernel_status):
     assert (qgemm(x, qt_) - y).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("B,N,K", [(1, 4096, 4096), (3, 500, 14336), (5, 136, 768), (8, 1000, 1024)])
+def test_q4k_matrix_vector_kernel(B, N, K, kernel_status, monkeypatch):
+    """Decode-sized batches take the dp4a matrix-vector kernel (both weight layouts); the result is
+    compared with the fp32 product of the dequantised weights and with the tensor-core kernel."""
+    from axonml_b200.ops.quant import qgemm, tile_weight
+    from axonml_b200.quant import QuantType, dequantize_tensor, quantize_tensor
+    torch.manual_seed(1)
+    w = torch.randn(N, K) * 0.05
+    q = quantize_tensor(w, QuantType.Q4_K).to("cuda")
+    x = torch.randn(B, K, device="cuda").bfloat16()
+    ref = x.float() @ dequantize_tensor(q).float().t()
+    y = qgemm(x, q)
+    tol = 0.01 * (K ** 0.5) * 0.05 * 4 + 1e-2          # int8 activations: about 0.4 % per element
+    if B > 4:                                           # larger batches stay on the tensor-core kernel
+        tol = 2 * tol + 0.05
+    assert y.shape == (B, N) and (y - ref).abs().max().item() < tol
+    yt = qgemm(x, tile_weight(q))
+    assert (yt - y).abs().max().item() < 1e-4
+    monkeypatch.setenv("AXONML_QGEMV", "0")
+    y_tc = qgemm(x, q)
+    assert (y_tc - ref).abs().max().item() < 2 * tol + 0.05
+
+
 def test_paged_kv_and_decode_attention():
     from axonml_b200.ops import paged
     B, Hq, Hkv, D, page, max_pages = 3, 4, 1, 128, 16, 8
