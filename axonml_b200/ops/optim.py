@@ -49,6 +49,10 @@ def multi_tensor(kind: str, params, grads, s1=None, s2=None, s3=None, lp=None, *
     nt = len(ref)
     if nt == 0:
         return
+    # the kernel refreshes bf16 mirrors itself; mirrors of another dtype are copied afterwards
+    late_lp = None
+    if lp is not None and any(l is not None and l.dtype != torch.bfloat16 for l in lp):
+        late_lp, lp = lp, None
     p_bf16 = int(params is not None and params[0].dtype == torch.bfloat16)
     g_bf16 = int(grads is not None and grads[0].dtype == torch.bfloat16)
     sizes = (ctypes.c_long * nt)(*[t.numel() for t in ref])
@@ -60,6 +64,10 @@ def multi_tensor(kind: str, params, grads, s1=None, s2=None, s3=None, lp=None, *
         _ptr_array(s2), _ptr_array(s3), _ptr_array(lp), sizes, hyper, flags, N.ptr(inv_scale),
         N.ptr(found_inf), N.ptr(norms), N.ptr(clip_coef), N.stream_ptr())
     N.check(rc, f"ax_multi_tensor[{kind}]")
+    if late_lp is not None and kind in ("sgd", "adam", "rmsprop", "lamb2"):
+        for l, q in zip(late_lp, params):
+            if l is not None:
+                l.copy_(q)
 
 
 def grad_sumsq(grads, out: torch.Tensor | None = None, inv_scale=None) -> torch.Tensor:

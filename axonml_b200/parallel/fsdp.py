@@ -169,6 +169,7 @@ class FullyShardedDataParallel(Module):
                 u.shard, dtype=self.param_dtype, device=self.device)
             u.master._axon_lp = u.lp_shard
             u.master._axon_grad = None
+        self._attach_segments()
         self._comm = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
 
         for u in self.block_units:
@@ -181,6 +182,24 @@ class FullyShardedDataParallel(Module):
                 if not u.is_root and p.dim() == 2:
                     p._axon_grad_sink = _GradSink(self, u, idx)
         self._built = True
+
+    def _attach_segments(self) -> None:
+        """Tells per-tensor optimizers (LAMB's trust ratio) which tensors a master shard holds:
+        ``_axon_segments`` = [(tensor id over all units, start in the shard, length)] and a
+        reduction that sums per-tensor statistics over the ranks holding the other slices."""
+        gid = 0
+        total = sum(len(u.params) for u in self.units)
+        for u in self.units:
+            lo, hi = u.rank * u.shard, (u.rank + 1) * u.shard
+            segs = []
+            for p, o in zip(u.params, u.offsets):
+                a, b = max(o, lo), min(o + p.numel(), hi)
+                segs.append((gid, a - lo, max(b - a, 0)))
+                gid += 1
+            u.master._axon_segments = segs
+            u.master._axon_num_tensors = total
+            if u.world > 1:
+                u.master._axon_norm_reduce = lambda t: self.pg.backend().all_reduce(t, ReduceOp.Sum)
 
     def _grad_storage(self, u: FlatUnit) -> torch.Tensor:
         """Flat gradient of a unit: a slice of the symmetric arena when the fused reduce-scatter +

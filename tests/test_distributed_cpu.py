@@ -200,6 +200,42 @@ def test_fsdp_matches_single_process(strategy):
         assert torch.allclose(sd0[k], v.detach(), atol=5e-4), (k, (sd0[k] - v).abs().max())
 
 
+def _mlp_fsdp_lamb(rank, world, be):
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import FSDP, ProcessGroup
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(24, 40), nn.Tanh(), nn.Linear(40, 40), nn.Tanh(), nn.Linear(40, 7))
+    f = FSDP(m, ProcessGroup(be))
+    opt = optim.LAMB(f.parameters(), 2e-2, weight_decay=0.05)
+    g = torch.Generator().manual_seed(5)
+    X, Y = torch.randn(3, 8, 24, generator=g), torch.randint(0, 7, (3, 8), generator=g)
+    for it in range(3):
+        nn.CrossEntropyLoss()(f(X[it].chunk(world)[rank]), Y[it].chunk(world)[rank]).backward()
+        opt.step()
+        f.zero_grad()
+    return f.full_state_dict()
+
+
+def test_fsdp_lamb_takes_trust_ratios_per_tensor_across_shards():
+    """LAMB on master shards: the norms of a tensor are summed over the ranks that hold its
+    slices, so the result equals LAMB on the unsharded model (a per-shard ratio would not)."""
+    from axonml_b200 import nn, optim
+    res = run_ranks(_mlp_fsdp_lamb, 2)
+    torch.manual_seed(0)
+    ref = nn.Sequential(nn.Linear(24, 40), nn.Tanh(), nn.Linear(40, 40), nn.Tanh(), nn.Linear(40, 7))
+    opt = optim.LAMB(list(ref.parameters()), 2e-2, weight_decay=0.05)
+    g = torch.Generator().manual_seed(5)
+    X, Y = torch.randn(3, 8, 24, generator=g), torch.randint(0, 7, (3, 8), generator=g)
+    for it in range(3):
+        nn.CrossEntropyLoss()(ref(X[it]), Y[it]).backward()
+        opt.step()
+        opt.zero_grad()
+    sd0, sd1 = res[0][1], res[1][1]
+    for k, v in ref.named_parameters():
+        assert torch.allclose(sd0[k], sd1[k], atol=1e-6), k
+        assert torch.allclose(sd0[k], v.detach(), atol=2e-5), (k, (sd0[k] - v).abs().max())
+
+
 def _waits_for_absent_rank(rank, world, be):
     from axonml_b200.parallel import CommTimeout
     try:

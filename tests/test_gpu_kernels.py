@@ -406,3 +406,30 @@ def test_whole_sequence_rnn_kernel_matches_the_step_by_step_path(kind, hidden, l
     last = m.last_state[-1]
     h_last = last[0] if kind == "lstm" else last
     assert (h_last.float().cpu() - want[:, -1]).abs().max().item() < 4e-2
+
+
+def test_lamb_on_a_flat_master_buffer_takes_trust_ratios_per_tensor():
+    """A sharded engine hands LAMB one flat fp32 buffer per unit; the multi-tensor kernels run on
+    the slices of the tensors inside it (odd starts included), so the result equals LAMB on the
+    separate tensors."""
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import FSDP
+    torch.manual_seed(0)
+    mk = lambda: nn.Sequential(nn.Linear(96, 251), nn.Tanh(), nn.Linear(251, 131), nn.Tanh(), nn.Linear(131, 9))
+    m, ref = mk().cuda(), mk().cuda()
+    ref.load_state_dict(m.state_dict())
+    f = FSDP(m, None, param_dtype=torch.float32)
+    opt = optim.LAMB(f.parameters(), 2e-2, weight_decay=0.05)
+    ropt = optim.LAMB(list(ref.parameters()), 2e-2, weight_decay=0.05)
+    X, Y = torch.randn(3, 16, 96, device="cuda"), torch.randint(0, 9, (3, 16), device="cuda")
+    for it in range(3):
+        nn.CrossEntropyLoss()(f(X[it]), Y[it]).backward()
+        opt.step()
+        f.zero_grad()
+        nn.CrossEntropyLoss()(ref(X[it]), Y[it]).backward()
+        ropt.step()
+        ropt.zero_grad()
+    sd = f.full_state_dict()
+    moved = max((v.detach() - sd0).abs().max().item() for v, sd0 in zip(ref.parameters(), mk().cuda().parameters()))
+    err = max((sd[k] - v.detach()).abs().max().item() for k, v in ref.named_parameters())
+    assert moved > 1e-3 and err < 1e-5, (moved, err)

@@ -108,6 +108,41 @@ def test_fsdp_fused_rs_adamw_matches_nccl_path(nvls):
         assert diff < 1e-2 and mean < 1e-4, (diff, mean)
 
 
+def _fsdp_lamb(rank, world, be):
+    from axonml_b200 import _native, nn, optim
+    from axonml_b200.parallel import FSDP, ProcessGroup
+    torch.manual_seed(0)
+    mk = lambda: nn.Sequential(nn.Linear(96, 250), nn.Tanh(), nn.Linear(250, 130), nn.Tanh(), nn.Linear(130, 9))
+    m = mk().cuda()
+    ref = mk().cuda()
+    ref.load_state_dict(m.state_dict())
+    f = FSDP(m, ProcessGroup(be), param_dtype=torch.float32)
+    opt = optim.LAMB(f.parameters(), 2e-2, weight_decay=0.05)
+    ropt = optim.LAMB(list(ref.parameters()), 2e-2, weight_decay=0.05)
+    g = torch.Generator().manual_seed(5)
+    X, Y = torch.randn(3, 8 * world, 96, generator=g).cuda(), torch.randint(0, 9, (3, 8 * world), generator=g).cuda()
+    for it in range(3):
+        nn.CrossEntropyLoss()(f(X[it].chunk(world)[rank]), Y[it].chunk(world)[rank]).backward()
+        opt.step()
+        f.zero_grad()
+        nn.CrossEntropyLoss()(ref(X[it]), Y[it]).backward()
+        ropt.step()
+        ropt.zero_grad()
+    torch.cuda.synchronize()
+    _native.check_status()
+    sd = f.full_state_dict()
+    return max((sd[k] - v.detach()).abs().max().item() for k, v in ref.named_parameters())
+
+
+def test_fsdp_lamb_trust_ratio_per_tensor_across_shards():
+    """The multi-tensor LAMB kernels run on the slices of each tensor that a rank holds; the
+    per-tensor sums of squares are all-reduced between the two phases, so sharded LAMB equals
+    LAMB on the whole model."""
+    res = run_gpu_ranks(_fsdp_lamb, WORLD, env={"AXONML_NVLS": "0"})
+    for r in range(WORLD):
+        assert res[r][1] < 5e-5, res[r][1]
+
+
 def _ddp_fused(rank, world, be):
     from axonml_b200 import nn, optim
     from axonml_b200.parallel import DDP, ProcessGroup
