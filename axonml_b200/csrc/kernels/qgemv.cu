@@ -2,9 +2,10 @@
 //
 // The tensor-core dequantising matmul (qgemm.cu) expands every weight tile through shared memory;
 // at batch 1 that work is wasted and the kernel sits at 0.18 of the HBM roofline.  Here a warp
-// owns one output row: each lane loads 16 bytes of packed nibbles straight from global memory
-// (32 weights), splits them into low / high nibbles with two logic ops per word and multiplies
-// them against the int8-quantised activations with dp4a (0.5 instructions per weight).  The
+// owns a few consecutive output rows: each lane loads 32 bytes of packed nibbles per row straight
+// from global memory (one 64-weight group), splits them into low / high nibbles with two logic ops
+// per word and multiplies them against the int8-quantised activations with dp4a (0.5 instructions
+// per weight).  The
 // activations are quantised once per call into 32-wide blocks (scale and block sum, as llama.cpp's
 // Q8_1 does), so that
 //     sum_i (d*sc*q_i - dmin*m) * (dx*q8_i) = d*sc*dx * dot(q, q8) - dmin*m * (dx * sum q8).
