@@ -147,6 +147,117 @@ q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, co
   }
 }
 
+// ---------------------------------------------------------------------------------- Q8_0
+// Q8_0 blocks are 34 bytes (half scale + 32 int8), so nothing in a row is 16-byte aligned.  In the
+// tile-contiguous layout ([N/128][K/256][128 rows][272 bytes]) the 128 rows of a k block are one
+// contiguous 34 KB piece: a producer lane streams the pieces of a row tile through a ring of
+// shared-memory stages with bulk copies, and eight warps read them back with 4-byte loads at a
+// 68-byte lane stride (17 words: conflict-free).  A lane owns a pair of blocks (68 bytes: word 0 =
+// scale 0 + two weights, words 1-7 weights, word 8 = two weights + scale 1, words 9-16 the second
+// block), four lanes a row, a warp 16 rows in two passes.
+constexpr int kQ8Row = 272;
+constexpr int kQ8Stage = 128 * kQ8Row;
+
+__device__ __forceinline__ uint32_t lds32s(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+
+__device__ __forceinline__ void bulk_load_g2s(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int NB, int S>
+__global__ void __launch_bounds__(288, NB <= 2 ? 2 : 1)
+q80_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, const float* __restrict__ dx,
+                float* __restrict__ out, int N, int K, int* status) {
+  extern __shared__ uint8_t q8_raw[];
+  __shared__ uint64_t full[S], empty[S];
+  __shared__ int dead_flag;
+  volatile int* dead = &dead_flag;
+  const uint32_t stage0 = (smem_u32(q8_raw) + 127u) & ~127u;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nkb = K / 256, per_row32 = K / 32;
+  const int tile = blockIdx.x;
+  if (threadIdx.x == 0) {
+    dead_flag = 0;
+    for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 8); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 8) {
+    if (lane == 0) {
+      const uint8_t* src = W + (long)tile * nkb * kQ8Stage;
+      for (int i = 0; i < nkb; ++i) {
+        const int st = i % S;
+        if (i >= S && !mbar_wait(&empty[st], ((i / S) - 1) & 1, dead, status, 760)) break;
+        mbar_expect_tx(&full[st], kQ8Stage);
+        bulk_load_g2s(stage0 + st * kQ8Stage, src + (long)i * kQ8Stage, kQ8Stage, &full[st]);
+      }
+    }
+    return;
+  }
+  const int q = lane & 3, rsub = lane >> 2;
+  float acc[2][NB];
+#pragma unroll
+  for (int ps = 0; ps < 2; ++ps)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) acc[ps][b] = 0.f;
+  for (int i = 0; i < nkb; ++i) {
+    const int st = i % S;
+    int xl[NB][8], xh[NB][8];
+    float2 dd[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {                       // issued before the wait: independent of the stage
+      const int4* xp = reinterpret_cast<const int4*>(x8 + (long)b * K + i * 256 + q * 64);
+      const int4 xa = __ldg(xp), xb = __ldg(xp + 1), xc = __ldg(xp + 2), xd = __ldg(xp + 3);
+      xl[b][0] = xa.x; xl[b][1] = xa.y; xl[b][2] = xa.z; xl[b][3] = xa.w;
+      xl[b][4] = xb.x; xl[b][5] = xb.y; xl[b][6] = xb.z; xl[b][7] = xb.w;
+      xh[b][0] = xc.x; xh[b][1] = xc.y; xh[b][2] = xc.z; xh[b][3] = xc.w;
+      xh[b][4] = xd.x; xh[b][5] = xd.y; xh[b][6] = xd.z; xh[b][7] = xd.w;
+      dd[b] = __ldg(reinterpret_cast<const float2*>(dx + (long)b * per_row32 + i * 8 + 2 * q));
+    }
+    if (!mbar_wait(&full[st], (i / S) & 1, dead, status, 761)) break;
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) {
+      const uint32_t a = stage0 + st * kQ8Stage + (warp * 16 + ps * 8 + rsub) * kQ8Row + q * 68;
+      uint32_t w[17];
+#pragma unroll
+      for (int k = 0; k < 17; ++k) w[k] = lds32s(a + 4 * k);
+      const float d0 = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xffffu)));
+      const float d1 = __half2float(__ushort_as_half((unsigned short)(w[8] >> 16)));
+      uint32_t q0[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) q0[k] = __funnelshift_r(w[k], w[k + 1], 16);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        int s0 = 0, s1 = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          s0 = __dp4a((int)q0[k], xl[b][k], s0);
+          s1 = __dp4a((int)w[9 + k], xh[b][k], s1);
+        }
+        acc[ps][b] += d0 * dd[b].x * (float)s0 + d1 * dd[b].y * (float)s1;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
+  }
+#pragma unroll
+  for (int ps = 0; ps < 2; ++ps)
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      float v = acc[ps][b];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      const int row = tile * 128 + warp * 16 + ps * 8 + rsub;
+      if (q == 0 && row < N) out[(long)b * N + row] = v;
+    }
+}
+
 }  // namespace
 
 // x [B, K] bf16 (row stride ldx) times Q4_K W[N, K]^T -> out [B, N] fp32, 1 <= B <= 8, K % 256 == 0.
@@ -170,5 +281,35 @@ AX_API int ax_q4k_gemv(const void* W, int tiled, const void* x, long ldx, void* 
     AX_GEMV(1, 4) AX_GEMV(2, 4) AX_GEMV(3, 2) AX_GEMV(4, 2) AX_GEMV(5, 2) AX_GEMV(6, 2) AX_GEMV(7, 2) AX_GEMV(8, 2)
   }
 #undef AX_GEMV
+  return (int)cudaGetLastError();
+}
+
+// The same product for a Q8_0 weight in the tile-contiguous layout (rows padded to a multiple of
+// 128), 1 <= B <= 4.  `sx` is scratch of the activation quantiser and not read here.
+AX_API int ax_q80_gemv(const void* W, const void* x, long ldx, void* x8, float* dx, float* sx, float* out, int B, int N, int K,
+                       int* status, cudaStream_t stream) {
+  if (B < 1 || B > 4 || N <= 0 || K <= 0 || K % 256) return -1;
+  if ((((uintptr_t)W) | ((uintptr_t)x8)) & 15) return -1;
+  if (((uintptr_t)dx) & 7) return -1;
+  const long blocks32 = (long)B * (K / 32);
+  q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8, dx,
+                                                                                 sx, B, K);
+  const int grid = (N + 127) / 128;
+  const auto* w = (const uint8_t*)W;
+  const auto* q8 = (const int8_t*)x8;
+#define AX_GEMV8(NB, S)                                                                                       \
+  case NB: {                                                                                                  \
+    constexpr int smem = S * kQ8Stage + 128;                                                                  \
+    static bool once = false;                                                                                 \
+    if (!once) {                                                                                              \
+      cudaFuncSetAttribute(q80_gemv_kernel<NB, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);        \
+      once = true;                                                                                            \
+    }                                                                                                         \
+    q80_gemv_kernel<NB, S><<<grid, 288, smem, stream>>>(w, q8, dx, out, N, K, status);                       \
+  } break;
+  switch (B) {
+    AX_GEMV8(1, 3) AX_GEMV8(2, 3) AX_GEMV8(3, 5) AX_GEMV8(4, 5)
+  }
+#undef AX_GEMV8
   return (int)cudaGetLastError();
 }

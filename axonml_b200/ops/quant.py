@@ -89,6 +89,18 @@ def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int
                                   N.ptr(x8), N.ptr(dxs), N.ptr(dxs[B * (K // 32):]), N.ptr(out), B, Nn, K, N.stream_ptr())
         N.check(rc, "ax_q4k_gemv")
         return out.view(*x.shape[:-1], Nn)
+    if (B <= 4 and qweight.quant_type is QuantType.Q8_0 and qweight.layout == "tile128" and Nn >= 128 * 148
+            and os.environ.get("AXONML_QGEMV", "1") != "0"):
+        # wide Q8_0 matrices (the LM head): one CTA per 128-row tile streams its k blocks through shared memory
+        if out is None:
+            out = torch.empty((B, Nn), dtype=torch.float32, device=x.device)
+        x8 = torch.empty(B * K, dtype=torch.int8, device=x.device)
+        dxs = torch.empty(2 * B * (K // 32), dtype=torch.float32, device=x.device)
+        rc = N.cuda().ax_q80_gemv(N.ptr(qweight.data), N.ptr(x2), N.c_int64(x2.stride(0)), N.ptr(x8), N.ptr(dxs),
+                                  N.ptr(dxs[B * (K // 32):]), N.ptr(out), B, Nn, K, N.ptr(N.status_word(x.device)),
+                                  N.stream_ptr())
+        N.check(rc, "ax_q80_gemv")
+        return out.view(*x.shape[:-1], Nn)
     if out is None:
         out = torch.zeros((B, Nn), dtype=torch.float32, device=x.device)
     for b0 in range(0, B, 64):

@@ -74,6 +74,26 @@ def test_q4k_matrix_vector_kernel(B, N, K, kernel_status, monkeypatch):
     assert (y_tc - ref).abs().max().item() < 2 * tol + 0.05
 
 
+@pytest.mark.parametrize("B,N,K", [(1, 18981, 4096), (2, 20000, 1024), (3, 19072, 256), (4, 19000, 1536)])
+def test_q80_matrix_vector_kernel(B, N, K, kernel_status, monkeypatch):
+    """Wide Q8_0 matrices (an LM head) at decode batch sizes: the shared-memory streaming kernel
+    against the fp32 product of the dequantised weights and against the tensor-core kernel."""
+    from axonml_b200.ops.quant import qgemm, tile_weight
+    from axonml_b200.quant import QuantType, dequantize_tensor, quantize_tensor
+    torch.manual_seed(2)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    q = quantize_tensor(w, QuantType.Q8_0)
+    x = torch.randn(B, K, device="cuda").bfloat16()
+    ref = x.float() @ dequantize_tensor(q).float().t()
+    tol = 0.01 * (K ** 0.5) * 0.05 * 4 + 1e-2
+    y = qgemm(x, tile_weight(q))
+    assert y.shape == (B, N) and (y - ref).abs().max().item() < tol
+    monkeypatch.setenv("AXONML_QGEMV", "0")
+    y_tc = qgemm(x, tile_weight(q))
+    assert (y_tc - ref).abs().max().item() < 2 * tol + 0.05
+    assert (y_tc - y).abs().max().item() < 2 * tol + 0.05
+
+
 def test_paged_kv_and_decode_attention():
     from axonml_b200.ops import paged
     B, Hq, Hkv, D, page, max_pages = 3, 4, 1, 128, 16, 8
