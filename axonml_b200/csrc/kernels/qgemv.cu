@@ -44,6 +44,11 @@ q8_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long ldx, int8_t* _
   if (lane == 0) { dx[blk] = d; sx[blk] = d * (float)s; }
 }
 
+__device__ __forceinline__ void store_out(void* out, int out_bf16, long i, float v) {
+  if (out_bf16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16(v);
+  else reinterpret_cast<float*>(out)[i] = v;
+}
+
 // 6-bit scales and mins of sub-blocks 2g and 2g+1 from the 12 packed bytes (hdr.y, hdr.z, hdr.w):
 // bytes 0-3 hold scales 0-3 (low 6 bits) and the top bits of scales 4-7, bytes 4-7 the same for the
 // mins, bytes 8-11 the low nibbles of scales / mins 4-7.
@@ -72,7 +77,7 @@ __device__ __forceinline__ void scales_of_group(const uint4& hdr, int g, float& 
 template <int NB, int R>
 __global__ void __launch_bounds__(256)
 q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, const float* __restrict__ dx,
-                const float* __restrict__ sx, float* __restrict__ out, int N, int K, int tiled) {
+                const float* __restrict__ sx, void* __restrict__ out, int out_bf16, int N, int K, int tiled) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nsb = K / 256, per_row32 = K / 32;
   const int sbi = lane >> 2, g = lane & 3;
@@ -142,7 +147,7 @@ q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, co
         float v = acc[r][b];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && row0 + r < N) out[(long)b * N + row0 + r] = v;
+        if (lane == 0 && row0 + r < N) store_out(out, out_bf16, (long)b * N + row0 + r, v);
       }
   }
 }
@@ -173,7 +178,7 @@ __device__ __forceinline__ void bulk_load_g2s(uint32_t dst, const void* src, uin
 template <int NB, int S>
 __global__ void __launch_bounds__(288, NB <= 2 ? 2 : 1)
 q80_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, const float* __restrict__ dx,
-                float* __restrict__ out, int N, int K, int* status) {
+                void* __restrict__ out, int out_bf16, int N, int K, int* status) {
   extern __shared__ uint8_t q8_raw[];
   __shared__ uint64_t full[S], empty[S];
   __shared__ int dead_flag;
@@ -254,40 +259,50 @@ q80_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, co
       v += __shfl_xor_sync(0xffffffffu, v, 1);
       v += __shfl_xor_sync(0xffffffffu, v, 2);
       const int row = tile * 128 + warp * 16 + ps * 8 + rsub;
-      if (q == 0 && row < N) out[(long)b * N + row] = v;
+      if (q == 0 && row < N) store_out(out, out_bf16, (long)b * N + row, v);
     }
 }
 
 }  // namespace
 
-// x [B, K] bf16 (row stride ldx) times Q4_K W[N, K]^T -> out [B, N] fp32, 1 <= B <= 8, K % 256 == 0.
+// x [B, K] bf16 (row stride ldx) times Q4_K W[N, K]^T -> out [B, N] (fp32, or bf16 when out_bf16), 1 <= B <= 8,
+// K % 256 == 0.
 // Scratch (caller-provided): x8 [B*K] int8, dx and sx [B*K/32] fp32.
-AX_API int ax_q4k_gemv(const void* W, int tiled, const void* x, long ldx, void* x8, float* dx, float* sx, float* out, int B,
-                       int N, int K, cudaStream_t stream) {
+AX_API int ax_q4k_gemv(const void* W, int tiled, const void* x, long ldx, void* x8, float* dx, float* sx, void* out,
+                       int out_bf16, int B, int N, int K, cudaStream_t stream) {
   if (B < 1 || B > 8 || N <= 0 || K <= 0 || K % 256) return -1;
   if ((((uintptr_t)W) | ((uintptr_t)x8)) & 15) return -1;
   if ((((uintptr_t)dx) | ((uintptr_t)sx)) & 7) return -1;
   const long blocks32 = (long)B * (K / 32);
   q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8, dx,
                                                                                  sx, B, K);
-  const int R = B <= 2 ? 4 : 2;                              // rows per warp
+  // rows per warp: four reuse the activations best, but a narrow matrix then has fewer CTAs than SMs
+  const int sms = axh::sm_count();
+  const int R = (B <= 2 && N >= 32 * 2 * sms) ? 4 : (N >= 16 * 2 * sms ? 2 : 1);
   int grid = (N + 8 * R - 1) / (8 * R);
   const int cap = axh::sm_count() * 8;
   if (grid > cap) grid = cap;
   const auto* w = (const uint8_t*)W;
   const auto* q8 = (const int8_t*)x8;
-#define AX_GEMV(NB, RR) case NB: q4k_gemv_kernel<NB, RR><<<grid, 256, 0, stream>>>(w, q8, dx, sx, out, N, K, tiled); break;
+#define AX_GEMV(NB, RR) q4k_gemv_kernel<NB, RR><<<grid, 256, 0, stream>>>(w, q8, dx, sx, out, out_bf16, N, K, tiled)
+#define AX_GEMV_B(NB)                                             \
+  case NB:                                                        \
+    if (R == 4 && NB <= 2) AX_GEMV(NB <= 2 ? NB : 1, 4);          \
+    else if (R == 2) AX_GEMV(NB, 2);                              \
+    else AX_GEMV(NB, 1);                                          \
+    break;
   switch (B) {
-    AX_GEMV(1, 4) AX_GEMV(2, 4) AX_GEMV(3, 2) AX_GEMV(4, 2) AX_GEMV(5, 2) AX_GEMV(6, 2) AX_GEMV(7, 2) AX_GEMV(8, 2)
+    AX_GEMV_B(1) AX_GEMV_B(2) AX_GEMV_B(3) AX_GEMV_B(4) AX_GEMV_B(5) AX_GEMV_B(6) AX_GEMV_B(7) AX_GEMV_B(8)
   }
+#undef AX_GEMV_B
 #undef AX_GEMV
   return (int)cudaGetLastError();
 }
 
 // The same product for a Q8_0 weight in the tile-contiguous layout (rows padded to a multiple of
 // 128), 1 <= B <= 4.  `sx` is scratch of the activation quantiser and not read here.
-AX_API int ax_q80_gemv(const void* W, const void* x, long ldx, void* x8, float* dx, float* sx, float* out, int B, int N, int K,
-                       int* status, cudaStream_t stream) {
+AX_API int ax_q80_gemv(const void* W, const void* x, long ldx, void* x8, float* dx, float* sx, void* out, int out_bf16, int B,
+                       int N, int K, int* status, cudaStream_t stream) {
   if (B < 1 || B > 4 || N <= 0 || K <= 0 || K % 256) return -1;
   if ((((uintptr_t)W) | ((uintptr_t)x8)) & 15) return -1;
   if (((uintptr_t)dx) & 7) return -1;
@@ -305,7 +320,7 @@ AX_API int ax_q80_gemv(const void* W, const void* x, long ldx, void* x8, float* 
       cudaFuncSetAttribute(q80_gemv_kernel<NB, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);        \
       once = true;                                                                                            \
     }                                                                                                         \
-    q80_gemv_kernel<NB, S><<<grid, 288, smem, stream>>>(w, q8, dx, out, N, K, status);                       \
+    q80_gemv_kernel<NB, S><<<grid, 288, smem, stream>>>(w, q8, dx, out, out_bf16, N, K, status);             \
   } break;
   switch (B) {
     AX_GEMV8(1, 3) AX_GEMV8(2, 3) AX_GEMV8(3, 5) AX_GEMV8(4, 5)

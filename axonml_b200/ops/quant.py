@@ -70,9 +70,12 @@ def qgemm_supported(x: torch.Tensor, qweight) -> bool:
             and qweight.shape[1] % 256 == 0 and qweight.layout in ("ggml", "tile128"))
 
 
-def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int = 0) -> torch.Tensor:
+def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int = 0,
+          out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """``x[B, K]`` (bf16, B <= 64 per launch) times the quantised ``W[N, K]``^T -> fp32 ``[B, N]``.
-    Larger batches are processed in slices of 64 rows."""
+    Larger batches are processed in slices of 64 rows.  ``out_dtype=torch.bfloat16`` lets the
+    matrix-vector kernels write bf16 themselves; the tensor-core kernel accumulates split-k partial
+    sums in fp32 and is converted afterwards."""
     Nn, K = qweight.shape
     x2 = x.reshape(-1, K)
     if x2.stride(1) != 1 or x2.stride(0) % 8:
@@ -82,23 +85,24 @@ def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int
     if B <= 4 and qweight.quant_type is QuantType.Q4_K and os.environ.get("AXONML_QGEMV", "1") != "0":
         # decode-sized batches: matrix-vector kernel (dp4a on int8 activations, weights read once from HBM)
         if out is None:
-            out = torch.empty((B, Nn), dtype=torch.float32, device=x.device)
+            out = torch.empty((B, Nn), dtype=out_dtype, device=x.device)
         x8 = torch.empty(B * K, dtype=torch.int8, device=x.device)
         dxs = torch.empty(2 * B * (K // 32), dtype=torch.float32, device=x.device)
         rc = N.cuda().ax_q4k_gemv(N.ptr(qweight.data), int(qweight.layout == "tile128"), N.ptr(x2), N.c_int64(x2.stride(0)),
-                                  N.ptr(x8), N.ptr(dxs), N.ptr(dxs[B * (K // 32):]), N.ptr(out), B, Nn, K, N.stream_ptr())
+                                  N.ptr(x8), N.ptr(dxs), N.ptr(dxs[B * (K // 32):]), N.ptr(out),
+                                  int(out.dtype == torch.bfloat16), B, Nn, K, N.stream_ptr())
         N.check(rc, "ax_q4k_gemv")
         return out.view(*x.shape[:-1], Nn)
     if (B <= 4 and qweight.quant_type is QuantType.Q8_0 and qweight.layout == "tile128" and Nn >= 128 * 148
             and os.environ.get("AXONML_QGEMV", "1") != "0"):
         # wide Q8_0 matrices (the LM head): one CTA per 128-row tile streams its k blocks through shared memory
         if out is None:
-            out = torch.empty((B, Nn), dtype=torch.float32, device=x.device)
+            out = torch.empty((B, Nn), dtype=out_dtype, device=x.device)
         x8 = torch.empty(B * K, dtype=torch.int8, device=x.device)
         dxs = torch.empty(2 * B * (K // 32), dtype=torch.float32, device=x.device)
         rc = N.cuda().ax_q80_gemv(N.ptr(qweight.data), N.ptr(x2), N.c_int64(x2.stride(0)), N.ptr(x8), N.ptr(dxs),
-                                  N.ptr(dxs[B * (K // 32):]), N.ptr(out), B, Nn, K, N.ptr(N.status_word(x.device)),
-                                  N.stream_ptr())
+                                  N.ptr(dxs[B * (K // 32):]), N.ptr(out), int(out.dtype == torch.bfloat16), B, Nn, K,
+                                  N.ptr(N.status_word(x.device)), N.stream_ptr())
         N.check(rc, "ax_q80_gemv")
         return out.view(*x.shape[:-1], Nn)
     if out is None:
@@ -109,6 +113,8 @@ def qgemm(x: torch.Tensor, qweight, out: torch.Tensor | None = None, splits: int
                                xs.shape[0], Nn, K, xs.stride(0), splits, int(qweight.layout == "tile128"),
                                N.ptr(N.status_word(x.device)), N.stream_ptr())
         N.check(rc, "ax_qgemm")
+    if out.dtype != out_dtype:
+        out = out.to(out_dtype)
     return out.view(*x.shape[:-1], Nn)
 
 
@@ -117,10 +123,9 @@ def qlinear(x: torch.Tensor, qweight, bias=None, out_dtype=torch.bfloat16) -> to
     dequantise + tcgen05 GEMM beyond that (compute-bound prefill)."""
     rows = x.numel() // x.shape[-1]
     if qgemm_supported(x, qweight) and rows <= 256:
-        y = qgemm(x, qweight)
-        if bias is not None:
-            y = y + bias.float()
-        return y.to(out_dtype)
+        if bias is None:
+            return qgemm(x, qweight, out_dtype=out_dtype)
+        return (qgemm(x, qweight) + bias.float()).to(out_dtype)
     from ..quant.quantize import dequantize_tensor
     from .linear import linear
     if qweight.layout == "tile128":

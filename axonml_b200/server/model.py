@@ -221,7 +221,14 @@ class QuantizedLlama:
         """Next token per row of ``h`` with the vocabulary split over ranks: local arg-max, then one
         tiny all-gather of (value, index) pairs."""
         lg = self._logits(h)
-        val, idx = lg.max(dim=-1)
+        V = lg.shape[-1]
+        if V >= 65536 and V % 256 == 0:
+            # two stages: a single-row reduction over the whole vocabulary runs in one thread block
+            v1, i1 = lg.view(-1, 256, V // 256).max(dim=-1)
+            val, i2 = v1.max(dim=-1)
+            idx = i2 * (V // 256) + i1.gather(-1, i2.unsqueeze(-1)).squeeze(-1)
+        else:
+            val, idx = lg.max(dim=-1)
         idx = idx + self.rank * self.vocab_local
         if self.tp == 1:
             return idx

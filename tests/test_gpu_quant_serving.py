@@ -69,6 +69,8 @@ def test_q4k_matrix_vector_kernel(B, N, K, kernel_status, monkeypatch):
     assert y.shape == (B, N) and (y - ref).abs().max().item() < tol
     yt = qgemm(x, tile_weight(q))
     assert (yt - y).abs().max().item() < 1e-4
+    yb = qgemm(x, q, out_dtype=torch.bfloat16)            # the matrix-vector kernel writes bf16 itself
+    assert yb.dtype == torch.bfloat16 and (yb.float() - y).abs().max().item() <= y.abs().max().item() / 128
     monkeypatch.setenv("AXONML_QGEMV", "0")
     y_tc = qgemm(x, q)
     assert (y_tc - ref).abs().max().item() < 2 * tol + 0.05
@@ -88,6 +90,8 @@ def test_q80_matrix_vector_kernel(B, N, K, kernel_status, monkeypatch):
     tol = 0.01 * (K ** 0.5) * 0.05 * 4 + 1e-2
     y = qgemm(x, tile_weight(q))
     assert y.shape == (B, N) and (y - ref).abs().max().item() < tol
+    yb = qgemm(x, tile_weight(q), out_dtype=torch.bfloat16)
+    assert yb.dtype == torch.bfloat16 and (yb.float() - y).abs().max().item() <= y.abs().max().item() / 128
     monkeypatch.setenv("AXONML_QGEMV", "0")
     y_tc = qgemm(x, tile_weight(q))
     assert (y_tc - ref).abs().max().item() < 2 * tol + 0.05
