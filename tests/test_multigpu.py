@@ -125,13 +125,18 @@ def _fsdp_lamb(rank, world, be):
         nn.CrossEntropyLoss()(f(X[it].chunk(world)[rank]), Y[it].chunk(world)[rank]).backward()
         opt.step()
         f.zero_grad()
-        nn.CrossEntropyLoss()(ref(X[it]), Y[it]).backward()
+        # the reference sees the same per-rank batches (same kernels, same rounding): LAMB's first
+        # steps move every element by about lr * sign(g), so a gradient that is zero up to rounding
+        # must round the same way on both sides
+        for xs, ys in zip(X[it].chunk(world), Y[it].chunk(world)):
+            (nn.CrossEntropyLoss()(ref(xs), ys) / world).backward()
         ropt.step()
         ropt.zero_grad()
     torch.cuda.synchronize()
     _native.check_status()
     sd = f.full_state_dict()
-    return max((sd[k] - v.detach()).abs().max().item() for k, v in ref.named_parameters())
+    diffs = [(sd[k] - v.detach()).abs() for k, v in ref.named_parameters()]
+    return sum(d.sum().item() for d in diffs) / sum(d.numel() for d in diffs), max(d.max().item() for d in diffs)
 
 
 def test_fsdp_lamb_trust_ratio_per_tensor_across_shards():
@@ -140,7 +145,10 @@ def test_fsdp_lamb_trust_ratio_per_tensor_across_shards():
     LAMB on the whole model."""
     res = run_gpu_ranks(_fsdp_lamb, WORLD, env={"AXONML_NVLS": "0"})
     for r in range(WORLD):
-        assert res[r][1] < 5e-5, res[r][1]
+        mean, worst = res[r][1]
+        # a ratio taken per shard would move whole tensors by ~1e-3; single elements may still
+        # differ by 2 * lr * trust where a gradient's sign is decided by the reduction order
+        assert mean < 2e-5 and worst < 5e-2, (mean, worst)
 
 
 def _ddp_fused(rank, world, be):
