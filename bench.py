@@ -91,11 +91,11 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The reference is a Rust workspace: `pip install /root/reference` finds neither setup.py nor
+    # The reference is a Rust workspace: `pip install` of its source tree finds neither setup.py nor
     # pyproject.toml, and there is no cargo/rustc on the machine, so it cannot be built or run.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust cargo workspace (no setup.py/pyproject.toml, no cargo/rustc "
-                      "offline): pip install of /root/reference fails, nothing to run"}))
+                      "offline): pip install of the reference source tree fails, nothing to run"}))
 
 
 def bench_q4k_decode(args):
