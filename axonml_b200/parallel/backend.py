@@ -77,6 +77,15 @@ class Backend:
     def scatter(self, send: torch.Tensor | None, recv: torch.Tensor, src: int = 0) -> None: raise NotImplementedError
     def reduce(self, data: torch.Tensor, dst: int = 0, op: ReduceOp = ReduceOp.Sum) -> None: raise NotImplementedError
     def barrier(self) -> None: raise NotImplementedError
+
+    def all_to_all(self, send: torch.Tensor, recv: torch.Tensor) -> None:
+        """``send`` and ``recv`` are ``[world, ...]``: ``recv[j]`` receives rank j's ``send[rank]``.
+        Generic form over ``all_gather``; transports with a native exchange override it."""
+        w, r = self.world_size(), self.rank()
+        full = torch.empty((w,) + tuple(send.shape), dtype=send.dtype, device=send.device)
+        self.all_gather(send.contiguous(), full)
+        recv.copy_(full[:, r])
+
     def send(self, data: torch.Tensor, dst: int, tag: int = 0) -> None: raise NotImplementedError
     def recv(self, data: torch.Tensor, src: int, tag: int = 0) -> None: raise NotImplementedError
     def new_group(self, ranks: Sequence[int]) -> "Backend": raise NotImplementedError
@@ -273,6 +282,11 @@ class _TorchDistBackend(Backend):
 
     def all_gather(self, send, recv):
         self._wrap(lambda: dist.all_gather_into_tensor(recv.view(-1), send.contiguous().view(-1), self._group), "all_gather")
+
+    def all_to_all(self, send, recv):
+        if self.BACKEND == "gloo":
+            return super().all_to_all(send, recv)
+        self._wrap(lambda: dist.all_to_all_single(recv.view(-1), send.contiguous().view(-1), group=self._group), "all_to_all")
 
     def reduce_scatter(self, send, recv, op=ReduceOp.Sum):
         if self.BACKEND == "gloo":

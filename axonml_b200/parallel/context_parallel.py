@@ -1,0 +1,106 @@
+"""Context (sequence) parallel attention, DeepSpeed-Ulysses style.
+
+Activations are sharded along the sequence: every rank holds ``[B, S/W, H, D]``.  Attention needs
+the whole sequence, so q, k and v are exchanged with one all-to-all each into ``[B, S, H/W, D]``
+(whole sequence, a slice of the heads), attention runs locally on the flash-attention kernel, and
+a fourth all-to-all brings the output back to the sequence sharding.  Every all-to-all moves
+``1/W`` of the tensor per peer, so the traffic per rank is independent of ``W``; over NVSwitch
+every peer is at full bandwidth.  The exchanges are autograd functions whose backward is the
+opposite exchange.
+
+The reference has no sequence or context parallelism (its blockwise attention,
+crates/axonml-llm/src/attention.rs:836-943, is single-device); this module is what lets a
+sequence longer than one GPU's activation memory train with the same attention kernel.
+
+Requirements: ``S`` sharded contiguously in rank order, ``Hq % W == 0``; K/V heads that do not
+divide by ``W`` (grouped-query attention with few KV heads) are repeated up to ``Hq`` first."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import attention as A
+from .process_group import ProcessGroup
+
+
+def _exchange(pg: ProcessGroup, send: torch.Tensor) -> torch.Tensor:
+    recv = torch.empty_like(send)
+    pg.backend().all_to_all(send, recv)
+    return recv
+
+
+def _seq_to_heads(x: torch.Tensor, pg: ProcessGroup) -> torch.Tensor:
+    """[B, s, H, D] (sequence shard, all heads) -> [B, W*s, H/W, D] (whole sequence, head slice)."""
+    W = pg.world_size()
+    B, s, H, D = x.shape
+    h = H // W
+    send = x.reshape(B, s, W, h, D).permute(2, 0, 1, 3, 4).contiguous()      # [W, B, s, h, D]
+    recv = _exchange(pg, send)                                                # recv[j]: rank j's tokens
+    return recv.permute(1, 0, 2, 3, 4).reshape(B, W * s, h, D)
+
+
+def _heads_to_seq(x: torch.Tensor, pg: ProcessGroup) -> torch.Tensor:
+    """[B, W*s, h, D] -> [B, s, W*h, D]: the inverse exchange."""
+    W = pg.world_size()
+    B, S, h, D = x.shape
+    s = S // W
+    send = x.reshape(B, W, s, h, D).permute(1, 0, 2, 3, 4).contiguous()      # [W, B, s, h, D]
+    recv = _exchange(pg, send)                                                # recv[j]: head slice j
+    return recv.permute(1, 2, 0, 3, 4).reshape(B, s, W * h, D)
+
+
+class _SeqToHeads(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pg):
+        ctx.pg = pg
+        return _seq_to_heads(x, pg)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _heads_to_seq(g.contiguous(), ctx.pg), None
+
+
+class _HeadsToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pg):
+        ctx.pg = pg
+        return _heads_to_seq(x, pg)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _seq_to_heads(g.contiguous(), ctx.pg), None
+
+
+def shard_sequence(x: torch.Tensor, pg: ProcessGroup, dim: int = 1) -> torch.Tensor:
+    """This rank's contiguous slice of ``x`` along ``dim``."""
+    W, r = pg.world_size(), pg.rank()
+    if x.shape[dim] % W:
+        raise ValueError(f"sequence length {x.shape[dim]} is not divisible by the group size {W}")
+    return x.chunk(W, dim=dim)[r]
+
+
+def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg: ProcessGroup, causal: bool = True,
+                      scale: float | None = None) -> torch.Tensor:
+    """q ``[B, S/W, Hq, D]``, k/v ``[B, S/W, Hkv, D]`` (this rank's tokens) -> ``[B, S/W, Hq, D]``."""
+    W = pg.world_size()
+    if W == 1:
+        return A.sdpa(q, k, v, causal=causal, scale=scale)
+    Hq, Hkv = q.shape[2], k.shape[2]
+    if Hq % W:
+        raise ValueError(f"{Hq} query heads cannot be split over {W} ranks")
+    if Hkv % W:
+        rep = Hq // Hkv
+        k, v = k.repeat_interleave(rep, dim=2), v.repeat_interleave(rep, dim=2)
+    qh, kh, vh = (_SeqToHeads.apply(t, pg) for t in (q, k, v))
+    o = A.sdpa(qh, kh, vh, causal=causal, scale=scale)
+    return _HeadsToSeq.apply(o.contiguous(), pg)
+
+
+class UlyssesAttention(torch.nn.Module):
+    """Drop-in attention core for sequence-sharded activations (see module docstring)."""
+
+    def __init__(self, process_group: ProcessGroup, causal: bool = True):
+        super().__init__()
+        self.pg, self.causal = process_group, causal
+
+    def forward(self, q, k, v, scale: float | None = None):
+        return ulysses_attention(q, k, v, self.pg, self.causal, scale)

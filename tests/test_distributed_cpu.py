@@ -236,6 +236,39 @@ def test_fsdp_lamb_takes_trust_ratios_per_tensor_across_shards():
         assert torch.allclose(sd0[k], v.detach(), atol=2e-5), (k, (sd0[k] - v).abs().max())
 
 
+def _ulysses(rank, world, be, hkv):
+    from axonml_b200.parallel import ProcessGroup, shard_sequence, ulysses_attention
+    pg = ProcessGroup(be)
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, 16, 4, 8, generator=g)
+    k, v = torch.randn(2, 16, hkv, 8, generator=g), torch.randn(2, 16, hkv, 8, generator=g)
+    wgt = torch.randn(2, 16, 4, 8, generator=g)
+    ql, kl, vl = (shard_sequence(t, pg).clone().requires_grad_(True) for t in (q, k, v))
+    o = ulysses_attention(ql, kl, vl, pg, causal=True)
+    (o * shard_sequence(wgt, pg)).sum().backward()
+    return o.detach(), ql.grad, kl.grad, vl.grad
+
+
+@pytest.mark.parametrize("world,hkv", [(2, 4), (2, 1), (4, 2)])
+def test_ulysses_context_parallel_attention_matches_single_process(world, hkv):
+    """Sequence-sharded attention (all-to-all to head shards and back), forward and backward,
+    against attention on the whole sequence; grouped-query heads that do not divide by the group
+    size are repeated first."""
+    from axonml_b200.ops.attention import sdpa_reference
+    res = run_ranks(_ulysses, world, args=(hkv,))
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, 16, 4, 8, generator=g).requires_grad_(True)
+    k = torch.randn(2, 16, hkv, 8, generator=g).requires_grad_(True)
+    v = torch.randn(2, 16, hkv, 8, generator=g).requires_grad_(True)
+    wgt = torch.randn(2, 16, 4, 8, generator=g)
+    o = sdpa_reference(q, k, v, causal=True)
+    (o * wgt).sum().backward()
+    for r in range(world):
+        got = res[r][1]
+        for a, full in zip(got, (o.detach(), q.grad, k.grad, v.grad)):
+            assert torch.allclose(a, full.chunk(world, dim=1)[r], atol=1e-5), (r, (a - full.chunk(world, dim=1)[r]).abs().max())
+
+
 def _waits_for_absent_rank(rank, world, be):
     from axonml_b200.parallel import CommTimeout
     try:

@@ -151,6 +151,41 @@ def test_fsdp_lamb_trust_ratio_per_tensor_across_shards():
         assert mean < 2e-5 and worst < 5e-2, (mean, worst)
 
 
+def _ulysses_gpu(rank, world, be):
+    from axonml_b200 import _native
+    from axonml_b200.ops.attention import sdpa_reference
+    from axonml_b200.parallel import ProcessGroup, shard_sequence, ulysses_attention
+    pg = ProcessGroup(be)
+    g = torch.Generator().manual_seed(11)
+    S, Hq, Hkv, D = 256 * world, 2 * world, world, 128
+    q = torch.randn(1, S, Hq, D, generator=g).cuda().bfloat16()
+    k = torch.randn(1, S, Hkv, D, generator=g).cuda().bfloat16()
+    v = torch.randn(1, S, Hkv, D, generator=g).cuda().bfloat16()
+    wgt = torch.randn(1, S, Hq, D, generator=g).cuda().bfloat16()
+    ql, kl, vl = (shard_sequence(t, pg).clone().requires_grad_(True) for t in (q, k, v))
+    o = ulysses_attention(ql, kl, vl, pg, causal=True)
+    (o.float() * shard_sequence(wgt, pg).float()).sum().backward()
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    of = sdpa_reference(qf, kf, vf, causal=True)
+    (of * wgt.float()).sum().backward()
+    torch.cuda.synchronize()
+    _native.check_status()
+    errs = [(o.float() - shard_sequence(of.detach(), pg)).abs().max().item()]
+    for a, full in ((ql.grad, qf.grad), (kl.grad, kf.grad), (vl.grad, vf.grad)):
+        ref = shard_sequence(full, pg)
+        errs.append(((a.float() - ref).abs().max() / ref.abs().max().clamp_min(1e-6)).item())
+    return errs
+
+
+def test_ulysses_context_parallel_attention_on_the_flash_kernels():
+    """Sequence-sharded attention: NCCL all-to-all to head shards, the flash-attention kernels on
+    the whole sequence, all-to-all back; forward and backward against fp32 attention."""
+    res = run_gpu_ranks(_ulysses_gpu, WORLD, env={"AXONML_NVLS": "0"})
+    for r in range(WORLD):
+        e = res[r][1]
+        assert e[0] < 3e-2 and max(e[1:]) < 4e-2, e
+
+
 def _ddp_fused(rank, world, be):
     from axonml_b200 import nn, optim
     from axonml_b200.parallel import DDP, ProcessGroup
