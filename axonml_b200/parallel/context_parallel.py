@@ -13,7 +13,14 @@ crates/axonml-llm/src/attention.rs:836-943, is single-device); this module is wh
 sequence longer than one GPU's activation memory train with the same attention kernel.
 
 Requirements: ``S`` sharded contiguously in rank order, ``Hq % W == 0``; K/V heads that do not
-divide by ``W`` (grouped-query attention with few KV heads) are repeated up to ``Hq`` first."""
+divide by ``W`` (grouped-query attention with few KV heads) are repeated up to ``Hq`` first.
+
+``allgather_kv_attention`` is the second form, for grouped-query models whose K/V are small: the
+queries stay sharded, K and V are all-gathered along the sequence (backward: reduce-scatter) and
+every rank attends from its own queries to the keys up to its last token - the kernels' causal
+mask is aligned to the end of the key range, so the slice ``K[:, :(rank + 1) * s]`` is all that
+is needed.  No restriction on the head counts; with a causal mask the last rank does the most
+work (contiguous sharding, no zigzag)."""
 from __future__ import annotations
 
 import torch
@@ -93,6 +100,42 @@ def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg: Pro
     qh, kh, vh = (_SeqToHeads.apply(t, pg) for t in (q, k, v))
     o = A.sdpa(qh, kh, vh, causal=causal, scale=scale)
     return _HeadsToSeq.apply(o.contiguous(), pg)
+
+
+class _AllGatherSeq(torch.autograd.Function):
+    """[B, s, H, D] -> [B, W*s, H, D]; backward sums the gradients of every rank's copy and keeps
+    this rank's slice (reduce-scatter)."""
+
+    @staticmethod
+    def forward(ctx, x, pg):
+        ctx.pg = pg
+        W = pg.world_size()
+        xt = x.transpose(0, 1).contiguous()
+        full = torch.empty((W * xt.shape[0],) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+        pg.backend().all_gather(xt, full)
+        return full.transpose(0, 1)
+
+    @staticmethod
+    def backward(ctx, g):
+        from .backend import ReduceOp
+        W = ctx.pg.world_size()
+        gt = g.transpose(0, 1).contiguous()
+        mine = torch.empty((gt.shape[0] // W,) + tuple(gt.shape[1:]), dtype=g.dtype, device=g.device)
+        ctx.pg.backend().reduce_scatter(gt, mine, ReduceOp.Sum)
+        return mine.transpose(0, 1), None
+
+
+def allgather_kv_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg: ProcessGroup, causal: bool = True,
+                           scale: float | None = None) -> torch.Tensor:
+    """q ``[B, S/W, Hq, D]``, k/v ``[B, S/W, Hkv, D]`` (this rank's tokens) -> ``[B, S/W, Hq, D]``."""
+    W, r = pg.world_size(), pg.rank()
+    if W == 1:
+        return A.sdpa(q, k, v, causal=causal, scale=scale)
+    s = q.shape[1]
+    K, V = _AllGatherSeq.apply(k, pg), _AllGatherSeq.apply(v, pg)
+    if causal:
+        K, V = K[:, :(r + 1) * s], V[:, :(r + 1) * s]
+    return A.sdpa(q, K, V, causal=causal, scale=scale)
 
 
 class UlyssesAttention(torch.nn.Module):

@@ -236,8 +236,10 @@ def test_fsdp_lamb_takes_trust_ratios_per_tensor_across_shards():
         assert torch.allclose(sd0[k], v.detach(), atol=2e-5), (k, (sd0[k] - v).abs().max())
 
 
-def _ulysses(rank, world, be, hkv):
-    from axonml_b200.parallel import ProcessGroup, shard_sequence, ulysses_attention
+def _ulysses(rank, world, be, hkv, form="ulysses"):
+    from axonml_b200.parallel import ProcessGroup, allgather_kv_attention, shard_sequence, ulysses_attention
+    if form == "allgather":
+        ulysses_attention = allgather_kv_attention
     pg = ProcessGroup(be)
     g = torch.Generator().manual_seed(11)
     q = torch.randn(2, 16, 4, 8, generator=g)
@@ -249,13 +251,14 @@ def _ulysses(rank, world, be, hkv):
     return o.detach(), ql.grad, kl.grad, vl.grad
 
 
+@pytest.mark.parametrize("form", ["ulysses", "allgather"])
 @pytest.mark.parametrize("world,hkv", [(2, 4), (2, 1), (4, 2)])
-def test_ulysses_context_parallel_attention_matches_single_process(world, hkv):
+def test_ulysses_context_parallel_attention_matches_single_process(world, hkv, form):
     """Sequence-sharded attention (all-to-all to head shards and back), forward and backward,
     against attention on the whole sequence; grouped-query heads that do not divide by the group
     size are repeated first."""
     from axonml_b200.ops.attention import sdpa_reference
-    res = run_ranks(_ulysses, world, args=(hkv,))
+    res = run_ranks(_ulysses, world, args=(hkv, form))
     g = torch.Generator().manual_seed(11)
     q = torch.randn(2, 16, 4, 8, generator=g).requires_grad_(True)
     k = torch.randn(2, 16, hkv, 8, generator=g).requires_grad_(True)
