@@ -65,3 +65,25 @@ def test_gpt_block_matches_reference_math(kernel_status):
     g = m.transformer.blocks[0].ffn.fc1.weight.grad.float().cpu()
     gr = ref.transformer.blocks[0].ffn.fc1.weight.grad
     assert ((g - gr).abs().max() / gr.abs().max()).item() < 0.1
+
+
+def test_flash_on_sequence_major_key_slices(kernel_status):
+    """The layout context-parallel attention produces: keys and values gathered as [S, B, H, D],
+    viewed as [B, S, H, D] and cut after this rank's last token; the causal mask is aligned to
+    the end of the key range.  Forward and backward against the fp32 reference."""
+    from axonml_b200.ops.attention import sdpa
+    B, s, W, r, Hq, Hkv = 2, 256, 4, 2, 4, 1
+    q = torch.randn(B, s, Hq, 128, device="cuda").bfloat16().requires_grad_()
+    ks = torch.randn(W * s, B, Hkv, 128, device="cuda").bfloat16().requires_grad_()
+    vs = torch.randn(W * s, B, Hkv, 128, device="cuda").bfloat16().requires_grad_()
+    K, V = ks.transpose(0, 1)[:, :(r + 1) * s], vs.transpose(0, 1)[:, :(r + 1) * s]
+    o = sdpa(q, K, V, causal=True)
+    g = torch.randn_like(o)
+    o.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, ks, vs))
+    ref = _ref(qr, kr.transpose(0, 1)[:, :(r + 1) * s], vr.transpose(0, 1)[:, :(r + 1) * s], True)
+    ref.backward(g.float())
+    assert (o.float() - ref).abs().max().item() < 3e-2
+    for a, b in ((q, qr), (ks, kr), (vs, vr)):
+        assert (a.grad.float() - b.grad).abs().max().item() < 4e-2 * max(1.0, b.grad.abs().max().item())
+    assert ks.grad[(r + 1) * s:].abs().max().item() == 0.0
