@@ -59,6 +59,18 @@ def test_mock_collectives():
     assert out[1][4].item() == 42.0
 
 
+def test_all_to_all_generic_form():
+    """``recv[j]`` is rank j's ``send[rank]`` (the form every backend inherits; NCCL overrides it)."""
+    def fn(r, be):
+        send = torch.tensor([[10.0 * r + j, -1.0 * j] for j in range(3)])
+        recv = torch.empty_like(send)
+        be.all_to_all(send, recv)
+        return recv
+    out = _run_threads(3, fn)
+    for r, recv in enumerate(out):
+        assert recv.tolist() == [[10.0 * j + r, -1.0 * r] for j in range(3)]
+
+
 def test_mock_missing_rank_times_out():
     from axonml_b200.parallel import CommTimeout, MockBackend
     world = MockBackend.create_world(2, timeout_s=0.3)
