@@ -61,6 +61,19 @@ class LLaMAAttention(nn.Module):
         B, S, _ = x.shape
         w = _cat_rows(self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
         qkv = linear(x, w)
+        cp = getattr(self, "cp_group", None)
+        if cp is not None and kv_cache is None and self.sliding_window is None:
+            # context parallel: x holds this rank's slice of the sequence; positions continue from
+            # the slices before it and attention runs over the whole sequence
+            from ..parallel import context_parallel as CP
+            nq, nk = self.nh * self.hd, self.nkv * self.hd
+            p0 = pos0 + cp.rank() * S
+            q = self.rotary.apply(qkv[..., :nq].reshape(B, S, self.nh, self.hd), S, p0)
+            k = self.rotary.apply(qkv[..., nq:nq + nk].reshape(B, S, self.nkv, self.hd), S, p0)
+            v = qkv[..., nq + nk:].reshape(B, S, self.nkv, self.hd)
+            attend = CP.ulysses_attention if getattr(self, "cp_form", "ulysses") == "ulysses" else CP.allgather_kv_attention
+            o = attend(q.contiguous(), k.contiguous(), v.contiguous(), cp, causal=True)
+            return self.o_proj(o.reshape(B, S, self.nh * self.hd))
         if kv_cache is None and self.sliding_window is None:
             packed = qkv.view(B, S, self.nh + 2 * self.nkv, self.hd)
             packed = Mi.rope(packed, self.rotary.cos_cached.to(x.device), self.rotary.sin_cached.to(x.device),
@@ -182,8 +195,32 @@ class LLaMAForCausalLM(nn.Module):
 
     forward_with_cache = forward
 
+    def enable_context_parallel(self, process_group, form: str = "ulysses"):
+        """Shards the sequence over ``process_group``: ``forward_with_loss`` then takes the whole
+        sequence on every rank, runs this rank's slice (``form``: "ulysses" all-to-all or
+        "allgather" of K/V) and returns a loss whose mean over the ranks is the loss of the whole
+        sequence, so a data-parallel wrapper's gradient average over the same ranks is exact."""
+        if form not in ("ulysses", "allgather"):
+            raise ValueError(f"unknown context-parallel form {form!r}")
+        self.cp_group = process_group
+        for layer in self.model.layers:
+            layer.self_attn.cp_group, layer.self_attn.cp_form = process_group, form
+        return self
+
     def forward_with_loss(self, ids, labels=None):
         labels = ids if labels is None else labels
+        cp = getattr(self, "cp_group", None)
+        if cp is not None and cp.world_size() > 1:
+            from ..parallel.context_parallel import shard_sequence
+            tgt = torch.full_like(labels, -100)
+            tgt[:, :-1] = labels[:, 1:]
+            total = (tgt != -100).sum().clamp_min(1)
+            logits = self.forward(shard_sequence(ids, cp))
+            tl = shard_sequence(tgt, cp).reshape(-1)
+            B, S, V = logits.shape
+            local = (tl != -100).sum()
+            loss = L.cross_entropy(logits.view(B * S, V), tl) * (local * cp.world_size() / total)
+            return loss, logits
         logits = self.forward(ids)
         B, S, V = logits.shape
         tgt = torch.full_like(labels, -100)

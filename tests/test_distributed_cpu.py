@@ -284,6 +284,42 @@ def test_ulysses_context_parallel_attention_matches_single_process(world, hkv, f
             assert torch.allclose(a, full.chunk(world, dim=1)[r], atol=1e-5), (r, (a - full.chunk(world, dim=1)[r]).abs().max())
 
 
+def _llama_cp(rank, world, be, form):
+    from axonml_b200.llm import LLaMAConfig, LLaMAForCausalLM
+    from axonml_b200.parallel import ProcessGroup, ReduceOp
+    torch.manual_seed(0)
+    cfg = LLaMAConfig(vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+    m = LLaMAForCausalLM(cfg).enable_context_parallel(ProcessGroup(be), form)
+    ids = torch.randint(0, 97, (2, 32), generator=torch.Generator().manual_seed(4))
+    loss, _ = m.forward_with_loss(ids)
+    loss.backward()
+    out = [loss.detach().clone()] + [p.grad.clone() for p in m.parameters()]
+    for t in out:
+        be.all_reduce(t, ReduceOp.Average)
+    return out
+
+
+@pytest.mark.parametrize("form", ["ulysses", "allgather"])
+def test_llama_context_parallel_loss_and_gradients(form):
+    """A LLaMA whose sequence is sharded over two ranks: the mean over ranks of the loss and of
+    every parameter gradient equals the single-process values (RoPE positions continue across
+    the slices, labels shift across the slice boundary)."""
+    from axonml_b200.llm import LLaMAConfig, LLaMAForCausalLM
+    res = run_ranks(_llama_cp, 2, args=(form,))
+    torch.manual_seed(0)
+    cfg = LLaMAConfig(vocab_size=97, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+    ref = LLaMAForCausalLM(cfg)
+    ids = torch.randint(0, 97, (2, 32), generator=torch.Generator().manual_seed(4))
+    loss, _ = ref.forward_with_loss(ids)
+    loss.backward()
+    got = res[0][1]
+    assert abs(got[0].item() - loss.item()) < 1e-5
+    for g, p in zip(got[1:], ref.parameters()):
+        assert torch.allclose(g, p.grad, atol=2e-5), (g - p.grad).abs().max()
+
+
 def _waits_for_absent_rank(rank, world, be):
     from axonml_b200.parallel import CommTimeout
     try:
