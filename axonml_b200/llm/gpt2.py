@@ -54,7 +54,16 @@ class CausalSelfAttention(nn.Module):
     def forward(self, x, kv_cache=None):
         B, S, E = x.shape
         drop = self.attn_dropout if self.training else 0.0
-        if kv_cache is None:
+        cp = getattr(self, "cp_group", None)
+        if cp is not None and kv_cache is None:
+            # context parallel: x is this rank's slice of the sequence, attention sees all of it
+            from ..parallel import context_parallel as CP
+            if drop > 0.0:
+                raise ValueError("context-parallel attention does not support attention dropout")
+            qkv = self.c_attn(x).view(B, S, 3, self.n_head, self.head_dim)
+            attend = CP.ulysses_attention if getattr(self, "cp_form", "ulysses") == "ulysses" else CP.allgather_kv_attention
+            o = attend(qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous(), cp, causal=True)
+        elif kv_cache is None:
             qkv = self.c_attn(x).view(B, S, 3 * self.n_head, self.head_dim)
             o = sdpa_packed(qkv, self.n_head, self.n_head, causal=True, dropout_p=drop)
         else:
@@ -161,10 +170,36 @@ class GPT2LMHead(nn.Module):
     def forward(self, ids, kv_caches=None, pos0: int = 0):
         return self.forward_ids(ids, kv_caches, pos0)[..., : self.cfg.vocab_size]
 
+    def enable_context_parallel(self, process_group, form: str = "ulysses"):
+        """Shards the sequence over ``process_group``: ``forward_with_loss`` then takes the whole
+        sequence on every rank, runs this rank's slice (position embeddings offset accordingly;
+        ``form``: "ulysses" all-to-all or "allgather" of K/V) and returns a loss whose mean over the
+        ranks is the loss of the whole sequence."""
+        if form not in ("ulysses", "allgather"):
+            raise ValueError(f"unknown context-parallel form {form!r}")
+        self.cp_group = process_group
+        for m in self.modules():
+            if isinstance(m, CausalSelfAttention):
+                m.cp_group, m.cp_form = process_group, form
+        return self
+
     def forward_with_loss(self, ids, labels=None):
         """Shifted next-token cross-entropy: position t predicts token t+1 (gpt2.rs:182-266).
         Returns ``(loss, logits)`` where logits carry the padded vocabulary."""
         labels = ids if labels is None else labels
+        cp = getattr(self, "cp_group", None)
+        if cp is not None and cp.world_size() > 1:
+            from ..parallel.context_parallel import shard_sequence
+            tgt = torch.full_like(labels, -100)
+            tgt[:, :-1] = labels[:, 1:]
+            total = (tgt != -100).sum().clamp_min(1)
+            local_ids = shard_sequence(ids, cp)
+            logits = self.forward_ids(local_ids, pos0=cp.rank() * local_ids.shape[1])
+            tl = shard_sequence(tgt, cp).reshape(-1)
+            B, S, Vp = logits.shape
+            scale = (tl != -100).sum() * cp.world_size() / total
+            loss = L.cross_entropy(logits.view(B * S, Vp), tl, valid_classes=self.cfg.vocab_size) * scale
+            return loss, logits
         logits = self.forward_ids(ids)
         B, S, Vp = logits.shape
         tgt = torch.full_like(labels, -100)

@@ -320,6 +320,39 @@ def test_llama_context_parallel_loss_and_gradients(form):
         assert torch.allclose(g, p.grad, atol=2e-5), (g - p.grad).abs().max()
 
 
+def _gpt_cp(rank, world, be, form):
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    from axonml_b200.parallel import ProcessGroup, ReduceOp
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=200, n_ctx=32, n_embd=32, n_layer=2, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    m = GPT2LMHead(cfg).enable_context_parallel(ProcessGroup(be), form)
+    ids = torch.randint(0, 200, (2, 32), generator=torch.Generator().manual_seed(4))
+    loss, _ = m.forward_with_loss(ids)
+    loss.backward()
+    out = [loss.detach().clone()] + [p.grad.clone() for p in m.parameters()]
+    for t in out:
+        be.all_reduce(t, ReduceOp.Average)
+    return out
+
+
+@pytest.mark.parametrize("form", ["ulysses", "allgather"])
+def test_gpt2_context_parallel_loss_and_gradients(form):
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    res = run_ranks(_gpt_cp, 2, args=(form,))
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=200, n_ctx=32, n_embd=32, n_layer=2, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    ref = GPT2LMHead(cfg)
+    ids = torch.randint(0, 200, (2, 32), generator=torch.Generator().manual_seed(4))
+    loss, _ = ref.forward_with_loss(ids)
+    loss.backward()
+    got = res[0][1]
+    assert abs(got[0].item() - loss.item()) < 1e-5
+    for g, p in zip(got[1:], ref.parameters()):
+        assert torch.allclose(g, p.grad, atol=2e-5), (g - p.grad).abs().max()
+
+
 def _waits_for_absent_rank(rank, world, be):
     from axonml_b200.parallel import CommTimeout
     try:
