@@ -61,7 +61,7 @@ class CausalSelfAttention(nn.Module):
             if drop > 0.0:
                 raise ValueError("context-parallel attention does not support attention dropout")
             qkv = self.c_attn(x).view(B, S, 3, self.n_head, self.head_dim)
-            attend = CP.ulysses_attention if getattr(self, "cp_form", "ulysses") == "ulysses" else CP.allgather_kv_attention
+            attend = CP.attention_fn(getattr(self, "cp_form", "ulysses"))
             o = attend(qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(), qkv[:, :, 2].contiguous(), cp, causal=True)
         elif kv_cache is None:
             qkv = self.c_attn(x).view(B, S, 3 * self.n_head, self.head_dim)
@@ -173,10 +173,10 @@ class GPT2LMHead(nn.Module):
     def enable_context_parallel(self, process_group, form: str = "ulysses"):
         """Shards the sequence over ``process_group``: ``forward_with_loss`` then takes the whole
         sequence on every rank, runs this rank's slice (position embeddings offset accordingly;
-        ``form``: "ulysses" all-to-all or "allgather" of K/V) and returns a loss whose mean over the
+        ``form``: "ulysses" all-to-all, "allgather" of K/V or "ring") and returns a loss whose mean over the
         ranks is the loss of the whole sequence."""
-        if form not in ("ulysses", "allgather"):
-            raise ValueError(f"unknown context-parallel form {form!r}")
+        from ..parallel.context_parallel import attention_fn
+        attention_fn(form)                                   # validates the name
         self.cp_group = process_group
         for m in self.modules():
             if isinstance(m, CausalSelfAttention):

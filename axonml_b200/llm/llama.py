@@ -71,7 +71,7 @@ class LLaMAAttention(nn.Module):
             q = self.rotary.apply(qkv[..., :nq].reshape(B, S, self.nh, self.hd), S, p0)
             k = self.rotary.apply(qkv[..., nq:nq + nk].reshape(B, S, self.nkv, self.hd), S, p0)
             v = qkv[..., nq + nk:].reshape(B, S, self.nkv, self.hd)
-            attend = CP.ulysses_attention if getattr(self, "cp_form", "ulysses") == "ulysses" else CP.allgather_kv_attention
+            attend = CP.attention_fn(getattr(self, "cp_form", "ulysses"))
             o = attend(q.contiguous(), k.contiguous(), v.contiguous(), cp, causal=True)
             return self.o_proj(o.reshape(B, S, self.nh * self.hd))
         if kv_cache is None and self.sliding_window is None:
@@ -197,11 +197,11 @@ class LLaMAForCausalLM(nn.Module):
 
     def enable_context_parallel(self, process_group, form: str = "ulysses"):
         """Shards the sequence over ``process_group``: ``forward_with_loss`` then takes the whole
-        sequence on every rank, runs this rank's slice (``form``: "ulysses" all-to-all or
-        "allgather" of K/V) and returns a loss whose mean over the ranks is the loss of the whole
+        sequence on every rank, runs this rank's slice (``form``: "ulysses" all-to-all,
+        "allgather" of K/V or "ring") and returns a loss whose mean over the ranks is the loss of the whole
         sequence, so a data-parallel wrapper's gradient average over the same ranks is exact."""
-        if form not in ("ulysses", "allgather"):
-            raise ValueError(f"unknown context-parallel form {form!r}")
+        from ..parallel.context_parallel import attention_fn
+        attention_fn(form)                                   # validates the name
         self.cp_group = process_group
         for layer in self.model.layers:
             layer.self_attn.cp_group, layer.self_attn.cp_form = process_group, form

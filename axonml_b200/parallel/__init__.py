@@ -16,4 +16,5 @@ from .tensor_parallel import (ColumnParallelLinear, RowParallelLinear, VocabPara
                               vocab_parallel_cross_entropy)
 from .mesh import DeviceMesh
 from .checkpoint import load_sharded, save_sharded
-from .context_parallel import UlyssesAttention, allgather_kv_attention, shard_sequence, ulysses_attention
+from .context_parallel import (UlyssesAttention, allgather_kv_attention, ring_attention, shard_sequence,
+                               ulysses_attention)

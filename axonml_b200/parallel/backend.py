@@ -88,6 +88,13 @@ class Backend:
 
     def send(self, data: torch.Tensor, dst: int, tag: int = 0) -> None: raise NotImplementedError
     def recv(self, data: torch.Tensor, src: int, tag: int = 0) -> None: raise NotImplementedError
+
+    def sendrecv(self, send: torch.Tensor, dst: int, recv: torch.Tensor, src: int, tag: int = 0) -> None:
+        """Sends to ``dst`` and receives from ``src`` in one step (a ring shift when every rank calls
+        it).  Generic form for transports whose ``send`` does not wait for the receiver."""
+        self.send(send, dst, tag)
+        self.recv(recv, src, tag)
+
     def new_group(self, ranks: Sequence[int]) -> "Backend": raise NotImplementedError
     def device(self) -> torch.device: return torch.device("cpu")
 
@@ -329,6 +336,14 @@ class _TorchDistBackend(Backend):
 
     def recv(self, data, src, tag=0):
         self._wrap(lambda: dist.recv(data, self._ranks[src], self._group, tag), "recv")
+
+    def sendrecv(self, send, dst, recv, src, tag=0):
+        def go():
+            ops = [dist.P2POp(dist.isend, send.contiguous(), self._ranks[dst], self._group, tag),
+                   dist.P2POp(dist.irecv, recv, self._ranks[src], self._group, tag)]
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        self._wrap(go, "sendrecv")
 
     def isend(self, data, dst, tag=0): return dist.isend(data.contiguous(), self._ranks[dst], self._group, tag)
     def irecv(self, data, src, tag=0): return dist.irecv(data, self._ranks[src], self._group, tag)

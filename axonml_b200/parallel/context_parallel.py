@@ -20,7 +20,14 @@ queries stay sharded, K and V are all-gathered along the sequence (backward: red
 every rank attends from its own queries to the keys up to its last token - the kernels' causal
 mask is aligned to the end of the key range, so the slice ``K[:, :(rank + 1) * s]`` is all that
 is needed.  No restriction on the head counts; with a causal mask the last rank does the most
-work (contiguous sharding, no zigzag)."""
+work (contiguous sharding, no zigzag).
+
+``ring_attention`` is the third form, for sequences whose K/V do not fit one GPU even once: the
+K/V slices travel around the ring (``Backend.sendrecv``), every rank attends from its queries to
+the slice it currently holds and merges the partial results with their log-sum-exp.  The block
+products are torch expressions (differentiable; the shifts are autograd functions whose backward
+shifts the gradient the other way), not the flash kernels, which do not return a differentiable
+log-sum-exp."""
 from __future__ import annotations
 
 import torch
@@ -136,6 +143,76 @@ def allgather_kv_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg
     if causal:
         K, V = K[:, :(r + 1) * s], V[:, :(r + 1) * s]
     return A.sdpa(q, K, V, causal=causal, scale=scale)
+
+
+class _RingShift(torch.autograd.Function):
+    """Every rank sends ``x`` to the next rank and receives the previous rank's; backward sends the
+    gradient to the previous rank and receives the next rank's."""
+
+    @staticmethod
+    def forward(ctx, x, pg):
+        ctx.pg = pg
+        W, r = pg.world_size(), pg.rank()
+        out = torch.empty_like(x)
+        pg.backend().sendrecv(x.contiguous(), (r + 1) % W, out, (r - 1) % W)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        W, r = ctx.pg.world_size(), ctx.pg.rank()
+        out = torch.empty_like(g)
+        ctx.pg.backend().sendrecv(g.contiguous(), (r - 1) % W, out, (r + 1) % W)
+        return out, None
+
+
+def _block_attention(q, k, v, scale, diagonal: bool):
+    """Partial attention of q [B,s,Hq,D] against one K/V slice -> (o [B,Hq,s,D] fp32, lse [B,Hq,s])."""
+    Hq, Hkv = q.shape[2], k.shape[2]
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    if Hkv != Hq:
+        kf, vf = kf.repeat_interleave(Hq // Hkv, dim=1), vf.repeat_interleave(Hq // Hkv, dim=1)
+    sc = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if diagonal:
+        s = sc.shape[-1]
+        sc = sc.masked_fill(~torch.ones(s, s, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+    lse = torch.logsumexp(sc, dim=-1)
+    return torch.matmul(torch.exp(sc - lse.unsqueeze(-1)), vf), lse
+
+
+def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pg: ProcessGroup, causal: bool = True,
+                   scale: float | None = None) -> torch.Tensor:
+    """q ``[B, S/W, Hq, D]``, k/v ``[B, S/W, Hkv, D]`` (this rank's tokens) -> ``[B, S/W, Hq, D]``."""
+    W, r = pg.world_size(), pg.rank()
+    if W == 1:
+        return A.sdpa(q, k, v, causal=causal, scale=scale)
+    scale = scale if scale is not None else q.shape[-1] ** -0.5
+    o = lse = None
+    kv = torch.stack([k, v])
+    for t in range(W):
+        src = (r - t) % W                                   # owner of the slice held in this step
+        if not causal or src <= r:
+            ob, lb = _block_attention(q, kv[0], kv[1], scale, diagonal=causal and src == r)
+            if o is None:
+                o, lse = ob, lb
+            else:
+                new = torch.logaddexp(lse, lb)
+                o = o * torch.exp(lse - new).unsqueeze(-1) + ob * torch.exp(lb - new).unsqueeze(-1)
+                lse = new
+        elif o is not None:
+            # a slice this rank does not attend to must stay in the graph, or this rank's backward
+            # would skip the ring shift its neighbours wait for
+            o = o + kv.float().sum() * 0.0
+        if t + 1 < W:
+            kv = _RingShift.apply(kv, pg)
+    return o.permute(0, 2, 1, 3).to(q.dtype)
+
+
+def attention_fn(form: str):
+    """The context-parallel attention function called ``form``: "ulysses", "allgather" or "ring"."""
+    fns = {"ulysses": ulysses_attention, "allgather": allgather_kv_attention, "ring": ring_attention}
+    if form not in fns:
+        raise ValueError(f"unknown context-parallel form {form!r} (one of {sorted(fns)})")
+    return fns[form]
 
 
 class UlyssesAttention(torch.nn.Module):

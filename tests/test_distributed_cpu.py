@@ -252,6 +252,8 @@ def _ulysses(rank, world, be, hkv, form="ulysses"):
     from axonml_b200.parallel import ProcessGroup, allgather_kv_attention, shard_sequence, ulysses_attention
     if form == "allgather":
         ulysses_attention = allgather_kv_attention
+    elif form == "ring":
+        from axonml_b200.parallel import ring_attention as ulysses_attention
     pg = ProcessGroup(be)
     g = torch.Generator().manual_seed(11)
     q = torch.randn(2, 16, 4, 8, generator=g)
@@ -263,7 +265,7 @@ def _ulysses(rank, world, be, hkv, form="ulysses"):
     return o.detach(), ql.grad, kl.grad, vl.grad
 
 
-@pytest.mark.parametrize("form", ["ulysses", "allgather"])
+@pytest.mark.parametrize("form", ["ulysses", "allgather", "ring"])
 @pytest.mark.parametrize("world,hkv", [(2, 4), (2, 1), (4, 2)])
 def test_ulysses_context_parallel_attention_matches_single_process(world, hkv, form):
     """Sequence-sharded attention (all-to-all to head shards and back), forward and backward,
@@ -300,7 +302,7 @@ def _llama_cp(rank, world, be, form):
     return out
 
 
-@pytest.mark.parametrize("form", ["ulysses", "allgather"])
+@pytest.mark.parametrize("form", ["ulysses", "allgather", "ring"])
 def test_llama_context_parallel_loss_and_gradients(form):
     """A LLaMA whose sequence is sharded over two ranks: the mean over ranks of the loss and of
     every parameter gradient equals the single-process values (RoPE positions continue across
