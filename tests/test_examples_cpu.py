@@ -46,3 +46,11 @@ def test_nlp_audio_tour(examples):
 
 def test_gpu_test_example_without_a_device(examples):
     assert examples("gpu_test").main() == 0
+
+
+def test_context_parallel_example_single_process(examples, monkeypatch):
+    monkeypatch.delenv("WORLD_SIZE", raising=False)
+    sys.modules.pop("context_parallel_llama", None)
+    first = examples("context_parallel_llama").main("ulysses", steps=1)
+    sys.modules.pop("context_parallel_llama", None)
+    assert examples("context_parallel_llama").main("ring", steps=8) < first
