@@ -58,8 +58,18 @@ def sdpa(q, k, v, mask=None, causal: bool = False, scale: float | None = None,
     Hkv = k.shape[2]
     if q.is_cuda and mask is None:
         qt, kt, vt = (t.permute(0, 2, 1, 3) for t in (q, k, v))
-        o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal, scale=scale,
-                                           dropout_p=dropout_p, enable_gqa=(Hkv != Hq))
+        Sk = k.shape[1]
+        attn_mask = None
+        is_causal = causal
+        if causal and Sq != Sk:
+            # The causal mask of this package is aligned to the END of the key sequence (query i
+            # sees keys up to i + Sk - Sq: what a KV cache and a key slice need); torch's
+            # ``is_causal`` aligns to the start, so the mask is passed explicitly.
+            is_causal = False
+            if Sq > 1:
+                attn_mask = torch.ones(Sq, Sk, dtype=torch.bool, device=q.device).tril(Sk - Sq)
+        o = F.scaled_dot_product_attention(qt, kt, vt, attn_mask=attn_mask, is_causal=is_causal,
+                                           scale=scale, dropout_p=dropout_p, enable_gqa=(Hkv != Hq))
         return o.permute(0, 2, 1, 3)
     o = sdpa_reference(q, k, v, mask, causal, scale)
     if dropout_p > 0:

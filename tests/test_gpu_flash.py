@@ -87,3 +87,46 @@ def test_flash_on_sequence_major_key_slices(kernel_status):
     for a, b in ((q, qr), (ks, kr), (vs, vr)):
         assert (a.grad.float() - b.grad).abs().max().item() < 4e-2 * max(1.0, b.grad.abs().max().item())
     assert ks.grad[(r + 1) * s:].abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Sq,Sk", [(1, 5), (3, 9), (7, 7)])
+def test_sdpa_off_the_flash_path_masks_from_the_end_of_the_keys(dtype, Sq, Sk):
+    """Head size 64 (and fp32) does not reach the flash kernels; the path taken instead must use
+    the same causal mask: query i sees keys up to i + Sk - Sq."""
+    from axonml_b200.ops.attention import sdpa, sdpa_reference
+    q = torch.randn(2, Sq, 4, 64, device="cuda", dtype=dtype)
+    k = torch.randn(2, Sk, 2, 64, device="cuda", dtype=dtype)
+    v = torch.randn(2, Sk, 2, 64, device="cuda", dtype=dtype)
+    o = sdpa(q, k, v, causal=True)
+    ref = sdpa_reference(q.float(), k.float(), v.float(), causal=True)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    assert (o.float() - ref).abs().max().item() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_cached_generation_equals_uncached_on_the_gpu(dtype):
+    """Greedy decoding with the KV cache (one query against all keys so far) gives the tokens of
+    decoding by full forward passes; the tiny configuration has head size 16."""
+    from axonml_b200 import llm
+    torch.manual_seed(0)
+    model = llm.LLaMAForCausalLM(llm.LLaMAConfig.tiny()).eval().to("cuda", dtype)
+    ids = torch.randint(0, 100, (1, 6), device="cuda")
+    out = model.generate(ids, max_new_tokens=5)
+    out = out if torch.is_tensor(out) else torch.tensor(out)
+    cur = ids.clone()
+    logits_seen = []
+    with torch.no_grad():
+        for _ in range(5):
+            lg = model(cur)[:, -1].float()
+            logits_seen.append(lg)
+            cur = torch.cat([cur, lg.argmax(-1, keepdim=True)], 1)
+    if dtype == torch.float32:
+        assert torch.equal(out.view(-1).cpu(), cur.view(-1).cpu())
+    else:
+        # bf16 ties can flip an arg-max; the cached run must at least pick a near-best token each step
+        got = out.view(-1)[6:].cpu().tolist()
+        for lg, tok in zip(logits_seen, got):
+            assert lg.max().item() - lg[0, tok].item() < 0.25
+            if tok != lg.argmax(-1).item():
+                break
