@@ -29,23 +29,50 @@ def _entry(rank, world, port, fn, args, q, env):
 
 
 def run_gpu_ranks(fn, world: int = 2, args=(), env=None, timeout_s: float = 180.0):
+    """Runs ``fn(rank, world, backend, *args)`` in one child process per GPU and returns
+    ``{rank: (status, value)}``.
+
+    A rank is never ended from outside while its buffers may be bound to an NVLink multicast
+    object (``AXONML_NVLS`` not "0"): the ranks leave on their own.  That always happens in
+    bounded time, because every device-side wait has a time budget (1 to 2 s) and the process
+    group ends a collective whose partner is missing after 60 s.  Only when NVLS is off is a
+    rank that is still alive after all of that killed, as a last resort."""
+    env = dict(env or {})
+    nvls_off = env.get("AXONML_NVLS", os.environ.get("AXONML_NVLS", "1")) == "0"
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, dict(env or {})), daemon=True)
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, env), daemon=False)
              for r in range(world)]
     [p.start() for p in procs]
     res = {}
+    # one failed rank makes the others run into the 60 s process-group timeout: leave room for it
+    grace = 60.0 + 30.0
     try:
-        for _ in procs:
-            r, st, val = q.get(timeout=timeout_s)
+        import queue as _queue
+        import time as _time
+        deadline = _time.monotonic() + timeout_s
+        while len(res) < world:
+            left = deadline - _time.monotonic()
+            if left <= 0:
+                break
+            try:
+                r, st, val = q.get(timeout=min(left, 5.0))
+            except _queue.Empty:
+                if not any(p.is_alive() for p in procs) and q.empty():
+                    break
+                continue
             res[r] = (st, _unplain(val))
+            if st != "ok":
+                deadline = min(deadline, _time.monotonic() + grace)
     finally:
-        # a rank that is stuck must not keep the test process alive
         for p in procs:
-            p.join(10 if len(res) == len(procs) else 0.1)
-            if p.is_alive():
+            p.join(grace)
+        for p in procs:
+            if p.is_alive() and nvls_off:
                 p.kill()
-    for r, (st, val) in res.items():
+                p.join(5)
+    for r, (st, val) in sorted(res.items()):
         assert st == "ok", f"rank {r}: {val}"
+    assert len(res) == world, f"only ranks {sorted(res)} of {world} reported"
     return res

@@ -9,7 +9,8 @@ from tests._mp_gpu import run_gpu_ranks
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu,
               pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
 
-WORLD = 2 if torch.cuda.device_count() < 4 else min(4, torch.cuda.device_count())
+# the largest power of two of GPUs present, up to 8: the same cases run at 2, 4 and 8 ranks
+WORLD = max(w for w in (1, 2, 4, 8) if w <= max(1, torch.cuda.device_count()))
 
 
 def _fused_allreduce(rank, world, be, dtype_name):
