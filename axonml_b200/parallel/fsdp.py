@@ -87,6 +87,7 @@ class FullyShardedDataParallel(Module):
         self._fused_hp = dict(fused_adamw) if fused_adamw else None
         self._fused = None
         self._fused_step = 0
+        self._fused_pending = False
         self._build()
 
     # ------------------------------------------------------------------ reference builders
@@ -289,9 +290,18 @@ class FullyShardedDataParallel(Module):
     def _enter_backward(self) -> None:
         if self._phase == "bwd":
             return
+        if self._fused is not None and self._sync and self._fused_pending:
+            raise RuntimeError(
+                "FSDP with the in-backward fused AdamW applies the update inside backward: a second "
+                "backward before fused_optimizer().step() would apply a second update. Accumulate "
+                "micro-batches under no_sync() and let only the last backward synchronise.")
         self._phase = "bwd"
         for u in self.units:
             u.pending = len(u.params)
+            # A reduced gradient of an earlier backward that no zero_grad() has cleared: keep it, the
+            # reduction of this backward is added to it (gradient accumulation over micro-batches).
+            if self._sync and u.master._axon_grad is not None:
+                u._carry = u.grad_shard.clone()
         torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)
 
     def _on_grad(self, u: FlatUnit, idx: int, p) -> None:
@@ -341,6 +351,12 @@ class FullyShardedDataParallel(Module):
                 else:
                     self.pg.backend().reduce_scatter(u.grad_flat, u.grad_shard, ReduceOp.Average)
             u.master._axon_grad = u.grad_shard
+        if getattr(u, "_carry", None) is not None:
+            with self._stream_ctx():
+                u.grad_shard.add_(u._carry)
+            u._carry = None
+        if self._fused is not None and u.world > 1:
+            self._fused_pending = True
         u.grad_written = [False] * len(u.params)
         u.reduced = True
 
@@ -357,7 +373,9 @@ class FullyShardedDataParallel(Module):
 
     @contextlib.contextmanager
     def no_sync(self):
-        """Accumulates gradients locally; the next backward outside the context reduces them."""
+        """Accumulates gradients locally; the next backward outside the context reduces them.
+        Backward calls outside the context accumulate as well (each one is reduced and added to the
+        sharded gradient until ``zero_grad``), at the price of one collective per call."""
         old, self._sync = self._sync, False
         try:
             yield
@@ -432,6 +450,7 @@ class FullyShardedDataParallel(Module):
     def zero_grad(self, set_to_none: bool = True) -> None:
         for u in self.units:
             u.master._axon_grad = None
+            u._carry = None
             u.grad_written = [False] * len(u.params)
         for p in self.module.parameters():
             p.grad = None
@@ -499,6 +518,7 @@ class _FusedOptimizerHandle:
 
     def step(self) -> None:
         self.engine._fused_step += 1
+        self.engine._fused_pending = False
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         self.engine.zero_grad()

@@ -6,6 +6,8 @@ single-process training, and failures are produced on the host only (a rank that
 dropped message)."""
 import threading
 
+import contextlib
+
 import pytest
 import torch
 
@@ -210,6 +212,47 @@ def test_fsdp_matches_single_process(strategy):
     for k, v in ref.named_parameters():
         assert torch.allclose(sd0[k], sd1[k], atol=1e-6), k
         assert torch.allclose(sd0[k], v.detach(), atol=5e-4), (k, (sd0[k] - v).abs().max())
+
+
+def _fsdp_accumulate(rank, world, be, strategy_name, use_no_sync):
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import FSDP, ProcessGroup, ShardingStrategy
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(12, 20), nn.Tanh(), nn.Linear(20, 5))
+    f = FSDP(m, ProcessGroup(be), strategy=ShardingStrategy[strategy_name])
+    opt = optim.SGD(f.parameters(), 0.1)
+    g = torch.Generator().manual_seed(11)
+    X, Y = torch.randn(2, 2, 8, 12, generator=g), torch.randint(0, 5, (2, 2, 8), generator=g)
+    for it in range(2):
+        for mb in range(2):
+            ctx = f.no_sync() if (use_no_sync and mb == 0) else contextlib.nullcontext()
+            with ctx:
+                (nn.CrossEntropyLoss()(f(X[it, mb].chunk(world)[rank]), Y[it, mb].chunk(world)[rank]) / 2).backward()
+        opt.step()
+        f.zero_grad()
+    return f.full_state_dict()
+
+
+@pytest.mark.parametrize("use_no_sync", [False, True])
+@pytest.mark.parametrize("strategy", ["FullShard", "NoShard"])
+def test_fsdp_accumulates_gradients_over_micro_batches(strategy, use_no_sync):
+    """Two backward calls before one optimizer step give the gradient of both micro-batches, with
+    and without ``no_sync`` around the first (the reference's torch-style accumulation)."""
+    from axonml_b200 import nn
+    res = run_ranks(_fsdp_accumulate, 2, args=(strategy, use_no_sync))
+    torch.manual_seed(0)
+    ref = nn.Sequential(nn.Linear(12, 20), nn.Tanh(), nn.Linear(20, 5))
+    opt = torch.optim.SGD(ref.parameters(), 0.1)
+    g = torch.Generator().manual_seed(11)
+    X, Y = torch.randn(2, 2, 8, 12, generator=g), torch.randint(0, 5, (2, 2, 8), generator=g)
+    for it in range(2):
+        for mb in range(2):
+            (nn.CrossEntropyLoss()(ref(X[it, mb]), Y[it, mb]) / 2).backward()
+        opt.step()
+        opt.zero_grad()
+    sd = res[0][1]
+    for k, v in ref.named_parameters():
+        assert torch.allclose(sd[k], v.detach(), atol=1e-5), (k, (sd[k] - v).abs().max())
 
 
 def _mlp_fsdp_lamb(rank, world, be):
