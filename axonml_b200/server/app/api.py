@@ -126,7 +126,7 @@ class Router:
 
 class PlatformServer:
     def __init__(self, host: str = "127.0.0.1", port: int = 3021, data_dir: str | None = None, jwt_secret: str | None = None,
-                 inference: InferenceServer | None = None, llm_engine=None, tokenizer=None, allow_registration: bool = True,
+                 inference: InferenceServer | None = None, llm_engine=None, tokenizer=None, allow_registration: bool | None = None,
                  admin_email: str = "admin@axonml.local", admin_password: str | None = None,
                  enable_terminal: bool = False):
         self.data_dir = data_dir
@@ -237,6 +237,7 @@ class PlatformServer:
     def stop(self) -> None:
         self.httpd.shutdown()
         self.httpd.server_close()
+        self.notebooks.shutdown()
 
 
 def _tmp_root() -> str:

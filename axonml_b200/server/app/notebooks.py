@@ -6,15 +6,18 @@ draft/running/completed/failed/stopped, ``CellOutput`` with output_type / text /
 error_name / error_value / traceback (crates/axonml-server/src/db/notebooks.rs:14-80); the
 endpoints create / import / export / start / stop / add, update, delete and execute a cell
 (api/notebooks.rs).  The reference's executor compiles Rust cells with cargo; here a cell is Python
-run in a namespace that persists across the notebook's cells, with ``axonml_b200`` importable.  The
+run by a kernel process of the notebook (never inside the server process) in a namespace that
+persists across the notebook's cells, with ``axonml_b200`` importable.  The
 AI-assist endpoint needs an external Ollama daemon and answers 503 without one."""
 from __future__ import annotations
 
-import contextlib
-import io
 import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
 import threading
-import traceback
 import uuid
 
 from .store import DocumentStore, NotFound, now_iso
@@ -29,48 +32,145 @@ def new_cell(cell_type: str = "code", source: str = "") -> dict:
             "execution_count": None, "metadata": {}}
 
 
-class NotebookKernel:
-    """One Python namespace per notebook; cells run one at a time."""
+# The kernel process: reads one JSON request per line on stdin ({"source": ...}), runs the cell in a
+# namespace that lives as long as the process, and answers with one JSON line on the pipe it was
+# started with.  Whatever the cell prints goes to buffers of this process only.
+_WORKER = r"""
+import ast, contextlib, io, json, os, sys, traceback
+proto = os.fdopen(os.dup(1), "w")
+devnull = os.open(os.devnull, os.O_WRONLY)
+os.dup2(devnull, 1)
+ns = {"__name__": "__notebook__"}
+count = 0
+for line in sys.stdin:
+    req = json.loads(line)
+    count += 1
+    out, err = io.StringIO(), io.StringIO()
+    outputs, ok = [], True
+    try:
+        tree = ast.parse(req["source"], mode="exec")
+        last = None
+        if tree.body and isinstance(tree.body[-1], ast.Expr):
+            last = ast.Expression(tree.body.pop().value)
+        with contextlib.redirect_stdout(out), contextlib.redirect_stderr(err):
+            exec(compile(tree, "<cell>", "exec"), ns)
+            value = eval(compile(last, "<cell>", "eval"), ns) if last is not None else None
+        if out.getvalue():
+            outputs.append({"output_type": "stream", "text": out.getvalue()})
+        if err.getvalue():
+            outputs.append({"output_type": "stream", "text": err.getvalue(), "data": {"name": "stderr"}})
+        if value is not None:
+            outputs.append({"output_type": "execute_result", "text": repr(value), "execution_count": count})
+    except BaseException as e:
+        ok = False
+        if out.getvalue():
+            outputs.append({"output_type": "stream", "text": out.getvalue()})
+        outputs.append({"output_type": "error", "error_name": type(e).__name__, "error_value": str(e),
+                        "traceback": traceback.format_exc().splitlines()})
+    proto.write(json.dumps({"outputs": outputs, "ok": ok, "count": count}) + "\n")
+    proto.flush()
+"""
 
-    def __init__(self):
-        self.ns: dict = {"__name__": "__notebook__"}
+
+class NotebookKernel:
+    """One Python process per notebook; cells run one at a time in a namespace that persists across
+    the notebook's cells.  The process has its own working directory and a scrubbed environment
+    (none of the server's secrets), and a cell that runs longer than ``timeout_s`` ends it: user
+    code never runs inside the server process, which holds the token secret and every user's data
+    (the reference likewise compiles and runs cells out of process)."""
+
+    def __init__(self, timeout_s: float = 120.0, workdir: str | None = None):
+        self.timeout_s = timeout_s
         self.count = 0
         self._lock = threading.Lock()
+        self._own_dir = workdir is None
+        self.workdir = workdir or tempfile.mkdtemp(prefix="axonml-nb-")
+        self._proc: subprocess.Popen | None = None
+
+    def _spawn(self) -> subprocess.Popen:
+        env = {k: v for k, v in os.environ.items()
+               if k in ("PATH", "HOME", "LANG", "LC_ALL", "LD_LIBRARY_PATH", "CUDA_VISIBLE_DEVICES", "VIRTUAL_ENV", "TMPDIR")}
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+        env["PYTHONPATH"] = root
+        return subprocess.Popen([sys.executable, "-u", "-c", _WORKER], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                                stderr=subprocess.DEVNULL, cwd=self.workdir, env=env, text=True, bufsize=1)
+
+    def _kill(self) -> None:
+        p, self._proc = self._proc, None
+        if p is not None:
+            try:
+                p.kill()          # the exact child this kernel started
+                p.wait(5)
+            except Exception:
+                pass
+
+    def close(self) -> None:
+        with self._lock:
+            self._kill()
+            if self._own_dir:
+                shutil.rmtree(self.workdir, ignore_errors=True)
+
+    def __del__(self):
+        try:
+            self._kill()
+        except Exception:
+            pass
 
     def execute(self, source: str) -> tuple[list[dict], bool]:
         with self._lock:
             self.count += 1
-            out, err = io.StringIO(), io.StringIO()
-            outputs: list[dict] = []
-            ok = True
+            if self._proc is None or self._proc.poll() is not None:
+                self._proc = self._spawn()
+            p = self._proc
+            answer: list = []
+
+            def read():
+                try:
+                    answer.append(p.stdout.readline())
+                except Exception:
+                    answer.append("")
             try:
-                import ast
-                tree = ast.parse(source, mode="exec")
-                last = None
-                if tree.body and isinstance(tree.body[-1], ast.Expr):
-                    last = ast.Expression(tree.body.pop().value)
-                with contextlib.redirect_stdout(out), contextlib.redirect_stderr(err):
-                    exec(compile(tree, "<cell>", "exec"), self.ns)
-                    value = eval(compile(last, "<cell>", "eval"), self.ns) if last is not None else None
-                if out.getvalue():
-                    outputs.append({"output_type": "stream", "text": out.getvalue()})
-                if err.getvalue():
-                    outputs.append({"output_type": "stream", "text": err.getvalue(), "data": {"name": "stderr"}})
-                if value is not None:
-                    outputs.append({"output_type": "execute_result", "text": repr(value), "execution_count": self.count})
-            except BaseException as e:  # noqa: BLE001 - a cell may raise anything, SystemExit included
-                ok = False
-                if out.getvalue():
-                    outputs.append({"output_type": "stream", "text": out.getvalue()})
-                outputs.append({"output_type": "error", "error_name": type(e).__name__, "error_value": str(e),
-                                "traceback": traceback.format_exc().splitlines()})
-            return outputs, ok
+                p.stdin.write(json.dumps({"source": source}) + "\n")
+                p.stdin.flush()
+            except (BrokenPipeError, OSError):
+                self._kill()
+                return [_error_output("KernelDied", "the notebook kernel process is gone; it restarts on the next cell")], False
+            t = threading.Thread(target=read, daemon=True)
+            t.start()
+            t.join(self.timeout_s)
+            if t.is_alive():
+                self._kill()
+                return [_error_output("CellTimeout", f"the cell ran longer than {self.timeout_s:g} s; the kernel was restarted "
+                                      "and its variables are gone")], False
+            line = answer[0] if answer else ""
+            if not line:
+                self._kill()
+                return [_error_output("KernelDied", "the notebook kernel process ended while running the cell")], False
+            res = json.loads(line)
+            for o in res["outputs"]:
+                if "execution_count" in o:
+                    o["execution_count"] = self.count
+            return res["outputs"], bool(res["ok"])
+
+
+def _error_output(name: str, value: str) -> dict:
+    return {"output_type": "error", "error_name": name, "error_value": value, "traceback": []}
 
 
 class NotebookService:
-    def __init__(self, store: DocumentStore):
+    def __init__(self, store: DocumentStore, cell_timeout_s: float = 120.0):
         self.col, self.ckpt = store["notebooks"], store["checkpoints"]
         self._kernels: dict[str, NotebookKernel] = {}
+        self.cell_timeout_s = cell_timeout_s
+
+    def _drop_kernel(self, nb_id: str) -> None:
+        k = self._kernels.pop(nb_id, None)
+        if k is not None:
+            k.close()
+
+    def shutdown(self) -> None:
+        for nb_id in list(self._kernels):
+            self._drop_kernel(nb_id)
 
     # ------------------------------------------------------------------ documents
     def create(self, user_id: str, name: str, description: str = "", cells: list[dict] | None = None) -> dict:
@@ -88,7 +188,7 @@ class NotebookService:
         return self.col.update(nb_id, {k: v for k, v in changes.items() if k in ("name", "description", "cells", "metadata")})
 
     def delete(self, nb_id: str) -> None:
-        self._kernels.pop(nb_id, None)
+        self._drop_kernel(nb_id)
         self.ckpt.delete_where({"notebook_id": nb_id})
         self.col.delete(nb_id)
 
@@ -125,11 +225,12 @@ class NotebookService:
 
     # ------------------------------------------------------------------ execution
     def start(self, nb_id: str) -> dict:
-        self._kernels[nb_id] = NotebookKernel()
+        self._drop_kernel(nb_id)
+        self._kernels[nb_id] = NotebookKernel(self.cell_timeout_s)
         return self.col.update(nb_id, {"status": "running"})
 
     def stop(self, nb_id: str) -> dict:
-        self._kernels.pop(nb_id, None)
+        self._drop_kernel(nb_id)
         return self.col.update(nb_id, {"status": "stopped"})
 
     def execute_cell(self, nb_id: str, cell_id: str) -> dict:
@@ -140,7 +241,7 @@ class NotebookService:
             return cell
         k = self._kernels.get(nb_id)
         if k is None:
-            k = self._kernels[nb_id] = NotebookKernel()
+            k = self._kernels[nb_id] = NotebookKernel(self.cell_timeout_s)
         outputs, ok = k.execute(cell["source"])
         cell.update({"outputs": outputs, "status": "completed" if ok else "error", "execution_count": k.count})
         nb = self.col.get(nb_id)                     # other cells may have been edited while this one ran

@@ -17,8 +17,10 @@ def register(app) -> None:
         return {**pair, "user": app.public_user(u), "requires_mfa": False}
 
     def auth_register(req):
-        if not app.allow_registration:
-            raise HttpError(403, "registration is disabled")
+        # allow_registration: True = anyone may register, False = nobody, None (default) = only the
+        # first account, which becomes the administrator and creates the others.
+        if app.allow_registration is False or (app.allow_registration is None and app.users.count() > 0):
+            raise HttpError(403, "registration is disabled; ask an administrator for an account")
         email, name, password = req.need("email", "name", "password")
         if "@" not in email or len(password) < 8:
             raise HttpError(400, "a valid e-mail address and a password of at least 8 characters are required")

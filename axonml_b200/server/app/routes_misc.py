@@ -78,8 +78,13 @@ def register(app) -> None:
         nb.delete_cell(req.params["id"], req.params["cell"])
         return {"deleted": True}
 
-    def nb_execute_cell(req):
+    def _may_run_code(req) -> None:
         _own_nb(req)
+        if req.claims.role not in ("admin", "user"):
+            raise HttpError(403, "running notebook code needs the user or admin role")
+
+    def nb_execute_cell(req):
+        _may_run_code(req)
         return nb.execute_cell(req.params["id"], req.params["cell"])
 
     def nb_ai_assist(req):
@@ -96,9 +101,9 @@ def register(app) -> None:
     r.add("PUT", "/api/notebooks/:id", nb_update)
     r.add("DELETE", "/api/notebooks/:id", nb_delete)
     r.add("GET", "/api/notebooks/:id/export", lambda req: (_own_nb(req), nb.export_ipynb(req.params["id"]))[1])
-    r.add("POST", "/api/notebooks/:id/start", lambda req: (_own_nb(req), nb.start(req.params["id"]))[1])
+    r.add("POST", "/api/notebooks/:id/start", lambda req: (_may_run_code(req), nb.start(req.params["id"]))[1])
     r.add("POST", "/api/notebooks/:id/stop", lambda req: (_own_nb(req), nb.stop(req.params["id"]))[1])
-    r.add("POST", "/api/notebooks/:id/run-all", lambda req: (_own_nb(req), nb.run_all(req.params["id"]))[1])
+    r.add("POST", "/api/notebooks/:id/run-all", lambda req: (_may_run_code(req), nb.run_all(req.params["id"]))[1])
     r.add("POST", "/api/notebooks/:id/cells", nb_add_cell)
     r.add("PUT", "/api/notebooks/:id/cells/:cell", nb_update_cell)
     r.add("DELETE", "/api/notebooks/:id/cells/:cell", nb_delete_cell)

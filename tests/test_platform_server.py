@@ -123,7 +123,8 @@ def test_auth_flow_with_totp_and_recovery(server):
     assert c.req("GET", "/api/auth/me")[0] == 401
     st, j = c.req("POST", "/api/auth/register", {"email": "Ada@example.com", "name": "Ada", "password": "s3cret-pass"})
     assert st == 201 and j["user"]["role"] == "admin"             # first account administers
-    assert c.req("POST", "/api/auth/register", {"email": "ada@example.com", "name": "x", "password": "s3cret-pass"})[0] == 409
+    # by default only the first account may register itself; later accounts come from the administrator
+    assert c.req("POST", "/api/auth/register", {"email": "bob@example.com", "name": "x", "password": "s3cret-pass"})[0] == 403
     assert c.req("POST", "/api/auth/login", {"email": "ada@example.com", "password": "nope"})[0] == 401
     j = _login(c)
     c.token = j["access_token"]
@@ -307,3 +308,55 @@ def test_system_hub_kaggle_terminal_and_dashboard(server):
     assert c.req("GET", "/api/terminal")[0] == 403
     page = c.req("GET", "/")[1]
     assert b"<title>AxonML</title>" in page and b"/api/training/runs" in page
+
+
+def test_open_registration_rejects_a_duplicate_address(tmp_path):
+    s = PlatformServer(port=0, data_dir=str(tmp_path / "srv"), allow_registration=True).start()
+    try:
+        c = Client(s.port)
+        assert c.req("POST", "/api/auth/register", {"email": "Ada@example.com", "name": "Ada", "password": "s3cret-pass"})[0] == 201
+        assert c.req("POST", "/api/auth/register", {"email": "ada@example.com", "name": "x", "password": "s3cret-pass"})[0] == 409
+        st, j = c.req("POST", "/api/auth/register", {"email": "bob@example.com", "name": "Bob", "password": "s3cret-pass"})
+        assert st == 201 and j["user"]["role"] == "user"
+    finally:
+        s.stop()
+
+
+def test_notebook_cells_run_outside_the_server_process(server):
+    """A cell sees neither the server's process nor its environment, output of one notebook never
+    lands in another, a viewer may not run code, and a cell that does not end is cut off."""
+    import os
+    from axonml_b200.server.app.notebooks import NotebookKernel
+    c = Client(server.port)
+    c.req("POST", "/api/auth/register", {"email": "ada@example.com", "name": "Ada", "password": "s3cret-pass"})
+    c.token = _login(c)["access_token"]
+    nb = c.req("POST", "/api/notebooks", {"name": "iso"})[1]
+    code = nb["cells"][1]["id"]
+    c.req("PUT", f"/api/notebooks/{nb['id']}/cells/{code}", {"source": "import os\nos.getpid()"})
+    cell = c.req("POST", f"/api/notebooks/{nb['id']}/cells/{code}/execute")[1]
+    assert cell["status"] == "completed" and int(cell["outputs"][0]["text"]) != os.getpid()
+    os.environ["AXONML_TEST_SECRET"] = "hunter2"
+    try:
+        k = NotebookKernel(timeout_s=20)
+        out, ok = k.execute("import os\nos.environ.get('AXONML_TEST_SECRET')")
+        assert ok and out == []                                        # None: the variable is not passed on
+        out, ok = k.execute("print('a'); 1 + 1")
+        assert ok and out[0]["text"] == "a\n" and out[1]["text"] == "2"
+        k.close()
+    finally:
+        del os.environ["AXONML_TEST_SECRET"]
+    slow = NotebookKernel(timeout_s=1.0)
+    out, ok = slow.execute("import time\ntime.sleep(30)")
+    assert not ok and out[0]["error_name"] == "CellTimeout"
+    out, ok = slow.execute("41 + 1")                                   # a fresh kernel process answers
+    assert ok and out[0]["text"] == "42"
+    slow.close()
+    # a viewer owns a notebook but may not run code
+    admin = c
+    st, v = admin.req("POST", "/api/admin/users", {"email": "vi@example.com", "name": "Vi", "password": "s3cret-pass", "role": "viewer"})
+    assert st in (200, 201), v
+    cv = Client(server.port)
+    cv.token = _login(cv, "vi@example.com")["access_token"]
+    nbv = cv.req("POST", "/api/notebooks", {"name": "mine"})[1]
+    assert cv.req("POST", f"/api/notebooks/{nbv['id']}/cells/{nbv['cells'][1]['id']}/execute")[0] == 403
+    assert cv.req("POST", f"/api/notebooks/{nbv['id']}/run-all")[0] == 403
