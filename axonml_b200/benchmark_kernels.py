@@ -4,6 +4,7 @@ file is present in the working directory, else the stated fallback figures).
 
     python -m axonml_b200.benchmark_kernels gemm flash_fwd rmsnorm      # chosen workloads
     python -m axonml_b200.benchmark_kernels all --iters 20
+    python -m axonml_b200.benchmark_kernels gemm_shapes                 # tile policies against cuBLAS
     python -m axonml_b200.benchmark_kernels gemm --small                # a few launches on a small case
                                                                         # (what a profiler capture uses)
 
@@ -126,6 +127,58 @@ WORKLOADS = {"gemm": w_gemm, "flash_fwd": w_flash_fwd, "flash_bwd": lambda s: w_
              "adamw": w_adamw, "conv": w_conv, "qgemm": w_qgemm, "paged_decode": w_paged}
 
 
+GEMM_SHAPES = [
+    # (name, M, N, K, trans_a, trans_b): the Linear layers of the GPT-1.3B step (8192 tokens) in
+    # forward, data-gradient and weight-gradient form, and the square case.
+    ("square 8192", 8192, 8192, 8192, False, True),
+    ("qkv fwd", 8192, 6144, 2048, False, True),
+    ("proj fwd", 8192, 2048, 2048, False, True),
+    ("fc1 fwd", 8192, 8192, 2048, False, True),
+    ("fc2 fwd", 8192, 2048, 8192, False, True),
+    ("head fwd", 8192, 50304, 2048, False, True),
+    ("qkv dgrad", 8192, 2048, 6144, False, False),
+    ("fc1 dgrad", 8192, 2048, 8192, False, False),
+    ("fc2 dgrad", 8192, 8192, 2048, False, False),
+    ("head dgrad", 8192, 2048, 50304, False, False),
+    ("qkv wgrad", 6144, 2048, 8192, True, False),
+    ("proj wgrad", 2048, 2048, 8192, True, False),
+    ("fc1 wgrad", 8192, 2048, 8192, True, False),
+    ("fc2 wgrad", 2048, 8192, 8192, True, False),
+    ("head wgrad", 50304, 2048, 8192, True, False),
+]
+
+
+def gemm_shapes(iters):
+    """Every tile policy of the GEMM kernel against ``torch.matmul`` (cuBLAS) on the Linear shapes of
+    the GPT-1.3B step.  Operands rotate through more than the L2 capacity between launches."""
+    from .ops.gemm import gemm_bf16, set_pair_mode
+    from .ops.gemm import pair_capacity
+    _, tflops, src = _peaks()
+    print(f"CTA pairs resident at once: {pair_capacity()}")
+    print(f"shape: cuBLAS us | one CTA bn128, bn256 | CTA pair bn128, bn256 | chosen -> TFLOP/s, of {src} peak, of cuBLAS")
+    for name, M, N, K, ta, tb in GEMM_SHAPES:
+        per = (M * K + N * K + M * N) * 2
+        nb = max(2, min(6, (300 << 20) // per + 1))
+        A = [torch.randn((K, M) if ta else (M, K), device="cuda").bfloat16() for _ in range(nb)]
+        B = [torch.randn((N, K) if tb else (K, N), device="cuda").bfloat16() for _ in range(nb)]
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+        def ref(i):
+            a = A[i % nb].t() if ta else A[i % nb]
+            b = B[i % nb].t() if tb else B[i % nb]
+            torch.matmul(a, b, out=out)
+        t_ref = _time(ref, iters)
+        ts = []
+        for mode, bn in ((0, 128), (0, 256), (1, 128), (1, 256), (-1, 0)):
+            set_pair_mode(mode)
+            ts.append(_time(lambda i: gemm_bf16(A[i % nb], B[i % nb], trans_a=ta, trans_b=tb, out=out, bn=bn), iters))
+        set_pair_mode(-1)
+        fl = 2.0 * M * N * K
+        print(f"{name} [{M}x{N}x{K}]: {t_ref:.1f} | {ts[0]:.1f}, {ts[1]:.1f} | {ts[2]:.1f}, {ts[3]:.1f} | {ts[4]:.1f} -> "
+              f"{fl / ts[4] / 1e6:.0f} TFLOP/s, {fl / ts[4] / 1e6 / tflops:.2f}, {t_ref / ts[4]:.2f}", flush=True)
+        del A, B, out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("names", nargs="+")
@@ -133,6 +186,10 @@ def main():
     ap.add_argument("--small", action="store_true", help="small case, three launches (for a profiler capture)")
     a = ap.parse_args()
     from . import _native
+    if a.names == ["gemm_shapes"]:
+        gemm_shapes(a.iters)
+        _native.check_status()
+        return
     names = list(WORKLOADS) if a.names == ["all"] else a.names
     hbm, tflops, src = _peaks()
     print(f"roofline denominators ({src}): {hbm:.0f} GB/s copy, {tflops:.0f} TFLOP/s bf16")

@@ -26,6 +26,17 @@ def gemm_supported(*tensors) -> bool:
     return True
 
 
+def set_pair_mode(mode: int) -> None:
+    """Tile policy of the GEMM: -1 chooses per shape (default), 0 always one CTA per tile, 1 CTA
+    pairs (``tcgen05 cta_group::2``, 256-row tiles) wherever the shape allows them."""
+    N.cuda().ax_gemm_set_pair_mode(int(mode))
+
+
+def pair_capacity() -> int:
+    """CTA pairs (clusters of two) the current GPU runs at once; at most half its SM count."""
+    return int(N.cuda().ax_gemm_pair_capacity())
+
+
 def _as2d(t: torch.Tensor) -> torch.Tensor:
     if t.dim() != 2:
         raise ValueError("expected a 2-D tensor")

@@ -50,6 +50,62 @@ def test_gemm_epilogue(act, bn, kernel_status):
     close(y, fn(zr), 2e-2, 2e-2)
 
 
+@pytest.fixture
+def pair_mode():
+    from axonml_b200.ops.gemm import set_pair_mode
+    set_pair_mode(1)
+    yield
+    set_pair_mode(-1)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 384, 192), (328, 264, 136), (2048, 1024, 1024),
+                                   (4096, 512, 2048), (136, 128, 72), (8192, 640, 520)])
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_cta_pair_layouts(M, N, K, ta, tb, bn, pair_mode, kernel_status):
+    """The two-CTA kernel (each CTA loads its half of the operands, the even CTA issues M = 256
+    MMAs) against an fp32 matmul, ragged edges in every dimension included."""
+    from axonml_b200.ops.gemm import gemm_bf16
+    a = torch.randn((K, M) if ta else (M, K), device=DEV).bfloat16()
+    b = torch.randn((N, K) if tb else (K, N), device=DEV).bfloat16()
+    c = gemm_bf16(a, b, trans_a=ta, trans_b=tb, bn=bn)
+    A = a.float().t() if ta else a.float()
+    B = b.float().t() if tb else b.float()
+    close(c, A @ B, atol=0.02 * (K ** 0.5), rtol=2e-2)
+    # the one-CTA kernel accumulates in the same order: results agree to the last bf16 bit or so
+    from axonml_b200.ops.gemm import set_pair_mode
+    set_pair_mode(0)
+    c1 = gemm_bf16(a, b, trans_a=ta, trans_b=tb, bn=bn)
+    set_pair_mode(1)
+    close(c, c1, atol=1e-2 * (K ** 0.5) * 0.1, rtol=1e-2)
+
+
+@pytest.mark.parametrize("act", ["none", "gelu", "silu"])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_gemm_cta_pair_epilogue(act, bn, pair_mode, kernel_status):
+    from axonml_b200.ops.gemm import gemm_bf16
+    M, N, K = 640, 512, 256
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / K ** 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    y, z = gemm_bf16(a, w, bias=bias, act=act, want_aux=True, bn=bn)
+    zr = a.float() @ w.float().t() + bias
+    fn = {"none": lambda t: t, "gelu": lambda t: F.gelu(t, approximate="tanh"), "silu": F.silu}[act]
+    close(z, zr, 2e-2, 2e-2)
+    close(y, fn(zr), 2e-2, 2e-2)
+
+
+def test_gemm_cta_pair_many_waves(pair_mode, kernel_status):
+    """More tiles than CTA pairs: the stage ring, both accumulators and the barrier phases wrap
+    several times."""
+    from axonml_b200.ops.gemm import gemm_bf16
+    a = torch.randn(8192, 512, device=DEV).bfloat16()
+    b = torch.randn(4096, 512, device=DEV).bfloat16()
+    for bn in (128, 256):
+        c = gemm_bf16(a, b, bn=bn)
+        close(c, a.float() @ b.float().t(), atol=0.02 * 512 ** 0.5, rtol=2e-2)
+
+
 def test_linear_autograd(kernel_status):
     from axonml_b200.ops.linear import linear
     x = torch.randn(4, 96, 256, device=DEV).bfloat16().requires_grad_()
