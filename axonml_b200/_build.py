@@ -64,10 +64,12 @@ def _build_lib(sources: list[Path], out: Path, compiler: list[str], flags: list[
     objs, jobs = [], []
     for src in sources:
         tag = _digest(src, " ".join(compiler + flags))
-        obj = OBJ / f"{src.stem}.{tag}.o"
+        # the library's name is part of the object's: sources of the two libraries share stems
+        stem = f"{out.stem}-{src.stem}"
+        obj = OBJ / f"{stem}.{tag}.o"
         objs.append(obj)
         if not obj.exists():
-            for old in OBJ.glob(f"{src.stem}.*.o"):
+            for old in OBJ.glob(f"{stem}.*.o"):
                 old.unlink()
             jobs.append(compiler + flags + ["-c", str(src), "-o", str(obj)])
     if jobs:
