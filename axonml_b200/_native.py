@@ -132,11 +132,22 @@ def status_word(device=None) -> torch.Tensor:
 class KernelTimeout(RuntimeError):
     """A bounded device-side wait ran out (the kernel still finished and freed its resources)."""
 
+    def __init__(self, code: int, where: int, block: int):
+        super().__init__(f"kernel status code={code} where={where} block={block}")
+        self.code, self.where, self.block = code, where, block
+
 
 def check_status(device=None) -> None:
     """Synchronises and raises ``KernelTimeout`` if any kernel recorded an error."""
     t = status_word(device)
     vals = t.tolist()
     if vals[0] != 0:
-        t.zero_()
-        raise KernelTimeout(f"kernel status code={vals[0]} where={vals[1]} block={vals[2]}")
+        t[:3].zero_()
+        raise KernelTimeout(vals[0], vals[1], vals[2])
+
+
+def set_wait_budget_us(us: int, device=None) -> None:
+    """Time budget of every device-side wait (mbarrier, peer signal) of the kernels launched on
+    ``device`` from now on, in microseconds; 0 restores the built-in budgets (1 to 2 s).  A wait
+    that runs out records code/where/block in the status word and the kernel runs to its end."""
+    status_word(device)[3] = int(us)

@@ -182,12 +182,17 @@ class CudaBackend(Backend):
     def silu_f32(self, x): return self._e().unary(x, "silu")
 
     def gemm_f32(self, a, b):
-        """C = A B for fp32 inputs: operands are rounded to bf16 and multiplied on the tcgen05
-        kernel with fp32 accumulation (tolerance of the reference's GEMM test: 1e-3 / 1e-2)."""
-        from ..ops.gemm import gemm_bf16
-        return gemm_bf16(a.bfloat16(), b.bfloat16(), trans_b=False).float()
+        """C = A B in fp32 (fp32 multiply-add and accumulation on the CUDA cores, the precision of the
+        reference's cuBLAS sgemm; tolerance of its GEMM test: 1e-3 / 1e-2)."""
+        from ..ops.gemm import sgemm_f32
+        return sgemm_f32(a.float(), b.float())
 
-    def gemm_batched_f32(self, a, b): return torch.stack([self.gemm_f32(x, y) for x, y in zip(a, b)])
+    def gemm_batched_f32(self, a, b):
+        """Batched C[i] = A[i] B[i] in one launch (cuda.rs:454-501, sgemmStridedBatched)."""
+        from ..ops.gemm import sgemm_f32
+        a = torch.stack(list(a)) if not torch.is_tensor(a) else a
+        b = torch.stack(list(b)) if not torch.is_tensor(b) else b
+        return sgemm_f32(a.float(), b.float())
 
 
 class _Unavailable(Backend):

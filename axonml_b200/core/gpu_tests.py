@@ -81,6 +81,6 @@ def run_all_tests(config: GpuTestConfig | None = None, backend: CudaBackend | No
             rep.add(GpuTestResult(f"{name}_{n}", ok, err))
     for m, k, n in ((4, 8, 4), (64, 64, 64), (128, 256, 64)):
         a, b = random_vec(m * k, 42).view(m, k), random_vec(k * n, 123).view(k, n)
-        ok, err = assert_close(be.gemm_f32(a.to(dev), b.to(dev)), CpuBackend.matmul(a, b), 2e-2 * k ** 0.5, 2e-2)
+        ok, err = assert_close(be.gemm_f32(a.to(dev), b.to(dev)), CpuBackend.matmul(a, b), 1e-3, 1e-2)
         rep.add(GpuTestResult(f"gemm_{m}x{k}x{n}", ok, err))
     return rep

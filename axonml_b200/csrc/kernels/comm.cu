@@ -36,11 +36,18 @@ __device__ __forceinline__ Ctl ctl_of(const Peers& P, int r) {
 }
 
 // Start of a collective kernel.  Returns false if a wait ran out (the caller skips its work).
-__device__ __forceinline__ bool collective_begin(const Peers& P, uint32_t epoch, int* status) {
+// `done_base` (meaningful in thread 0 of block 0): the count of finished blocks before this launch; it
+// is read before any block of this launch can have reported, and makes the end-of-launch count
+// independent of how many calls this rank has made (a rank may have left a call out).
+__device__ __forceinline__ bool collective_begin(const Peers& P, uint32_t epoch, int* status, uint32_t& done_base) {
   __shared__ int s_ok;
   Ctl me = ctl_of(P, P.rank);
+  done_base = 0;
   if (blockIdx.x == 0) {
-    if (threadIdx.x == 0) s_ok = 1;
+    if (threadIdx.x == 0) {
+      s_ok = 1;
+      done_base = ld_acquire_gpu(me.done);
+    }
     __syncthreads();
     if ((int)threadIdx.x < P.world) {
       st_release_sys(ctl_of(P, threadIdx.x).a + P.rank, epoch);
@@ -65,7 +72,7 @@ __device__ __forceinline__ bool collective_begin(const Peers& P, uint32_t epoch,
 // End of a collective kernel: all blocks report, block 0 exchanges `flag` (0/1) with every rank.
 // Returns the OR of all ranks' flags (valid in block 0 only).
 __device__ __forceinline__ int collective_end(const Peers& P, uint32_t epoch, int local_flag,
-                                              int* status) {
+                                              int* status, uint32_t done_base) {
   __shared__ int s_any;
   Ctl me = ctl_of(P, P.rank);
   __syncthreads();
@@ -77,7 +84,7 @@ __device__ __forceinline__ int collective_end(const Peers& P, uint32_t epoch, in
   if (blockIdx.x != 0) return 0;
   if (threadIdx.x == 0) {
     s_any = 0;
-    wait_ge<false>(me.done, epoch * gridDim.x, status, 602);
+    wait_ge<false>(me.done, done_base + gridDim.x, status, 602);
   }
   __syncthreads();
   if ((int)threadIdx.x < P.world) {
@@ -157,7 +164,8 @@ fused_allreduce_kernel(const Peers P, long base_off, long n, float mul, const fl
   // captured in a CUDA graph and replayed: every block reads the counter at entry, block 0
   // advances it after all blocks of this launch have finished.
   if (epoch_dev != nullptr) epoch = *(volatile uint32_t*)epoch_dev + 1;
-  const bool ok = collective_begin(P, epoch, status);
+  uint32_t done_base;
+  const bool ok = collective_begin(P, epoch, status, done_base);
   int bad = 0;
   if (ok) {
     const int esz = BF16 ? 2 : 4;
@@ -183,7 +191,7 @@ fused_allreduce_kernel(const Peers P, long base_off, long n, float mul, const fl
     }
   }
   bad = __syncthreads_or(bad);
-  const int any = collective_end(P, epoch, bad, status);
+  const int any = collective_end(P, epoch, bad, status, done_base);
   if (blockIdx.x == 0 && threadIdx.x == 0 && any && found_inf) *found_inf = 1;
   if (blockIdx.x == 0 && threadIdx.x == 0 && epoch_dev != nullptr) *(volatile uint32_t*)epoch_dev = epoch;
 }
@@ -200,7 +208,8 @@ __global__ void __launch_bounds__(kThreads)
 fused_rs_adamw_kernel(const Peers P, long grad_off, long shard, float* master, float* m1, float* m2,
                       __nv_bfloat16* lp, const Peers push, long push_off, const AdamW h,
                       const int* skip_flag, uint32_t epoch, int* status) {
-  const bool ok = collective_begin(P, epoch, status);
+  uint32_t done_base;
+  const bool ok = collective_begin(P, epoch, status, done_base);
   if (ok && !(skip_flag && *skip_flag)) {
     const long lo = grad_off + shard * 2 * P.rank;
     for (long i = ((long)blockIdx.x * kThreads + threadIdx.x) * 8; i < shard;
@@ -241,7 +250,7 @@ fused_rs_adamw_kernel(const Peers P, long grad_off, long shard, float* master, f
       }
     }
   }
-  collective_end(P, epoch, 0, status);
+  collective_end(P, epoch, 0, status, done_base);
 }
 
 // Every launch on one communicator uses the same grid (the per-GPU completion counter advances by

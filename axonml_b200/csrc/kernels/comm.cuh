@@ -54,7 +54,7 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target, int*
     if (++spins >= 32) {
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kPeerWaitBudgetNs) {
+      else if (now - t0 > wait_budget_ns(status, kPeerWaitBudgetNs)) {
         set_status(status, kPeerTimeout, where);
         return false;
       }

@@ -16,7 +16,8 @@
 namespace ax {
 
 // ---------------------------------------------------------------- status word
-// status[0] = first error code (0 = ok), status[1] = detail (where), status[2] = block id
+// status[0] = first error code (0 = ok), status[1] = detail (where), status[2] = block id,
+// status[3] = wait budget in microseconds set by the host (0 = the built-in budgets)
 enum StatusCode : int {
   kOk = 0,
   kWaitTimeout = 1,   // an mbarrier / flag wait ran out
@@ -41,6 +42,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 
 // Wait budget for on-chip waits (TMA landing, MMA retiring): far above any legal latency.
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s
+
+// The budget a wait works with: the host's value from the status word when it set one (tests make
+// a wait run out in milliseconds that way), else `builtin_ns`.  Read on the slow path only.
+__device__ __forceinline__ uint64_t wait_budget_ns(const int* status, uint64_t builtin_ns) {
+  if (status != nullptr) {
+    const int us = *(const volatile int*)(status + 3);
+    if (us > 0) return (uint64_t)us * 1000ull;
+  }
+  return builtin_ns;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -123,7 +134,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitBudgetNs) {
+      } else if (now - t0 > wait_budget_ns(status, kWaitBudgetNs)) {
         *dead = 1;
         set_status(status, kWaitTimeout, where);
         return false;

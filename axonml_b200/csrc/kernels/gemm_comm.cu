@@ -11,12 +11,17 @@
 //
 //  MODE_RS  GEMM -> reduce-scatter (row-parallel Linear with sequence-parallel output):
 //           out[Tl, N] = act(sum_r (X_r[W*Tl, Kl] * B_r[N, Kl]^T)[rows of this rank] + bias).
-//           Every rank computes its partial product tile by tile, the destination shard after
-//           its own first and its own shard last, and the epilogue sends each finished tile
-//           (bf16, TMEM -> shared memory -> tensor bulk store) into the destination rank's staging
-//           slot for this source, then raises a per-tile flag there.  The tiles of the rank's own
-//           rows come last: their epilogue waits for the peers' flags, adds the W-1 staged copies
-//           to the fp32 accumulator and writes the result.  Deterministic (no floating-point atomics).
+//           Every rank computes its whole partial product tile by tile.  The epilogue sends each
+//           finished tile in bf16 (TMEM -> shared memory -> contiguous 4 KB bulk stores, which need
+//           no thread while they are in flight) into slot `source rank` of the staging buffer of the
+//           rank that owns those rows, its own tiles into its own slot, and raises the tile's flag
+//           there one tile later, when the stores have landed.  The accumulator is released as
+//           soon as the tile is in shared memory: the math never waits for the network.  All ranks
+//           walk the tiles in the same order, so the W copies of a tile exist at about the same time.
+//           Reducer warps (four dedicated ones per CTA, joined by the epilogue warps when those
+//           run out of tiles) take the tiles of this rank's own rows: when the W flags of a tile
+//           are up they add its W staged copies, all in local memory by then, in fp32, add the
+//           bias, apply the activation and write the output.  Deterministic (no atomics on data).
 //
 // Flags hold the call's epoch and only grow; a rank tells its peers "call e consumed" at the end
 // of the kernel, and the next call waits for that before it overwrites peer memory.  Every wait
@@ -35,6 +40,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;      // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: epilogue
+constexpr int kThreadsRS = 320;    // MODE_RS adds warps 6..9: reducers of this rank's own rows
 constexpr int kEpiWarps = 4;
 constexpr int kStageBufBytes = 32 * 128;
 constexpr int kSigDone = 0;        // [kMaxRanks] "rank p consumed call e"
@@ -58,6 +64,9 @@ struct CommParams {
   int bias_kind;             // 0 none, 1 fp32, 2 bf16
   int act;
   int pushers;               // AG: CTAs that only copy
+  int fill_own;              // AG: the copy CTAs also fill this rank's own slot of its gathered buffer
+  int lazy_done;             // AG: "call e consumed" is sent at the start of call e+1 instead of the end of
+                             //     call e, because later kernels on the stream still read the gathered buffer
   int max_tiles;             // flags per source rank
   int* status;
   unsigned long long* trace; // optional timeline [grid][kTraceSlots] of globaltimer stamps, or null
@@ -84,18 +93,38 @@ __device__ __forceinline__ void fence_proxy_async_global() {
   asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 
-// Tile t of this CTA's schedule -> (shard, m block inside the shard, n block).
+// Tile t of the schedule -> (shard, m block inside the shard, n block).  Tiles are taken in groups
+// of `g` 128-row blocks of every shard (g * W row blocks, about eight); inside a group the column
+// block is the outer index, so CTAs that run together share B tiles and the group's rows of A stay
+// in L2 while all column blocks sweep over them.
+//  AG: the pushers send block c of every shard at about the same time (one multimem store or one
+//      round of bulk stores reaches all peers), so the blocks are consumed in that order; inside a
+//      group the ring starts at this rank's own shard, which needs no transfer.
+//  RS: the same order on every rank, so that the W partial copies of a tile exist at about the
+//      same time and its owner can add them up while the next tiles are computed.
 struct TileMap {
-  int mbs, num_n, rank, world, first;   // first: offset of the first shard relative to `rank`
-  __device__ __forceinline__ void coords(int t, int& ring_pos, int& shard, int& mb, int& nb) const {
-    const int per_shard = mbs * num_n;
-    ring_pos = t / per_shard;
-    const int r = t - ring_pos * per_shard;
-    mb = r / num_n;
-    nb = r - mb * num_n;
-    shard = (rank + first + ring_pos) % world;
+  int mbs, num_n, rank, world, rs, g;
+  __device__ __forceinline__ void coords(int t, int& shard, int& mb, int& nb) const {
+    const int per_group = g * world * num_n;
+    const int grp = t / per_group;
+    const int first = grp * g;
+    const int gsz = min(g, mbs - first);
+    const int r = t - grp * per_group;
+    const int rows = gsz * world;
+    nb = r / rows;
+    const int m = r - nb * rows;
+    const int pos = m / gsz;
+    mb = first + (m - pos * gsz);
+    shard = rs ? pos : (rank + pos) % world;
   }
 };
+
+// RS staging buffer of a rank: [source rank][128-row block][64-column chunk][row quarter] pieces
+// of 4 KB, each the shared-memory image (128-byte swizzle) of a 32 x 64 bf16 sub-tile.
+__device__ __forceinline__ long stage_off(int mbs, int N, int src, int mb, int chunk, int quarter) {
+  const int nchunks = (N + 63) >> 6;
+  return ((((long)src * mbs + mb) * nchunks + chunk) * kEpiWarps + quarter) * (long)kStageBufBytes;
+}
 
 // This rank's shard -> slot `rank` of every peer's gathered buffer, one 128-row chunk at a time.
 // One thread runs the whole copy as an asynchronous pipeline: bulk loads bring 16 KB pieces of the
@@ -135,8 +164,11 @@ __device__ void push_shard_multimem(const CommParams& p, int pusher, int npusher
     mbar_fence_init();
   }
   __syncthreads();
-  if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank)
+  if ((int)threadIdx.x < p.world && (int)threadIdx.x != p.rank) {
+    // stream order has put every reader of the previous call's gathered rows on this GPU before this launch
+    if (p.lazy_done && pusher == 0) st_release_sys(p.sig[threadIdx.x] + kSigDone + p.rank, p.epoch - 1);
     if (!wait_ge<true>(p.sig[p.rank] + kSigDone + threadIdx.x, p.epoch - 1, p.status, 802)) s_ok = 0;
+  }
   __syncthreads();
   if (!s_ok) return;
   int my_chunks = 0;
@@ -197,6 +229,11 @@ __device__ void push_shard(const CommParams& p, int pusher, int npushers, uint8_
   for (int i = 0; i < kPushStages; ++i) mbar_init(&full[i], 1);
   mbar_fence_init();
   // the peers must have finished reading what the previous call put there
+  if (p.lazy_done && pusher == 0) {
+    __threadfence_system();
+    for (int q = 0; q < p.world; ++q)
+      if (q != p.rank) st_release_sys(p.sig[q] + kSigDone + p.rank, p.epoch - 1);
+  }
   for (int q = 0; q < p.world; ++q)
     if (q != p.rank && !wait_ge<true>(p.sig[p.rank] + kSigDone + q, p.epoch - 1, p.status, 800)) return;
   int my_chunks = 0;
@@ -215,7 +252,7 @@ __device__ void push_shard(const CommParams& p, int pusher, int npushers, uint8_
     if (!mbar_wait(&full[st], (uint32_t)((i / kPushStages) & 1), dead, p.status, 801)) break;
     const int c = pusher + (int)(i / pieces) * npushers;
     const long dst_off = ((long)p.rank * p.Tl + (long)c * BM) * row_bytes + (i % pieces) * (long)kPushPiece;
-    for (int q = 1; q < p.world; ++q)
+    for (int q = p.fill_own ? 0 : 1; q < p.world; ++q)
       bulk_store_1d(p.sym[(p.rank + q) % p.world] + dst_off, buf + st * kPushPiece, kPushPiece);
     tma_store_commit();
     // the stage that piece i + kPushAhead will use was last read by the stores of piece
@@ -244,27 +281,87 @@ __device__ __forceinline__ void finish_call(const CommParams& p) {
     __threadfence_system();
     uint32_t* counter = p.sig[p.rank] + kSigCounter;
     const uint32_t old = atomicAdd(counter, 1u);
-    if (old + 1 == p.epoch * gridDim.x) {
+    if (old + 1 == p.epoch * gridDim.x && !p.lazy_done) {
       for (int q = 0; q < p.world; ++q)
         if (q != p.rank) st_release_sys(p.sig[q] + kSigDone + p.rank, p.epoch);
     }
   }
 }
 
-// RS staging buffer of a rank: [source rank][128-row block][64-column chunk][epilogue warp] pieces
-// of 4 KB, each the shared-memory image (128-byte swizzle) of a 32 x 64 bf16 sub-tile.
-__device__ __forceinline__ long stage_off(const CommParams& p, const TileMap& tm, int src, int mb, int chunk, int ew) {
-  const int nchunks = (p.N + 63) >> 6;
-  return ((((long)src * tm.mbs + mb) * nchunks + chunk) * kEpiWarps + ew) * (long)kStageBufBytes;
+// Reduction of this rank's own rows (MODE_RS).  Work items are (own tile of this CTA, row quarter)
+// pairs handed out through a shared counter, in tile order.  A warp adds the W staged copies of
+// the quarter's 4 KB pieces; lane l owns the 16-byte units l, l + 32, ... of a piece (unit u = row
+// u / 8, physical chunk u % 8 of the swizzled image).
+template <int BN>
+__device__ void reduce_own_rows(const CommParams& p, const TileMap& tm, int cta, int ncta, int* next_item, int lane) {
+  const uint32_t* my_flags = p.sig[p.rank] + kSigFlags;
+  const int own_tiles = tm.mbs * tm.num_n;
+  const int my_tiles = own_tiles > cta ? (own_tiles - cta + ncta - 1) / ncta : 0;
+  const uint8_t* stage = p.sym[p.rank];
+  while (true) {
+    int item = 0;
+    if (lane == 0) item = atomicAdd(next_item, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= my_tiles * kEpiWarps) return;
+    const int j = cta + (item / kEpiWarps) * ncta;
+    const int quarter = item % kEpiWarps;
+    const int mb = j / tm.num_n, nb = j - mb * tm.num_n;
+    bool w_ok = true;      // lane l: this quarter of the tile as sent by rank l
+    if (lane < p.world)
+      w_ok = wait_ge<true>(my_flags + ((lane * p.max_tiles + j) * kFlagsPerTile + quarter), p.epoch, p.status, 840);
+    if (!__all_sync(0xffffffffu, w_ok)) return;
+#pragma unroll 1
+    for (int ch = 0; ch < BN / 64; ++ch) {
+      const int ncol0 = nb * BN + ch * 64;
+      if (ncol0 >= p.N) break;
+      float a[8][8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[i][e] = 0.f;
+      for (int src = 0; src < p.world; ++src) {
+        const uint8_t* piece = stage + stage_off(tm.mbs, p.N, src, mb, ncol0 >> 6, quarter) + lane * 16;
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = ld_peer_v4(piece + i * 512);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 f0 = unpack_bf16x2(v[i].x), f1 = unpack_bf16x2(v[i].y), f2 = unpack_bf16x2(v[i].z),
+                       f3 = unpack_bf16x2(v[i].w);
+          a[i][0] += f0.x; a[i][1] += f0.y; a[i][2] += f1.x; a[i][3] += f1.y;
+          a[i][4] += f2.x; a[i][5] += f2.y; a[i][6] += f3.x; a[i][7] += f3.y;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int u = lane + 32 * i;
+        const int row = u >> 3;
+        const int col = ncol0 + (((u & 7) ^ (row & 7)) << 3);      // logical 8-column group of this unit
+        if (p.bias_kind == 1) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[i][e] += __ldg((const float*)p.bias + col + e);
+        } else if (p.bias_kind == 2) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[i][e] += __bfloat162float(((const __nv_bfloat16*)p.bias)[col + e]);
+        }
+        if (p.act != kActNone) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[i][e] = apply_act(a[i][e], p.act);
+        }
+        uint4 o;
+        o.x = pack_bf16x2(a[i][0], a[i][1]); o.y = pack_bf16x2(a[i][2], a[i][3]);
+        o.z = pack_bf16x2(a[i][4], a[i][5]); o.w = pack_bf16x2(a[i][6], a[i][7]);
+        *reinterpret_cast<uint4*>(p.out + (((long)(mb * BM + quarter * 32 + row)) * p.N + col) * 2) = o;
+      }
+    }
+  }
 }
 
-struct DstMaps { CUtensorMap m[kMaxRanks]; };     // RS: every rank's staging buffer as [world*Tl, N]
-
-template <int BN, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int MODE, int B_MN>
+__global__ void __launch_bounds__(MODE == MODE_RS ? kThreadsRS : kThreads, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_local,
                  const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
-                 const __grid_constant__ DstMaps dst_maps, const CommParams p) {
+                 const CommParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -294,7 +391,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   tm.num_n = (p.N + BN - 1) / BN;
   tm.rank = p.rank;
   tm.world = p.world;
-  tm.first = MODE == MODE_AG ? 0 : 1;          // AG: own shard first; RS: own shard last
+  tm.rs = MODE == MODE_RS ? 1 : 0;
+  tm.g = max(1, 8 / p.world);
+  __shared__ int s_next_item;
   const int num_tiles = p.world * tm.mbs * tm.num_n;
   const int num_kb = (p.K + BK - 1) / BK;
   uint32_t* my_flags = p.sig[p.rank] + kSigFlags;
@@ -302,6 +401,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (threadIdx.x == 0) {
     trace_at(p, 0);
     *dead = 0;
+    s_next_item = 0;
     for (int i = 0; i < C::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], kEpiWarps); }
     mbar_fence_init();
@@ -320,8 +420,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int s = 0;
       uint32_t ph = 0;
       for (int t = cta; t < num_tiles; t += ncta) {
-        int ring_pos, shard, mb, nb;
-        tm.coords(t, ring_pos, shard, mb, nb);
+        int shard, mb, nb;
+        tm.coords(t, shard, mb, nb);
         const CUtensorMap* ma = &map_a;
         int m0 = shard * p.Tl + mb * BM;
         if (MODE == MODE_AG) {
@@ -338,9 +438,15 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, dead, p.status, 811)) break;
           uint8_t* sa = stage_base + s * C::kStage;
+          uint8_t* sb = sa + C::kStageA;
           mbar_expect_tx(&full_bar[s], C::kStage);
           tma_load_2d(sa, ma, &full_bar[s], kb * BK, m0);
-          tma_load_2d(sa + C::kStageA, &map_b, &full_bar[s], kb * BK, n0);
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &map_b, &full_bar[s], n0 + j * 64, kb * BK);
+          } else {
+            tma_load_2d(sb, &map_b, &full_bar[s], kb * BK, n0);
+          }
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
         if (*dead) break;
@@ -349,10 +455,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, 0, 0);
+      constexpr uint32_t idesc = umma_idesc_f16(1, BM, BN, 0, B_MN);
       // descriptors of stage 0, advanced per stage and k step (keeps the issuing thread short)
       const uint64_t da0 = umma_desc_sw128(smem_u32(stage_base), 16, 1024);
-      const uint64_t db0 = umma_desc_sw128(smem_u32(stage_base) + C::kStageA, 16, 1024);
+      const uint64_t db0 = B_MN ? umma_desc_sw128(smem_u32(stage_base) + C::kStageA, BK * 128, 1024)
+                                : umma_desc_sw128(smem_u32(stage_base) + C::kStageA, 16, 1024);
+      constexpr uint32_t kStepA = (UMMA_K * 2) >> 4;
+      constexpr uint32_t kStepB = (B_MN ? UMMA_K * 128 : UMMA_K * 2) >> 4;
       int s = 0, it = 0;
       uint32_t ph = 0;
       for (int t = cta; t < num_tiles; t += ncta, ++it) {
@@ -366,40 +475,28 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint64_t soff = (uint64_t)((uint32_t)(s * C::kStage) >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_f16_ss(d_tmem, da0 + soff + (uint64_t)(k * ((UMMA_K * 2) >> 4)), db0 + soff + (uint64_t)(k * ((UMMA_K * 2) >> 4)),
+            umma_f16_ss(d_tmem, da0 + soff + (uint64_t)(k * kStepA), db0 + soff + (uint64_t)(k * kStepB),
                         idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&empty_bar[s]);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
         umma_commit(&tfull_bar[acc]);
-        trace_at(p, 2 + 4 * it + 3);
+        if (it < 15) trace_at(p, 2 + 4 * it + 3);
         if (*dead) break;
       }
     }
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     // ------------------------------------------------------------ epilogue (4 warps)
-    const int q = warp & 3;
+    const int q = warp & 3;            // TMEM lane quarter = row quarter of the tile this warp drains
     const int ew = warp - 2;
     uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
     int buf = 0, it = 0;
+    int pend_shard = -1, pend_tile = 0;          // lane 0: the tile whose flag is still owed
     bool ok = true;
-    // lane 0: remote tiles [pend_first, pend_first + pend_n * ncta) of ring phase `pend_shard` whose
-    // flags are still owed.  A completion wait on stores to a peer costs a round trip under load,
-    // so flags go out once per ring phase (the owner needs them only for its own rows, which it
-    // computes last), one tile into the next phase so that the wait overlaps that tile's work.
-    int pend_first = 0, pend_n = 0, pend_shard = -1;
-    auto release_flags = [&](int first, int n) {
-      fence_proxy_async_global();
-      __threadfence_system();
-      for (int i = 0; i < n; ++i) {
-        int rp, sh, mb2, nb2;
-        tm.coords(first + i * ncta, rp, sh, mb2, nb2);
-        st_release_sys(p.sig[sh] + kSigFlags + ((p.rank * p.max_tiles + mb2 * tm.num_n + nb2) * kFlagsPerTile + ew), p.epoch);
-      }
-    };
     if (MODE == MODE_RS) {
-      // peers must have consumed the previous call before their staging slots are overwritten
-      // (every warp checks for itself: no barrier that a timed-out warp could leave hanging)
+      // the peers must have added up the previous call's partial tiles before their staging slots
+      // are overwritten (every warp checks for itself: no barrier that a timed-out warp could
+      // leave hanging)
       bool w_ok = true;
       if (lane < p.world && lane != p.rank) w_ok = wait_ge<true>(p.sig[p.rank] + kSigDone + lane, p.epoch - 1, p.status, 830);
       ok = __all_sync(0xffffffffu, w_ok);
@@ -407,15 +504,15 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     if (ew == 0 && lane == 0) trace_at(p, 1);
     for (int t = cta; t < num_tiles && ok; t += ncta, ++it) {
-      int ring_pos, shard, mb, nb;
-      tm.coords(t, ring_pos, shard, mb, nb);
+      int shard, mb, nb;
+      tm.coords(t, shard, mb, nb);
       const int m0 = shard * p.Tl + mb * BM, n0 = nb * BN;
       const int acc = it & 1;
       ok = mbar_wait(&tfull_bar[acc], (it >> 1) & 1, dead, p.status, 831);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      if (ew == 0 && lane == 0) trace_at(p, 2 + 4 * it);
+      if (ew == 0 && lane == 0 && it < 15) trace_at(p, 2 + 4 * it);
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int ch = 0; ch < BN / 64; ++ch) {
@@ -437,149 +534,64 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (MODE == MODE_AG) {
           add_bias_chunk(r, p.bias, p.bias_kind, ncol0, p.N);
           apply_act_chunk(r, p.act);
-          uint8_t* dst = stg + buf * kStageBufBytes;
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
-            o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
-            o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
-            o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&map_c, dst, ncol0, m0 + q * 32);
-            tma_store_commit();
-          }
-          buf ^= 1;
-        } else if (shard != p.rank) {
-          // partial tile -> staging slot `rank` on the rank that owns these rows: the warp's
-          // 32 x 64 sub-tile is staged in shared memory and sent as one contiguous 4 KB bulk
-          // store (the staging buffer is tile-ordered; row-strided 128-byte writes over NVLink
-          // ran at a third of the rate)
-          uint8_t* dst = stg + buf * kStageBufBytes;
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
-            o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
-            o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
-            o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            bulk_store_1d(p.sym[shard] + stage_off(p, tm, p.rank, mb, ncol0 >> 6, ew), dst, kStageBufBytes);
-            tma_store_commit();
-          }
-          buf ^= 1;
-        } else {
-          // a tile of this rank's own rows (scheduled last): add the peers' staged partial tiles
-          // to the fp32 accumulator and write the finished output; nothing is staged locally
-          if (ch == 0) {
-            // the flag still owed for the last remote tile must go out first: the peers' own-row
-            // tiles wait for it exactly as this one waits for theirs
-            if (lane == 0 && pend_n > 0) {
-              tma_store_wait<0>();
-              release_flags(pend_first, pend_n);
-              pend_n = 0;
-            }
-            __syncwarp();
-            bool w_ok = true;       // lane l: the same quarter of this tile as sent by rank l
-            if (lane < p.world && lane != p.rank)
-              w_ok = wait_ge<true>(my_flags + ((lane * p.max_tiles + mb * tm.num_n + nb) * kFlagsPerTile + ew), p.epoch,
-                                   p.status, 840);
-            ok = __all_sync(0xffffffffu, w_ok);
-            if (ew == 0 && lane == 0) trace_at(p, 2 + 4 * it + 1);
-          }
-          if (ok) {
-            // two peers' pieces per round: sixteen 16-byte loads in flight per lane, so the W-1
-            // dependent round trips to memory become (W-1)/2
-            for (int j = 1; j < p.world; j += 2) {
-              const int s0 = (p.rank + j) % p.world;
-              const bool two = j + 1 < p.world;
-              const int s1 = two ? (p.rank + j + 1) % p.world : s0;
-              // the staged piece keeps the shared-memory image: row `lane`, 16-byte chunks swizzled
-              const uint8_t* sp0 = p.sym[p.rank] + stage_off(p, tm, s0, mb, ncol0 >> 6, ew) + lane * 128;
-              const uint8_t* sp1 = p.sym[p.rank] + stage_off(p, tm, s1, mb, ncol0 >> 6, ew) + lane * 128;
-              uint4 u[8], v[8];
-#pragma unroll
-              for (int c = 0; c < 8; ++c) u[c] = ld_peer_v4(sp0 + ((c ^ (lane & 7)) << 4));
-              if (two) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = ld_peer_v4(sp1 + ((c ^ (lane & 7)) << 4));
-              } else {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = make_uint4(0u, 0u, 0u, 0u);
-              }
-#pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const float2 x0 = unpack_bf16x2(u[c].x), x1 = unpack_bf16x2(u[c].y), x2 = unpack_bf16x2(u[c].z),
-                             x3 = unpack_bf16x2(u[c].w);
-                const float2 y0 = unpack_bf16x2(v[c].x), y1 = unpack_bf16x2(v[c].y), y2 = unpack_bf16x2(v[c].z),
-                             y3 = unpack_bf16x2(v[c].w);
-                r[c * 8 + 0] = __float_as_uint(__uint_as_float(r[c * 8 + 0]) + (x0.x + y0.x));
-                r[c * 8 + 1] = __float_as_uint(__uint_as_float(r[c * 8 + 1]) + (x0.y + y0.y));
-                r[c * 8 + 2] = __float_as_uint(__uint_as_float(r[c * 8 + 2]) + (x1.x + y1.x));
-                r[c * 8 + 3] = __float_as_uint(__uint_as_float(r[c * 8 + 3]) + (x1.y + y1.y));
-                r[c * 8 + 4] = __float_as_uint(__uint_as_float(r[c * 8 + 4]) + (x2.x + y2.x));
-                r[c * 8 + 5] = __float_as_uint(__uint_as_float(r[c * 8 + 5]) + (x2.y + y2.y));
-                r[c * 8 + 6] = __float_as_uint(__uint_as_float(r[c * 8 + 6]) + (x3.x + y3.x));
-                r[c * 8 + 7] = __float_as_uint(__uint_as_float(r[c * 8 + 7]) + (x3.y + y3.y));
-              }
-            }
-            add_bias_chunk(r, p.bias, p.bias_kind, ncol0, p.N);
-            apply_act_chunk(r, p.act);
-            uint8_t* dst = stg + buf * kStageBufBytes;
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&map_c, dst, ncol0, mb * BM + q * 32);
-              tma_store_commit();
-            }
-            buf ^= 1;
-          }
         }
-      }
-      if (ew == 0 && lane == 0) trace_at(p, 2 + 4 * it + 2);
-      if (MODE == MODE_RS && shard != p.rank) {
+        // AG: a tile of the result (tensor store).  RS: a partial tile for the owner of these rows,
+        // sent as one contiguous 4 KB piece per warp and chunk (row-strided 128-byte writes over
+        // NVLink ran at a third of the rate); this rank's own tiles take the same path locally.
+        uint8_t* dst = stg + buf * kStageBufBytes;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(r[c * 8 + 0]), __uint_as_float(r[c * 8 + 1]));
+          o.y = pack_bf16x2(__uint_as_float(r[c * 8 + 2]), __uint_as_float(r[c * 8 + 3]));
+          o.z = pack_bf16x2(__uint_as_float(r[c * 8 + 4]), __uint_as_float(r[c * 8 + 5]));
+          o.w = pack_bf16x2(__uint_as_float(r[c * 8 + 6]), __uint_as_float(r[c * 8 + 7]));
+          *reinterpret_cast<uint4*>(dst + lane * 128 + ((c ^ (lane & 7)) << 4)) = o;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
         if (lane == 0) {
-          if (pend_n > 0 && pend_shard != shard) {
-            tma_store_wait<BN / 64>();          // all but this tile's groups: the last phase has landed
-            release_flags(pend_first, pend_n);
-            pend_n = 0;
+          if (MODE == MODE_AG) tma_store_2d(&map_c, dst, ncol0, m0 + q * 32);
+          else bulk_store_1d(p.sym[shard] + stage_off(tm.mbs, p.N, p.rank, mb, ncol0 >> 6, q), dst, kStageBufBytes);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      if (MODE == MODE_RS) {
+        // The flag of a tile goes out one tile later: by then its stores have landed and the
+        // completion wait costs nothing (a wait right after the stores costs a round trip).
+        if (lane == 0) {
+          if (pend_shard >= 0) {
+            tma_store_wait<BN / 64>();              // everything but this tile's stores
+            fence_proxy_async_global();
+            __threadfence_system();
+            st_release_sys(p.sig[pend_shard] + kSigFlags + ((p.rank * p.max_tiles + pend_tile) * kFlagsPerTile + q), p.epoch);
           }
-          if (pend_n == 0) { pend_first = t; pend_shard = shard; }
-          ++pend_n;
+          pend_shard = shard;
+          pend_tile = mb * tm.num_n + nb;
         }
         __syncwarp();
       }
-    }
-    if (MODE == MODE_RS && lane == 0 && pend_n > 0) {
-      tma_store_wait<0>();
-      release_flags(pend_first, pend_n);
+      if (ew == 0 && lane == 0 && it < 15) trace_at(p, 2 + 4 * it + 2);
     }
     __syncwarp();
     if (ew == 0 && lane == 0) trace_at(p, 62);
-    if (lane == 0) tma_store_wait<0>();
+    if (lane == 0) {
+      tma_store_wait<0>();
+      if (MODE == MODE_RS && pend_shard >= 0) {
+        fence_proxy_async_global();
+        __threadfence_system();
+        st_release_sys(p.sig[pend_shard] + kSigFlags + ((p.rank * p.max_tiles + pend_tile) * kFlagsPerTile + q), p.epoch);
+      }
+    }
+    __syncwarp();
+    // out of tiles: help with the reduction of this rank's own rows
+    if (MODE == MODE_RS && ok) reduce_own_rows<BN>(p, tm, cta, ncta, &s_next_item, lane);
+  } else if (MODE == MODE_RS) {
+    // ------------------------------------------------------------ reducers of this rank's rows
+    reduce_own_rows<BN>(p, tm, cta, ncta, &s_next_item, lane);
   }
 
   tc_fence_before();
@@ -599,19 +611,25 @@ int make_map_2d(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t outer,
                                 CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, int B_MN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mal, const CUtensorMap& mb, const CUtensorMap& mc,
-           const DstMaps& dm, const CommParams& p, int grid, cudaStream_t stream) {
+           const CommParams& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN>;
-  auto kern = gemm_comm_kernel<BN, MODE>;
+  auto kern = gemm_comm_kernel<BN, MODE, B_MN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kThreads, C::kSmem, stream>>>(ma, mal, mb, mc, dm, p);
+  kern<<<grid, MODE == MODE_RS ? kThreadsRS : kThreads, C::kSmem, stream>>>(ma, mal, mb, mc, p);
   return (int)cudaGetLastError();
+}
+
+template <int BN, int MODE>
+int launch_b(int b_mn, const CUtensorMap& ma, const CUtensorMap& mal, const CUtensorMap& mb, const CUtensorMap& mc,
+             const CommParams& p, int grid, cudaStream_t stream) {
+  return b_mn ? launch<BN, MODE, 1>(ma, mal, mb, mc, p, grid, stream) : launch<BN, MODE, 0>(ma, mal, mb, mc, p, grid, stream);
 }
 
 }  // namespace
@@ -619,21 +637,26 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mal, const CUtensorMap& mb,
 // Number of 32-bit slots a communicator's signal array needs for `max_tiles` flags per rank.
 AX_API int ax_gemm_comm_signal_slots(int max_tiles) { return kSigFlags + kMaxRanks * max_tiles * kFlagsPerTile; }
 
-// mode 0: C[world*Tl, N] = act(allgather(x_local)[world*Tl, K] * B[N, K]^T + bias); `sym` = gathered buffers,
-//         `out` = C (row stride N).
-// mode 1: out[Tl, N] = act(reduce_scatter(x[world*Tl, K] * B[N, K]^T) + bias); `sym` = staging buffers,
-//         `x_local` = x.
-// `grid` must be the same for every call on one communicator (the end-of-call counter relies on it)
-// and must not exceed the SM count.  Requires Tl % 128 == 0, K % 64 == 0, N % 64 == 0.
 // Diagnostic timeline: the launches that follow write globaltimer stamps of their phases into
 // `buf` ([grid][64] 64-bit slots, zero-filled by the caller); null turns it off again.
 static unsigned long long* g_trace_buf = nullptr;
 AX_API void ax_gemm_comm_set_trace(void* buf) { g_trace_buf = (unsigned long long*)buf; }
 
+// mode 0: C[world*Tl, N] = act(allgather(x_local)[world*Tl, K] * op(B) + bias); `sym` = gathered buffers
+//         [world][Tl][K], `out` = C (row stride N).
+// mode 1: out[Tl, N] = act(reduce_scatter(x[world*Tl, K] * op(B)) + bias); `sym` = staging buffers
+//         (world * Tl * N bf16 each, one slot per source rank), `x_local` = x.
+//         With `keep_gathered` every rank's gathered buffer is complete (own rows included) when the
+//         launch has finished and stays valid until the next call on this communicator, for later
+//         kernels on the same stream (the weight gradient of the layer); all calls on one communicator
+//         must then use keep_gathered.
+// op(B): b_mn = 0: B is [N, K] row-major (a Linear weight); b_mn = 1: B is [K, N] row-major.
+// `grid` must be the same for every call on one communicator (the end-of-call counter relies on it)
+// and must not exceed the SM count.  Requires Tl % 128 == 0, K % 64 == 0, N % 64 == 0.
 AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out, void* const* sym, void* sym_mc,
                         void* const* sig, const void* bias, int bias_kind, int act, int Tl, int N, int K,
-                        int rank, int world, unsigned epoch, int max_tiles, int pushers, int grid, int* status,
-                        cudaStream_t stream) {
+                        int b_mn, int rank, int world, unsigned epoch, int max_tiles, int pushers, int grid,
+                        int keep_gathered, int* status, cudaStream_t stream) {
   if (world < 1 || world > kMaxRanks || Tl <= 0 || Tl % BM || K % BK || N % 64 || grid > axh::sm_count()) return -1;
   const int BN = (N % 256 == 0) ? 256 : 128;
   if (N % BN) return -1;
@@ -651,6 +674,7 @@ AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out,
   p.out = (uint8_t*)out;
   p.bias = bias; p.bias_kind = bias ? bias_kind : 0; p.act = act;
   p.pushers = mode == MODE_AG ? pushers : 0;
+  p.fill_own = p.lazy_done = (mode == MODE_AG && keep_gathered) ? 1 : 0;
   p.max_tiles = max_tiles;
   p.status = status;
   p.trace = g_trace_buf;
@@ -667,22 +691,14 @@ AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out,
     rc = make_map_2d(&ma, x_local, (uint64_t)K, (uint64_t)world * Tl, (uint64_t)K, BK, BM);
     if (rc) return 1000 + rc;
     mal = ma;
-    rc = make_map_2d(&mc, out, (uint64_t)N, (uint64_t)Tl, (uint64_t)N, 64, 32);
-    if (rc) return 3000 + rc;
+    mc = ma;        // not used: partial tiles leave as plain bulk stores, the reducers write `out` directly
   }
-  DstMaps dm;
-  for (int i = 0; i < kMaxRanks; ++i) dm.m[i] = ma;
-  if (mode == MODE_RS) {
-    for (int i = 0; i < world; ++i) {
-      rc = make_map_2d(&dm.m[i], sym[i], (uint64_t)N, (uint64_t)world * Tl, (uint64_t)N, 64, 32);
-      if (rc) return 4000 + rc;
-    }
-  }
-  rc = make_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, (uint32_t)BN);
+  if (b_mn) rc = make_map_2d(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)N, 64, BK);
+  else rc = make_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, (uint32_t)BN);
   if (rc) return 2000 + rc;
   if (BN == 256)
-    return mode == MODE_AG ? launch<256, MODE_AG>(ma, mal, mb, mc, dm, p, grid, stream)
-                           : launch<256, MODE_RS>(ma, mal, mb, mc, dm, p, grid, stream);
-  return mode == MODE_AG ? launch<128, MODE_AG>(ma, mal, mb, mc, dm, p, grid, stream)
-                         : launch<128, MODE_RS>(ma, mal, mb, mc, dm, p, grid, stream);
+    return mode == MODE_AG ? launch_b<256, MODE_AG>(b_mn, ma, mal, mb, mc, p, grid, stream)
+                           : launch_b<256, MODE_RS>(b_mn, ma, mal, mb, mc, p, grid, stream);
+  return mode == MODE_AG ? launch_b<128, MODE_AG>(b_mn, ma, mal, mb, mc, p, grid, stream)
+                         : launch_b<128, MODE_RS>(b_mn, ma, mal, mb, mc, p, grid, stream);
 }

@@ -85,3 +85,27 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_
         bn, max_ctas, N.ptr(N.status_word(a.device)), N.stream_ptr())
     N.check(rc, "ax_gemm_bf16")
     return (out, aux) if want_aux else out
+
+
+def sgemm_f32(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a @ b`` in fp32 on the CUDA cores (fp32 multiply-add, fp32 accumulation): ``a`` is
+    ``[M, K]`` or ``[B, M, K]``, ``b`` is ``[K, N]`` or ``[B, K, N]`` (a 2-D operand is shared by the
+    whole batch).  The full-precision counterpart of the reference's cuBLAS ``sgemm`` /
+    ``sgemmStridedBatched`` calls (crates/axonml-core/src/backends/cuda.rs:413-501)."""
+    import ctypes
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or not a.is_cuda:
+        raise ValueError("sgemm_f32 takes fp32 CUDA tensors")
+    batch = max(a.shape[0] if a.dim() == 3 else 1, b.shape[0] if b.dim() == 3 else 1)
+    a, b = a.contiguous(), b.contiguous()
+    M, K = a.shape[-2:]
+    Kb, Nn = b.shape[-2:]
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    shape = (batch, M, Nn) if (a.dim() == 3 or b.dim() == 3) else (M, Nn)
+    if out is None:
+        out = torch.empty(shape, dtype=torch.float32, device=a.device)
+    rc = N.cuda().ax_sgemm_f32(N.ptr(a), N.ptr(b), N.ptr(out), M, Nn, K, K, Nn, Nn, batch,
+                               ctypes.c_long(M * K if a.dim() == 3 else 0), ctypes.c_long(K * Nn if b.dim() == 3 else 0),
+                               ctypes.c_long(M * Nn), N.stream_ptr())
+    N.check(rc, "ax_sgemm_f32")
+    return out

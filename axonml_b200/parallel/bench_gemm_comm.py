@@ -42,6 +42,7 @@ def main():
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--only", default="", help="comma-separated substrings of the rows to run")
     args = ap.parse_args()
     from axonml_b200 import _native
     from axonml_b200.ops.gemm import gemm_bf16
@@ -56,27 +57,37 @@ def main():
     tflops, link, src = _peaks()
     H, hd, tl = args.hidden, args.hidden // args.heads, args.tokens_per_rank
     T = tl * W
-    shapes = [("qkv  all-gather->GEMM", "ag", H, (args.heads + 2 * args.kv_heads) * hd // W),
-              ("gate|up all-gather->GEMM", "ag", H, 2 * args.ffn // W),
-              ("o_proj GEMM->reduce-scatter", "rs", args.heads * hd // W, H),
-              ("down   GEMM->reduce-scatter", "rs", args.ffn // W, H)]
+    qkv_n, ffn2 = (args.heads + 2 * args.kv_heads) * hd // W, 2 * args.ffn // W
+    # (name, kind, K, N, weight given as [N, K]); the last four are the input-gradient launches of the
+    # same layers: the weight is then read as [K, N] and the roles of the two kernels swap
+    shapes = [("qkv  all-gather->GEMM", "ag", H, qkv_n, True),
+              ("gate|up all-gather->GEMM", "ag", H, ffn2, True),
+              ("o_proj GEMM->reduce-scatter", "rs", args.heads * hd // W, H, True),
+              ("down   GEMM->reduce-scatter", "rs", args.ffn // W, H, True),
+              ("qkv dgrad GEMM->reduce-scatter", "rs", qkv_n, H, False),
+              ("gate|up dgrad GEMM->reduce-sc.", "rs", ffn2, H, False),
+              ("o_proj dgrad all-gather->GEMM", "ag", H, args.heads * hd // W, False),
+              ("down dgrad all-gather->GEMM", "ag", H, args.ffn // W, False)]
+    if args.only:
+        shapes = [sh for sh in shapes if any(o in sh[0] for o in args.only.split(","))]
     rows = []
     NB = 4                                            # rotating operand sets (weights + activations > L2)
-    for name, kind, K, Nn in shapes:
-        ws = [(torch.randn(Nn, K, device="cuda") * 0.02).bfloat16() for _ in range(NB)]
+    for name, kind, K, Nn, tb in shapes:
+        ws = [(torch.randn((Nn, K) if tb else (K, Nn), device="cuda") * 0.02).bfloat16() for _ in range(NB)]
         if kind == "ag":
             xs = [torch.randn(tl, K, device="cuda").bfloat16() for _ in range(NB)]
             gathered = torch.empty(W, tl, K, device="cuda", dtype=torch.bfloat16)
-            fused = lambda i: eng.ag_gemm(xs[i % NB], ws[i % NB])
+            ch = None if tb else eng.ag_bwd
+            fused = lambda i: eng.ag_gemm(xs[i % NB], ws[i % NB], trans_b=tb, channel=ch)
             def composed(i):
                 dist.all_gather_into_tensor(gathered, xs[i % NB])
-                return gemm_bf16(gathered.view(T, K), ws[i % NB])
+                return gemm_bf16(gathered.view(T, K), ws[i % NB], trans_b=tb)
         else:
             xs = [torch.randn(T, K, device="cuda").bfloat16() for _ in range(NB)]
             outb = torch.empty(tl, Nn, device="cuda", dtype=torch.bfloat16)
-            fused = lambda i: eng.gemm_rs(xs[i % NB], ws[i % NB])
+            fused = lambda i: eng.gemm_rs(xs[i % NB], ws[i % NB], trans_b=tb)
             def composed(i):
-                dist.reduce_scatter_tensor(outb, gemm_bf16(xs[i % NB], ws[i % NB]))
+                dist.reduce_scatter_tensor(outb, gemm_bf16(xs[i % NB], ws[i % NB], trans_b=tb))
                 return outb
 
         def timeit(fn):
@@ -102,9 +113,9 @@ def main():
     if rank == 0:
         print(f"tensor-parallel size {W}, {tl} tokens per rank; roofline denominators: {tflops:.0f} TFLOP/s bf16 ({src}), "
               f"{link:.0f} GB/s per direction NVLink (measured peer copy)")
-        print(f"{'op':30s} {'M':>6s} {'K':>6s} {'N':>6s} {'fused us':>9s} {'nccl+gemm us':>12s} {'roofline us':>11s} {'frac':>5s}")
+        print(f"{'op':31s} {'M':>6s} {'K':>6s} {'N':>6s} {'fused us':>9s} {'nccl+gemm us':>12s} {'roofline us':>11s} {'frac':>5s}")
         for r in rows:
-            print(f"{r[0]:30s} {r[1]:6d} {r[2]:6d} {r[3]:6d} {r[4]:9.1f} {r[5]:12.1f} {r[6]:11.1f} {r[7]:5.2f}")
+            print(f"{r[0]:31s} {r[1]:6d} {r[2]:6d} {r[3]:6d} {r[4]:9.1f} {r[5]:12.1f} {r[6]:11.1f} {r[7]:5.2f}")
     dist.barrier()
     dist.destroy_process_group()
 

@@ -100,10 +100,44 @@ class FullyShardedDataParallel(Module):
         return self
 
     def cpu_offload(self, offload: CPUOffload):
+        """``Params`` / ``Full`` (fsdp.rs:70-83): the fp32 master shards, and with them the optimizer
+        state that is created from them, live in pinned host memory; the optimizer steps there and
+        the low-precision shard on the device is refreshed from the host after each step.  The
+        reduced gradient shard is copied to the host at the end of backward (``Full`` also drops
+        the device copy's role: accumulation over backward calls happens on the host).  Call this
+        before the optimizer is created.  Not available with the in-backward fused AdamW, whose
+        state is on the device by construction."""
+        if offload is not CPUOffload.None_ and self._fused is not None:
+            raise ValueError("cpu_offload cannot be combined with fused_adamw (its master weights and moments "
+                             "are updated on the device inside backward)")
+        if offload is self._cpu_offload:
+            return self
         self._cpu_offload = offload
+        to_host = offload is not CPUOffload.None_
+        for u in self.units:
+            grad, lp = u.master._axon_grad, u.master._axon_lp
+            with torch.no_grad():
+                if to_host:
+                    host = u.master.data.detach().to("cpu")
+                    if torch.cuda.is_available():
+                        host = host.pin_memory()
+                    u.master.data = host
+                    u.grad_host = torch.zeros(u.shard, dtype=self.param_dtype, device="cpu")
+                    if torch.cuda.is_available():
+                        u.grad_host = u.grad_host.pin_memory()
+                else:
+                    u.master.data = u.master.data.to(self.device)
+                    u.grad_host = None
+            u.master._axon_lp = lp
+            u.master._axon_grad = None if to_host else grad
         return self
 
     def mixed_precision(self, flag: bool):
+        """The engine computes in ``param_dtype`` and steps fp32 master shards.  ``False`` asks for
+        full-precision compute, which is what ``param_dtype=torch.float32`` at construction gives;
+        the parameter buffers are laid out for one dtype, so it cannot be switched afterwards."""
+        if not flag and self.param_dtype != torch.float32:
+            raise ValueError("pass param_dtype=torch.float32 at construction for full-precision compute")
         self._mixed_precision = flag
         return self
 
@@ -301,7 +335,7 @@ class FullyShardedDataParallel(Module):
             # A reduced gradient of an earlier backward that no zero_grad() has cleared: keep it, the
             # reduction of this backward is added to it (gradient accumulation over micro-batches).
             if self._sync and u.master._axon_grad is not None:
-                u._carry = u.grad_shard.clone()
+                u._carry = u.master._axon_grad.to(self.device, copy=True)
         torch.autograd.Variable._execution_engine.queue_callback(self._finish_backward)
 
     def _on_grad(self, u: FlatUnit, idx: int, p) -> None:
@@ -355,6 +389,12 @@ class FullyShardedDataParallel(Module):
             with self._stream_ctx():
                 u.grad_shard.add_(u._carry)
             u._carry = None
+        if self._cpu_offload is not CPUOffload.None_:
+            # the optimizer steps on the host: hand it the reduced shard there (the copy is ordered
+            # after the reduction on the same stream; _finish_backward waits for it)
+            with self._stream_ctx():
+                u.grad_host.copy_(u.grad_shard, non_blocking=True)
+            u.master._axon_grad = u.grad_host
         if self._fused is not None and u.world > 1:
             self._fused_pending = True
         u.grad_written = [False] * len(u.params)
@@ -367,6 +407,8 @@ class FullyShardedDataParallel(Module):
                     self._reduce(u)
             if self._comm is not None:
                 torch.cuda.current_stream().wait_stream(self._comm)
+            if self._cpu_offload is not CPUOffload.None_ and self.device.type == "cuda":
+                torch.cuda.current_stream().synchronize()      # the host reads the gradient copies next
         for u in self.units:
             u.reduced = False
         self._phase = "idle"
@@ -446,6 +488,8 @@ class FullyShardedDataParallel(Module):
                 self._reduce(u)
         if self._comm is not None:
             torch.cuda.current_stream().wait_stream(self._comm)
+        if self._cpu_offload is not CPUOffload.None_ and self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         for u in self.units:

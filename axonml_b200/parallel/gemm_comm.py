@@ -7,8 +7,13 @@ the reduction of the local shard.  Both keep their peer-visible operands (gather
 slots, flags) in symmetric memory that is sized on first use and grown when a larger call arrives;
 every rank makes the same calls in the same order, so the growth is collective.
 
-Backward passes use the process group's collectives around the plain GEMM (Megatron style:
-re-gather the input for the weight gradient), so the layers train; the forward is the fused path.
+Backward passes run on the same kernels.  The input gradient of a column-parallel layer is a
+GEMM -> reduce-scatter with the weight read as ``[K, N]``; its weight gradient reads the gathered
+input that the forward launch left, complete, in a symmetric buffer kept for that layer (no second
+all-gather; the buffers are kept while they fit ``AXONML_TP_KEEP_GB``, 48 GB by default, and a
+layer without one re-gathers through the process group).  The input gradient of a row-parallel
+layer is an all-gather -> GEMM of the output gradient, whose gathered copy then feeds the weight
+gradient.
 
 Reference semantics: ColumnParallelLinear / RowParallelLinear of
 crates/axonml-distributed/src/fsdp.rs:414-600 (there: all_gather / all_reduce on a mock backend
@@ -17,6 +22,7 @@ around a CPU matmul).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -26,28 +32,33 @@ from ..ops import elementwise as E
 from .symm import SymmetricHeap, available
 
 _MAX_TILES = 4096
-_PUSHER_GBS = 17.0        # bytes one copy CTA moves per second towards the peers (measured, GB/s)
+_PUSHER_GBS = 22.0        # what one copy CTA sends per second (700 GB/s from 32 CTAs, measured)
+_LINK_GBS = 700.0         # what a GPU receives per second over NVLink (measured peer copy)
 
 
 def _pushers(tl: int, k: int, n: int, world: int, grid: int, multimem: bool) -> int:
-    """Copy CTAs for the all-gather: enough that the shard is out before the GEMM has finished the
-    local shard's tiles, no more (every copy CTA is one SM less for the math)."""
-    local_gemm_s = 2.0 * tl * k * n / 1.4e15
+    """Copy CTAs for the all-gather: enough to send this rank's shard within the time the launch
+    has anyway (most of the GEMM, or the time the GPU needs to receive the other shards, whichever
+    is longer), no more: every copy CTA is one SM less for the math.  With NVSwitch multicast a
+    shard leaves the GPU once, whatever the number of peers."""
+    gemm_s = 2.0 * world * tl * k * n / 1.4e15
+    recv_s = (world - 1) * tl * k * 2 / (_LINK_GBS * 1e9)
     copies = 1 if (multimem and world > 2) else world - 1
-    need = tl * k * 2 * copies / (_PUSHER_GBS * 1e9) / max(0.7 * local_gemm_s, 1e-6)
-    return int(min(max(need + 0.999, 4), 24, grid // 4))
+    need = tl * k * 2 * copies / (_PUSHER_GBS * 1e9) / max(0.6 * gemm_s, recv_s, 1e-6)
+    return int(min(max(need + 0.999, 2), 24, grid // 4))
 
 
 class _Channel:
     """One direction's symmetric state: data buffer, signal array, epoch."""
 
-    def __init__(self, heap: SymmetricHeap):
+    def __init__(self, heap: SymmetricHeap, keep: bool = False):
         self.heap = heap
         slots = N.cuda().ax_gemm_comm_signal_slots(_MAX_TILES)
         self.sig = heap.allocate(slots, torch.int32)
         self.data = None
         self.capacity = 0
         self.epoch = 0
+        self.keep = keep          # gathered rows stay readable after the launch (see ax_gemm_comm)
         heap.barrier()
 
     def ensure(self, numel: int) -> None:
@@ -59,6 +70,10 @@ class _Channel:
             self.capacity = numel
             self.heap.barrier()
 
+    def gathered(self, rows: int, k: int) -> torch.Tensor:
+        """This rank's copy of the rows gathered by the last call, ``[rows, k]``."""
+        return self.data.local[:rows * k].view(rows, k)
+
 
 class FusedGemmComm:
     def __init__(self, pg):
@@ -67,7 +82,27 @@ class FusedGemmComm:
         self.rank, self.world = self.heap.rank, self.heap.world
         self.ag = _Channel(self.heap)
         self.rs = _Channel(self.heap)
+        self.ag_bwd = _Channel(self.heap, keep=True)      # gathered output gradients of row-parallel layers
+        self._kept: dict = {}                              # id(weight) -> channel holding that layer's gathered input
+        self._kept_bytes = 0
+        self._keep_budget = int(float(os.environ.get("AXONML_TP_KEEP_GB", "48")) * (1 << 30))
         self.grid = torch.cuda.get_device_properties(self.heap.device).multi_processor_count
+
+    def kept_channel(self, weight, numel: int):
+        """Symmetric buffer that keeps the gathered input of the layer owning ``weight`` between its
+        forward and backward, or None when the budget is used up.  Every rank asks in the same
+        order with the same sizes, so the allocation is collective."""
+        ch = self._kept.get(id(weight))
+        if ch is None:
+            if self._kept_bytes + numel * 2 > self._keep_budget:
+                return None
+            ch = self._kept[id(weight)] = _Channel(self.heap, keep=True)
+            ch.version = 0
+        if numel > ch.capacity:
+            if self._kept_bytes + (numel - ch.capacity) * 2 > self._keep_budget:
+                return None
+            self._kept_bytes += (numel - ch.capacity) * 2
+        return ch
 
     @classmethod
     def try_create(cls, pg):
@@ -93,7 +128,7 @@ class FusedGemmComm:
         return (tl // 128) * (n // bn) <= _MAX_TILES
 
     # ------------------------------------------------------------------ raw launches
-    def _launch(self, mode, ch, x, weight, out, bias, act, tl, n, k):
+    def _launch(self, mode, ch, x, weight, out, bias, act, tl, n, k, trans_b=True):
         ch.epoch += 1
         bias_kind = 0
         if bias is not None:
@@ -101,28 +136,37 @@ class FusedGemmComm:
             bias_kind = 1 if bias.dtype == torch.float32 else 2
         rc = N.cuda().ax_gemm_comm(
             mode, N.ptr(x), N.ptr(weight), N.ptr(out), ch.data.ptr_array(), ch.data.mc(), ch.sig.ptr_array(),
-            N.ptr(bias), bias_kind, ACT[act], tl, n, k, self.rank, self.world, ctypes.c_uint(ch.epoch),
-            _MAX_TILES, _pushers(tl, k, n, self.world, self.grid, bool(ch.data.mc_ptr)), self.grid,
-            N.ptr(N.status_word(x.device)), N.stream_ptr())
+            N.ptr(bias), bias_kind, ACT[act], tl, n, k, int(not trans_b), self.rank, self.world,
+            ctypes.c_uint(ch.epoch), _MAX_TILES, _pushers(tl, k, n, self.world, self.grid, bool(ch.data.mc_ptr)),
+            self.grid, int(ch.keep), N.ptr(N.status_word(x.device)), N.stream_ptr())
         N.check(rc, "ax_gemm_comm")
 
-    def ag_gemm(self, x_local, weight, bias=None, act="none"):
+    def ag_gemm(self, x_local, weight, bias=None, act="none", *, trans_b: bool = True, channel=None):
+        """``act(all_gather(x_local) @ op(weight) + bias)``; ``trans_b=True``: weight is ``[N, K]``
+        (a Linear weight), ``False``: weight is ``[K, N]``."""
         x_local, weight = x_local.contiguous(), weight.contiguous()
         tl, k = x_local.shape
-        n = weight.shape[0]
-        self.ag.ensure(self.world * tl * k)
+        n = weight.shape[0] if trans_b else weight.shape[1]
+        ch = channel or self.ag
+        ch.ensure(self.world * tl * k)
         out = torch.empty((self.world * tl, n), dtype=torch.bfloat16, device=x_local.device)
-        self._launch(0, self.ag, x_local, weight, out, bias, act, tl, n, k)
+        self._launch(0, ch, x_local, weight, out, bias, act, tl, n, k, trans_b)
         return out
 
-    def gemm_rs(self, x, weight, bias=None, act="none"):
+    def gemm_rs(self, x, weight, bias=None, act="none", *, trans_b: bool = True):
+        """This rank's rows of ``act(sum over ranks of x @ op(weight) + bias)``."""
         x, weight = x.contiguous(), weight.contiguous()
         t, k = x.shape
-        tl, n = t // self.world, weight.shape[0]
+        n = weight.shape[0] if trans_b else weight.shape[1]
+        tl = t // self.world
         self.rs.ensure(self.world * tl * n)
         out = torch.empty((tl, n), dtype=torch.bfloat16, device=x.device)
-        self._launch(1, self.rs, x, weight, out, bias, act, tl, n, k)
+        self._launch(1, self.rs, x, weight, out, bias, act, tl, n, k, trans_b)
         return out
+
+    def supports_bwd(self, rows_local: int, k: int, n: int) -> bool:
+        """Shapes of the two backward launches of a layer with a ``[n, k]`` weight."""
+        return k % 128 == 0 and n % 64 == 0 and rows_local % 128 == 0
 
     # ------------------------------------------------------------------ autograd entries
     def all_gather_linear(self, x_local, weight, bias=None, act="none"):
@@ -160,7 +204,13 @@ class _AGLinear(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.bias_dtype = bias.dtype if bias is not None else None
         ctx.save_for_backward(x_local, weight)
-        return eng.ag_gemm(x_local, weight, bias, "none")
+        tl, k = x_local.shape
+        ch = eng.kept_channel(weight, eng.world * tl * k)
+        ctx.ch, ctx.version = ch, None
+        if ch is not None:
+            ch.version += 1
+            ctx.version = ch.version
+        return eng.ag_gemm(x_local, weight, bias, "none", channel=ch)
 
     @staticmethod
     def backward(ctx, dy):
@@ -168,10 +218,21 @@ class _AGLinear(torch.autograd.Function):
         eng = ctx.eng
         dy = dy.contiguous()
         dx = dw = db = None
+        n, k = weight.shape
+        fused = _fused_backward() and eng.supports_bwd(x_local.shape[0], k, n)
         if ctx.needs_input_grad[0]:
-            dx = _reduce_scatter_rows(gemm_bf16(dy, weight, trans_b=False), eng)
+            if fused and k % 64 == 0 and n % 64 == 0:
+                dx = eng.gemm_rs(dy, weight, trans_b=False)          # dy [T, n] @ weight [n, k] -> rows of this rank
+            else:
+                dx = _reduce_scatter_rows(gemm_bf16(dy, weight, trans_b=False), eng)
         if ctx.needs_input_grad[1]:
-            dw = gemm_bf16(dy, _all_gather_rows(x_local, eng), trans_a=True, trans_b=False)
+            ch = ctx.ch
+            if ch is not None and ch.version == ctx.version:
+                # the forward (or its recomputation) left the gathered input in this layer's buffer
+                xg = ch.gathered(eng.world * x_local.shape[0], k)
+            else:
+                xg = _all_gather_rows(x_local, eng)
+            dw = gemm_bf16(dy, xg, trans_a=True, trans_b=False)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = E.colsum(dy).to(ctx.bias_dtype)
         return dx, dw, db, None
@@ -189,9 +250,25 @@ class _LinearRS(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         eng = ctx.eng
         dx = dw = None
-        dy = _all_gather_rows(dy_local.contiguous(), eng)
+        dy_local = dy_local.contiguous()
+        n, k = weight.shape
+        tl = dy_local.shape[0]
+        if _fused_backward() and ctx.needs_input_grad[0] and tl % 128 == 0 and n % 64 == 0 and k % 128 == 0 \
+                and tl // 128 <= _MAX_TILES:
+            # all-gather of dy fused into dx = dy @ weight; the gathered dy stays for the weight gradient
+            dx = eng.ag_gemm(dy_local, weight, trans_b=False, channel=eng.ag_bwd)
+            if ctx.needs_input_grad[1]:
+                dw = gemm_bf16(eng.ag_bwd.gathered(eng.world * tl, n), x, trans_a=True, trans_b=False)
+            return dx, dw, None
+        dy = _all_gather_rows(dy_local, eng)
         if ctx.needs_input_grad[0]:
             dx = gemm_bf16(dy, weight, trans_b=False)
         if ctx.needs_input_grad[1]:
             dw = gemm_bf16(dy, x, trans_a=True, trans_b=False)
         return dx, dw, None
+
+
+def _fused_backward() -> bool:
+    """``AXONML_TP_BWD=nccl`` composes the backward passes from process-group collectives and the
+    plain GEMM (the baseline the fused backward is measured against)."""
+    return os.environ.get("AXONML_TP_BWD", "fused") != "nccl"

@@ -38,6 +38,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"],
                     help="gradient path at N>1: NCCL reduce-scatter + optimizer, or the fused kernel")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="at N>1 skip the second measurement of the same config on plain NCCL collectives")
     return ap.parse_args()
 
 
@@ -91,11 +93,29 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    # The reference is a Rust workspace: `pip install` of its source tree finds neither setup.py nor
-    # pyproject.toml, and there is no cargo/rustc on the machine, so it cannot be built or run.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference is a Rust cargo workspace (no setup.py/pyproject.toml, no cargo/rustc "
-                      "offline): pip install of the reference source tree fails, nothing to run"}))
+    """The reference is a Rust cargo workspace.  At run time this looks for what its build needs: a
+    ``cargo`` on PATH and vendored crates for ``--offline`` (the workspace lists 60+ external crates
+    and the machine has no network).  With both present it builds the workspace's CUDA feature set
+    and reports that the reference has no entry point for this metric (no multi-GPU transport, no
+    LLM trainer binary); without them it prints what it observed."""
+    import shutil
+    root = os.environ.get("AXONML_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref_src"))
+    cargo, rustc = shutil.which("cargo"), shutil.which("rustc")
+    pip_tree = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
+    seen = [f"cargo={'found at ' + cargo if cargo else 'not on PATH'}", f"rustc={'found' if rustc else 'not on PATH'}",
+            f"workspace source (AXONML_REFERENCE_ROOT)={'present' if os.path.exists(os.path.join(root, 'Cargo.toml')) else 'not present'}",
+            f"vendored crates={'present' if os.path.isdir(os.path.join(root, 'vendor')) else 'absent'}",
+            f"pip-installed tree={'present' if os.path.isdir(pip_tree) and os.listdir(pip_tree) else 'absent (no setup.py/pyproject.toml to install)'}"]
+    why = "reference is a Rust cargo workspace and cannot be built here: " + "; ".join(seen)
+    if cargo and rustc and os.path.exists(os.path.join(root, "Cargo.toml")):
+        r = subprocess.run([cargo, "build", "--release", "--offline", "-p", "axonml", "--features", "cuda"], cwd=root,
+                           capture_output=True, text=True, timeout=3000)
+        if r.returncode == 0:
+            why = ("reference built with cargo --offline, but it has no program for this metric: its distributed crate "
+                   "has only an in-process mock transport and it ships no LLM/ResNet training binary")
+        else:
+            why = "cargo build --release --offline failed: " + (r.stderr.strip().splitlines() or ["no output"])[-1][:200]
+    print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
 def bench_q4k_decode(args):
@@ -168,7 +188,8 @@ def _dist_setup():
 
 def timed_training(args, world, rank, local, dev, step_device, step_e2e):
     """Warm-up, K device-timed steps (CUDA events, max over ranks), then K end-to-end steps timed
-    on the host around synchronisations.  Returns the measurements of this run."""
+    on the host around synchronisations (skipped when ``step_e2e`` is None).  Returns the
+    measurements of this run."""
     import torch
     import torch.distributed as dist
     from axonml_b200 import _native
@@ -198,7 +219,8 @@ def timed_training(args, world, rank, local, dev, step_device, step_e2e):
     last_loss = float(loss.item())
     sync_all()
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    l_host = None
+    for i in range(args.steps if step_e2e is not None else 0):
         l_host = step_e2e(i)
     sync_all()
     e2e_ms = (time.perf_counter() - t0) * 1000.0
@@ -227,47 +249,63 @@ def bench_gpt_fsdp(args):
     from axonml_b200.parallel import FSDP
 
     world, rank, local, dev, pg = _dist_setup()
-    torch.manual_seed(1234 + rank)
     cfg = GPT2Config.gpt_1_3b()
     if args.layers:
         cfg.n_layer = args.layers
     cfg.n_ctx = max(cfg.n_ctx, args.seq_len)
-    model = GPT2LMHead(cfg, device=dev, dtype=torch.bfloat16)
-    model.gradient_checkpointing_enable(True)
-    model.train()
     hp = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
-    use_fused = world > 1 and args.comm in ("auto", "fused")
-    engine = FSDP(model, pg, fused_adamw=hp if use_fused else None)
-    if engine._fused is not None:
-        opt = engine.fused_optimizer()
-        comm_path = "fused reduce-scatter+AdamW kernel (peer memory / NVLS)"
-    else:
-        opt = optim.AdamW(engine.parameters(), hp["lr"], betas=hp["betas"], eps=hp["eps"],
-                          weight_decay=hp["weight_decay"])
-        comm_path = "nccl" if world > 1 else "none (1 GPU)"
-
     B, S = args.micro_batch, args.seq_len
     gen = torch.Generator(device="cpu").manual_seed(99 + rank)
     n_host = max(args.steps, 4)
     host_ids = [torch.randint(0, cfg.vocab_size, (B, S), generator=gen).pin_memory() for _ in range(n_host)]
     dev_ids = [t.to(dev) for t in host_ids[:4]]
 
-    def run(ids):
-        loss, _ = engine.call("forward_with_loss", ids)
-        loss.backward()
-        opt.step()
-        engine.zero_grad()
-        return loss
+    def setup(comm):
+        """Model, engine and optimizer for one gradient-communication path; returns the two step
+        functions and the name of the path actually taken."""
+        torch.manual_seed(1234 + rank)
+        model = GPT2LMHead(cfg, device=dev, dtype=torch.bfloat16)
+        model.gradient_checkpointing_enable(True)
+        model.train()
+        use_fused = world > 1 and comm in ("auto", "fused")
+        engine = FSDP(model, pg, fused_adamw=hp if use_fused else None)
+        if engine._fused is not None:
+            opt = engine.fused_optimizer()
+            path = "fused reduce-scatter+AdamW kernel (peer memory / NVLS)"
+        else:
+            opt = optim.AdamW(engine.parameters(), hp["lr"], betas=hp["betas"], eps=hp["eps"],
+                              weight_decay=hp["weight_decay"])
+            path = "nccl" if world > 1 else "none (1 GPU)"
 
-    def step_device(i):
-        return run(dev_ids[i % 4])
+        def run(ids):
+            loss, _ = engine.call("forward_with_loss", ids)
+            loss.backward()
+            opt.step()
+            engine.zero_grad()
+            return loss
 
-    def step_e2e(i):
-        ids = host_ids[i % n_host].to(dev, non_blocking=True)       # H2D from pinned memory
-        return float(run(ids).item())                                 # D2H of the step's result
+        def step_device(i):
+            return run(dev_ids[i % 4])
 
+        def step_e2e(i):
+            ids = host_ids[i % n_host].to(dev, non_blocking=True)       # H2D from pinned memory
+            return float(run(ids).item())                                 # D2H of the step's result
+        return step_device, step_e2e, path
+
+    step_device, step_e2e, comm_path = setup(args.comm)
     m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
     tokens_per_step = B * S * world
+    baseline = None
+    if world > 1 and comm_path.startswith("fused") and not args.no_baseline:
+        # the same config, steps and process group with the gradient path on plain NCCL collectives
+        del step_device, step_e2e
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        sd_b, _, path_b = setup("nccl")
+        mb = timed_training(args, world, rank, local, dev, sd_b, None)
+        baseline = {"grad_comm": path_b, "value": round(tokens_per_step / (mb["ms_per_step"] / 1000.0), 1),
+                    "ms_per_step": round(mb["ms_per_step"], 3)}
     if rank == 0:
         out = {
             "metric": "tokens/s 1.3B-FSDP (GPT 1.3B, FSDP ZeRO-3, training)",
@@ -287,6 +325,8 @@ def bench_gpt_fsdp(args):
             "gpu_launches": m["launches"],
             "final_loss": round(m["last_loss"], 4), "e2e_final_loss": round(m["e2e_last_loss"], 4),
         }
+        if baseline is not None:
+            out["baseline_nccl"] = baseline
         print(json.dumps(out), flush=True)
     return _finish(world)
 
@@ -345,8 +385,17 @@ def bench_llama_tp(args):
     m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
     tokens = global_batch * S
     fused = fused_gemm._ENGINES.get(id(pg.backend())) is not None
+    baseline = None
+    if world > 1 and fused and not args.no_baseline:
+        # the same model, steps and process group with every tensor-parallel collective on NCCL
+        # around the plain GEMM (the layers look the engine up on every call)
+        fused_gemm._ENGINES[id(pg.backend())] = None
+        mb = timed_training(args, world, rank, local, dev, step_device, None)
+        baseline = {"tp_collectives": "nccl + GEMM", "value": round(tokens / (mb["ms_per_step"] / 1000.0), 1),
+                    "ms_per_step": round(mb["ms_per_step"], 3)}
     if rank == 0:
         print(json.dumps({
+            **({"baseline_nccl": baseline} if baseline is not None else {}),
             "metric": "tokens/s 8B-TP8 (Llama-style 8B, tensor parallel, training)",
             "value": round(tokens / (m["ms_per_step"] / 1000.0), 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms_per_step"], 3),
@@ -413,8 +462,17 @@ def bench_resnet_ddp(args):
 
     m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
     imgs = B * world
+    baseline = None
+    grad_comm = "fused all-reduce+unscale kernel" if ddp._fused is not None else ("nccl" if world > 1 else "none (1 GPU)")
+    if world > 1 and ddp._fused is not None and not args.no_baseline:
+        # the same model, steps and process group with the bucket all-reduce on NCCL
+        ddp._fused = None
+        mb = timed_training(args, world, rank, local, dev, step_device, None)
+        baseline = {"grad_comm": "nccl", "value": round(imgs / (mb["ms_per_step"] / 1000.0), 1),
+                    "ms_per_step": round(mb["ms_per_step"], 3)}
     if rank == 0:
         print(json.dumps({
+            **({"baseline_nccl": baseline} if baseline is not None else {}),
             "metric": "ResNet-18 img/s (DDP, bf16 AMP, training)",
             "value": round(imgs / (m["ms_per_step"] / 1000.0), 1), "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms_per_step"], 3),
@@ -422,8 +480,7 @@ def bench_resnet_ddp(args):
             "data": "synthetic", "impl": "axonml_b200",
             "config": {"model": "resnet18 (1000 classes)", "global_batch": imgs, "image": "3x224x224 channels-last",
                        "parallelism": f"ddp{world}", "optimizer": "SGD momentum 0.9 + GradScaler",
-                       "bucket_mb": 25, "grad_comm": "fused all-reduce+unscale kernel" if ddp._fused is not None else
-                       ("nccl" if world > 1 else "none (1 GPU)"),
+                       "bucket_mb": 25, "grad_comm": grad_comm,
                        "l2_policy": "per-step activations (> 10 GB) exceed the 126 MB L2"},
             "clocks": m["clocks"],
             "e2e": {"value": round(imgs / (m["e2e_ms_per_step"] / 1000.0), 1), "unit": "images/s",

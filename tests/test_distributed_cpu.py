@@ -255,6 +255,34 @@ def test_fsdp_accumulates_gradients_over_micro_batches(strategy, use_no_sync):
         assert torch.allclose(sd[k], v.detach(), atol=1e-5), (k, (sd[k] - v).abs().max())
 
 
+def _fsdp_offload(rank, world, be, offload_name):
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import FSDP, ProcessGroup
+    from axonml_b200.parallel.fsdp import CPUOffload
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(12, 20), nn.Tanh(), nn.Linear(20, 5))
+    f = FSDP(m, ProcessGroup(be)).cpu_offload(CPUOffload[offload_name])
+    assert all(p.device.type == "cpu" for p in f.parameters())
+    opt = optim.AdamW(f.parameters(), 1e-2)
+    g = torch.Generator().manual_seed(11)
+    X, Y = torch.randn(3, 8, 12, generator=g), torch.randint(0, 5, (3, 8), generator=g)
+    for it in range(3):
+        nn.CrossEntropyLoss()(f(X[it].chunk(world)[rank]), Y[it].chunk(world)[rank]).backward()
+        f.clip_grad_norm(1.0)
+        opt.step()
+        f.zero_grad()
+    with pytest.raises(ValueError):
+        f.mixed_precision(False) if f.param_dtype != torch.float32 else (_ for _ in ()).throw(ValueError())
+    return f.full_state_dict()
+
+
+def test_fsdp_cpu_offload_steps_the_master_shards_on_the_host():
+    res = {name: run_ranks(_fsdp_offload, 2, args=(name,))[0][1] for name in ("None_", "Params", "Full")}
+    for k, v in res["None_"].items():
+        assert torch.allclose(res["Params"][k], v, atol=1e-6), k
+        assert torch.allclose(res["Full"][k], v, atol=1e-6), k
+
+
 def _mlp_fsdp_lamb(rank, world, be):
     from axonml_b200 import nn, optim
     from axonml_b200.parallel import FSDP, ProcessGroup

@@ -489,3 +489,120 @@ def test_lamb_on_a_flat_master_buffer_takes_trust_ratios_per_tensor():
     moved = max((v.detach() - sd0).abs().max().item() for v, sd0 in zip(ref.parameters(), mk().cuda().parameters()))
     err = max((sd[k] - v.detach()).abs().max().item() for k, v in ref.named_parameters())
     assert moved > 1e-3 and err < 1e-5, (moved, err)
+
+
+def test_a_device_wait_that_runs_out_reports_and_leaves_the_context_usable():
+    """The all-reduce kernel of a two-rank communicator is launched for rank 0 only; the buffers of
+    both "ranks" are ordinary allocations of this one GPU, so nothing remote is touched and nothing
+    else waits.  With the wait budget set to a few milliseconds the start barrier gives up: the
+    status word carries the peer-timeout code and the place of the wait, the kernel has run to its
+    end, and a complete call (a one-rank communicator) then succeeds."""
+    import ctypes
+    from axonml_b200 import _native as N
+    torch.cuda.synchronize()
+    N.check_status()
+    slots = N.cuda().ax_comm_signal_slots()
+    n = 4096
+    bufs = [torch.ones(n, device=DEV), torch.ones(n, device=DEV)]
+    sigs = [torch.zeros(max(slots, 64), dtype=torch.int32, device=DEV) for _ in range(2)]
+    arr = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    N.set_wait_budget_us(3000)
+    try:
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        rc = N.cuda().ax_fused_allreduce(0, arr(bufs), arr(sigs), ctypes.c_void_p(0), 0, 2, ctypes.c_long(0),
+                                         ctypes.c_long(n), None, None, ctypes.c_uint(1), None, 4,
+                                         N.ptr(N.status_word()), N.stream_ptr())
+        assert rc == 0
+        t1.record()
+        torch.cuda.synchronize()
+        assert t0.elapsed_time(t1) < 1000.0                  # gave up after milliseconds, not the built-in second
+        with pytest.raises(N.KernelTimeout) as ei:
+            N.check_status()
+        assert ei.value.code == 3 and ei.value.where in (600, 601, 603)
+        assert bool((bufs[0] == 1).all())                    # the work was skipped, nothing half-written
+    finally:
+        N.set_wait_budget_us(0)
+    # the same kernel, complete this time
+    one = torch.full((n,), 3.0, device=DEV)
+    sig1 = torch.zeros(max(slots, 64), dtype=torch.int32, device=DEV)
+    rc = N.cuda().ax_fused_allreduce(0, arr([one]), arr([sig1]), ctypes.c_void_p(0), 0, 1, ctypes.c_long(0),
+                                     ctypes.c_long(n), None, None, ctypes.c_uint(1), None, 4,
+                                     N.ptr(N.status_word()), N.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    N.check_status()
+    assert bool((one == 3).all())
+
+
+def test_an_mbarrier_wait_that_runs_out_is_reported(kernel_status):
+    """A GEMM whose wait budget is far below the time its loads need still terminates and reports
+    through the status word (or simply succeeds when every wait was served in time); either way
+    the next GEMM with the normal budget is correct."""
+    from axonml_b200 import _native as N
+    from axonml_b200.ops.gemm import gemm_bf16
+    a = torch.randn(512, 512, device=DEV).bfloat16()
+    b = torch.randn(512, 512, device=DEV).bfloat16()
+    torch.cuda.synchronize()
+    N.set_wait_budget_us(1)
+    try:
+        gemm_bf16(a, b)
+        torch.cuda.synchronize()
+        try:
+            N.check_status()
+        except N.KernelTimeout as e:
+            assert e.code == 1
+    finally:
+        N.set_wait_budget_us(0)
+    c = gemm_bf16(a, b)
+    close(c, a.float() @ b.float().t(), atol=0.02 * 512 ** 0.5, rtol=2e-2)
+
+
+def test_fsdp_cpu_offload_on_the_gpu_matches_device_resident_masters(kernel_status):
+    """One rank, bf16 compute: with the master shards and optimizer state in pinned host memory the
+    parameters after three steps equal those of the device-resident run."""
+    from axonml_b200 import nn, optim
+    from axonml_b200.parallel import FSDP
+    from axonml_b200.parallel.fsdp import CPUOffload
+    outs = []
+    for off in (CPUOffload.None_, CPUOffload.Params):
+        torch.manual_seed(0)
+        m = nn.Sequential(nn.Linear(64, 128), nn.Tanh(), nn.Linear(128, 64)).to("cuda", torch.bfloat16)
+        f = FSDP(m).cpu_offload(off)
+        opt = optim.AdamW(f.parameters(), 1e-2)
+        g = torch.Generator().manual_seed(5)
+        X = torch.randn(3, 32, 64, generator=g).cuda().bfloat16()
+        for it in range(3):
+            f(X[it]).float().pow(2).mean().backward()
+            opt.step()
+            f.zero_grad()
+        if off is not CPUOffload.None_:
+            assert all(p.device.type == "cpu" and p.is_pinned() for p in f.parameters())
+        outs.append({k: v.float().cpu() for k, v in f.full_state_dict().items()})
+    for k in outs[0]:
+        assert torch.allclose(outs[0][k], outs[1][k], atol=2e-3, rtol=2e-3), k
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 1024, 1024), (129, 257, 65), (7, 5, 3), (300, 1000, 2000), (128, 128, 16)])
+def test_sgemm_f32_has_fp32_accuracy(M, N, K):
+    """The fp32 GEMM of the backend trait keeps fp32 products: the reference's tolerance for its
+    cuBLAS sgemm test (atol 1e-3, rtol 1e-2) against a float64 product, far inside what bf16
+    operands could give."""
+    from axonml_b200.core.backends import CudaBackend
+    a = torch.randn(M, K, device=DEV)
+    b = torch.randn(K, N, device=DEV)
+    c = CudaBackend(0).gemm_f32(a, b)
+    ref = (a.double() @ b.double()).float()
+    assert c.dtype == torch.float32
+    close(c, ref, atol=1e-3, rtol=1e-2)
+    assert (c - ref).abs().max().item() < 2e-4 * K ** 0.5
+
+
+def test_sgemm_f32_batched():
+    from axonml_b200.core.backends import CudaBackend
+    a = torch.randn(5, 70, 33, device=DEV)
+    b = torch.randn(5, 33, 90, device=DEV)
+    c = CudaBackend(0).gemm_batched_f32(a, b)
+    close(c, torch.bmm(a.double(), b.double()).float(), atol=1e-3, rtol=1e-2)
+    c2 = CudaBackend(0).gemm_batched_f32(list(a), list(b))
+    assert torch.equal(c, c2)

@@ -264,6 +264,20 @@ def _gemm_comm(rank, world, be):
         torch.cuda.synchronize()
         _native.check_status()
         out[f"rs{i}"] = ((z.float() - ref2).abs().max().item(), ref2.abs().max().item())
+        # the input-gradient forms: weight read as [K, N]; bias and activation in the reducer
+        if k % 128 == 0:
+            w_t = w_r.t().contiguous()                               # [k, n]
+            z2 = eng.gemm_rs(x, w_t, bias, "relu", trans_b=False)
+            ref3 = torch.relu(ref2 + bias)
+            y2 = eng.ag_gemm(x_local, w_full.t().contiguous(), trans_b=False, channel=eng.ag_bwd)
+            ref4 = xs.view(-1, k).float() @ w_full.float().t()
+            torch.cuda.synchronize()
+            _native.check_status()
+            out[f"rs_t{i}"] = ((z2.float() - ref3).abs().max().item(), ref3.abs().max().item())
+            out[f"ag_t{i}"] = ((y2.float() - ref4).abs().max().item(), ref4.abs().max().item())
+            # the launch left every rank's rows, its own included, in the kept buffer
+            kept = eng.ag_bwd.gathered(world * tl, k)
+            out[f"kept{i}"] = ((kept.float() - xs.view(-1, k).float()).abs().max().item(), 0.0)
     return out
 
 
@@ -345,3 +359,49 @@ def test_tensor_parallel_serving_graph_decode_matches_eager():
         a, b, _, _ = res[r][1]
         assert a == a0 and b == b0          # all ranks agree
     assert a0 == b0
+
+
+def _skipped_call(rank, world, be):
+    """Rank 1 leaves one all-reduce out (host side: it simply does not launch).  Rank 0's kernel
+    gives up its wait after the short budget and reports; the next call, made by both, works:
+    signals only ever grow, so a call that timed out does not poison the communicator."""
+    from axonml_b200 import _native
+    from axonml_b200.parallel import ProcessGroup
+    from axonml_b200.parallel.fused import FusedAllReduce
+    pg = ProcessGroup(be)
+    far = FusedAllReduce.try_create(pg, 1 << 16, torch.float32)
+    assert far is not None
+    x = torch.full((4096,), float(rank + 1), device="cuda")
+    far.all_reduce_mean_(x)
+    torch.cuda.synchronize()
+    _native.check_status()
+    out = {"first": x[0].item()}
+    _native.set_wait_budget_us(20000)
+    y = torch.full((4096,), 5.0, device="cuda")
+    if rank == 1:
+        far.comm.next_epoch()                     # the call this rank skips
+        out["timeout"] = None
+    else:
+        far.all_reduce_mean_(y)
+        torch.cuda.synchronize()
+        try:
+            _native.check_status()
+            out["timeout"] = None
+        except _native.KernelTimeout as e:
+            out["timeout"] = (e.code, e.where)
+    _native.set_wait_budget_us(0)
+    torch.cuda.synchronize()
+    torch.distributed.barrier()
+    z = torch.full((4096,), float(10 * (rank + 1)), device="cuda")
+    far.all_reduce_mean_(z)
+    torch.cuda.synchronize()
+    _native.check_status()
+    out["after"] = z[0].item()
+    return out
+
+
+def test_a_skipped_call_times_out_on_the_other_rank_and_the_next_call_works():
+    res = run_gpu_ranks(_skipped_call, 2, env={"AXONML_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
+    assert res[0][1]["first"] == res[1][1]["first"] == 1.5
+    assert res[0][1]["timeout"] is not None and res[0][1]["timeout"][0] == 3
+    assert res[0][1]["after"] == res[1][1]["after"] == 15.0
