@@ -44,6 +44,9 @@ struct Hyper {
   const int* found_inf;    // may be null: skip everything when *found_inf != 0
   float* norms;            // LAMB: [tensor][2] sums of squares; grad-norm: [1]
   const float* clip_coef;  // optional device scalar multiplied into the gradient
+  const int* step_dev;     // optional: steps taken so far, kept on the device; when given, the bias
+                           // corrections are 1 - beta^(*step_dev + 1) and bc1 / bc2 are ignored (the
+                           // host cannot know how many steps a device-side found-inf flag skipped)
 };
 
 template <typename T> __device__ __forceinline__ float ld(const T* p, long i);
@@ -75,7 +78,8 @@ enum Kind : int { K_SGD = 0, K_ADAM, K_RMSPROP, K_LAMB1, K_LAMB2, K_SUMSQ, K_SCA
 
 template <int KIND, typename PT, typename GT>
 __global__ void __launch_bounds__(512)
-mt_kernel(const TensorTable tt, const Hyper h) {
+mt_kernel(const TensorTable tt, const Hyper h_in) {
+  Hyper h = h_in;
   if (KIND != K_SUMSQ && KIND != K_UNSCALE_CHECK && h.found_inf && *h.found_inf) return;
   int t = 0;
   while (t + 1 < tt.num && (int)blockIdx.x >= tt.first_blk[t + 1]) ++t;
@@ -90,6 +94,11 @@ mt_kernel(const TensorTable tt, const Hyper h) {
   __nv_bfloat16* lp = tt.lp[t];
   float gmul = h.inv_scale ? *h.inv_scale : 1.f;
   if (h.clip_coef) gmul *= *h.clip_coef;
+  if ((KIND == K_ADAM || KIND == K_LAMB1) && h.step_dev != nullptr && h.bc1 != 1.f) {
+    const double t = (double)(*h.step_dev + 1);
+    h.bc1 = (float)(1.0 - pow((double)h.beta1, t));
+    h.bc2 = (float)(1.0 - pow((double)h.beta2, t));
+  }
   float acc0 = 0.f, acc1 = 0.f;
   int bad = 0;
   float trust = 1.f;
@@ -231,12 +240,13 @@ int launch_typed(int p_bf16, int g_bf16, const TensorTable& tt, const Hyper& h, 
 AX_API int ax_multi_tensor(int kind, int p_bf16, int g_bf16, int nt, void** p, void** g, void** s1,
                            void** s2, void** s3, void** lp, const long* n, const float* hyper,
                            const int* flags, const float* inv_scale, const int* found_inf,
-                           float* norms, const float* clip_coef, cudaStream_t stream) {
+                           float* norms, const float* clip_coef, const int* step_dev, cudaStream_t stream) {
   Hyper h;
   h.lr = hyper[0]; h.beta1 = hyper[1]; h.beta2 = hyper[2]; h.eps = hyper[3]; h.wd = hyper[4];
   h.bc1 = hyper[5]; h.bc2 = hyper[6]; h.momentum = hyper[7]; h.dampening = hyper[8]; h.alpha = hyper[9];
   h.nesterov = flags[0]; h.first_step = flags[1]; h.adamw = flags[2]; h.amsgrad = flags[3]; h.centered = flags[4];
   h.inv_scale = inv_scale; h.found_inf = found_inf; h.norms = norms; h.clip_coef = clip_coef;
+  h.step_dev = step_dev;
 
   TensorTable tt;
   int nt_in = 0, nb = 0, rc = 0;

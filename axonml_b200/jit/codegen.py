@@ -1,10 +1,12 @@
 """Executors for compiled graphs (crates/axonml-jit/src/codegen.rs:14-741).
 
 ``JitCompiler.compile(graph)`` optimises the graph, looks it up in the ``FunctionCache`` and
-returns a ``CompiledFunction``.  Two executors exist: an interpreter over torch ops (any device,
-every op) and, for graphs that are one same-shape elementwise expression on CUDA fp32 tensors, a
-single generated CUDA kernel compiled with NVRTC for sm_100a (the reference's native path,
-Cranelift, is unreachable there: ``use_native: false``, codegen.rs:503)."""
+returns a ``CompiledFunction``.  Executors: an interpreter over torch ops (any device, every op);
+on CUDA, generated kernels compiled with NVRTC for sm_100a: one kernel when the graph is a single
+same-shape elementwise expression, else the multi-kernel plan of ``lower.py`` (broadcasting, shape
+ops, ``Where`` / ``Cast``, reductions fused with their producer expressions, ``MatMul`` on the
+library GEMM).  The reference's native path, Cranelift, is unreachable there (``use_native:
+false``, codegen.rs:503)."""
 from __future__ import annotations
 
 import ctypes
@@ -138,13 +140,20 @@ class CompiledFunction:
     def __init__(self, graph: Graph, original: Graph | None = None):
         self._graph, self._original = graph, original or graph
         self._kernel, self._cuda = None, None
+        self._plan = None
         self._tried_cuda = False
 
     @classmethod
     def placeholder(cls): return cls(Graph())
 
     def graph(self) -> Graph: return self._graph
-    def uses_generated_kernel(self) -> bool: return self._kernel is not None
+    def uses_generated_kernel(self) -> bool: return self._kernel is not None or self._plan is not None
+
+    def generated_source(self) -> str | None:
+        """CUDA C of the generated kernels (after the first run on a GPU), for inspection."""
+        if self._kernel is not None:
+            return self._cuda[0]
+        return self._plan.source if self._plan is not None else None
 
     def _try_cuda(self) -> None:
         self._tried_cuda = True
@@ -152,10 +161,15 @@ class CompiledFunction:
         if not nvrtc.available():
             return
         gen = generate_cuda(self._graph)
-        if gen is None:
+        if gen is not None:
+            self._cuda = gen
+            self._kernel = nvrtc.Kernel(gen[0], "axonml_fused")
             return
-        self._cuda = gen
-        self._kernel = nvrtc.Kernel(gen[0], "axonml_fused")
+        from . import lower
+        if lower.lowerable(self._graph):
+            plan = lower.Plan(self._graph)
+            plan.compile()
+            self._plan = plan
 
     def run_tensors(self, inputs: dict) -> dict:
         """Tensor-level entry: ``{name: tensor}`` -> ``{name: tensor}``."""
@@ -175,6 +189,11 @@ class CompiledFunction:
                 grid = max(1, min((n + 255) // 256, 148 * 16))
                 self._kernel.launch(grid, 256, args, types)
                 return dict(zip(out_names, outs))
+        if first is not None and first.is_cuda:
+            if not self._tried_cuda:
+                self._try_cuda()
+            if self._plan is not None:
+                return self._plan.run(inputs)
         return interpret(self._graph, inputs)
 
     def run(self, inputs):

@@ -26,8 +26,11 @@ def available() -> bool:
         return False
 
 
-class Kernel:
-    def __init__(self, source: str, name: str):
+class Module:
+    """One NVRTC compilation unit loaded into the current context; ``function(name)`` returns a
+    launchable entry point."""
+
+    def __init__(self, source: str):
         driver, nvrtc = _bindings()
         self._driver = driver
         err, prog = nvrtc.nvrtcCreateProgram(source.encode(), b"axonml_jit.cu", 0, [], [])
@@ -48,16 +51,33 @@ class Kernel:
         err, self._module = driver.cuModuleLoadData(cubin)
         if int(err) != 0:
             raise RuntimeError(f"cuModuleLoadData failed: {err}")
-        err, self._fn = driver.cuModuleGetFunction(self._module, name.encode())
-        if int(err) != 0:
-            raise RuntimeError(f"cuModuleGetFunction failed: {err}")
         self.source = source
+
+    def function(self, name: str) -> "Function":
+        err, fn = self._driver.cuModuleGetFunction(self._module, name.encode())
+        if int(err) != 0:
+            raise RuntimeError(f"cuModuleGetFunction({name}) failed: {err}")
+        return Function(self, fn)
+
+
+class Function:
+    def __init__(self, module: Module, fn):
+        self._module, self._fn = module, fn      # the module must outlive its functions
 
     def launch(self, grid: int, block: int, args, arg_types) -> None:
         """``args``: python ints (device pointers, sizes) / floats; ``arg_types``: ctypes types."""
-        driver = self._driver
+        driver = self._module._driver
         stream = torch.cuda.current_stream().cuda_stream
-        vals = tuple(args)
-        (err,) = driver.cuLaunchKernel(self._fn, grid, 1, 1, block, 1, 1, 0, stream, (vals, tuple(arg_types)), 0)
+        (err,) = driver.cuLaunchKernel(self._fn, grid, 1, 1, block, 1, 1, 0, stream, (tuple(args), tuple(arg_types)), 0)
         if int(err) != 0:
             raise RuntimeError(f"cuLaunchKernel failed: {err}")
+
+
+class Kernel(Function):
+    """A module with a single entry point."""
+
+    def __init__(self, source: str, name: str):
+        mod = Module(source)
+        f = mod.function(name)
+        super().__init__(mod, f._fn)
+        self.source = source

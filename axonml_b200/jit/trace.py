@@ -53,9 +53,9 @@ class TracedValue:
     def silu(self): return self._un("Silu")
     def contiguous(self): return self._un("Contiguous")
 
-    def _shape_op(self, kind, shape, **attrs):
+    def _shape_op(self, kind, out_shape, **attrs):
         g = self.tracer.graph
-        return TracedValue(self.tracer, g.add_node(Op.make(kind, (self.id,), **attrs), g.node(self.id).dtype, shape))
+        return TracedValue(self.tracer, g.add_node(Op.make(kind, (self.id,), **attrs), g.node(self.id).dtype, out_shape))
 
     def sum(self): return self._shape_op("Sum", ())
     def mean(self): return self._shape_op("Mean", ())

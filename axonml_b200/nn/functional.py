@@ -35,4 +35,6 @@ def dropout(x, p: float = 0.5, training: bool = True): return E.dropout(x, p, tr
 def mse_loss(input, target): return F.mse_loss(input, target)
 def cross_entropy(input, target): return L.cross_entropy(input, target.long() if target.is_floating_point() else target)
 def binary_cross_entropy(input, target): return F.binary_cross_entropy(input, target)
-def adaptive_avg_pool2d(x, output_size): return F.adaptive_avg_pool2d(x, output_size)
+def adaptive_avg_pool2d(x, output_size):
+    from ..ops.pool import adaptive_avg_pool2d as _aap
+    return _aap(x, output_size)

@@ -35,11 +35,19 @@ class MaxPool2d(_Pool):
 
 
 class AvgPool1d(_Pool):
-    def forward(self, x): return F.avg_pool1d(x, self.kernel_size, self.stride, self.padding)
+    """Mean over each window; padded positions do not count (pooling.rs:120-200)."""
+
+    def forward(self, x):
+        from ...ops.pool import avg_pool1d
+        return avg_pool1d(x, self.kernel_size, self.stride, self.padding)
 
 
 class AvgPool2d(_Pool):
-    def forward(self, x): return F.avg_pool2d(x, self.kernel_size, self.stride, self.padding)
+    """Mean over each window; padded positions do not count (pooling.rs:296-357)."""
+
+    def forward(self, x):
+        from ...ops.pool import avg_pool2d
+        return avg_pool2d(x, self.kernel_size, self.stride, self.padding)
 
 
 class AdaptiveAvgPool2d(Module):
@@ -53,4 +61,6 @@ class AdaptiveAvgPool2d(Module):
     @classmethod
     def square(cls, n: int): return cls((n, n))
 
-    def forward(self, x): return F.adaptive_avg_pool2d(x, self.output_size)
+    def forward(self, x):
+        from ...ops.pool import adaptive_avg_pool2d
+        return adaptive_avg_pool2d(x, self.output_size)

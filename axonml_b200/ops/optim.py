@@ -3,7 +3,9 @@
 ``multi_tensor(kind, params, grads, ...)`` packs raw pointers into ctypes arrays and issues one
 native call; the native side splits the list into as few launches as the kernel-parameter table
 allows.  All scalars that change every step (lr, bias corrections) are passed by value, the loss
-scale and the found-inf flag by device pointer, so a step never synchronises with the host.
+scale and the found-inf flag by device pointer, so a step never synchronises with the host.  When
+a device-side found-inf flag can skip a step, the step count used for Adam's and LAMB's bias
+corrections is kept on the device too (``step_dev``) and only advances on steps that were taken.
 """
 from __future__ import annotations
 
@@ -44,7 +46,7 @@ def multi_tensor(kind: str, params, grads, s1=None, s2=None, s3=None, lp=None, *
                  beta1=0.0, beta2=0.0, eps=0.0, wd=0.0, bc1=1.0, bc2=1.0, momentum=0.0,
                  dampening=0.0, alpha=0.0, nesterov=False, first_step=False, adamw=False,
                  amsgrad=False, centered=False, inv_scale=None, found_inf=None, norms=None,
-                 clip_coef=None) -> None:
+                 clip_coef=None, step_dev=None) -> None:
     ref = params if params is not None else grads
     nt = len(ref)
     if nt == 0:
@@ -62,7 +64,7 @@ def multi_tensor(kind: str, params, grads, s1=None, s2=None, s3=None, lp=None, *
     rc = N.cuda().ax_multi_tensor(
         KIND[kind], p_bf16, g_bf16, nt, _ptr_array(params), _ptr_array(grads), _ptr_array(s1),
         _ptr_array(s2), _ptr_array(s3), _ptr_array(lp), sizes, hyper, flags, N.ptr(inv_scale),
-        N.ptr(found_inf), N.ptr(norms), N.ptr(clip_coef), N.stream_ptr())
+        N.ptr(found_inf), N.ptr(norms), N.ptr(clip_coef), N.ptr(step_dev), N.stream_ptr())
     N.check(rc, f"ax_multi_tensor[{kind}]")
     if late_lp is not None and kind in ("sgd", "adam", "rmsprop", "lamb2"):
         for l, q in zip(late_lp, params):

@@ -51,6 +51,7 @@ class Adam(Optimizer):
         bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
         names = ("exp_avg", "exp_avg_sq") + (("max_exp_avg_sq",) if self._amsgrad else ())
         fused, rest = self._groups(self._active())
+        step_dev = self._device_step(fused[0][0].device) if fused else None
         for grp in fused:
             sts = [self._state(p, names) for p in grp]
             O.multi_tensor("adam", grp, [self._g(p) for p in grp], [s["exp_avg"] for s in sts],
@@ -58,7 +59,9 @@ class Adam(Optimizer):
                            [s["max_exp_avg_sq"] for s in sts] if self._amsgrad else None,
                            lp=self._lp(grp), lr=self.lr, beta1=b1, beta2=b2, eps=self._eps, wd=self._weight_decay,
                            bc1=bc1, bc2=bc2, adamw=self._DECOUPLED, amsgrad=self._amsgrad,
-                           inv_scale=self._inv_scale, found_inf=self._found_inf)
+                           inv_scale=self._inv_scale, found_inf=self._found_inf, step_dev=step_dev)
+        if step_dev is not None:
+            self._advance_device_step()
         if rest and self._skip():
             self._step_count -= 1
             return

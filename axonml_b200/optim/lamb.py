@@ -86,18 +86,21 @@ class LAMB(Optimizer):
         fused, rest = self._groups(active)
         if reducers and len(fused) + bool(rest) > 1:          # one reduction per step: keep the slices together
             fused, rest = ([[p for grp in fused for p in grp]], rest) if not rest else ([], active)
+        step_dev = self._device_step(fused[0][0].device) if (fused and self._bias_correction) else None
         for grp in fused:
             pcs = self._pieces(grp, names)
             norms = torch.zeros(len(pcs), 2, dtype=torch.float32, device=grp[0].device)
             lps = [pc[5] for pc in pcs]
             hp = dict(lp=lps if any(l is not None for l in lps) else None, lr=self.lr, beta1=b1, beta2=b2,
                       eps=self._eps, wd=self._weight_decay, bc1=bc1, bc2=bc2, inv_scale=self._inv_scale,
-                      found_inf=self._found_inf, norms=norms)
+                      found_inf=self._found_inf, norms=norms, step_dev=step_dev)
             args = ([pc[0] for pc in pcs], [pc[1] for pc in pcs], [pc[2] for pc in pcs], [pc[3] for pc in pcs],
                     [pc[4] for pc in pcs])
             O.multi_tensor("lamb1", *args, **hp)
             hp["norms"] = self._reduce_norms(norms, pcs, reducers)
             O.multi_tensor("lamb2", *args, **hp)
+        if step_dev is not None:
+            self._advance_device_step()
         if rest and self._skip():
             self._step_count -= 1
             return

@@ -93,6 +93,23 @@ class Optimizer:
     def _active(self):
         return [p for p in self.params if self._g(p) is not None]
 
+    def _device_step(self, device):
+        """Steps actually taken, as an int32 device scalar, for the kernels' bias corrections while
+        a device-side found-inf flag may skip steps (the host counter would run ahead after every
+        overflow).  None when no such flag is attached."""
+        if self._found_inf is None or not torch.is_tensor(self._found_inf) or not self._found_inf.is_cuda:
+            return None
+        st = getattr(self, "_step_dev", None)
+        if st is None or st.device != device:
+            # the host count includes the step in progress
+            st = self._step_dev = torch.full((1,), max(self._step_count - 1, 0), dtype=torch.int32, device=device)
+        return st
+
+    def _advance_device_step(self) -> None:
+        st = getattr(self, "_step_dev", None)
+        if st is not None and self._found_inf is not None and torch.is_tensor(self._found_inf):
+            st += (self._found_inf.to(st.device) == 0).to(torch.int32)
+
     def _groups(self, ps):
         """Splits into lists the fused kernel can take plus a remainder for the torch path."""
         fused: dict[tuple, list] = {}

@@ -102,6 +102,19 @@ class _Bucket:
         self.work = None
         self.event = None
 
+    def rebind(self, buf: torch.Tensor) -> None:
+        """Moves the bucket into ``buf`` (a slice of symmetric memory, so that the fused
+        all-reduce works on the bucket in place instead of copying it into a staging buffer and
+        back); the parameter views are rebuilt, gradients already pointing at the old views are
+        re-pointed by the next backward."""
+        buf.copy_(self.flat)
+        self.flat = buf
+        self.views = []
+        off = 0
+        for p in self.params:
+            self.views.append(self.flat[off:off + p.numel()].view(p.shape))
+            off += p.numel()
+
 
 class DistributedDataParallel(Module):
     def __init__(self, module: torch.nn.Module, process_group: ProcessGroup | None = None, *,
@@ -124,13 +137,26 @@ class DistributedDataParallel(Module):
         self._build_buckets()
         first = params[0]
         self._comm = torch.cuda.Stream(first.device) if first.is_cuda else None
-        self._fused = None
+        # dtype -> fused all-reduce whose symmetric arena holds all buckets of that dtype; a dtype
+        # without an entry (or any bucket when the dict is empty) goes through the process group
+        self._fused: dict = {}
         if fused is not False and first.is_cuda and self.pg.world_size() > 1:
             try:
                 from . import fused as F
-                self._fused = F.FusedAllReduce.try_create(self.pg, max(b.padded for b in self._buckets),
-                                                          self._buckets[0].flat.dtype)
+                by_dtype: dict = {}
+                for b in self._buckets:
+                    by_dtype.setdefault(b.flat.dtype, []).append(b)
+                for dt, bs in by_dtype.items():
+                    far = F.FusedAllReduce.try_create(self.pg, sum(b.padded for b in bs), dt)
+                    if far is None:
+                        continue
+                    off = 0
+                    for b in bs:
+                        b.rebind(far.stage.local[off:off + b.padded])
+                        off += b.padded
+                    self._fused[dt] = far
             except Exception:
+                self._fused = {}
                 if fused:
                     raise
         for p in params:
@@ -220,13 +246,14 @@ class DistributedDataParallel(Module):
         b.reduced = True
 
     def _launch(self, b: _Bucket) -> None:
-        if self._fused is not None:
+        far = self._fused.get(b.flat.dtype) if self._fused else None
+        if far is not None and far.holds(b.flat):
             inv, flag = None, None
             if self._scaler is not None and self._scaler.is_enabled():
                 self._scaler._ensure_device(b.flat.device)
                 inv, flag = self._scaler._inv_scale_t, self._scaler._found_inf_t
                 self._scaler._unscaled = True
-            self._fused.all_reduce_mean_(b.flat, inv_scale=inv, found_inf=flag)
+            far.all_reduce_mean_(b.flat, inv_scale=inv, found_inf=flag)
         else:
             self.pg.backend().all_reduce(b.flat, ReduceOp.Average)
 

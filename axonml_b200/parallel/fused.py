@@ -4,10 +4,11 @@
 * ``FusedShardedAdamW`` - FSDP reduce-scatter + sharded AdamW (+ push of the updated bf16 shard
   into every rank's resident parameter buffer), one kernel per flat unit.
 
-Both stage their operands in symmetric memory: DDP copies a bucket into a symmetric staging
-buffer (the bucket itself when it was allocated there), FSDP allocates its flat gradient arena
-symmetrically.  The NCCL path (``all_reduce`` / ``reduce_scatter_tensor``) remains the fallback and
-the baseline that the fused path is measured against.
+Both keep their operands in symmetric memory: DDP allocates its gradient buckets inside the
+all-reduce's symmetric arena, so a bucket is reduced in place (a tensor from elsewhere is staged
+through the arena), FSDP allocates its flat gradient arena symmetrically.  The NCCL path
+(``all_reduce`` / ``reduce_scatter_tensor``) remains the fallback and the baseline that the fused
+path is measured against.
 """
 from __future__ import annotations
 
@@ -39,9 +40,16 @@ class FusedAllReduce:
             return None
         return cls(SymmetricHeap(pg), max_numel, dtype, grid_blocks, device_epoch)
 
+    def holds(self, flat: torch.Tensor) -> bool:
+        """True when ``flat`` can be reduced by this instance: it lies inside the symmetric arena
+        (reduced in place) or fits into it (staged)."""
+        return flat.dtype == self.dtype and flat.numel() <= self.capacity
+
     def all_reduce_mean_(self, flat: torch.Tensor, inv_scale=None, found_inf=None) -> None:
         """In-place mean over ranks of ``flat`` (optionally times ``inv_scale``); sets
-        ``found_inf`` (int32[1]) when any reduced value is not finite."""
+        ``found_inf`` (int32[1]) when any reduced value is not finite.  A tensor that is a slice of
+        this instance's symmetric arena (DDP allocates its buckets there) is reduced where it is;
+        any other tensor is copied into the arena and back."""
         n = flat.numel()
         if n > self.capacity or flat.dtype != self.dtype:
             raise ValueError("bucket does not fit the fused all-reduce staging buffer")
@@ -49,15 +57,19 @@ class FusedAllReduce:
         unit = 16 * self.heap.world // esz
         n_pad = (n + unit - 1) // unit * unit
         stage = self.stage.local
-        in_place = flat.data_ptr() == stage.data_ptr()
+        off = flat.data_ptr() - stage.data_ptr()
+        # in place only for a whole number of 16-byte-per-rank units: a ragged slice is staged instead
+        in_place = (0 <= off and off + n * esz <= self.capacity * esz and off % 16 == 0 and n_pad == n
+                    and flat.is_contiguous())
         if not in_place:
+            off = 0
             stage[:n].copy_(flat)
             if n_pad > n:
                 stage[n:n_pad].zero_()
         rc = N.cuda().ax_fused_allreduce(
             1 if self.dtype == torch.bfloat16 else 0, self.stage.ptr_array(),
             self.comm.signals.ptr_array(), self.stage.mc(), self.heap.rank, self.heap.world,
-            ctypes.c_long(0), ctypes.c_long(n_pad), N.ptr(inv_scale), N.ptr(found_inf),
+            ctypes.c_long(off), ctypes.c_long(n_pad), N.ptr(inv_scale), N.ptr(found_inf),
             ctypes.c_uint(0 if self._epoch_dev is not None else self.comm.next_epoch()), N.ptr(self._epoch_dev),
             self.comm.grid, N.ptr(N.status_word(flat.device)), N.stream_ptr())
         N.check(rc, "ax_fused_allreduce")

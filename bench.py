@@ -463,10 +463,10 @@ def bench_resnet_ddp(args):
     m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
     imgs = B * world
     baseline = None
-    grad_comm = "fused all-reduce+unscale kernel" if ddp._fused is not None else ("nccl" if world > 1 else "none (1 GPU)")
-    if world > 1 and ddp._fused is not None and not args.no_baseline:
+    grad_comm = "fused all-reduce+unscale kernel, buckets reduced in place in symmetric memory" if ddp._fused else ("nccl" if world > 1 else "none (1 GPU)")
+    if world > 1 and ddp._fused and not args.no_baseline:
         # the same model, steps and process group with the bucket all-reduce on NCCL
-        ddp._fused = None
+        ddp._fused = {}
         mb = timed_training(args, world, rank, local, dev, step_device, None)
         baseline = {"grad_comm": "nccl", "value": round(imgs / (mb["ms_per_step"] / 1000.0), 1),
                     "ms_per_step": round(mb["ms_per_step"], 3)}

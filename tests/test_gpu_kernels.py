@@ -606,3 +606,142 @@ def test_sgemm_f32_batched():
     close(c, torch.bmm(a.double(), b.double()).float(), atol=1e-3, rtol=1e-2)
     c2 = CudaBackend(0).gemm_batched_f32(list(a), list(b))
     assert torch.equal(c, c2)
+
+
+def test_adam_bias_correction_does_not_run_ahead_after_skipped_steps(kernel_status):
+    """With a GradScaler the decision to skip a step is taken on the device.  A skipped step must
+    not count for the bias corrections: after overflow, good, good steps the parameters equal those
+    of two plain steps."""
+    from axonml_b200 import optim
+    torch.manual_seed(0)
+    w0 = torch.randn(4096, device=DEV)
+    g1, g2 = torch.randn(4096, device=DEV), torch.randn(4096, device=DEV)
+    ref = torch.nn.Parameter(w0.clone())
+    o_ref = torch.optim.Adam([ref], 1e-2)
+    for g in (g1, g2):
+        ref.grad = g.clone()
+        o_ref.step()
+    p = torch.nn.Parameter(w0.clone())
+    opt = optim.Adam([p], 1e-2)
+    scaler = optim.GradScaler.with_scale(8.0)
+    bad = g1.clone()
+    bad[7] = float("inf")
+    for g in (bad, g1, g2):
+        opt.zero_grad()
+        p.grad = g * scaler.get_scale()          # what backward of the scaled loss would leave
+        scaler.step(opt)
+        scaler.update()
+    close(p.detach(), ref.detach(), atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("channels_last", [False, True])
+@pytest.mark.parametrize("k,s,p", [(2, 2, 0), (3, 2, 1), (3, 1, 1), ((2, 3), (1, 2), (1, 0))])
+def test_avg_pool2d_kernel_forward_backward(dtype, channels_last, k, s, p):
+    """AvgPool2d kernels (divisor = pixels inside the image) against torch's
+    count_include_pad=False in fp32, values and input gradient, both memory layouts."""
+    from axonml_b200.ops.pool import avg_pool2d
+    x = torch.randn(3, 10, 13, 11, device=DEV).to(dtype)
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
+    x.requires_grad_()
+    y = avg_pool2d(x, k, s, p)
+    xr = x.detach().float().requires_grad_()
+    yr = F.avg_pool2d(xr, k, s, p, count_include_pad=False)
+    g = torch.randn_like(yr)
+    y.backward(g.to(dtype))
+    yr.backward(g)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    close(y, yr, tol, tol)
+    close(x.grad, xr.grad, tol, tol)
+    y2 = avg_pool2d(x.detach(), k, s, p, count_include_pad=True)
+    close(y2, F.avg_pool2d(xr.detach(), k, s, p, count_include_pad=True), tol, tol)
+
+
+@pytest.mark.parametrize("out", [(1, 1), (7, 7), (3, 5), (4, 2)])
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_adaptive_avg_pool2d_kernel(out, channels_last):
+    """Adaptive pooling kernels against the same window rule written with averaging matrices
+    (the CPU path of the op), forward and backward; sizes that do not divide included."""
+    from axonml_b200.ops.pool import adaptive_avg_pool2d
+    x = torch.randn(2, 6, 14, 15, device=DEV)
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
+    x.requires_grad_()
+    y = adaptive_avg_pool2d(x, out)
+    xr = x.detach().cpu().requires_grad_()
+    yr = adaptive_avg_pool2d(xr, out)
+    g = torch.randn_like(yr)
+    y.backward(g.to(DEV))
+    yr.backward(g)
+    close(y.cpu(), yr, 1e-5, 1e-5)
+    close(x.grad.cpu(), xr.grad, 1e-5, 1e-5)
+    if 14 % out[0] == 0 and 15 % out[1] == 0:
+        close(y.cpu(), F.adaptive_avg_pool2d(xr.detach(), out), 1e-5, 1e-5)
+
+
+def test_avg_pool1d_kernel():
+    from axonml_b200 import nn
+    x = torch.randn(4, 5, 37, device=DEV, requires_grad=True)
+    y = nn.AvgPool1d.with_options(4, 3, 1)(x)
+    xr = x.detach().requires_grad_()
+    yr = F.avg_pool1d(xr, 4, 3, 1, count_include_pad=False)
+    close(y, yr, 1e-5, 1e-5)
+    y.sum().backward(); yr.sum().backward()
+    close(x.grad, xr.grad, 1e-5, 1e-5)
+
+
+def _softmax_like_graph():
+    from axonml_b200 import jit
+
+    def f(tr):
+        x, b, m = tr.input("x", [64, 300]), tr.input("b", [300]), tr.input("m", [64, 1])
+        z = x.add(b)                                   # implicit broadcast of a row vector
+        e = z.sub(z.max_axis(1, True)).exp()
+        p = e.div(e.sum_axis(1, True))                 # two reductions fused with their producers
+        w = p.where(m.gt(0.0), p.mul_scalar(0.0))      # Where on a broadcast comparison
+        t = w.transpose(0, 1).reshape([300, 64])
+        tr.output("p", w)
+        tr.output("t", t)
+        tr.output("tot", w.sum())
+        tr.output("mean0", w.mean_axis(0))
+        tr.output("mm", w.matmul(t))
+        tr.output("mask", m.gt(0.0).broadcast([64, 300]))
+    return jit.trace(f)
+
+
+def test_jit_lowers_reductions_broadcast_where_and_matmul_to_generated_kernels(kernel_status):
+    """A graph far outside the one-kernel case (row-vector broadcast, two per-axis reductions, a full
+    sum, Where, Transpose + Reshape, MatMul, a boolean output) runs as generated kernels and gives
+    what the interpreter gives on the CPU."""
+    from axonml_b200 import jit
+    from axonml_b200.jit import nvrtc
+    if not nvrtc.available():
+        pytest.skip("cuda-python bindings not importable")
+    g = _softmax_like_graph()
+    x, b, m = torch.randn(64, 300), torch.randn(300), torch.randn(64, 1)
+    ref = jit.interpret(g, {"x": x, "b": b, "m": m})
+    fn = jit.JitCompiler.new().compile(g)
+    out = fn.run_tensors({"x": x.cuda(), "b": b.cuda(), "m": m.cuda()})
+    assert fn.uses_generated_kernel() and "__global__" in fn.generated_source()
+    for k, r in ref.items():
+        o = out[k]
+        assert o.is_cuda and o.dtype == r.dtype and tuple(o.shape) == tuple(r.shape), k
+        assert (o.float().cpu() - r.float()).abs().max().item() < 2e-3, k
+
+
+def test_jit_split_reduction_over_a_large_tensor(kernel_status):
+    from axonml_b200 import jit
+    from axonml_b200.jit import nvrtc
+    if not nvrtc.available():
+        pytest.skip("cuda-python bindings not importable")
+
+    def f(tr):
+        x = tr.input("x", [1 << 20])
+        tr.output("s", x.mul(x).sum())
+        tr.output("m", x.abs().mean())
+    g = jit.trace(f)
+    x = torch.randn(1 << 20, device="cuda")
+    out = jit.JitCompiler.new().compile(g).run_tensors({"x": x})
+    assert abs(out["s"].item() - (x.double() ** 2).sum().item()) < 1e-3 * (1 << 20) ** 0.5 * 4
+    assert abs(out["m"].item() - x.abs().double().mean().item()) < 1e-4

@@ -85,6 +85,34 @@ def test_jit_trace_optimize_interpret_and_codegen():
     assert "__global__" in src
 
 
+def test_jit_lowering_plan_for_reductions_and_broadcast_is_generated_without_a_gpu():
+    """The multi-kernel lowering is a source-to-source step: it can be checked here for structure
+    (one kernel per materialised value, the matrix product left to the GEMM), and the interpreter
+    evaluates the same graph, reshape and broadcast included."""
+    from axonml_b200.jit import lower
+
+    def f(tr):
+        x, b = tr.input("x", [8, 12]), tr.input("b", [12])
+        z = x.add(b)
+        p = z.sub(z.max_axis(1, True)).exp()
+        p = p.div(p.sum_axis(1, True))
+        tr.output("p", p)
+        tr.output("pt", p.transpose(0, 1).reshape([12, 8]))
+        tr.output("g", p.matmul(p.transpose(0, 1)))
+        tr.output("big", b.broadcast([8, 12]))
+    g = jit.trace(f)
+    assert lower.lowerable(g)
+    plan = lower.Plan(g)
+    kinds = [s["kind"] for s in plan.steps]
+    assert kinds.count("matmul") == 1 and kinds.count("kernel") >= 4
+    assert plan.source.count("__global__") == kinds.count("kernel")
+    x, b = torch.randn(8, 12), torch.randn(12)
+    out = jit.interpret(g, {"x": x, "b": b})
+    ref = torch.softmax(x + b, -1)
+    assert torch.allclose(out["p"], ref, atol=1e-6) and torch.allclose(out["pt"], ref.t(), atol=1e-6)
+    assert torch.allclose(out["g"], ref @ ref.t(), atol=1e-6) and torch.equal(out["big"], b.expand(8, 12))
+
+
 def test_fusion_linear_and_elementwise_and_conv_bn_fold():
     torch.manual_seed(0)
     w, b = torch.randn(3, 4), torch.randn(3)

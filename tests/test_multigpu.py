@@ -194,7 +194,7 @@ def _ddp_fused(rank, world, be):
     torch.manual_seed(0)
     model = LeNet.new().cuda()
     ddp = DDP(model, ProcessGroup(be), bucket_bytes=64 * 1024)
-    fused = ddp._fused is not None
+    fused = bool(ddp._fused)
     opt = optim.SGD(model.parameters(), 0.01).momentum(0.9)
     scaler = optim.GradScaler.with_scale(1024.0)
     ddp.attach_scaler(scaler)
@@ -208,7 +208,42 @@ def _ddp_fused(rank, world, be):
         scaler.scale(loss).backward()
         scaler.step(opt)
         scaler.update()
-    return [p.detach().float().cpu() for p in model.parameters()], fused
+    in_place = all(far.stage.local.data_ptr() <= b.flat.data_ptr() < far.stage.local.data_ptr() + far.capacity * b.flat.element_size()
+                   for b in ddp._buckets for far in [ddp._fused.get(b.flat.dtype)] if far is not None)
+    return [p.detach().float().cpu() for p in model.parameters()], fused and in_place
+
+
+def _ddp_mixed_dtypes(rank, world, be):
+    """fp32 and bf16 parameters in one model: every dtype gets its own symmetric arena, and the
+    result equals the run whose buckets go through the process group."""
+    from axonml_b200 import _native, nn, optim
+    from axonml_b200.parallel import DDP, ProcessGroup
+    outs = []
+    for fused in (None, False):
+        torch.manual_seed(0)
+        model = nn.Sequential(nn.Linear(32, 64), nn.Tanh(), nn.Linear(64, 16)).cuda()
+        model[2].to(torch.bfloat16)
+        ddp = DDP(model, ProcessGroup(be), bucket_bytes=4 * 1024, fused=fused)
+        if fused is None:
+            assert set(ddp._fused) == {torch.float32, torch.bfloat16}
+        opt = optim.SGD(model.parameters(), 0.05)
+        g = torch.Generator().manual_seed(3)
+        X = torch.randn(3, 8 * world, 32, generator=g).cuda()
+        for it in range(3):
+            opt.zero_grad()
+            h = model[1](model[0](X[it].chunk(world)[rank]))
+            model[2](h.bfloat16()).float().pow(2).mean().backward()
+            opt.step()
+        torch.cuda.synchronize()
+        _native.check_status()
+        outs.append([p.detach().float().cpu() for p in model.parameters()])
+    return [(a - b).abs().max().item() for a, b in zip(*outs)]
+
+
+def test_ddp_fused_allreduce_with_mixed_parameter_dtypes():
+    res = run_gpu_ranks(_ddp_mixed_dtypes, WORLD)
+    for r in range(WORLD):
+        assert max(res[r][1]) < 2e-2, res[r][1]
 
 
 def test_ddp_fused_allreduce_with_scaler_matches_single_process():
