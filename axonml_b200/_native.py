@@ -42,7 +42,7 @@ class _CountingLib:
     (every ``ax_*`` entry that takes a stream launches at least one kernel)."""
 
     _NO_LAUNCH = {"ax_version", "ax_sm_count", "ax_norm_bwd_groups", "ax_multi_tensor_limits", "ax_gemm_comm_set_trace",
-                  "ax_flash_fwd_set_trace", "ax_gemm_comm_signal_slots", "ax_norm_bwd_noalloc_limits", "ax_gemm_set_pair_mode", "ax_gemm_pair_capacity"}
+                  "ax_flash_fwd_set_trace", "ax_gemm_comm_signal_slots", "ax_norm_bwd_noalloc_limits", "ax_gemm_set_pair_mode", "ax_flash_fwd_set_one_tile", "ax_gemm_pair_capacity"}
 
     def __init__(self, lib):
         self._lib = lib

@@ -123,7 +123,20 @@ def w_paged(small):
     return (lambda i: paged.decode_attention(q, kc, vc, table, lens, page)), 0.0, 2 * B * ctx * Hkv * D * 2, f"paged decode attention B{B} ctx{ctx} GQA {Hq}/{Hkv}"
 
 
-WORKLOADS = {"gemm": w_gemm, "flash_fwd": w_flash_fwd, "flash_bwd": lambda s: w_flash_fwd(s, True), "rmsnorm": w_rmsnorm,
+def w_flash_fwd_one_tile(small):
+    from .ops import flash
+    fn, flops, nbytes, desc = w_flash_fwd(small)
+
+    def run(i):
+        flash.set_one_tile(True)
+        try:
+            return fn(i)
+        finally:
+            flash.set_one_tile(False)
+    return run, flops, nbytes, desc + " (one query tile per CTA)"
+
+
+WORKLOADS = {"gemm": w_gemm, "flash_fwd": w_flash_fwd, "flash_fwd_one_tile": w_flash_fwd_one_tile, "flash_bwd": lambda s: w_flash_fwd(s, True), "rmsnorm": w_rmsnorm,
              "adamw": w_adamw, "conv": w_conv, "qgemm": w_qgemm, "paged_decode": w_paged}
 
 

@@ -22,13 +22,14 @@ def _flash_ok(q, k, v, mask, dropout_p) -> bool:
 
 
 def sdpa_reference(q, k, v, mask=None, causal: bool = False, scale: float | None = None):
-    """fp32 reference: q [B,Sq,Hq,D], k/v [B,Sk,Hkv,D] -> [B,Sq,Hq,D]."""
+    """Reference in fp32 (fp64 for fp64 inputs): q [B,Sq,Hq,D], k/v [B,Sk,Hkv,D] -> [B,Sq,Hq,D]."""
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    qf = q.float().permute(0, 2, 1, 3)
-    kf = k.float().permute(0, 2, 1, 3)
-    vf = v.float().permute(0, 2, 1, 3)
+    cd = torch.float64 if q.dtype == torch.float64 else torch.float32      # never below the input's precision
+    qf = q.to(cd).permute(0, 2, 1, 3)
+    kf = k.to(cd).permute(0, 2, 1, 3)
+    vf = v.to(cd).permute(0, 2, 1, 3)
     if Hkv != Hq:
         rep = Hq // Hkv
         kf = kf.repeat_interleave(rep, dim=1)

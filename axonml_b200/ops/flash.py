@@ -29,6 +29,12 @@ def _strides(t):
     return t, t.stride(1), t.stride(0)
 
 
+def set_one_tile(flag: bool) -> None:
+    """Forces the forward kernel with one 128-query tile per CTA (``True``) instead of the choice by
+    sequence length; for comparisons of the two kernels."""
+    N.cuda().ax_flash_fwd_set_one_tile(int(bool(flag)))
+
+
 def flash_fwd(q, k, v, causal: bool, scale: float | None = None):
     B, Sq, Hq, D = q.shape
     Skv, Hkv = k.shape[1], k.shape[2]

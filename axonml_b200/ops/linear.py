@@ -41,10 +41,19 @@ class _LinearFn(torch.autograd.Function):
         ctx.sink = sink
         x2 = x.reshape(-1, x.shape[-1])
         need_z = act != "none" and (x.requires_grad or w.requires_grad)
-        if need_z:
-            y, z = gemm_bf16(x2, w, bias=b, act=act, want_aux=True)
-        else:
-            y, z = gemm_bf16(x2, w, bias=b, act=act), None
+        y = None
+        gate = getattr(w, "_axon_gate", None)
+        if gate is not None and gate.pending:
+            # first use of a sharded unit's parameters in this pass: gather them inside this GEMM
+            if gate.usable(x2, w, need_z):
+                y, z = gate.gemm(x2.contiguous(), w, b, act), None
+            else:
+                gate.fallback()
+        if y is None:
+            if need_z:
+                y, z = gemm_bf16(x2, w, bias=b, act=act, want_aux=True)
+            else:
+                y, z = gemm_bf16(x2, w, bias=b, act=act), None
         ctx.act = act
         ctx.has_bias = b is not None
         ctx.bias_dtype = b.dtype if b is not None else None
@@ -85,6 +94,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
            act: str = "none") -> torch.Tensor:
     """``act(x @ weight.T + bias)`` for ``weight[out, in]``; any number of leading dims."""
     act = act or "none"
+    gate = getattr(weight, "_axon_gate", None)
+    if gate is not None and gate.pending and not _use_kernel(x, weight):
+        gate.fallback()            # a sharded unit's gather is still owed and this call cannot carry it
     if _use_kernel(x, weight):
         if bias is not None and bias.dtype not in (torch.float32, torch.bfloat16):
             bias = bias.float()

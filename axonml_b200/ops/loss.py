@@ -85,7 +85,8 @@ def cross_entropy(logits, target, *, valid_classes: int | None = None, ignore_in
     if _ok(logits) and target.dtype in (torch.int64, torch.int32, torch.float32):
         return _CEFn.apply(logits, target, valid_classes, ignore_index, reduction)
     lg = logits if valid_classes is None else logits[..., :valid_classes]
-    return F.cross_entropy(lg.reshape(-1, lg.shape[-1]).float(), target.reshape(-1).long(),
+    cd = torch.float64 if lg.dtype == torch.float64 else torch.float32      # never below the input's precision
+    return F.cross_entropy(lg.reshape(-1, lg.shape[-1]).to(cd), target.reshape(-1).long(),
                            ignore_index=ignore_index, reduction=reduction).reshape(
                                target.shape if reduction == "none" else ())
 

@@ -66,11 +66,12 @@ class _NormFn(torch.autograd.Function):
 
 def _ref(x, residual, w, b, eps, rms):
     h = x if residual is None else x + residual
-    hf = h.float()
+    cd = torch.float64 if h.dtype == torch.float64 else torch.float32     # never below the input's precision
+    hf = h.to(cd)
     if rms:
-        y = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        y = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * w.to(cd)
     else:
-        y = F.layer_norm(hf, (h.shape[-1],), w.float(), None if b is None else b.float(), eps)
+        y = F.layer_norm(hf, (h.shape[-1],), w.to(cd), None if b is None else b.to(cd), eps)
     y = y.to(x.dtype)
     return (y, h) if residual is not None else (y, None)
 

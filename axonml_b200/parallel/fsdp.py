@@ -9,7 +9,13 @@ the result of its reduce-scatter (fsdp.rs:259-268, :350-354); here the engine is
 
 * one flat unit per transformer block (plus a root unit for what is left), see ``flat_param``;
 * forward / recompute / backward gather a unit's parameters just in time on a communication
-  stream and prefetch the next unit while the current one computes;
+  stream and prefetch the next unit while the current one computes; with ``gather="fused"`` (the
+  default on B200s with symmetric memory, bf16 and more than one rank) the forward and the
+  recomputed forward do not gather at all: the first Linear of a unit runs as ONE kernel that
+  gathers the unit's flat buffer over peer memory and computes that Linear, its weight loads gated
+  on the arrival of the rows they read (``csrc/kernels/gemm_gather.cu``).  For this the 1-D
+  parameters of the units (norm weights, biases) move into the root unit, which is gathered once
+  per step, so that everything a unit gathers is first touched by a GEMM;
 * ZeRO-3 with more than one rank rotates three full-size buffers between the block units (a
   unit's parameters always view the same buffer, so no pointer is ever re-bound); ZeRO-2, NoShard
   and single-rank runs keep one resident buffer per unit;
@@ -23,6 +29,7 @@ from __future__ import annotations
 import contextlib
 import dataclasses
 import enum
+import os
 
 import torch
 import torch.distributed as dist
@@ -57,17 +64,78 @@ class FSDPMemoryStats:
 
 
 class _Buffer:
-    def __init__(self, numel, dtype, device):
-        self.data = torch.zeros(numel, dtype=dtype, device=device)
+    def __init__(self, numel, dtype, device, heap=None):
+        self.sym = self.sig = None
+        self.epoch = 0
+        if heap is not None:
+            # symmetric memory: peers write their shards into this buffer from inside the fused
+            # gather + GEMM kernel; `sig` holds that kernel's flags
+            from .. import _native as N
+            self.sym = heap.allocate(numel, dtype)
+            self.data = self.sym.local
+            self.sig = heap.allocate(max(int(N.cuda().ax_gemm_gather_signal_slots(numel, heap.world)), 64), torch.int32)
+            heap.barrier()
+        else:
+            self.data = torch.zeros(numel, dtype=dtype, device=device)
         self.owner = None
         self.free_event = None
+
+
+class _GatherGate:
+    """Pending gather of one unit, carried by the unit's 2-D weights (``_axon_gate``): the first
+    Linear that runs on one of them turns it into the fused gather + GEMM launch."""
+
+    def __init__(self, engine, unit):
+        self.engine, self.unit = engine, unit
+        self.pending = False
+
+    def usable(self, x2, w, act_needs_aux: bool) -> bool:
+        return (self.pending and not act_needs_aux and x2.dtype == torch.bfloat16
+                and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0 and x2.shape[0] > 0)
+
+    def gemm(self, x2, w, bias, act: str):
+        """``act(x2 @ w.T + bias)`` with the gather of the whole unit inside the same launch."""
+        import ctypes
+        from .. import _native as N
+        from ..ops.gemm import ACT
+        u, eng = self.unit, self.engine
+        buf = u.buffer
+        buf.epoch += 1
+        w_off = (w.data_ptr() - u.full.data_ptr()) // 2
+        out = torch.empty((x2.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x2.device)
+        bias_kind = 0
+        if bias is not None:
+            bias = bias.contiguous()
+            bias_kind = 1 if bias.dtype == torch.float32 else 2
+        # what one copy CTA moves per second (measured on peer copies); the gather has the time of
+        # the GEMM to finish, a multicast store leaves the GPU once
+        copies = 1 if (buf.sym.mc_ptr and eng.world > 2) else eng.world
+        gemm_s = 2.0 * x2.shape[0] * w.shape[0] * w.shape[1] / 1.4e15
+        need = u.shard * 2 * copies / 22e9 / max(0.5 * gemm_s, 2e-5)
+        copy_pairs = int(min(max(need / 2 + 0.999, 1), 12))
+        rc = N.cuda().ax_gemm_gather(
+            N.ptr(x2), N.ptr(out), N.ptr(bias), bias_kind, ACT[act], x2.shape[0], w.shape[0], w.shape[1],
+            ctypes.c_long(w_off), ctypes.c_long(u.padded), N.ptr(u.lp_shard), buf.sym.ptr_array(), buf.sym.mc(),
+            buf.sig.ptr_array(), eng.rank, eng.world, ctypes.c_uint(buf.epoch), copy_pairs,
+            N.ptr(N.status_word(x2.device)), N.stream_ptr())
+        N.check(rc, "ax_gemm_gather")
+        self.pending = False
+        eng._mark_gathered(u)
+        eng.fused_gathers += 1
+        return out
+
+    def fallback(self) -> None:
+        """The first consumer is not a Linear this kernel can take: gather the plain way, now."""
+        self.pending = False
+        self.engine._gather(self.unit)
+        self.engine._wait(self.unit)
 
 
 class FullyShardedDataParallel(Module):
     def __init__(self, module: torch.nn.Module, process_group: ProcessGroup | None = None, *,
                  units: list | None = None, param_dtype: torch.dtype | None = None,
                  strategy: ShardingStrategy = ShardingStrategy.FullShard, device=None,
-                 fused_adamw: dict | None = None):
+                 fused_adamw: dict | None = None, gather: str = "auto"):
         super().__init__()
         self.module = module
         self.pg = process_group or ProcessGroup.mock()
@@ -88,6 +156,9 @@ class FullyShardedDataParallel(Module):
         self._fused = None
         self._fused_step = 0
         self._fused_pending = False
+        self._gather_mode = os.environ.get("AXONML_FSDP_GATHER", gather)
+        self._k4 = False
+        self.fused_gathers = 0           # launches of the fused gather + GEMM kernel so far
         self._build()
 
     # ------------------------------------------------------------------ reference builders
@@ -160,8 +231,10 @@ class FullyShardedDataParallel(Module):
         shard_params = self._strategy is not ShardingStrategy.NoShard
         w = self.world if shard_params else 1
         r = self.rank if shard_params else 0
+        self._k4 = self._want_fused_gather(unit_mods)
         for i, m in enumerate(unit_mods):
-            ps = [p for p in m.parameters() if id(p) not in seen and p.requires_grad]
+            ps = [p for p in m.parameters() if id(p) not in seen and p.requires_grad
+                  and (p.dim() >= 2 or not self._k4)]     # fused gather: 1-D parameters go to the root unit
             for p in ps:
                 seen.add(id(p))
             if not ps:
@@ -183,14 +256,18 @@ class FullyShardedDataParallel(Module):
         rotate = (self._strategy in (ShardingStrategy.FullShard, ShardingStrategy.HybridShard)
                   and self.world > 1 and len(self.block_units) > 3)
         self._rotate = rotate
+        heap = None
+        if self._k4:
+            from .symm import SymmetricHeap
+            heap = SymmetricHeap(self.pg)
         if rotate:
             size = max(u.padded for u in self.block_units)
-            self._pool = [_Buffer(size, self.param_dtype, self.device) for _ in range(3)]
+            self._pool = [_Buffer(size, self.param_dtype, self.device, heap) for _ in range(3)]
         for u in self.units:
             if rotate and not u.is_root:
                 u.buffer = self._pool[u.index % 3]
             else:
-                u.buffer = _Buffer(u.padded, self.param_dtype, self.device)
+                u.buffer = _Buffer(u.padded, self.param_dtype, self.device, heap if (not u.is_root and u.world > 1) else None)
                 u.buffer.owner = u
             u.bind_full(u.buffer.data[:u.padded])
             if u.world == 1:
@@ -206,6 +283,20 @@ class FullyShardedDataParallel(Module):
             u.master._axon_grad = None
         self._attach_segments()
         self._comm = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        if self._k4:
+            from ..nn.layers.linear import Linear as _Linear
+            for u in self.block_units:
+                u.gate = _GatherGate(self, u)
+                for p in u.params:
+                    if p.dim() == 2:
+                        p._axon_gate = u.gate
+                # Safety net: a submodule that owns weights but does not go through ops.linear (which
+                # consumes the gate) must find its weights gathered when its forward starts.
+                own = {id(p) for p in u.params}
+                for sub in u.module.modules():
+                    if isinstance(sub, _Linear) or not any(id(p) in own for p in sub.parameters(recurse=False)):
+                        continue
+                    sub.register_forward_pre_hook(lambda m, a, g=u.gate: g.fallback() if g.pending else None)
 
         for u in self.block_units:
             u.module.register_forward_pre_hook(lambda m, a, u=u: self._pre_forward(u))
@@ -217,6 +308,29 @@ class FullyShardedDataParallel(Module):
                 if not u.is_root and p.dim() == 2:
                     p._axon_grad_sink = _GradSink(self, u, idx)
         self._built = True
+
+    def _want_fused_gather(self, unit_mods) -> bool:
+        """Whether the forward gathers of the block units run inside their first GEMM."""
+        if self._gather_mode == "nccl" or not unit_mods:
+            return False
+        ok = (self.world > 1 and self.device.type == "cuda" and self.param_dtype == torch.bfloat16
+              and self._strategy in (ShardingStrategy.FullShard, ShardingStrategy.HybridShard))
+        if ok:
+            from .. import _native as N
+            from .symm import available
+            ok = available(self.pg) and N.is_blackwell() and self.world <= 8
+        if not ok and self._gather_mode == "fused":
+            raise ValueError("gather='fused' needs more than one rank on B200s with symmetric memory, bf16 parameters "
+                             "and the FullShard strategy")
+        return ok
+
+    def _mark_gathered(self, u: FlatUnit) -> None:
+        buf = u.buffer
+        if buf.owner is not None and buf.owner is not u:
+            buf.owner.gathered = False
+        buf.owner = u
+        u.gathered = True
+        u.gather_event = None
 
     def _attach_segments(self) -> None:
         """Tells per-tensor optimizers (LAMB's trust ratio) which tensors a master shard holds:
@@ -303,21 +417,30 @@ class FullyShardedDataParallel(Module):
         return self.block_units[j] if 0 <= j < len(self.block_units) else None
 
     def _pre_forward(self, u: FlatUnit) -> None:
+        if self._k4 and not u.gathered and u.world > 1:
+            # no gather here: the unit's first Linear gathers inside its own kernel
+            u.gate.pending = True
+            return
         self._gather(u)
         self._wait(u)
         nxt = self._neighbor(u, -1 if self._phase == "bwd" else 1)
-        if nxt is not None:
+        if nxt is not None and not self._k4:
             self._gather(nxt)
 
     def _post_forward(self, u: FlatUnit) -> None:
+        if self._k4 and getattr(u, "gate", None) is not None and u.gate.pending:
+            # nothing in the unit consumed the gate (a unit without a Linear on the kernel path)
+            u.gate.pending = False
         self._mark_free(u)
 
     def _pre_backward(self, u: FlatUnit) -> None:
         self._enter_backward()
+        if self._k4 and getattr(u, "gate", None) is not None:
+            u.gate.pending = False
         self._gather(u)
         self._wait(u)
         prv = self._neighbor(u, -1)
-        if prv is not None:
+        if prv is not None and not self._k4:
             self._gather(prv)
 
     # ------------------------------------------------------------------ gradients
@@ -446,7 +569,7 @@ class FullyShardedDataParallel(Module):
         if self.root is not None:
             self._gather(self.root)
             self._wait(self.root)
-        if self.block_units:
+        if self.block_units and not self._k4:
             self._gather(self.block_units[0])
         out = fn(*args, **kwargs)
         for t in (out if isinstance(out, (tuple, list)) else (out,)):

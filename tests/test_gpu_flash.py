@@ -130,3 +130,27 @@ def test_cached_generation_equals_uncached_on_the_gpu(dtype):
             assert lg.max().item() - lg[0, tok].item() < 0.25
             if tok != lg.argmax(-1).item():
                 break
+
+
+@pytest.mark.parametrize("B,Sq,Skv,Hq,Hkv,causal", [
+    (1, 256, 256, 2, 2, True), (2, 384, 384, 4, 2, True), (1, 300, 300, 2, 1, True), (1, 129, 700, 2, 2, True),
+    (1, 2048, 2048, 2, 2, True), (1, 512, 512, 2, 2, False), (1, 260, 999, 2, 1, False), (2, 640, 1000, 4, 4, True)])
+def test_flash_forward_two_query_tiles_per_cta(B, Sq, Skv, Hq, Hkv, causal, kernel_status):
+    """Sequences longer than 128 queries run the kernel with two query tiles per CTA (probabilities
+    kept in TMEM): against the fp32 reference, against the one-tile kernel, and its log-sum-exp."""
+    from axonml_b200.ops import flash
+    q = torch.randn(B, Sq, Hq, 128, device="cuda").bfloat16()
+    k = torch.randn(B, Skv, Hkv, 128, device="cuda").bfloat16()
+    v = torch.randn(B, Skv, Hkv, 128, device="cuda").bfloat16()
+    out, lse, _ = flash.flash_fwd(q, k, v, causal)
+    flash.set_one_tile(True)
+    try:
+        out1, lse1, _ = flash.flash_fwd(q, k, v, causal)
+    finally:
+        flash.set_one_tile(False)
+    ref = _ref(q.float(), k.float(), v.float(), causal)
+    assert (out.float() - ref).abs().max().item() < 3e-2
+    assert (out.float() - out1.float()).abs().max().item() < 2e-2
+    fin = torch.isfinite(lse1)
+    assert torch.equal(fin, torch.isfinite(lse))
+    assert (lse[fin] - lse1[fin]).abs().max().item() < 1e-2

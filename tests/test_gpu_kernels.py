@@ -646,16 +646,16 @@ def test_avg_pool2d_kernel_forward_backward(dtype, channels_last, k, s, p):
         x = x.contiguous(memory_format=torch.channels_last)
     x.requires_grad_()
     y = avg_pool2d(x, k, s, p)
-    xr = x.detach().float().requires_grad_()
+    xr = x.detach().float().cpu().contiguous().requires_grad_()       # reference on the CPU, plain layout
     yr = F.avg_pool2d(xr, k, s, p, count_include_pad=False)
     g = torch.randn_like(yr)
-    y.backward(g.to(dtype))
+    y.backward(g.to(DEV).to(dtype))
     yr.backward(g)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
-    close(y, yr, tol, tol)
-    close(x.grad, xr.grad, tol, tol)
+    close(y.cpu(), yr, tol, tol)
+    close(x.grad.cpu(), xr.grad, tol, tol)
     y2 = avg_pool2d(x.detach(), k, s, p, count_include_pad=True)
-    close(y2, F.avg_pool2d(xr.detach(), k, s, p, count_include_pad=True), tol, tol)
+    close(y2.cpu(), F.avg_pool2d(xr.detach(), k, s, p, count_include_pad=True), tol, tol)
 
 
 @pytest.mark.parametrize("out", [(1, 1), (7, 7), (3, 5), (4, 2)])

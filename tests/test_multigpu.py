@@ -109,6 +109,53 @@ def test_fsdp_fused_rs_adamw_matches_nccl_path(nvls):
         assert diff < 1e-2 and mean < 1e-4, (diff, mean)
 
 
+def _fsdp_fused_gather(rank, world, be):
+    """The same model trained with the unit gathers as NCCL all-gathers and with the gathers inside
+    the units' first GEMM (activation checkpointing on, so every unit is gathered twice per step)."""
+    import copy
+    from axonml_b200 import _native, optim
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    from axonml_b200.parallel import FSDP, ProcessGroup
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=512, n_ctx=128, n_embd=256, n_layer=5, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    base = GPT2LMHead(cfg, device="cuda", dtype=torch.bfloat16)
+    pg = ProcessGroup(be)
+    runs = {}
+    for mode in ("nccl", "fused"):
+        m = copy.deepcopy(base)
+        m.gradient_checkpointing_enable(True)
+        m.train()
+        f = FSDP(m, pg, gather=mode)
+        assert f._k4 == (mode == "fused")
+        o = optim.AdamW(f.parameters(), 1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+        g = torch.Generator().manual_seed(5)
+        ids = torch.randint(0, 512, (3, 2 * world, 128), generator=g).cuda()
+        losses = []
+        for it in range(3):
+            loss, _ = f.call("forward_with_loss", ids[it].chunk(world)[rank])
+            loss.backward()
+            o.step()
+            f.zero_grad()
+            losses.append(loss.item())
+        torch.cuda.synchronize()
+        _native.check_status()
+        runs[mode] = (losses, f.full_state_dict(), f.fused_gathers)
+    (l1, sd1, n1), (l2, sd2, n2) = runs["nccl"], runs["fused"]
+    mean = sum((sd1[k] - sd2[k]).abs().sum().item() for k in sd1) / sum(v.numel() for v in sd1.values())
+    return l1, l2, mean, n1, n2
+
+
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fsdp_gather_inside_the_first_gemm_matches_nccl_gathers(nvls):
+    res = run_gpu_ranks(_fsdp_fused_gather, WORLD, env={"AXONML_NVLS": nvls})
+    for r in range(WORLD):
+        l1, l2, mean, n1, n2 = res[r][1]
+        assert n1 == 0 and n2 == 3 * 5 * 2, (n1, n2)          # forward and recomputation of 5 units, 3 steps
+        assert max(abs(a - b) for a, b in zip(l1, l2)) < 3e-2, (l1, l2)
+        assert mean < 1e-4, mean
+
+
 def _fsdp_lamb(rank, world, be):
     from axonml_b200 import _native, nn, optim
     from axonml_b200.parallel import FSDP, ProcessGroup
