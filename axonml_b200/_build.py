@@ -86,11 +86,15 @@ def _build_lib(sources: list[Path], out: Path, compiler: list[str], flags: list[
     return False
 
 
-def build_cuda(verbose: bool = True) -> Path:
-    out = LIB / "libaxonml_cuda.so"
+def build_cuda(verbose: bool = True, bounds: bool = False) -> Path:
+    """``bounds=True`` builds ``libaxonml_cuda_bounds.so``: the same sources with ``-DAX_BOUNDS=1``
+    (index checks that report instead of accessing, see ``common.cuh``) as relocatable device code,
+    because the violation word is one device symbol shared by all translation units."""
+    out = LIB / ("libaxonml_cuda_bounds.so" if bounds else "libaxonml_cuda.so")
     srcs = sorted((CSRC / "kernels").glob("*.cu"))
-    _build_lib(srcs, out, [_nvcc()], NVCC_FLAGS, ["-Xcompiler", "-fPIC", "-cudart", "static"],
-               verbose)
+    flags = NVCC_FLAGS + (["-DAX_BOUNDS=1", "-rdc=true"] if bounds else [])
+    link = ["-Xcompiler", "-fPIC", "-cudart", "static"] + (["-gencode", "arch=compute_100a,code=sm_100a", "-rdc=true"] if bounds else [])
+    _build_lib(srcs, out, [_nvcc()], flags, link, verbose)
     return out
 
 
@@ -103,10 +107,12 @@ def build_host(verbose: bool = True) -> Path:
     return out
 
 
-def build(verbose: bool = True) -> None:
+def build(verbose: bool = True, bounds: bool = True) -> None:
     LIB.mkdir(exist_ok=True)
     build_host(verbose)
     build_cuda(verbose)
+    if bounds:
+        build_cuda(verbose, bounds=True)
 
 
 if __name__ == "__main__":

@@ -42,7 +42,7 @@ class _CountingLib:
     (every ``ax_*`` entry that takes a stream launches at least one kernel)."""
 
     _NO_LAUNCH = {"ax_version", "ax_sm_count", "ax_norm_bwd_groups", "ax_multi_tensor_limits", "ax_gemm_comm_set_trace",
-                  "ax_flash_fwd_set_trace", "ax_gemm_comm_signal_slots", "ax_norm_bwd_noalloc_limits", "ax_gemm_set_pair_mode", "ax_flash_fwd_set_one_tile", "ax_gemm_pair_capacity"}
+                  "ax_flash_fwd_set_trace", "ax_gemm_comm_signal_slots", "ax_norm_bwd_noalloc_limits", "ax_gemm_set_pair_mode", "ax_flash_fwd_set_one_tile", "ax_bounds_enabled", "ax_bounds_read", "ax_gemm_pair_capacity"}
 
     def __init__(self, lib):
         self._lib = lib
@@ -63,14 +63,38 @@ class _CountingLib:
         return fn
 
 
+def bounds_build() -> bool:
+    """``AXONML_BOUNDS=1`` selects the debug build of the kernels whose index checks report a wrong
+    index (``bounds_report``) instead of using it."""
+    return os.environ.get("AXONML_BOUNDS") == "1"
+
+
 def cuda():
     """Handle of the CUDA kernel library (built for sm_100a)."""
     global _CUDA
     if _CUDA is None:
         with _LOCK:
             if _CUDA is None:
-                _CUDA = _CountingLib(_load("libaxonml_cuda.so", "build_cuda"))
+                if bounds_build():
+                    path = _LIBDIR / "libaxonml_cuda_bounds.so"
+                    if not path.exists() or os.environ.get("AXONML_REBUILD") == "1":
+                        from . import _build
+                        _build.build_cuda(verbose=True, bounds=True)
+                    _CUDA = _CountingLib(ctypes.CDLL(str(path)))
+                else:
+                    _CUDA = _CountingLib(_load("libaxonml_cuda.so", "build_cuda"))
     return _CUDA
+
+
+def bounds_report():
+    """First index violation the debug build recorded since the last call, as a dict, or None.
+    Synchronises the device."""
+    out = (ctypes.c_int * 6)()
+    check(cuda().ax_bounds_read(out), "ax_bounds_read")
+    if out[0] == 0:
+        return None
+    u = lambda lo, hi: (int(lo) & 0xffffffff) | (int(hi) << 32)
+    return {"code": int(out[0]), "where": int(out[1]), "index": u(out[2], out[3]), "extent": u(out[4], out[5])}
 
 
 def launch_count() -> int:

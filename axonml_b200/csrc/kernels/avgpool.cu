@@ -69,8 +69,12 @@ __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const T* __restrict__ 
     window(p, oh, p.H, p.OH, p.kh, p.sh, p.ph, h0, h1, hs);
     window(p, ow, p.W, p.OW, p.kw, p.sw, p.pw, w0, w1, ws);
     float acc = 0.f;
+    const long in_total = (long)p.N * p.C * p.H * p.W;
     for (int h = h0; h < h1; ++h)
-      for (int w = w0; w < w1; ++w) acc += to_f(x[offset(n, c, h, w, p.C, p.H, p.W, p.channels_last)]);
+      for (int w = w0; w < w1; ++w) {
+        const long off = offset(n, c, h, w, p.C, p.H, p.W, p.channels_last);
+        if (AX_INB(off, 1, in_total, 3000)) acc += to_f(x[off]);
+      }
     const int cnt = (!p.adaptive && p.count_pad) ? hs * ws : max(h1 - h0, 0) * max(w1 - w0, 0);
     from_f(&y[i], cnt > 0 ? acc / (float)cnt : 0.f);
   }
@@ -108,7 +112,8 @@ __global__ void __launch_bounds__(256) avgpool_bwd_kernel(const T* __restrict__ 
         window(p, ow, p.W, p.OW, p.kw, p.sw, p.pw, w0, w1, ws);
         if (w < w0 || w >= w1) continue;
         const int cnt = (!p.adaptive && p.count_pad) ? hs * ws : (h1 - h0) * (w1 - w0);
-        acc += to_f(dy[offset(n, c, oh, ow, p.C, p.OH, p.OW, p.channels_last)]) / (float)cnt;
+        const long off = offset(n, c, oh, ow, p.C, p.OH, p.OW, p.channels_last);
+        if (AX_INB(off, 1, (long)p.N * p.C * p.OH * p.OW, 3001)) acc += to_f(dy[off]) / (float)cnt;
       }
     }
     from_f(&dx[i], acc);

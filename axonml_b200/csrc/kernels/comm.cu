@@ -253,6 +253,75 @@ fused_rs_adamw_kernel(const Peers P, long grad_off, long shard, float* master, f
   collective_end(P, epoch, 0, status, done_base);
 }
 
+// First phase of LAMB on a sharded unit, fused with the gradient reduce-scatter: rank r sums its shard
+// of every peer's flat gradient, updates the moments and writes the per-element update
+//   c = (m / bc1) / (sqrt(v / bc2) + eps) + wd * w
+// into `upd`, and adds this shard's share of sum(w^2) and sum(c^2) of every tensor to
+// norms[2 * tensor id + {0, 1}].  A shard holds whole or partial tensors back to back; seg_start
+// [nseg + 1] are their boundaries inside the shard (multiples of 8 elements, the tensors are laid out
+// on 64-element boundaries) and seg_gid[nseg] their ids.  The second phase (trust ratio per tensor
+// from the norms summed over ranks, then w -= lr * trust * c) runs once all units have finished
+// this one (lamb.rs:200-280 of the reference does both per parameter on unsharded tensors).
+template <bool MC>
+__global__ void __launch_bounds__(kThreads)
+fused_rs_lamb1_kernel(const Peers P, long grad_off, long shard, const float* __restrict__ master, float* m1, float* m2,
+                      float* upd, const long* __restrict__ seg_start, const int* __restrict__ seg_gid, int nseg,
+                      float* norms, const AdamW h, const int* skip_flag, uint32_t epoch, int* status) {
+  uint32_t done_base;
+  const bool ok = collective_begin(P, epoch, status, done_base);
+  if (ok && !(skip_flag && *skip_flag)) {
+    const long lo = grad_off + shard * 2 * P.rank;
+    for (long i0 = (long)blockIdx.x * kThreads * 8; i0 < shard; i0 += (long)gridDim.x * kThreads * 8) {
+      const long i = i0 + (long)threadIdx.x * 8;
+      float sw = 0.f, sc = 0.f;
+      int seg = -1;
+      if (i < shard) {
+        float g[8];
+        reduce16<true, MC>(P, lo + i * 2, g);
+        const float4 w0 = *reinterpret_cast<const float4*>(master + i), w1 = *reinterpret_cast<const float4*>(master + i + 4);
+        float4 a0 = *reinterpret_cast<float4*>(m1 + i), a1 = *reinterpret_cast<float4*>(m1 + i + 4);
+        float4 b0 = *reinterpret_cast<float4*>(m2 + i), b1 = *reinterpret_cast<float4*>(m2 + i + 4);
+        const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        float c[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float gr = g[j] * h.mul;
+          a[j] = h.beta1 * a[j] + (1.f - h.beta1) * gr;
+          b[j] = h.beta2 * b[j] + (1.f - h.beta2) * gr * gr;
+          c[j] = (a[j] / h.bc1) / (sqrtf(b[j] / h.bc2) + h.eps) + h.wd * w[j];
+          sw += w[j] * w[j];
+          sc += c[j] * c[j];
+        }
+        *reinterpret_cast<float4*>(m1 + i) = make_float4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<float4*>(m1 + i + 4) = make_float4(a[4], a[5], a[6], a[7]);
+        *reinterpret_cast<float4*>(m2 + i) = make_float4(b[0], b[1], b[2], b[3]);
+        *reinterpret_cast<float4*>(m2 + i + 4) = make_float4(b[4], b[5], b[6], b[7]);
+        *reinterpret_cast<float4*>(upd + i) = make_float4(c[0], c[1], c[2], c[3]);
+        *reinterpret_cast<float4*>(upd + i + 4) = make_float4(c[4], c[5], c[6], c[7]);
+        // the tensor these 8 elements belong to (a handful of tensors per shard: a linear scan)
+        for (int k = 0; k < nseg; ++k)
+          if (i >= seg_start[k] && i < seg_start[k + 1]) { seg = k; break; }
+      }
+      // one pair of atomics per warp when the whole warp sits in one tensor, else per lane
+      const int seg0 = __shfl_sync(0xffffffffu, seg, 0);
+      if (__all_sync(0xffffffffu, seg == seg0)) {
+        sw = warp_sum(sw);
+        sc = warp_sum(sc);
+        if ((threadIdx.x & 31) == 0 && seg0 >= 0) {
+          atomicAdd(norms + 2 * seg_gid[seg0], sw);
+          atomicAdd(norms + 2 * seg_gid[seg0] + 1, sc);
+        }
+      } else if (seg >= 0) {
+        atomicAdd(norms + 2 * seg_gid[seg], sw);
+        atomicAdd(norms + 2 * seg_gid[seg] + 1, sc);
+      }
+    }
+  }
+  collective_end(P, epoch, 0, status, done_base);
+}
+
 // Every launch on one communicator uses the same grid (the per-GPU completion counter advances by
 // exactly `grid` per epoch); kernels are grid-stride, so any size is correct.
 int checked_grid(int grid) {
@@ -319,5 +388,24 @@ AX_API int ax_fused_rs_adamw(void* const* grad_bufs, void* const* sigs, void* gr
     fused_rs_adamw_kernel<true><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, (__nv_bfloat16*)lp, push, push_off, h, skip_flag, epoch, status);
   else
     fused_rs_adamw_kernel<false><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, (__nv_bfloat16*)lp, push, push_off, h, skip_flag, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+// First LAMB phase fused with the reduce-scatter of a unit's flat gradient (see the kernel).
+// hyper: float[7] as for ax_fused_rs_adamw (lr is not used here).  `upd` [shard] fp32 receives the
+// per-element update, `norms` [num_tensors][2] fp32 (zeroed by the caller once per step) the sums.
+AX_API int ax_fused_rs_lamb1(void* const* grad_bufs, void* const* sigs, void* grad_mc, int rank, int world,
+                             long grad_off, long shard, const float* master, float* m1, float* m2, float* upd,
+                             const long* seg_start, const int* seg_gid, int nseg, float* norms,
+                             const float* hyper, const int* skip_flag, unsigned epoch, int grid_blocks,
+                             int* status, cudaStream_t stream) {
+  if (world < 1 || world > axc::kMaxRanks || shard % 8 || grad_off % 16 || nseg < 0) return -1;
+  Peers P = make_peers(grad_bufs, sigs, grad_mc, rank, world);
+  AdamW h{hyper[0], hyper[1], hyper[2], hyper[3], hyper[4], hyper[5], hyper[6], 1.f / world};
+  const int grid = checked_grid(grid_blocks);
+  if (grad_mc)
+    fused_rs_lamb1_kernel<true><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, upd, seg_start, seg_gid, nseg, norms, h, skip_flag, epoch, status);
+  else
+    fused_rs_lamb1_kernel<false><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, upd, seg_start, seg_gid, nseg, norms, h, skip_flag, epoch, status);
   return (int)cudaGetLastError();
 }

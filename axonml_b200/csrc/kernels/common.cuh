@@ -34,6 +34,29 @@ __device__ __forceinline__ void set_status(int* status, int code, int detail) {
   }
 }
 
+// ---------------------------------------------------------------- bounds-checked debug build
+// Compiled with -DAX_BOUNDS=1 (relocatable device code, its own shared object) the kernels check the
+// indices they compute before they use them: AX_INB(i, width, n, where) is true when elements
+// [i, i + width) lie inside an n-element extent; otherwise it records {code 4, where, index,
+// extent} once in a word that the host reads with ax_bounds_read and returns false, and the caller
+// skips the access, so a wrong index is reported instead of reading or writing memory it should
+// not.  In the normal build the macro is the constant `true` and the checks vanish.
+#ifdef AX_BOUNDS
+extern __device__ int g_bounds_word[6];   // code, where, index lo/hi 32 bits, extent lo/hi 32 bits
+__device__ __forceinline__ bool in_bounds(long i, long width, long n, int where) {
+  if (i >= 0 && i + width <= n) return true;
+  if (atomicCAS(&g_bounds_word[0], 0, 4) == 0) {
+    g_bounds_word[1] = where;
+    g_bounds_word[2] = (int)(i & 0xffffffffL); g_bounds_word[3] = (int)(i >> 32);
+    g_bounds_word[4] = (int)(n & 0xffffffffL); g_bounds_word[5] = (int)(n >> 32);
+  }
+  return false;
+}
+#define AX_INB(i, width, n, where) ax::in_bounds((long)(i), (long)(width), (long)(n), (where))
+#else
+#define AX_INB(i, width, n, where) true
+#endif
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -106,10 +129,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Upper bound (ns) the hardware may keep a waiting thread suspended inside one try_wait; the thread
-// wakes as soon as the phase completes, so a long hint costs no latency and frees issue slots that
-// a tight polling loop would take from the warps doing the work.
-constexpr uint32_t kSuspendHintNs = 20000;
+// mbarrier.try_wait may carry a hint of how long (ns) the hardware may keep the waiting thread
+// suspended before it returns.  0 compiles the plain form, which returns after the hardware's own
+// short limit; the loop around it then polls again.
+#ifndef AX_SUSPEND_HINT_NS
+#define AX_SUSPEND_HINT_NS 0
+#endif
+constexpr uint32_t kSuspendHintNs = AX_SUSPEND_HINT_NS;
 
 // Bounded wait.  `dead` is a shared-memory flag of the CTA: once any wait of the CTA has
 // given up, all later waits return at once so that the CTA drains quickly.
@@ -119,15 +145,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint32_t spins = 0;
   uint64_t t0 = 0;
   while (true) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
-        "selp.b32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
-        : "memory");
+    if (kSuspendHintNs != 0) {
+      asm volatile(
+          "{\n\t"
+          ".reg .pred P;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+          "selp.b32 %0, 1, 0, P;\n\t"
+          "}\n"
+          : "=r"(ok)
+          : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
+          : "memory");
+    } else {
+      asm volatile(
+          "{\n\t"
+          ".reg .pred P;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+          "selp.b32 %0, 1, 0, P;\n\t"
+          "}\n"
+          : "=r"(ok)
+          : "r"(smem_u32(bar)), "r"(parity)
+          : "memory");
+    }
     if (ok) return true;
     if (++spins >= 16) {
       if (*dead) return false;

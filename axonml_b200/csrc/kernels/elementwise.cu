@@ -105,13 +105,17 @@ __global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n,
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long nv = aligned ? n / V : 0;
   for (long i = tid; i < nv; i += stride) {
+    if (!AX_INB(i * V, V, n, 1000)) continue;
     float v[V];
     IO<T>::load(x + i * V, v);
 #pragma unroll
     for (int j = 0; j < V; ++j) v[j] = unary(v[j], op, p0, p1);
     IO<T>::store(y + i * V, v);
   }
-  for (long i = nv * V + tid; i < n; i += stride) IO<T>::st1(y + i, unary(IO<T>::ld1(x + i), op, p0, p1));
+  for (long i = nv * V + tid; i < n; i += stride) {
+    if (!AX_INB(i, 1, n, 1001)) continue;
+    IO<T>::st1(y + i, unary(IO<T>::ld1(x + i), op, p0, p1));
+  }
 }
 
 template <typename T, int op>

@@ -57,3 +57,53 @@ int sm_count() {
 
 AX_API int ax_version() { return 1; }
 AX_API int ax_sm_count() { return axh::sm_count(); }
+
+// ---------------------------------------------------------------- bounds-checked debug build
+#ifdef AX_BOUNDS
+namespace ax { __device__ int g_bounds_word[6] = {0, 0, 0, 0, 0, 0}; }
+namespace {
+// Walks one element past an n-element extent on purpose, through the checked accessor: in this
+// build the access is skipped and reported, which is what the self-test looks for.
+__global__ void bounds_selftest_kernel(float* p, long n) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i <= n && AX_INB(i, 1, n, 9000)) p[i] += 1.f;
+}
+}  // namespace
+#endif
+
+// 1 when this library was compiled with the index checks.
+AX_API int ax_bounds_enabled() {
+#ifdef AX_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Copies the first recorded violation {code, where, index lo, index hi, extent lo, extent hi} into
+// out[6] (all zero: none) and clears it.  Synchronises the device.
+AX_API int ax_bounds_read(int* out) {
+  for (int i = 0; i < 6; ++i) out[i] = 0;
+#ifdef AX_BOUNDS
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemcpyFromSymbol(out, ax::g_bounds_word, sizeof(int) * 6);
+  if (e != cudaSuccess) return (int)e;
+  const int zero[6] = {0, 0, 0, 0, 0, 0};
+  e = cudaMemcpyToSymbol(ax::g_bounds_word, zero, sizeof(zero));
+  return (int)e;
+#else
+  return 0;
+#endif
+}
+
+// Debug build only: increments p[0..n) through the checked accessor with one thread too many.
+AX_API int ax_bounds_selftest(float* p, long n, cudaStream_t stream) {
+#ifdef AX_BOUNDS
+  bounds_selftest_kernel<<<(unsigned)((n + 1 + 255) / 256), 256, 0, stream>>>(p, n);
+  return (int)cudaGetLastError();
+#else
+  (void)p; (void)n; (void)stream;
+  return -1;
+#endif
+}

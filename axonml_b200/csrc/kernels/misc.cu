@@ -22,6 +22,7 @@ __global__ void embedding_fwd_kernel(const long* __restrict__ idx, const T* __re
   for (long t = blockIdx.x; t < tokens; t += gridDim.x) {
     long id = idx[t];
     const bool valid = id >= 0 && id < V;
+    (void)AX_INB(id, 1, V, 2000);            // debug build: a token id outside the table is reported
     const T* w = W + (valid ? id : 0) * (long)D;
     const T* p = P ? P + ((long)(t % S) + pos0) * D : nullptr;
     T* o = out + t * D;
@@ -41,6 +42,7 @@ __global__ void embedding_bwd_kernel(const long* __restrict__ idx, const T* __re
                                      int D, int S, int pos0, long V, long padding_idx) {
   for (long t = blockIdx.x; t < tokens; t += gridDim.x) {
     long id = idx[t];
+    (void)AX_INB(id, 1, V, 2001);
     const bool valid = id >= 0 && id < V && id != padding_idx;
     const T* g = dout + t * D;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {

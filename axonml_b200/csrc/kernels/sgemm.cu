@@ -128,6 +128,8 @@ __global__ void __launch_bounds__(kThreads) sgemm_kernel(const SgemmParams p) {
     for (int h = 0; h < 2; ++h) {
       const int n = n0 + h * 64 + tx * 4;
       float* dst = C + (long)m * p.ldc + n;
+      if (n >= p.N) continue;               // this thread's columns lie past the matrix
+      if (!AX_INB((long)m * p.ldc + n, n + 3 < p.N ? 4 : p.N - n, (long)(p.M - 1) * p.ldc + p.N, 4000)) continue;
       if (p.vec_ok && n + 3 < p.N) {
         *reinterpret_cast<float4*>(dst) = make_float4(acc[i][4 * h], acc[i][4 * h + 1], acc[i][4 * h + 2], acc[i][4 * h + 3]);
       } else {

@@ -163,6 +163,7 @@ ce_fwd_kernel(const T* __restrict__ logits, const long* __restrict__ target,
     const float lse = m + __logf(s);
     lse_out[blockIdx.x] = lse;
     const long t = target[blockIdx.x];
+    (void)AX_INB(t == ignore_index ? 0 : t, 1, V, 5000);     // debug build: a class index outside the vocabulary is reported
     loss[blockIdx.x] = (t == ignore_index || t < 0 || t >= V) ? 0.f : lse - ldf(row, t);
   }
 }

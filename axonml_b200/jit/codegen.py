@@ -119,7 +119,7 @@ def generate_cuda(graph: Graph):
         if k == "Input":
             idx = [i for i, (_, nid) in enumerate(ins) if nid == n.id][0]
             expr = f"in{idx}[0]" if n.shape == () else f"in{idx}[i]"
-        elif k == "Constant": expr = f"{float(n.op.attr('value'))!r}f".replace("inff", "INFINITY")
+        elif k == "Constant": expr = f"{float(n.op.attr('value'))!r}f".replace("-inff", "__int_as_float(0xff800000)").replace("inff", "__int_as_float(0x7f800000)").replace("nanf", "__int_as_float(0x7fffffff)")
         elif k == "AddScalar": expr = f"({a[0]} + {float(n.op.attr('scalar'))!r}f)"
         elif k == "MulScalar": expr = f"({a[0]} * {float(n.op.attr('scalar'))!r}f)"
         elif k == "Output":

@@ -47,10 +47,10 @@ def _numel(shape) -> int:
 
 
 def _lit(x: float) -> str:
-    if math.isinf(x):
-        return "INFINITY" if x > 0 else "(-INFINITY)"
+    if math.isinf(x):       # NVRTC compiles without <cmath>: spell the bit patterns
+        return "__int_as_float(0x7f800000)" if x > 0 else "__int_as_float(0xff800000)"
     if math.isnan(x):
-        return "NAN"
+        return "__int_as_float(0x7fffffff)"
     return f"{float(x)!r}f"
 
 
@@ -210,7 +210,7 @@ class Plan:
                 body = "\n      ".join(kb.stmts)
                 params = ", ".join([f"const float* __restrict__ b{l}" for l in kb.leaves] + ["float* __restrict__ out"])
                 comb = "fmaxf(acc, {0})" if is_max else "(acc + {0})"
-                init = "-INFINITY" if is_max else "0.f"
+                init = "__int_as_float(0xff800000)" if is_max else "0.f"
                 scale = f" * {1.0 / red!r}f" if k in ("Mean", "MeanAxis") else ""
                 src.append(f"""
 extern "C" __global__ void __launch_bounds__({threads}) {name}({params}) {{

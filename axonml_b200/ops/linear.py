@@ -63,7 +63,10 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w, z = ctx.saved_tensors
+        x2, w, z = ctx.saved_tensors          # with activation checkpointing this recomputes the unit's forward
+        gate = getattr(w, "_axon_gate", None)
+        if gate is not None and gate.pending:
+            gate.fallback()                   # a sharded unit whose gather is still owed (no recomputation ran)
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()

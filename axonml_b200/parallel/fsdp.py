@@ -88,6 +88,7 @@ class _GatherGate:
     def __init__(self, engine, unit):
         self.engine, self.unit = engine, unit
         self.pending = False
+        self.linear_only = True      # every 2-D weight of the unit belongs to a Linear (which checks the gate)
 
     def usable(self, x2, w, act_needs_aux: bool) -> bool:
         return (self.pending and not act_needs_aux and x2.dtype == torch.bfloat16
@@ -135,7 +136,7 @@ class FullyShardedDataParallel(Module):
     def __init__(self, module: torch.nn.Module, process_group: ProcessGroup | None = None, *,
                  units: list | None = None, param_dtype: torch.dtype | None = None,
                  strategy: ShardingStrategy = ShardingStrategy.FullShard, device=None,
-                 fused_adamw: dict | None = None, gather: str = "auto"):
+                 fused_adamw: dict | None = None, fused_lamb: dict | None = None, gather: str = "auto"):
         super().__init__()
         self.module = module
         self.pg = process_group or ProcessGroup.mock()
@@ -152,7 +153,10 @@ class FullyShardedDataParallel(Module):
         self._built = False
         self._phase = "idle"
         self._sync = True
-        self._fused_hp = dict(fused_adamw) if fused_adamw else None
+        if fused_adamw and fused_lamb:
+            raise ValueError("give fused_adamw or fused_lamb, not both")
+        self._fused_hp = dict(fused_adamw or fused_lamb) if (fused_adamw or fused_lamb) else None
+        self._fused_kind = "lamb" if fused_lamb else "adamw"
         self._fused = None
         self._fused_step = 0
         self._fused_pending = False
@@ -296,6 +300,7 @@ class FullyShardedDataParallel(Module):
                 for sub in u.module.modules():
                     if isinstance(sub, _Linear) or not any(id(p) in own for p in sub.parameters(recurse=False)):
                         continue
+                    u.gate.linear_only = False
                     sub.register_forward_pre_hook(lambda m, a, g=u.gate: g.fallback() if g.pending else None)
 
         for u in self.block_units:
@@ -363,6 +368,8 @@ class FullyShardedDataParallel(Module):
                 for x in self.units:
                     x.m1 = torch.zeros(x.shard, dtype=torch.float32, device=self.device)
                     x.m2 = torch.zeros(x.shard, dtype=torch.float32, device=self.device)
+                    if self._fused_kind == "lamb":
+                        x.upd = torch.zeros(x.shard, dtype=torch.float32, device=self.device)
             else:
                 self._fused_hp = None
         if self._fused is not None:
@@ -371,9 +378,45 @@ class FullyShardedDataParallel(Module):
             return self._fused.arena.local[u.grad_off:u.grad_off + u.padded]
         return torch.zeros(u.padded, dtype=self.param_dtype, device=self.device)
 
+    def _lamb_tables(self, u: FlatUnit) -> None:
+        """Device tables for the fused LAMB kernel: where each tensor's slice starts inside this
+        rank's shard of the unit and which tensor it is; one [tensors, 2] accumulator for all units."""
+        if getattr(u, "seg_gid", None) is not None:
+            return
+        segs = [(gid, s, n) for gid, s, n in u.master._axon_segments if n > 0]
+        starts = [s for _, s, _ in segs] + [u.shard]
+        u.seg_start = torch.tensor(starts if segs else [0], dtype=torch.int64, device=self.device)
+        u.seg_gid = torch.tensor([g for g, _, _ in segs], dtype=torch.int32, device=self.device)
+        u.seg_list = segs
+        if getattr(self, "_lamb_norms", None) is None:
+            self._lamb_norms = torch.zeros(u.master._axon_num_tensors, 2, dtype=torch.float32, device=self.device)
+
+    def _lamb_phase2(self) -> None:
+        """Trust ratio per tensor from the sums of squares added over the ranks, then the update."""
+        from ..ops import optim as O
+        hp = self._fused_hp
+        if getattr(self, "_lamb_norms", None) is None:
+            return
+        norms = self._lamb_norms
+        if self.world > 1:
+            self.pg.backend().all_reduce(norms, ReduceOp.Sum)
+        ps, us, lps, gids = [], [], [], []
+        for u in self.units:
+            if getattr(u, "seg_list", None) is None or u.world == 1:
+                continue
+            w, lp = u.master.data, u.lp_shard
+            for gid, s0, n in u.seg_list:
+                ps.append(w[s0:s0 + n]); us.append(u.upd[s0:s0 + n]); lps.append(lp[s0:s0 + n]); gids.append(gid)
+        if ps:
+            rows = norms[torch.tensor(gids, dtype=torch.long, device=self.device)].contiguous()
+            O.multi_tensor("lamb2", ps, us, us, us, us, lp=lps, lr=hp["lr"], norms=rows)
+        norms.zero_()
+
     def fused_optimizer(self):
-        """Handle with the optimizer API for the in-backward fused AdamW (``step`` only advances
-        the step counter: the update itself runs inside backward, fused with the reduce-scatter)."""
+        """Handle with the optimizer API for the in-backward fused optimizer.  AdamW: ``step`` only
+        advances the step counter, the update itself runs inside backward, fused with the
+        reduce-scatter.  LAMB: backward runs the first phase inside the reduce-scatter kernel, ``step``
+        adds the per-tensor sums over the ranks and applies the trust-ratio update."""
         return _FusedOptimizerHandle(self)
 
     # ------------------------------------------------------------------ gather / release
@@ -435,8 +478,16 @@ class FullyShardedDataParallel(Module):
 
     def _pre_backward(self, u: FlatUnit) -> None:
         self._enter_backward()
-        if self._k4 and getattr(u, "gate", None) is not None:
-            u.gate.pending = False
+        if self._k4 and getattr(u, "gate", None) is not None and u.world > 1:
+            if u.gathered:
+                u.gate.pending = False
+                return
+            if u.gate.linear_only:
+                # With activation checkpointing the unit's forward is recomputed before any weight is
+                # read, and its first Linear gathers inside its kernel; without, the first Linear
+                # backward that finds the gate still pending gathers the plain way.
+                u.gate.pending = True
+                return
         self._gather(u)
         self._wait(u)
         prv = self._neighbor(u, -1)
@@ -493,9 +544,17 @@ class FullyShardedDataParallel(Module):
                 if self._comm is not None:
                     self._comm.wait_stream(torch.cuda.current_stream())
                 b1, b2 = hp.get("betas", (0.9, 0.999))
-                self._fused.step_unit(u.grad_off, u.shard, u.master.data, u.m1, u.m2, u.lp_shard,
-                                      lr=hp["lr"], beta1=b1, beta2=b2, eps=hp.get("eps", 1e-8),
-                                      wd=hp.get("weight_decay", 0.01), step=self._fused_step + 1)
+                if self._fused_kind == "lamb":
+                    self._lamb_tables(u)
+                    self._fused.step_unit_lamb1(u.grad_off, u.shard, u.master.data, u.m1, u.m2, u.upd, u.seg_start,
+                                                u.seg_gid, self._lamb_norms, beta1=b1, beta2=b2,
+                                                eps=hp.get("eps", 1e-6), wd=hp.get("weight_decay", 0.0),
+                                                step=self._fused_step + 1,
+                                                bias_correction=hp.get("bias_correction", True))
+                else:
+                    self._fused.step_unit(u.grad_off, u.shard, u.master.data, u.m1, u.m2, u.lp_shard,
+                                          lr=hp["lr"], beta1=b1, beta2=b2, eps=hp.get("eps", 1e-8),
+                                          wd=hp.get("weight_decay", 0.01), step=self._fused_step + 1)
         else:
             with self._stream_ctx():
                 if self._comm is not None:
@@ -684,6 +743,8 @@ class _FusedOptimizerHandle:
         self.engine = engine
 
     def step(self) -> None:
+        if self.engine._fused_kind == "lamb" and self.engine._fused is not None:
+            self.engine._lamb_phase2()
         self.engine._fused_step += 1
         self.engine._fused_pending = False
 

@@ -1,8 +1,9 @@
 """Python drivers of the fused compute+collective kernels (``csrc/kernels/comm.cu``).
 
 * ``FusedAllReduce``    - DDP bucket mean all-reduce + GradScaler unscale + found-inf, one kernel.
-* ``FusedShardedAdamW`` - FSDP reduce-scatter + sharded AdamW (+ push of the updated bf16 shard
-  into every rank's resident parameter buffer), one kernel per flat unit.
+* ``FusedShardedAdamW`` - FSDP reduce-scatter + sharded AdamW, one kernel per flat unit; or, for LAMB,
+  reduce-scatter + the first LAMB phase (moments, update, per-tensor sums of squares), the second
+  phase following once the sums of all units have been added over the ranks.
 
 Both keep their operands in symmetric memory: DDP allocates its gradient buckets inside the
 all-reduce's symmetric arena, so a bucket is reduced in place (a tensor from elsewhere is staged
@@ -103,3 +104,18 @@ class FusedShardedAdamW:
             ctypes.c_uint(self.comm.next_epoch()), self.comm.grid, N.ptr(N.status_word(master.device)),
             N.stream_ptr())
         N.check(rc, "ax_fused_rs_adamw")
+
+    def step_unit_lamb1(self, grad_off_elems: int, shard: int, master, m1, m2, upd, seg_start, seg_gid, norms, *,
+                        beta1, beta2, eps, wd, step: int, bias_correction: bool = True, skip_flag=None) -> None:
+        """Reduce-scatter of one unit's flat gradient fused with the first LAMB phase (moments, the
+        per-element update into ``upd``, this shard's share of the per-tensor sums of squares into
+        ``norms``)."""
+        bc1 = 1 - beta1 ** step if bias_correction else 1.0
+        bc2 = 1 - beta2 ** step if bias_correction else 1.0
+        hyper = (ctypes.c_float * 7)(0.0, beta1, beta2, eps, wd, bc1, bc2)
+        rc = N.cuda().ax_fused_rs_lamb1(
+            self.arena.ptr_array(), self.comm.signals.ptr_array(), self.arena.mc(), self.heap.rank, self.heap.world,
+            ctypes.c_long(grad_off_elems * 2), ctypes.c_long(shard), N.ptr(master), N.ptr(m1), N.ptr(m2), N.ptr(upd),
+            N.ptr(seg_start), N.ptr(seg_gid), int(seg_gid.numel()), N.ptr(norms), hyper, N.ptr(skip_flag),
+            ctypes.c_uint(self.comm.next_epoch()), self.comm.grid, N.ptr(N.status_word(master.device)), N.stream_ptr())
+        N.check(rc, "ax_fused_rs_lamb1")

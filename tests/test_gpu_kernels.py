@@ -745,3 +745,47 @@ def test_jit_split_reduction_over_a_large_tensor(kernel_status):
     out = jit.JitCompiler.new().compile(g).run_tensors({"x": x})
     assert abs(out["s"].item() - (x.double() ** 2).sum().item()) < 1e-3 * (1 << 20) ** 0.5 * 4
     assert abs(out["m"].item() - x.abs().double().mean().item()) < 1e-4
+
+
+def test_bounds_checked_build_reports_a_wrong_index_instead_of_using_it():
+    """The debug build of the kernel library (``AXONML_BOUNDS=1``): its self-test walks one element
+    past an extent through the checked accessor, which skips the access and records where and which
+    index; a token id outside the embedding table and a class index outside the vocabulary are
+    reported the same way; correct calls leave the record empty and give the usual results."""
+    import os
+    import subprocess
+    import sys
+    prog = r'''
+import ctypes, torch
+from axonml_b200 import _native as N
+assert N.bounds_build() and N.cuda().ax_bounds_enabled() == 1
+assert N.bounds_report() is None
+buf = torch.zeros(1000 + 64, device="cuda")
+assert N.cuda().ax_bounds_selftest(N.ptr(buf), ctypes.c_long(1000), N.stream_ptr()) == 0
+r = N.bounds_report()
+assert r == {"code": 4, "where": 9000, "index": 1000, "extent": 1000}, r
+assert bool((buf[:1000] == 1).all()) and bool((buf[1000:] == 0).all())      # the stray access was skipped
+assert N.bounds_report() is None                                            # reading clears the record
+# correct calls: no record, right values
+from axonml_b200.ops import elementwise as E
+from axonml_b200.ops.gemm import gemm_bf16, sgemm_f32
+x = torch.randn(4099, device="cuda")
+assert torch.allclose(E.unary(x, "relu"), torch.relu(x))
+a, b = torch.randn(300, 256, device="cuda").bfloat16(), torch.randn(512, 256, device="cuda").bfloat16()
+assert (gemm_bf16(a, b).float() - a.float() @ b.float().t()).abs().max().item() < 0.5
+af, bf = torch.randn(70, 33, device="cuda"), torch.randn(33, 90, device="cuda")
+assert torch.allclose(sgemm_f32(af, bf), af @ bf, atol=1e-4)
+assert N.bounds_report() is None
+# a token id outside the table: reported, and the row comes back as zeros
+from axonml_b200 import nn
+emb = nn.Embedding(10, 8).cuda()
+out = emb(torch.tensor([[1, 12, 3]], device="cuda"))
+r = N.bounds_report()
+assert r is not None and r["where"] == 2000 and r["index"] == 12 and r["extent"] == 10, r
+assert bool((out[0, 1] == 0).all())
+print("BOUNDS-OK")
+'''
+    env = dict(os.environ, AXONML_BOUNDS="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", prog], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "BOUNDS-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]

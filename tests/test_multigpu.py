@@ -106,7 +106,7 @@ def test_fsdp_fused_rs_adamw_matches_nccl_path(nvls):
     for r in range(WORLD):
         l1, l2, diff, mean = res[r][1]
         assert abs(l1[-1] - l2[-1]) < 5e-2, (l1, l2)
-        assert diff < 1e-2 and mean < 1e-4, (diff, mean)
+        assert diff < 1e-2 and mean < 5e-4, (diff, mean)
 
 
 def _fsdp_fused_gather(rank, world, be):
@@ -151,7 +151,9 @@ def test_fsdp_gather_inside_the_first_gemm_matches_nccl_gathers(nvls):
     res = run_gpu_ranks(_fsdp_fused_gather, WORLD, env={"AXONML_NVLS": nvls})
     for r in range(WORLD):
         l1, l2, mean, n1, n2 = res[r][1]
-        assert n1 == 0 and n2 == 3 * 5 * 2, (n1, n2)          # forward and recomputation of 5 units, 3 steps
+        # per step: the forward of 5 units, and the recomputation of the 2 units whose rotating buffer
+        # was taken over by a later unit (the last 3 are still resident when backward reaches them)
+        assert n1 == 0 and n2 == 3 * (5 + 2), (n1, n2)
         assert max(abs(a - b) for a, b in zip(l1, l2)) < 3e-2, (l1, l2)
         assert mean < 1e-4, mean
 
@@ -197,6 +199,54 @@ def test_fsdp_lamb_trust_ratio_per_tensor_across_shards():
         # a ratio taken per shard would move whole tensors by ~1e-3; single elements may still
         # differ by 2 * lr * trust where a gradient's sign is decided by the reduction order
         assert mean < 2e-5 and worst < 5e-2, (mean, worst)
+
+
+def _fsdp_fused_lamb(rank, world, be):
+    """LAMB with its first phase inside the reduce-scatter kernel against LAMB stepped on the
+    shards after an NCCL reduce-scatter (both take trust ratios per tensor across the shards)."""
+    import copy
+    from axonml_b200 import _native, optim
+    from axonml_b200.llm import GPT2Config, GPT2LMHead
+    from axonml_b200.parallel import FSDP, ProcessGroup
+    torch.manual_seed(0)
+    cfg = GPT2Config(vocab_size=512, n_ctx=128, n_embd=256, n_layer=4, n_head=2, dropout=0.0,
+                     attn_dropout=0.0, resid_dropout=0.0)
+    base = GPT2LMHead(cfg, device="cuda", dtype=torch.bfloat16)
+    m1, m2 = copy.deepcopy(base), copy.deepcopy(base)
+    pg = ProcessGroup(be)
+    hp = dict(lr=2e-3, betas=(0.9, 0.999), eps=1e-6, weight_decay=0.01)
+    f1 = FSDP(m1, pg)
+    o1 = optim.LAMB(f1.parameters(), hp["lr"], betas=hp["betas"], eps=hp["eps"], weight_decay=hp["weight_decay"])
+    f2 = FSDP(m2, pg, fused_lamb=hp)
+    assert f2._fused is not None and f2._fused_kind == "lamb"
+    o2 = f2.fused_optimizer()
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 512, (3, 2 * world, 128), generator=g).cuda()
+    l1s, l2s = [], []
+    for it in range(3):
+        x = ids[it].chunk(world)[rank]
+        for f, o, ls in ((f1, o1, l1s), (f2, o2, l2s)):
+            loss, _ = f.call("forward_with_loss", x)
+            loss.backward()
+            o.step()
+            f.zero_grad()
+            ls.append(loss.item())
+    torch.cuda.synchronize()
+    _native.check_status()
+    sd1, sd2 = f1.full_state_dict(), f2.full_state_dict()
+    mean = sum((sd1[k] - sd2[k]).abs().sum().item() for k in sd1) / sum(v.numel() for v in sd1.values())
+    moved = sum((sd1[k] - base.state_dict()[k].float()).abs().sum().item() for k in sd1) / sum(v.numel() for v in sd1.values())
+    return l1s, l2s, mean, moved
+
+
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fsdp_lamb_first_phase_inside_the_reduce_scatter_kernel(nvls):
+    res = run_gpu_ranks(_fsdp_fused_lamb, WORLD, env={"AXONML_NVLS": nvls})
+    for r in range(WORLD):
+        l1, l2, mean, moved = res[r][1]
+        assert max(abs(a - b) for a, b in zip(l1, l2)) < 5e-2, (l1, l2)
+        # the two runs differ by far less than the three steps moved the parameters
+        assert moved > 1e-5 and mean < 0.2 * moved, (mean, moved)
 
 
 def _ulysses_gpu(rank, world, be):
