@@ -130,10 +130,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // mbarrier.try_wait may carry a hint of how long (ns) the hardware may keep the waiting thread
-// suspended before it returns.  0 compiles the plain form, which returns after the hardware's own
-// short limit; the loop around it then polls again.
+// suspended before it returns; the thread wakes when the phase completes.  0 compiles the plain
+// form, which returns after the hardware's own short limit so that the loop around it polls more
+// often.  Measured both ways on one B200: the flash kernels gain 2 % from the plain form, the
+// 8192^3 GEMM loses 4 % (the polling takes issue slots from the warps that work).
 #ifndef AX_SUSPEND_HINT_NS
-#define AX_SUSPEND_HINT_NS 0
+#define AX_SUSPEND_HINT_NS 20000
 #endif
 constexpr uint32_t kSuspendHintNs = AX_SUSPEND_HINT_NS;
 
