@@ -1,6 +1,7 @@
 // LayerNorm / RMSNorm forward and backward, bf16 or fp32 activations, fp32 statistics.
-// One warp per row; rows are read twice (the second read is served by L1/L2), so HBM traffic is
-// one read of x and one write of y.  The optional residual input fuses `h = x + r` (h is written
+// One warp per row.  bf16 rows up to 8192 wide are read once and kept in registers (packed) between
+// the statistics and the normalisation; other rows are read twice (the second read is served by
+// L1/L2), so HBM traffic is one read of x and one write of y either way.  The optional residual input fuses `h = x + r` (h is written
 // out as the new residual stream) with the normalisation of h.
 //
 // Backward: per-row dx in one pass; weight/bias gradients are accumulated per CTA in shared
@@ -112,6 +113,114 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const WT* __
       Vec8<T>::store(yr + c, v);
     }
   }
+}
+
+// Many rows of bf16 with D <= 256 * NV: one warp per row, the row read ONCE and kept in registers as
+// the packed bf16 it arrived as (4 registers per 8 values, so even D = 8192 fits), all loads of a
+// row in flight together; the statistics and the normalisation both unpack from the registers.
+// For NV <= 8 the weight (and bias) vectors of the lane's columns are loaded once per warp and
+// reused for every row the warp handles.
+template <typename WT, bool RMS, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+norm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res, const WT* __restrict__ w,
+                    const WT* __restrict__ b, __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ hout,
+                    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int D, float eps) {
+  using T = __nv_bfloat16;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  constexpr bool kKeepW = NV <= 8;
+  float wreg[kKeepW ? NV : 1][8], breg[kKeepW ? NV : 1][8];
+  if (kKeepW) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < D) {
+        Vec8<WT>::load(w + c, wreg[i]);
+        if (b) Vec8<WT>::load(b + c, breg[i]);
+      }
+    }
+  }
+  for (long row = (long)blockIdx.x * kWarpsPerCta + warp; row < rows; row += (long)gridDim.x * kWarpsPerCta) {
+    const T* xr = x + row * D;
+    const T* rr = res ? res + row * D : nullptr;
+    T* hr = hout ? hout + row * D : nullptr;
+    uint4 xv[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < D) xv[i] = *reinterpret_cast<const uint4*>(xr + c);
+    }
+    if (rr) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane * 8 + i * 256;
+        if (c < D) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(rr + c);
+          const float2 a0 = unpack_bf16x2(xv[i].x), a1 = unpack_bf16x2(xv[i].y), a2 = unpack_bf16x2(xv[i].z), a3 = unpack_bf16x2(xv[i].w);
+          const float2 r0 = unpack_bf16x2(rv.x), r1 = unpack_bf16x2(rv.y), r2 = unpack_bf16x2(rv.z), r3 = unpack_bf16x2(rv.w);
+          // h = x + r rounded to the storage type: the statistics are those of what backward re-reads
+          xv[i].x = pack_bf16x2(a0.x + r0.x, a0.y + r0.y); xv[i].y = pack_bf16x2(a1.x + r1.x, a1.y + r1.y);
+          xv[i].z = pack_bf16x2(a2.x + r2.x, a2.y + r2.y); xv[i].w = pack_bf16x2(a3.x + r3.x, a3.y + r3.y);
+          if (hr) *reinterpret_cast<uint4*>(hr + c) = xv[i];
+        }
+      }
+    }
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < D) {
+        const float2 a0 = unpack_bf16x2(xv[i].x), a1 = unpack_bf16x2(xv[i].y), a2 = unpack_bf16x2(xv[i].z), a3 = unpack_bf16x2(xv[i].w);
+        s += (a0.x + a0.y) + (a1.x + a1.y) + (a2.x + a2.y) + (a3.x + a3.y);
+        ss += (a0.x * a0.x + a0.y * a0.y) + (a1.x * a1.x + a1.y * a1.y) + (a2.x * a2.x + a2.y * a2.y) + (a3.x * a3.x + a3.y * a3.y);
+      }
+    }
+    s = warp_sum(s);
+    ss = warp_sum(ss);
+    const float mean = RMS ? 0.f : s / D;
+    const float var = RMS ? ss / D : fmaxf(ss / D - mean * mean, 0.f);
+    const float rstd = rsqrtf(var + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    T* yr = y + row * D;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane * 8 + i * 256;
+      if (c < D) {
+        float v[8], wv[8], bv[8];
+        const float2 a0 = unpack_bf16x2(xv[i].x), a1 = unpack_bf16x2(xv[i].y), a2 = unpack_bf16x2(xv[i].z), a3 = unpack_bf16x2(xv[i].w);
+        v[0] = a0.x; v[1] = a0.y; v[2] = a1.x; v[3] = a1.y; v[4] = a2.x; v[5] = a2.y; v[6] = a3.x; v[7] = a3.y;
+        if (!kKeepW) {
+          Vec8<WT>::load(w + c, wv);
+          if (b) Vec8<WT>::load(b + c, bv);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float o = (v[j] - mean) * rstd * (kKeepW ? wreg[i][j] : wv[j]);
+          v[j] = b ? o + (kKeepW ? breg[i][j] : bv[j]) : o;
+        }
+        Vec8<T>::store(yr + c, v);
+      }
+    }
+  }
+}
+
+template <typename WT, int NV>
+int launch_fwd_reg(bool rms, const void* x, const void* res, const void* w, const void* b, void* y, void* hout,
+                   float* mean, float* rstd, int rows, int D, float eps, cudaStream_t stream) {
+  int grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int cap = axh::sm_count() * (NV <= 8 ? 8 : 4);
+  if (grid > cap) grid = cap;
+  using T = __nv_bfloat16;
+  if (rms)
+    norm_fwd_reg_kernel<WT, true, NV><<<grid, kWarpsPerCta * 32, 0, stream>>>((const T*)x, (const T*)res, (const WT*)w,
+                                                                         (const WT*)b, (T*)y, (T*)hout, mean, rstd, rows, D, eps);
+  else
+    norm_fwd_reg_kernel<WT, false, NV><<<grid, kWarpsPerCta * 32, 0, stream>>>((const T*)x, (const T*)res, (const WT*)w,
+                                                                          (const WT*)b, (T*)y, (T*)hout, mean, rstd, rows, D, eps);
+  return (int)cudaGetLastError();
 }
 
 // Few rows (decode steps, small batches): one CTA per row, the row held in registers between
@@ -383,6 +492,13 @@ int launch_fwd(bool rms, const void* x, const void* res, const void* w, const vo
       norm_fwd_block_kernel<T, WT, false><<<rows, kWarpsPerCta * 32, 0, stream>>>(
           (const T*)x, (const T*)res, (const WT*)w, (const WT*)b, (T*)y, (T*)hout, mean, rstd, D, eps);
     return (int)cudaGetLastError();
+  }
+  if (sizeof(T) == 2 && D <= 8192 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)res | (uintptr_t)hout | (uintptr_t)w | (uintptr_t)b) & 15) == 0) {
+    // bf16 rows that fit the register file: single pass
+    if (D <= 1024) return launch_fwd_reg<WT, 4>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
+    if (D <= 2048) return launch_fwd_reg<WT, 8>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
+    if (D <= 4096) return launch_fwd_reg<WT, 16>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
+    return launch_fwd_reg<WT, 32>(rms, x, res, w, b, y, hout, mean, rstd, rows, D, eps, stream);
   }
   int grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
   int cap = axh::sm_count() * 8;

@@ -168,6 +168,22 @@ ce_fwd_kernel(const T* __restrict__ logits, const long* __restrict__ target,
   }
 }
 
+// stats[row] = {row max, sum exp(x - max), x[target] if 0 <= target < V else 0, unused}
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+vp_ce_stats_kernel(const T* __restrict__ logits, const long* __restrict__ target, float* __restrict__ stats,
+                   int V, long stride) {
+  const T* row = logits + (long)blockIdx.x * stride;
+  float m = -INFINITY, s = 0.f;
+  if (V > 0) row_max_sum(row, V, m, s);
+  if (threadIdx.x == 0) {
+    const long t = target[blockIdx.x];
+    float4 o;
+    o.x = m; o.y = s; o.z = (t >= 0 && t < V) ? ldf(row, t) : 0.f; o.w = 0.f;
+    *reinterpret_cast<float4*>(stats + (long)blockIdx.x * 4) = o;
+  }
+}
+
 // dlogits = (softmax - onehot) * gscale[row or 0]; columns in [V, stride_cols) are zeroed so
 // that a padded vocabulary contributes nothing to the following GEMMs.
 template <typename T>
@@ -175,11 +191,14 @@ __global__ void __launch_bounds__(kThreads)
 ce_bwd_kernel(const T* __restrict__ logits, const long* __restrict__ target,
               const float* __restrict__ lse, const float* __restrict__ gscale, int gscale_per_row,
               float gmul, T* __restrict__ dlogits, int V, int Vpad, long stride,
-              long ignore_index) {
+              long ignore_index, int partial) {
   const T* row = logits + (long)blockIdx.x * stride;
   T* out = dlogits + (long)blockIdx.x * stride;
   const long t = target[blockIdx.x];
-  const bool ignored = (t == ignore_index || t < 0 || t >= V);
+  // `partial`: the row is one rank's slice of a vocabulary split over ranks and `lse` is the
+  // log-sum-exp over the whole vocabulary; a target outside [0, V) then lives on another rank, so
+  // the row still gets its softmax share and only the one-hot term is missing
+  const bool ignored = partial ? (t == ignore_index) : (t == ignore_index || t < 0 || t >= V);
   const float g = ignored ? 0.f : gmul * (gscale ? gscale[gscale_per_row ? blockIdx.x : 0] : 1.f);
   const float l = lse[blockIdx.x];
   constexpr int kVec = 16 / (int)sizeof(T);
@@ -295,11 +314,41 @@ AX_API int ax_ce_bwd(int dtype, const void* logits, const long* target, const fl
   if (dtype == 1)
     ce_bwd_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>(
         (const __nv_bfloat16*)logits, target, lse, gscale, gscale_per_row, gmul,
-        (__nv_bfloat16*)dlogits, V, Vpad, stride, ignore_index);
+        (__nv_bfloat16*)dlogits, V, Vpad, stride, ignore_index, 0);
   else
     ce_bwd_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, target, lse, gscale,
                                                         gscale_per_row, gmul, (float*)dlogits, V,
-                                                        Vpad, stride, ignore_index);
+                                                        Vpad, stride, ignore_index, 0);
+  return (int)cudaGetLastError();
+}
+
+// Vocabulary-parallel cross-entropy, this rank's part (the class dimension of the logits is split
+// over the ranks of a tensor-parallel group):
+//  stats: per row {max, sum exp(x - max), logit of the target or 0} over this rank's V columns; the
+//         target index is relative to this rank's first column, outside [0, V) = not on this rank.
+//         The caller combines the rows' statistics over the ranks (one small collective).
+//  bwd:   dlogits = (exp(x - lse) - onehot) * scale with the log-sum-exp over the WHOLE vocabulary
+//         and the one-hot term only where the target is on this rank.
+AX_API int ax_vp_ce_stats(int dtype, const void* logits, const long* local_target, float* stats, int rows, int V,
+                          long stride, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype == 1)
+    vp_ce_stats_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>((const __nv_bfloat16*)logits, local_target, stats, V, stride);
+  else
+    vp_ce_stats_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, local_target, stats, V, stride);
+  return (int)cudaGetLastError();
+}
+
+AX_API int ax_vp_ce_bwd(int dtype, const void* logits, const long* local_target, const float* lse,
+                        const float* gscale, float gmul, void* dlogits, int rows, int V, int Vpad, long stride,
+                        long ignore_index, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype == 1)
+    ce_bwd_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>((const __nv_bfloat16*)logits, local_target, lse, gscale, 0, gmul,
+                                                                 (__nv_bfloat16*)dlogits, V, Vpad, stride, ignore_index, 1);
+  else
+    ce_bwd_kernel<float><<<rows, kThreads, 0, stream>>>((const float*)logits, local_target, lse, gscale, 0, gmul,
+                                                        (float*)dlogits, V, Vpad, stride, ignore_index, 1);
   return (int)cudaGetLastError();
 }
 

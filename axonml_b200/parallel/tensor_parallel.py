@@ -215,9 +215,18 @@ class VocabParallelEmbedding(Module):
         return reduce_from_tensor_parallel(out, self.pg)
 
 
+def _vp_kernel_ok(logits) -> bool:
+    from .. import _native as N
+    return (logits.is_cuda and N.have_gpu() and logits.dtype in (torch.bfloat16, torch.float32)
+            and logits.dim() == 2 and logits.stride(1) == 1)
+
+
 class _VocabParallelCE(torch.autograd.Function):
-    """Mean cross-entropy from a vocabulary slice of the logits.  Rows are processed in chunks so
-    that the fp32 temporaries stay small next to the (large) bf16 logits."""
+    """Mean cross-entropy from a vocabulary slice of the logits.  On a GPU two kernels of
+    ``csrc/kernels/softmax_ce.cu`` do the work (per-row max / sum-exp / target logit of the slice,
+    then (softmax - onehot) * scale in place of the logits' gradient) around ONE small all-gather of
+    the row statistics; elsewhere rows are processed in chunks of torch ops so that the fp32
+    temporaries stay small next to the (large) bf16 logits."""
 
     CHUNK = 4096
 
@@ -226,6 +235,34 @@ class _VocabParallelCE(torch.autograd.Function):
         T, V = logits.shape
         dev = logits.device
         n_valid_cols = V if valid_vocab is None else max(0, min(V, valid_vocab - vocab_start))
+        ctx.kernel = _vp_kernel_ok(logits)
+        if ctx.kernel:
+            from .. import _native as N
+            local_t = (target - vocab_start).contiguous()
+            # targets on another rank get a negative marker; rows to ignore keep ignore_index
+            off = -1 if ignore_index != -1 else -2
+            local_t = torch.where((local_t >= 0) & (local_t < n_valid_cols), local_t, torch.full_like(local_t, off))
+            valid = target != ignore_index
+            local_t = torch.where(valid, local_t, torch.full_like(local_t, ignore_index)).contiguous()
+            stats = torch.empty(T, 4, dtype=torch.float32, device=dev)
+            N.check(N.cuda().ax_vp_ce_stats(1 if logits.dtype == torch.bfloat16 else 0, N.ptr(logits), N.ptr(local_t),
+                                            N.ptr(stats), T, n_valid_cols, N.c_int64(logits.stride(0)), N.stream_ptr()),
+                    "ax_vp_ce_stats")
+            W = pg.world_size()
+            if W > 1:
+                allst = torch.empty(W, T, 4, dtype=torch.float32, device=dev)
+                pg.backend().all_gather(stats, allst)
+            else:
+                allst = stats.unsqueeze(0)
+            m = allst[..., 0].max(dim=0).values
+            s = (allst[..., 1] * (allst[..., 0] - m).exp()).sum(0)
+            picked = allst[..., 2].sum(0)
+            lse = m + s.log()
+            count = valid.sum().clamp_min(1).float()
+            loss = torch.where(valid, lse - picked, torch.zeros_like(lse)).sum() / count
+            ctx.save_for_backward(logits, lse.contiguous(), local_t, count)
+            ctx.n_valid_cols, ctx.ignore_index = n_valid_cols, ignore_index
+            return loss
         m = torch.empty(T, dtype=torch.float32, device=dev)
         for i in range(0, T, _VocabParallelCE.CHUNK):
             blk = logits[i:i + _VocabParallelCE.CHUNK, :n_valid_cols]
@@ -257,6 +294,17 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
+        if ctx.kernel:
+            from .. import _native as N
+            logits, lse, local_t, count = ctx.saved_tensors
+            T, V = logits.shape
+            grad = torch.empty_like(logits)
+            scale = (g / count).float().reshape(1).contiguous()
+            N.check(N.cuda().ax_vp_ce_bwd(1 if logits.dtype == torch.bfloat16 else 0, N.ptr(logits), N.ptr(local_t),
+                                          N.ptr(lse), N.ptr(scale), N.c_float(1.0), N.ptr(grad), T, ctx.n_valid_cols, V,
+                                          N.c_int64(logits.stride(0)), N.c_int64(ctx.ignore_index), N.stream_ptr()),
+                    "ax_vp_ce_bwd")
+            return grad, None, None, None, None, None
         logits, lse, local_t, hit, valid, count = ctx.saved_tensors
         T, V = logits.shape
         nv = ctx.n_valid_cols

@@ -789,3 +789,78 @@ print("BOUNDS-OK")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", prog], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "BOUNDS-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.parametrize("rows,D", [(3000, 264), (1500, 1000), (4096, 2048), (2000, 4096), (1200, 5120), (700, 8192)])
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("with_res", [False, True])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_norm_forward_single_pass_widths(rows, D, rms, with_res, wdtype):
+    """Many bf16 rows take the forward that keeps a row in registers: every width class (ragged
+    last vector included), both norms, with and without the fused residual add, bf16 and fp32
+    weights, against fp32 torch maths; the saved statistics too."""
+    from axonml_b200 import _native as N
+    x = torch.randn(rows, D, device=DEV).bfloat16()
+    r = torch.randn(rows, D, device=DEV).bfloat16() if with_res else None
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(wdtype)
+    b = None if rms else (0.1 * torch.randn(D, device=DEV)).to(wdtype)
+    y, h = torch.empty_like(x), (torch.empty_like(x) if with_res else None)
+    mean, rstd = torch.empty(rows, device=DEV), torch.empty(rows, device=DEV)
+    rc = N.cuda().ax_norm_fwd(int(rms), 1, 1 if wdtype == torch.bfloat16 else 0, N.ptr(x), N.ptr(r), N.ptr(w), N.ptr(b),
+                              N.ptr(y), N.ptr(h), N.ptr(mean), N.ptr(rstd), rows, D, N.c_float(1e-5), N.stream_ptr())
+    assert rc == 0
+    hf = (x.float() + r.float()).bfloat16().float() if with_res else x.float()
+    if rms:
+        ref = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+        close(rstd, torch.rsqrt(hf.pow(2).mean(-1) + 1e-5), 1e-3, 1e-3)
+    else:
+        ref = F.layer_norm(hf, (D,), w.float(), b.float(), 1e-5)
+        close(mean, hf.mean(-1), 1e-3, 1e-3)
+        close(rstd, torch.rsqrt(hf.var(-1, unbiased=False) + 1e-5), 1e-3, 1e-3)
+    close(y, ref, 3e-2, 2e-2)
+    if with_res:
+        assert torch.equal(h.float(), hf)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_vocab_parallel_cross_entropy_kernels_on_two_slices(dtype, kernel_status):
+    """The vocabulary-parallel loss kernels, with the two ranks' slices evaluated one after the other
+    on one GPU: statistics per slice, combined as the collective would, equal the loss over the
+    whole vocabulary; the backward of each slice with the global log-sum-exp gives the slices of
+    the full gradient.  Ignored rows, a padded last slice and targets on either slice included."""
+    from axonml_b200 import _native as N
+    T, V0, V1, pad = 300, 1000, 920, 8          # second slice: 920 real classes in 928 columns
+    V = V0 + V1
+    logits = torch.randn(T, V0 + V1 + pad, device=DEV).to(dtype)
+    target = torch.randint(0, V, (T,), device=DEV)
+    target[::17] = -100
+    ref_in = logits[:, :V].float().requires_grad_()
+    ref = F.cross_entropy(ref_in, target, ignore_index=-100)
+    ref.backward()
+    code = 1 if dtype == torch.bfloat16 else 0
+    slices = [(logits[:, :V0].contiguous(), 0, V0, V0), (logits[:, V0:].contiguous(), V0, V1, V1 + pad)]
+    stats, locals_ = [], []
+    for sl, start, nvalid, width in slices:
+        lt = target - start
+        lt = torch.where((lt >= 0) & (lt < nvalid), lt, torch.full_like(lt, -1))
+        lt = torch.where(target != -100, lt, torch.full_like(lt, -100)).contiguous()
+        st = torch.empty(T, 4, device=DEV)
+        assert N.cuda().ax_vp_ce_stats(code, N.ptr(sl), N.ptr(lt), N.ptr(st), T, nvalid, N.c_int64(sl.stride(0)), N.stream_ptr()) == 0
+        stats.append(st); locals_.append(lt)
+    allst = torch.stack(stats)
+    m = allst[..., 0].max(0).values
+    lse = (m + (allst[..., 1] * (allst[..., 0] - m).exp()).sum(0).log()).contiguous()
+    valid = target != -100
+    loss = torch.where(valid, lse - allst[..., 2].sum(0), torch.zeros_like(lse)).sum() / valid.sum()
+    assert abs(loss.item() - ref.item()) < (1e-4 if dtype == torch.float32 else 2e-2)
+    scale = (1.0 / valid.sum().float()).reshape(1).contiguous()
+    grads = []
+    for (sl, start, nvalid, width), lt in zip(slices, locals_):
+        g = torch.full_like(sl, 7.0)
+        assert N.cuda().ax_vp_ce_bwd(code, N.ptr(sl), N.ptr(lt), N.ptr(lse), N.ptr(scale), N.c_float(1.0), N.ptr(g), T, nvalid,
+                                     width, N.c_int64(sl.stride(0)), N.c_int64(-100), N.stream_ptr()) == 0
+        grads.append(g)
+    full = torch.cat(grads, 1)
+    tol = 1e-6 if dtype == torch.float32 else 2e-4
+    close(full[:, :V], ref_in.grad, tol, 2e-2)
+    assert bool((full[:, V:] == 0).all())                       # padded columns get a zero gradient
