@@ -1,6 +1,6 @@
-// Implicit-GEMM 2-D convolution (stride 1, NHWC bf16, fp32 accumulation) on tcgen05:
+// Implicit-GEMM 2-D convolution (NHWC bf16, fp32 accumulation) on tcgen05:
 //
-//     y[n, ho, wo, co] = act(bias[co] + sum_{r,s,ci} x[n, ho + r - ph, wo + s - pw, ci] * w[co, r, s, ci])
+//     y[n, ho, wo, co] = act(bias[co] + sum_{r,s,ci} x[n, sh*ho + r - ph, sw*wo + s - pw, ci] * w[co, r, s, ci])
 //
 // No im2col matrix is materialised.  A GEMM row is an output pixel; a tile of 128 rows is a
 // TN x TH x TW box of pixels, so for filter tap (r, s) and a block of 64 input channels the A
@@ -12,8 +12,19 @@
 // taps x channel blocks.  The epilogue (bias, optional ReLU) stores each warp's 32 pixels x 64
 // channels with one 4-D TMA store, which also clips ragged tiles.
 //
-// The data gradient of a stride-1 convolution is the same kernel on the output gradient with the
-// filter flipped and its channel dims exchanged and padding k-1-p.
+// Strides.  For one filter tap the rows sh*ho + r - ph all have the same remainder a modulo sh, so
+// they are consecutive rows of the "parity view" a of the input: the tensor map whose base is row a
+// and whose row stride is sh rows.  A strided convolution therefore needs sh*sw tensor maps over
+// the same memory and a table that gives, per tap, its view and its (dh, dw) shift inside the view;
+// the loads stay plain boxes and the out-of-range fill still provides the padding.  The kernel only
+// sees the table, so the same code runs
+//   * the forward of any stride,
+//   * the data gradient of a stride-1 convolution (output gradient as input, filter rotated by 180
+//     degrees with its channel dims exchanged, padding k-1-p),
+//   * the data gradient of a strided convolution, one launch per parity class (a, b) of the INPUT
+//     pixels: dx[sh*i + a, sw*j + b] only receives the taps with r = a + ph (mod sh), s = b + pw (mod sw),
+//     a stride-1 problem over dy whose result is stored through a parity view of dx.  No tap is
+//     computed that the strided forward did not have (no zero-insertion).
 //
 // Replaces the reference's 7-deep scalar loop (crates/axonml-nn/src/layers/conv.rs:256-337) and
 // its WGSL direct-convolution shader (crates/axonml-core/src/backends/wgpu_backend.rs:1364-1427).
@@ -29,9 +40,15 @@ constexpr int kThreads = 192;
 constexpr int kEpiWarps = 4;
 constexpr int kStageBufBytes = 32 * 128;
 
+constexpr int kMaxTaps = 64;
+
+struct XMaps { CUtensorMap m[4]; };     // parity views of the input (one for stride 1)
+
 struct ConvParams {
-  int N, H, W, Cin, Cout, Ho, Wo;
-  int kh, kw, ph, pw;
+  int N, Cin, Cout, Ho, Wo;               // Ho, Wo: extents of the output view this launch writes
+  int ntaps;
+  int8_t tap_map[kMaxTaps], tap_dh[kMaxTaps], tap_dw[kMaxTaps];
+  uint8_t tap_wcol[kMaxTaps];             // the tap's column block in the filter matrix [Cout, taps * Cin]
   int TN, TH, TW;          // pixel box of a tile, TN*TH*TW == 128
   int bw, bh, bn;          // pixel box of one epilogue warp, bw*bh*bn == 32
   const void* bias;
@@ -60,8 +77,8 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void*
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                  const __grid_constant__ CUtensorMap map_y, const ConvParams p) {
+conv_fprop_kernel(const __grid_constant__ XMaps maps_x, const __grid_constant__ CUtensorMap map_w,
+                  const __grid_constant__ CUtensorMap map_y, const __grid_constant__ ConvParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -84,7 +101,7 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const int tiles_c = (p.Cout + BN - 1) / BN;
   const int num_tiles = tiles_w * tiles_h * tiles_n * tiles_c;
   const int cblocks = p.Cin / BK;
-  const int num_kb = p.kh * p.kw * cblocks;
+  const int num_kb = p.ntaps * cblocks;
 
   // consecutive tiles share the pixel box (the A operand) and differ in the output-channel block
   auto tile_coords = [&](int t, int& n0, int& h0, int& w0, int& c0) {
@@ -100,7 +117,7 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     for (int i = 0; i < C::kStages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], kEpiWarps); }
     mbar_fence_init();
-    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&maps_x.m[0]);
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_y);
   }
@@ -118,18 +135,17 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
         int n0, h0, w0, c0;
         tile_coords(t, n0, h0, w0, c0);
-        int kb = 0;
-        for (int r = 0; r < p.kh && !*dead; ++r) {
-          for (int sx = 0; sx < p.kw; ++sx) {
-            for (int cb = 0; cb < cblocks; ++cb, ++kb) {
-              if (!mbar_wait(&empty_bar[s], ph ^ 1, dead, p.status, 900)) break;
-              uint8_t* sa = stage_base + s * C::kStage;
-              mbar_expect_tx(&full_bar[s], C::kStage);
-              // the tile's pixel box of the input, shifted by the tap; padding comes back as zeros
-              tma_load_4d(sa, &map_x, &full_bar[s], cb * BK, w0 + sx - p.pw, h0 + r - p.ph, n0);
-              tma_load_2d(sa + C::kStageA, &map_w, &full_bar[s], (r * p.kw + sx) * p.Cin + cb * BK, c0);
-              if (++s == C::kStages) { s = 0; ph ^= 1; }
-            }
+        for (int tap = 0; tap < p.ntaps && !*dead; ++tap) {
+          const CUtensorMap* mx = &maps_x.m[p.tap_map[tap]];
+          const int dh = p.tap_dh[tap], dw = p.tap_dw[tap], wcol = p.tap_wcol[tap] * p.Cin;
+          for (int cb = 0; cb < cblocks; ++cb) {
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, dead, p.status, 900)) break;
+            uint8_t* sa = stage_base + s * C::kStage;
+            mbar_expect_tx(&full_bar[s], C::kStage);
+            // the tile's pixel box of the tap's input view, shifted by the tap; padding comes back as zeros
+            tma_load_4d(sa, mx, &full_bar[s], cb * BK, w0 + dw, h0 + dh, n0);
+            tma_load_2d(sa + C::kStageA, &map_w, &full_bar[s], wcol + cb * BK, c0);
+            if (++s == C::kStages) { s = 0; ph ^= 1; }
           }
         }
         if (*dead) break;
@@ -234,7 +250,7 @@ conv_fprop_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 }
 
 template <int BN>
-int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, const ConvParams& p, int max_ctas,
+int launch(const XMaps& mx, const CUtensorMap& mw, const CUtensorMap& my, const ConvParams& p, int max_ctas,
            cudaStream_t stream) {
   using C = Cfg<BN>;
   auto kern = conv_fprop_kernel<BN>;
@@ -253,17 +269,17 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my, 
 }
 
 // ------------------------------------------------------------------ weight gradient
-//   dw[co, r, s, ci] = sum_{n, ho, wo} dy[n, ho, wo, co] * x[n, ho + r - ph, wo + s - pw, ci]
+//   dw[co, r, s, ci] = sum_{n, ho, wo} dy[n, ho, wo, co] * x[n, sh*ho + r - ph, sw*wo + s - pw, ci]
 // as a GEMM whose reduction dimension is the pixels: for one filter tap, M = 128 output channels,
 // N = BNC input channels, K = boxes of 64 pixels.  Both operands are "MN-major" (the channel is the
 // contiguous dimension in memory): the A slabs are 4-D TMA boxes of dy, the B slabs the same pixel
-// box of x shifted by the tap (zero fill = padding).  The pixel range is split over CTAs; partial
-// sums are added to an fp32 buffer with global reductions.
+// box of the tap's parity view of x, shifted by the tap (zero fill = padding).  The pixel range is
+// split over CTAs; partial sums are added to an fp32 buffer with global reductions.
 constexpr int WBK = 64;          // pixels per k block
 
 struct WgradParams {
   int N, H, W, Cin, Cout, Ho, Wo;
-  int kh, kw, ph, pw;
+  int kh, kw, ph, pw, sh, sw;
   int TN, TH, TW;          // pixel box of a k block, TN*TH*TW == 64
   int splits;              // pixel-range splits per (tap, co block, ci block)
   float* dw;               // [Cout, kh, kw, Cin] fp32, zero-initialised by the caller
@@ -281,7 +297,7 @@ struct WCfg {
 
 template <int BNC>
 __global__ void __launch_bounds__(kThreads, 1)
-conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x,
+conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ XMaps maps_x,
                   const WgradParams p) {
   using C = WCfg<BNC>;
   extern __shared__ uint8_t smem_raw[];
@@ -319,7 +335,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
     mbar_init(tempty_bar, kEpiWarps);
     mbar_fence_init();
     prefetch_tensormap(&map_dy);
-    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&maps_x.m[0]);
   }
   if (warp == 1) { tmem_alloc<BNC>(tmem_slot); tmem_relinquish(); }
   tc_fence_before();
@@ -335,6 +351,10 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
         int tap, cob, cib, b0, b1;
         item_coords(it, tap, cob, cib, b0, b1);
         const int r = tap / p.kw, sx = tap % p.kw;
+        // view and shift of this tap: sh*ho + r - ph = sh*(ho + dh) + a with 0 <= a < sh
+        const int a = (((r - p.ph) % p.sh) + p.sh) % p.sh, dh = (r - p.ph - a) / p.sh;
+        const int bb = (((sx - p.pw) % p.sw) + p.sw) % p.sw, dw = (sx - p.pw - bb) / p.sw;
+        const CUtensorMap* mx = &maps_x.m[a * p.sw + bb];
         for (int b = b0; b < b1; ++b) {
           const int tw = b % tiles_w, th = (b / tiles_w) % tiles_h, tn = b / (tiles_w * tiles_h);
           const int w0 = tw * p.TW, h0 = th * p.TH, n0 = tn * p.TN;
@@ -346,8 +366,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
             tma_load_4d(sa + j * (WBK * 128), &map_dy, &full_bar[s], cob * 128 + j * 64, w0, h0, n0);
 #pragma unroll
           for (int j = 0; j < BNC / 64; ++j)
-            tma_load_4d(sa + C::kStageA + j * (WBK * 128), &map_x, &full_bar[s], cib * BNC + j * 64, w0 + sx - p.pw,
-                        h0 + r - p.ph, n0);
+            tma_load_4d(sa + C::kStageA + j * (WBK * 128), mx, &full_bar[s], cib * BNC + j * 64, w0 + dw, h0 + dh, n0);
           if (++s == C::kStages) { s = 0; ph ^= 1; }
         }
       }
@@ -413,7 +432,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_const
 }
 
 template <int BNC>
-int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const WgradParams& p, int grid, cudaStream_t stream) {
+int launch_wgrad(const CUtensorMap& mdy, const XMaps& mx, const WgradParams& p, int grid, cudaStream_t stream) {
   using C = WCfg<BNC>;
   auto kern = conv_wgrad_kernel<BNC>;
   static bool configured = false;
@@ -426,20 +445,44 @@ int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const WgradParam
   return (int)cudaGetLastError();
 }
 
-int pow2_floor(int v) { int r = 1; while (r * 2 <= v) r *= 2; return r; }
-
 }  // namespace
 
-// x [N, H, W, Cin] bf16 (NHWC), w [Cout, kh, kw, Cin] bf16, y [N, Ho, Wo, Cout] bf16 with
-// Ho = H + 2*ph - kh + 1, Wo = W + 2*pw - kw + 1 (stride 1).  Cin and Cout multiples of 64.
-// Returns a cudaError_t value, -1 for an unsupported argument.
-AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bias, int bias_kind, int act, int N,
-                           int H, int W, int Cin, int Cout, int kh, int kw, int ph, int pw, int max_ctas,
-                           int* status, cudaStream_t stream) {
-  const int Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
+namespace {
+
+// floor division and the matching non-negative remainder
+inline int floordiv(int a, int b) { int q = a / b; return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q; }
+
+// Tensor maps of the sh*sw parity views of an NHWC tensor: view (a, b) holds the pixels
+// (sh*i + a, sw*j + b).  valid[a*sw+b] is 0 for a view without pixels.
+int encode_parity_views(XMaps* out, int* valid, const void* x, int N, int H, int W, int C, int sh, int sw,
+                        const uint32_t box[4]) {
+  for (int a = 0; a < sh; ++a)
+    for (int b = 0; b < sw; ++b) {
+      const int Ha = (H - a + sh - 1) / sh, Wb = (W - b + sw - 1) / sw;
+      valid[a * sw + b] = Ha > 0 && Wb > 0;
+      if (!valid[a * sw + b]) continue;
+      const uint8_t* base = (const uint8_t*)x + ((long)a * W + b) * C * 2;
+      uint64_t dims[4] = {(uint64_t)C, (uint64_t)Wb, (uint64_t)Ha, (uint64_t)N};
+      uint64_t strides[3] = {(uint64_t)sw * C * 2, (uint64_t)sh * W * C * 2, (uint64_t)H * W * C * 2};
+      int rc = axh::encode_tensor_map(&out->m[a * sw + b], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides,
+                                      box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+    }
+  return 0;
+}
+
+struct TapList { int n = 0; int map[kMaxTaps], dh[kMaxTaps], dw[kMaxTaps], wcol[kMaxTaps]; };
+
+// One launch of the tap-table kernel.  The input x [N, H, W, Cin] is read through its xsh*xsw parity
+// views; the filter matrix is w [Cout, wtaps * Cin]; the output view has extents [N, Ho, Wo, Cout],
+// starts y_off elements into y and has the given element strides between columns, rows and images.
+int run_taps(const void* x, int N, int H, int W, int Cin, int xsh, int xsw, const TapList& taps, const void* w,
+             int wtaps, void* y, int Ho, int Wo, int Cout, long y_off, long y_sw, long y_sh, long y_sn,
+             const void* bias, int bias_kind, int act, int max_ctas, int* status, cudaStream_t stream) {
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
-  if (Cin % 64 || Cout % 64 || kh < 1 || kw < 1) return -1;
+  if (Cin % 64 || Cout % 64 || taps.n < 1 || taps.n > kMaxTaps || xsh * xsw > 4 || wtaps > 255) return -1;
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) return -1;
+  if ((y_off | y_sw | y_sh | y_sn) % 8) return -1;
   int sms = axh::sm_count();
   if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
 
@@ -454,8 +497,8 @@ AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bi
       if (eff > best + 1e-9 || (eff > best - 1e-9 && tw > TW)) { best = eff; TW = tw; TH = th; TN = tn; }
     }
   ConvParams p;
-  p.N = N; p.H = H; p.W = W; p.Cin = Cin; p.Cout = Cout; p.Ho = Ho; p.Wo = Wo;
-  p.kh = kh; p.kw = kw; p.ph = ph; p.pw = pw;
+  memset(&p, 0, sizeof(p));
+  p.N = N; p.Cin = Cin; p.Cout = Cout; p.Ho = Ho; p.Wo = Wo;
   p.TN = TN; p.TH = TH; p.TW = TW;
   // the 32 pixels of one epilogue warp, in (n, h, w) order with w fastest
   if (TW >= 32) { p.bw = 32; p.bh = 1; p.bn = 1; }
@@ -469,20 +512,29 @@ AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bi
     const long pix_tiles = (long)((Wo + TW - 1) / TW) * ((Ho + TH - 1) / TH) * ((N + TN - 1) / TN);
     while (BN > 64 && pix_tiles * (Cout / BN) < max_ctas) BN /= 2;
   }
-  (void)pow2_floor;
 
-  CUtensorMap mx, mw, my;
+  XMaps mx;
+  CUtensorMap mw, my;
+  int valid[4] = {0, 0, 0, 0};
   {
-    uint64_t dims[4] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)N};
-    uint64_t strides[3] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2};
     uint32_t box[4] = {64, (uint32_t)TW, (uint32_t)TH, (uint32_t)TN};
-    int rc = axh::encode_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = encode_parity_views(&mx, valid, x, N, H, W, Cin, xsh, xsw, box);
     if (rc) return 1000 + rc;
   }
+  // taps whose view has no pixels read nothing but padding
+  for (int t = 0; t < taps.n; ++t) {
+    if (taps.map[t] < 0 || taps.map[t] >= xsh * xsw || !valid[taps.map[t]]) continue;
+    if (taps.dh[t] < -128 || taps.dh[t] > 127 || taps.dw[t] < -128 || taps.dw[t] > 127) return -1;
+    p.tap_map[p.ntaps] = (int8_t)taps.map[t];
+    p.tap_dh[p.ntaps] = (int8_t)taps.dh[t];
+    p.tap_dw[p.ntaps] = (int8_t)taps.dw[t];
+    p.tap_wcol[p.ntaps] = (uint8_t)taps.wcol[t];
+    ++p.ntaps;
+  }
+  if (p.ntaps == 0) return -1;
   {
-    uint64_t dims[2] = {(uint64_t)kh * kw * Cin, (uint64_t)Cout};
-    uint64_t strides[1] = {(uint64_t)kh * kw * Cin * 2};
+    uint64_t dims[2] = {(uint64_t)wtaps * Cin, (uint64_t)Cout};
+    uint64_t strides[1] = {(uint64_t)wtaps * Cin * 2};
     uint32_t box[2] = {64, (uint32_t)BN};
     int rc = axh::encode_tensor_map(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, dims, strides, box,
                                     CU_TENSOR_MAP_SWIZZLE_128B);
@@ -490,10 +542,10 @@ AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bi
   }
   {
     uint64_t dims[4] = {(uint64_t)Cout, (uint64_t)Wo, (uint64_t)Ho, (uint64_t)N};
-    uint64_t strides[3] = {(uint64_t)Cout * 2, (uint64_t)Wo * Cout * 2, (uint64_t)Ho * Wo * Cout * 2};
+    uint64_t strides[3] = {(uint64_t)y_sw * 2, (uint64_t)y_sh * 2, (uint64_t)y_sn * 2};
     uint32_t box[4] = {64, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
-    int rc = axh::encode_tensor_map(&my, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, y, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = axh::encode_tensor_map(&my, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (uint8_t*)y + y_off * 2, dims, strides,
+                                    box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return 3000 + rc;
   }
   switch (BN) {
@@ -503,11 +555,56 @@ AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bi
   }
 }
 
+}  // namespace
+
+// x [N, H, W, Cin] bf16 (NHWC), w [Cout, kh, kw, Cin] bf16, y [N, Ho, Wo, Cout] bf16 with
+// Ho = (H + 2*ph - kh) / sh + 1, Wo = (W + 2*pw - kw) / sw + 1.  Cin and Cout multiples of 64,
+// sh * sw <= 4, kh * kw <= 64.  Returns a cudaError_t value, -1 for an unsupported argument.
+AX_API int ax_conv2d_fprop(const void* x, const void* w, void* y, const void* bias, int bias_kind, int act, int N,
+                           int H, int W, int Cin, int Cout, int kh, int kw, int ph, int pw, int sh, int sw,
+                           int max_ctas, int* status, cudaStream_t stream) {
+  if (kh < 1 || kw < 1 || sh < 1 || sw < 1 || kh * kw > kMaxTaps) return -1;
+  if (H + 2 * ph < kh || W + 2 * pw < kw) return 0;
+  const int Ho = (H + 2 * ph - kh) / sh + 1, Wo = (W + 2 * pw - kw) / sw + 1;
+  TapList taps;
+  for (int r = 0; r < kh; ++r)
+    for (int s = 0; s < kw; ++s) {
+      const int dh = floordiv(r - ph, sh), dw = floordiv(s - pw, sw);
+      const int a = r - ph - dh * sh, b = s - pw - dw * sw;
+      taps.map[taps.n] = a * sw + b; taps.dh[taps.n] = dh; taps.dw[taps.n] = dw; taps.wcol[taps.n] = r * kw + s;
+      ++taps.n;
+    }
+  return run_taps(x, N, H, W, Cin, sh, sw, taps, w, kh * kw, y, Ho, Wo, Cout, 0, Cout, (long)Wo * Cout,
+                  (long)Ho * Wo * Cout, bias, bias_kind, act, max_ctas, status, stream);
+}
+
+// One parity class (a, b) of the data gradient of a strided convolution: the pixels
+// dx[n, sh*i + a, sw*j + b, :] of dx [N, H, W, Cin] from dy [N, Ho, Wo, Cout] and the class's filter
+// matrix wc [Cin, ntaps * Cout] (tap t of the class: filter position (r_t, s_t), listed by the caller
+// as the shifts dh[t] = (a + ph - r_t) / sh, dw[t] = (b + pw - s_t) / sw).
+AX_API int ax_conv2d_dgrad_class(const void* dy, const void* wc, void* dx, int N, int H, int W, int Cin, int Ho,
+                                 int Wo, int Cout, int sh, int sw, int a, int b, int ntaps, const int* dh,
+                                 const int* dw, int max_ctas, int* status, cudaStream_t stream) {
+  if (ntaps < 1 || ntaps > kMaxTaps || a < 0 || a >= sh || b < 0 || b >= sw) return -1;
+  const int Ha = (H - a + sh - 1) / sh, Wb = (W - b + sw - 1) / sw;
+  if (Ha <= 0 || Wb <= 0) return 0;
+  TapList taps;
+  for (int t = 0; t < ntaps; ++t) {
+    taps.map[t] = 0; taps.dh[t] = dh[t]; taps.dw[t] = dw[t]; taps.wcol[t] = t;
+  }
+  taps.n = ntaps;
+  return run_taps(dy, N, Ho, Wo, Cout, 1, 1, taps, wc, ntaps, dx, Ha, Wb, Cin, ((long)a * W + b) * Cin,
+                  (long)sw * Cin, (long)sh * W * Cin, (long)H * W * Cin, nullptr, 0, 0, max_ctas, status, stream);
+}
+
 // dy [N, Ho, Wo, Cout] bf16, x [N, H, W, Cin] bf16 (NHWC), dw [Cout, kh, kw, Cin] fp32 which must be
-// zero on entry (partial sums are added).  Stride 1; Cin and Cout multiples of 64.
+// zero on entry (partial sums are added).  Cin and Cout multiples of 64, sh * sw <= 4; every parity
+// view of x must hold at least one pixel (H >= sh, W >= sw).
 AX_API int ax_conv2d_wgrad(const void* dy, const void* x, float* dw, int N, int H, int W, int Cin, int Cout, int kh,
-                           int kw, int ph, int pw, int max_ctas, int* status, cudaStream_t stream) {
-  const int Ho = H + 2 * ph - kh + 1, Wo = W + 2 * pw - kw + 1;
+                           int kw, int ph, int pw, int sh, int sw, int max_ctas, int* status, cudaStream_t stream) {
+  if (sh < 1 || sw < 1 || sh * sw > 4 || H < sh || W < sw || kh < 1 || kw < 1) return -1;
+  if (H + 2 * ph < kh || W + 2 * pw < kw) return 0;
+  const int Ho = (H + 2 * ph - kh) / sh + 1, Wo = (W + 2 * pw - kw) / sw + 1;
   if (N <= 0 || Ho <= 0 || Wo <= 0) return 0;
   if (Cin % 64 || Cout % 64) return -1;
   if (((uintptr_t)dy | (uintptr_t)x | (uintptr_t)dw) & 15) return -1;
@@ -525,7 +622,7 @@ AX_API int ax_conv2d_wgrad(const void* dy, const void* x, float* dw, int N, int 
   const int BNC = Cin % 128 == 0 ? 128 : 64;
   WgradParams p;
   p.N = N; p.H = H; p.W = W; p.Cin = Cin; p.Cout = Cout; p.Ho = Ho; p.Wo = Wo;
-  p.kh = kh; p.kw = kw; p.ph = ph; p.pw = pw; p.TN = TN; p.TH = TH; p.TW = TW;
+  p.kh = kh; p.kw = kw; p.ph = ph; p.pw = pw; p.sh = sh; p.sw = sw; p.TN = TN; p.TH = TH; p.TW = TW;
   p.dw = dw; p.status = status;
   const int nboxes = ((Wo + TW - 1) / TW) * ((Ho + TH - 1) / TH) * ((N + TN - 1) / TN);
   const int base_items = kh * kw * ((Cout + 127) / 128) * (Cin / BNC);
@@ -535,7 +632,8 @@ AX_API int ax_conv2d_wgrad(const void* dy, const void* x, float* dw, int N, int 
   p.splits = splits;
   const long items = (long)base_items * splits;
   const int grid = items < max_ctas ? (int)items : max_ctas;
-  CUtensorMap mdy, mx;
+  CUtensorMap mdy;
+  XMaps mx;
   {
     uint64_t dims[4] = {(uint64_t)Cout, (uint64_t)Wo, (uint64_t)Ho, (uint64_t)N};
     uint64_t strides[3] = {(uint64_t)Cout * 2, (uint64_t)Wo * Cout * 2, (uint64_t)Ho * Wo * Cout * 2};
@@ -545,11 +643,9 @@ AX_API int ax_conv2d_wgrad(const void* dy, const void* x, float* dw, int N, int 
     if (rc) return 1000 + rc;
   }
   {
-    uint64_t dims[4] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)N};
-    uint64_t strides[3] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2};
     uint32_t box[4] = {64, (uint32_t)TW, (uint32_t)TH, (uint32_t)TN};
-    int rc = axh::encode_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, x, dims, strides, box,
-                                    CU_TENSOR_MAP_SWIZZLE_128B);
+    int valid[4];
+    int rc = encode_parity_views(&mx, valid, x, N, H, W, Cin, sh, sw, box);
     if (rc) return 2000 + rc;
   }
   return BNC == 128 ? launch_wgrad<128>(mdy, mx, p, grid, stream) : launch_wgrad<64>(mdy, mx, p, grid, stream);

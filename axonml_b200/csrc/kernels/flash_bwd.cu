@@ -32,7 +32,11 @@ constexpr int kThreads = 320;
 constexpr int kStat = BS * HD * 2;        // 32 KB
 constexpr int kStream = BT * HD * 2;      // 16 KB
 constexpr int kETile = BS * BT * 2;       // 16 KB
-constexpr int kSmem = 1024 + 2 * kStat + 2 * 2 * kStream + 2 * kETile + 256;
+constexpr int kMaxStages = 3;             // streamed-tile stages: a stage is released by the accumulate MMAs of
+                                          // its tile, so two stages put the TMA latency of tile t+1 in series
+                                          // with the accumulate of tile t-1
+constexpr int kLseBytes = 8 * 2 * 32 * 4; // per compute warp: 32 scaled log-sum-exps and 32 deltas of its columns
+constexpr int smem_bytes(int stages) { return 1024 + 2 * kStat + stages * 2 * kStream + 2 * kETile + kLseBytes + 256; }
 constexpr int kTmemCols = 512;            // T1[0] T2[0] T1[1] T2[1] (64 each) | acc1 (128) | acc2 (128)
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -47,7 +51,7 @@ struct BwdParams {
   int* status;
 };
 
-template <int MODE>
+template <int MODE, int kStages, bool kStageLse>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constant__ CUtensorMap map_a2,
                  const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
@@ -57,22 +61,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
   uint8_t* sA1 = smem;
   uint8_t* sA2 = sA1 + kStat;
   uint8_t* sB = sA2 + kStat;               // stage s: B1 at sB + s*2*kStream, B2 right after it
-  uint8_t* sE1 = sB + 4 * kStream;
+  uint8_t* sE1 = sB + kStages * 2 * kStream;
   uint8_t* sE2 = sE1 + kETile;
-  uint64_t* bars = (uint64_t*)(sE2 + kETile);
+  float* sLse = (float*)(sE2 + kETile);   // [8 warps][2][32]
+  uint64_t* bars = (uint64_t*)((uint8_t*)sLse + kLseBytes);
   uint64_t* stat_full = bars;        // 1
-  uint64_t* b_full = bars + 1;       // 2
-  uint64_t* b_empty = bars + 3;      // 2
-  uint64_t* t_full = bars + 5;       // 2
-  uint64_t* t_empty = bars + 7;      // 2
-  uint64_t* e_full = bars + 9;       // 1
-  uint64_t* e_free = bars + 10;      // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+  uint64_t* b_full = bars + 1;       // kStages (room for kMaxStages)
+  uint64_t* b_empty = bars + 4;      // kStages
+  uint64_t* t_full = bars + 7;       // 2
+  uint64_t* t_empty = bars + 9;      // 2
+  uint64_t* e_full = bars + 11;      // 1
+  uint64_t* e_free = bars + 12;      // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
   volatile int* dead = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int blk = (MODE == MODE_DQ) ? ((int)gridDim.x - 1 - (int)blockIdx.x) : (int)blockIdx.x;
-  const int hh = blockIdx.y, b = blockIdx.z;       // DKV: hh = kv head; DQ: hh = query head
+  // One-dimensional grid, longest CTAs first: with a causal mask a key block early in the sequence (DKV) or a
+  // query block late in it (DQ) sees the most tiles, and CTAs are handed out in index order, so the block index
+  // is the slow coordinate and (head, batch) the fast one.
+  const int nblk = (int)gridDim.x / (p.B * ((MODE == MODE_DQ) ? p.Hq : p.Hkv));
+  const int slow = (int)blockIdx.x / (p.B * ((MODE == MODE_DQ) ? p.Hq : p.Hkv));
+  const int fast = (int)blockIdx.x - slow * (p.B * ((MODE == MODE_DQ) ? p.Hq : p.Hkv));
+  const int blk = (MODE == MODE_DQ) ? (nblk - 1 - slow) : slow;
+  const int hh = fast % ((MODE == MODE_DQ) ? p.Hq : p.Hkv);   // DKV: hh = kv head; DQ: hh = query head
+  const int b = fast / ((MODE == MODE_DQ) ? p.Hq : p.Hkv);
   const int G = p.Hq / p.Hkv;
   const int offset = p.Skv - p.Sq;
   const int row0 = blk * BS;                       // first stationary row (key or query index)
@@ -97,10 +109,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
   if (threadIdx.x == 0) {
     *dead = 0;
     mbar_init(stat_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1);
-      mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 8);
-    }
+    for (int i = 0; i < kStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 8); }
     mbar_init(e_full, 8);
     mbar_init(e_free, 1);
     mbar_fence_init();
@@ -121,8 +131,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
       tma_load_4d(sA2, &map_a2, stat_full, 0, hs, row0, b);
       tma_load_4d(sA2 + slab_bytes(BS), &map_a2, stat_full, 64, hs, row0, b);
       for (int t = 0; t < T; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int s = t % kStages;
+        const uint32_t ph = (t / kStages) & 1;
         int head, r0;
         if (MODE == MODE_DKV) {
           const int g = t / tiles_per_head;
@@ -150,12 +160,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
       const uint32_t aE1 = smem_u32(sE1), aE2 = smem_u32(sE2);
       bool ok = mbar_wait(stat_full, 0, dead, p.status, 510);
       auto issue_scores = [&](int t) {
-        const int s = t & 1;
+        const int s = t & 1, bs = t % kStages;
         const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&b_full[s], ph, dead, p.status, 511)) return false;
+        if (!mbar_wait(&b_full[bs], (t / kStages) & 1, dead, p.status, 511)) return false;
         if (!mbar_wait(&t_empty[s], ph ^ 1, dead, p.status, 512)) return false;
         tc_fence_after();
-        const uint32_t aB1 = smem_u32(sB + s * 2 * kStream), aB2 = aB1 + kStream;
+        const uint32_t aB1 = smem_u32(sB + bs * 2 * kStream), aB2 = aB1 + kStream;
         const uint32_t tT1 = tmem_base + s * 128, tT2 = tT1 + 64;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
@@ -170,7 +180,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
       for (int t = 0; ok && t < T; ++t) {
         if (t + 1 < T) ok = issue_scores(t + 1);
         if (!ok) break;
-        const int s = t & 1;
+        const int s = t % kStages;
         if (!mbar_wait(e_full, t & 1, dead, p.status, 513)) break;
         tc_fence_after();
         const uint32_t aB1 = smem_u32(sB + s * 2 * kStream), aB2 = aB1 + kStream;
@@ -200,15 +210,36 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
       lse_r = v ? p.lse[idx] * kLog2e : INFINITY;
       delta_r = v ? p.delta[idx] : 0.f;
     }
+    // DKV: the columns of a score tile are queries, so every lane of a warp needs the same 32
+    // log-sum-exps and deltas.  Lane i fetches those of column i one tile ahead (one coalesced load
+    // each), the warp parks them in its own slice of shared memory and reads them back as
+    // broadcast float4s.
+    float* my_lse = sLse + cw * 64;
+    float nl = INFINITY, nd = 0.f;
+    auto fetch_cols = [&](int t) {
+      const int g = t / tiles_per_head;
+      const int qi = (first_tile + (t - g * tiles_per_head)) * BT + half * 32 + lane;
+      const long idx = ((long)b * p.Hq + hh * G + g) * p.Sq + qi;
+      const bool v = qi < p.Sq;
+      nl = v ? __ldg(p.lse + idx) * kLog2e : INFINITY;
+      nd = v ? __ldg(p.delta + idx) : 0.f;
+    };
+    if (MODE == MODE_DKV && kStageLse && T > 0) fetch_cols(0);
     bool ok = true;
     for (int t = 0; t < T && ok; ++t) {
       const int s = t & 1;
       const uint32_t ph = (t >> 1) & 1;
-      int head = hh, c0;
+      int c0;
       if (MODE == MODE_DKV) {
         const int g = t / tiles_per_head;
-        head = hh * G + g;
         c0 = (first_tile + (t - g * tiles_per_head)) * BT + half * 32;   // first query of my columns
+        if (kStageLse) {
+          __syncwarp();                                                  // the previous tile's reads are done
+          my_lse[lane] = nl;
+          my_lse[32 + lane] = nd;
+          if (t + 1 < T) fetch_cols(t + 1);
+          __syncwarp();
+        }
       } else {
         c0 = t * BT + half * 32;                                         // first key of my columns
       }
@@ -234,9 +265,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
           pr[i] = e;
           ds[i] = e * (__uint_as_float(dv[i]) - delta_r);
         }
-      } else {
-        const float* lse_c = p.lse + ((long)b * p.Hq + head) * p.Sq;
-        const float* delta_c = p.delta + ((long)b * p.Hq + head) * p.Sq;
+      } else if (!kStageLse) {
+        const int g = t / tiles_per_head;
+        const float* lse_c = p.lse + ((long)b * p.Hq + hh * G + g) * p.Sq;
+        const float* delta_c = p.delta + ((long)b * p.Hq + hh * G + g) * p.Sq;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int qi = c0 + i;
@@ -247,6 +279,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
           if (!v) e = 0.f;
           pr[i] = e;
           ds[i] = e * (__uint_as_float(dv[i]) - dl);
+        }
+      } else {
+        // columns past Sq carry an infinite log-sum-exp (probability 0); the causal rule hides
+        // queries before key ri - offset
+        const int first_visible = p.causal ? ri - offset : -0x7fffffff;
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(my_lse + i4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(my_lse + 32 + i4 * 4);
+          const float l[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = i4 * 4 + j;
+            float e = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - l[j]);
+            if (c0 + i < first_visible) e = 0.f;
+            pr[i] = e;
+            ds[i] = e * (__uint_as_float(dv[i]) - dl[j]);
+          }
         }
       }
       // the E tiles are free once the accumulate MMAs of the previous tile have retired
@@ -337,6 +387,33 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
   if (lane == 0) delta[((long)b * H + h) * S + s] = acc;
 }
 
+int g_stages = 3;
+bool g_stage_lse = true;
+
+template <int MODE, int STAGES, bool LSE>
+int launch_one(dim3 grid, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1, const CUtensorMap& b2,
+               const BwdParams& p, cudaStream_t stream) {
+  auto kern = flash_bwd_kernel<MODE, STAGES, LSE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(STAGES));
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, kThreads, smem_bytes(STAGES), stream>>>(a1, a2, b1, b2, p);
+  return (int)cudaGetLastError();
+}
+
+template <int MODE>
+int launch_variant(dim3 grid, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1,
+                   const CUtensorMap& b2, const BwdParams& p, cudaStream_t stream) {
+  const bool lse = MODE == MODE_DKV && g_stage_lse;
+  if (g_stages == 2) return lse ? launch_one<MODE, 2, true>(grid, a1, a2, b1, b2, p, stream)
+                                : launch_one<MODE, 2, false>(grid, a1, a2, b1, b2, p, stream);
+  return lse ? launch_one<MODE, 3, true>(grid, a1, a2, b1, b2, p, stream)
+             : launch_one<MODE, 3, false>(grid, a1, a2, b1, b2, p, stream);
+}
+
 }  // namespace
 
 // All tensors token-major [B, S, H, 128] bf16; strides in elements.  dq/dk/dv are written densely
@@ -359,14 +436,6 @@ AX_API int ax_flash_bwd(const void* q, const void* k, const void* v, const void*
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
   }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_bwd_kernel<MODE_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(flash_bwd_kernel<MODE_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
   CUtensorMap mq128, mdo128, mk128, mv128, mq64, mdo64, mk64, mv64;
   int rc;
   if ((rc = axh::make_bshd_map(&mq128, q, D, Hq, Sq, B, q_row, q_batch, BS))) return 1000 + rc;
@@ -384,13 +453,18 @@ AX_API int ax_flash_bwd(const void* q, const void* k, const void* v, const void*
   p.scale = scale; p.scale_log2 = scale * kLog2e; p.status = status;
   // dK, dV
   p.out1 = dv; p.out2 = dk; p.o_row = dkv_row; p.o_batch = dkv_batch;
-  dim3 g1((Skv + BS - 1) / BS, Hkv, B);
-  flash_bwd_kernel<MODE_DKV><<<g1, kThreads, kSmem, stream>>>(mk128, mv128, mq64, mdo64, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
+  dim3 g1(((Skv + BS - 1) / BS) * Hkv * B, 1, 1);
+  int e = launch_variant<MODE_DKV>(g1, mk128, mv128, mq64, mdo64, p, stream);
+  if (e != 0) return e;
   // dQ
   p.out1 = nullptr; p.out2 = dq; p.o_row = dq_row; p.o_batch = dq_batch;
-  dim3 g2((Sq + BS - 1) / BS, Hq, B);
-  flash_bwd_kernel<MODE_DQ><<<g2, kThreads, kSmem, stream>>>(mq128, mdo128, mk64, mv64, p);
-  return (int)cudaGetLastError();
+  dim3 g2(((Sq + BS - 1) / BS) * Hq * B, 1, 1);
+  return launch_variant<MODE_DQ>(g2, mq128, mdo128, mk64, mv64, p, stream);
+}
+
+// Pipeline variant of the backward kernels (for measurements): stages of streamed tiles (2 or 3) and
+// whether the dK/dV launch stages the per-query statistics through shared memory.
+AX_API void ax_flash_bwd_set_variant(int stages, int stage_lse) {
+  g_stages = stages == 2 ? 2 : 3;
+  g_stage_lse = stage_lse != 0;
 }

@@ -64,8 +64,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   volatile int* dead = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // longest (last) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // one-dimensional grid, handed out in index order: the query block is the slow coordinate, so the
+  // longest (last) query blocks of every head start first and the short ones fill the tail
+  const int slow = (int)blockIdx.x / (p.Hq * p.B), fast = (int)blockIdx.x - slow * (p.Hq * p.B);
+  const int qb = (int)gridDim.x / (p.Hq * p.B) - 1 - slow;
+  const int h = fast % p.Hq, b = fast / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qb * BQ;
   const int offset = p.Skv - p.Sq;                        // causal: row i sees keys <= i + offset
@@ -155,9 +158,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t sP_u32 = smem_u32(sP);
     unsigned long long* tr = nullptr;
-    if (p.trace != nullptr && warp == 2 && lane == 0 && blockIdx.x == 0 &&
-        ((blockIdx.y == 0 && blockIdx.z == 0) || (blockIdx.y == gridDim.y - 1 && blockIdx.z == gridDim.z - 1)))
-      tr = p.trace + (blockIdx.z == 0 ? 0 : kTraceSlots);
+    if (p.trace != nullptr && warp == 2 && lane == 0 && slow == 0 &&
+        ((h == 0 && b == 0) || (h == p.Hq - 1 && b == p.B - 1)))
+      tr = p.trace + (b == 0 && h == 0 ? 0 : kTraceSlots);
     auto stamp = [&](int slot) { if (tr != nullptr && slot < kTraceSlots) tr[slot] = globaltimer_ns(); };
     stamp(0);
     float m = -INFINITY, l = 0.f;
@@ -334,8 +337,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   volatile int* dead = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;   // longest (last) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // one-dimensional grid with the query block as the slow coordinate: longest CTAs first
+  const int slow = (int)blockIdx.x / (p.Hq * p.B), fast = (int)blockIdx.x - slow * (p.Hq * p.B);
+  const int qb = (int)gridDim.x / (p.Hq * p.B) - 1 - slow;
+  const int h = fast % p.Hq, b = fast / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qb * 2 * BQ;
   const int offset = p.Skv - p.Sq;                        // causal: row i sees keys <= i + offset
@@ -623,11 +628,11 @@ AX_API int ax_flash_fwd(const void* q, const void* k, const void* v, void* out, 
       if (e != cudaSuccess) return (int)e;
       configured2 = true;
     }
-    dim3 grid2((Sq + 2 * BQ - 1) / (2 * BQ), Hq, B);
+    dim3 grid2(((Sq + 2 * BQ - 1) / (2 * BQ)) * Hq * B, 1, 1);
     flash_fwd2_kernel<<<grid2, kThreads2, kSmem2, stream>>>(mq, mk, mv, p);
     return (int)cudaGetLastError();
   }
-  dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
+  dim3 grid(((Sq + BQ - 1) / BQ) * Hq * B, 1, 1);
   flash_fwd_kernel<<<grid, kThreads, kSmem, stream>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();
 }

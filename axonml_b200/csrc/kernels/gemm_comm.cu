@@ -47,6 +47,7 @@ constexpr int kSigDone = 0;        // [kMaxRanks] "rank p consumed call e"
 constexpr int kSigCounter = 8;     // local: CTAs of this rank that finished the call
 constexpr int kSigFlags = 16;      // [world][max_tiles][4] chunk / tile flags (RS: one per epilogue warp)
 constexpr int kFlagsPerTile = 4;
+constexpr int kFlagLag = 3;        // MODE_RS: tiles between a tile's stores and its flag
 
 enum { MODE_AG = 0, MODE_RS = 1 };
 
@@ -491,7 +492,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int ew = warp - 2;
     uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
     int buf = 0, it = 0;
-    int pend_shard = -1, pend_tile = 0;          // lane 0: the tile whose flag is still owed
+    // lane 0: the tiles whose flags are still owed.  The flag of a tile goes out kFlagLag tiles
+    // later: a completion wait right after the stores costs a full trip through the switch, which
+    // under the all-to-all load of eight ranks is tens of microseconds.
+    int pend_shard[kFlagLag], pend_tile[kFlagLag];
+#pragma unroll
+    for (int i = 0; i < kFlagLag; ++i) { pend_shard[i] = -1; pend_tile[i] = 0; }
     bool ok = true;
     if (MODE == MODE_RS) {
       // the peers must have added up the previous call's partial tiles before their staging slots
@@ -530,7 +536,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (lane == 0) mbar_arrive(&tempty_bar[acc]);
         }
         const int ncol0 = n0 + ch * 64;
-        if (ncol0 >= p.N) continue;
+        if (ncol0 >= p.N) {
+          // every tile commits BN / 64 store groups, empty ones included: the flag logic below counts them
+          if (MODE == MODE_RS && lane == 0) tma_store_commit();
+          continue;
+        }
         if (MODE == MODE_AG) {
           add_bias_chunk(r, p.bias, p.bias_kind, ncol0, p.N);
           apply_act_chunk(r, p.act);
@@ -560,17 +570,18 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         buf ^= 1;
       }
       if (MODE == MODE_RS) {
-        // The flag of a tile goes out one tile later: by then its stores have landed and the
-        // completion wait costs nothing (a wait right after the stores costs a round trip).
+        if (ew == 0 && lane == 0 && it < 15) trace_at(p, 2 + 4 * it + 1);
         if (lane == 0) {
-          if (pend_shard >= 0) {
-            tma_store_wait<BN / 64>();              // everything but this tile's stores
+          if (pend_shard[0] >= 0) {
+            tma_store_wait<kFlagLag * (BN / 64)>();      // everything but the stores of the last kFlagLag tiles
             fence_proxy_async_global();
             __threadfence_system();
-            st_release_sys(p.sig[pend_shard] + kSigFlags + ((p.rank * p.max_tiles + pend_tile) * kFlagsPerTile + q), p.epoch);
+            st_release_sys(p.sig[pend_shard[0]] + kSigFlags + ((p.rank * p.max_tiles + pend_tile[0]) * kFlagsPerTile + q), p.epoch);
           }
-          pend_shard = shard;
-          pend_tile = mb * tm.num_n + nb;
+#pragma unroll
+          for (int i = 0; i + 1 < kFlagLag; ++i) { pend_shard[i] = pend_shard[i + 1]; pend_tile[i] = pend_tile[i + 1]; }
+          pend_shard[kFlagLag - 1] = shard;
+          pend_tile[kFlagLag - 1] = mb * tm.num_n + nb;
         }
         __syncwarp();
       }
@@ -580,10 +591,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (ew == 0 && lane == 0) trace_at(p, 62);
     if (lane == 0) {
       tma_store_wait<0>();
-      if (MODE == MODE_RS && pend_shard >= 0) {
+      if (MODE == MODE_RS) {
         fence_proxy_async_global();
         __threadfence_system();
-        st_release_sys(p.sig[pend_shard] + kSigFlags + ((p.rank * p.max_tiles + pend_tile) * kFlagsPerTile + q), p.epoch);
+#pragma unroll
+        for (int i = 0; i < kFlagLag; ++i)
+          if (pend_shard[i] >= 0)
+            st_release_sys(p.sig[pend_shard[i]] + kSigFlags + ((p.rank * p.max_tiles + pend_tile[i]) * kFlagsPerTile + q), p.epoch);
       }
     }
     __syncwarp();

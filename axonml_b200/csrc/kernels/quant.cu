@@ -1,4 +1,4 @@
-// Block quantisation on the GPU: quantise fp32/bf16 -> Q8_0 / Q4_K and dequantise every GGML block
+// Block quantisation on the GPU: quantise fp32/bf16 -> Q8_0 / Q4_0 / Q4_1 / Q5_0 / Q5_1 / Q4_K and dequantise every GGML block
 // format this package reads (Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, Q4_K) to bf16 or fp32.  Layouts are the
 // GGML ones, identical to the CPU codecs in csrc/host/quant.cpp, so tensors quantised here can be
 // written to a GGUF file unchanged.
@@ -42,6 +42,51 @@ __global__ void quantize_q8_0_kernel(const T* __restrict__ x, uint8_t* __restric
   int q = __float2int_rn(v * id);
   q = max(-127, min(127, q));
   o[2 + lane] = (uint8_t)(int8_t)q;
+}
+
+// Q4_0 / Q4_1 / Q5_0 / Q5_1: one warp per 32-element block, lane l owns element l.  The rules are
+// those of the CPU codec (scale = absmax / 7 or 15 for the symmetric formats, (max - min) / 15 or 31
+// with a stored minimum for the others; round to nearest even; GGML nibble order: elements j and
+// j + 16 share a byte, the fifth bits go to a 32-bit mask).
+template <typename T, int TYPE>
+__global__ void quantize_q45_kernel(const T* __restrict__ x, uint8_t* __restrict__ out, long nblocks) {
+  constexpr bool kFive = TYPE == 3 || TYPE == 4;
+  constexpr bool kMin = TYPE == 2 || TYPE == 4;
+  constexpr int kBytes = TYPE == 1 ? 18 : TYPE == 2 ? 20 : TYPE == 3 ? 22 : 24;
+  constexpr int kHdr = kMin ? 4 : 2;
+  constexpr int kTop = kFive ? 31 : 15;
+  const long b = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (b >= nblocks) return;
+  const float v = ldx(x, b * 32 + lane);
+  float mn = v, mx = v;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  const float amax = fmaxf(fabsf(mn), fabsf(mx));
+  // correctly rounded division and reciprocal (the library is built with fast-math, whose
+  // approximate division would move a value that sits on a rounding boundary)
+  const float d = kMin ? __fdiv_rn(mx - mn, (float)kTop) : __fdiv_rn(amax, (float)(kTop / 2));
+  const float id = d != 0.f ? __frcp_rn(d) : 0.f;
+  int q;
+  if (kMin) q = max(0, min(kTop, __float2int_rn(__fmul_rn(__fsub_rn(v, mn), id))));
+  else q = max(-(kTop + 1) / 2, min(kTop / 2, __float2int_rn(__fmul_rn(v, id)))) + (kTop + 1) / 2;
+  uint8_t* o = out + b * kBytes;
+  if (lane == 0) {
+    f2h(o, d);
+    if (kMin) f2h(o + 2, mn);
+  }
+  const int hi_q = __shfl_down_sync(0xffffffffu, q, 16);       // element lane + 16, for lanes 0..15
+  if (lane < 16) o[kHdr + (kFive ? 4 : 0) + lane] = (uint8_t)((q & 0xF) | ((hi_q & 0xF) << 4));
+  if (kFive) {
+    const uint32_t qh = __ballot_sync(0xffffffffu, (q >> 4) & 1);   // bit l = fifth bit of element l
+    if (lane == 0) {
+      o[kHdr + 0] = (uint8_t)(qh & 0xFF); o[kHdr + 1] = (uint8_t)((qh >> 8) & 0xFF);
+      o[kHdr + 2] = (uint8_t)((qh >> 16) & 0xFF); o[kHdr + 3] = (uint8_t)(qh >> 24);
+    }
+  }
 }
 
 // one warp per 256-element super-block; lane l owns elements [8l, 8l+8) (sub-block l/4)
@@ -175,6 +220,17 @@ AX_API int ax_quantize_cuda(int type, int in_bf16, const void* x, void* out, lon
     const int grid = (int)((nb * 32 + 255) / 256);
     if (in_bf16) quantize_q4_k_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)out, nb);
     else quantize_q4_k_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (uint8_t*)out, nb);
+  } else if (type >= 1 && type <= 4) {
+    if (n % 32) return -1;
+    const long nb = n / 32;
+    const int grid = (int)((nb * 32 + 255) / 256);
+#define AX_Q45(TY)                                                                                         \
+    if (type == TY) {                                                                                      \
+      if (in_bf16) quantize_q45_kernel<__nv_bfloat16, TY><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)out, nb); \
+      else quantize_q45_kernel<float, TY><<<grid, 256, 0, stream>>>((const float*)x, (uint8_t*)out, nb);   \
+    }
+    AX_Q45(1) AX_Q45(2) AX_Q45(3) AX_Q45(4)
+#undef AX_Q45
   } else {
     return -2;
   }

@@ -10,12 +10,12 @@ from .. import _native as N
 
 
 def quantize_cuda(x: torch.Tensor, quant_type) -> torch.Tensor:
-    """fp32/bf16 CUDA tensor -> packed uint8 blocks (GGML layout).  Q8_0 and Q4_K run on the GPU;
-    the other formats round-trip through the CPU codec."""
+    """fp32/bf16 CUDA tensor -> packed uint8 blocks (GGML layout), on the GPU for every block format
+    of the package (Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, Q4_K); other inputs go through the CPU codec."""
     from ..quant.types import QuantType
     n = x.numel()
     nbytes = n // quant_type.block_size() * quant_type.bytes_per_block()
-    if quant_type in (QuantType.Q8_0, QuantType.Q4_K) and x.dtype in (torch.float32, torch.bfloat16):
+    if quant_type.codec_id() in (0, 1, 2, 3, 4, 5) and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16):
         xc = x.contiguous()
         out = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
         rc = N.cuda().ax_quantize_cuda(quant_type.codec_id(), int(xc.dtype == torch.bfloat16), N.ptr(xc), N.ptr(out),

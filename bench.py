@@ -290,9 +290,14 @@ def bench_gpt_fsdp(args):
         def step_e2e(i):
             ids = host_ids[i % n_host].to(dev, non_blocking=True)       # H2D from pinned memory
             return float(run(ids).item())                                 # D2H of the step's result
+        nonlocal param_gather
+        param_gather = ("fused into each unit's first GEMM (peer memory)" if engine._k4
+                        else ("nccl all-gather, prefetched one unit ahead" if world > 1 else "none (1 GPU)"))
         return step_device, step_e2e, path
 
+    param_gather = ""
     step_device, step_e2e, comm_path = setup(args.comm)
+    gather_main = param_gather
     m = timed_training(args, world, rank, local, dev, step_device, step_e2e)
     tokens_per_step = B * S * world
     baseline = None
@@ -316,7 +321,7 @@ def bench_gpt_fsdp(args):
             "config": {"model": "gpt-1.3b (24L d2048 16h ffn8192 vocab50257)",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"fsdp{world}-zero3",
                        "optimizer": "AdamW lr3e-4 b(0.9,0.95) wd0.1", "grad_checkpointing": True,
-                       "layers": cfg.n_layer, "grad_comm": comm_path,
+                       "layers": cfg.n_layer, "grad_comm": comm_path, "param_gather": gather_main,
                        "l2_policy": "per-step working set (weights+optimizer state > 20 GB) far exceeds the 126 MB L2"},
             "clocks": m["clocks"],
             "e2e": {"value": round(tokens_per_step / (m["e2e_ms_per_step"] / 1000.0), 1), "unit": "tokens/s",

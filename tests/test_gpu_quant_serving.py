@@ -33,6 +33,24 @@ def test_gpu_quantize_error_and_cpu_readable(qt, limit):
     assert ((dequantize_tensor(q16).cpu() - x.cpu()) ** 2).mean().sqrt().item() / 0.02 < limit * 1.3
 
 
+@pytest.mark.parametrize("qt", ["Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1"])
+def test_gpu_quantize_writes_the_bytes_of_the_cpu_codec(qt):
+    """The 32-element formats follow one rule on both devices (scale from the block's extremes,
+    round to nearest even), so the GPU's blocks must be the CPU codec's blocks byte for byte; a
+    zero block and a constant block exercise the zero-scale branches."""
+    from axonml_b200.quant import QuantType, quantize_tensor
+    t = QuantType[qt]
+    torch.manual_seed(3)
+    x = torch.randn(96, 1024) * 0.05
+    x[0, :32] = 0.0
+    x[1, :32] = 0.7
+    ref = quantize_tensor(x, t).data
+    got = quantize_tensor(x.cuda(), t).data
+    assert got.is_cuda and got.dtype == torch.uint8 and got.numel() == ref.numel()
+    differing = (got.cpu() != ref).sum().item()
+    assert differing == 0, f"{differing} of {ref.numel()} bytes differ"
+
+
 @pytest.mark.parametrize("qt", ["Q4_K", "Q8_0"])
 @pytest.mark.parametrize("B,N,K", [(1, 128, 256), (8, 768, 4096), (33, 200, 1024), (64, 4096, 1792 // 256 * 256), (100, 384, 512)])
 def test_qgemm(qt, B, N, K, kernel_status):
