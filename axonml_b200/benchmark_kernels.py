@@ -71,7 +71,7 @@ def w_flash_fwd(small, bwd=False):
     return run, flops, 8 * B * S * H * D * 2, f"flash fwd+bwd B{B} H{H} S{S} D{D} causal"
 
 
-def w_flash_bwd_only(small, stages=3, stage_lse=True):
+def w_flash_bwd_only(small):
     """The three backward launches alone (delta pre-pass, dK/dV, dQ), without autograd."""
     import math
     from .ops import flash
@@ -85,13 +85,9 @@ def w_flash_bwd_only(small, stages=3, stage_lse=True):
 
     def run(i):
         q, k, v, out, lse, g, dq, dk, dv = sets[i % nb]
-        flash.set_bwd_variant(stages, stage_lse)
-        try:
-            flash.flash_bwd(q, k, v, out, g, lse, True, 1.0 / math.sqrt(D), dq, dk, dv)
-        finally:
-            flash.set_bwd_variant()
+        flash.flash_bwd(q, k, v, out, g, lse, True, 1.0 / math.sqrt(D), dq, dk, dv)
     flops = 4.0 * B * H * S * S * D / 2 * 2.5
-    return run, flops, 8 * B * S * H * D * 2, f"flash bwd only B{B} H{H} S{S} D{D} causal, {stages} stages, statistics via {'shared memory' if stage_lse else 'global loads'}"
+    return run, flops, 8 * B * S * H * D * 2, f"flash bwd only B{B} H{H} S{S} D{D} causal"
 
 
 def w_rmsnorm(small):
@@ -159,10 +155,7 @@ def w_flash_fwd_one_tile(small):
     return run, flops, nbytes, desc + " (one query tile per CTA)"
 
 
-WORKLOADS = {"gemm": w_gemm, "flash_fwd": w_flash_fwd, "flash_fwd_one_tile": w_flash_fwd_one_tile, "flash_bwd": lambda s: w_flash_fwd(s, True), "flash_bwd_only": w_flash_bwd_only,
-             "flash_bwd_only_2stage": lambda s: w_flash_bwd_only(s, 2, True),
-             "flash_bwd_only_ldg": lambda s: w_flash_bwd_only(s, 3, False),
-             "flash_bwd_only_2stage_ldg": lambda s: w_flash_bwd_only(s, 2, False), "rmsnorm": w_rmsnorm,
+WORKLOADS = {"gemm": w_gemm, "flash_fwd": w_flash_fwd, "flash_fwd_one_tile": w_flash_fwd_one_tile, "flash_bwd": lambda s: w_flash_fwd(s, True), "flash_bwd_only": w_flash_bwd_only, "rmsnorm": w_rmsnorm,
              "adamw": w_adamw, "conv": w_conv, "qgemm": w_qgemm, "paged_decode": w_paged}
 
 

@@ -12,8 +12,8 @@
 // a small pre-pass kernel.  Scores are recomputed in both launches (7 GEMM-equivalents instead of
 // 5) in exchange for never needing atomic accumulation of dQ.
 //
-// Warp roles: 0 = TMA, 1 = MMA issue + TMEM owner, 2..9 = compute (each score row is split
-// between two threads, 32 of the 64 columns each, so that every SM sub-partition has two compute
+// Warp roles: 0 = TMA, 1 = MMA issue + TMEM owner, 2..17 = compute (each score row is split
+// between four threads, 16 of the 64 columns each, so that every SM sub-partition has four compute
 // warps to interleave).
 //
 // The reference has no attention backward at all (its attention builds a fresh leaf,
@@ -28,15 +28,18 @@ using namespace fa;
 constexpr int MODE_DKV = 0, MODE_DQ = 1;
 constexpr int BS = 128;                   // rows of the stationary tiles
 constexpr int BT = 64;                    // rows of the streamed tiles (= score tile width)
-constexpr int kThreads = 320;
+constexpr int kComputeWarps = 16;         // four per TMEM lane quarter: latency of the TMEM loads, exponentials and
+                                          // shared-memory stores of one warp hides behind the other three
+constexpr int CPT = BT * 4 / kComputeWarps;   // score columns per compute thread
+constexpr int kThreads = 64 + kComputeWarps * 32;
 constexpr int kStat = BS * HD * 2;        // 32 KB
 constexpr int kStream = BT * HD * 2;      // 16 KB
 constexpr int kETile = BS * BT * 2;       // 16 KB
-constexpr int kMaxStages = 3;             // streamed-tile stages: a stage is released by the accumulate MMAs of
+constexpr int kStages = 3;                // streamed-tile stages: a stage is released by the accumulate MMAs of
                                           // its tile, so two stages put the TMA latency of tile t+1 in series
-                                          // with the accumulate of tile t-1
-constexpr int kLseBytes = 8 * 2 * 32 * 4; // per compute warp: 32 scaled log-sum-exps and 32 deltas of its columns
-constexpr int smem_bytes(int stages) { return 1024 + 2 * kStat + stages * 2 * kStream + 2 * kETile + kLseBytes + 256; }
+                                          // with the accumulate of tile t-1 (660 -> 554 us at B4 H16 S2048)
+constexpr int kLseBytes = kComputeWarps * 2 * CPT * 4; // per compute warp: the scaled log-sum-exps and deltas of its columns
+constexpr int kSmem = 1024 + 2 * kStat + kStages * 2 * kStream + 2 * kETile + kLseBytes + 256;
 constexpr int kTmemCols = 512;            // T1[0] T2[0] T1[1] T2[1] (64 each) | acc1 (128) | acc2 (128)
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -51,7 +54,7 @@ struct BwdParams {
   int* status;
 };
 
-template <int MODE, int kStages, bool kStageLse>
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_constant__ CUtensorMap map_a2,
                  const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
@@ -63,10 +66,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
   uint8_t* sB = sA2 + kStat;               // stage s: B1 at sB + s*2*kStream, B2 right after it
   uint8_t* sE1 = sB + kStages * 2 * kStream;
   uint8_t* sE2 = sE1 + kETile;
-  float* sLse = (float*)(sE2 + kETile);   // [8 warps][2][32]
+  float* sLse = (float*)(sE2 + kETile);   // [compute warp][log-sum-exps | deltas][CPT]
   uint64_t* bars = (uint64_t*)((uint8_t*)sLse + kLseBytes);
   uint64_t* stat_full = bars;        // 1
-  uint64_t* b_full = bars + 1;       // kStages (room for kMaxStages)
+  uint64_t* b_full = bars + 1;       // kStages
   uint64_t* b_empty = bars + 4;      // kStages
   uint64_t* t_full = bars + 7;       // 2
   uint64_t* t_empty = bars + 9;      // 2
@@ -110,8 +113,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
     *dead = 0;
     mbar_init(stat_full, 1);
     for (int i = 0; i < kStages; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 8); }
-    mbar_init(e_full, 8);
+    for (int i = 0; i < 2; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], kComputeWarps); }
+    mbar_init(e_full, kComputeWarps);
     mbar_init(e_free, 1);
     mbar_fence_init();
   }
@@ -199,7 +202,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
   } else {
     const int cw = warp - 2;
     const int q = warp & 3;                         // TMEM lane quarter
-    const int half = cw >> 2;                       // which 32 of the 64 score columns
+    const int part = cw >> 2;                       // which CPT of the 64 score columns
     const int r = q * 32 + lane;                    // stationary row inside the tile
     const int ri = row0 + r;                        // its key (DKV) or query (DQ) index
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
@@ -210,93 +213,84 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
       lse_r = v ? p.lse[idx] * kLog2e : INFINITY;
       delta_r = v ? p.delta[idx] : 0.f;
     }
-    // DKV: the columns of a score tile are queries, so every lane of a warp needs the same 32
-    // log-sum-exps and deltas.  Lane i fetches those of column i one tile ahead (one coalesced load
-    // each), the warp parks them in its own slice of shared memory and reads them back as
-    // broadcast float4s.
-    float* my_lse = sLse + cw * 64;
-    float nl = INFINITY, nd = 0.f;
+    // DKV: the columns of a score tile are queries, so every lane of a warp needs the same CPT
+    // log-sum-exps and deltas.  Lanes 0..15 fetch the scaled log-sum-exps of the warp's columns one
+    // tile ahead, lanes 16..31 the deltas (one coalesced load), the warp parks them in its own slice
+    // of shared memory and reads them back as broadcast float4s.  A column past Sq gets an infinite
+    // log-sum-exp, i.e. probability zero.
+    float* my_lse = sLse + cw * 32;
+    float nstat = 0.f;
     auto fetch_cols = [&](int t) {
       const int g = t / tiles_per_head;
-      const int qi = (first_tile + (t - g * tiles_per_head)) * BT + half * 32 + lane;
+      const int qi = (first_tile + (t - g * tiles_per_head)) * BT + part * CPT + (lane & (CPT - 1));
       const long idx = ((long)b * p.Hq + hh * G + g) * p.Sq + qi;
       const bool v = qi < p.Sq;
-      nl = v ? __ldg(p.lse + idx) * kLog2e : INFINITY;
-      nd = v ? __ldg(p.delta + idx) : 0.f;
+      if (lane < CPT) nstat = v ? __ldg(p.lse + idx) * kLog2e : INFINITY;
+      else nstat = v ? __ldg(p.delta + idx) : 0.f;
     };
-    if (MODE == MODE_DKV && kStageLse && T > 0) fetch_cols(0);
+    if (MODE == MODE_DKV && T > 0) fetch_cols(0);
     bool ok = true;
     for (int t = 0; t < T && ok; ++t) {
       const int s = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       int c0;
+      bool need_mask;                               // warp-uniform: some (row, column) of this warp is hidden
       if (MODE == MODE_DKV) {
         const int g = t / tiles_per_head;
-        c0 = (first_tile + (t - g * tiles_per_head)) * BT + half * 32;   // first query of my columns
-        if (kStageLse) {
-          __syncwarp();                                                  // the previous tile's reads are done
-          my_lse[lane] = nl;
-          my_lse[32 + lane] = nd;
-          if (t + 1 < T) fetch_cols(t + 1);
-          __syncwarp();
-        }
+        c0 = (first_tile + (t - g * tiles_per_head)) * BT + part * CPT;   // first query of my columns
+        need_mask = p.causal && c0 < row0 + q * 32 + 31 - offset;
+        __syncwarp();                                                    // the previous tile's reads are done
+        my_lse[lane] = nstat;
+        if (t + 1 < T) fetch_cols(t + 1);
+        __syncwarp();
       } else {
-        c0 = t * BT + half * 32;                                         // first key of my columns
+        c0 = t * BT + part * CPT;                                        // first key of my columns
+        const int min_limit = p.causal ? min(p.Skv - 1, row0 + q * 32 + offset) : p.Skv - 1;
+        need_mask = c0 + CPT - 1 > min_limit;
       }
       ok = mbar_wait(&t_full[s], ph, dead, p.status, 520);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32b_x32(tmem_base + s * 128 + half * 32 + lane_addr, sv);
-      tmem_ld_32x32b_x32(tmem_base + s * 128 + 64 + half * 32 + lane_addr, dv);
+      uint32_t sv[CPT], dv[CPT];
+      tmem_ld_32x32b_x16(tmem_base + s * 128 + part * CPT + lane_addr, sv);
+      tmem_ld_32x32b_x16(tmem_base + s * 128 + 64 + part * CPT + lane_addr, dv);
       tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&t_empty[s]);
 
-      float pr[32], ds[32];
+      float pr[CPT], ds[CPT];
       if (MODE == MODE_DQ) {
-        const int limit = p.causal ? min(p.Skv - 1, ri + offset) : p.Skv - 1;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - lse_r);
-          if (c0 + i > limit) e = 0.f;
-          pr[i] = e;
-          ds[i] = e * (__uint_as_float(dv[i]) - delta_r);
+        for (int i = 0; i < CPT; ++i) {
+          pr[i] = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - lse_r);
+          ds[i] = pr[i] * (__uint_as_float(dv[i]) - delta_r);
         }
-      } else if (!kStageLse) {
-        const int g = t / tiles_per_head;
-        const float* lse_c = p.lse + ((long)b * p.Hq + hh * G + g) * p.Sq;
-        const float* delta_c = p.delta + ((long)b * p.Hq + hh * G + g) * p.Sq;
+        if (need_mask) {
+          const int limit = p.causal ? min(p.Skv - 1, ri + offset) : p.Skv - 1;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c0 + i;
-          const bool v = qi < p.Sq && (!p.causal || ri <= qi + offset);
-          const float l2 = v ? __ldg(lse_c + qi) * kLog2e : INFINITY;
-          const float dl = v ? __ldg(delta_c + qi) : 0.f;
-          float e = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - l2);
-          if (!v) e = 0.f;
-          pr[i] = e;
-          ds[i] = e * (__uint_as_float(dv[i]) - dl);
+          for (int i = 0; i < CPT; ++i)
+            if (c0 + i > limit) { pr[i] = 0.f; ds[i] = 0.f; }
         }
       } else {
-        // columns past Sq carry an infinite log-sum-exp (probability 0); the causal rule hides
-        // queries before key ri - offset
-        const int first_visible = p.causal ? ri - offset : -0x7fffffff;
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
+        for (int i4 = 0; i4 < CPT / 4; ++i4) {
           const float4 l4 = *reinterpret_cast<const float4*>(my_lse + i4 * 4);
-          const float4 d4 = *reinterpret_cast<const float4*>(my_lse + 32 + i4 * 4);
+          const float4 d4 = *reinterpret_cast<const float4*>(my_lse + CPT + i4 * 4);
           const float l[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int i = i4 * 4 + j;
-            float e = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - l[j]);
-            if (c0 + i < first_visible) e = 0.f;
-            pr[i] = e;
-            ds[i] = e * (__uint_as_float(dv[i]) - dl[j]);
+            pr[i] = exp2f(__uint_as_float(sv[i]) * p.scale_log2 - l[j]);
+            ds[i] = pr[i] * (__uint_as_float(dv[i]) - dl[j]);
           }
+        }
+        if (need_mask) {
+          const int first_visible = ri - offset;    // the causal rule hides queries before key ri - offset
+#pragma unroll
+          for (int i = 0; i < CPT; ++i)
+            if (c0 + i < first_visible) { pr[i] = 0.f; ds[i] = 0.f; }
         }
       }
       // the E tiles are free once the accumulate MMAs of the previous tile have retired
@@ -306,22 +300,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
         if (!ok) break;
       }
 #pragma unroll
-      for (int g4 = 0; g4 < 4; ++g4) {
+      for (int g4 = 0; g4 < CPT / 8; ++g4) {
         uint4 o;
         if (MODE == MODE_DKV) {
           o.x = pack_bf16x2(pr[g4 * 8 + 0], pr[g4 * 8 + 1]); o.y = pack_bf16x2(pr[g4 * 8 + 2], pr[g4 * 8 + 3]);
           o.z = pack_bf16x2(pr[g4 * 8 + 4], pr[g4 * 8 + 5]); o.w = pack_bf16x2(pr[g4 * 8 + 6], pr[g4 * 8 + 7]);
-          store_tile_chunk(sE1, BS, r, half * 4 + g4, o);
+          store_tile_chunk(sE1, BS, r, part * (CPT / 8) + g4, o);
         }
         o.x = pack_bf16x2(ds[g4 * 8 + 0], ds[g4 * 8 + 1]); o.y = pack_bf16x2(ds[g4 * 8 + 2], ds[g4 * 8 + 3]);
         o.z = pack_bf16x2(ds[g4 * 8 + 4], ds[g4 * 8 + 5]); o.w = pack_bf16x2(ds[g4 * 8 + 6], ds[g4 * 8 + 7]);
-        store_tile_chunk(sE2, BS, r, half * 4 + g4, o);
+        store_tile_chunk(sE2, BS, r, part * (CPT / 8) + g4, o);
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(e_full);
     }
-    // epilogue: accumulators -> global (this thread: row ri, columns [half*64, half*64+64))
+    // epilogue: accumulators -> global (this thread: row ri, columns [part*32, part*32+32))
     if (ok && T > 0) {
       ok = mbar_wait(e_free, (T - 1) & 1, dead, p.status, 522);
       ok = __all_sync(0xffffffffu, ok);
@@ -330,32 +324,31 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_a1, const __grid_consta
       tc_fence_after();
       const int rows_total = (MODE == MODE_DKV) ? p.Skv : p.Sq;
       const bool valid = ri < rows_total;
-      const long base = (long)b * p.o_batch + (long)ri * p.o_row + (long)hh * HD + half * 64;
+      constexpr int kCols = HD / (kComputeWarps / 4);            // 32 output columns per thread
+      static_assert(kCols == 32, "the epilogue reads one 32-column TMEM chunk per accumulator");
+      const long base = (long)b * p.o_batch + (long)ri * p.o_row + (long)hh * HD + part * kCols;
 #pragma unroll 1
       for (int which = (MODE == MODE_DKV ? 0 : 1); which < 2; ++which) {
         __nv_bfloat16* orow = (__nv_bfloat16*)(which == 0 ? p.out1 : p.out2) + base;
-        const uint32_t tacc = (which == 0 ? tAcc1 : tAcc2) + lane_addr + half * 64;
+        const uint32_t tacc = (which == 0 ? tAcc1 : tAcc2) + lane_addr + part * kCols;
         const float mul = which == 0 ? 1.f : p.scale;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          if (T > 0) {
-            tmem_ld_32x32b_x32(tacc + c * 32, v);
-            tc_wait_ld();
-          } else {
+        uint32_t v[32];
+        if (T > 0) {
+          tmem_ld_32x32b_x32(tacc, v);
+          tc_wait_ld();
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0;
-          }
-          if (valid) {
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (valid) {
 #pragma unroll
-            for (int g4 = 0; g4 < 4; ++g4) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[g4 * 8 + 0]) * mul, __uint_as_float(v[g4 * 8 + 1]) * mul);
-              o.y = pack_bf16x2(__uint_as_float(v[g4 * 8 + 2]) * mul, __uint_as_float(v[g4 * 8 + 3]) * mul);
-              o.z = pack_bf16x2(__uint_as_float(v[g4 * 8 + 4]) * mul, __uint_as_float(v[g4 * 8 + 5]) * mul);
-              o.w = pack_bf16x2(__uint_as_float(v[g4 * 8 + 6]) * mul, __uint_as_float(v[g4 * 8 + 7]) * mul);
-              *reinterpret_cast<uint4*>(orow + c * 32 + g4 * 8) = o;
-            }
+          for (int g4 = 0; g4 < 4; ++g4) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[g4 * 8 + 0]) * mul, __uint_as_float(v[g4 * 8 + 1]) * mul);
+            o.y = pack_bf16x2(__uint_as_float(v[g4 * 8 + 2]) * mul, __uint_as_float(v[g4 * 8 + 3]) * mul);
+            o.z = pack_bf16x2(__uint_as_float(v[g4 * 8 + 4]) * mul, __uint_as_float(v[g4 * 8 + 5]) * mul);
+            o.w = pack_bf16x2(__uint_as_float(v[g4 * 8 + 6]) * mul, __uint_as_float(v[g4 * 8 + 7]) * mul);
+            *reinterpret_cast<uint4*>(orow + g4 * 8) = o;
           }
         }
       }
@@ -387,31 +380,18 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
   if (lane == 0) delta[((long)b * H + h) * S + s] = acc;
 }
 
-int g_stages = 3;
-bool g_stage_lse = true;
-
-template <int MODE, int STAGES, bool LSE>
-int launch_one(dim3 grid, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1, const CUtensorMap& b2,
+template <int MODE>
+int launch_bwd(dim3 grid, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1, const CUtensorMap& b2,
                const BwdParams& p, cudaStream_t stream) {
-  auto kern = flash_bwd_kernel<MODE, STAGES, LSE>;
+  auto kern = flash_bwd_kernel<MODE>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(STAGES));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, kThreads, smem_bytes(STAGES), stream>>>(a1, a2, b1, b2, p);
+  kern<<<grid, kThreads, kSmem, stream>>>(a1, a2, b1, b2, p);
   return (int)cudaGetLastError();
-}
-
-template <int MODE>
-int launch_variant(dim3 grid, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1,
-                   const CUtensorMap& b2, const BwdParams& p, cudaStream_t stream) {
-  const bool lse = MODE == MODE_DKV && g_stage_lse;
-  if (g_stages == 2) return lse ? launch_one<MODE, 2, true>(grid, a1, a2, b1, b2, p, stream)
-                                : launch_one<MODE, 2, false>(grid, a1, a2, b1, b2, p, stream);
-  return lse ? launch_one<MODE, 3, true>(grid, a1, a2, b1, b2, p, stream)
-             : launch_one<MODE, 3, false>(grid, a1, a2, b1, b2, p, stream);
 }
 
 }  // namespace
@@ -454,17 +434,10 @@ AX_API int ax_flash_bwd(const void* q, const void* k, const void* v, const void*
   // dK, dV
   p.out1 = dv; p.out2 = dk; p.o_row = dkv_row; p.o_batch = dkv_batch;
   dim3 g1(((Skv + BS - 1) / BS) * Hkv * B, 1, 1);
-  int e = launch_variant<MODE_DKV>(g1, mk128, mv128, mq64, mdo64, p, stream);
+  int e = launch_bwd<MODE_DKV>(g1, mk128, mv128, mq64, mdo64, p, stream);
   if (e != 0) return e;
   // dQ
   p.out1 = nullptr; p.out2 = dq; p.o_row = dq_row; p.o_batch = dq_batch;
   dim3 g2(((Sq + BS - 1) / BS) * Hq * B, 1, 1);
-  return launch_variant<MODE_DQ>(g2, mq128, mdo128, mk64, mv64, p, stream);
-}
-
-// Pipeline variant of the backward kernels (for measurements): stages of streamed tiles (2 or 3) and
-// whether the dK/dV launch stages the per-query statistics through shared memory.
-AX_API void ax_flash_bwd_set_variant(int stages, int stage_lse) {
-  g_stages = stages == 2 ? 2 : 3;
-  g_stage_lse = stage_lse != 0;
+  return launch_bwd<MODE_DQ>(g2, mq128, mdo128, mk64, mv64, p, stream);
 }

@@ -35,12 +35,6 @@ def set_one_tile(flag: bool) -> None:
     N.cuda().ax_flash_fwd_set_one_tile(int(bool(flag)))
 
 
-def set_bwd_variant(stages: int = 3, stage_lse: bool = True) -> None:
-    """Pipeline variant of the backward kernels, for measurements: stages of streamed tiles (2 or
-    3) and whether the dK/dV launch passes the per-query statistics through shared memory."""
-    N.cuda().ax_flash_bwd_set_variant(int(stages), int(bool(stage_lse)))
-
-
 def flash_fwd(q, k, v, causal: bool, scale: float | None = None):
     B, Sq, Hq, D = q.shape
     Skv, Hkv = k.shape[1], k.shape[2]

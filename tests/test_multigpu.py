@@ -459,6 +459,55 @@ def test_sequence_parallel_block_fused_matches_composed():
             assert rel < 3e-2, res[r][1]
 
 
+def _vocab_parallel_gpu(rank, world, be):
+    """Vocabulary-parallel embedding, head and loss on GPUs against the unsharded computation."""
+    from axonml_b200 import _native
+    from axonml_b200.parallel import ProcessGroup
+    from axonml_b200.parallel.tensor_parallel import VocabParallelEmbedding, vocab_parallel_cross_entropy
+    pg = ProcessGroup(be)
+    V, Vpad, H, T = 1000, 1024, 256, 512            # the real vocabulary does not fill the padded split
+    per = Vpad // world
+    torch.manual_seed(11)
+    table = (torch.randn(Vpad, H, device="cuda") * 0.05).bfloat16()
+    head = (torch.randn(Vpad, H, device="cuda") * 0.05).bfloat16()
+    ids = torch.randint(0, V, (T,), device="cuda")
+    target = torch.randint(0, V, (T,), device="cuda")
+    target[::7] = -100
+    emb = VocabParallelEmbedding(Vpad, H, pg, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        emb.weight.copy_(table[rank * per:(rank + 1) * per])
+    w_local = head[rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    launches = _native.launch_count()
+    h = emb(ids)
+    logits = torch.nn.functional.linear(h, w_local)
+    loss = vocab_parallel_cross_entropy(logits, target, pg, rank * per, -100, V)
+    loss.backward()
+    used_kernels = _native.launch_count() - launches
+    torch.cuda.synchronize()
+    _native.check_status()
+    # unsharded reference in fp32 on the same bf16 values
+    tf = table.float().requires_grad_(True)
+    hf = head.float().requires_grad_(True)
+    h_ref = torch.nn.functional.embedding(ids, tf).bfloat16().float()
+    lg = (h_ref @ hf.t())[:, :V]
+    ref = torch.nn.functional.cross_entropy(lg, target, ignore_index=-100)
+    ref.backward()
+    sl = slice(rank * per, (rank + 1) * per)
+    return (abs(loss.item() - ref.item()),
+            (h.float() - h_ref).abs().max().item(),
+            (w_local.grad.float() - hf.grad[sl]).abs().max().item() / (hf.grad.abs().max().item() + 1e-9),
+            (emb.weight.grad.float() - tf.grad[sl]).abs().max().item() / (tf.grad.abs().max().item() + 1e-9),
+            used_kernels)
+
+
+def test_vocab_parallel_embedding_head_and_loss_on_gpus():
+    res = run_gpu_ranks(_vocab_parallel_gpu, WORLD, env={"AXONML_NVLS": "0"})
+    for r in range(WORLD):
+        dl, dh, dw, de, used = res[r][1]
+        assert dl < 2e-2 and dh < 1e-6 and dw < 5e-2 and de < 5e-2, res[r][1]
+        assert used >= 3            # embedding gather, slice statistics, gradient kernel
+
+
 def _tp_serving_gpu(rank, world, be):
     """Tensor-parallel quantised LLaMA decode: CUDA-graph steps with the peer-memory all-reduce
     against eager steps, same weights, same prompts."""
