@@ -5,6 +5,7 @@ file is present in the working directory, else the stated fallback figures).
     python -m axonml_b200.benchmark_kernels gemm flash_fwd rmsnorm      # chosen workloads
     python -m axonml_b200.benchmark_kernels all --iters 20
     python -m axonml_b200.benchmark_kernels gemm_shapes                 # tile policies against cuBLAS
+    python -m axonml_b200.benchmark_kernels gemv_shapes                 # decode matrix-vector kernels, both layouts
     python -m axonml_b200.benchmark_kernels gemm --small                # a few launches on a small case
                                                                         # (what a profiler capture uses)
 
@@ -40,6 +41,26 @@ def _time(fn, iters):
     e0.record()
     for i in range(iters):
         fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3          # us
+
+
+def _time_graph(fn, iters):
+    """Device time per call of a short launch sequence: ``iters`` calls are captured in one CUDA graph
+    and the graph is timed, so that the host's launch rate does not bound the result."""
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters * 1e3          # us
@@ -128,6 +149,26 @@ def w_qgemm(small):
     ws = [tile_weight(quantize_tensor(torch.randn(Nn, K, device="cuda") * 0.02, QuantType.Q4_K)) for _ in range(nb)]
     x = torch.randn(1, K, device="cuda").bfloat16()
     return (lambda i: qgemm(x, ws[i % nb])), 0.0, Nn * K * 0.5625, f"Q4_K dequantising matmul batch 1, [{Nn}, {K}]"
+
+
+def gemv_shapes(iters):
+    """The four Q4_K projections of a Llama-3-8B layer at batch 1 in both weight layouts, and the
+    Q8_0 head: device time and fraction of the measured copy bandwidth."""
+    from .ops.quant import qgemm, tile_weight
+    from .quant.quantize import quantize_tensor
+    from .quant.types import QuantType
+    gbs, _, src = _peaks()
+    for name, Nn, K in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate|up", 28672, 4096), ("down", 4096, 14336),
+                        ("qkv tp8", 768, 4096), ("o tp8", 4096, 512), ("gate|up tp8", 3584, 4096), ("down tp8", 4096, 1792)):
+        nb = max(2, min(8, (400 << 20) // int(Nn * K * 0.5625) + 1))
+        ws = [quantize_tensor(torch.randn(Nn, K, device="cuda") * 0.02, QuantType.Q4_K) for _ in range(nb)]
+        x = torch.randn(1, K, device="cuda").bfloat16()
+        line = f"{name:12s} [{Nn:6d}, {K:6d}]"
+        for layout, mats in (("row-major", ws), ("tile128", [tile_weight(w) for w in ws])):
+            us = _time_graph(lambda i: qgemm(x, mats[i % nb], out_dtype=torch.bfloat16), iters)
+            tb = Nn * K * 0.5625 / us / 1e6
+            line += f"  {layout}: {us:6.1f} us {tb:5.2f} TB/s ({tb * 1000 / gbs:.2f} of {src})"
+        print(line, flush=True)
 
 
 def w_paged(small):
@@ -220,6 +261,10 @@ def main():
     from . import _native
     if a.names == ["gemm_shapes"]:
         gemm_shapes(a.iters)
+        _native.check_status()
+        return
+    if a.names == ["gemv_shapes"]:
+        gemv_shapes(a.iters)
         _native.check_status()
         return
     names = list(WORKLOADS) if a.names == ["all"] else a.names

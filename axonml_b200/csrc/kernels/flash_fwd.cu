@@ -316,6 +316,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 constexpr int kThreads2 = 320;
 constexpr int kSmem2 = 1024 + 2 * kTile /*Q A,B*/ + 2 * kTile /*K*/ + 2 * kTile /*V*/ + 256;
 
+template <bool kTrace>
 __global__ void __launch_bounds__(kThreads2, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
@@ -456,6 +457,12 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const uint32_t tS = tmem_base + t * 128 + lane_addr;
     const uint32_t tO = tmem_base + 256 + t * 128 + lane_addr;
     const int my_blk = nblk_t[t];
+    // timeline of the first CTA (the longest one of head 0, batch 0): quarter-0 warp of tile A in
+    // slot row 0, of tile B in row 1; five stamps per KV block
+    unsigned long long* tr = nullptr;
+    if (kTrace && p.trace != nullptr && q == 0 && lane == 0 && blockIdx.x == 0) tr = p.trace + t * kTraceSlots;
+    auto stamp = [&](int slot) { if (kTrace && tr != nullptr && slot < kTraceSlots) tr[slot] = globaltimer_ns(); };
+    stamp(0);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_blk && ok; ++j) {
@@ -464,12 +471,14 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      stamp(1 + 5 * j);
       uint32_t v[128];
       tmem_ld_32x32b_x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
       tmem_ld_32x32b_x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
       tmem_ld_32x32b_x32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&v[64]));
       tmem_ld_32x32b_x32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&v[96]));
       tc_wait_ld();
+      stamp(2 + 5 * j);
       const int limit = p.causal ? min(p.Skv - 1, qi + offset) : p.Skv - 1;   // last visible key
       if (__any_sync(0xffffffffu, kv0 + BKV - 1 > limit)) {
 #pragma unroll
@@ -511,6 +520,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         tc_wait_st();
       }
+      stamp(3 + 5 * j);
       // probabilities as packed bf16 pairs into the first 64 score columns, row sum in fp32
       const float neg_m = -m;
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -523,13 +533,16 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         pk[i] = pack_bf16x2(e0, e1);
       }
       l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      stamp(4 + 5 * j);
       tmem_st_32x32b_x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       tmem_st_32x32b_x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
+      stamp(5 + 5 * j);
     }
+    stamp(kTraceSlots - 1);
     // epilogue: O / l -> global, lse
     if (ok && my_blk > 0) {
       ok = mbar_wait(&pv_done[t], (my_blk - 1) & 1, dead, p.status, 452);
@@ -620,16 +633,19 @@ AX_API int ax_flash_fwd(const void* q, const void* k, const void* v, void* out, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.trace = g_flash_trace;
-  if (Sq > BQ && g_flash_trace == nullptr && g_flash_one_tile == 0) {
-    // two query tiles per CTA (the timeline facility belongs to the one-tile kernel)
+  if (Sq > BQ && g_flash_one_tile == 0) {
+    // two query tiles per CTA
     static bool configured2 = false;
     if (!configured2) {
-      cudaError_t e = cudaFuncSetAttribute(flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+      cudaError_t e = cudaFuncSetAttribute(flash_fwd2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+      if (e != cudaSuccess) return (int)e;
+      e = cudaFuncSetAttribute(flash_fwd2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
       if (e != cudaSuccess) return (int)e;
       configured2 = true;
     }
     dim3 grid2(((Sq + 2 * BQ - 1) / (2 * BQ)) * Hq * B, 1, 1);
-    flash_fwd2_kernel<<<grid2, kThreads2, kSmem2, stream>>>(mq, mk, mv, p);
+    if (g_flash_trace != nullptr) flash_fwd2_kernel<true><<<grid2, kThreads2, kSmem2, stream>>>(mq, mk, mv, p);
+    else flash_fwd2_kernel<false><<<grid2, kThreads2, kSmem2, stream>>>(mq, mk, mv, p);
     return (int)cudaGetLastError();
   }
   dim3 grid(((Sq + BQ - 1) / BQ) * Hq * B, 1, 1);

@@ -68,6 +68,8 @@ struct CommParams {
   int fill_own;              // AG: the copy CTAs also fill this rank's own slot of its gathered buffer
   int lazy_done;             // AG: "call e consumed" is sent at the start of call e+1 instead of the end of
                              //     call e, because later kernels on the stream still read the gathered buffer
+  int rs_pull;               // RS: partial tiles stay in the sender's staging buffer and the owner of the rows
+                             //     adds them up with one multimem load-reduce through the switch
   int max_tiles;             // flags per source rank
   int* status;
   unsigned long long* trace; // optional timeline [grid][kTraceSlots] of globaltimer stamps, or null
@@ -311,6 +313,7 @@ __device__ void reduce_own_rows(const CommParams& p, const TileMap& tm, int cta,
     if (lane < p.world)
       w_ok = wait_ge<true>(my_flags + ((lane * p.max_tiles + j) * kFlagsPerTile + quarter), p.epoch, p.status, 840);
     if (!__all_sync(0xffffffffu, w_ok)) return;
+    __syncwarp();              // the loads below follow the flag reads of the polling lanes
 #pragma unroll 1
     for (int ch = 0; ch < BN / 64; ++ch) {
       const int ncol0 = nb * BN + ch * 64;
@@ -320,7 +323,22 @@ __device__ void reduce_own_rows(const CommParams& p, const TileMap& tm, int cta,
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int e = 0; e < 8; ++e) a[i][e] = 0.f;
-      for (int src = 0; src < p.world; ++src) {
+      if (p.rs_pull) {
+        // every rank holds its partial copy of this piece at the same offset of its own buffer:
+        // the switch fetches the W copies, adds them in fp32 and returns one
+        const uint8_t* piece = p.sym_mc + stage_off(tm.mbs, p.N, p.rank, mb, ncol0 >> 6, quarter) + lane * 16;
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = multimem_ld_reduce_bf16x8(piece + i * 512);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 f0 = unpack_bf16x2(v[i].x), f1 = unpack_bf16x2(v[i].y), f2 = unpack_bf16x2(v[i].z),
+                       f3 = unpack_bf16x2(v[i].w);
+          a[i][0] = f0.x; a[i][1] = f0.y; a[i][2] = f1.x; a[i][3] = f1.y;
+          a[i][4] = f2.x; a[i][5] = f2.y; a[i][6] = f3.x; a[i][7] = f3.y;
+        }
+      }
+      for (int src = 0; src < (p.rs_pull ? 0 : p.world); ++src) {
         const uint8_t* piece = stage + stage_off(tm.mbs, p.N, src, mb, ncol0 >> 6, quarter) + lane * 16;
         uint4 v[8];
 #pragma unroll
@@ -492,7 +510,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int ew = warp - 2;
     uint8_t* stg = epi_base + ew * 2 * kStageBufBytes;
     int buf = 0, it = 0;
-    // lane 0: the tiles whose flags are still owed.  The flag of a tile goes out kFlagLag tiles
+    // The tiles whose flags are still owed.  The flag of a tile goes out kFlagLag tiles
     // later: a completion wait right after the stores costs a full trip through the switch, which
     // under the all-to-all load of eight ranks is tens of microseconds.
     int pend_shard[kFlagLag], pend_tile[kFlagLag];
@@ -564,6 +582,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         __syncwarp();
         if (lane == 0) {
           if (MODE == MODE_AG) tma_store_2d(&map_c, dst, ncol0, m0 + q * 32);
+          else if (p.rs_pull) bulk_store_1d(p.sym[p.rank] + stage_off(tm.mbs, p.N, shard, mb, ncol0 >> 6, q), dst, kStageBufBytes);
           else bulk_store_1d(p.sym[shard] + stage_off(tm.mbs, p.N, p.rank, mb, ncol0 >> 6, q), dst, kStageBufBytes);
           tma_store_commit();
         }
@@ -571,18 +590,23 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
       if (MODE == MODE_RS) {
         if (ew == 0 && lane == 0 && it < 15) trace_at(p, 2 + 4 * it + 1);
-        if (lane == 0) {
-          if (pend_shard[0] >= 0) {
+        // Lane 0 issued the stores, so only it can wait for them; the flag is raised by lane 1.  A
+        // system-scope fence or release by lane 0 would also wait for the stores of the later tiles it
+        // has in flight (22 us per tile on four GPUs), which is what the lag is there to avoid; lane 1
+        // has no writes of its own, and its release is ordered after lane 0's wait by the warp barrier.
+        if (pend_shard[0] >= 0) {
+          if (lane == 0) {
             tma_store_wait<kFlagLag * (BN / 64)>();      // everything but the stores of the last kFlagLag tiles
             fence_proxy_async_global();
-            __threadfence_system();
-            st_release_sys(p.sig[pend_shard[0]] + kSigFlags + ((p.rank * p.max_tiles + pend_tile[0]) * kFlagsPerTile + q), p.epoch);
           }
-#pragma unroll
-          for (int i = 0; i + 1 < kFlagLag; ++i) { pend_shard[i] = pend_shard[i + 1]; pend_tile[i] = pend_tile[i + 1]; }
-          pend_shard[kFlagLag - 1] = shard;
-          pend_tile[kFlagLag - 1] = mb * tm.num_n + nb;
+          __syncwarp();
+          if (lane == 1)
+            st_release_sys(p.sig[pend_shard[0]] + kSigFlags + ((p.rank * p.max_tiles + pend_tile[0]) * kFlagsPerTile + q), p.epoch);
         }
+#pragma unroll
+        for (int i = 0; i + 1 < kFlagLag; ++i) { pend_shard[i] = pend_shard[i + 1]; pend_tile[i] = pend_tile[i + 1]; }
+        pend_shard[kFlagLag - 1] = shard;
+        pend_tile[kFlagLag - 1] = mb * tm.num_n + nb;
         __syncwarp();
       }
       if (ew == 0 && lane == 0 && it < 15) trace_at(p, 2 + 4 * it + 2);
@@ -591,14 +615,14 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (ew == 0 && lane == 0) trace_at(p, 62);
     if (lane == 0) {
       tma_store_wait<0>();
-      if (MODE == MODE_RS) {
-        fence_proxy_async_global();
-        __threadfence_system();
+      if (MODE == MODE_RS) fence_proxy_async_global();
+    }
+    __syncwarp();
+    if (MODE == MODE_RS && lane == 1) {
 #pragma unroll
-        for (int i = 0; i < kFlagLag; ++i)
-          if (pend_shard[i] >= 0)
-            st_release_sys(p.sig[pend_shard[i]] + kSigFlags + ((p.rank * p.max_tiles + pend_tile[i]) * kFlagsPerTile + q), p.epoch);
-      }
+      for (int i = 0; i < kFlagLag; ++i)
+        if (pend_shard[i] >= 0)
+          st_release_sys(p.sig[pend_shard[i]] + kSigFlags + ((p.rank * p.max_tiles + pend_tile[i]) * kFlagsPerTile + q), p.epoch);
     }
     __syncwarp();
     // out of tiles: help with the reduction of this rank's own rows
@@ -654,6 +678,7 @@ AX_API int ax_gemm_comm_signal_slots(int max_tiles) { return kSigFlags + kMaxRan
 // Diagnostic timeline: the launches that follow write globaltimer stamps of their phases into
 // `buf` ([grid][64] 64-bit slots, zero-filled by the caller); null turns it off again.
 static unsigned long long* g_trace_buf = nullptr;
+static int g_rs_pull = -1;
 AX_API void ax_gemm_comm_set_trace(void* buf) { g_trace_buf = (unsigned long long*)buf; }
 
 // mode 0: C[world*Tl, N] = act(allgather(x_local)[world*Tl, K] * op(B) + bias); `sym` = gathered buffers
@@ -667,6 +692,10 @@ AX_API void ax_gemm_comm_set_trace(void* buf) { g_trace_buf = (unsigned long lon
 // op(B): b_mn = 0: B is [N, K] row-major (a Linear weight); b_mn = 1: B is [K, N] row-major.
 // `grid` must be the same for every call on one communicator (the end-of-call counter relies on it)
 // and must not exceed the SM count.  Requires Tl % 128 == 0, K % 64 == 0, N % 64 == 0.
+// Reduce-scatter transport of MODE_RS: -1 = by rank count (in-switch reduction above two ranks when a
+// multicast mapping exists), 0 = partial tiles are pushed to the owner, 1 = the owner pulls the sum.
+AX_API void ax_gemm_comm_set_rs_pull(int mode) { g_rs_pull = mode; }
+
 AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out, void* const* sym, void* sym_mc,
                         void* const* sig, const void* bias, int bias_kind, int act, int Tl, int N, int K,
                         int b_mn, int rank, int world, unsigned epoch, int max_tiles, int pushers, int grid,
@@ -689,6 +718,9 @@ AX_API int ax_gemm_comm(int mode, const void* x_local, const void* B, void* out,
   p.bias = bias; p.bias_kind = bias ? bias_kind : 0; p.act = act;
   p.pushers = mode == MODE_AG ? pushers : 0;
   p.fill_own = p.lazy_done = (mode == MODE_AG && keep_gathered) ? 1 : 0;
+  // reduce-scatter transport: the in-switch reduction needs the multicast mapping; with two ranks the
+  // switch has nothing to add up and the push form (no read round trip) is faster
+  p.rs_pull = (mode == MODE_RS && sym_mc != nullptr && (g_rs_pull == 1 || (g_rs_pull < 0 && world > 2))) ? 1 : 0;
   p.max_tiles = max_tiles;
   p.status = status;
   p.trace = g_trace_buf;

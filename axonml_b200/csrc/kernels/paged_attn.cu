@@ -376,9 +376,12 @@ int launch_mma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, void
   return (int)cudaGetLastError();
 }
 
-// One CTA of D threads per (sequence, query head): combines the S partial results.
+// One CTA of D threads per (sequence, query head): combines the S partial results.  With `x8`
+// given, the result is also written as int8 blocks of 32 with their scales and scaled sums (the
+// input format of the decode matrix-vector kernels), one block per warp.
 __global__ void __launch_bounds__(D)
-paged_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int Hq, int S, long o_stride) {
+paged_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int Hq, int S, long o_stride,
+                   int8_t* __restrict__ x8, float* __restrict__ dx, float* __restrict__ sx) {
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const float* pp = part + ((long)b * Hq + h) * S * (D + 2);
   float M = -INFINITY;
@@ -390,7 +393,22 @@ paged_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ o
     L += pp[s * (D + 2) + D + 1] * f;
     O += pp[s * (D + 2) + d] * f;
   }
-  out[(long)b * o_stride + (long)h * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  const __nv_bfloat16 ob = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  out[(long)b * o_stride + (long)h * D + d] = ob;
+  if (x8 != nullptr) {
+    const float v = __bfloat162float(ob);
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = amax / 127.f;
+    const int q = sc > 0.f ? __float2int_rn(v / sc) : 0;
+    int qs = q;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);
+    const long e = ((long)b * Hq + h) * D + d;
+    x8[e] = (int8_t)q;
+    if ((d & 31) == 0) { dx[e >> 5] = sc; sx[e >> 5] = sc * (float)qs; }
+  }
 }
 
 }  // namespace
@@ -415,8 +433,9 @@ AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* 
                                      const int* block_table, const int* ctx_lens, int B, int Hq, int Hkv,
                                      int Dh, int page_size, int max_pages, float scale, long q_stride,
                                      long o_stride, int splits, float* workspace, int num_pages, int* status,
-                                     cudaStream_t stream) {
+                                     void* x8, float* dx, float* sx, cudaStream_t stream) {
   if (B <= 0) return 0;
+  if (x8 != nullptr && splits < 2) return -3;        // the int8 copy is written by the merge kernel
   if (Dh != D || Hq % Hkv || splits < 1 || (splits > 1 && !workspace)) return -1;
   const int G = Hq / Hkv;
   dim3 grid(B, Hkv, splits);
@@ -442,7 +461,7 @@ AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* 
     }
     if (e) return e;
     if (splits > 1) {
-      paged_merge_kernel<<<dim3(B, Hq), D, 0, stream>>>(workspace, (__nv_bfloat16*)out, Hq, splits, o_stride);
+      paged_merge_kernel<<<dim3(B, Hq), D, 0, stream>>>(workspace, (__nv_bfloat16*)out, Hq, splits, o_stride, (int8_t*)x8, dx, sx);
       return (int)cudaGetLastError();
     }
     return 0;
@@ -462,7 +481,7 @@ AX_API int ax_paged_decode_attention(const void* q, const void* kc, const void* 
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (splits > 1) {
-    paged_merge_kernel<<<dim3(B, Hq), D, 0, stream>>>(workspace, (__nv_bfloat16*)out, Hq, splits, o_stride);
+    paged_merge_kernel<<<dim3(B, Hq), D, 0, stream>>>(workspace, (__nv_bfloat16*)out, Hq, splits, o_stride, (int8_t*)x8, dx, sx);
     e = cudaGetLastError();
   }
   return (int)e;

@@ -70,19 +70,32 @@ __device__ __forceinline__ void scales_of_group(const uint4& hdr, int g, float& 
 }
 
 // A lane owns one 64-weight group (32 bytes of nibbles = sub-blocks 2g and 2g+1) of a super-block,
-// four lanes a super-block, a warp eight super-blocks per iteration - for R consecutive rows at
-// once: the int8 activations of the group (64 bytes per batch row) are loaded into registers once
-// and multiplied against R rows, which divides the L1 traffic per weight by R (with one row per
-// warp the kernel ran at 86 % of the L1 pipe and 2.2 TB/s).
-template <int NB, int R>
+// four lanes a super-block, for R consecutive rows at once: the int8 activations of the group (64
+// bytes per batch row) are loaded into registers once and multiplied against R rows, which divides
+// the L1 traffic per weight by R (with one row per warp the kernel ran at 86 % of the L1 pipe and
+// 2.2 TB/s).
+//
+// Shapes.  LPR lanes work on one row (LPR / 4 super-blocks per iteration); with short rows (K <
+// 2048, tensor-parallel shards) LPR is 16 or 8 and a warp takes 32 / LPR row groups side by side, so
+// no lane idles.  With few rows (N of a few thousand) KS warps of a CTA split the super-blocks of
+// their rows between them and add their partial sums through shared memory, so that the GPU still
+// holds a few thousand warps with loads in flight.
+template <int NB, int R, int LPR>
 __global__ void __launch_bounds__(256)
 q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, const float* __restrict__ dx,
-                const float* __restrict__ sx, void* __restrict__ out, int out_bf16, int N, int K, int tiled) {
+                const float* __restrict__ sx, void* __restrict__ out, int out_bf16, int N, int K, int tiled, int KS) {
+  constexpr int SUBS = 32 / LPR;                 // row groups side by side in a warp
+  __shared__ float part[8][SUBS * R * NB];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nsb = K / 256, per_row32 = K / 32;
-  const int sbi = lane >> 2, g = lane & 3;
+  const int sub = lane / LPR, l = lane % LPR;
+  const int sbi = l >> 2, g = l & 3;
   const long sb_stride = tiled ? 128L * kSB : kSB;
-  for (int row0 = (blockIdx.x * 8 + warp) * R; row0 < N; row0 += gridDim.x * 8 * R) {
+  const int ks = warp % KS, wg = warp / KS;      // split index, row-group index inside the CTA
+  const int rows_per_cta = (8 / KS) * SUBS * R;
+  const int sb_begin = (int)((long)nsb * ks / KS), sb_end = (int)((long)nsb * (ks + 1) / KS);
+  for (int base_row = blockIdx.x * rows_per_cta; base_row < N; base_row += gridDim.x * rows_per_cta) {
+    const int row0 = base_row + (wg * SUBS + sub) * R;
     const uint8_t* base[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -94,9 +107,9 @@ q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, co
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-    for (int sb0 = 0; sb0 < nsb; sb0 += 8) {
+    for (int sb0 = sb_begin; sb0 < sb_end; sb0 += LPR / 4) {
       const int sb = sb0 + sbi;
-      if (sb < nsb) {
+      if (sb < sb_end) {
         const int i32 = sb * 8 + 2 * g;
         const long xo = (long)sb * 256 + g * 64;
         int xl[NB][8], xh[NB][8];
@@ -146,9 +159,27 @@ q4k_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, co
       for (int b = 0; b < NB; ++b) {
         float v = acc[r][b];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && row0 + r < N) store_out(out, out_bf16, (long)b * N + row0 + r, v);
+        for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (KS == 1) {
+          if (l == 0 && row0 + r < N) store_out(out, out_bf16, (long)b * N + row0 + r, v);
+        } else if (l == 0) {
+          part[warp][(sub * R + r) * NB + b] = v;
+        }
       }
+    if (KS > 1) {                                  // uniform over the CTA: every warp runs the same row loop
+      __syncthreads();
+      if (ks == 0 && l == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            float v = 0.f;
+            for (int j = 0; j < KS; ++j) v += part[warp + j][(sub * R + r) * NB + b];
+            if (row0 + r < N) store_out(out, out_bf16, (long)b * N + row0 + r, v);
+          }
+      }
+      __syncthreads();
+    }
   }
 }
 
@@ -268,33 +299,52 @@ q80_gemv_kernel(const uint8_t* __restrict__ W, const int8_t* __restrict__ x8, co
 // x [B, K] bf16 (row stride ldx) times Q4_K W[N, K]^T -> out [B, N] (fp32, or bf16 when out_bf16), 1 <= B <= 8,
 // K % 256 == 0.
 // Scratch (caller-provided): x8 [B*K] int8, dx and sx [B*K/32] fp32.
+// `x` may be null: the activations are then already in x8 / dx / sx (written by a producer kernel,
+// decode_fused.cu) and no quantiser launch is made.
 AX_API int ax_q4k_gemv(const void* W, int tiled, const void* x, long ldx, void* x8, float* dx, float* sx, void* out,
                        int out_bf16, int B, int N, int K, cudaStream_t stream) {
   if (B < 1 || B > 8 || N <= 0 || K <= 0 || K % 256) return -1;
   if ((((uintptr_t)W) | ((uintptr_t)x8)) & 15) return -1;
   if ((((uintptr_t)dx) | ((uintptr_t)sx)) & 7) return -1;
   const long blocks32 = (long)B * (K / 32);
-  q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8, dx,
-                                                                                 sx, B, K);
-  // rows per warp: four reuse the activations best, but a narrow matrix then has fewer CTAs than SMs
+  if (x != nullptr)
+    q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8,
+                                                                                   dx, sx, B, K);
+  // Lanes per row: all 32 unless the row has fewer than 8 super-blocks.  Rows per lane (R): four reuse
+  // the activations best.  Then K is split over warps until the GPU holds about 16 warps per SM.
   const int sms = axh::sm_count();
-  const int R = (B <= 2 && N >= 32 * 2 * sms) ? 4 : (N >= 16 * 2 * sms ? 2 : 1);
-  int grid = (N + 8 * R - 1) / (8 * R);
-  const int cap = axh::sm_count() * 8;
+  const int nsb = K / 256;
+  const int LPR = nsb >= 5 ? 32 : (nsb >= 3 ? 16 : 8);
+  const int SUBS = 32 / LPR;
+  int ks_max = 1;                                     // every split keeps at least one full iteration of its lanes
+  if (B <= 4)
+    while (ks_max < 4 && nsb / (ks_max * 2) >= LPR / 4) ks_max *= 2;
+  int R = (B <= 2) ? 4 : 2;
+  while (R > 1 && (long)(N / (R * SUBS)) * ks_max < 16L * sms) R /= 2;  // even the widest split would not fill the GPU
+  int KS = 1;
+  while (KS < ks_max && (long)(N / (R * SUBS)) * KS < 16L * sms) KS *= 2;
+  const int rows_per_cta = (8 / KS) * SUBS * R;
+  int grid = (N + rows_per_cta - 1) / rows_per_cta;
+  const int cap = sms * 8;
   if (grid > cap) grid = cap;
   const auto* w = (const uint8_t*)W;
   const auto* q8 = (const int8_t*)x8;
-#define AX_GEMV(NB, RR) q4k_gemv_kernel<NB, RR><<<grid, 256, 0, stream>>>(w, q8, dx, sx, out, out_bf16, N, K, tiled)
+#define AX_GEMV(NB, RR, LL) q4k_gemv_kernel<NB, RR, LL><<<grid, 256, 0, stream>>>(w, q8, dx, sx, out, out_bf16, N, K, tiled, KS)
+#define AX_GEMV_L(NB, RR)                          \
+  if (LPR == 32) AX_GEMV(NB, RR, 32);              \
+  else if (LPR == 16) AX_GEMV(NB, RR, 16);         \
+  else AX_GEMV(NB, RR, 8);
 #define AX_GEMV_B(NB)                                             \
   case NB:                                                        \
-    if (R == 4 && NB <= 2) AX_GEMV(NB <= 2 ? NB : 1, 4);          \
-    else if (R == 2) AX_GEMV(NB, 2);                              \
-    else AX_GEMV(NB, 1);                                          \
+    if (R == 4 && NB <= 2) { AX_GEMV_L(NB <= 2 ? NB : 1, 4) }     \
+    else if (R >= 2) { AX_GEMV_L(NB, 2) }                         \
+    else { AX_GEMV_L(NB, 1) }                                     \
     break;
   switch (B) {
     AX_GEMV_B(1) AX_GEMV_B(2) AX_GEMV_B(3) AX_GEMV_B(4) AX_GEMV_B(5) AX_GEMV_B(6) AX_GEMV_B(7) AX_GEMV_B(8)
   }
 #undef AX_GEMV_B
+#undef AX_GEMV_L
 #undef AX_GEMV
   return (int)cudaGetLastError();
 }
@@ -307,8 +357,9 @@ AX_API int ax_q80_gemv(const void* W, const void* x, long ldx, void* x8, float* 
   if ((((uintptr_t)W) | ((uintptr_t)x8)) & 15) return -1;
   if (((uintptr_t)dx) & 7) return -1;
   const long blocks32 = (long)B * (K / 32);
-  q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8, dx,
-                                                                                 sx, B, K);
+  if (x != nullptr)      // null: x8 / dx already hold the quantised activations
+    q8_quantize_rows_kernel<<<(int)((blocks32 * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (int8_t*)x8,
+                                                                                   dx, sx, B, K);
   const int grid = (N + 127) / 128;
   const auto* w = (const uint8_t*)W;
   const auto* q8 = (const int8_t*)x8;

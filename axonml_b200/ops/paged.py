@@ -45,7 +45,7 @@ def decode_attention(q, k_cache, v_cache, block_table, ctx_lens, page_size: int,
                                                 N.ptr(ctx_lens), B, Hq, Hkv, D, page_size, block_table.shape[1],
                                                 N.c_float(scale), N.c_int64(q.stride(0)), N.c_int64(out.stride(0)),
                                                 splits, N.ptr(ws) if ws is not None else None, k_cache.shape[0],
-                                                N.ptr(N.status_word(q.device)), N.stream_ptr())
+                                                N.ptr(N.status_word(q.device)), N.ptr(None), N.ptr(None), N.ptr(None), N.stream_ptr())
         N.check(rc, "ax_paged_decode_attention")
         return out
     outs = []

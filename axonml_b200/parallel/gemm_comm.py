@@ -108,6 +108,10 @@ class FusedGemmComm:
     def try_create(cls, pg):
         if not (available(pg) and N.is_blackwell()) or pg.world_size() > 8:
             return None
+        # AXONML_TP_RS=push|pull overrides the reduce-scatter transport (default: in-switch reduction
+        # above two ranks when the buffers have a multicast mapping)
+        mode = os.environ.get("AXONML_TP_RS", "auto")
+        N.cuda().ax_gemm_comm_set_rs_pull({"push": 0, "pull": 1}.get(mode, -1))
         return cls(pg)
 
     # ------------------------------------------------------------------ shape checks

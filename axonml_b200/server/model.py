@@ -215,6 +215,11 @@ class QuantizedLlama:
         return dequantize_tensor(q, torch.bfloat16)
 
     def _logits(self, h: torch.Tensor) -> torch.Tensor:
+        from ..ops import decode as Dc
+        if (h.dim() == 2 and h.shape[0] <= 4 and h.is_contiguous() and Dc.supported(h)
+                and Dc.gemv_ok(self.head, h.shape[0])):
+            a, _, _ = Dc.rms_norm_q8(h, self.final_norm, self.cfg.rms_norm_eps)     # norm -> int8 for the head kernel
+            return Dc.qgemv(a, self.head, out_dtype=torch.float32)
         return qlinear(Nm.rms_norm(h, self.final_norm, self.cfg.rms_norm_eps), self.head, out_dtype=torch.float32)
 
     def greedy(self, h: torch.Tensor) -> torch.Tensor:
@@ -270,10 +275,52 @@ class QuantizedLlama:
             x = x + d
         return x.view(B, S, -1)[:, -1]
 
+    def _fused_decode_ok(self, B: int, cache) -> bool:
+        """Batches of up to four rows on the matrix-vector kernels: every producer writes int8
+        activations itself and RoPE + KV write are one launch (``ops/decode.py``)."""
+        import os
+        from ..ops import decode as Dc
+        if os.environ.get("AXONML_DECODE_FUSED", "1") == "0" or self.hd != 128 or not self.layers:
+            return False
+        from .. import _native as N
+        L = self.layers[0]
+        return (N.is_blackwell() and self.device.type == "cuda" and self.cfg.hidden_size % 32 == 0 and self.ffn % 32 == 0
+                and self.hq // self.hkv in (1, 2, 4, 8)
+                and all(Dc.gemv_ok(w, B) for w in (L.wqkv, L.wo, L.wgu, L.wdown)))
+
+    def _decode_fused(self, tokens, cache, slots_t, positions) -> torch.Tensor:
+        """The decode step with ten launches per layer: qkv product, rope + q copy + KV write,
+        attention (split and merge, the merge writing int8), o product, add + norm -> int8, gate|up
+        product, SwiGLU -> int8, down product, add + norm -> int8."""
+        from ..ops import decode as Dc
+        B = tokens.shape[0]
+        eps = self.cfg.rms_norm_eps
+        x = self._embed(tokens)
+        ctx = positions + 1
+        table = cache.block_table[slots_t.long()].contiguous()
+        seq_local = torch.arange(B, dtype=torch.int32, device=self.device)
+        a, x, _ = Dc.rms_norm_q8(x, self.layers[0].attn_norm, eps)
+        for li, L in enumerate(self.layers):
+            qkv = Dc.qgemv(a, L.wqkv).view(B, self.hq + 2 * self.hkv, self.hd)
+            q = Dc.rope_kv_write(qkv, self.cos, self.sin, positions, cache.k[li], cache.v[li], table, seq_local,
+                                 self.hq, self.hkv, cache.page_size)
+            _, a = Dc.decode_attention_q8(q, cache.k[li], cache.v[li], table, ctx, cache.page_size)
+            o = self._all_reduce(Dc.qgemv(a, L.wo))
+            a, x, _ = Dc.rms_norm_q8(x, L.ffn_norm, eps, residual=o)
+            a = Dc.swiglu_q8(Dc.qgemv(a, L.wgu))
+            d = self._all_reduce(Dc.qgemv(a, L.wdown))
+            if li + 1 < len(self.layers):
+                a, x, _ = Dc.rms_norm_q8(x, self.layers[li + 1].attn_norm, eps, residual=d)
+            else:
+                x = x + d
+        return x
+
     def decode(self, tokens: torch.Tensor, cache, slots_t: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """One token per running sequence.  ``tokens`` [B], ``slots_t`` [B] int32 cache slots,
         ``positions`` [B] int32 position of the new token.  Returns the hidden state [B, H]."""
         B = tokens.shape[0]
+        if B <= 4 and self._fused_decode_ok(B, cache):
+            return self._decode_fused(tokens, cache, slots_t, positions)
         x = self._embed(tokens)
         ctx = positions + 1
         table = cache.block_table[slots_t.long()]

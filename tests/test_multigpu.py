@@ -155,7 +155,7 @@ def test_fsdp_gather_inside_the_first_gemm_matches_nccl_gathers(nvls):
         # was taken over by a later unit (the last 3 are still resident when backward reaches them)
         assert n1 == 0 and n2 == 3 * (5 + 2), (n1, n2)
         assert max(abs(a - b) for a, b in zip(l1, l2)) < 3e-2, (l1, l2)
-        assert mean < 1e-4, mean
+        assert mean < 5e-4, mean           # three AdamW steps of lr 1e-3 on bf16 gradients summed in another order
 
 
 def _fsdp_lamb(rank, world, be):
@@ -463,7 +463,8 @@ def _vocab_parallel_gpu(rank, world, be):
     """Vocabulary-parallel embedding, head and loss on GPUs against the unsharded computation."""
     from axonml_b200 import _native
     from axonml_b200.parallel import ProcessGroup
-    from axonml_b200.parallel.tensor_parallel import VocabParallelEmbedding, vocab_parallel_cross_entropy
+    from axonml_b200.parallel.tensor_parallel import (VocabParallelEmbedding, copy_to_tensor_parallel,
+                                                       vocab_parallel_cross_entropy)
     pg = ProcessGroup(be)
     V, Vpad, H, T = 1000, 1024, 256, 512            # the real vocabulary does not fill the padded split
     per = Vpad // world
@@ -479,7 +480,8 @@ def _vocab_parallel_gpu(rank, world, be):
     w_local = head[rank * per:(rank + 1) * per].clone().requires_grad_(True)
     launches = _native.launch_count()
     h = emb(ids)
-    logits = torch.nn.functional.linear(h, w_local)
+    # the head is column-parallel: each rank's data gradient is a partial sum, added up in backward
+    logits = torch.nn.functional.linear(copy_to_tensor_parallel(h, pg), w_local)
     loss = vocab_parallel_cross_entropy(logits, target, pg, rank * per, -100, V)
     loss.backward()
     used_kernels = _native.launch_count() - launches
