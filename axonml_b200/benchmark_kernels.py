@@ -6,6 +6,7 @@ file is present in the working directory, else the stated fallback figures).
     python -m axonml_b200.benchmark_kernels all --iters 20
     python -m axonml_b200.benchmark_kernels gemm_shapes                 # tile policies against cuBLAS
     python -m axonml_b200.benchmark_kernels gemv_shapes                 # decode matrix-vector kernels, both layouts
+    python -m axonml_b200.benchmark_kernels flash_timeline              # in-kernel timeline of the flash forward
     python -m axonml_b200.benchmark_kernels gemm --small                # a few launches on a small case
                                                                         # (what a profiler capture uses)
 
@@ -171,6 +172,42 @@ def gemv_shapes(iters):
         print(line, flush=True)
 
 
+def flash_timeline(blocks: int = 8):
+    """In-kernel timeline of the two-tile flash forward (the kernel stamps ``globaltimer`` when a
+    trace buffer is set): per KV block of the first, longest CTA the softmax warps of tile A and
+    tile B record when the scores are ready, in registers, the row maximum is known, the
+    exponentials are done and the probabilities are stored."""
+    import ctypes
+    from .ops.flash import flash_attention
+    q, k, v = (torch.randn(4, 2048, 16, 128, device="cuda").bfloat16() for _ in range(3))
+    with torch.no_grad():
+        for _ in range(3):
+            flash_attention(q, k, v, True)
+        torch.cuda.synchronize()
+        tr = torch.zeros(4 * 128, dtype=torch.int64, device="cuda")
+        _native.cuda().ax_flash_fwd_set_trace(ctypes.c_void_p(tr.data_ptr()))
+        try:
+            flash_attention(q, k, v, True)
+            torch.cuda.synchronize()
+        finally:
+            _native.cuda().ax_flash_fwd_set_trace(ctypes.c_void_p(0))
+    t = tr.cpu().view(4, 128)
+    for tile in range(2):
+        r = [int(x) for x in t[tile]]
+        if r[0] == 0:
+            continue
+        print(f"tile {'AB'[tile]}: softmax loop done {(r[127] - r[0]) / 1e3:.2f} us after the CTA's start")
+        prev = r[0]
+        for j in range(blocks):
+            s = r[1 + 5 * j:6 + 5 * j]
+            if s[0] == 0:
+                break
+            print(f"  block {j:2d}: wait for scores {(s[0] - prev) / 1e3:5.2f} | TMEM load {(s[1] - s[0]) / 1e3:5.2f} | "
+                  f"max / rescale {(s[2] - s[1]) / 1e3:5.2f} | exponentials {(s[3] - s[2]) / 1e3:5.2f} | "
+                  f"store + arrive {(s[4] - s[3]) / 1e3:5.2f}  (us)")
+            prev = s[4]
+
+
 def w_paged(small):
     from .ops import paged
     B, ctx, Hq, Hkv, D, page = (8, 512, 32, 8, 128, 16) if small else (64, 768, 32, 8, 128, 16)
@@ -261,6 +298,10 @@ def main():
     from . import _native
     if a.names == ["gemm_shapes"]:
         gemm_shapes(a.iters)
+        _native.check_status()
+        return
+    if a.names == ["flash_timeline"]:
+        flash_timeline()
         _native.check_status()
         return
     if a.names == ["gemv_shapes"]:

@@ -196,6 +196,83 @@ fused_allreduce_kernel(const Peers P, long base_off, long n, float mul, const fl
   if (blockIdx.x == 0 && threadIdx.x == 0 && epoch_dev != nullptr) *(volatile uint32_t*)epoch_dev = epoch;
 }
 
+// ---------------------------------------------------------------------------------------------
+// One-shot sum for small vectors (tensor-parallel decode: a few KB per call, two calls per layer).
+// The two-shot kernel above needs a start barrier, a reduce / broadcast round and an end barrier,
+// three trips across NVLink; here every rank writes its vector into slot `rank` of every rank's
+// staging area (one multimem store per 16 bytes when the switch multicasts, W peer stores
+// otherwise), raises one flag per peer, waits for the W flags of its own area and adds the W
+// slots it holds: one trip.  Two staging areas alternate by call parity: a rank can only reach
+// call e + 2 after every peer has signalled call e + 1, i.e. after every peer has finished
+// reading call e.  One CTA; the call counter lives on the device (CUDA-graph capture).
+//   staging: [2 parities][W slots][slot_bytes]; flags (after the barrier words): [2][W].
+constexpr int kOneShotThreads = 512;
+constexpr int kOneShotFlags = 2 * kMaxRanks + 4;      // first flag word inside the signal array
+
+template <bool BF16, bool MC>
+__global__ void __launch_bounds__(kOneShotThreads)
+oneshot_allreduce_kernel(const Peers P, const uint8_t* __restrict__ x, uint8_t* __restrict__ out, long bytes,
+                         long slot_bytes, float mul, uint32_t* epoch_dev, int* status) {
+  __shared__ int s_ok;
+  const uint32_t epoch = *(volatile uint32_t*)epoch_dev + 1;
+  const int par = (int)(epoch & 1u);
+  const long area = (long)par * P.world * slot_bytes;
+  if (threadIdx.x == 0) s_ok = 1;
+  for (long o = (long)threadIdx.x * 16; o < bytes; o += (long)kOneShotThreads * 16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + o);
+    const long dst = area + (long)P.rank * slot_bytes + o;
+    if (MC) {
+      multimem_st_b32x4((char*)P.mc_buf + dst, v);
+    } else {
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p)
+        if (p < P.world) st_peer_v4((char*)P.buf[(P.rank + p) % P.world] + dst, v);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < P.world) {
+    st_release_sys(P.sig[threadIdx.x] + kOneShotFlags + par * kMaxRanks + P.rank, epoch);
+    if (!wait_ge<true>(P.sig[P.rank] + kOneShotFlags + par * kMaxRanks + threadIdx.x, epoch, status, 620)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const uint8_t* mine = (const uint8_t*)P.buf[P.rank] + area;
+    for (long o = (long)threadIdx.x * 16; o < bytes; o += (long)kOneShotThreads * 16) {
+      float a[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] = 0.f;
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p)
+        if (p < P.world) v[p] = ld_peer_v4(mine + (long)p * slot_bytes + o);
+#pragma unroll
+      for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < P.world) {
+          if (BF16) {
+            acc_bf16x8(a, v[p]);
+          } else {
+            a[0] += __uint_as_float(v[p].x); a[1] += __uint_as_float(v[p].y);
+            a[2] += __uint_as_float(v[p].z); a[3] += __uint_as_float(v[p].w);
+          }
+        }
+      }
+      uint4 r;
+      if (BF16) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] *= mul;
+        r = pack_bf16x8(a);
+      } else {
+        r = make_uint4(__float_as_uint(a[0] * mul), __float_as_uint(a[1] * mul), __float_as_uint(a[2] * mul),
+                       __float_as_uint(a[3] * mul));
+      }
+      *reinterpret_cast<uint4*>(out + o) = r;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *(volatile uint32_t*)epoch_dev = epoch;
+}
+
 struct AdamW {
   float lr, beta1, beta2, eps, wd, bc1, bc2, mul;
 };
@@ -346,7 +423,31 @@ Peers make_peers(void* const* bufs, void* const* sigs, void* mc, int rank, int w
 }  // namespace
 
 // Number of 32-bit signal slots a communicator must provide per rank (zero-initialised once).
-AX_API int ax_comm_signal_slots() { return 2 * axc::kMaxRanks + 4; }
+AX_API int ax_comm_signal_slots() { return 2 * axc::kMaxRanks + 4 + 2 * axc::kMaxRanks; }
+
+// out = mul * sum over ranks of x (`bytes` of bf16 (dtype 1) or fp32 (dtype 0), a multiple of 16, at most
+// `slot_bytes`); x and out may be the same ordinary device buffer.  `bufs` are the ranks' staging buffers of
+// 2 * world * slot_bytes bytes; `epoch_dev` is this communicator's call counter on the device (one per
+// communicator, used for nothing else).  Every rank must make the same sequence of calls.
+AX_API int ax_oneshot_allreduce(int dtype, void* const* bufs, void* const* sigs, void* mc_buf, int rank, int world,
+                                const void* x, void* out, long bytes, long slot_bytes, float mul, unsigned* epoch_dev,
+                                int* status, cudaStream_t stream) {
+  if (world < 1 || world > axc::kMaxRanks || bytes <= 0 || bytes % 16 || slot_bytes % 16 || bytes > slot_bytes ||
+      epoch_dev == nullptr)
+    return -1;
+  if (((uintptr_t)x | (uintptr_t)out) & 15) return -1;
+  Peers P = make_peers(bufs, sigs, mc_buf, rank, world);
+  const auto* xi = (const uint8_t*)x;
+  auto* xo = (uint8_t*)out;
+  if (dtype == 1) {
+    if (mc_buf) oneshot_allreduce_kernel<true, true><<<1, kOneShotThreads, 0, stream>>>(P, xi, xo, bytes, slot_bytes, mul, epoch_dev, status);
+    else oneshot_allreduce_kernel<true, false><<<1, kOneShotThreads, 0, stream>>>(P, xi, xo, bytes, slot_bytes, mul, epoch_dev, status);
+  } else {
+    if (mc_buf) oneshot_allreduce_kernel<false, true><<<1, kOneShotThreads, 0, stream>>>(P, xi, xo, bytes, slot_bytes, mul, epoch_dev, status);
+    else oneshot_allreduce_kernel<false, false><<<1, kOneShotThreads, 0, stream>>>(P, xi, xo, bytes, slot_bytes, mul, epoch_dev, status);
+  }
+  return (int)cudaGetLastError();
+}
 
 // In-place mean all-reduce of `n` elements (dtype: 0 fp32, 1 bf16) located at byte offset
 // `base_off` of every rank's symmetric buffer.  n * elsize must be a multiple of 16 * world.

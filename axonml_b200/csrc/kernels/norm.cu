@@ -211,7 +211,13 @@ template <typename WT, int NV>
 int launch_fwd_reg(bool rms, const void* x, const void* res, const void* w, const void* b, void* y, void* hout,
                    float* mean, float* rstd, int rows, int D, float eps, cudaStream_t stream) {
   int grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
-  const int cap = axh::sm_count() * (NV <= 8 ? 8 : 4);
+  // One resident wave: a warp then walks over several rows with the weights it loaded once.  (With eight
+  // CTAs per SM in the grid a [8192, 2048] call gave every warp ONE row and 8 KB of weights to load for
+  // it: 60 us for 134 MB in the GPT-1.3B step.)
+  int occ = 1;
+  if (rms) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_fwd_reg_kernel<WT, true, NV>, kWarpsPerCta * 32, 0);
+  else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, norm_fwd_reg_kernel<WT, false, NV>, kWarpsPerCta * 32, 0);
+  const int cap = axh::sm_count() * (occ < 1 ? 1 : occ);
   if (grid > cap) grid = cap;
   using T = __nv_bfloat16;
   if (rms)

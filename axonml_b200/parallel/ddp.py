@@ -16,6 +16,7 @@ found-inf flag, so unscaling costs no extra pass.
 from __future__ import annotations
 
 import contextlib
+import os
 import enum
 
 import torch
@@ -147,7 +148,10 @@ class DistributedDataParallel(Module):
                 for b in self._buckets:
                     by_dtype.setdefault(b.flat.dtype, []).append(b)
                 for dt, bs in by_dtype.items():
-                    far = F.FusedAllReduce.try_create(self.pg, sum(b.padded for b in bs), dt)
+                    # CTAs of the all-reduce kernel: they sit on SMs while they wait for the other ranks, next
+                    # to the backward kernels that are still running, so no more than the bucket needs
+                    blocks = int(os.environ.get("AXONML_DDP_AR_BLOCKS", "16"))      # 4 GPUs, ResNet-18: 17.6 ms/step with 32, 15.5 with 16
+                    far = F.FusedAllReduce.try_create(self.pg, sum(b.padded for b in bs), dt, grid_blocks=blocks)
                     if far is None:
                         continue
                     off = 0

@@ -34,6 +34,9 @@ class FusedAllReduce:
         align = 8 * heap.world * 16
         self.capacity = (max_numel + align - 1) // align * align
         self.stage = heap.allocate(self.capacity, dtype)
+        self._small = None
+        if device_epoch:            # serving: the one-trip path for decode-sized vectors, allocated before any capture
+            self._alloc_small()
 
     @classmethod
     def try_create(cls, pg, max_numel: int, dtype: torch.dtype, grid_blocks: int = 32, device_epoch: bool = False):
@@ -76,6 +79,35 @@ class FusedAllReduce:
         N.check(rc, "ax_fused_allreduce")
         if not in_place:
             flat.copy_(stage[:n])
+
+
+    # ------------------------------------------------------------------ small vectors (decode)
+    SMALL_BYTES = 64 * 1024
+
+    def _alloc_small(self) -> None:
+        self._small = self.heap.allocate(2 * self.heap.world * self.SMALL_BYTES // 2, torch.bfloat16)
+        self._small_epoch = torch.zeros(1, dtype=torch.int32, device=self.heap.device)
+        self.heap.barrier()
+
+    def sum_small_(self, x: torch.Tensor, scale: float = 1.0) -> bool:
+        """In-place ``x = scale * sum over ranks of x`` for a contiguous vector of at most
+        ``SMALL_BYTES`` (a multiple of 16 bytes) through the one-trip kernel: every rank writes its
+        vector into every rank's staging area and adds what it received.  ``x`` is an ordinary
+        tensor (no staging copy).  Graph-capturable: the call counter is on the device.  Returns
+        False (nothing done) when the vector does not qualify."""
+        nbytes = x.numel() * x.element_size()
+        if (x.dtype != self.dtype or not x.is_contiguous() or nbytes > self.SMALL_BYTES or nbytes % 16
+                or x.data_ptr() % 16):
+            return False
+        if self._small is None:
+            self._alloc_small()
+        rc = N.cuda().ax_oneshot_allreduce(
+            1 if self.dtype == torch.bfloat16 else 0, self._small.ptr_array(), self.comm.signals.ptr_array(),
+            self._small.mc(), self.heap.rank, self.heap.world, N.ptr(x), N.ptr(x), ctypes.c_long(nbytes),
+            ctypes.c_long(self.SMALL_BYTES), ctypes.c_float(scale), N.ptr(self._small_epoch),
+            N.ptr(N.status_word(x.device)), N.stream_ptr())
+        N.check(rc, "ax_oneshot_allreduce")
+        return True
 
 
 class FusedShardedAdamW:

@@ -22,6 +22,7 @@ around a CPU matmul).
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 
 import torch
@@ -33,6 +34,7 @@ from .symm import SymmetricHeap, available
 
 _MAX_TILES = 4096
 _PUSHER_GBS = 22.0        # what one copy CTA sends per second (700 GB/s from 32 CTAs, measured)
+_PUSHER_MC_GBS = 11.0     # the same through multimem stores (4 GPUs: 8 copy CTAs deliver a 33.5 MB shard in 365 us)
 _LINK_GBS = 700.0         # what a GPU receives per second over NVLink (measured peer copy)
 
 
@@ -41,11 +43,21 @@ def _pushers(tl: int, k: int, n: int, world: int, grid: int, multimem: bool) -> 
     has anyway (most of the GEMM, or the time the GPU needs to receive the other shards, whichever
     is longer), no more: every copy CTA is one SM less for the math.  With NVSwitch multicast a
     shard leaves the GPU once, whatever the number of peers."""
+    forced = os.environ.get("AXONML_TP_PUSHERS")
+    if forced:
+        return int(min(max(int(forced), 1), grid // 2))
     gemm_s = 2.0 * world * tl * k * n / 1.4e15
     recv_s = (world - 1) * tl * k * 2 / (_LINK_GBS * 1e9)
-    copies = 1 if (multimem and world > 2) else world - 1
-    need = tl * k * 2 * copies / (_PUSHER_GBS * 1e9) / max(0.6 * gemm_s, recv_s, 1e-6)
-    return int(min(max(need + 0.999, 2), 24, grid // 4))
+    mc = multimem and world > 2
+    copies = 1 if mc else world - 1
+    rate = _PUSHER_MC_GBS if mc else _PUSHER_GBS
+    need = tl * k * 2 * copies / (rate * 1e9) / max(0.6 * gemm_s, recv_s, 1e-6)
+    need = min(max(need, 2.0), 24.0, grid // 4)
+    # a copy CTA takes whole 128-row chunks: with a count that does not divide the chunks some CTAs
+    # run one round more than the others, which costs SMs without shortening the transfer
+    chunks = max(tl // 128, 1)
+    rounds = max(1, math.ceil(chunks / need - 1e-9))
+    return int(max(2, min(math.ceil(chunks / rounds), grid // 4)))
 
 
 class _Channel:

@@ -200,6 +200,8 @@ class QuantizedLlama:
                 self._ar32 = FusedAllReduce.try_create(self.pg, 4096, torch.float32, device_epoch=True) if self._ar else None
         if self._ar and x.dtype == torch.bfloat16 and x.numel() <= self._ar.capacity:
             flat = x.reshape(-1)
+            if x.is_contiguous() and self._ar.sum_small_(flat):          # decode-sized vectors: one trip, no staging copy
+                return x
             self._ar.all_reduce_mean_(flat)
             return x.mul_(self.tp)
         from ..parallel.backend import ReduceOp
@@ -244,8 +246,9 @@ class QuantizedLlama:
             # (graph-capturable, unlike the process group's all-gather)
             out = torch.zeros((self.tp,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
             out[self.rank] = pair
-            ar32.all_reduce_mean_(out.view(-1))
-            out = out * self.tp
+            if not ar32.sum_small_(out.view(-1)):
+                ar32.all_reduce_mean_(out.view(-1))
+                out = out * self.tp
         else:
             out = torch.empty((self.tp,) + tuple(pair.shape), dtype=pair.dtype, device=pair.device)
             self.pg.backend().all_gather(pair, out)

@@ -59,6 +59,54 @@ def test_fused_allreduce(dtype, nvls):
         assert out["inf"] == 1
 
 
+def _oneshot_sum(rank, world, be):
+    """The one-trip sum of decode-sized vectors against NCCL, several calls in a row (the two staging
+    areas alternate), eager and replayed from a CUDA graph."""
+    from axonml_b200 import _native
+    from axonml_b200.parallel import ProcessGroup
+    from axonml_b200.parallel.fused import FusedAllReduce
+    pg = ProcessGroup(be)
+    out = {}
+    for dtype_name in ("bfloat16", "float32"):
+        dtype = getattr(torch, dtype_name)
+        far = FusedAllReduce.try_create(pg, 65536, dtype, device_epoch=True)
+        assert far is not None
+        worst = 0.0
+        for it, n in enumerate((4096, 8, 32768 if dtype == torch.bfloat16 else 16384, 4096, 520)):
+            torch.manual_seed(7 * it + rank)
+            x = torch.randn(n, device="cuda").to(dtype)
+            ref = x.clone().float()
+            torch.distributed.all_reduce(ref)
+            assert far.sum_small_(x, 0.5)
+            worst = max(worst, ((x.float() - 0.5 * ref).abs().max() / ref.abs().max()).item())
+        # captured once, replayed three times on fresh data
+        x = torch.zeros(4096, device="cuda", dtype=dtype)
+        src = torch.randn(3, 4096, device="cuda").to(dtype) + rank
+        g = torch.cuda.CUDAGraph()
+        x.copy_(src[0])
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            far.sum_small_(x)
+        for i in range(3):
+            x.copy_(src[i])
+            g.replay()
+            ref = src[i].clone().float()
+            torch.distributed.all_reduce(ref)
+            worst = max(worst, ((x.float() - ref).abs().max() / ref.abs().max()).item())
+        assert not far.sum_small_(torch.zeros(7, device="cuda", dtype=dtype))      # not a multiple of 16 bytes
+        torch.cuda.synchronize()
+        _native.check_status()
+        out[dtype_name] = worst
+    return out
+
+
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_one_trip_sum_of_small_vectors(nvls):
+    res = run_gpu_ranks(_oneshot_sum, WORLD, env={"AXONML_NVLS": nvls})
+    for r in range(WORLD):
+        assert res[r][1]["bfloat16"] < 2e-2 and res[r][1]["float32"] < 1e-5, res[r][1]
+
+
 def _fsdp_fused_vs_nccl(rank, world, be):
     import copy
     from axonml_b200 import _native, optim
