@@ -128,11 +128,24 @@ class PlatformServer:
     def __init__(self, host: str = "127.0.0.1", port: int = 3021, data_dir: str | None = None, jwt_secret: str | None = None,
                  inference: InferenceServer | None = None, llm_engine=None, tokenizer=None, allow_registration: bool | None = None,
                  admin_email: str = "admin@axonml.local", admin_password: str | None = None,
-                 enable_terminal: bool = False):
+                 enable_terminal: bool = False, secrets=None, email=None, ollama_url: str | None = None,
+                 ollama_model: str | None = None, public_url: str | None = None):
+        """``secrets``: an ``integrations.secrets.SecretsManager`` (default: Vault when ``VAULT_ADDR``
+        is set, then ``AXONML_*`` environment variables) consulted for the JWT secret and the e-mail
+        API key.  ``email``: an ``integrations.email.EmailService``; when it is configured, new
+        accounts must confirm their address through a mailed link before they can sign in.
+        ``ollama_url``: daemon behind the notebook AI assist.  ``public_url``: origin users reach
+        the server at (links in e-mails, WebAuthn relying-party origin)."""
+        from ...integrations.email import EmailService
+        from ...integrations.secrets import SecretKey, SecretsManager
         self.data_dir = data_dir
         self.store = DocumentStore(os.path.join(data_dir, "db") if data_dir else None)
         files = os.path.join(data_dir, "files") if data_dir else os.path.join(_tmp_root(), "files")
-        secret = jwt_secret or self.store.kv_get("jwt_secret")
+        self.secrets = secrets if secrets is not None else SecretsManager.default()
+        self.email = email if email is not None else EmailService(self.secrets.get_secret_optional(SecretKey.RESEND_API_KEY))
+        self.ollama_url = ollama_url or os.environ.get("AXONML_OLLAMA_URL")
+        self.ollama_model = ollama_model or os.environ.get("AXONML_OLLAMA_MODEL")
+        secret = jwt_secret or self.secrets.get_secret_optional(SecretKey.JWT_SECRET) or self.store.kv_get("jwt_secret")
         if not secret:
             secret = os.urandom(32).hex()
             self.store.kv_set("jwt_secret", secret)
@@ -162,6 +175,10 @@ class PlatformServer:
         self.httpd = ThreadingHTTPServer((host, port), _make_handler(self))
         self.httpd.daemon_threads = True
         self.port = self.httpd.server_address[1]
+        self.public_url = (public_url or f"http://localhost:{self.port}").rstrip("/")
+        from urllib.parse import urlparse as _urlparse
+        from .webauthn import WebAuthnAuth
+        self.webauthn = WebAuthnAuth(_urlparse(self.public_url).hostname or "localhost", "AxonML", self.public_url)
         self._thread = None
 
     # ------------------------------------------------------------------ users
@@ -172,12 +189,15 @@ class PlatformServer:
             raise AlreadyExists(f"user {email}")
         return self.users.insert({"email": email.lower(), "name": name, "password_hash": A.hash_password(password),
                                   "role": role, "mfa_enabled": False, "totp_secret": None, "pending_totp_secret": None,
-                                  "recovery_codes": [], "email_verified": True, "approved": True, "last_login": None})
+                                  "recovery_codes": [], "webauthn_credentials": [], "email_verified": True,
+                                  "approved": True, "last_login": None})
 
     @staticmethod
     def public_user(u: dict) -> dict:
-        return {k: u.get(k) for k in ("id", "email", "name", "role", "mfa_enabled", "email_verified", "approved",
-                                      "created_at", "last_login")}
+        out = {k: u.get(k) for k in ("id", "email", "name", "role", "mfa_enabled", "email_verified", "approved",
+                                     "created_at", "last_login")}
+        out["webauthn_enabled"] = bool(u.get("webauthn_credentials"))
+        return out
 
     # ------------------------------------------------------------------ dispatch
     def authenticate(self, req: Request, access: str) -> None:

@@ -5,8 +5,7 @@ Parity: JWT claims ``sub/email/role/exp/iat/token_type/mfa_verified`` and the to
 token shapes (crates/axonml-server/src/auth/jwt.rs:12-46, 84-227); TOTP SHA-1, 6 digits, 30 s
 period, one step of tolerance (auth/totp.rs:84-98); ten ``NNNNN-NNNNN`` recovery codes stored only
 as salted hashes and consumed on use (auth/recovery.rs:28-87); roles admin/user/viewer
-(db/users.rs:16-27).  WebAuthn needs a browser authenticator and is not offered: the endpoints
-answer 501."""
+(db/users.rs:16-27).  The WebAuthn second factor lives in ``webauthn.py``."""
 from __future__ import annotations
 
 import base64

@@ -7,8 +7,8 @@ error_name / error_value / traceback (crates/axonml-server/src/db/notebooks.rs:1
 endpoints create / import / export / start / stop / add, update, delete and execute a cell
 (api/notebooks.rs).  The reference's executor compiles Rust cells with cargo; here a cell is Python
 run by a kernel process of the notebook (never inside the server process) in a namespace that
-persists across the notebook's cells, with ``axonml_b200`` importable.  The
-AI-assist endpoint needs an external Ollama daemon and answers 503 without one."""
+persists across the notebook's cells, with ``axonml_b200`` importable.  The AI-assist endpoint
+asks the configured Ollama daemon (``integrations/ollama.py``) and answers 503 when none runs."""
 from __future__ import annotations
 
 import json

@@ -1,9 +1,16 @@
 """Authentication and administration routes (crates/axonml-server/src/api/auth.rs; route table
-api/mod.rs:111-146, 342-350): register, login (with the MFA hand-off token), logout, refresh, me,
-TOTP setup / enable / verify, recovery codes, MFA disable, user administration, admin query."""
+api/mod.rs:111-146, 342-350): register (with e-mail verification when a mail service is
+configured), login (with the MFA hand-off token), logout, refresh, me, TOTP setup / enable /
+verify, WebAuthn registration and assertion, recovery codes, MFA disable, user administration,
+admin query."""
 from __future__ import annotations
 
+import hashlib
+import os
+import time
+
 from . import auth as A
+from . import webauthn as W
 from .api import ADMIN, PUBLIC, USER, HttpError
 from .store import now_iso
 
@@ -26,17 +33,48 @@ def register(app) -> None:
             raise HttpError(400, "a valid e-mail address and a password of at least 8 characters are required")
         role = "admin" if app.users.count() == 0 else "user"      # the first account administers the server
         u = app.create_user(email, name, password, role)
+        if role == "user" and app.email.is_configured():
+            # the address has to be confirmed through the mailed link before the account can sign in
+            token = os.urandom(24).hex()
+            u = app.users.update(u["id"], {"email_verified": False, "approved": False,
+                                           "verify_token_hash": hashlib.sha256(token.encode()).hexdigest(),
+                                           "verify_expires": time.time() + 24 * 3600})
+            try:
+                app.email.send_verification_email(u["email"], u["name"], f"{app.public_url}/api/auth/verify-email?token={token}")
+                for adm in app.users.find({"role": "admin"}):
+                    app.email.send_admin_signup_notification(adm["email"], u["email"], u["name"])
+            except Exception as e:                      # the account exists; an administrator can still approve it
+                return 201, {"user": app.public_user(u), "message": f"registered; the verification e-mail could not be sent ({e})"}
+            return 201, {"user": app.public_user(u), "message": "registered; check your inbox for the verification link"}
         return 201, {"user": app.public_user(u), "message": "registered"}
+
+    def auth_verify_email(req):
+        token = req.q("token") or (req.json or {}).get("token")
+        if not token:
+            raise HttpError(400, "token is required")
+        u = app.users.find_one(verify_token_hash=hashlib.sha256(str(token).encode()).hexdigest())
+        if u is None or time.time() > float(u.get("verify_expires") or 0):
+            raise HttpError(400, "the verification link is invalid or has expired")
+        u = app.users.update(u["id"], {"email_verified": True, "approved": True, "verify_token_hash": None,
+                                       "verify_expires": None})
+        try:
+            app.email.send_welcome_email(u["email"], u["name"], app.public_url)
+        except Exception:
+            pass
+        return {"user": app.public_user(u), "message": "e-mail address verified"}
 
     def auth_login(req):
         email, password = req.need("email", "password")
         u = app.users.find_one(email=email.lower())
         if u is None or not A.verify_password(password, u["password_hash"]):
             raise HttpError(401, "invalid e-mail or password")
+        if not u.get("email_verified", True):
+            raise HttpError(403, "e-mail address not verified yet")
         if not u.get("approved", True):
             raise HttpError(403, "account not approved yet")
-        if u.get("mfa_enabled"):
-            return {"requires_mfa": True, "mfa_methods": ["totp", "recovery"], **app.jwt.create_mfa_token(u["id"], u["email"])}
+        if u.get("mfa_enabled") or u.get("webauthn_credentials"):
+            methods = (["totp", "recovery"] if u.get("mfa_enabled") else []) + (["webauthn"] if u.get("webauthn_credentials") else [])
+            return {"requires_mfa": True, "mfa_methods": methods, **app.jwt.create_mfa_token(u["id"], u["email"])}
         return _login_response(u, False)
 
     def _mfa_user(req) -> dict:
@@ -110,25 +148,78 @@ def register(app) -> None:
         if not A.verify_password(password, u["password_hash"]):
             raise HttpError(401, "wrong password")
         app.users.update(u["id"], {"mfa_enabled": False, "totp_secret": None, "pending_totp_secret": None,
-                                   "recovery_codes": []})
+                                   "recovery_codes": [], "webauthn_credentials": []})
         return {"mfa_enabled": False}
 
-    def webauthn_unavailable(req):
-        raise HttpError(501, "WebAuthn needs a browser authenticator; use TOTP")
+    # ------------------------------------------------------------------ WebAuthn
+    def _webauthn():
+        if not W.available():
+            raise HttpError(501, "WebAuthn needs the 'cryptography' package on the server; use TOTP")
+        return app.webauthn
+
+    def _webauthn_call(fn, *args):
+        try:
+            return fn(*args)
+        except W.WebAuthnError as e:
+            raise HttpError(400, str(e)) from None
+
+    def webauthn_register_start(req):
+        u = app.users.get(req.user_id)
+        return _webauthn_call(_webauthn().start_registration, u["id"], u["email"], u["name"], u.get("webauthn_credentials") or [])
+
+    def webauthn_register_finish(req):
+        u = app.users.get(req.user_id)
+        body = req.json or {}
+        cred = _webauthn_call(_webauthn().finish_registration, u["id"], body.get("credential") or body, str(body.get("name") or ""))
+        creds = list(u.get("webauthn_credentials") or [])
+        if any(c["credential_id"] == cred["credential_id"] for c in creds):
+            raise HttpError(409, "this credential is already registered")
+        creds.append(cred)
+        app.users.update(u["id"], {"webauthn_credentials": creds})
+        return 201, {"credential": {k: cred[k] for k in ("credential_id", "name", "created_at")}, "webauthn_enabled": True}
+
+    def webauthn_auth_start(req):
+        u = _mfa_user(req)
+        return _webauthn_call(_webauthn().start_authentication, u["id"], u.get("webauthn_credentials") or [])
+
+    def webauthn_auth_finish(req):
+        u = _mfa_user(req)
+        body = req.json or {}
+        creds = list(u.get("webauthn_credentials") or [])
+        used = _webauthn_call(_webauthn().finish_authentication, u["id"], body.get("credential") or body, creds)
+        creds = [used if c["credential_id"] == used["credential_id"] else c for c in creds]
+        app.users.update(u["id"], {"webauthn_credentials": creds})
+        return _login_response(u, True)
+
+    def webauthn_list(req):
+        u = app.users.get(req.user_id)
+        return [{k: c.get(k) for k in ("credential_id", "name", "created_at", "counter")} for c in u.get("webauthn_credentials") or []]
+
+    def webauthn_delete(req):
+        u = app.users.get(req.user_id)
+        left = [c for c in u.get("webauthn_credentials") or [] if c["credential_id"] != req.params["cred"]]
+        if len(left) == len(u.get("webauthn_credentials") or []):
+            raise HttpError(404, "no such credential")
+        app.users.update(u["id"], {"webauthn_credentials": left})
+        return {"deleted": True, "webauthn_enabled": bool(left)}
 
     r.add("POST", "/api/auth/register", auth_register, PUBLIC)
     r.add("POST", "/api/auth/login", auth_login, PUBLIC)
     r.add("POST", "/api/auth/mfa/totp/verify", mfa_totp_verify, PUBLIC)
     r.add("POST", "/api/auth/mfa/recovery", mfa_recovery_use, PUBLIC)
-    r.add("POST", "/api/auth/mfa/webauthn/authenticate/start", webauthn_unavailable, PUBLIC)
-    r.add("POST", "/api/auth/mfa/webauthn/authenticate/finish", webauthn_unavailable, PUBLIC)
+    r.add("GET", "/api/auth/verify-email", auth_verify_email, PUBLIC)
+    r.add("POST", "/api/auth/verify-email", auth_verify_email, PUBLIC)
+    r.add("POST", "/api/auth/mfa/webauthn/authenticate/start", webauthn_auth_start, PUBLIC)
+    r.add("POST", "/api/auth/mfa/webauthn/authenticate/finish", webauthn_auth_finish, PUBLIC)
     r.add("POST", "/api/auth/logout", auth_logout)
     r.add("POST", "/api/auth/refresh", auth_refresh, PUBLIC)
     r.add("GET", "/api/auth/me", auth_me)
     r.add("POST", "/api/auth/mfa/totp/setup", totp_setup)
     r.add("POST", "/api/auth/mfa/totp/enable", totp_enable)
-    r.add("POST", "/api/auth/mfa/webauthn/register/start", webauthn_unavailable)
-    r.add("POST", "/api/auth/mfa/webauthn/register/finish", webauthn_unavailable)
+    r.add("POST", "/api/auth/mfa/webauthn/register/start", webauthn_register_start)
+    r.add("POST", "/api/auth/mfa/webauthn/register/finish", webauthn_register_finish)
+    r.add("GET", "/api/auth/mfa/webauthn/credentials", webauthn_list)
+    r.add("DELETE", "/api/auth/mfa/webauthn/credentials/:cred", webauthn_delete)
     r.add("POST", "/api/auth/mfa/recovery/generate", recovery_generate)
     r.add("GET", "/api/auth/mfa/recovery/status", recovery_status)
     r.add("POST", "/api/auth/mfa/disable", mfa_disable)

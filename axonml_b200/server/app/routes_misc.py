@@ -88,7 +88,22 @@ def register(app) -> None:
         return nb.execute_cell(req.params["id"], req.params["cell"])
 
     def nb_ai_assist(req):
-        raise HttpError(503, "AI assist needs an Ollama daemon, which this host does not run")
+        """A code or markdown suggestion for the notebook from the configured Ollama daemon; the
+        notebook's existing cells are sent as context (api/notebooks.rs ai_assist)."""
+        from ...integrations.ollama import DEFAULT_MODEL, DEFAULT_URL, OllamaClient, OllamaError
+        doc = _own_nb(req)
+        (prompt,) = req.need("prompt")
+        client = OllamaClient(app.ollama_url or DEFAULT_URL, (req.json or {}).get("model") or app.ollama_model or DEFAULT_MODEL)
+        if not client.is_available():
+            raise HttpError(503, f"AI assist needs an Ollama daemon; none answers at {client.base_url}")
+        context = "\n\n".join(f"[{c.get('cell_type', 'code')}]\n{c.get('source', '')}" for c in doc.get("cells", [])[-8:]) \
+            if (req.json or {}).get("include_context", True) else ""
+        try:
+            if (req.json or {}).get("cell_type", "code") == "markdown":
+                return client.generate_markdown(prompt, context)
+            return client.generate_code(prompt, context)
+        except OllamaError as e:
+            raise HttpError(502, str(e)) from None
 
     def nb_restore(req):
         _own_nb(req)

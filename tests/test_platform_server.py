@@ -163,7 +163,6 @@ def test_auth_flow_with_totp_and_recovery(server):
     assert bob.req("GET", "/api/admin/users")[0] == 403
     assert c.req("POST", "/api/admin/query", {"collection": "users"})[0] == 403
     assert c.req("DELETE", f"/api/admin/users/{u2['id']}")[1] == {"deleted": True}
-    assert c.req("POST", "/api/auth/mfa/webauthn/register/start")[0] == 501
     assert c.req("GET", "/nope")[0] == 404 and c.req("DELETE", "/health")[0] == 405
 
 
@@ -360,3 +359,209 @@ def test_notebook_cells_run_outside_the_server_process(server):
     nbv = cv.req("POST", "/api/notebooks", {"name": "mine"})[1]
     assert cv.req("POST", f"/api/notebooks/{nbv['id']}/cells/{nbv['cells'][1]['id']}/execute")[0] == 403
     assert cv.req("POST", f"/api/notebooks/{nbv['id']}/run-all")[0] == 403
+
+
+# ----------------------------------------------------------------------------- WebAuthn
+def test_webauthn_primitives_reject_tampering():
+    from axonml_b200.server.app import webauthn as W
+    assert W.cbor_decode(W.cbor_encode({"a": [1, -5, b"xy", "t", None, True, 70000], -2: {1: 2}}))[0] == \
+        {"a": [1, -5, b"xy", "t", None, True, 70000], -2: {1: 2}}
+    rp = W.WebAuthnAuth("localhost", "AxonML", "http://localhost:3021")
+    key = W.SoftwareAuthenticator("http://localhost:3021")
+    cred = rp.finish_registration("u1", key.create(rp.start_registration("u1", "a@b.c", "Ada")), "yubikey")
+    assert cred["name"] == "yubikey" and cred["counter"] == 0 and len(W.b64u_dec(cred["public_key"])) == 64
+    # a good assertion, then the same one replayed (challenge is single use)
+    resp = key.get(rp.start_authentication("u1", [cred]))
+    cred2 = rp.finish_authentication("u1", resp, [cred])
+    assert cred2["counter"] == 1
+    with pytest.raises(W.WebAuthnError, match="pending"):
+        rp.finish_authentication("u1", resp, [cred2])
+    # tampered signature, wrong origin, stale counter, unknown credential
+    resp = key.get(rp.start_authentication("u1", [cred2]))
+    bad = json.loads(json.dumps(resp))
+    sig = bytearray(W.b64u_dec(bad["response"]["signature"]))
+    sig[-1] ^= 1
+    bad["response"]["signature"] = W.b64u(bytes(sig))
+    with pytest.raises(W.WebAuthnError, match="signature"):
+        rp.finish_authentication("u1", bad, [cred2])
+    evil = W.SoftwareAuthenticator("http://evil.example")
+    evil._keys, evil._counter = key._keys, 10
+    with pytest.raises(W.WebAuthnError, match="origin"):
+        rp.finish_authentication("u1", evil.get(rp.start_authentication("u1", [cred2])), [cred2])
+    with pytest.raises(W.WebAuthnError, match="counter"):
+        rp.finish_authentication("u1", key.get(rp.start_authentication("u1", [cred2])), [{**cred2, "counter": 99}])
+    other = W.SoftwareAuthenticator("http://localhost:3021")
+    other_cred = rp.finish_registration("u2", other.create(rp.start_registration("u2", "x@y.z", "X")), "")
+    with pytest.raises(W.WebAuthnError, match="unknown credential"):
+        rp.finish_authentication("u1", other.get(rp.start_authentication("u1", [other_cred])), [cred2])
+    # registration with a client-data type of the other ceremony
+    opts = rp.start_registration("u3", "q@r.s", "Q")
+    wrong = key.create(opts)
+    cd = json.loads(W.b64u_dec(wrong["response"]["client_data_json"]))
+    cd["type"] = "webauthn.get"
+    wrong["response"]["client_data_json"] = W.b64u(json.dumps(cd).encode())
+    with pytest.raises(W.WebAuthnError, match="type"):
+        rp.finish_registration("u3", wrong, "")
+
+
+def test_webauthn_second_factor_over_http(server):
+    from axonml_b200.server.app import webauthn as W
+    c = Client(server.port)
+    c.req("POST", "/api/auth/register", {"email": "ada@example.com", "name": "Ada", "password": "s3cret-pass"})
+    c.token = _login(c)["access_token"]
+    key = W.SoftwareAuthenticator(server.public_url)
+    st, opts = c.req("POST", "/api/auth/mfa/webauthn/register/start")
+    assert st == 200 and opts["rp"]["id"] == "localhost" and opts["pub_key_cred_params"][0]["alg"] == -7
+    st, out = c.req("POST", "/api/auth/mfa/webauthn/register/finish", {"credential": key.create(opts), "name": "laptop key"})
+    assert st == 201 and out["webauthn_enabled"]
+    assert c.req("GET", "/api/auth/me")[1]["webauthn_enabled"] is True
+    assert [k["name"] for k in c.req("GET", "/api/auth/mfa/webauthn/credentials")[1]] == ["laptop key"]
+    c.token = None
+    j = _login(c)
+    assert j["requires_mfa"] and j["mfa_methods"] == ["webauthn"]
+    st, ch = c.req("POST", "/api/auth/mfa/webauthn/authenticate/start", {"mfa_token": j["mfa_token"]})
+    assert st == 200 and ch["allow_credentials"][0]["id"] == out["credential"]["credential_id"]
+    assertion = key.get(ch)
+    forged = json.loads(json.dumps(assertion))
+    forged["response"]["authenticator_data"] = W.b64u(W.b64u_dec(forged["response"]["authenticator_data"])[:-1] + b"\x09")
+    assert c.req("POST", "/api/auth/mfa/webauthn/authenticate/finish", {"mfa_token": j["mfa_token"], "credential": forged})[0] == 400
+    st, ch = c.req("POST", "/api/auth/mfa/webauthn/authenticate/start", {"mfa_token": j["mfa_token"]})
+    st, ok = c.req("POST", "/api/auth/mfa/webauthn/authenticate/finish", {"mfa_token": j["mfa_token"], "credential": key.get(ch)})
+    assert st == 200 and ok["access_token"]
+    c.token = ok["access_token"]
+    cid = out["credential"]["credential_id"]
+    assert c.req("DELETE", f"/api/auth/mfa/webauthn/credentials/{cid}")[1] == {"deleted": True, "webauthn_enabled": False}
+
+
+# ----------------------------------------------------------------------------- external services (faked over HTTP)
+class _Fake:
+    """A tiny HTTP server that records requests and answers from a table of (method, path prefix)."""
+
+    def __init__(self, routes):
+        import http.server
+        import threading
+        fake = self
+        self.calls = []
+
+        class H(http.server.BaseHTTPRequestHandler):
+            def _serve(self):
+                n = int(self.headers.get("Content-Length") or 0)
+                body = json.loads(self.rfile.read(n) or b"null") if n else None
+                fake.calls.append((self.command, self.path, dict(self.headers), body))
+                for (m, prefix), fn in routes.items():
+                    if m == self.command and self.path.startswith(prefix):
+                        status, payload = fn(self.path, dict(self.headers), body)
+                        raw = json.dumps(payload).encode()
+                        self.send_response(status)
+                        self.send_header("Content-Type", "application/json")
+                        self.send_header("Content-Length", str(len(raw)))
+                        self.end_headers()
+                        self.wfile.write(raw)
+                        return
+                self.send_response(404)
+                self.send_header("Content-Length", "0")
+                self.end_headers()
+            do_GET = do_POST = _serve
+
+            def log_message(self, *a):
+                pass
+        self.httpd = http.server.ThreadingHTTPServer(("127.0.0.1", 0), H)
+        self.url = f"http://127.0.0.1:{self.httpd.server_address[1]}"
+        threading.Thread(target=self.httpd.serve_forever, daemon=True).start()
+
+    def close(self):
+        self.httpd.shutdown()
+        self.httpd.server_close()
+
+
+def test_secrets_manager_reads_vault_then_environment(monkeypatch):
+    from axonml_b200.integrations.secrets import EnvBackend, SecretKey, SecretsError, SecretsManager, VaultBackend
+    doc = {"jwt_secret": "from-vault-0123456789abcdef0123456789"}
+
+    def read(path, headers, body):
+        return (200, {"data": {"data": doc}}) if headers.get("X-Vault-Token") == "tok" else (403, {"errors": ["denied"]})
+
+    def write(path, headers, body):
+        doc.clear()
+        doc.update(body["data"])
+        return 200, {}
+    fake = _Fake({("GET", "/v1/secret/data/axonml"): read, ("POST", "/v1/secret/data/axonml"): write,
+                  ("POST", "/v1/auth/approle/login"): lambda p, h, b: (200, {"auth": {"client_token": "tok"}})})
+    try:
+        monkeypatch.setenv("AXONML_RESEND_API_KEY", "re_env")
+        mgr = SecretsManager([VaultBackend(fake.url, "tok"), EnvBackend()])
+        assert mgr.backend_names() == ["vault", "env"]
+        assert mgr.get_secret(SecretKey.JWT_SECRET).startswith("from-vault")
+        assert mgr.get_secret(SecretKey.RESEND_API_KEY) == "re_env"           # not in Vault: the next backend answers
+        with pytest.raises(SecretsError, match="not found"):
+            mgr.get_secret("db_password")
+        approle = VaultBackend(fake.url, None, role_id="r", secret_id="s")       # AppRole login gets the token
+        approle.put_secrets({"db_password": "pw"})
+        assert VaultBackend(fake.url, "tok").get_secret("db_password") == "pw"
+        with pytest.raises(SecretsError, match="refused"):
+            VaultBackend(fake.url, "wrong").get_secret("jwt_secret")
+        monkeypatch.setenv("VAULT_ADDR", fake.url)
+        monkeypatch.setenv("VAULT_TOKEN", "tok")
+        # the server signs its tokens with the secret from Vault
+        srv = PlatformServer(port=0)
+        try:
+            assert srv.jwt.validate_access_token(JwtAuth(doc["jwt_secret"]).create_access_token("u", "e", "user")).sub == "u"
+        finally:
+            srv.httpd.server_close()
+    finally:
+        fake.close()
+
+
+def test_registration_waits_for_the_mailed_verification_link(tmp_path):
+    from axonml_b200.integrations.email import EmailService
+    mails = []
+
+    def send(path, headers, body):
+        assert headers.get("Authorization") == "Bearer re_test"
+        mails.append(body)
+        return 200, {"id": f"mail-{len(mails)}"}
+    fake = _Fake({("POST", "/emails"): send})
+    srv = PlatformServer(port=0, data_dir=str(tmp_path / "srv"), allow_registration=True,
+                         email=EmailService("re_test", base_url=fake.url)).start()
+    try:
+        c = Client(srv.port)
+        assert c.req("POST", "/api/auth/register", {"email": "root@example.com", "name": "Root", "password": "s3cret-pass"})[0] == 201
+        assert not mails                                                     # the first account (administrator) needs no link
+        st, j = c.req("POST", "/api/auth/register", {"email": "eve@example.com", "name": "Eve", "password": "s3cret-pass"})
+        assert st == 201 and j["user"]["email_verified"] is False and "inbox" in j["message"]
+        assert [m["to"] for m in mails] == [["eve@example.com"], ["root@example.com"]]
+        assert c.req("POST", "/api/auth/login", {"email": "eve@example.com", "password": "s3cret-pass"})[0] == 403
+        link = mails[0]["html"].split('href="')[1].split('"')[0]
+        assert link.startswith(srv.public_url + "/api/auth/verify-email?token=")
+        assert c.req("GET", "/api/auth/verify-email?token=bogus")[0] == 400
+        st, j = c.req("GET", link[len(srv.public_url):])
+        assert st == 200 and j["user"]["email_verified"] and j["user"]["approved"]
+        assert mails[-1]["subject"].startswith("Your AxonML account")          # welcome message
+        assert c.req("GET", link[len(srv.public_url):])[0] == 400              # the link works once
+        assert _login(c, "eve@example.com")["access_token"]
+    finally:
+        srv.stop()
+        fake.close()
+
+
+def test_notebook_ai_assist_asks_the_ollama_daemon(tmp_path):
+    def gen(path, headers, body):
+        assert body["stream"] is False and "Task: plot the loss" in body["prompt"] and "import torch" in body["prompt"]
+        return 200, {"response": "Here you go:\n```python\nplt.plot(losses)\n```\n", "done": True}
+    fake = _Fake({("GET", "/api/tags"): lambda p, h, b: (200, {"models": [{"name": "qwen2.5-coder:7b"}]}),
+                  ("POST", "/api/generate"): gen})
+    srv = PlatformServer(port=0, data_dir=str(tmp_path / "srv"), ollama_url=fake.url).start()
+    try:
+        c = Client(srv.port)
+        c.req("POST", "/api/auth/register", {"email": "ada@example.com", "name": "Ada", "password": "s3cret-pass"})
+        c.token = _login(c)["access_token"]
+        nb = c.req("POST", "/api/notebooks", {"name": "n", "cells": [{"cell_type": "code", "source": "import torch"}]})[1]
+        st, j = c.req("POST", f"/api/notebooks/{nb['id']}/ai-assist", {"prompt": "plot the loss"})
+        assert st == 200 and j == {"kind": "code", "language": "python", "content": "plt.plot(losses)", "model": "qwen2.5-coder:7b"}
+        from axonml_b200.integrations.ollama import OllamaClient
+        assert OllamaClient(fake.url).list_models() == ["qwen2.5-coder:7b"]
+        srv.ollama_url = "http://127.0.0.1:9"                                   # nothing listens there
+        assert c.req("POST", f"/api/notebooks/{nb['id']}/ai-assist", {"prompt": "x"})[0] == 503
+    finally:
+        srv.stop()
+        fake.close()
