@@ -8,8 +8,7 @@
 //    separate unscale pass of crates/axonml-optim/src/grad_scaler.rs:187-206.
 //  * ax_fused_rs_adamw  : FSDP gradient reduce-scatter fused with the sharded AdamW update: rank r
 //    sums its shard of every peer's flat gradient, applies AdamW to its fp32 master shard and
-//    moments, writes the bf16 shard and (optionally) pushes it into every peer's full parameter
-//    buffer, which makes the next all-gather unnecessary.
+//    moments and writes the bf16 shard.
 //    Replaces fsdp.rs:259-268 (reduce-scatter whose result is dropped) + adam.rs:376-445.
 //
 // Synchronisation: block 0 runs the cross-GPU barriers (comm.cuh); the other blocks of the same
@@ -278,13 +277,11 @@ struct AdamW {
 };
 
 // grads: bf16, every rank's flat gradient at byte offset grad_off of P.buf[*]; this rank owns
-// elements [rank*shard, (rank+1)*shard).  push[p] (optional) = rank p's full bf16 parameter buffer
-// for this unit (peer-mapped); the updated shard is written at element offset rank*shard.
+// elements [rank*shard, (rank+1)*shard).
 template <bool MC>
 __global__ void __launch_bounds__(kThreads)
 fused_rs_adamw_kernel(const Peers P, long grad_off, long shard, float* master, float* m1, float* m2,
-                      __nv_bfloat16* lp, const Peers push, long push_off, const AdamW h,
-                      const int* skip_flag, uint32_t epoch, int* status) {
+                      __nv_bfloat16* lp, const AdamW h, const int* skip_flag, uint32_t epoch, int* status) {
   uint32_t done_base;
   const bool ok = collective_begin(P, epoch, status, done_base);
   if (ok && !(skip_flag && *skip_flag)) {
@@ -315,16 +312,6 @@ fused_rs_adamw_kernel(const Peers P, long grad_off, long shard, float* master, f
       *reinterpret_cast<float4*>(m2 + i + 4) = make_float4(b[4], b[5], b[6], b[7]);
       const uint4 packed = pack_bf16x8(w);
       if (lp) *reinterpret_cast<uint4*>(lp + i) = packed;
-      if (push.world > 0) {
-        const long po = push_off + (shard * P.rank + i) * 2;
-        if (MC && push.mc_buf) {
-          multimem_st_b32x4((char*)push.mc_buf + po, packed);
-        } else {
-#pragma unroll
-          for (int p = 0; p < kMaxRanks; ++p)
-            if (p < push.world) st_peer_v4((char*)push.buf[(P.rank + p) % push.world] + po, packed);
-        }
-      }
     }
   }
   collective_end(P, epoch, 0, status, done_base);
@@ -474,21 +461,19 @@ AX_API int ax_fused_allreduce(int dtype, void* const* bufs, void* const* sigs, v
 }
 
 // hyper: float[7] = lr, beta1, beta2, eps, wd, bc1 (1-beta1^t), bc2 (1-beta2^t).
-// `shard` (elements per rank) must be a multiple of 8; grad_off / push_off are byte offsets.
+// `shard` (elements per rank) must be a multiple of 8; grad_off is a byte offset.
 AX_API int ax_fused_rs_adamw(void* const* grad_bufs, void* const* sigs, void* grad_mc, int rank,
                              int world, long grad_off, long shard, float* master, float* m1, float* m2,
-                             void* lp, void* const* push_bufs, void* push_mc, long push_off,
-                             const float* hyper, const int* skip_flag, unsigned epoch, int grid_blocks,
+                             void* lp, const float* hyper, const int* skip_flag, unsigned epoch, int grid_blocks,
                              int* status, cudaStream_t stream) {
-  if (world < 1 || world > axc::kMaxRanks || shard % 8 || grad_off % 16 || push_off % 16) return -1;
+  if (world < 1 || world > axc::kMaxRanks || shard % 8 || grad_off % 16) return -1;
   Peers P = make_peers(grad_bufs, sigs, grad_mc, rank, world);
-  Peers push = make_peers(push_bufs, nullptr, push_mc, rank, push_bufs ? world : 0);
   AdamW h{hyper[0], hyper[1], hyper[2], hyper[3], hyper[4], hyper[5], hyper[6], 1.f / world};
   const int grid = checked_grid(grid_blocks);
   if (grad_mc)
-    fused_rs_adamw_kernel<true><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, (__nv_bfloat16*)lp, push, push_off, h, skip_flag, epoch, status);
+    fused_rs_adamw_kernel<true><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, (__nv_bfloat16*)lp, h, skip_flag, epoch, status);
   else
-    fused_rs_adamw_kernel<false><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, (__nv_bfloat16*)lp, push, push_off, h, skip_flag, epoch, status);
+    fused_rs_adamw_kernel<false><<<grid, kThreads, 0, stream>>>(P, grad_off, shard, master, m1, m2, (__nv_bfloat16*)lp, h, skip_flag, epoch, status);
   return (int)cudaGetLastError();
 }
 

@@ -1,7 +1,8 @@
 """Conv1d / Conv2d (crates/axonml-nn/src/layers/conv.rs:47-87, :202-337): NCHW API, weights
 ``[cout, cin, k(,k)]`` kaiming-uniform with fan_in = cin*k*k, zero bias.  Unlike the reference the
-layers are differentiable.  bf16 channels-last inputs on a B200 go through the implicit-GEMM
-kernel in ``ops.conv``; everything else uses the torch convolution."""
+layers are differentiable.  bf16 inputs on a B200 (channels-last for Conv2d, channel counts that
+are multiples of 64 or a thin stem) go through the implicit-GEMM kernels of ``ops.conv_igemm``;
+everything else uses the torch convolution."""
 from __future__ import annotations
 
 import math
@@ -35,6 +36,9 @@ class Conv1d(Module):
     def with_options(cls, cin, cout, k, stride, padding, bias): return cls(cin, cout, k, stride, padding, bias)
 
     def forward(self, x):
+        from ...ops import conv_igemm as C
+        if isinstance(self.stride, int) and isinstance(self.padding, int) and C.conv1d_supported(x, self.weight, self.stride, self.padding):
+            return C.conv1d(x, self.weight, self.bias, self.stride, self.padding)
         return F.conv1d(x, self.weight.to(x.dtype), None if self.bias is None else self.bias.to(x.dtype),
                         self.stride, self.padding)
 
@@ -59,7 +63,7 @@ class Conv2d(Module):
     def with_options(cls, cin, cout, k, stride, padding, bias): return cls(cin, cout, k, stride, padding, bias)
 
     def forward(self, x):
-        from ...ops import conv as C
+        from ...ops import conv_igemm as C
         if C.conv2d_supported(x, self.weight, self.stride, self.padding):
             return C.conv2d(x, self.weight, self.bias, self.stride, self.padding)
         w = self.weight if self.weight.dtype == x.dtype else self.weight.to(x.dtype)

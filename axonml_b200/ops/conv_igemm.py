@@ -157,6 +157,36 @@ def conv2d(x, weight, bias, stride, padding):
     return _ConvFn.apply(x, weight, bias, tuple(padding), tuple(stride))
 
 
+def conv2d_supported(x, weight, stride, padding) -> bool:
+    """Whether ``conv2d`` takes this call (the nn layer falls back to the torch convolution otherwise)."""
+    return supported(x, weight, stride, padding) or thin_supported(x, weight, stride, padding)
+
+
+# ------------------------------------------------------------------------------ one-dimensional convolutions
+def _as_2d(x):
+    """``[N, C, L]`` -> ``[N, C, 1, L]`` in channels-last storage (N, L, C): a view when ``x`` already
+    is the squeezed result of an earlier call, one transposing copy otherwise."""
+    return x.unsqueeze(2).contiguous(memory_format=torch.channels_last)
+
+
+def conv1d_supported(x, weight, stride: int, padding: int) -> bool:
+    if not (x.dim() == 3 and x.is_cuda and x.dtype == torch.bfloat16 and N.is_blackwell()):
+        return False
+    n, c, l = x.shape
+    cout, cin, k = weight.shape
+    if stride < 1 or stride > 4 or cin != c or cin % 64 or cout % 64 or k > 64 or l < stride or l + 2 * padding < k:
+        return False
+    return n * ((l + 2 * padding - k) // stride + 1) >= 128
+
+
+def conv1d(x, weight, bias, stride: int, padding: int):
+    """Conv1d on the implicit-GEMM kernels: the sequence is the width of an image of height one
+    (forward, data gradient and weight gradient are those of ``conv2d``).  The result is a
+    ``[N, Cout, Lo]`` view of channels-last storage, so a stack of such layers never transposes."""
+    y = _ConvFn.apply(_as_2d(x), weight.unsqueeze(2), bias, (0, padding), (1, stride))
+    return y.squeeze(2)
+
+
 # ------------------------------------------------------------------------------ thin inputs (RGB stem)
 def thin_supported(x, weight, stride, padding) -> bool:
     """Convolutions with fewer than 64 input channels (any stride): patches are gathered by the

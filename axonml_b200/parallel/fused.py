@@ -117,22 +117,14 @@ class FusedShardedAdamW:
         self.heap = heap
         self.comm = Communicator(heap, grid_blocks)
         self.arena = heap.allocate(arena_numel, torch.bfloat16)
-        self.params = None          # optional symmetric arena of resident full parameter buffers
-
-    def attach_param_arena(self, numel: int):
-        self.params = self.heap.allocate(numel, torch.bfloat16)
-        return self.params
 
     def step_unit(self, grad_off_elems: int, shard: int, master, m1, m2, lp, *, lr, beta1, beta2, eps,
-                  wd, step: int, push_off_elems: int | None = None, skip_flag=None) -> None:
+                  wd, step: int, skip_flag=None) -> None:
         hyper = (ctypes.c_float * 7)(lr, beta1, beta2, eps, wd, 1 - beta1 ** step, 1 - beta2 ** step)
-        push = self.params if (push_off_elems is not None and self.params is not None) else None
         rc = N.cuda().ax_fused_rs_adamw(
             self.arena.ptr_array(), self.comm.signals.ptr_array(), self.arena.mc(), self.heap.rank,
             self.heap.world, ctypes.c_long(grad_off_elems * 2), ctypes.c_long(shard), N.ptr(master),
-            N.ptr(m1), N.ptr(m2), N.ptr(lp), push.ptr_array() if push else None,
-            push.mc() if push else ctypes.c_void_p(0),
-            ctypes.c_long((push_off_elems or 0) * 2), hyper, N.ptr(skip_flag),
+            N.ptr(m1), N.ptr(m2), N.ptr(lp), hyper, N.ptr(skip_flag),
             ctypes.c_uint(self.comm.next_epoch()), self.comm.grid, N.ptr(N.status_word(master.device)),
             N.stream_ptr())
         N.check(rc, "ax_fused_rs_adamw")

@@ -187,3 +187,29 @@ def test_thin_input_convolution_im2col_gemm(cin, cout, k, stride, pad, hw, kerne
     ref.backward(g.float())
     assert (w.grad - wr.grad).abs().max().item() < 0.03 * wr.grad.abs().max().item() + 1e-2
     assert (b.grad - br.grad).abs().max().item() < 0.02 * br.grad.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("n,cin,l,cout,k,stride,pad", [(4, 64, 200, 128, 3, 1, 1), (2, 128, 333, 64, 5, 2, 2), (8, 64, 64, 64, 1, 1, 0)])
+def test_conv1d_runs_on_the_implicit_gemm_kernels(n, cin, l, cout, k, stride, pad, kernel_status):
+    """Conv1d as a convolution over an image of height one: forward and all three gradients against
+    the fp32 reference, and a second layer on the (channels-last) result without a transpose."""
+    from axonml_b200 import _native, nn
+    torch.manual_seed(5)
+    conv = nn.Conv1d(cin, cout, k, stride, pad).cuda()
+    x = torch.randn(n, cin, l, device="cuda").bfloat16().requires_grad_(True)
+    before = _native.launch_count()
+    y = conv(x)
+    assert _native.launch_count() > before and y.shape == (n, cout, (l + 2 * pad - k) // stride + 1)
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2 = x.detach().float().requires_grad_(True)
+    w2 = conv.weight.detach().bfloat16().float().requires_grad_(True)
+    b2 = conv.bias.detach().clone().requires_grad_(True)
+    ref = F.conv1d(x2, w2, b2, stride, pad)
+    ref.backward(g.float())
+    assert (y.float() - ref).abs().max().item() < 0.03 * max(ref.abs().max().item(), 1.0)
+    for a, r, tol in ((x.grad, x2.grad, 0.03), (conv.weight.grad, w2.grad, 0.05), (conv.bias.grad, b2.grad, 0.02)):
+        assert (a.float() - r).abs().max().item() < tol * max(r.abs().max().item(), 1.0)
+    if cout % 64 == 0:
+        z = nn.Conv1d(cout, 64, 3, 1, 1).cuda()(y.detach())          # consumes the strided view directly
+        assert z.shape[:2] == (n, 64)
