@@ -1,12 +1,11 @@
 """Reference-counted storage with offset/length views (crates/axonml-core/src/storage.rs:43-236)
 and allocators (allocator.rs).  A ``Storage`` wraps a flat torch tensor, so views share memory and
 ``to_device`` works for CUDA as well (the reference refuses every non-CPU device,
-storage.rs:224-235).  ``CachingDeviceAllocator`` is a size-bucketed free list on top of
-``torch.empty`` for runtime buffers that are reused across steps (communication staging, kernel
-scratch) without going back to the driver."""
+storage.rs:224-235).  ``CachingDeviceAllocator`` pools device segments and carves them with the
+native offset allocator (``csrc/host/arena.cpp``, ``OffsetArena``), which the symmetric heap of the
+fused collectives uses too."""
 from __future__ import annotations
 
-import collections
 import threading
 
 import torch
@@ -85,47 +84,134 @@ class DefaultAllocator(Allocator):
     def free_memory(self) -> int: return self.dev.capabilities().available_memory
 
 
-class CachingDeviceAllocator(Allocator):
-    def __init__(self, device=None, round_to: int = 512):
-        self.dev = device or (Device.Cuda(torch.cuda.current_device()) if torch.cuda.is_available() else Device.Cpu())
-        self.round_to = round_to
-        self._free = collections.defaultdict(list)
-        self._lock = threading.Lock()
-        self.hits = self.misses = 0
+class OffsetArena:
+    """Native offset allocator over ``[0, capacity)`` (``csrc/host/arena.cpp``): best fit with
+    splitting, neighbours merged on free, deterministic.  It never touches memory; the caller owns
+    the range the offsets refer to."""
 
-    def _bucket(self, nbytes: int) -> int:
-        return (nbytes + self.round_to - 1) // self.round_to * self.round_to
+    def __init__(self, capacity: int, alignment: int = 512):
+        import ctypes
+        from .. import _native as N
+        self._lib = N.host()
+        self._lib.ax_arena_create.restype = ctypes.c_void_p
+        self._lib.ax_arena_alloc.restype = ctypes.c_int64
+        self._lib.ax_arena_block_size.restype = ctypes.c_uint64
+        self._h = self._lib.ax_arena_create(ctypes.c_uint64(capacity), ctypes.c_uint64(alignment))
+        if not self._h:
+            raise ValueError("capacity must be positive and the alignment a power of two")
+        self.alignment = alignment
+
+    def alloc(self, nbytes: int) -> int:
+        """Offset of a block of at least ``nbytes`` bytes, or -1."""
+        import ctypes
+        return int(self._lib.ax_arena_alloc(ctypes.c_void_p(self._h), ctypes.c_uint64(nbytes)))
+
+    def free(self, offset: int) -> bool:
+        import ctypes
+        return self._lib.ax_arena_free(ctypes.c_void_p(self._h), ctypes.c_int64(offset)) == 0
+
+    def block_size(self, offset: int) -> int:
+        import ctypes
+        return int(self._lib.ax_arena_block_size(ctypes.c_void_p(self._h), ctypes.c_int64(offset)))
+
+    def reset(self) -> None:
+        import ctypes
+        self._lib.ax_arena_reset(ctypes.c_void_p(self._h))
+
+    def stats(self) -> dict:
+        import ctypes
+        out = (ctypes.c_uint64 * 7)()
+        self._lib.ax_arena_stats(ctypes.c_void_p(self._h), out)
+        keys = ("capacity", "in_use", "peak", "live_blocks", "free_blocks", "largest_free", "allocations")
+        return dict(zip(keys, (int(v) for v in out)))
+
+    def __del__(self):
+        try:
+            import ctypes
+            if getattr(self, "_h", None):
+                self._lib.ax_arena_destroy(ctypes.c_void_p(self._h))
+                self._h = None
+        except Exception:
+            pass
+
+
+class CachingDeviceAllocator(Allocator):
+    """Pool allocator for runtime buffers that are reused across steps (communication staging,
+    kernel scratch): memory comes from the device in segments of ``segment_bytes`` (one driver call
+    each) and the native offset allocator carves tensors out of them, so the steady state of a
+    training loop makes no driver calls.  Requests larger than a segment get a segment of their own.
+    ``deallocate`` returns a block to its segment (neighbouring free blocks merge); ``empty_cache``
+    releases the segments that hold no live block."""
+
+    def __init__(self, device=None, round_to: int = 512, segment_bytes: int = 64 << 20):
+        self.dev = device or (Device.Cuda(torch.cuda.current_device()) if torch.cuda.is_available() else Device.Cpu())
+        self.round_to, self.segment_bytes = round_to, segment_bytes
+        self._segments: list[tuple[torch.Tensor, OffsetArena]] = []
+        self._owner: dict[int, tuple[int, int]] = {}          # data_ptr -> (segment index, offset)
+        self._lock = threading.Lock()
+        self.hits = self.misses = 0                           # served from a cached segment / needed a new one
+
+    def _new_segment(self, nbytes: int):
+        size = max(self.segment_bytes, (nbytes + self.round_to - 1) // self.round_to * self.round_to)
+        try:
+            raw = torch.empty(size + self.round_to, dtype=torch.uint8, device=self.dev.to_torch())
+        except RuntimeError as e:
+            raise AllocationFailed(size, str(self.dev)) from e
+        shift = (-raw.data_ptr()) % self.round_to          # blocks are aligned in memory, not only inside the segment
+        raw = raw[shift:shift + size]
+        seg = (raw, OffsetArena(size, self.round_to))
+        for i, s in enumerate(self._segments):
+            if s is None:
+                self._segments[i] = seg
+                return i
+        self._segments.append(seg)
+        return len(self._segments) - 1
 
     def allocate(self, count: int, dtype=torch.float32):
         dt = as_torch_dtype(dtype)
-        nbytes = self._bucket(count * torch.empty((), dtype=dt).element_size())
+        nbytes = max(1, count * torch.empty((), dtype=dt).element_size())
         with self._lock:
-            lst = self._free.get(nbytes)
-            if lst:
-                self.hits += 1
-                raw = lst.pop()
-            else:
+            idx, off = -1, -1
+            for i, seg in enumerate(self._segments):
+                if seg is None:
+                    continue
+                off = seg[1].alloc(nbytes)
+                if off >= 0:
+                    idx = i
+                    self.hits += 1
+                    break
+            if idx < 0:
                 self.misses += 1
-                raw = None
-        if raw is None:
-            try:
-                raw = torch.empty(nbytes, dtype=torch.uint8, device=self.dev.to_torch())
-            except RuntimeError as e:
-                raise AllocationFailed(nbytes, str(self.dev)) from e
-        t = raw.view(dt)[:count]
-        t._axon_raw = raw
+                idx = self._new_segment(nbytes)
+                off = self._segments[idx][1].alloc(nbytes)
+            raw = self._segments[idx][0]
+            t = raw[off:off + nbytes].view(dt)[:count]
+            self._owner[t.data_ptr()] = (idx, off)
         return t
 
     def deallocate(self, t) -> None:
-        raw = getattr(t, "_axon_raw", None)
-        if raw is not None:
-            with self._lock:
-                self._free[raw.numel()].append(raw)
+        with self._lock:
+            where = self._owner.pop(t.data_ptr(), None)
+            if where is not None:
+                self._segments[where[0]][1].free(where[1])
 
     def empty_cache(self) -> None:
         with self._lock:
-            self._free.clear()
+            for i, seg in enumerate(self._segments):
+                if seg is not None and seg[1].stats()["live_blocks"] == 0:
+                    self._segments[i] = None
 
     def total_memory(self) -> int: return self.dev.capabilities().total_memory
     def free_memory(self) -> int: return self.dev.capabilities().available_memory
-    def cached_bytes(self) -> int: return sum(k * len(v) for k, v in self._free.items())
+
+    def cached_bytes(self) -> int:
+        """Bytes held in segments but not handed out."""
+        with self._lock:
+            return sum(s[1].stats()["capacity"] - s[1].stats()["in_use"] for s in self._segments if s is not None)
+
+    def stats(self) -> dict:
+        with self._lock:
+            segs = [s[1].stats() for s in self._segments if s is not None]
+        return {"segments": len(segs), "reserved": sum(s["capacity"] for s in segs), "in_use": sum(s["in_use"] for s in segs),
+                "peak": sum(s["peak"] for s in segs), "live_blocks": sum(s["live_blocks"] for s in segs),
+                "hits": self.hits, "misses": self.misses}

@@ -60,11 +60,50 @@ class SymmetricBuffer:
         return self.handle.get_buffer(rank, shape, dtype, offset_elems)
 
 
+class SymmetricSlice:
+    """A sub-range of a symmetric arena with the interface of ``SymmetricBuffer``: the arena was
+    exchanged once, so the slice's peer and multicast addresses are the arena's plus the offset
+    (the same on every rank, because every rank makes the same allocation calls)."""
+
+    def __init__(self, arena: "SymmetricBuffer", offset: int, numel: int, dtype: torch.dtype, release=None):
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        self.arena, self.offset, self._release = arena, offset, release
+        self.local = arena.local[offset:offset + nbytes].view(dtype)
+        self.handle, self.world, self.rank = arena.handle, arena.world, arena.rank
+        self.peer_ptrs = [p + offset for p in arena.peer_ptrs]
+        self.mc_ptr = arena.mc_ptr + offset if arena.mc_ptr else 0
+        self._arr = (ctypes.c_void_p * self.world)(*self.peer_ptrs)
+        self._esz = nbytes // max(numel, 1)
+
+    def ptr_array(self):
+        return self._arr
+
+    def mc(self):
+        return ctypes.c_void_p(self.mc_ptr) if self.mc_ptr else ctypes.c_void_p(0)
+
+    def peer_tensor(self, rank: int, shape, dtype, offset_elems: int = 0) -> torch.Tensor:
+        esz = torch.empty((), dtype=dtype).element_size()
+        return self.handle.get_buffer(rank, shape, dtype, self.offset // esz + offset_elems)
+
+    def free(self) -> None:
+        """Returns the range to the arena (every rank must do so at the same point of its program)."""
+        if self._release is not None:
+            self._release(self.offset)
+            self._release = None
+
+
 class SymmetricHeap:
     """Allocator of symmetric buffers for one process group, plus the communicator state the
-    fused kernels need: a zero-initialised signal array per rank and a call epoch."""
+    fused kernels need: a zero-initialised signal array per rank and a call epoch.
 
-    def __init__(self, pg):
+    Two modes.  By default every ``allocate`` makes its own symmetric allocation and exchanges its
+    handles (a rendezvous of all ranks).  With ``arena_bytes`` (or ``AXONML_SYMM_ARENA_MB``) the
+    heap makes ONE symmetric allocation at construction and serves ``allocate`` from it through the
+    native offset allocator (``csrc/host/arena.cpp``): no further rendezvous, one multicast binding
+    for everything, and buffers can be given back (``SymmetricSlice.free``).  A request that does not
+    fit falls back to an allocation of its own."""
+
+    def __init__(self, pg, arena_bytes: int | None = None):
         import torch.distributed._symmetric_memory as symm_mem
         self._symm = symm_mem
         self.pg = pg
@@ -73,12 +112,32 @@ class SymmetricHeap:
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.use_mc = os.environ.get("AXONML_NVLS", "1") != "0"
         self.rank, self.world = pg.rank(), pg.world_size()
+        if arena_bytes is None:
+            arena_bytes = int(os.environ.get("AXONML_SYMM_ARENA_MB", "0")) << 20
+        self._arena = self._offsets = None
+        if arena_bytes > 0:
+            from ..core.storage import OffsetArena
+            self._arena = self._allocate_own(arena_bytes, torch.uint8)
+            self._offsets = OffsetArena(arena_bytes, 4096)
 
-    def allocate(self, numel: int, dtype: torch.dtype) -> SymmetricBuffer:
+    def _allocate_own(self, numel: int, dtype: torch.dtype) -> SymmetricBuffer:
         t = self._symm.empty(numel, dtype=dtype, device=self.device)
         t.zero_()
         hdl = self._symm.rendezvous(t, self.group)
         return SymmetricBuffer(t, hdl, self.use_mc)
+
+    def allocate(self, numel: int, dtype: torch.dtype):
+        if self._offsets is not None:
+            nbytes = numel * torch.empty((), dtype=dtype).element_size()
+            off = self._offsets.alloc(nbytes)
+            if off >= 0:
+                sl = SymmetricSlice(self._arena, off, numel, dtype, release=self._offsets.free)
+                sl.local.zero_()
+                return sl
+        return self._allocate_own(numel, dtype)
+
+    def arena_stats(self) -> dict | None:
+        return self._offsets.stats() if self._offsets is not None else None
 
     def barrier(self) -> None:
         torch.cuda.synchronize()

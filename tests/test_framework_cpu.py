@@ -186,3 +186,66 @@ def test_axonml_alias_package_and_prelude():
     assert nn2.Linear is nn.Linear and DistributedDataParallel is P.DistributedDataParallel
     pre = axonml.prelude()
     assert {"Tensor", "Variable", "Linear", "Adam", "DataLoader", "Trainer"} <= set(pre)
+
+
+def test_offset_arena_best_fit_split_and_coalesce():
+    """The native offset allocator: aligned blocks, best fit, neighbours merged on free,
+    deterministic offsets for the same call sequence, exhaustion reported as -1."""
+    import random
+    from axonml_b200.core.storage import OffsetArena
+    a = OffsetArena(1 << 20, 512)
+    x, y, z = a.alloc(1000), a.alloc(5000), a.alloc(300)
+    assert (x, y, z) == (0, 1024, 1024 + 5120) and a.block_size(y) == 5120
+    assert a.free(y) and not a.free(y) and not a.free(7)            # double free and a foreign offset are refused
+    assert a.alloc(4000) == 1024                                    # best fit: the hole, not the tail
+    assert a.alloc(600) == 1024 + 4096                              # the remainder of the hole
+    st = a.stats()
+    assert st["live_blocks"] == 4 and st["in_use"] == 1024 + 4096 + 1024 + 512
+    assert a.alloc(2 << 20) == -1
+    for off in (x, 1024, 1024 + 4096, z):
+        assert a.free(off)
+    st = a.stats()
+    assert st["in_use"] == 0 and st["free_blocks"] == 1 and st["largest_free"] == 1 << 20    # everything merged back
+    # random workload: no overlap, accounting exact, same offsets on a second arena given the same calls
+    rng = random.Random(0)
+    b = OffsetArena(1 << 20, 512)
+    live = {}
+    for step in range(2000):
+        if live and rng.random() < 0.45:
+            off = rng.choice(sorted(live))
+            assert a.free(off) and b.free(off)
+            del live[off]
+        else:
+            n = rng.randint(1, 40000)
+            off, off_b = a.alloc(n), b.alloc(n)
+            assert off == off_b
+            if off >= 0:
+                size = a.block_size(off)
+                assert off % 512 == 0 and size >= n
+                for o, s_ in live.items():
+                    assert off + size <= o or o + s_ <= off
+                live[off] = size
+    assert a.stats()["in_use"] == sum(live.values()) and a.stats()["peak"] >= a.stats()["in_use"]
+    a.reset()
+    assert a.stats()["in_use"] == 0 and a.alloc(1 << 20) == 0
+
+
+def test_caching_allocator_reuses_segments_without_new_allocations():
+    from axonml_b200.core import CachingDeviceAllocator, Device
+    al = CachingDeviceAllocator(Device.Cpu(), segment_bytes=1 << 20)
+    t1 = al.allocate(1000, torch.float32)
+    t2 = al.allocate(3000, torch.bfloat16)
+    assert t1.numel() == 1000 and t2.dtype == torch.bfloat16 and t1.data_ptr() % 512 == 0
+    t1.fill_(3.0)
+    t2.fill_(1.0)
+    assert float(t1.sum()) == 3000.0                                 # the two blocks do not overlap
+    p1 = t1.data_ptr()
+    al.deallocate(t1)
+    t3 = al.allocate(900, torch.float32)
+    assert t3.data_ptr() == p1 and al.stats()["segments"] == 1 and al.misses == 1 and al.hits == 2
+    big = al.allocate(3 << 20, torch.uint8)                          # larger than a segment: a segment of its own
+    assert al.stats()["segments"] == 2 and big.numel() == 3 << 20
+    al.deallocate(big)
+    al.empty_cache()
+    assert al.stats()["segments"] == 1                               # the idle segment went back, the busy one stayed
+    assert al.cached_bytes() == (1 << 20) - al.stats()["in_use"]

@@ -107,6 +107,51 @@ def test_one_trip_sum_of_small_vectors(nvls):
         assert res[r][1]["bfloat16"] < 2e-2 and res[r][1]["float32"] < 1e-5, res[r][1]
 
 
+def _arena_heap(rank, world, be):
+    """The symmetric heap in arena mode: one exchange, sub-buffers at equal offsets on every rank,
+    used by the all-reduce kernels exactly like individually exchanged buffers."""
+    from axonml_b200 import _native
+    from axonml_b200.parallel import ProcessGroup
+    from axonml_b200.parallel.fused import FusedAllReduce
+    from axonml_b200.parallel.symm import SymmetricHeap, SymmetricSlice
+    pg = ProcessGroup(be)
+    heap = SymmetricHeap(pg, arena_bytes=64 << 20)
+    far = FusedAllReduce(heap, 1 << 20, torch.bfloat16, device_epoch=True)
+    assert isinstance(far.stage, SymmetricSlice) and isinstance(far.comm.signals, SymmetricSlice)
+    offs = torch.tensor([far.stage.offset, far.comm.signals.offset, far._small.offset], device="cuda")
+    same = [torch.zeros_like(offs) for _ in range(world)]
+    torch.distributed.all_gather(same, offs)
+    assert all(torch.equal(t, offs) for t in same)                    # equal offsets on every rank
+    errs = []
+    for n in (4096, 300000):
+        torch.manual_seed(3 + rank)
+        x = torch.randn(n, device="cuda").bfloat16()
+        ref = x.clone().float()
+        torch.distributed.all_reduce(ref)
+        y = x.clone()
+        far.all_reduce_mean_(y)
+        errs.append(((y.float() - ref / world).abs().max() / ref.abs().max()).item())
+        if n * 2 <= far.SMALL_BYTES:
+            z = x.clone()
+            assert far.sum_small_(z)
+            errs.append(((z.float() - ref).abs().max() / ref.abs().max()).item())
+    before = heap.arena_stats()["in_use"]
+    tmp = heap.allocate(1000, torch.float32)
+    tmp.free()
+    assert heap.arena_stats()["in_use"] == before
+    big = heap.allocate(80 << 20, torch.uint8)                        # does not fit: its own allocation
+    assert not isinstance(big, SymmetricSlice)
+    torch.cuda.synchronize()
+    _native.check_status()
+    return max(errs)
+
+
+def test_symmetric_heap_arena_mode():
+    res = run_gpu_ranks(_arena_heap, WORLD, env={"AXONML_NVLS": "1"})
+    for r in range(WORLD):
+        assert res[r][1] < 2e-2, res[r][1]
+
+
 def _fsdp_fused_vs_nccl(rank, world, be):
     import copy
     from axonml_b200 import _native, optim
