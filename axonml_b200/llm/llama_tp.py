@@ -249,12 +249,52 @@ class TPPipelineStage(nn.Module):
         return self.model.loss_from_hidden(y[0], y[1], labels)
 
 
+class TPPipelineChunks(nn.Module):
+    """The model chunks a rank holds under the interleaved schedule (virtual stages ``s``, ``s +
+    pp``, ...) behind the interface of a single ``TPPipelineStage``: ``loss`` belongs to the chunk
+    that ends the model, parameter helpers cover all chunks."""
+
+    def __init__(self, chunks):
+        super().__init__()
+        self.chunks = nn.ModuleList(chunks)
+
+    @property
+    def model(self):
+        """Callers written for a single stage use ``stage.model``."""
+        return self
+
+    @property
+    def last_stage(self) -> bool:
+        return any(c.model.last_stage for c in self.chunks)
+
+    def loss(self, y, labels):
+        return next(c for c in self.chunks if c.model.last_stage).loss(y, labels)
+
+    def sync_replicated_grads(self) -> None:
+        for c in self.chunks:
+            c.model.sync_replicated_grads()
+
+    def load_full_state_dict(self, sd: dict) -> None:
+        for c in self.chunks:
+            c.model.load_full_state_dict(sd)
+
+    def full_state_dict(self) -> dict:
+        out = {}
+        for c in self.chunks:
+            out.update(c.model.full_state_dict())
+        return out
+
+
 def build_tp_pp(cfg: LLaMAConfig, world, tp: int, pp: int, seq_len: int, device=None, dtype=torch.bfloat16,
-                num_microbatches: int = 8):
+                num_microbatches: int = 8, chunks: int = 1):
     """Lays ``tp * pp`` ranks out as ``pp`` consecutive tensor-parallel groups (stage s = ranks
     ``[s*tp, (s+1)*tp)``) and returns ``(pipeline, stage_module, tp_group)`` for the calling rank.
     ``world``: a ``parallel.World``.  Every rank creates every sub-group (required by the
-    process-group rendezvous) and keeps the ones it belongs to."""
+    process-group rendezvous) and keeps the ones it belongs to.
+
+    ``chunks > 1`` selects the interleaved 1F1B schedule: the layers are cut into ``pp * chunks``
+    virtual stages and pipeline rank ``s`` holds stages ``s, s + pp, ...`` (a smaller bubble for
+    more, smaller transfers); the returned module is then a ``TPPipelineChunks``."""
     from ..parallel.pipeline import Pipeline, PipelineSchedule, PipelineStage
     rank = world.rank()
     if world.world_size() != tp * pp:
@@ -263,6 +303,20 @@ def build_tp_pp(cfg: LLaMAConfig, world, tp: int, pp: int, seq_len: int, device=
     tp_groups = [world.new_group(list(range(s * tp, (s + 1) * tp))) for s in range(pp)]
     pp_groups = [world.new_group([s * tp + t for s in range(pp)]) for t in range(tp)]
     tp_pg, pp_pg = tp_groups[my_stage], pp_groups[my_tp]
+    if chunks > 1:
+        n_stages = pp * chunks
+        if cfg.num_hidden_layers < n_stages:
+            raise ValueError(f"{cfg.num_hidden_layers} layers cannot fill {n_stages} virtual stages")
+        per = cfg.num_hidden_layers // n_stages
+        mine = {}
+        for sid in range(my_stage, n_stages, pp):
+            layers = range(sid * per, cfg.num_hidden_layers if sid == n_stages - 1 else (sid + 1) * per)
+            model = TPLLaMAForCausalLM(cfg, tp_pg, device=device, dtype=dtype, layers=layers,
+                                       first_stage=sid == 0, last_stage=sid == n_stages - 1)
+            mine[sid] = TPPipelineStage(model, seq_len)
+        stages = [PipelineStage(mine.get(sid), sid, sid % pp) for sid in range(n_stages)]
+        pipe = Pipeline(stages, pp_pg, PipelineSchedule.InterleavedOneFOneB, num_microbatches)
+        return pipe, TPPipelineChunks([mine[sid] for sid in sorted(mine)]), tp_pg
     per = cfg.num_hidden_layers // pp
     layers = range(my_stage * per, cfg.num_hidden_layers if my_stage == pp - 1 else (my_stage + 1) * per)
     model = TPLLaMAForCausalLM(cfg, tp_pg, device=device, dtype=dtype, layers=layers,

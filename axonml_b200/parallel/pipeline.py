@@ -132,6 +132,7 @@ class Pipeline(Module):
                                           if s.device_rank == self.pg.rank() and s.module is not None])
         self._shape_cache = {}
         self._pending = []
+        self.last_comm = None        # set by the scheduled (interleaved) path after every step
 
     def _drain(self) -> None:
         for work, _ in self._pending:

@@ -38,6 +38,8 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
     ap.add_argument("--comm", default="auto", choices=["auto", "nccl", "fused"],
                     help="gradient path at N>1: NCCL reduce-scatter + optimizer, or the fused kernel")
+    ap.add_argument("--pp-chunks", type=int, default=1,
+                    help="llama8b_tp_pp: model chunks per pipeline rank (> 1 = interleaved 1F1B, reports the transfer/compute split)")
     ap.add_argument("--no-baseline", action="store_true",
                     help="at N>1 skip the second measurement of the same config on plain NCCL collectives")
     return ap.parse_args()
@@ -565,7 +567,8 @@ def bench_llama_tp_pp(args):
     global_batch, n_micro = 8, 8
     torch.manual_seed(4321 + rank)
     w = World.init(pg.backend())
-    pipe, stage, tp_pg = build_tp_pp(cfg, w, world // 2, 2, S, device=dev, dtype=torch.bfloat16, num_microbatches=n_micro)
+    pipe, stage, tp_pg = build_tp_pp(cfg, w, world // 2, 2, S, device=dev, dtype=torch.bfloat16, num_microbatches=n_micro,
+                                     chunks=args.pp_chunks)
     if args.comm == "nccl":
         fused_gemm._ENGINES[id(tp_pg.backend())] = None
     stage.train()
@@ -597,15 +600,25 @@ def bench_llama_tp_pp(args):
     t = torch.tensor([m["last_loss"] if last_stage else 0.0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     tokens = global_batch * S
+    # interleaved schedule: how long the last step waited for transfers against how long it computed (max over ranks)
+    pipeline = None
+    if pipe.last_comm is not None:
+        c = torch.tensor([pipe.last_comm["wait_s"], pipe.last_comm["compute_s"]], device=dev)
+        dist.all_reduce(c, op=dist.ReduceOp.MAX)
+        pipeline = {"schedule": f"interleaved 1F1B, {args.pp_chunks} chunks per rank", "wait_ms_max": round(c[0].item() * 1e3, 2),
+                    "compute_ms_max": round(c[1].item() * 1e3, 2),
+                    "wait_fraction": round(c[0].item() / max(c[0].item() + c[1].item(), 1e-9), 3),
+                    "timing": "host clock around the receives and around the stage computations of the last step"}
     if rank == 0:
         print(json.dumps({
+            "pipeline": pipeline,
             "metric": "tokens/s 8B TP x PP (Llama-style 8B, tensor + pipeline parallel, training)",
             "value": round(tokens / (m["ms_per_step"] / 1000.0), 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(m["ms_per_step"], 3),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "axonml_b200",
             "config": {"model": f"llama-8b ({cfg.num_hidden_layers}L d4096 32q/8kv ffn14336 vocab128256)",
-                       "global_batch": global_batch, "seq_len": S, "parallelism": f"tp{world // 2} x pp2 (1F1B, {n_micro} microbatches)",
+                       "global_batch": global_batch, "seq_len": S, "parallelism": f"tp{world // 2} x pp2 ({'interleaved ' if args.pp_chunks > 1 else ''}1F1B, {n_micro} microbatches)",
                        "optimizer": "AdamW lr3e-4 b(0.9,0.95) wd0.1, fp32 master weights",
                        "l2_policy": "per-step working set (>= 14 GB per GPU) exceeds the 126 MB L2"},
             "clocks": m["clocks"],

@@ -651,6 +651,53 @@ def test_tensor_plus_pipeline_parallel_llama_matches_unsharded():
         assert errs and max(errs.values()) < 1e-3, errs
 
 
+def _tp_pp_llama_interleaved(rank, world, be, tp):
+    """TP x PP=2 with two model chunks per pipeline rank (interleaved 1F1B over four virtual stages)
+    against the unsharded model."""
+    import dataclasses
+    from axonml_b200.llm import LLaMAConfig, LLaMAForCausalLM
+    from axonml_b200.llm.llama_tp import TPPipelineChunks, build_tp_pp
+    from axonml_b200.parallel import World
+    cfg = dataclasses.replace(LLaMAConfig.tiny(), num_hidden_layers=4)
+    torch.manual_seed(11)
+    ref = LLaMAForCausalLM(cfg)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    S = 32
+    pipe, stage, tp_pg = build_tp_pp(cfg, World.init(be), tp, 2, S, dtype=torch.float32, num_microbatches=4, chunks=2)
+    assert isinstance(stage, TPPipelineChunks) and len(stage.chunks) == 2
+    stage.model.load_full_state_dict(sd)
+    torch.manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (4, S))
+    loss_ref, _ = ref.forward_with_loss(ids)
+    loss_ref.backward()
+    loss = pipe.train_step(ids, ids, stage.loss, act_dtype=torch.float32)
+    stage.model.sync_replicated_grads()
+    with torch.no_grad():
+        for p in stage.parameters():
+            p.copy_(p.grad)
+    g = stage.model.full_state_dict()
+    gref = dict(ref.named_parameters())
+    errs = {n: float((g[n] - gref[n].grad).abs().max() / (gref[n].grad.abs().max() + 1e-12))
+            for n in g if n in gref and ("q_proj" in n or "down_proj" in n or n == "lm_head.weight")}
+    layers_here = sorted({int(n.split(".")[2]) for n in g if n.startswith("model.layers.")})
+    return (float(loss) if loss is not None else None), float(loss_ref), errs, layers_here, stage.last_stage, pipe.last_comm
+
+
+@pytest.mark.parametrize("tp", [1, 2])
+def test_interleaved_tensor_plus_pipeline_parallel_llama_matches_unsharded(tp):
+    world = 2 * tp
+    res = run_ranks(_tp_pp_llama_interleaved, world, args=(tp,))
+    for r in range(world):
+        loss, loss_ref, errs, layers_here, last, comm = res[r][1]
+        stage_rank = r // tp
+        assert layers_here == ([0, 2] if stage_rank == 0 else [1, 3])         # virtual stages s and s + pp
+        assert last == (stage_rank == 1)
+        if last:
+            assert abs(loss - loss_ref) < 1e-4, (loss, loss_ref)
+        assert errs and max(errs.values()) < 1e-3, errs
+        assert comm["operations"] == 16 and 0.0 <= comm["overlap"] <= 1.0     # 4 microbatches x 2 chunks x (F, B)
+
+
 def _fsdp_train(rank, world, be, ckpt_dir, mode):
     """mode 'save': 2 steps, save a sharded checkpoint, 2 more steps.  mode 'resume': load the
     checkpoint (possibly written at another world size), run the same last 2 steps."""
