@@ -172,7 +172,7 @@ __device__ void copy_shard(const GatherParams& p, int me, int n, uint8_t* smem) 
       }
       __threadfence_system();
     } else if (!mc && threadIdx.x == 0) {
-      tma_store_wait_read<1>();            // all but this round's stores have read their stage
+      tma_store_wait_read<1>();            // all but the latest group of stores have read their stage
     }
     __syncthreads();
     if (chunk_done && (int)threadIdx.x < p.world)
