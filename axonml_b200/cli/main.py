@@ -203,6 +203,11 @@ def cmd_train(a, resume_from: str | None = None):
                                                                   "learning_rate": t.learning_rate, "optimizer": t.optimizer.name,
                                                                   "architecture": cfg.model.architecture},
                            directory=os.path.join(t.output_dir, "wandb"))
+    # one JSON object per line: the run's configuration first, then one line per epoch; the terminal
+    # interface follows this file (axonml tui --watch <output_dir>/training_log.jsonl)
+    log = open(os.path.join(t.output_dir, "training_log.jsonl"), "a" if resume_from else "w", buffering=1)
+    log.write(json.dumps({"model_name": cfg.model.architecture, "total_epochs": t.epochs, "batch_size": t.batch_size,
+                          "optimizer": t.optimizer.name, "total_batches": len(loader)}) + "\n")
     for epoch in range(start_epoch, t.epochs):
         t0, losses = time.time(), []
         for b in loader:
@@ -222,11 +227,15 @@ def cmd_train(a, resume_from: str | None = None):
         print(f"epoch {epoch + 1}/{t.epochs}  loss {mean:.4f}  val_acc {acc:.4f}  {time.time() - t0:.1f}s", flush=True)
         if wb is not None:
             wb.log_at_step(epoch + 1, {"train_loss": mean, **({} if acc != acc else {"val_accuracy": acc})})
+        log.write(json.dumps({"epoch": epoch + 1, "train_loss": mean, **({} if acc != acc else {"val_acc": acc}),
+                              "learning_rate": opt.get_lr(), "duration_secs": time.time() - t0}) + "\n")
         if t.checkpoint_frequency and (epoch + 1) % t.checkpoint_frequency == 0:
             ck = (Checkpoint.builder().model_state(StateDict.from_module(model))
                   .optimizer_state(optimizer_to_state_dict(opt)).training_state(state)
                   .config("architecture", cfg.model.architecture).config("val_acc", acc).build())
             save_checkpoint(ck, _checkpoint_path(t.output_dir, epoch + 1))
+    log.write(json.dumps({"status": "completed"}) + "\n")
+    log.close()
     if wb is not None:
         print(f"W&B offline run: {wb.finish()}")
     print(f"done: {t.output_dir}")

@@ -383,6 +383,7 @@ def add_parsers(sub) -> None:
 
     from . import tui
     p = sub.add_parser("tui", help="terminal user interface")
-    p.add_argument("--model"); p.add_argument("--data"); p.add_argument("--once", action="store_true",
-                                                                         help="render every view once and exit")
+    p.add_argument("--model"); p.add_argument("--data")
+    p.add_argument("--watch", help="training log (JSON lines) to follow in the Training and Graphs views")
+    p.add_argument("--once", action="store_true", help="render every view once and exit")
     p.set_defaults(fn=tui.cmd_tui)
