@@ -1,4 +1,5 @@
 """Audio processing (crates/axonml-audio)."""
-from .datasets import SyntheticCommandDataset, SyntheticMusicDataset, SyntheticSpeakerDataset
+from .datasets import (AudioClassificationDataset, AudioSeq2SeqDataset, SyntheticCommandDataset, SyntheticMusicDataset,
+                       SyntheticSpeakerDataset)
 from .transforms import (MFCC, AddNoise, MelSpectrogram, NormalizeAudio, PitchShift, Resample, TimeStretch,
                          TrimSilence, mel_filterbank)

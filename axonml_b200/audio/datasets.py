@@ -56,3 +56,69 @@ class SyntheticSpeakerDataset(_Synthetic):
         pitch = 100.0 + 10 * label
         src = torch.sign(torch.sin(2 * math.pi * pitch * t))
         return 0.5 * src * (torch.sin(2 * math.pi * f1 * t) + 0.6 * torch.sin(2 * math.pi * f2 * t)) + 0.03 * torch.randn(self.len_s, generator=g)
+
+
+class AudioClassificationDataset(Dataset):
+    """Waveforms with class labels held in memory (datasets.rs:18-75).  ``get`` returns the class
+    index; ``one_hot=True`` gives the reference's one-hot float target instead."""
+
+    def __init__(self, waveforms, labels, sample_rate: int, num_classes: int, one_hot: bool = False):
+        if len(waveforms) != len(labels):
+            raise ValueError(f"{len(waveforms)} waveforms but {len(labels)} labels")
+        bad = [l for l in labels if not 0 <= int(l) < num_classes]
+        if bad:
+            raise ValueError(f"label {bad[0]} is outside 0..{num_classes - 1}")
+        self.waveforms = [torch.as_tensor(w, dtype=torch.float32) for w in waveforms]
+        self.labels = [int(l) for l in labels]
+        self._sr, self._classes, self.one_hot = sample_rate, num_classes, one_hot
+
+    @classmethod
+    def new(cls, waveforms, labels, sample_rate, num_classes): return cls(waveforms, labels, sample_rate, num_classes)
+
+    def len(self) -> int: return len(self.waveforms)
+    def sample_rate(self) -> int: return self._sr
+    def num_classes(self) -> int: return self._classes
+
+    def get(self, i: int):
+        if not 0 <= i < self.len():
+            return None
+        if self.one_hot:
+            t = torch.zeros(self._classes)
+            t[self.labels[i]] = 1.0
+            return self.waveforms[i], t
+        return self.waveforms[i], torch.tensor(self.labels[i], dtype=torch.long)
+
+
+class AudioSeq2SeqDataset(Dataset):
+    """Pairs of source and target waveforms (datasets.rs:451-505)."""
+
+    def __init__(self, sources, targets):
+        if len(sources) != len(targets):
+            raise ValueError(f"{len(sources)} sources but {len(targets)} targets")
+        self.sources = [torch.as_tensor(s, dtype=torch.float32) for s in sources]
+        self.targets = [torch.as_tensor(t, dtype=torch.float32) for t in targets]
+
+    @classmethod
+    def new(cls, sources, targets): return cls(sources, targets)
+
+    @classmethod
+    def noise_reduction_task(cls, num_samples: int, sample_rate: int, duration: float):
+        """Noisy sine -> clean sine: tone i has frequency 200 + (50 i mod 800) Hz and amplitude 0.5;
+        the source adds uniform noise in [-0.2, 0.2) drawn from a generator seeded with i."""
+        n = int(sample_rate * duration)
+        t = torch.arange(n, dtype=torch.float32) / sample_rate
+        sources, targets = [], []
+        for i in range(num_samples):
+            freq = 200.0 + (i * 50.0) % 800.0
+            clean = 0.5 * torch.sin(2 * math.pi * freq * t)
+            g = torch.Generator().manual_seed(i)
+            sources.append(clean + (torch.rand(n, generator=g) * 0.4 - 0.2))
+            targets.append(clean)
+        return cls(sources, targets)
+
+    def len(self) -> int: return len(self.sources)
+
+    def get(self, i: int):
+        if not 0 <= i < self.len():
+            return None
+        return self.sources[i], self.targets[i]

@@ -2,8 +2,10 @@
 ``Variable``, ``backward``, ``no_grad`` / ``enable_grad`` / ``inference_mode``, ``amp.autocast``,
 ``checkpoint`` / ``checkpoint_sequential`` (real recomputation; the reference's version only runs
 under no_grad, checkpoint.rs:70-95), ``numerical_gradient`` / ``gradcheck``."""
-from .amp import AutocastGuard, AutocastPolicy, autocast, disable_autocast, is_autocast_enabled
+from .amp import (AutocastGuard, AutocastPolicy, autocast, autocast_depth, autocast_dtype, disable_autocast,
+                  is_autocast_enabled)
 from .checkpoint import checkpoint, checkpoint_sequential
-from .grad_mode import (enable_grad, inference_mode, is_grad_enabled, is_inference_mode, no_grad,
+from .grad_mode import (NoGradGuard, enable_grad, inference_mode, is_grad_enabled, is_inference_mode, no_grad,
                         set_grad_enabled_context)
+from .graph import ComputationGraph, GradFn, GradientFunction, GraphNode
 from .variable import Variable, backward, gradcheck, numerical_gradient

@@ -21,10 +21,34 @@ def _device_type() -> str:
     return "cuda" if torch.cuda.is_available() else "cpu"
 
 
+_STACK: list = []          # dtypes of the enabled autocast regions this thread is inside
+
+
 @contextlib.contextmanager
 def autocast(dtype=torch.bfloat16, enabled: bool = True, device_type: str | None = None):
-    with torch.autocast(device_type or _device_type(), dtype=as_torch_dtype(dtype), enabled=enabled):
-        yield
+    td = as_torch_dtype(dtype)
+    with torch.autocast(device_type or _device_type(), dtype=td, enabled=enabled):
+        if enabled:
+            _STACK.append(td)
+        try:
+            yield
+        finally:
+            if enabled:
+                _STACK.pop()
+
+
+def autocast_dtype(device_type: str | None = None):
+    """Compute dtype of the innermost autocast region as a ``DType`` (meaningful only while
+    ``is_autocast_enabled()``; amp.rs:49-54)."""
+    from ..core.dtype import DType
+    if _STACK:
+        return DType.from_torch(_STACK[-1])
+    return DType.from_torch(torch.get_autocast_dtype(device_type or _device_type()))
+
+
+def autocast_depth() -> int:
+    """How many enabled ``autocast`` regions are open (amp.rs:56-60)."""
+    return len(_STACK)
 
 
 @contextlib.contextmanager

@@ -7,3 +7,25 @@ inference_mode = torch.inference_mode
 set_grad_enabled_context = torch.set_grad_enabled
 is_grad_enabled = torch.is_grad_enabled
 is_inference_mode = torch.is_inference_mode_enabled
+
+
+class NoGradGuard:
+    """Gradient recording is off from construction until ``drop()`` (or the end of a ``with``
+    block); the previous mode comes back afterwards (no_grad.rs: ``NoGradGuard::new`` + Drop)."""
+
+    def __init__(self):
+        self._prev = torch.is_grad_enabled()
+        self._live = True
+        torch.set_grad_enabled(False)
+
+    @classmethod
+    def new(cls): return cls()
+
+    def drop(self) -> None:
+        if self._live:
+            torch.set_grad_enabled(self._prev)
+            self._live = False
+
+    def __enter__(self): return self
+    def __exit__(self, *exc): self.drop()
+    def __del__(self): self.drop()

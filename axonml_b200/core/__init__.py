@@ -1,7 +1,7 @@
 """Core runtime types (crates/axonml-core): Device, DType, errors, storage, backends."""
 from .device import (Device, DeviceCapabilities, as_torch_device, cuda_device_count,
                      default_device, vulkan_device_count)
-from .dtype import DType, as_torch_dtype
+from .dtype import DType, Float, Numeric, Scalar, as_torch_dtype
 from .error import *  # noqa: F401,F403
 from .error import AxonmlError, Error
 from .backends import (Backend, CpuBackend, CudaBackend, MetalBackend, VulkanBackend, WgpuBackend,

@@ -72,3 +72,60 @@ def as_torch_dtype(dt) -> torch.dtype:
     if isinstance(dt, str):
         return DType(dt).to_torch()
     raise TypeError(f"not a dtype: {dt!r}")
+
+
+# ---------------------------------------------------------------------------------------------
+# Scalar tower (dtype.rs:134-256).  The reference's traits are implemented per Rust scalar type;
+# here one descriptor object per dtype carries the same associated constants, and the classes
+# answer "does this dtype belong to the group" the way a trait bound would.
+class Scalar:
+    """Any element type a tensor can hold.  ``Scalar.of(dtype)`` returns the descriptor."""
+    _accepts = staticmethod(lambda d: True)
+
+    def __init__(self, dtype: DType):
+        self.DTYPE = dtype
+
+    def dtype(self) -> DType:
+        return self.DTYPE
+
+    @classmethod
+    def accepts(cls, dt) -> bool:
+        d = dt if isinstance(dt, DType) else DType.from_torch(as_torch_dtype(dt))
+        return cls._accepts(d)
+
+    @classmethod
+    def of(cls, dt):
+        d = dt if isinstance(dt, DType) else DType.from_torch(as_torch_dtype(dt))
+        if not cls._accepts(d):
+            raise TypeError(f"{d} is not a {cls.__name__} type")
+        return cls(d)
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({self.DTYPE})"
+
+
+class Numeric(Scalar):
+    """Scalars with arithmetic and an order: every dtype but Bool."""
+    _accepts = staticmethod(lambda d: d is not DType.Bool)
+
+    def __init__(self, dtype: DType):
+        super().__init__(dtype)
+        t = dtype.to_torch()
+        info = torch.finfo(t) if dtype.is_float() else torch.iinfo(t)
+        cast = float if dtype.is_float() else int
+        self.ZERO, self.ONE = cast(0), cast(1)
+        self._min, self._max = cast(info.min), cast(info.max)
+
+    def min_value(self): return self._min
+    def max_value(self): return self._max
+
+
+class Float(Numeric):
+    """Floating-point scalars: F16, BF16, F32, F64."""
+    _accepts = staticmethod(lambda d: d.is_float())
+
+    def __init__(self, dtype: DType):
+        super().__init__(dtype)
+        info = torch.finfo(dtype.to_torch())
+        self.NAN, self.INFINITY, self.NEG_INFINITY = float("nan"), float("inf"), float("-inf")
+        self.EPSILON, self.MIN_POSITIVE = float(info.eps), float(info.tiny)

@@ -13,6 +13,32 @@ from ..jit.trace import Tracer
 from ..ops.linear import linear
 
 
+class FusionError(Exception):
+    """Errors of the fusion package (crates/axonml-fusion/src/error.rs:15-40), one subclass per variant."""
+
+
+class ShapeMismatch(FusionError, ValueError):
+    def __init__(self, expected, actual):
+        super().__init__(f"Invalid input shape: expected {list(expected)}, got {list(actual)}")
+        self.expected, self.actual = list(expected), list(actual)
+
+
+class NotFusable(FusionError):
+    def __init__(self, what): super().__init__(f"Pattern not fusable: {what}")
+
+
+class InvalidConfig(FusionError, ValueError):
+    def __init__(self, what): super().__init__(f"Invalid fusion configuration: {what}")
+
+
+class ExecutionError(FusionError, RuntimeError):
+    def __init__(self, what): super().__init__(f"Execution error: {what}")
+
+
+class TensorError(FusionError):
+    def __init__(self, what): super().__init__(f"Tensor conversion error: {what}")
+
+
 class FusedOp:
     def execute(self, x: torch.Tensor) -> torch.Tensor: raise NotImplementedError
     def name(self) -> str: return type(self).__name__
@@ -31,13 +57,24 @@ class Activation(enum.Enum):
 
 class FusedLinear(FusedOp):
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, activation=Activation.None_):
+        if weight.dim() != 2:
+            raise InvalidConfig(f"weight must be [out_features, in_features], got {list(weight.shape)}")
+        if bias is not None and tuple(bias.shape) != (weight.shape[0],):
+            raise ShapeMismatch([weight.shape[0]], bias.shape)
         self.weight, self.bias = weight, bias
-        self.activation = activation if isinstance(activation, Activation) else Activation(activation or "none")
+        try:
+            self.activation = activation if isinstance(activation, Activation) else Activation(activation or "none")
+        except ValueError as e:
+            raise InvalidConfig(f"unknown activation {activation!r}") from e
 
     @classmethod
     def new(cls, weight, bias=None, activation=Activation.None_): return cls(weight, bias, activation)
 
-    def execute(self, x): return linear(x, self.weight, self.bias, self.activation.value)
+    def execute(self, x):
+        if x.shape[-1] != self.weight.shape[1]:
+            raise ShapeMismatch([self.weight.shape[1]], [x.shape[-1]])
+        return linear(x, self.weight, self.bias, self.activation.value)
+
     def num_ops(self) -> int: return 1 + (self.bias is not None) + (self.activation is not Activation.None_)
     def name(self) -> str: return f"FusedLinear[{self.activation.value}]"
 
@@ -126,3 +163,29 @@ def fuse_linear(weight, bias=None, activation=Activation.None_) -> FusedLinear:
 
 def fused_elementwise() -> FusedElementwiseBuilder:
     return FusedElementwiseBuilder()
+
+
+# convenience constructors (crates/axonml-fusion/src/linear.rs:206-224, elementwise.rs:241-262)
+def fuse_matmul_bias_relu(weight, bias) -> FusedLinear: return FusedLinear(weight, bias, Activation.Relu)
+def fuse_matmul_bias_gelu(weight, bias) -> FusedLinear: return FusedLinear(weight, bias, Activation.Gelu)
+def fuse_matmul_bias(weight, bias) -> FusedLinear: return FusedLinear(weight, bias, Activation.None_)
+
+
+def fuse_elementwise(ops) -> FusedElementwise:
+    """Chain from a list of steps: ``ElementwiseOp`` members for the argument-free ones, ``(op,
+    arg, ...)`` tuples for Add / Mul / LeakyRelu / Clamp."""
+    steps = []
+    for o in ops:
+        op, args = (o[0], tuple(float(a) for a in o[1:])) if isinstance(o, (tuple, list)) else (o, ())
+        if not isinstance(op, ElementwiseOp):
+            raise InvalidConfig(f"{op!r} is not an ElementwiseOp")
+        steps.append((op, args))
+    return FusedElementwise(steps)
+
+
+def fused_add_relu(bias: float) -> FusedElementwise: return FusedElementwise.builder().add(bias).relu().build()
+def fused_mul_add(scale: float, bias: float) -> FusedElementwise: return FusedElementwise.builder().mul(scale).add(bias).build()
+
+
+def fused_scale_bias_relu(scale: float, bias: float) -> FusedElementwise:
+    return FusedElementwise.builder().mul(scale).add(bias).relu().build()

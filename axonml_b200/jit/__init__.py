@@ -3,6 +3,8 @@ from .cache import CacheStats, FunctionCache
 from .codegen import CompiledFunction, JitCompiler, generate_cuda, interpret
 from .compile import (Backend, CompileConfig, CompiledModel, CompileStats, LazyCompiled, Mode, compile_fn,
                       compile_fn_with_config, compile_graph, compile_graph_with_config)
-from .ir import DataType, Graph, Node, Op
+from . import error
+from .error import JitError
+from .ir import DataType, Graph, Node, NodeId, Op, Shape
 from .optimize import OptimizationPass, Optimizer
 from .trace import TracedValue, Tracer, trace

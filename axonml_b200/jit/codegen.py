@@ -15,6 +15,7 @@ import torch
 import torch.nn.functional as F
 
 from .cache import FunctionCache
+from .error import InputNotFound, OutputNotFound, ShapeMismatch, UnsupportedOp
 from .ir import Graph
 from .optimize import Optimizer
 
@@ -27,7 +28,10 @@ def interpret(graph: Graph, inputs: dict) -> dict:
     for n in graph.nodes:
         k, a = n.op.kind, [v[i] for i in n.op.inputs]
         at = n.op.attr
-        if k == "Input": r = inputs[at("name")]
+        if k == "Input":
+            if at("name") not in inputs:
+                raise InputNotFound(at("name"))
+            r = inputs[at("name")]
         elif k == "Output":
             r = a[0]
             outs[at("name")] = r
@@ -70,7 +74,7 @@ def interpret(graph: Graph, inputs: dict) -> dict:
         elif k == "Where": r = torch.where(a[0].bool(), a[1], a[2])
         elif k == "Cast": r = a[0].to(_TORCH_DT[at("dtype")])
         elif k == "Contiguous": r = a[0].contiguous()
-        else: raise NotImplementedError(k)
+        else: raise UnsupportedOp(k)
         v[n.id] = r
     return outs
 
@@ -201,11 +205,26 @@ class CompiledFunction:
         g = self._graph
         tin = {}
         for name, vals in (inputs.items() if isinstance(inputs, dict) else inputs):
+            if name not in g.inputs:
+                raise InputNotFound(name)
             t = torch.as_tensor(vals, dtype=torch.float32)
-            tin[name] = t.reshape(g.node(g.inputs[name]).shape) if t.dim() <= 1 else t
+            want = g.node(g.inputs[name]).shape
+            if t.dim() <= 1:
+                n = 1
+                for d in want:
+                    n *= d
+                if t.numel() != n:
+                    raise ShapeMismatch(want, t.shape)
+                t = t.reshape(want)
+            tin[name] = t
+        missing = [k for k in g.inputs if k not in tin]
+        if missing:
+            raise InputNotFound(missing[0])
         outs = self.run_tensors(tin)
         if isinstance(inputs, dict):
             return {k: v.reshape(-1).tolist() for k, v in outs.items()}
+        if not outs:
+            raise OutputNotFound("the graph declares no output")
         return next(iter(outs.values())).reshape(-1).tolist()
 
 

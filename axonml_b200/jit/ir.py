@@ -5,6 +5,58 @@ from __future__ import annotations
 import dataclasses
 import enum
 
+from .error import InvalidGraph, UnsupportedOp
+
+
+class NodeId(int):
+    """Index of a node in its graph (ir.rs:8-16); an ``int`` with the reference's ``index()``."""
+
+    def index(self) -> int:
+        return int(self)
+
+    def __repr__(self) -> str:
+        return f"%{int(self)}"
+
+
+class Shape(tuple):
+    """Static shape of a traced value (ir.rs:52-110)."""
+
+    def __new__(cls, dims=()):
+        return super().__new__(cls, (int(d) for d in dims))
+
+    @classmethod
+    def new(cls, dims): return cls(dims)
+
+    def dims(self) -> tuple: return tuple(self)
+    def ndim(self) -> int: return len(self)
+
+    def numel(self) -> int:
+        n = 1
+        for d in self:
+            n *= d
+        return n
+
+    def broadcast_compatible(self, other) -> bool:
+        other = tuple(other)
+        for i in range(max(len(self), len(other))):
+            a = self[len(self) - 1 - i] if i < len(self) else 1
+            b = other[len(other) - 1 - i] if i < len(other) else 1
+            if a != b and a != 1 and b != 1:
+                return False
+        return True
+
+    def broadcast_shape(self, other):
+        """The common shape, or ``None`` when the two do not broadcast."""
+        if not self.broadcast_compatible(other):
+            return None
+        other = tuple(other)
+        out = []
+        for i in range(max(len(self), len(other))):
+            a = self[len(self) - 1 - i] if i < len(self) else 1
+            b = other[len(other) - 1 - i] if i < len(other) else 1
+            out.append(max(a, b) if 0 not in (a, b) else 0)
+        return Shape(reversed(out))
+
 
 class DataType(enum.Enum):
     F32 = "f32"
@@ -39,7 +91,7 @@ class Op:
     @staticmethod
     def make(kind: str, inputs=(), **attrs) -> "Op":
         if kind not in ALL_OPS:
-            raise ValueError(f"unknown op {kind}")
+            raise UnsupportedOp(kind)
         norm = tuple(sorted((k, tuple(v) if isinstance(v, list) else v) for k, v in attrs.items()))
         return Op(kind, tuple(inputs), norm)
 
@@ -65,8 +117,8 @@ class Graph:
     def new(cls): return cls()
 
     def add_node(self, op: Op, dtype: DataType, shape) -> int:
-        nid = len(self.nodes)
-        self.nodes.append(Node(nid, op, dtype, tuple(shape)))
+        nid = NodeId(len(self.nodes))
+        self.nodes.append(Node(nid, op, dtype, Shape(shape)))
         if op.kind == "Input":
             self.inputs[op.attr("name")] = nid
         if op.kind == "Output":
@@ -91,7 +143,7 @@ class Graph:
         for n in self.nodes:
             for i in n.op.inputs:
                 if not 0 <= i < n.id:
-                    raise ValueError(f"node {n.id} uses {i} before its definition")
+                    raise InvalidGraph(f"node {n.id} uses {i} before its definition")
 
     def signature(self) -> tuple:
         return tuple((n.op.kind, n.op.inputs, n.op.attrs, n.dtype.value, n.shape) for n in self.nodes)

@@ -27,6 +27,7 @@ import math
 
 import torch
 
+from .error import UnsupportedOp
 from .ir import Graph
 
 _UN = {"Neg": "(-{0})", "Abs": "fabsf({0})", "Sqrt": "sqrtf({0})", "Exp": "__expf({0})", "Log": "__logf({0})",
@@ -142,7 +143,7 @@ class _KernelBuilder:
         elif k == "Output":
             e = self.value(ins[0], idx)
         else:
-            raise NotImplementedError(k)
+            raise UnsupportedOp(k)
         v = self._new("v")
         self.stmts.append(f"const float {v} = {e};")
         self.memo[key] = v

@@ -7,6 +7,8 @@ import ctypes
 
 import torch
 
+from .error import CompilationFailed, JitRuntimeError
+
 
 def _bindings():
     try:
@@ -42,7 +44,7 @@ class Module:
             _, n = nvrtc.nvrtcGetProgramLogSize(prog)
             log = b" " * n
             nvrtc.nvrtcGetProgramLog(prog, log)
-            raise RuntimeError("NVRTC compilation failed:\n" + log.decode(errors="replace") + "\n" + source)
+            raise CompilationFailed("NVRTC:\n" + log.decode(errors="replace") + "\n" + source)
         _, n = nvrtc.nvrtcGetCUBINSize(prog)
         cubin = b" " * n
         nvrtc.nvrtcGetCUBIN(prog, cubin)
@@ -50,13 +52,13 @@ class Module:
         torch.zeros(1, device="cuda")          # make sure the primary context is current
         err, self._module = driver.cuModuleLoadData(cubin)
         if int(err) != 0:
-            raise RuntimeError(f"cuModuleLoadData failed: {err}")
+            raise CompilationFailed(f"cuModuleLoadData: {err}")
         self.source = source
 
     def function(self, name: str) -> "Function":
         err, fn = self._driver.cuModuleGetFunction(self._module, name.encode())
         if int(err) != 0:
-            raise RuntimeError(f"cuModuleGetFunction({name}) failed: {err}")
+            raise CompilationFailed(f"cuModuleGetFunction({name}): {err}")
         return Function(self, fn)
 
 
@@ -70,7 +72,7 @@ class Function:
         stream = torch.cuda.current_stream().cuda_stream
         (err,) = driver.cuLaunchKernel(self._fn, grid, 1, 1, block, 1, 1, 0, stream, (tuple(args), tuple(arg_types)), 0)
         if int(err) != 0:
-            raise RuntimeError(f"cuLaunchKernel failed: {err}")
+            raise JitRuntimeError(f"cuLaunchKernel: {err}")
 
 
 class Kernel(Function):

@@ -3,6 +3,8 @@
 re-concatenates on every token, attention.rs:61-67); tensors are token-major ``[B, S, H, D]``."""
 from __future__ import annotations
 
+import dataclasses
+
 import torch
 
 from ..ops.attention import sdpa
@@ -52,6 +54,17 @@ class LayerKVCache:
     def clear(self) -> None:
         for c in self.layers:
             c.clear()
+
+
+@dataclasses.dataclass
+class FlashAttentionConfig:
+    """Parity: crates/axonml-llm/src/attention.rs:636-660.  The block sizes are accepted for
+    compatibility; the GPU kernel tiles 128 queries x 128 keys on its own."""
+    block_size_q: int = 64
+    block_size_kv: int = 64
+    causal: bool = True
+    softmax_scale: float | None = None
+    dropout_p: float = 0.0
 
 
 class FlashAttention:

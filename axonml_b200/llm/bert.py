@@ -7,6 +7,7 @@ import torch
 from .. import nn
 from ..ops.attention import sdpa
 from .config import BertConfig
+from .hf_loader import LoadStateDict
 
 
 class BertEmbeddings(nn.Module):
@@ -52,7 +53,7 @@ class BertLayer(nn.Module):
         return self.out_norm(x + self.dropout(self.output(self.intermediate(x))))
 
 
-class Bert(nn.Module):
+class Bert(nn.Module, LoadStateDict):
     def __init__(self, cfg: BertConfig):
         super().__init__()
         self.cfg = cfg

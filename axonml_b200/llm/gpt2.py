@@ -19,6 +19,7 @@ from ..ops import misc as Mi
 from ..ops.attention import sdpa, sdpa_packed
 from ..ops.linear import linear
 from .config import GPT2Config
+from .hf_loader import LoadStateDict
 
 
 class GPT2Embedding(nn.Module):
@@ -144,7 +145,7 @@ class GPT2(nn.Module):
         return h
 
 
-class GPT2LMHead(nn.Module):
+class GPT2LMHead(nn.Module, LoadStateDict):
     """Language-model head tied to the token embedding (``lm_head.weight`` is ``wte``)."""
 
     def __init__(self, cfg: GPT2Config, device=None, dtype=None):

@@ -23,6 +23,7 @@ from ..ops.attention import sdpa, sdpa_packed
 from ..ops.linear import linear
 from .attention import LayerKVCache
 from .config import LLaMAConfig
+from .hf_loader import LoadStateDict
 
 
 class RotaryEmbedding(nn.Module):
@@ -164,7 +165,7 @@ class LLaMA(nn.Module):
     forward_with_cache = forward
 
 
-class LLaMAForCausalLM(nn.Module):
+class LLaMAForCausalLM(nn.Module, LoadStateDict):
     def __init__(self, cfg: LLaMAConfig, tie_word_embeddings: bool = False, device=None, dtype=None):
         super().__init__()
         self.cfg = cfg

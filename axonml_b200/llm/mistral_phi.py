@@ -10,6 +10,7 @@ from ..ops.attention import sdpa
 from ..ops.linear import linear
 from .attention import LayerKVCache
 from .config import MistralConfig, PhiConfig
+from .hf_loader import LoadStateDict
 from .llama import LLaMAForCausalLM
 
 
@@ -73,7 +74,7 @@ class PhiDecoderLayer(nn.Module):
         return x + self.fc2(self.fc1(self.post_layernorm(x)))
 
 
-class PhiForCausalLM(nn.Module):
+class PhiForCausalLM(nn.Module, LoadStateDict):
     def __init__(self, cfg: PhiConfig):
         super().__init__()
         self.cfg = cfg

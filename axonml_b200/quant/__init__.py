@@ -3,4 +3,4 @@ from .calibration import CalibrationData, CalibrationMethod, calibrate, calibrat
 from .gguf import GGUFFile, read_gguf, write_gguf
 from .quantize import (QuantizationStats, compute_quantization_error, compute_quantization_stats,
                        dequantize_block, dequantize_tensor, quantize_model, quantize_tensor)
-from .types import QuantError, QuantizedTensor, QuantType
+from .types import QuantError, QuantizedBlock, QuantizedTensor, QuantType

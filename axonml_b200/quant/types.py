@@ -92,3 +92,55 @@ class QuantizedTensor:
 
     def to(self, device) -> "QuantizedTensor":
         return QuantizedTensor(self.shape, self.quant_type, self.data.to(device), self.layout)
+
+    def block(self, index: int) -> "QuantizedBlock":
+        """One block of the tensor as a ``QuantizedBlock`` (a copy of its bytes)."""
+        n = self.quant_type.bytes_per_block()
+        if not 0 <= index < self.num_blocks():
+            raise IndexError(f"block {index} of {self.num_blocks()}")
+        return QuantizedBlock(self.quant_type, bytes(self.data[index * n:(index + 1) * n].cpu().numpy().tobytes()), self.layout)
+
+    def blocks(self):
+        return (self.block(i) for i in range(self.num_blocks()))
+
+
+@dataclasses.dataclass(frozen=True)
+class QuantizedBlock:
+    """One block of quantised values with its header (types.rs:128-288: ``Q8Block{scale: f16, data:
+    [i8; 32]}``, ``Q4Block{scale, [u8; 16]}``, ``Q4_1Block{scale, min, [u8; 16]}`` and the
+    ``QuantizedBlock`` enum over them).  The block is its packed bytes plus the type; ``scale`` /
+    ``min`` read the fp16 header fields and ``dequantize`` expands the values."""
+    quant_type: QuantType
+    data: bytes
+    layout: str = "ggml"
+
+    def __post_init__(self):
+        if len(self.data) != self.quant_type.bytes_per_block():
+            raise QuantError(f"a {self.quant_type.value} block is {self.quant_type.bytes_per_block()} bytes, got {len(self.data)}")
+
+    @classmethod
+    def from_bytes(cls, quant_type: QuantType, data: bytes, layout: str = "ggml"):
+        return cls(quant_type, bytes(data), layout)
+
+    def to_bytes(self) -> bytes:
+        return self.data
+
+    def _half(self, offset: int) -> float:
+        import struct
+        return struct.unpack_from("<e", self.data, offset)[0]
+
+    @property
+    def scale(self) -> float | None:
+        """fp16 scale ``d`` of the block (None for the unquantised types)."""
+        return self._half(0) if self.quant_type.is_block_quantized() else None
+
+    @property
+    def min(self) -> float | None:
+        """fp16 minimum ``m`` of the asymmetric types (Q4_1, Q5_1) and ``dmin`` of Q4_K."""
+        return self._half(2) if self.quant_type in (QuantType.Q4_1, QuantType.Q5_1, QuantType.Q4_K) else None
+
+    def dequantize(self) -> list:
+        from .quantize import dequantize_tensor
+        q = QuantizedTensor([self.quant_type.block_size()], self.quant_type, torch.frombuffer(bytearray(self.data), dtype=torch.uint8),
+                            self.layout)
+        return dequantize_tensor(q).tolist()

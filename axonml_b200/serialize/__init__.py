@@ -9,9 +9,9 @@ import os
 from . import codec
 from .checkpoint import (Checkpoint, CheckpointBuilder, TrainingState, decode_checkpoint,
                          encode_checkpoint, optimizer_from_state_dict, optimizer_to_state_dict)
-from .convert import (OnnxOpType, convert_from_pytorch_key, convert_to_pytorch_key,
-                      from_pytorch_state_dict, pytorch_layer_mapping, to_pytorch_state_dict,
-                      transpose_linear_weights)
+from .convert import (OnnxOpType, convert_from_pytorch, convert_from_pytorch_key, convert_to_pytorch_key, from_onnx_shape,
+                      from_pytorch_key, from_pytorch_state_dict, pytorch_layer_mapping, to_onnx_shape, to_pytorch_key,
+                      to_pytorch_state_dict, transpose_linear_weights)
 from .format import Format, detect_format, detect_format_from_bytes
 from .state_dict import StateDict, StateDictEntry, TensorData
 

@@ -20,6 +20,31 @@ def convert_to_pytorch_key(key: str) -> str:
     return key
 
 
+# the reference's function names (convert.rs:20-39)
+from_pytorch_key = convert_from_pytorch_key
+to_pytorch_key = convert_to_pytorch_key
+
+
+def convert_from_pytorch(state_dict: StateDict) -> StateDict:
+    """A copy of ``state_dict`` with every key passed through ``from_pytorch_key`` (convert.rs:247-256)."""
+    out = StateDict()
+    for k, e in state_dict.entries():
+        out.insert_entry(from_pytorch_key(k), e)
+    out.metadata = dict(state_dict.metadata)
+    return out
+
+
+def to_onnx_shape(shape, include_batch: bool = False) -> list:
+    """Shape as ONNX dimensions; with ``include_batch`` a dynamic (-1) batch dimension is put in front."""
+    dims = [int(d) for d in shape]
+    return [-1] + dims if include_batch else dims
+
+
+def from_onnx_shape(shape, default_dynamic: int = 1) -> list:
+    """ONNX dimensions as a concrete shape: dynamic (negative) entries become ``default_dynamic``."""
+    return [default_dynamic if int(d) < 0 else int(d) for d in shape]
+
+
 def from_pytorch_state_dict(tensors: dict) -> StateDict:
     sd = StateDict()
     for k, v in tensors.items():

@@ -2,9 +2,11 @@
 operations and sparse formats keep the reference's names."""
 import torch
 
-from . import ops, sparse, view
+from ..core import DType, Device, Error
+from . import ops, shape, sparse, view
 from .creation import (arange, diag, empty, eye, from_vec, full, full_like, linspace, logspace, normal,
                        ones, ones_like, rand, randint, randn, scalar, uniform, zeros, zeros_like)
+from .shape import Shape, Strides
 from .sparse import SparseCOO, SparseCSR
 
 Tensor = torch.Tensor

@@ -4,7 +4,10 @@ from .models import (MLP, BasicBlock, Bottleneck, LeNet, ResNet, SimpleCNN, resn
                      resnet50)
 from . import datasets, transforms
 from .datasets import (CIFAR10, CIFAR100, MNIST, FashionMNIST, SyntheticCIFAR, SyntheticImageNet, SyntheticMNIST)
-from .models import (VGG, Transformer, TransformerDecoder, TransformerEncoder, VisionTransformer, vgg11, vgg16,
-                     vgg19)
+from .models import (VGG, Transformer, TransformerDecoder, TransformerEncoder, VisionTransformer, vgg11, vgg11_bn, vgg13,
+                     vgg13_bn, vgg16, vgg16_bn, vgg19, vgg19_bn)
 from .transforms import (CenterCrop, ColorJitter, Grayscale, ImageNormalize, Pad, RandomHorizontalFlip,
                          RandomRotation, RandomVerticalFlip, Resize, ToTensorImage)
+from . import hub
+from .hub import (HubError, PretrainedModel, cache_dir, download_weights, is_cached, list_models, load_state_dict, model_info,
+                  model_registry)

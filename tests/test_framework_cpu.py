@@ -249,3 +249,156 @@ def test_caching_allocator_reuses_segments_without_new_allocations():
     al.empty_cache()
     assert al.stats()["segments"] == 1                               # the idle segment went back, the busy one stayed
     assert al.cached_bytes() == (1 << 20) - al.stats()["in_use"]
+
+
+def test_shape_arithmetic_matches_torch():
+    """tensor.shape helpers against what torch reports for the same views (shape.rs tests)."""
+    from axonml_b200.core.error import BroadcastError, IndexOutOfBounds, InvalidDimension, InvalidOperation, ShapeMismatch
+    from axonml_b200.tensor import shape as S
+    t = torch.arange(24.0).view(2, 3, 4)
+    assert S.numel((2, 3, 4)) == 24 and S.numel(()) == 1 and S.numel((3, 0)) == 0
+    assert S.contiguous_strides((2, 3, 4)) == t.stride() and S.contiguous_strides(()) == ()
+    assert S.is_contiguous(t.shape, t.stride()) and not S.is_contiguous(t.transpose(0, 2).shape, t.transpose(0, 2).stride())
+    assert S.is_contiguous((2, 1, 4), (4, 99, 1)) and S.is_contiguous((0, 3), (7, 7))
+    for idx in ((0, 0, 0), (1, 2, 3), (1, 0, 2)):
+        lin = S.linear_index(idx, t.stride())
+        assert t.flatten()[lin] == t[idx] and S.unravel_index(lin, t.shape) == list(idx)
+    tt = t.transpose(0, 2)
+    assert S.transpose_shape(t.shape, 0, 2) == tuple(tt.shape) and S.transpose_strides(t.stride(), 0, 2) == tt.stride()
+    for a, b in (((2, 3, 4), (4,)), ((5, 1, 4), (3, 1)), ((1,), (7, 2)), ((), (2, 2)), ((2, 0), (1,))):
+        assert S.broadcast_shape(a, b) == tuple(torch.broadcast_shapes(a, b)) and S.can_broadcast(a, b)
+    assert not S.can_broadcast((2, 3), (4,))
+    with pytest.raises(BroadcastError):
+        S.broadcast_shape((2, 3), (3, 2))
+    src = torch.arange(3.0).view(3, 1)
+    assert S.broadcast_strides(src.shape, src.stride(), (2, 3, 4)) == src.expand(2, 3, 4).stride()
+    with pytest.raises(BroadcastError):
+        S.broadcast_strides((3, 2), (2, 1), (3, 4))
+    assert S.reshape((2, 3, 4), (6, -1)) == (6, 4) and S.reshape((2, 3, 4), (24,)) == (24,) and S.reshape((0, 4), (-1, 2)) == (0, 2)
+    with pytest.raises(InvalidOperation):
+        S.reshape((2, 3), (-1, -1))
+    with pytest.raises(InvalidOperation):
+        S.reshape((2, 3), (4, -1))
+    with pytest.raises(InvalidOperation):
+        S.reshape((2, 3), (-2, 3))
+    with pytest.raises(ShapeMismatch):
+        S.reshape((2, 3), (7,))
+    assert S.squeeze((1, 3, 1, 4)) == (3, 4) and S.squeeze((1, 3, 1), 2) == (1, 3) and S.squeeze((1, 3), 1) == (1, 3) and S.squeeze((2,), 5) == (2,)
+    assert S.unsqueeze((2, 3), 0) == (1, 2, 3) and S.unsqueeze((2, 3), 2) == (2, 3, 1)
+    with pytest.raises(InvalidDimension):
+        S.unsqueeze((2, 3), 3)
+    with pytest.raises(InvalidDimension):
+        S.transpose_shape((2, 3), 0, 2)
+    assert S.normalize_dim(-1, 3) == 2 and S.normalize_dim(0, 3) == 0
+    for bad in (3, -4):
+        with pytest.raises(InvalidDimension):
+            S.normalize_dim(bad, 3)
+    S.validate_indices((1, 2), (2, 3))
+    with pytest.raises(IndexOutOfBounds):
+        S.validate_indices((1, 3), (2, 3))
+    with pytest.raises(InvalidOperation):
+        S.validate_indices((1,), (2, 3))
+    from axonml_b200 import tensor
+    assert tensor.Shape is tuple and tensor.Strides is tuple and tensor.DType.F32.size_of() == 4
+
+
+def test_scalar_tower_constants():
+    from axonml_b200.core import DType, Float, Numeric, Scalar
+    assert Scalar.of(DType.Bool).dtype() is DType.Bool and Scalar.accepts(torch.int8)
+    assert not Numeric.accepts(DType.Bool) and Numeric.accepts(DType.U8) and not Float.accepts(DType.I32) and Float.accepts(torch.bfloat16)
+    n = Numeric.of(DType.I8)
+    assert (n.ZERO, n.ONE, n.min_value(), n.max_value()) == (0, 1, -128, 127) and Numeric.of(DType.U8).max_value() == 255
+    f = Float.of(DType.F32)
+    assert f.EPSILON == torch.finfo(torch.float32).eps and f.max_value() == torch.finfo(torch.float32).max and f.NAN != f.NAN
+    assert f.INFINITY == float("inf") and f.NEG_INFINITY == float("-inf") and f.MIN_POSITIVE == torch.finfo(torch.float32).tiny
+    assert Float.of(DType.BF16).EPSILON == 2 ** -7 and Float.of(DType.F16).max_value() == 65504.0
+    with pytest.raises(TypeError):
+        Float.of(DType.I64)
+
+
+def test_computation_graph_view_and_gradient_functions():
+    from axonml_b200 import autograd as ag
+    w = torch.randn(4, 3, requires_grad=True)
+    b = torch.randn(4, requires_grad=True)
+    x = torch.randn(2, 3)
+    y = torch.tanh(x @ w.t() + b).sum()
+    g = ag.ComputationGraph.from_output(y)
+    assert len(g.leaves()) == 2 and all(n.requires_grad and n.topo_order == 0 for n in g.leaves())
+    names = [n.grad_fn.name() for n in g.operations()]
+    assert names[-1].startswith("Sum") and any(n.startswith("Tanh") for n in names) and any("Mm" in n or "Addmm" in n for n in names)
+    orders = [n.topo_order for n in g.nodes()]
+    assert orders == sorted(orders) and g.depth() == max(orders) >= 3              # inputs come before their users
+    assert g.len() == len(g) == len(names) + 2 and not g.is_empty() and g.get_node(0).is_leaf and g.get_node(999) is None
+    assert sum(g.op_counts().values()) == len(names)
+    dot = g.to_dot()
+    assert dot.startswith("digraph autograd {") and dot.count("->") >= len(names) and "shape=box" in dot
+    root = ag.GradFn(y.grad_fn)
+    assert root.id() == id(y.grad_fn) and root == ag.GradFn(y.grad_fn) and len(root.next_functions()) == 1
+    (gin,) = root.apply(torch.tensor(1.0))
+    assert gin.shape == (2, 4) and torch.all(gin == 1)
+    g.clear()
+    assert g.is_empty() and g.register_leaf(False).id == 0
+    op = g.register_operation(root, True)
+    assert not op.is_leaf and op.topo_order == 1 and op.id == 1
+    lone = ag.ComputationGraph.from_output(torch.ones(2))
+    assert lone.len() == 1 and not lone.get_node(0).requires_grad
+
+    class Cube(ag.GradientFunction):
+        def forward(self, x):
+            self.save_for_backward(x)
+            return x ** 3
+
+        def apply(self, grad_output):
+            (x,) = self.saved_tensors
+            return (3 * x ** 2 * grad_output,)
+
+    class ScaledAdd(ag.GradientFunction):
+        def __init__(self, alpha=2.0):
+            self.alpha = alpha
+
+        def forward(self, a, b):
+            return a + self.alpha * b
+
+        def apply(self, grad_output):
+            return grad_output, None                                          # b is treated as a constant
+
+    t = torch.randn(5, requires_grad=True)
+    out = Cube.call(t)
+    assert out.grad_fn is not None and Cube().name() == "Cube"
+    out.sum().backward()
+    assert torch.allclose(t.grad, 3 * t.detach() ** 2)
+    a, c = torch.randn(3, requires_grad=True), torch.randn(3, requires_grad=True)
+    ScaledAdd.call(a, c, alpha=0.5).sum().backward()
+    assert torch.all(a.grad == 1) and c.grad is None
+
+    class Wrong(ag.GradientFunction):
+        def forward(self, a, b): return a + b
+        def apply(self, grad_output): return (grad_output,)
+
+    with pytest.raises(RuntimeError, match="1 gradients for 2 inputs"):
+        Wrong.call(a, c).sum().backward()
+
+
+def test_no_grad_guard_and_autocast_state():
+    from axonml_b200 import autograd as ag
+    from axonml_b200.core import DType
+    x = torch.ones(2, requires_grad=True)
+    guard = ag.NoGradGuard()
+    assert not torch.is_grad_enabled() and not (x * 2).requires_grad
+    guard.drop(); guard.drop()
+    assert torch.is_grad_enabled() and (x * 2).requires_grad
+    with ag.NoGradGuard.new():
+        with ag.enable_grad():
+            assert (x * 2).requires_grad
+        assert not (x * 2).requires_grad
+    assert torch.is_grad_enabled()
+    assert ag.autocast_depth() == 0 and not ag.is_autocast_enabled("cpu")
+    with ag.autocast(DType.BF16, device_type="cpu"):
+        assert ag.is_autocast_enabled("cpu") and ag.autocast_dtype("cpu") is DType.BF16 and ag.autocast_depth() == 1
+        assert (torch.randn(4, 4) @ torch.randn(4, 4)).dtype == torch.bfloat16
+        with ag.autocast(torch.float16, device_type="cpu"):
+            assert ag.autocast_dtype("cpu") is DType.F16 and ag.autocast_depth() == 2
+        with ag.autocast(enabled=False, device_type="cpu"):
+            assert ag.autocast_depth() == 1
+        assert ag.autocast_dtype("cpu") is DType.BF16
+    assert ag.autocast_depth() == 0

@@ -256,3 +256,57 @@ def test_trainer_fit_with_early_stopping():
     metrics = t.evaluate(loader)
     acc = metrics.accuracy if hasattr(metrics, "accuracy") else metrics["accuracy"]
     assert acc > 0.85
+
+
+def test_jit_errors_node_ids_and_shapes():
+    from axonml_b200.jit import error as JE
+    g = jit.trace(lambda t: t.output("y", t.input("x", [2, 3]).relu().mul_scalar(2.0)))
+    assert all(isinstance(n.id, jit.NodeId) and n.id.index() == i for i, n in enumerate(g.nodes)) and repr(g.nodes[1].id) == "%1"
+    assert isinstance(g.nodes[0].shape, jit.Shape) and g.nodes[0].shape.numel() == 6 and g.nodes[0].shape.ndim() == 2
+    f = jit.JitCompiler().compile(g)
+    assert f.run([("x", [-1.0, 2.0, -3.0, 4.0, 0.5, -0.5])]) == [0.0, 4.0, 0.0, 8.0, 1.0, 0.0]
+    with pytest.raises(JE.InputNotFound) as e:
+        f.run([("z", [1.0] * 6)])
+    assert str(e.value) == "Input not found: z" and isinstance(e.value, (jit.JitError, KeyError))
+    with pytest.raises(JE.InputNotFound):
+        f.run([])
+    with pytest.raises(JE.ShapeMismatch) as e:
+        f.run([("x", [1.0, 2.0])])
+    assert e.value.expected == [2, 3] and e.value.found == [2]
+    with pytest.raises(JE.UnsupportedOp) as e:
+        jit.Op.make("Conv3d")
+    assert isinstance(e.value, NotImplementedError) and "Conv3d" in str(e.value)
+    bad = jit.Graph()
+    bad.add_node(jit.Op.make("Neg", [3]), jit.DataType.F32, [2])
+    with pytest.raises(JE.InvalidGraph):
+        bad.validate()
+    s = jit.Shape.new([4, 1, 3])
+    assert s.dims() == (4, 1, 3) and s.broadcast_compatible([5, 3]) and not s.broadcast_compatible([2, 3, 3])
+    assert s.broadcast_shape([5, 1]) == (4, 5, 3) and s.broadcast_shape([2, 2, 2]) is None and jit.Shape().numel() == 1
+    for cls in (JE.TypeMismatch("f32", "i64"), JE.CodegenError("x"), JE.JitRuntimeError("x"), JE.OutputNotFound("y"), JE.CompilationFailed("x")):
+        assert isinstance(cls, jit.JitError)
+    assert str(JE.TypeMismatch("f32", "i64")) == "Type mismatch: expected f32, found i64"
+
+
+def test_fusion_errors_and_convenience_constructors():
+    w, b = torch.randn(4, 3), torch.randn(4)
+    x = torch.randn(5, 3)
+    assert torch.allclose(fusion.fuse_matmul_bias_relu(w, b)(x), torch.relu(x @ w.t() + b), atol=1e-5)
+    assert torch.allclose(fusion.fuse_matmul_bias(w, b)(x), x @ w.t() + b, atol=1e-5)
+    assert torch.allclose(fusion.fuse_matmul_bias_gelu(w, b)(x), torch.nn.functional.gelu(x @ w.t() + b, approximate="tanh"), atol=1e-5)
+    with pytest.raises(fusion.FusionError, match=r"expected \[4\], got \[3\]"):
+        fusion.fuse_matmul_bias_relu(w, torch.randn(3))
+    with pytest.raises(fusion.FusionError, match=r"expected \[3\], got \[7\]"):
+        fusion.fuse_matmul_bias(w, b)(torch.randn(2, 7))
+    with pytest.raises(fusion.FusionError, match="Invalid fusion configuration"):
+        fusion.FusedLinear(torch.randn(4), None)
+    with pytest.raises(fusion.FusionError, match="unknown activation"):
+        fusion.FusedLinear(w, b, "softsign")
+    E = fusion.ElementwiseOp
+    chain = fusion.fuse_elementwise([(E.Mul, 2.0), (E.Add, -1.0), E.Relu, (E.Clamp, 0.0, 3.0)])
+    v = torch.linspace(-2, 4, 13)
+    assert chain.num_ops() == 4 and torch.allclose(chain(v), torch.clamp(torch.relu(v * 2 - 1), 0, 3), atol=1e-6)
+    assert torch.allclose(fusion.fused_add_relu(0.5)(v), torch.relu(v + 0.5)) and torch.allclose(fusion.fused_mul_add(3.0, 1.0)(v), v * 3 + 1)
+    assert torch.allclose(fusion.fused_scale_bias_relu(-1.0, 1.0)(v), torch.relu(1 - v))
+    with pytest.raises(fusion.FusionError):
+        fusion.fuse_elementwise(["relu"])
