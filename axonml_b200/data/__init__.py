@@ -1,6 +1,6 @@
 """Data loading (crates/axonml-data)."""
 from .collate import Collate, DefaultCollate, StackCollate, concat_tensors, stack_tensors
-from .dataloader import Batch, DataLoader, GenericDataLoader
+from .dataloader import Batch, DataLoader, DataLoaderIter, GenericDataLoader
 from .dataset import (ConcatDataset, Dataset, InMemoryDataset, MapDataset, SubsetDataset, TensorDataset,
                       random_split)
 from .sampler import (BatchSampler, DistributedSampler, RandomSampler, Sampler, SequentialSampler,

@@ -60,7 +60,7 @@ class DataLoader:
             data, targets = data.pin_memory(), targets.pin_memory()
         return Batch(data, targets, len(indices))
 
-    def iter(self): return iter(self)
+    def iter(self): return DataLoaderIter(self)
 
     def __iter__(self):
         pool = cf.ThreadPoolExecutor(self._num_workers) if self._num_workers > 0 else None
@@ -88,6 +88,35 @@ class DataLoader:
         finally:
             if pool:
                 pool.shutdown(wait=False)
+
+
+class DataLoaderIter:
+    """One pass over a loader (dataloader.rs:160-225): an iterator that also knows how many batches
+    are left.  The index order is drawn when the iterator is created, so two iterators of a
+    shuffling loader see different orders."""
+
+    def __init__(self, loader: DataLoader):
+        self.loader = loader
+        self.position = 0                   # batches handed out so far
+        self._total = len(loader)
+        self._it = loader.__iter__()
+
+    def __iter__(self): return self
+
+    def __next__(self):
+        b = next(self._it)
+        self.position += 1
+        return b
+
+    def next(self):
+        """The next batch, or ``None`` after the last one."""
+        try:
+            return self.__next__()
+        except StopIteration:
+            return None
+
+    def remaining(self) -> int: return max(self._total - self.position, 0)
+    def __len__(self) -> int: return self.remaining()
 
 
 class GenericDataLoader(DataLoader):

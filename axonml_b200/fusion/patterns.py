@@ -113,10 +113,31 @@ class FusionStats:
     def fusion_ratio(self) -> float: return self.fused_ops / self.total_ops if self.total_ops else 0.0
 
 
+@dataclasses.dataclass
+class OptimizationStats:
+    """Running totals of an optimizer (crates/axonml-fusion/src/optimizer.rs:81-105): each fusion
+    removes ``pattern.num_ops() - 1`` operations and multiplies the estimated speedup."""
+    fusions_applied: int = 0
+    ops_eliminated: int = 0
+    estimated_speedup: float = 1.0
+    patterns: list = dataclasses.field(default_factory=list)          # [pattern, count] pairs, first seen first
+
+    def add_fusion(self, pattern: FusionPattern, length: int | None = None) -> None:
+        self.fusions_applied += 1
+        self.ops_eliminated += (length if length is not None else pattern.num_ops()) - 1
+        self.estimated_speedup *= pattern.estimated_speedup()
+        for entry in self.patterns:
+            if entry[0] is pattern:
+                entry[1] += 1
+                return
+        self.patterns.append([pattern, 1])
+
+
 class FusionOptimizer:
     def __init__(self, config: FusionConfig | None = None):
         self.config = config or FusionConfig()
         self._stats = FusionStats()
+        self.optimization_stats = OptimizationStats()
 
     @classmethod
     def new(cls): return cls()
@@ -132,6 +153,7 @@ class FusionOptimizer:
             if p.name.startswith("MatMul") and not self.config.fuse_linear: continue
             if p.name.startswith("Conv") and not self.config.fuse_conv: continue
             pats.append((p, s, n))
+            self.optimization_stats.add_fusion(p, n)
         fused = sum(n for _, _, n in pats)
         self._stats = FusionStats(len(ops), fused, len(pats), estimate_speedup(ops, pats))
         return pats

@@ -16,6 +16,31 @@ class ReportFormat(enum.Enum):
 
 
 @dataclasses.dataclass
+class MemorySummary:
+    current_usage: int = 0
+    peak_usage: int = 0
+    total_allocated: int = 0
+    total_freed: int = 0
+    allocation_count: int = 0
+
+
+@dataclasses.dataclass
+class OperationSummary:
+    name: str
+    total_time_ns: int
+    call_count: int
+    avg_time_ns: int
+    time_percentage: float
+
+
+@dataclasses.dataclass
+class ComputeSummary:
+    operation_count: int = 0
+    total_time_ns: int = 0
+    top_operations: list = dataclasses.field(default_factory=list)
+
+
+@dataclasses.dataclass
 class ProfileReport:
     operations: list
     total_time_ms: float
@@ -23,14 +48,22 @@ class ProfileReport:
     current_memory: int
     bottlenecks: list
     device_memory: dict
+    memory: MemorySummary = dataclasses.field(default_factory=MemorySummary)
+    compute: ComputeSummary = dataclasses.field(default_factory=ComputeSummary)
 
     @classmethod
     def generate(cls, profiler) -> "ProfileReport":
         ops = profiler.compute.top(1000)
+        total_ns = profiler.compute.total_time_ns()
+        m = profiler.memory.stats()
+        top = [OperationSummary(s.name, int(s.total_ns), s.count, int(s.avg_ns()), 100.0 * s.total_ns / total_ns if total_ns else 0.0)
+               for s in ops[:10]]
         return cls([dataclasses.asdict(s) | {"avg_ns": s.avg_ns(), "gflops": s.gflops(), "gbps": s.gbps()} for s in ops],
-                   profiler.compute.total_time_ns() / 1e6, profiler.memory.peak, profiler.memory.current,
-                   [dataclasses.asdict(b) | {"kind": b.kind.value} for b in BottleneckAnalyzer().analyze(profiler)],
-                   profiler.memory.device_stats())
+                   total_ns / 1e6, profiler.memory.peak, profiler.memory.current,
+                   [dataclasses.asdict(b) | {"kind": b.kind.value, "severity": b.severity.name} for b in BottleneckAnalyzer().analyze(profiler)],
+                   profiler.memory.device_stats(),
+                   MemorySummary(m.current_usage, m.peak_usage, m.total_allocated, m.total_freed, m.allocation_count),
+                   ComputeSummary(len(ops), int(total_ns), top))
 
     def format(self, fmt: ReportFormat) -> str:
         return {ReportFormat.Text: self.to_text, ReportFormat.Json: self.to_json,
@@ -46,7 +79,7 @@ class ProfileReport:
         for n, c, t, a, g, b in self._rows():
             lines.append(f"{n[:32]:32s} {c:8d} {t:10.3f} {a:10.2f} {g:9.2f} {b:8.2f}")
         for b in self.bottlenecks:
-            lines.append(f"[{b['kind']}] {b['description']} -> {b['suggestion']}")
+            lines.append(f"[{b['severity']}] [{b['kind']}] {b['description']} -> {b['suggestion']}")
         return "\n".join(lines)
 
     def to_json(self) -> str: return json.dumps(dataclasses.asdict(self), indent=2, default=str)

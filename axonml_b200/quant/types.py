@@ -144,3 +144,119 @@ class QuantizedBlock:
         q = QuantizedTensor([self.quant_type.block_size()], self.quant_type, torch.frombuffer(bytearray(self.data), dtype=torch.uint8),
                             self.layout)
         return dequantize_tensor(q).tolist()
+
+
+DEFAULT_BLOCK_SIZE = 32        # values per block of the Q8_0 / Q4_x / Q5_x types
+MAX_BLOCK_SIZE = 256           # values per Q4_K super-block
+
+
+def _f16_bytes(x: float) -> bytes:
+    import struct
+    return struct.pack("<e", float(x))
+
+
+def _f16_round(x: float) -> float:
+    import struct
+    return struct.unpack("<e", struct.pack("<e", float(x)))[0]
+
+
+@dataclasses.dataclass
+class Q8Block:
+    """fp16 scale + 32 signed bytes (types.rs:125-160); value i = scale * data[i]."""
+    scale: float
+    data: list
+
+    def __post_init__(self):
+        self.scale, self.data = _f16_round(self.scale), [int(v) for v in self.data]
+        if len(self.data) != 32 or any(not -128 <= v <= 127 for v in self.data):
+            raise QuantError("a Q8 block holds 32 values in -128..127")
+
+    @classmethod
+    def new(cls, scale, data): return cls(scale, data)
+    def to_bytes(self) -> bytes: return _f16_bytes(self.scale) + bytes(v & 0xFF for v in self.data)
+
+    @classmethod
+    def from_bytes(cls, b: bytes):
+        if len(b) < 34:
+            return None
+        import struct
+        return cls(struct.unpack_from("<e", b, 0)[0], list(struct.unpack_from("<32b", b, 2)))
+
+    def dequantize(self) -> list: return [self.scale * v for v in self.data]
+    def as_block(self) -> QuantizedBlock: return QuantizedBlock(QuantType.Q8_0, self.to_bytes())
+
+
+@dataclasses.dataclass
+class Q4Block:
+    """fp16 scale + 16 bytes of nibbles in the reference's adjacent-pair order (types.rs:162-215):
+    byte i carries value 2i in its low and 2i+1 in its high nibble, each stored as value + 8."""
+    scale: float
+    data: bytes
+
+    def __post_init__(self):
+        self.scale, self.data = _f16_round(self.scale), bytes(self.data)
+        if len(self.data) != 16:
+            raise QuantError("a Q4 block holds 16 packed bytes")
+
+    @classmethod
+    def new(cls, scale, data): return cls(scale, data)
+
+    def unpack(self) -> list:
+        out = []
+        for byte in self.data:
+            out += [(byte & 0x0F) - 8, (byte >> 4) - 8]
+        return out
+
+    @staticmethod
+    def pack(values) -> bytes:
+        values = [int(v) for v in values]
+        if len(values) != 32 or any(not -8 <= v <= 7 for v in values):
+            raise QuantError("Q4 packs 32 values in -8..7")
+        return bytes(((values[2 * i] + 8) & 0x0F) | (((values[2 * i + 1] + 8) & 0x0F) << 4) for i in range(16))
+
+    def to_bytes(self) -> bytes: return _f16_bytes(self.scale) + self.data
+
+    @classmethod
+    def from_bytes(cls, b: bytes):
+        if len(b) < 18:
+            return None
+        import struct
+        return cls(struct.unpack_from("<e", b, 0)[0], bytes(b[2:18]))
+
+    def dequantize(self) -> list: return [self.scale * v for v in self.unpack()]
+    def as_block(self) -> QuantizedBlock: return QuantizedBlock(QuantType.Q4_0, self.to_bytes(), "adjacent")
+
+
+@dataclasses.dataclass
+class Q4_1Block:
+    """fp16 scale, fp16 minimum and 16 bytes of unsigned nibbles in adjacent-pair order
+    (types.rs:217-250); value i = min + scale * nibble i."""
+    scale: float
+    min: float
+    data: bytes
+
+    def __post_init__(self):
+        self.scale, self.min, self.data = _f16_round(self.scale), _f16_round(self.min), bytes(self.data)
+        if len(self.data) != 16:
+            raise QuantError("a Q4_1 block holds 16 packed bytes")
+
+    @classmethod
+    def new(cls, scale, min, data): return cls(scale, min, data)
+
+    def unpack(self) -> list:
+        out = []
+        for byte in self.data:
+            out += [byte & 0x0F, byte >> 4]
+        return out
+
+    def to_bytes(self) -> bytes: return _f16_bytes(self.scale) + _f16_bytes(self.min) + self.data
+
+    @classmethod
+    def from_bytes(cls, b: bytes):
+        if len(b) < 20:
+            return None
+        import struct
+        return cls(struct.unpack_from("<e", b, 0)[0], struct.unpack_from("<e", b, 2)[0], bytes(b[4:20]))
+
+    def dequantize(self) -> list: return [self.min + self.scale * v for v in self.unpack()]
+    def as_block(self) -> QuantizedBlock: return QuantizedBlock(QuantType.Q4_1, self.to_bytes(), "adjacent")

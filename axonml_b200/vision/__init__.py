@@ -11,3 +11,4 @@ from .transforms import (CenterCrop, ColorJitter, Grayscale, ImageNormalize, Pad
 from . import hub
 from .hub import (HubError, PretrainedModel, cache_dir, download_weights, is_cached, list_models, load_state_dict, model_info,
                   model_registry)
+from ..serialize.state_dict import StateDict

@@ -310,3 +310,151 @@ def test_fusion_errors_and_convenience_constructors():
     assert torch.allclose(fusion.fused_scale_bias_relu(-1.0, 1.0)(v), torch.relu(1 - v))
     with pytest.raises(fusion.FusionError):
         fusion.fuse_elementwise(["relu"])
+
+
+def test_profiler_records_stats_and_events():
+    m = profile.MemoryProfiler()
+    m.record_alloc("weights", 4096)
+    m.record_alloc("acts", 1024)
+    m.record_alloc("acts", 1024)
+    m.record_free("acts", 1024)
+    st = m.stats()
+    assert isinstance(st, profile.MemoryStats) and (st.current_usage, st.peak_usage, st.total_allocated, st.total_freed) == (5120, 6144, 6144, 1024)
+    assert (st.allocation_count, st.deallocation_count) == (3, 1) and st.per_name_usage == {"weights": 4096, "acts": 1024}
+    leaks = m.leaks()
+    assert [(r.name, r.size, r.freed) for r in leaks] == [("weights", 4096, False), ("acts", 1024, False)]
+    assert all(isinstance(r, profile.AllocationRecord) for r in leaks) and leaks[0].timestamp <= leaks[1].timestamp
+    assert sum(r.freed for r in m.records) == 1 and m.current_usage() == 5120 and m.peak_usage() == 6144
+    assert profile.format_bytes(1536) == "1.50 KB" and profile.MemoryProfiler.format_bytes(3 << 30) == "3.00 GB" and profile.format_bytes(12) == "12 B"
+    m.reset()
+    assert m.stats() == profile.MemoryStats()
+
+    c = profile.ComputeProfiler()
+    c.start_with_flops("gemm", 2e9)
+    assert [(op.name, op.flops) for op in c.active()] == [("gemm", 2e9)] and isinstance(c.active()[0], profile.ProfiledOp)
+    c.stop("gemm")
+    c.start_with_bytes("copy", 1 << 20); c.stop("copy")
+    c.record("gemm", 1e6, flops=2e9)
+    g = c.get_stats("gemm")
+    assert g.count == 2 and g.flops == 4e9 and g.gflops() > 0 and c.get_stats("copy").bytes == 1 << 20 and c.get_stats("nope") is None
+    assert c.total_time("gemm") == g.total_time() > 0 and c.avg_time("gemm") == pytest.approx(g.total_time() / 2) and c.total_time("nope") == 0.0
+    assert g.min_time() <= g.avg_time() <= g.max_time() and not c.active()
+    assert [s.name for s in c.top_by_calls(1)] == ["gemm"] and set(c.all_stats()) == {"gemm", "copy"}
+    with pytest.raises(profile.ProfileError, match="Operation not found: nope"):
+        c.require_stats("nope")
+    assert profile.format_duration(1.5e6) == "1.500 ms" and profile.format_duration(2.5e9) == "2.500 s" and profile.format_duration(750) == "750 ns"
+
+    t = profile.TimelineProfiler.with_capacity(6)
+    t.start("step"); t.instant("mark"); t.record_with_metadata("buf", profile.EventType.Alloc, "4096"); t.end("step")
+    t.record("note", profile.EventType.Custom)
+    assert t.event_count() == 5 and [e.event_type for e in t.events] == [profile.EventType.Start, profile.EventType.Instant,
+                                                                         profile.EventType.Alloc, profile.EventType.End, profile.EventType.Custom]
+    assert len(t.events_by_name("step")) == 2 and t.events_by_type(profile.EventType.Alloc)[0].metadata == "4096"
+    assert 0 <= t.duration("step") <= t.total_duration() and t.duration("mark") is None and t.duration("absent") is None
+    assert all(isinstance(e, profile.Event) and e.thread_id is not None for e in t.events)
+    t.instant("six"); t.instant("seven")
+    assert t.event_count() == 6 and t.dropped == 1                              # capacity reached
+    trace = json.loads(t.to_chrome_trace())["traceEvents"]
+    assert [e["ph"] for e in trace[:4]] == ["B", "i", "i", "E"] and trace[2]["args"] == {"type": "Alloc", "metadata": "4096"}
+    rows = json.loads(t.to_json())
+    assert rows[0]["event_type"] == "Start" and rows[2]["metadata"] == "4096"
+    with pytest.raises(profile.ProfileError):
+        t.export_chrome_trace("/nonexistent-dir/trace.json")
+
+    p = profile.Profiler()
+    p.record_alloc("kv", 100); p.record_free("kv", 100)
+    assert [e.event_type for e in p.timeline.events] == [profile.EventType.Alloc, profile.EventType.Free] and not p.memory.leaks()
+    p.disable()
+    p.record_alloc("kv", 100)
+    assert p.memory.stats().allocation_count == 1
+
+
+def test_quant_block_types_agree_with_the_codec():
+    from axonml_b200 import quant as Q
+    torch.manual_seed(0)
+    w = torch.randn(2, 64)
+    assert Q.DEFAULT_BLOCK_SIZE == 32 and Q.MAX_BLOCK_SIZE == 256 == Q.QuantType.Q4_K.block_size()
+    q8 = Q.quantize_tensor(w, Q.QuantType.Q8_0)
+    raw = q8.block(1).to_bytes()
+    b8 = Q.Q8Block.from_bytes(raw)
+    assert b8.to_bytes() == raw and b8.scale == q8.block(1).scale and len(b8.data) == 32
+    assert torch.allclose(torch.tensor(b8.dequantize()), Q.dequantize_tensor(q8).flatten()[32:64])
+    assert b8.as_block().quant_type is Q.QuantType.Q8_0 and Q.Q8Block.from_bytes(raw[:10]) is None
+    # the reference's nibble order: value 2i in the low and 2i+1 in the high half of byte i
+    vals = [(i % 16) - 8 for i in range(32)]
+    packed = Q.Q4Block.pack(vals)
+    assert packed[0] == (0 | (1 << 4)) and packed[1] == (2 | (3 << 4))
+    b4 = Q.Q4Block.new(0.25, packed)
+    assert b4.unpack() == vals and Q.Q4Block.from_bytes(b4.to_bytes()) == b4 and len(b4.to_bytes()) == 18
+    q4 = Q.quantize_tensor(w, Q.QuantType.Q4_0, layout="adjacent")
+    blk = Q.Q4Block.from_bytes(q4.block(3).to_bytes())
+    assert torch.allclose(torch.tensor(blk.dequantize()), Q.dequantize_tensor(q4).flatten()[96:128])
+    assert blk.as_block().dequantize() == pytest.approx(blk.dequantize())
+    q41 = Q.quantize_tensor(w, Q.QuantType.Q4_1, layout="adjacent")
+    b41 = Q.Q4_1Block.from_bytes(q41.block(0).to_bytes())
+    assert len(b41.to_bytes()) == 20 and all(0 <= v <= 15 for v in b41.unpack())
+    assert torch.allclose(torch.tensor(b41.dequantize()), Q.dequantize_tensor(q41).flatten()[:32], atol=1e-6)
+    assert b41.min == q41.block(0).min and [b.quant_type for b in q41.blocks()] == [Q.QuantType.Q4_1] * 4
+    with pytest.raises(Q.QuantError):
+        Q.Q4Block.pack([9] * 32)
+    with pytest.raises(Q.QuantError):
+        Q.Q8Block(1.0, [0] * 31)
+    with pytest.raises(Q.QuantError):
+        Q.QuantizedBlock(Q.QuantType.Q8_0, b"\x00" * 5)
+    with pytest.raises(IndexError):
+        q8.block(99)
+
+
+def test_bottleneck_severities_summaries_and_guards():
+    S, T = profile.Severity, profile.BottleneckType
+    p = profile.Profiler()
+    p.compute.record("attention", 55e6)
+    p.compute.record("mlp", 30e6)
+    p.compute.record("norm", 15e6, flops=1e3)                # 6.7e-5 GFLOPS: a throughput finding
+    for _ in range(3):
+        p.compute.record("tiny", 1.0)
+    p.compute.stats["tiny"].count = 60_000
+    p.memory.record_alloc("kv_cache", 700)
+    p.memory.record_alloc("acts", 300)
+    p.memory.record_free("acts", 300)
+    found = profile.BottleneckAnalyzer().analyze(p)
+    by = {(b.kind, b.name.split(",")[0]): b for b in found}
+    assert by[(T.SlowOperation, "attention")].severity is S.Critical and by[(T.SlowOperation, "mlp")].severity is S.Medium
+    assert (T.SlowOperation, "norm") not in by and by[(T.LowThroughput, "norm")].severity is S.Medium
+    assert by[(T.HighCallCount, "tiny")].severity is S.Medium and by[(T.HighCallCount, "tiny")].metrics["calls"] == 60_000
+    assert by[(T.MemoryHotspot, "kv_cache")].severity is S.High and by[(T.MemoryHotspot, "acts")].severity is S.Low
+    leak = by[(T.MemoryLeak, "kv_cache")]
+    assert leak.severity is S.Critical and leak.metrics["leaked_bytes"] == 700 and leak.bottleneck_type is T.MemoryLeak
+    sev = [b.severity for b in found]
+    assert sev == sorted(sev, reverse=True) and S.Low < S.Medium < S.High < S.Critical and float(S.High) == 0.75
+    cfg = profile.AnalyzerConfig(slow_op_threshold_pct=60.0, high_call_threshold=100_000, memory_hotspot_threshold_pct=90.0, check_memory_leaks=False)
+    assert {b.kind for b in profile.BottleneckAnalyzer.with_config(cfg).analyze(p)} == {T.LowThroughput}
+    d = profile.AnalyzerConfig()
+    assert (d.slow_op_threshold_pct, d.high_call_threshold, d.memory_hotspot_threshold_pct, d.min_gflops_threshold, d.check_memory_leaks) == (20.0, 10_000, 30.0, 1.0, True)
+    assert "[CRITICAL] SlowOperation" in profile.BottleneckAnalyzer().summary(p) and profile.BottleneckAnalyzer().summary(profile.Profiler()) == "No bottlenecks detected."
+    rep = p.report()
+    assert isinstance(rep.memory, profile.MemorySummary) and (rep.memory.peak_usage, rep.memory.current_usage, rep.memory.allocation_count) == (1000, 700, 2)
+    assert isinstance(rep.compute, profile.ComputeSummary) and rep.compute.operation_count == 4 and rep.compute.total_time_ns == 100_000_003
+    top = rep.compute.top_operations[0]
+    assert isinstance(top, profile.OperationSummary) and top.name == "attention" and top.time_percentage == pytest.approx(55.0, abs=1e-3)
+    assert "[Critical] [slow_operation]" in rep.to_text() and '"severity": "Critical"' in rep.to_json()
+
+    c = profile.ComputeProfiler()
+    with profile.TimingGuard(c, "step"):
+        assert [op.name for op in c.active()] == ["step"]
+    g = profile.TimingGuard.new(c, "step")
+    g.drop(); g.drop()
+    assert c.get_stats("step").count == 2 and not c.active()
+    gp = profile.global_profiler()
+    before = gp.memory.stats().allocation_count
+    profile.start("global-op"); profile.stop("global-op"); profile.record_alloc("g", 8); profile.record_free("g", 8)
+    assert gp.compute.get_stats("global-op").count >= 1 and gp.memory.stats().allocation_count == before + 1
+
+    opt = fusion.FusionOptimizer()
+    O = fusion.OpType
+    opt.analyze([O.MatMul, O.Add, O.Relu, O.Conv, O.BatchNorm, O.MatMul, O.Add, O.Relu])
+    st = opt.optimization_stats
+    P = fusion.FusionPattern
+    assert isinstance(st, fusion.OptimizationStats) and st.fusions_applied == 3 and st.ops_eliminated == 5
+    assert st.patterns == [[P.MatMulBiasRelu, 2], [P.ConvBatchNorm, 1]]
+    assert st.estimated_speedup == pytest.approx(P.MatMulBiasRelu.estimated_speedup() ** 2 * P.ConvBatchNorm.estimated_speedup())
