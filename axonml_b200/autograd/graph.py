@@ -198,3 +198,15 @@ class _Bridge(torch.autograd.Function):
         if len(grads) != ctx.n:
             raise RuntimeError(f"{ctx.inst.name()}.apply returned {len(grads)} gradients for {ctx.n} inputs")
         return (None, *grads)
+
+
+_THREAD_GRAPHS = __import__("threading").local()
+
+
+def with_graph(f):
+    """Calls ``f`` with this thread's ``ComputationGraph`` registry (graph.rs:158-163): a graph
+    that lives as long as the thread, for code that registers its own leaves and operations."""
+    g = getattr(_THREAD_GRAPHS, "graph", None)
+    if g is None:
+        g = _THREAD_GRAPHS.graph = ComputationGraph()
+    return f(g)

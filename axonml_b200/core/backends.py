@@ -6,11 +6,14 @@ cuda.rs:413-629); the graphics-API backends exist as names whose ``is_available(
 from __future__ import annotations
 
 import ctypes
+import dataclasses
+import enum
 
 import torch
 
 from .. import _native as N
 from .device import Device
+from .error import DeviceNotAvailable as DeviceNotAvailableError
 
 _BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3}
 _UN = {"neg": 0, "abs": 1, "relu": 2, "sigmoid": 3, "tanh": 4, "exp": 5, "ln": 6, "sqrt": 7, "square": 8,
@@ -20,6 +23,135 @@ _RED = {"sum": 0, "prod": 1, "max": 2, "min": 3, "mean": 4, "argmax": 5, "argmin
 
 def _p(t): return ctypes.c_void_p(t.data_ptr())
 def _f(t): return t.detach().to("cpu", torch.float32).contiguous()
+
+
+class BackendType(enum.Enum):
+    """Which kind of device a buffer or stream belongs to (backends/mod.rs:116-132)."""
+    Cpu = "cpu"
+    Cuda = "cuda"
+    Vulkan = "vulkan"
+    Metal = "metal"
+    Wgpu = "wgpu"
+
+
+BLOCK_SIZE = 256        # threads per block of the one-dimensional launches (cuda_kernels/mod.rs)
+
+
+@dataclasses.dataclass(frozen=True)
+class LaunchConfig:
+    grid_dim: tuple
+    block_dim: tuple
+    shared_mem_bytes: int = 0
+
+
+def launch_config(n: int) -> LaunchConfig:
+    """One-dimensional launch covering ``n`` elements with 256-thread blocks (cuda_kernels/mod.rs:339-346)."""
+    return LaunchConfig(((int(n) + BLOCK_SIZE - 1) // BLOCK_SIZE, 1, 1), (BLOCK_SIZE, 1, 1), 0)
+
+
+class CudaError(RuntimeError):
+    """Failures of the CUDA backend (cuda.rs:272-320), one subclass per variant."""
+
+
+class DeviceNotFound(CudaError):
+    def __init__(self, index=None): super().__init__("CUDA device not found" + (f": {index}" if index is not None else ""))
+
+
+class CudaAllocationFailed(CudaError):
+    def __init__(self, size=None): super().__init__("CUDA memory allocation failed" + (f" ({size} bytes)" if size is not None else ""))
+
+
+class CopyFailed(CudaError):
+    def __init__(self, what=""): super().__init__("CUDA memory copy failed" + (f": {what}" if what else ""))
+
+
+class KernelLaunchFailed(CudaError):
+    def __init__(self, what=""): super().__init__("CUDA kernel launch failed" + (f": {what}" if what else ""))
+
+
+class BlasError(CudaError):
+    def __init__(self, what): super().__init__(f"cuBLAS error: {what}")
+
+
+class DriverError(CudaError):
+    def __init__(self, what): super().__init__(f"CUDA driver error: {what}")
+
+
+class ModuleLoadFailed(CudaError):
+    def __init__(self, what): super().__init__(f"Failed to load CUDA module: {what}")
+
+
+class KernelNotFound(CudaError):
+    def __init__(self, what): super().__init__(f"CUDA kernel not found: {what}")
+
+
+class GpuMemory:
+    """A device allocation by address (backends/mod.rs:108-172).  ``GpuMemory.of(tensor)`` describes
+    a tensor's memory and keeps the tensor alive for as long as the handle exists."""
+
+    def __init__(self, ptr: int, size: int, device_index: int, backend_type: BackendType, owner=None):
+        self._ptr, self._size, self._device_index, self._backend_type, self._owner = int(ptr), int(size), device_index, backend_type, owner
+
+    @classmethod
+    def new(cls, ptr, size, device_index, backend_type): return cls(ptr, size, device_index, backend_type)
+
+    @classmethod
+    def of(cls, t: torch.Tensor):
+        kind = BackendType.Cuda if t.is_cuda else BackendType.Cpu
+        return cls(t.data_ptr(), t.numel() * t.element_size(), t.device.index or 0, kind, t)
+
+    def ptr(self) -> int: return self._ptr
+    def size(self) -> int: return self._size
+    def device_index(self) -> int: return self._device_index
+    def backend_type(self) -> BackendType: return self._backend_type
+    def is_null(self) -> bool: return self._ptr == 0
+    def __repr__(self) -> str: return f"GpuMemory(0x{self._ptr:x}, {self._size} B, {self._backend_type.value}:{self._device_index})"
+
+
+def stream_synchronize(handle: int = 0, device_index: int = 0) -> None:
+    """Waits for the CUDA stream with this raw handle (0 = the default stream) to drain."""
+    if not torch.cuda.is_available():
+        return
+    if handle == 0:
+        torch.cuda.default_stream(device_index).synchronize()
+    else:
+        torch.cuda.ExternalStream(handle, device=device_index).synchronize()
+
+
+class GpuStream:
+    """A queue of device work by raw handle (backends/mod.rs:176-220)."""
+
+    def __init__(self, handle: int, device_index: int, backend_type: BackendType):
+        self._handle, self._device_index, self._backend_type = int(handle), device_index, backend_type
+
+    @classmethod
+    def new(cls, handle, device_index, backend_type): return cls(handle, device_index, backend_type)
+
+    @classmethod
+    def current(cls, device_index: int = 0):
+        """The stream kernels are being launched on right now (a CPU stream when there is no GPU)."""
+        if torch.cuda.is_available():
+            return cls(torch.cuda.current_stream(device_index).cuda_stream, device_index, BackendType.Cuda)
+        return cls(0, 0, BackendType.Cpu)
+
+    def handle(self) -> int: return self._handle
+    def device_index(self) -> int: return self._device_index
+    def backend_type(self) -> BackendType: return self._backend_type
+
+    def synchronize(self) -> None:
+        if self._backend_type is BackendType.Cuda:
+            stream_synchronize(self._handle, self._device_index)
+        elif self._backend_type is not BackendType.Cpu:
+            raise DeviceNotAvailableError(self._backend_type.value)
+
+
+def gpu_count() -> int:
+    """Devices over all GPU backends (backends/mod.rs:266-291): the CUDA devices here."""
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def best_available_backend_type() -> BackendType:
+    return BackendType.Cuda if torch.cuda.is_available() else BackendType.Cpu
 
 
 class Backend:
@@ -35,6 +167,7 @@ class Backend:
 
 class CpuBackend(Backend):
     def name(self) -> str: return "cpu"
+    def backend_type(self) -> BackendType: return BackendType.Cpu
     def is_available(self) -> bool: return True
     def device(self) -> Device: return Device.Cpu()
 
@@ -160,6 +293,7 @@ class CpuBackend(Backend):
 class CudaBackend(Backend):
     def __init__(self, index: int = 0): self.index = index
     def name(self) -> str: return "cuda"
+    def backend_type(self) -> BackendType: return BackendType.Cuda
     def is_available(self) -> bool: return torch.cuda.is_available() and self.index < torch.cuda.device_count()
     def device(self) -> Device: return Device.Cuda(self.index)
     def synchronize(self) -> None: torch.cuda.synchronize(self.index)
@@ -198,6 +332,7 @@ class CudaBackend(Backend):
 class _Unavailable(Backend):
     NAME = "none"
     def name(self) -> str: return self.NAME
+    def backend_type(self) -> BackendType: return BackendType(self.NAME)
     def is_available(self) -> bool: return False
     def device(self) -> Device: return Device(self.NAME, 0)
 

@@ -15,11 +15,98 @@ from .dtype import as_torch_dtype
 from .error import AllocationFailed, DeviceNotAvailable, IndexOutOfBounds
 
 
+class _RwLock:
+    """Many readers or one writer; shared by every view of one buffer."""
+
+    def __init__(self):
+        self._cond = threading.Condition()
+        self._readers = 0
+        self._writer = False
+
+    def acquire_read(self, timeout=None) -> bool:
+        with self._cond:
+            if not self._cond.wait_for(lambda: not self._writer, timeout):
+                return False
+            self._readers += 1
+            return True
+
+    def release_read(self) -> None:
+        with self._cond:
+            self._readers -= 1
+            if self._readers == 0:
+                self._cond.notify_all()
+
+    def acquire_write(self, timeout=None) -> bool:
+        with self._cond:
+            if not self._cond.wait_for(lambda: not self._writer and self._readers == 0, timeout):
+                return False
+            self._writer = True
+            return True
+
+    def release_write(self) -> None:
+        with self._cond:
+            self._writer = False
+            self._cond.notify_all()
+
+
+class _Guard:
+    def __init__(self, storage, timeout):
+        self._storage, self._live = storage, True
+        if not self._acquire(storage._lock, timeout):
+            self._live = False
+            raise TimeoutError("storage is locked")
+
+    def tensor(self) -> torch.Tensor:
+        """The guarded elements (a view; valid until the guard is dropped)."""
+        if not self._live:
+            raise RuntimeError("the guard has been dropped")
+        return self._storage.as_tensor()
+
+    def __len__(self) -> int: return self._storage.len()
+    def __getitem__(self, i): return self.tensor()[i]
+    def to_vec(self) -> list: return self.tensor().tolist()
+
+    def drop(self) -> None:
+        if self._live:
+            self._live = False
+            self._release(self._storage._lock)
+
+    def __enter__(self): return self
+    def __exit__(self, *exc): self.drop()
+    def __del__(self): self.drop()
+
+
+class StorageReadGuard(_Guard):
+    """Shared access to a storage's elements (storage.rs:253-266): any number at a time, none while
+    a write guard is held."""
+    _acquire = staticmethod(_RwLock.acquire_read)
+    _release = staticmethod(_RwLock.release_read)
+
+
+class StorageWriteGuard(_Guard):
+    """Exclusive access (storage.rs:268-290): waits for every other guard of the buffer to be dropped."""
+    _acquire = staticmethod(_RwLock.acquire_write)
+    _release = staticmethod(_RwLock.release_write)
+
+    def __setitem__(self, i, value): self.tensor()[i] = value
+    def fill(self, value) -> None: self.tensor().fill_(value)
+    def copy_from(self, values) -> None: self.tensor().copy_(torch.as_tensor(values, dtype=self.tensor().dtype))
+
+
 class Storage:
-    def __init__(self, data: torch.Tensor, offset: int = 0, length: int | None = None):
+    def __init__(self, data: torch.Tensor, offset: int = 0, length: int | None = None, _lock: _RwLock | None = None):
         self._base = data.reshape(-1)
         self._offset = offset
         self._len = self._base.numel() - offset if length is None else length
+        self._lock = _lock or _RwLock()               # views made with slice() share it
+
+    def read(self, timeout: float | None = None) -> StorageReadGuard:
+        """Read guard (``as_slice`` of the reference): ``with st.read() as r: r.tensor()``."""
+        return StorageReadGuard(self, timeout)
+
+    def write(self, timeout: float | None = None) -> StorageWriteGuard:
+        """Write guard (``as_slice_mut`` of the reference)."""
+        return StorageWriteGuard(self, timeout)
 
     @classmethod
     def zeros(cls, length: int, device=Device.Cpu(), dtype=torch.float32):
@@ -44,7 +131,7 @@ class Storage:
     def slice(self, offset: int, length: int) -> "Storage":
         if offset + length > self._len:
             raise IndexOutOfBounds(offset + length, self._len)
-        return Storage(self._base, self._offset + offset, length)
+        return Storage(self._base, self._offset + offset, length, self._lock)
 
     def is_unique(self) -> bool:
         import sys

@@ -126,3 +126,10 @@ class GenericDataLoader(DataLoader):
     def _make(self, indices, pool):
         samples = list(pool.map(self.dataset.get, indices)) if pool else [self.dataset.get(i) for i in indices]
         return self._collate(samples)
+
+    def iter(self): return GenericDataLoaderIter(self)
+
+
+class GenericDataLoaderIter(DataLoaderIter):
+    """One pass over a ``GenericDataLoader`` (dataloader.rs ``GenericDataLoaderIter``): yields what
+    the loader's collate function returns."""

@@ -52,19 +52,40 @@ class WeightedRandomSampler(Sampler):
     def __len__(self): return self.num_samples
 
 
+class BatchIter:
+    """Iterator over lists of indices, ``batch_size`` at a time (sampler.rs:323-348); a short last
+    batch is dropped when ``drop_last``."""
+
+    def __init__(self, indices, batch_size: int, drop_last: bool = False):
+        if batch_size <= 0:
+            raise ValueError("batch_size must be positive")
+        self.indices, self.batch_size, self.drop_last, self.position = list(indices), batch_size, drop_last, 0
+
+    def __iter__(self): return self
+
+    def __next__(self) -> list:
+        if self.position >= len(self.indices):
+            raise StopIteration
+        batch = self.indices[self.position:self.position + self.batch_size]
+        if len(batch) < self.batch_size and self.drop_last:
+            self.position = len(self.indices)
+            raise StopIteration
+        self.position += len(batch)
+        return batch
+
+    def remaining(self) -> int:
+        left = len(self.indices) - self.position
+        return left // self.batch_size if self.drop_last else -(-left // self.batch_size)
+
+
 class BatchSampler(Sampler):
     def __init__(self, sampler: Sampler, batch_size: int, drop_last: bool = False):
         self.sampler, self.batch_size, self.drop_last = sampler, batch_size, drop_last
 
     def __iter__(self):
-        batch = []
-        for i in self.sampler:
-            batch.append(i)
-            if len(batch) == self.batch_size:
-                yield batch
-                batch = []
-        if batch and not self.drop_last:
-            yield batch
+        return BatchIter(self.sampler, self.batch_size, self.drop_last)
+
+    iter = __iter__
 
     def __len__(self):
         n = len(self.sampler)

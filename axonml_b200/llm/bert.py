@@ -53,13 +53,65 @@ class BertLayer(nn.Module):
         return self.out_norm(x + self.dropout(self.output(self.intermediate(x))))
 
 
+class BertPooler(nn.Module):
+    """tanh(dense(hidden state of the first token)) (bert.rs:29-60)."""
+
+    def __init__(self, hidden_size: int):
+        super().__init__()
+        self.dense = nn.Linear(hidden_size, hidden_size, activation="tanh")
+
+    @classmethod
+    def new(cls, hidden_size: int): return cls(hidden_size)
+
+    def forward(self, hidden_states):
+        return self.dense(hidden_states[:, 0])
+
+
+class BertPredictionHeadTransform(nn.Module):
+    """dense -> activation -> LayerNorm in front of the vocabulary projection (bert.rs:260-300)."""
+
+    def __init__(self, hidden_size: int, layer_norm_eps: float = 1e-12, activation: str = "gelu"):
+        super().__init__()
+        act = {"gelu": "gelu", "relu": "relu", "silu": "silu", "swish": "silu", "tanh": "tanh"}[activation]
+        self.dense = nn.Linear(hidden_size, hidden_size, activation=act)
+        self.layer_norm = nn.LayerNorm(hidden_size, layer_norm_eps)
+        self.activation = activation
+
+    @classmethod
+    def new(cls, hidden_size, layer_norm_eps, activation): return cls(hidden_size, layer_norm_eps, activation)
+
+    def forward(self, x):
+        return self.layer_norm(self.dense(x))
+
+
+class BertLMPredictionHead(nn.Module):
+    """Transform followed by the projection onto the vocabulary (bert.rs:251-258).  With
+    ``tied_weight`` (the word-embedding matrix) the head owns only the output bias, as in the
+    published checkpoints; without it the head has a ``decoder`` Linear of its own."""
+
+    def __init__(self, hidden_size: int, vocab_size: int, layer_norm_eps: float = 1e-12, activation: str = "gelu", tied_weight=None):
+        super().__init__()
+        self.transform = BertPredictionHeadTransform(hidden_size, layer_norm_eps, activation)
+        self._tied = [tied_weight] if tied_weight is not None else None          # in a list: not registered a second time
+        if tied_weight is None:
+            self.decoder = nn.Linear(hidden_size, vocab_size)
+        else:
+            self.bias = nn.Parameter(torch.zeros(vocab_size))
+
+    def forward(self, x):
+        h = self.transform(x)
+        if self._tied is None:
+            return self.decoder(h)
+        return torch.nn.functional.linear(h, self._tied[0].to(h.dtype), self.bias.to(h.dtype))
+
+
 class Bert(nn.Module, LoadStateDict):
     def __init__(self, cfg: BertConfig):
         super().__init__()
         self.cfg = cfg
         self.embeddings = BertEmbeddings(cfg)
         self.layers = nn.ModuleList([BertLayer(cfg) for _ in range(cfg.num_hidden_layers)])
-        self.pooler = nn.Linear(cfg.hidden_size, cfg.hidden_size, activation="tanh")
+        self.pooler = BertPooler(cfg.hidden_size)
 
     @classmethod
     def new(cls, cfg): return cls(cfg)
@@ -68,10 +120,10 @@ class Bert(nn.Module, LoadStateDict):
         h = self.embeddings(ids, token_type_ids)
         for l in self.layers:
             h = l(h, attention_mask)
-        return h, self.pooler(h[:, 0])
+        return h, self.pooler(h)
 
 
-class BertForSequenceClassification(nn.Module):
+class BertForSequenceClassification(nn.Module, LoadStateDict):
     def __init__(self, cfg: BertConfig, num_labels: int = 2):
         super().__init__()
         self.bert, self.dropout = Bert(cfg), nn.Dropout(cfg.hidden_dropout_prob)
@@ -81,14 +133,44 @@ class BertForSequenceClassification(nn.Module):
         return self.classifier(self.dropout(self.bert(ids, token_type_ids, attention_mask)[1]))
 
 
-class BertForMaskedLM(nn.Module):
+class BertForMaskedLM(nn.Module, LoadStateDict):
     def __init__(self, cfg: BertConfig):
         super().__init__()
         self.bert = Bert(cfg)
-        self.transform = nn.Linear(cfg.hidden_size, cfg.hidden_size, activation="gelu")
-        self.norm = nn.LayerNorm(cfg.hidden_size, cfg.layer_norm_eps)
-        self.decoder_bias = nn.Parameter(torch.zeros(cfg.vocab_size))
+        self.cls = BertLMPredictionHead(cfg.hidden_size, cfg.vocab_size, cfg.layer_norm_eps, getattr(cfg, "hidden_act", "gelu"),
+                                        tied_weight=self.bert.embeddings.word_embeddings.weight)
 
     def forward(self, ids, token_type_ids=None, attention_mask=None):
-        h = self.norm(self.transform(self.bert(ids, token_type_ids, attention_mask)[0]))
-        return torch.nn.functional.linear(h, self.bert.embeddings.word_embeddings.weight.to(h.dtype), self.decoder_bias.to(h.dtype))
+        return self.cls(self.bert(ids, token_type_ids, attention_mask)[0])
+
+
+_BERT_RENAMES = (("attention.self.query", "query"), ("attention.self.key", "key"), ("attention.self.value", "value"),
+                 ("attention.output.dense", "attn_out"), ("attention.output.LayerNorm", "attn_norm"),
+                 ("intermediate.dense", "intermediate"), ("output.dense", "output"), ("output.LayerNorm", "out_norm"))
+
+
+def map_bert_weights(sd: dict, prefix: str = "") -> dict:
+    """Names of a published BERT checkpoint -> the names of ``Bert`` (``prefix=""``) or of the
+    task models that hold it as ``.bert`` (``prefix="bert."``).  ``encoder.layer.N.attention.self.
+    query`` becomes ``layers.N.query`` and so on; the masked-LM head ``cls.predictions.*`` becomes
+    ``cls.*``; the tied ``cls.predictions.decoder.weight`` and the position-id buffer are dropped;
+    old checkpoints' ``gamma`` / ``beta`` are read as ``weight`` / ``bias``."""
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("position_ids") or k == "cls.predictions.decoder.weight" or k == "cls.predictions.decoder.bias":
+            continue
+        k = k.replace(".gamma", ".weight").replace(".beta", ".bias")
+        if k.startswith("cls.predictions."):
+            k = "cls." + k[len("cls.predictions."):].replace("transform.LayerNorm", "transform.layer_norm")
+            out[k] = v
+            continue
+        if k.startswith(("classifier.", "cls.seq_relationship")):
+            out[k] = v
+            continue
+        k = k.removeprefix("bert.")
+        if k.startswith("encoder.layer."):
+            k = "layers." + k[len("encoder.layer."):]
+            for old, new in _BERT_RENAMES:
+                k = k.replace("." + old + ".", "." + new + ".")
+        out[prefix + k] = v
+    return out

@@ -108,27 +108,79 @@ def _takes_pos(model) -> bool:
         return False
 
 
+@dataclasses.dataclass
+class Beam:
+    """One hypothesis of a beam search (generation.rs:279-303): its tokens, the sum of the
+    log-probabilities of the generated ones, and whether it has produced an end token."""
+    tokens: list
+    score: float = 0.0
+    finished: bool = False
+
+    @classmethod
+    def new(cls, initial_tokens): return cls(list(initial_tokens))
+
+    def normalized_score(self, length_penalty: float) -> float:
+        return self.score / (len(self.tokens) ** length_penalty)
+
+    def extended(self, token: int, log_prob: float, finished: bool) -> "Beam":
+        return Beam(self.tokens + [int(token)], self.score + float(log_prob), finished)
+
+
 class BeamSearch:
-    def __init__(self, num_beams: int, length_penalty: float = 1.0, early_stopping: bool = False):
+    """Beam search as separate steps (generation.rs:306-395) -- ``init_beams``, ``expand_beams``,
+    ``should_stop``, ``best_sequence`` -- and ``search``, which drives them with a model."""
+
+    def __init__(self, num_beams: int, length_penalty: float = 1.0, early_stopping: bool = False, eos_token_ids=()):
         self.num_beams, self.length_penalty, self.early_stopping = num_beams, length_penalty, early_stopping
+        self.eos_token_ids = [int(t) for t in eos_token_ids]
+
+    @classmethod
+    def new(cls, num_beams, length_penalty, early_stopping, eos_token_ids): return cls(num_beams, length_penalty, early_stopping, eos_token_ids)
+
+    def init_beams(self, input_ids) -> list:
+        return [Beam.new(torch.as_tensor(input_ids).reshape(-1).tolist())]
+
+    def expand_beams(self, beams, next_token_logits) -> list:
+        """One step: every live beam is extended by its ``2 * num_beams`` best tokens (scores are
+        added as given: pass log-probabilities), finished beams are carried over, and the
+        ``num_beams`` candidates with the best length-normalised score are kept."""
+        eos = set(self.eos_token_ids)
+        cand = []
+        for beam, logits in zip(beams, next_token_logits):
+            if beam.finished:
+                cand.append(beam)
+                continue
+            lp = torch.as_tensor(logits, dtype=torch.float32).reshape(-1)
+            top = torch.topk(lp, min(2 * self.num_beams, lp.numel()))
+            for v, i in zip(top.values.tolist(), top.indices.tolist()):
+                cand.append(beam.extended(i, v, i in eos))
+        cand.sort(key=lambda b: b.normalized_score(self.length_penalty), reverse=True)
+        return cand[:self.num_beams]
+
+    def should_stop(self, beams) -> bool:
+        return self.early_stopping and all(b.finished for b in beams)
+
+    def best_sequence(self, beams):
+        """Tokens of the best finished beam; of the first beam when none has finished; None without beams."""
+        done = [b for b in beams if b.finished]
+        if done:
+            return list(max(done, key=lambda b: b.normalized_score(self.length_penalty)).tokens)
+        return list(beams[0].tokens) if beams else None
 
     @torch.no_grad()
     def search(self, model, ids: torch.Tensor, config: GenerationConfig) -> torch.Tensor:
         """Beam search for batch size 1 (as in the reference); returns the best sequence."""
-        beams = [(ids[:1], 0.0, False)]
-        eos = set(config.eos_token_ids)
+        if not self.eos_token_ids:
+            self.eos_token_ids = [int(t) for t in config.eos_token_ids]
+        beams = self.init_beams(ids[:1])
         for _ in range(config.max_new_tokens):
-            cand = []
-            for seq, score, fin in beams:
-                if fin:
-                    cand.append((seq, score, True))
-                    continue
-                lp = torch.log_softmax(model(seq)[:, -1].float(), -1)[0]
-                top = torch.topk(lp, self.num_beams)
-                for v, i in zip(top.values.tolist(), top.indices.tolist()):
-                    cand.append((torch.cat([seq, torch.tensor([[i]], device=seq.device)], 1), score + v, i in eos))
-            cand.sort(key=lambda c: c[1] / (c[0].shape[1] ** self.length_penalty), reverse=True)
-            beams = cand[: self.num_beams]
-            if all(b[2] for b in beams) or (self.early_stopping and beams[0][2]):
+            live = [b for b in beams if not b.finished]
+            if not live:
                 break
-        return beams[0][0]
+            batch = torch.tensor([b.tokens for b in live], device=ids.device)      # live beams have equal lengths
+            lps = torch.log_softmax(model(batch)[:, -1].float(), -1)
+            it = iter(lps)
+            beams = self.expand_beams(beams, [None if b.finished else next(it) for b in beams])
+            if all(b.finished for b in beams) or (self.early_stopping and beams[0].finished):
+                break
+        return torch.tensor([self.best_sequence(beams)], device=ids.device)

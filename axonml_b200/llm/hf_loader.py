@@ -103,6 +103,15 @@ class HFLoader:
         t = self.get_tensor(name)
         return None if t is None else t.to(dtype)
 
+    def tensor_info(self, name: str):
+        """``TensorInfo`` of one tensor (its stored dtype and shape), or ``None``."""
+        t = self.get_tensor(name)
+        if t is None:
+            return None
+        names = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16", torch.float64: "F64", torch.int64: "I64",
+                 torch.int32: "I32", torch.int8: "I8", torch.uint8: "U8", torch.bool: "BOOL"}
+        return TensorInfo(list(t.shape), t, names.get(t.dtype, str(t.dtype)))
+
     def require(self, name: str, dtype=torch.float32) -> torch.Tensor:
         t = self.get_as_tensor(name, dtype)
         if t is None:
@@ -142,6 +151,77 @@ def map_gpt2_weights(sd: dict) -> dict:
             out[f"transformer.blocks.{i}.{rest}"] = v
     return out
 
+
+
+@dataclasses.dataclass
+class TensorInfo:
+    """One tensor of a checkpoint as the loader reports it (hf_loader.rs:46-53)."""
+    shape: list
+    data: torch.Tensor
+    dtype: str                     # the stored type: "F32", "F16", "BF16", ...
+
+    def numel(self) -> int: return self.data.numel()
+
+
+class WeightMapper:
+    """Names of a family's checkpoint -> names of this package's model (hf_loader.rs:343-349)."""
+
+    def __init__(self, num_layers: int):
+        self.num_layers = num_layers
+
+    @classmethod
+    def new(cls, num_layers: int): return cls(num_layers)
+
+    def map_name(self, hf_name: str):
+        """The model's name for ``hf_name``, or ``None`` for a tensor the model does not use."""
+        raise NotImplementedError
+
+    def expected_weights(self) -> list:
+        raise NotImplementedError
+
+    def map_all(self, tensors: dict) -> dict:
+        out = {}
+        for k, v in tensors.items():
+            name = self.map_name(k)
+            if name is not None:
+                out[name] = v
+        return out
+
+    def missing(self, tensors: dict) -> list:
+        """Expected names absent from ``tensors`` (after mapping)."""
+        have = set(self.map_all(tensors))
+        return [w for w in self.expected_weights() if w not in have]
+
+
+class LLaMAWeightMapper(WeightMapper):
+    _PER_LAYER = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj", "mlp.up_proj",
+                  "mlp.down_proj", "input_layernorm", "post_attention_layernorm")
+    _TOP = ("embed_tokens.weight", "norm.weight")
+
+    def map_name(self, hf_name: str):
+        if "rotary_emb.inv_freq" in hf_name:
+            return None
+        return hf_name.removeprefix("model.")
+
+    def expected_weights(self) -> list:
+        return list(self._TOP) + [f"layers.{i}.{n}.weight" for i in range(self.num_layers) for n in self._PER_LAYER]
+
+
+class MistralWeightMapper(LLaMAWeightMapper):
+    """Mistral checkpoints use LLaMA's names."""
+
+
+class PhiWeightMapper(WeightMapper):
+    _PER_LAYER = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.dense", "mlp.fc1", "mlp.fc2", "input_layernorm")
+
+    def map_name(self, hf_name: str):
+        if "rotary_emb.inv_freq" in hf_name:
+            return None
+        return hf_name.removeprefix("model.") if hf_name.startswith("model.") else hf_name.removeprefix("transformer.")
+
+    def expected_weights(self) -> list:
+        return (["embed_tokens.weight", "final_layernorm.weight"]
+                + [f"layers.{i}.{n}.weight" for i in range(self.num_layers) for n in self._PER_LAYER])
 
 
 def map_hf_to_axonml(hf_name: str, arch: str) -> str:
@@ -192,7 +272,10 @@ def load_with_mapping(model, weights: dict, arch: str, strict: bool = False) -> 
     is dropped, GPT-2's transposed Conv1D weights are turned, and names the model does not have are
     retried in the reference's alternative scheme."""
     own = {k for k, _ in model.named_parameters()}
-    if arch == "gpt2":
+    if arch == "bert":
+        from .bert import map_bert_weights
+        mapped = map_bert_weights(weights, "bert." if any(k.startswith("bert.") for k in own) else "")
+    elif arch == "gpt2":
         mapped = map_gpt2_weights(weights)
         if not any(k in own for k in mapped):               # a bare GPT2 without the LM-head wrapper
             mapped = {k.removeprefix("transformer."): v for k, v in mapped.items()}

@@ -25,6 +25,11 @@ class MistralForCausalLM(LLaMAForCausalLM):
 
 
 Mistral = MistralForCausalLM
+# the blocks are LLaMA's (grouped-query attention with the window taken from the config, SwiGLU MLP);
+# the reference names them per family (mistral.rs: MistralAttention, MistralMLP, MistralDecoderLayer)
+from .llama import LLaMAAttention as MistralAttention  # noqa: E402
+from .llama import LLaMADecoderLayer as MistralDecoderLayer  # noqa: E402
+from .llama import LLaMAMLP as MistralMLP  # noqa: E402
 
 
 class PhiAttention(nn.Module):
@@ -55,6 +60,18 @@ class PhiAttention(nn.Module):
         return self.dense(sdpa(q, k, v, causal=True).reshape(B, S, self.nh * self.hd))
 
 
+class PhiMLP(nn.Module):
+    """fc1 -> GELU -> fc2 (phi.rs ``PhiMLP``); the activation runs in the first GEMM's epilogue."""
+
+    def __init__(self, cfg: PhiConfig):
+        super().__init__()
+        self.fc1 = nn.Linear(cfg.hidden_size, cfg.intermediate_size, activation="gelu")
+        self.fc2 = nn.Linear(cfg.intermediate_size, cfg.hidden_size)
+
+    def forward(self, x):
+        return self.fc2(self.fc1(x))
+
+
 class PhiDecoderLayer(nn.Module):
     def __init__(self, cfg: PhiConfig):
         super().__init__()
@@ -62,16 +79,15 @@ class PhiDecoderLayer(nn.Module):
         self.input_layernorm = nn.LayerNorm(cfg.hidden_size, cfg.layer_norm_eps)
         self.post_layernorm = None if self.parallel else nn.LayerNorm(cfg.hidden_size, cfg.layer_norm_eps)
         self.self_attn = PhiAttention(cfg)
-        self.fc1 = nn.Linear(cfg.hidden_size, cfg.intermediate_size, activation="gelu")
-        self.fc2 = nn.Linear(cfg.intermediate_size, cfg.hidden_size)
+        self.mlp = PhiMLP(cfg)
 
     def forward(self, x, kv_cache=None, pos0=0):
         h = self.input_layernorm(x)
         a = self.self_attn(h, kv_cache, pos0)
         if self.parallel:
-            return x + a + self.fc2(self.fc1(h))
+            return x + a + self.mlp(h)
         x = x + a
-        return x + self.fc2(self.fc1(self.post_layernorm(x)))
+        return x + self.mlp(self.post_layernorm(x))
 
 
 class PhiForCausalLM(nn.Module, LoadStateDict):

@@ -4,7 +4,7 @@ from .grad_scaler import GradScaler, GradScalerState
 from .lamb import LAMB
 from .lr_scheduler import (CosineAnnealingLR, ExponentialLR, LRScheduler, MultiStepLR, OneCycleLR,
                            ReduceLROnPlateau, StepLR, WarmupLR)
-from .optimizer import Optimizer
+from .optimizer import Optimizer, ParamState
 from .rmsprop import RMSprop
 from .sgd import SGD
 

@@ -14,6 +14,35 @@ import torch
 from ..ops import optim as O
 
 
+class ParamState:
+    """Per-parameter optimizer state (optimizer.rs:49-84): ``momentum_buffer`` (SGD momentum, or
+    Adam's first moment), ``exp_avg_sq`` (second moment), ``max_exp_avg_sq`` (AMSGrad) and the
+    ``step`` count.  ``Optimizer.param_state(p)`` returns the live state of a parameter in this
+    form; the buffers are the fp32 tensors the update kernels work on, not copies."""
+
+    def __init__(self, momentum_buffer=None, exp_avg_sq=None, max_exp_avg_sq=None, step: int = 0):
+        self.momentum_buffer, self.exp_avg_sq, self.max_exp_avg_sq, self.step = momentum_buffer, exp_avg_sq, max_exp_avg_sq, step
+
+    @classmethod
+    def new(cls): return cls()
+
+    def init_momentum(self, size, device=None) -> None:
+        self.momentum_buffer = torch.zeros(size, dtype=torch.float32, device=device)
+
+    def init_exp_avg_sq(self, size, device=None) -> None:
+        self.exp_avg_sq = torch.zeros(size, dtype=torch.float32, device=device)
+
+    def __repr__(self) -> str:
+        has = [n for n in ("momentum_buffer", "exp_avg_sq", "max_exp_avg_sq") if getattr(self, n) is not None]
+        return f"ParamState(step={self.step}, buffers={has})"
+
+
+# names under which the optimizers keep the buffers of a ParamState
+_FIRST_MOMENT = ("momentum_buffer", "buf", "exp_avg", "m", "grad_avg")
+_SECOND_MOMENT = ("exp_avg_sq", "v", "square_avg", "sq")
+_MAX_SECOND = ("max_exp_avg_sq", "vmax", "max_v")
+
+
 class Optimizer:
     def __init__(self, params: Iterable[torch.Tensor], lr: float):
         self.params = [p for p in params]
@@ -51,6 +80,12 @@ class Optimizer:
 
     def num_parameters(self) -> int:
         return sum(p.numel() for p in self.params)
+
+    def param_state(self, p) -> ParamState:
+        """The state kept for parameter ``p`` as a ``ParamState`` (empty before the first step)."""
+        st = self.state.get(id(p), {})
+        pick = lambda names: next((st[n] for n in names if n in st), None)
+        return ParamState(pick(_FIRST_MOMENT), pick(_SECOND_MOMENT), pick(_MAX_SECOND), self._step_count)
 
     # torch-style view used by the schedulers
     @property

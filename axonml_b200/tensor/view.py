@@ -89,3 +89,54 @@ def unravel_index(index: int, shape) -> list:
         out.append(index % s)
         index //= s
     return list(reversed(out))
+
+
+class SliceSpec:
+    """One entry of a multi-dimensional index (view.rs:27-85): ``SliceSpec.Index(i)`` picks one
+    position and drops the dimension, ``SliceSpec.range(a, b)`` / ``range_step(a, b, s)`` /
+    ``from_(a)`` / ``to(b)`` take a strided range, ``SliceSpec.All`` keeps the dimension and
+    ``SliceSpec.NewAxis`` inserts one of extent 1.  Negative positions count from the end."""
+
+    def __init__(self, kind: str, start=None, stop=None, step: int = 1):
+        self.kind, self.start, self.stop, self.step = kind, start, stop, step
+
+    @classmethod
+    def Index(cls, i: int): return cls("index", int(i))
+    @classmethod
+    def Range(cls, start=None, stop=None, step: int = 1): return cls("range", start, stop, step)
+    @classmethod
+    def range(cls, start: int, stop: int): return cls("range", start, stop, 1)
+    @classmethod
+    def range_step(cls, start: int, stop: int, step: int): return cls("range", start, stop, step)
+    @classmethod
+    def from_(cls, start: int): return cls("range", start, None, 1)
+    @classmethod
+    def to(cls, stop: int): return cls("range", None, stop, 1)
+
+    def as_index(self):
+        """The Python indexing object that means the same."""
+        if self.kind == "index":
+            return self.start
+        if self.kind == "range":
+            return slice(self.start, self.stop, self.step)
+        return slice(None) if self.kind == "all" else None
+
+    def __repr__(self) -> str:
+        return {"index": f"Index({self.start})", "range": f"Range({self.start}, {self.stop}, {self.step})", "all": "All",
+                "newaxis": "NewAxis"}[self.kind]
+
+
+SliceSpec.All = SliceSpec("all")
+SliceSpec.NewAxis = SliceSpec("newaxis")
+
+
+def slice_with(t, specs):
+    """View of ``t`` selected by a list of ``SliceSpec`` (fewer specs than dimensions leave the
+    rest whole).  Steps must be positive: a view cannot run backwards through storage here."""
+    from ..core.error import InvalidOperation
+    specs = list(specs)
+    if sum(s.kind != "newaxis" for s in specs) > t.dim():
+        raise InvalidOperation(f"{len(specs)} index entries for a tensor with {t.dim()} dimensions")
+    if any(s.kind == "range" and s.step <= 0 for s in specs):
+        raise InvalidOperation("slice step must be positive")
+    return t[tuple(s.as_index() for s in specs)]

@@ -4,8 +4,9 @@ from .models import (MLP, BasicBlock, Bottleneck, LeNet, ResNet, SimpleCNN, resn
                      resnet50)
 from . import datasets, transforms
 from .datasets import (CIFAR10, CIFAR100, MNIST, FashionMNIST, SyntheticCIFAR, SyntheticImageNet, SyntheticMNIST)
-from .models import (VGG, Transformer, TransformerDecoder, TransformerEncoder, VisionTransformer, vgg11, vgg11_bn, vgg13,
-                     vgg13_bn, vgg16, vgg16_bn, vgg19, vgg19_bn)
+from .models import (VGG, PositionalEncoding, Transformer, TransformerDecoder, TransformerEncoder, VggClassifier, VggFeatures,
+                     VggLayer, VisionTransformer, vgg11, vgg11_bn, vgg11_config, vgg13, vgg13_bn, vgg13_config, vgg16, vgg16_bn,
+                     vgg16_config, vgg19, vgg19_bn, vgg19_config, vit_base, vit_large)
 from .transforms import (CenterCrop, ColorJitter, Grayscale, ImageNormalize, Pad, RandomHorizontalFlip,
                          RandomRotation, RandomVerticalFlip, Resize, ToTensorImage)
 from . import hub

@@ -2,6 +2,8 @@
 (crates/axonml-vision/src/models/transformer.rs)."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ... import nn
@@ -21,6 +23,33 @@ class _MHA(nn.Module):
         o = sdpa(self.q_proj(q).view(B, Sq, self.h, self.hd), self.k_proj(k).view(B, Sk, self.h, self.hd),
                  self.v_proj(v).view(B, Sk, self.h, self.hd), causal=causal)
         return self.out_proj(o.reshape(B, Sq, E))
+
+
+class PositionalEncoding(nn.Module):
+    """Fixed sinusoidal position signal added to a [batch, seq, d_model] input
+    (crates/axonml-vision/src/models/transformer.rs:29-90).  Column pairs (2k, 2k+1) share the
+    frequency 10000^(-2k/d_model): sine in the even, cosine in the odd column.  (The reference
+    gives every column its own exponent i/d_model, so its odd columns sit half a step off the
+    usual table; the usual table is what is built here.)"""
+
+    def __init__(self, d_model: int, max_len: int = 5000):
+        super().__init__()
+        pos = torch.arange(max_len, dtype=torch.float32).unsqueeze(1)
+        k = torch.arange(0, d_model, 2, dtype=torch.float32)
+        div = torch.exp(-(k / d_model) * math.log(10000.0))
+        pe = torch.zeros(max_len, d_model)
+        pe[:, 0::2] = torch.sin(pos * div)
+        pe[:, 1::2] = torch.cos(pos * div[: d_model // 2])
+        self.register_buffer("encoding", pe, persistent=False)
+        self.max_len, self.d_model = max_len, d_model
+
+    @classmethod
+    def new(cls, d_model: int, max_len: int): return cls(d_model, max_len)
+
+    def forward(self, x):
+        if x.shape[1] > self.max_len:
+            raise ValueError(f"sequence of {x.shape[1]} exceeds max_len {self.max_len}")
+        return x + self.encoding[: x.shape[1]].to(x.dtype)
 
 
 class TransformerEncoderLayer(nn.Module):
@@ -115,3 +144,13 @@ class VisionTransformer(nn.Module):
         h = self.patch_embed(patches)
         h = torch.cat([self.cls_token.to(h.dtype).expand(B, -1, -1), h], 1) + self.pos_embed.to(h.dtype)
         return self.head(self.encoder(h)[:, 0])
+
+
+def vit_base() -> VisionTransformer:
+    """ViT-Base/16 for 224x224 inputs and 1000 classes (transformer.rs:754-756)."""
+    return VisionTransformer.vit_base(224, 1000)
+
+
+def vit_large() -> VisionTransformer:
+    """ViT-Large/16 for 224x224 inputs and 1000 classes (transformer.rs:760-762)."""
+    return VisionTransformer.vit_large(224, 1000)

@@ -402,3 +402,248 @@ def test_no_grad_guard_and_autocast_state():
             assert ag.autocast_depth() == 1
         assert ag.autocast_dtype("cpu") is DType.BF16
     assert ag.autocast_depth() == 0
+
+
+def test_vgg_building_blocks_and_positional_encoding():
+    from axonml_b200 import vision
+    cfg = vision.vgg11_config()
+    L = vision.VggLayer
+    assert cfg == [L.Conv(64), L.MaxPool, L.Conv(128), L.MaxPool, L.Conv(256), L.Conv(256), L.MaxPool, L.Conv(512), L.Conv(512), L.MaxPool,
+                   L.Conv(512), L.Conv(512), L.MaxPool]
+    assert [sum(not l.is_pool() for l in c()) for c in (vision.vgg11_config, vision.vgg13_config, vision.vgg16_config, vision.vgg19_config)] == [8, 10, 13, 16]
+    assert repr(cfg[0]) == "Conv(64)" and repr(cfg[1]) == "MaxPool"
+    small = [L.Conv(4), L.MaxPool, L.Conv(8), L.MaxPool]
+    feats = vision.VggFeatures(small, batch_norm=True)
+    assert feats.out_channels == 8 and feats(torch.randn(2, 3, 16, 16)).shape == (2, 8, 4, 4)
+    assert [k for k, _ in feats.named_parameters()] == ["0.weight", "0.bias", "1.weight", "1.bias", "4.weight", "4.bias", "5.weight", "5.bias"]
+    head = vision.VggClassifier(10, in_features=8 * 16).eval()
+    assert head(torch.randn(2, 128)).shape == (2, 10) and [k for k, _ in head.named_parameters()][-1] == "6.bias"
+    m = vision.vgg11(num_classes=5)
+    keys = [k for k, _ in m.named_parameters()]
+    assert keys[0] == "features.0.weight" and keys[-1] == "classifier.6.bias" and isinstance(m.features, vision.VggFeatures)
+    pe = vision.PositionalEncoding.new(8, 50)
+    x = torch.zeros(2, 10, 8)
+    y = pe(x)
+    assert torch.equal(y[0], y[1]) and torch.all(y[0, 0, 0::2] == 0) and torch.all(y[0, 0, 1::2] == 1)
+    pos, k = 7, 2
+    freq = 10000.0 ** (-2 * k / 8)
+    assert y[0, pos, 2 * k].item() == pytest.approx(math.sin(pos * freq), abs=1e-6) and y[0, pos, 2 * k + 1].item() == pytest.approx(math.cos(pos * freq), abs=1e-6)
+    assert not list(pe.parameters())
+    with pytest.raises(ValueError):
+        pe(torch.zeros(1, 51, 8))
+    assert callable(vision.vit_base) and callable(vision.vit_large)
+
+
+def test_slice_specs_sparse_tensor_param_state_and_batch_iter():
+    from axonml_b200 import data, optim, tensor
+    from axonml_b200.core.error import InvalidOperation
+    S = tensor.SliceSpec
+    t = torch.arange(60.0).view(3, 4, 5)
+    assert torch.equal(tensor.slice_with(t, [S.Index(1), S.All, S.range(1, 4)]), t[1, :, 1:4])
+    assert torch.equal(tensor.slice_with(t, [S.range_step(0, 3, 2), S.NewAxis, S.from_(2), S.to(-1)]), t[0:3:2, None, 2:, :-1])
+    assert torch.equal(tensor.slice_with(t, [S.Index(-1)]), t[-1]) and tensor.slice_with(t, [S.All]).data_ptr() == t.data_ptr()
+    assert repr(S.range(1, 4)) == "Range(1, 4, 1)" and repr(S.All) == "All" and repr(S.Index(2)) == "Index(2)"
+    with pytest.raises(InvalidOperation):
+        tensor.slice_with(t, [S.All] * 4)
+    with pytest.raises(InvalidOperation):
+        tensor.slice_with(t, [S.range_step(3, 0, -1)])
+
+    dense = torch.tensor([[0.0, 2.0, 0.0], [1.0, 0.0, 0.0], [0.0, 0.0, 3.0], [0.0, 0.0, 0.0]])
+    sp = tensor.SparseTensor.from_dense(dense)
+    assert sp.format() is tensor.SparseFormat.COO and sp.nnz() == 3 and sp.shape() == (4, 3) and sp.density() == 0.25
+    assert torch.equal(sp.to_dense(), dense) and torch.equal(sp.as_format(tensor.SparseFormat.CSR).to_dense(), dense)
+    assert sp.as_format(tensor.SparseFormat.CSR).format() is tensor.SparseFormat.CSR and [f.name for f in tensor.SparseFormat] == ["COO", "CSR", "CSC"]
+    x = torch.tensor([1.0, 2.0, 3.0])
+    assert torch.equal(sp.matvec(x), dense @ x) and torch.equal(sp.matvec([1.0, 2.0, 3.0]), dense @ x)
+    b = torch.randn(3, 2)
+    assert torch.allclose(sp.matmul(b), dense @ b) and torch.equal(sp.mul_scalar(2.0).to_dense(), dense * 2)
+    assert torch.equal(sp.as_format(tensor.SparseFormat.CSR).mul_scalar(-1.0).to_dense(), -dense)
+    same = tensor.SparseTensor.from_coords([(0, 1), (1, 0), (2, 2)], [2.0, 1.0, 3.0], (4, 3))
+    also = tensor.SparseTensor.from_coo([[0, 1, 2], [1, 0, 2]], [2.0, 1.0, 3.0], (4, 3))
+    assert torch.equal(same.to_dense(), dense) and torch.equal(also.to_dense(), dense)
+    assert torch.equal(tensor.SparseTensor.eye(3).to_dense(), torch.eye(3)) and torch.equal(tensor.SparseTensor.diag([1, 2]).to_dense(), torch.diag(torch.tensor([1.0, 2.0])))
+    with pytest.raises(NotImplementedError):
+        sp.as_format(tensor.SparseFormat.CSC)
+    with pytest.raises(TypeError):
+        tensor.SparseTensor(dense)
+
+    w = torch.nn.Parameter(torch.randn(4))
+    for make, want in ((lambda: optim.SGD([w], 0.1, momentum=0.9), (True, False, False)), (lambda: optim.Adam([w], 0.1), (True, True, False)),
+                       (lambda: optim.Adam([w], 0.1, amsgrad=True), (True, True, True)), (lambda: optim.RMSprop([w], 0.1), (True, True, False))):
+        opt = make()
+        empty = opt.param_state(w)
+        assert isinstance(empty, optim.ParamState) and empty.step == 0 and empty.momentum_buffer is None and empty.exp_avg_sq is None
+        w.grad = torch.ones(4)
+        opt.step(); opt.step()
+        st = opt.param_state(w)
+        assert st.step == 2 and (st.momentum_buffer is not None, st.exp_avg_sq is not None, st.max_exp_avg_sq is not None) == want, (type(opt).__name__, st)
+    manual = optim.ParamState.new()
+    manual.init_momentum(5); manual.init_exp_avg_sq((2, 3))
+    assert manual.momentum_buffer.shape == (5,) and manual.exp_avg_sq.shape == (2, 3) and "momentum_buffer" in repr(manual)
+
+    it = data.BatchIter(range(10), 4)
+    assert it.remaining() == 3 and list(it) == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9]] and it.remaining() == 0
+    assert list(data.BatchIter(range(10), 4, drop_last=True)) == [[0, 1, 2, 3], [4, 5, 6, 7]] and data.BatchIter(range(10), 4, True).remaining() == 2
+    bs = data.BatchSampler(data.SequentialSampler(5), 2)
+    assert isinstance(iter(bs), data.BatchIter) and list(bs) == [[0, 1], [2, 3], [4]] and len(bs) == 3
+    with pytest.raises(ValueError):
+        data.BatchIter(range(3), 0)
+    ds = data.TensorDataset(torch.arange(6.0).view(6, 1), torch.arange(6.0))
+    gi = data.GenericDataLoader(ds, 4).iter()
+    assert isinstance(gi, data.GenericDataLoaderIter) and gi.remaining() == 2
+    first = gi.next()
+    assert gi.remaining() == 1 and gi.next() is not None and gi.next() is None
+
+
+def test_named_backward_functions_match_the_tape():
+    """Every backward formula against torch's own differentiation of the same operation, in fp64."""
+    from axonml_b200 import autograd as ag
+    torch.manual_seed(0)
+    D = torch.float64
+
+    def check(fn_cls, torch_fn, inputs, n_grad=None, **opts):
+        want = lambda i, t: t.is_floating_point() and (n_grad is None or i < n_grad)
+        ours = [t.clone().requires_grad_(want(i, t)) for i, t in enumerate(inputs)]
+        ref = [t.clone().requires_grad_(want(i, t)) for i, t in enumerate(inputs)]
+        y1, y2 = fn_cls.call(*ours, **opts), torch_fn(*ref)
+        assert torch.allclose(y1, y2, atol=1e-12), fn_cls.__name__
+        w = torch.randn_like(y2)
+        (y1 * w).sum().backward()
+        (y2 * w).sum().backward()
+        for a, b in zip(ours, ref):
+            if b.grad is not None:
+                assert a.grad is not None and torch.allclose(a.grad, b.grad, atol=1e-10), fn_cls.__name__
+            else:
+                assert a.grad is None, fn_cls.__name__
+
+    r = lambda *s: torch.randn(*s, dtype=D)
+    pos = lambda *s: torch.rand(*s, dtype=D) + 0.5
+    check(ag.AddBackward, torch.add, [r(3, 4), r(4)])                       # the second operand is broadcast
+    check(ag.SubBackward, torch.sub, [r(2, 1, 4), r(3, 1)])
+    check(ag.MulBackward, torch.mul, [r(3, 4), r(3, 1)])
+    check(ag.DivBackward, torch.div, [r(3, 4), pos(4)])
+    check(ag.NegBackward, torch.neg, [r(5)])
+    check(ag.PowBackward, lambda x: x ** 3.0, [pos(4)], exponent=3.0)
+    check(ag.SumBackward, torch.sum, [r(3, 4)])
+    check(ag.MeanBackward, torch.mean, [r(3, 4)])
+    check(ag.NarrowBackward, lambda x: x.narrow(1, 1, 2), [r(3, 4)], dim=1, start=1, length=2)
+    check(ag.ReluBackward, torch.relu, [r(10)])
+    check(ag.LeakyReluBackward, lambda x: torch.nn.functional.leaky_relu(x, 0.2), [r(10)], negative_slope=0.2)
+    check(ag.SigmoidBackward, torch.sigmoid, [r(10)])
+    check(ag.TanhBackward, torch.tanh, [r(10)])
+    check(ag.GeluBackward, lambda x: torch.nn.functional.gelu(x, approximate="tanh"), [r(10)])
+    check(ag.SoftmaxBackward, lambda x: torch.softmax(x, 1), [r(3, 5)], dim=1)
+    check(ag.MatMulBackward, torch.matmul, [r(3, 4), r(4, 5)])
+    check(ag.MatMulBackward, torch.matmul, [r(2, 3, 4), r(4, 5)])             # the right operand is shared by the batch
+    check(ag.MatMulBackward, torch.matmul, [r(3, 4), r(4)])
+    check(ag.MatMulBackward, torch.matmul, [r(4), r(4)])
+    check(ag.TransposeBackward, lambda x: x.transpose(0, 2), [r(2, 3, 4)], dim0=0, dim1=2)
+    check(ag.ReshapeBackward, lambda x: x.reshape(6, 4), [r(2, 3, 4)], shape=(6, 4))
+    check(ag.ViewBackward, lambda x: x.reshape(-1), [r(2, 3)], shape=(-1,))
+    check(ag.SqueezeBackward, lambda x: x.squeeze(1), [r(2, 1, 3)], dim=1)
+    check(ag.UnsqueezeBackward, lambda x: x.unsqueeze(0), [r(2, 3)], dim=0)
+    F = torch.nn.functional
+    tgt = torch.tensor([0, 2, 1])
+    for red in ("mean", "sum", "none"):
+        check(ag.MseLossBackward, lambda x, t: F.mse_loss(x, t, reduction=red), [r(3, 4), r(3, 4).detach()], n_grad=1, reduction=red)
+        check(ag.L1LossBackward, lambda x, t: F.l1_loss(x, t, reduction=red), [r(3, 4), r(3, 4)], n_grad=1, reduction=red)
+        check(ag.SmoothL1LossBackward, lambda x, t: F.smooth_l1_loss(x, t, reduction=red, beta=0.7), [r(3, 4) * 2, r(3, 4)], n_grad=1, reduction=red, beta=0.7)
+        check(ag.BceLossBackward, lambda p, t: F.binary_cross_entropy(p, t, reduction=red), [torch.rand(6, dtype=D) * 0.9 + 0.05, torch.rand(6, dtype=D).round()], n_grad=1, reduction=red)
+        check(ag.NllLossBackward, lambda lp, t: F.nll_loss(lp, t, reduction=red), [torch.log_softmax(r(3, 4), 1), tgt], n_grad=1, reduction=red)
+        check(ag.CrossEntropyLossBackward, lambda x, t: F.cross_entropy(x, t, reduction=red), [r(3, 4), tgt], n_grad=1, reduction=red)
+    with pytest.raises(ValueError):
+        ag.MseLossBackward("median")
+    assert torch.equal(ag.functions.sum_to_shape(torch.ones(2, 3, 4), (3, 1)), torch.full((3, 1), 8.0))
+    acc = ag.functions.GradAccumulator()
+    node = ag.AccumulateGrad.new(acc)
+    node.accumulate(torch.ones(3)); node.accumulate(torch.full((3,), 2.0))
+    assert torch.equal(acc.get(), torch.full((3,), 3.0))
+    x = torch.ones(3, requires_grad=True)
+    (ag.AccumulateGrad.call(x, grad_accumulator=acc) * 5).sum().backward()
+    assert torch.equal(acc.get(), torch.full((3,), 8.0)) and torch.equal(x.grad, torch.full((3,), 5.0))
+    acc.clear()
+    assert acc.get() is None and ag.GradFnId is int
+
+
+def test_grad_guards_checkpoint_estimates_and_thread_graph():
+    from axonml_b200 import autograd as ag
+    x = torch.ones(2, requires_grad=True)
+    with ag.no_grad():
+        g = ag.EnableGradGuard()
+        assert (x * 2).requires_grad
+        g.drop()
+        assert not (x * 2).requires_grad
+    im = ag.InferenceModeGuard.new()
+    assert torch.is_inference_mode_enabled() and not (x * 2).requires_grad
+    im.drop(); im.drop()
+    assert not torch.is_inference_mode_enabled() and (x * 2).requires_grad
+    assert ag.estimate_memory_savings(24, 4, 100.0) == (2400.0, 600.0) and ag.estimate_memory_savings(10, 3, 1.0) == (10.0, 4.0)
+    assert ag.estimate_memory_savings(24, 0, 100.0) == (2400.0, 2400.0)
+    assert ag.suggest_segments(24, 100.0, 5000.0) == 0 and ag.suggest_segments(24, 100.0, 50.0) == 24
+    assert ag.suggest_segments(24, 100.0, 600.0) == 4 and ag.suggest_segments(25, 100.0, 600.0) == 5
+    seen = []
+    ag.with_graph(lambda g: seen.append(g.register_leaf(True).id))
+    ag.with_graph(lambda g: seen.append(g.len()))
+    assert seen[1] == seen[0] + 1                                         # the same per-thread graph both times
+    import threading
+    other = []
+    th = threading.Thread(target=lambda: ag.with_graph(lambda g: other.append(g.len())))
+    th.start(); th.join()
+    assert other == [0]
+
+
+def test_backend_handles_launch_config_and_storage_guards():
+    import threading
+    from axonml_b200 import core
+    assert [b.name for b in core.BackendType] == ["Cpu", "Cuda", "Vulkan", "Metal", "Wgpu"]
+    assert core.gpu_count() == (torch.cuda.device_count() if torch.cuda.is_available() else 0)
+    assert core.best_available_backend_type() is (core.BackendType.Cuda if torch.cuda.is_available() else core.BackendType.Cpu)
+    assert core.CpuBackend().backend_type() is core.BackendType.Cpu and core.VulkanBackend().backend_type() is core.BackendType.Vulkan
+    lc = core.launch_config(1000)
+    assert core.BLOCK_SIZE == 256 and lc == core.LaunchConfig((4, 1, 1), (256, 1, 1), 0) and core.launch_config(256).grid_dim == (1, 1, 1)
+    assert core.launch_config(257).grid_dim[0] == 2 and core.launch_config(0).grid_dim[0] == 0
+    t = torch.arange(6, dtype=torch.float32)
+    mem = core.GpuMemory.of(t)
+    assert (mem.ptr(), mem.size(), mem.device_index(), mem.backend_type()) == (t.data_ptr(), 24, 0, core.BackendType.Cpu) and not mem.is_null()
+    assert core.GpuMemory.new(0, 0, 0, core.BackendType.Cuda).is_null() and "24 B" in repr(mem)
+    st = core.GpuStream.new(0, 0, core.BackendType.Cpu)
+    st.synchronize()                                                       # nothing to wait for on the host
+    assert st.handle() == 0 and st.backend_type() is core.BackendType.Cpu and core.GpuStream.current().device_index() == 0
+    with pytest.raises(core.Error):
+        core.GpuStream.new(0, 0, core.BackendType.Metal).synchronize()
+    core.stream_synchronize(0)
+    from axonml_b200.core import backends as B
+    for e, text in ((B.DeviceNotFound(3), "CUDA device not found: 3"), (B.BlasError("x"), "cuBLAS error: x"), (B.KernelNotFound("k"), "CUDA kernel not found: k"),
+                    (B.ModuleLoadFailed("m"), "Failed to load CUDA module: m"), (B.DriverError("d"), "CUDA driver error: d")):
+        assert isinstance(e, core.CudaError) and str(e) == text
+
+    s = core.Storage.from_vec([1.0, 2.0, 3.0, 4.0])
+    with s.read() as a, s.read() as b:                                     # readers share
+        assert a.to_vec() == [1.0, 2.0, 3.0, 4.0] and len(b) == 4 and b[1] == 2.0
+        with pytest.raises(TimeoutError):
+            s.write(timeout=0.05)                                          # a writer waits for them
+    view = s.slice(1, 2)
+    with view.write() as w:                                                # a view shares the buffer's lock
+        w[0] = 20.0
+        with pytest.raises(TimeoutError):
+            s.read(timeout=0.05)
+        w.fill(7.0)
+    assert s.as_tensor().tolist() == [1.0, 7.0, 7.0, 4.0]
+    g = s.write()
+    g.copy_from([9, 8, 7, 6])
+    done = []
+    th = threading.Thread(target=lambda: done.append(s.read().to_vec()))
+    th.start()
+    th.join(0.1)
+    assert th.is_alive() and not done                                      # blocked behind the writer
+    g.drop(); g.drop()
+    th.join(2.0)
+    assert done == [[9.0, 8.0, 7.0, 6.0]]
+    with pytest.raises(RuntimeError):
+        g.tensor()
+    r = s.read()
+    assert isinstance(r, core.StorageReadGuard)
+    r.drop()
+    w = s.write(timeout=1.0)
+    assert isinstance(w, core.StorageWriteGuard)
+    w.drop()

@@ -475,3 +475,112 @@ def test_flash_attention_config_defaults_and_exports():
         assert hasattr(llm, name), name
     for name in ("vgg11_bn", "vgg13", "vgg13_bn", "vgg16_bn", "vgg19_bn", "PretrainedModel", "model_registry", "download_weights"):
         assert hasattr(vision, name), name
+
+
+def test_beam_search_steps_and_search():
+    import math
+    bs = llm.BeamSearch.new(2, 1.0, True, [3])
+    beams = bs.init_beams(torch.tensor([[5, 6]]))
+    assert len(beams) == 1 and beams[0].tokens == [5, 6] and beams[0].score == 0.0 and not beams[0].finished
+    lp = torch.log(torch.tensor([0.1, 0.6, 0.25, 0.05]))
+    beams = bs.expand_beams(beams, [lp])
+    assert [b.tokens[-1] for b in beams] == [1, 2] and beams[0].score == pytest.approx(math.log(0.6)) and not any(b.finished for b in beams)
+    assert beams[0].normalized_score(1.0) == pytest.approx(math.log(0.6) / 3) and beams[0].normalized_score(0.0) == pytest.approx(math.log(0.6))
+    step2 = [torch.log(torch.tensor([0.05, 0.05, 0.1, 0.8])), torch.log(torch.tensor([0.25, 0.25, 0.25, 0.25]))]
+    beams = bs.expand_beams(beams, step2)
+    assert beams[0].tokens == [5, 6, 1, 3] and beams[0].finished and not bs.should_stop(beams)        # the second beam is still open
+    assert bs.best_sequence(beams) == [5, 6, 1, 3]
+    kept = bs.expand_beams(beams, [None, torch.log(torch.tensor([0.01, 0.01, 0.01, 0.97]))])
+    assert kept[0].tokens == [5, 6, 1, 3] and all(b.finished for b in kept) and bs.should_stop(kept)      # finished beams are carried over
+    assert llm.BeamSearch(2).best_sequence([]) is None and llm.BeamSearch(2).best_sequence([llm.Beam.new([1])]) == [1]
+    assert not llm.BeamSearch(2, early_stopping=False).should_stop(kept)
+
+    class Chain(torch.nn.Module):            # token t is followed by t+1 with p=0.9, by 0 otherwise; 4 ends the text
+        def forward(self, ids):
+            nxt = (ids[:, -1] + 1).clamp(max=4)
+            logits = torch.full((ids.shape[0], ids.shape[1], 5), math.log(0.1 / 4))
+            logits[torch.arange(ids.shape[0]), -1, nxt] = math.log(0.9)
+            return logits
+
+    out = llm.BeamSearch(3, 1.0, True).search(Chain(), torch.tensor([[1]]), llm.GenerationConfig(max_new_tokens=8, eos_token_ids=[4]))
+    assert out.tolist() == [[1, 2, 3, 4]]
+
+
+def test_bert_heads_and_published_checkpoint_names():
+    cfg = llm.BertConfig(vocab_size=60, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                         max_position_embeddings=16, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    torch.manual_seed(0)
+    ref = llm.BertForMaskedLM(cfg).eval()
+    keys = [k for k, _ in ref.named_parameters()]
+    assert "bert.pooler.dense.weight" in keys and "cls.transform.dense.weight" in keys and "cls.transform.layer_norm.bias" in keys and "cls.bias" in keys
+    assert not any("decoder" in k for k in keys) and len(keys) == len(set(keys))          # the projection is the embedding matrix
+    inv = {"query": "attention.self.query", "key": "attention.self.key", "value": "attention.self.value", "attn_out": "attention.output.dense",
+           "attn_norm": "attention.output.LayerNorm", "intermediate": "intermediate.dense", "output": "output.dense", "out_norm": "output.LayerNorm"}
+    hf = {"bert.embeddings.position_ids": torch.arange(16).unsqueeze(0)}
+    for k, v in ref.named_parameters():
+        if k.startswith("bert.layers."):
+            _, _, i, name, leaf = k.split(".")
+            hf[f"bert.encoder.layer.{i}.{inv[name]}.{leaf}"] = v.detach()
+        elif k.startswith("cls."):
+            hf["cls.predictions." + k[4:].replace("layer_norm", "LayerNorm")] = v.detach()
+        else:
+            hf[k] = v.detach()
+    hf["cls.predictions.decoder.weight"] = ref.bert.embeddings.word_embeddings.weight.detach()
+    hf["bert.embeddings.LayerNorm.gamma"] = hf.pop("bert.embeddings.LayerNorm.weight")          # the oldest checkpoints' spelling
+    hf["bert.embeddings.LayerNorm.beta"] = hf.pop("bert.embeddings.LayerNorm.bias")
+    model = llm.BertForMaskedLM(cfg).eval()
+    res = llm.load_with_mapping(model, hf, "bert", strict=True)
+    assert res.loaded_count == len(keys) and not res.unexpected_keys and not res.missing_keys
+    ids = torch.randint(0, 60, (2, 7))
+    with torch.no_grad():
+        assert torch.allclose(model(ids), ref(ids), atol=1e-5) and model(ids).shape == (2, 7, 60)
+    bare = llm.Bert(cfg).eval()
+    r2 = llm.load_with_mapping(bare, hf, "bert")
+    assert not r2.missing_keys and sorted(r2.unexpected_keys) == sorted(k for k in keys if k.startswith("cls."))
+    with torch.no_grad():
+        seq, pooled = bare(ids)
+        assert torch.allclose(pooled, torch.tanh(torch.nn.functional.linear(seq[:, 0], bare.pooler.dense.weight, bare.pooler.dense.bias)), atol=1e-5)
+    pooler = llm.BertPooler.new(8)
+    assert pooler(torch.randn(3, 5, 8)).shape == (3, 8)
+    head = llm.BertLMPredictionHead(8, 20, activation="relu")                                    # untied: owns its decoder
+    assert head(torch.randn(2, 3, 8)).shape == (2, 3, 20) and "decoder.weight" in dict(head.named_parameters())
+    t = llm.BertPredictionHeadTransform.new(8, 1e-12, "gelu")
+    x = torch.randn(4, 8)
+    want = torch.nn.functional.layer_norm(torch.nn.functional.gelu(torch.nn.functional.linear(x, t.dense.weight, t.dense.bias), approximate="tanh"),
+                                          (8,), t.layer_norm.weight, t.layer_norm.bias, 1e-12)
+    assert torch.allclose(t(x), want, atol=1e-5)
+
+
+def test_weight_mappers_cover_what_the_models_expect(tmp_path):
+    cfg, _ = _tiny_llama_dir(str(tmp_path / "ck"), dtype=torch.bfloat16)
+    loader = llm.HFLoader.from_local(str(tmp_path / "ck"))
+    m = llm.LLaMAWeightMapper.new(cfg.num_hidden_layers)
+    mapped = m.map_all(loader.load_tensors())
+    assert m.map_name("model.layers.0.self_attn.rotary_emb.inv_freq") is None and m.map_name("lm_head.weight") == "lm_head.weight"
+    assert m.map_name("model.layers.1.mlp.up_proj.weight") == "layers.1.mlp.up_proj.weight" and m.missing(loader.load_tensors()) == []
+    bare = llm.LLaMA(cfg)
+    assert set(m.expected_weights()) == {k for k, _ in bare.named_parameters()}                # exactly the decoder's parameters
+    assert len(m.expected_weights()) == 2 + 9 * cfg.num_hidden_layers and set(mapped) - set(m.expected_weights()) == {"lm_head.weight"}
+    part = {k: v for k, v in loader.load_tensors().items() if "q_proj" not in k}
+    assert m.missing(part) == [f"layers.{i}.self_attn.q_proj.weight" for i in range(cfg.num_hidden_layers)]
+    assert llm.MistralWeightMapper(3).expected_weights() == llm.LLaMAWeightMapper(3).expected_weights()
+    info = loader.tensor_info("model.norm.weight")
+    assert isinstance(info, llm.TensorInfo) and info.dtype == "BF16" and info.shape == [cfg.hidden_size] and info.numel() == cfg.hidden_size
+    assert loader.tensor_info("absent") is None
+    pcfg = llm.PhiConfig(vocab_size=50, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
+                         max_position_embeddings=32)
+    phi = llm.PhiForCausalLM(pcfg)
+    names = {k for k, _ in phi.named_parameters()}
+    pm = llm.PhiWeightMapper(2)
+    assert set(pm.expected_weights()) <= names and "layers.1.mlp.fc2.weight" in names and isinstance(phi.layers[0].mlp, llm.PhiMLP)
+    assert pm.map_name("transformer.layers.0.mlp.fc1.bias") == "layers.0.mlp.fc1.bias" and pm.map_name("model.final_layernorm.bias") == "final_layernorm.bias"
+    hf = {"model." + k if not k.startswith("lm_head") else k: v.detach() for k, v in phi.named_parameters()}
+    fresh = llm.PhiForCausalLM(pcfg)
+    res = llm.load_with_mapping(fresh, hf, "phi", strict=True)
+    assert res.loaded_count == len(names)
+    ids = torch.randint(0, 50, (1, 6))
+    with torch.no_grad():
+        assert torch.allclose(fresh.eval()(ids), phi.eval()(ids), atol=1e-5)
+    assert llm.MistralAttention is llm.LLaMAAttention and llm.MistralMLP is llm.LLaMAMLP and llm.MistralDecoderLayer is llm.LLaMADecoderLayer
+    with pytest.raises(NotImplementedError):
+        llm.WeightMapper(1).map_name("x")
