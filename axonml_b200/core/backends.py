@@ -145,6 +145,69 @@ class GpuStream:
             raise DeviceNotAvailableError(self._backend_type.value)
 
 
+# module-level queries of the CUDA backend (crates/axonml-core/src/backends/cuda.rs ``is_available``,
+# ``device_count``, ``is_device_available``, ``get_capabilities``)
+def is_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def device_count() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def is_device_available(index: int) -> bool:
+    return 0 <= index < device_count()
+
+
+def get_capabilities(index: int = 0):
+    """``DeviceCapabilities`` of CUDA device ``index``; raises ``DeviceNotFound`` when there is none."""
+    if not is_device_available(index):
+        raise DeviceNotFound(index)
+    return Device.Cuda(index).capabilities()
+
+
+class CudaKernels:
+    """The kernel library as an object (backends/cuda_kernels/mod.rs ``CudaKernels``: the loaded
+    module plus launch helpers).  The reference embeds PTX for six elementwise kernels; here the
+    object fronts the sm_100a library the package is built with: ``has(name)`` says whether an
+    entry point exists, ``launch_elementwise`` runs one of the unary / binary elementwise kernels."""
+    @property
+    def UNARY(self) -> tuple:
+        from ..ops import elementwise
+        return tuple(elementwise.UNARY)
+
+    @property
+    def BINARY(self) -> tuple:
+        from ..ops import elementwise
+        return tuple(elementwise.BINARY)
+
+    def __init__(self, device_index: int = 0):
+        if not is_device_available(device_index):
+            raise DeviceNotFound(device_index)
+        self.device_index = device_index
+        try:
+            self._lib = N.cuda()
+        except Exception as e:  # noqa: BLE001 - any loader failure is a module-load failure here
+            raise ModuleLoadFailed(str(e)) from e
+
+    @classmethod
+    def load(cls, device_index: int = 0): return cls(device_index)
+
+    def has(self, entry_point: str) -> bool:
+        return hasattr(getattr(self._lib, "_lib", self._lib), entry_point)        # dlsym through ctypes
+
+    def launch_config(self, n: int) -> LaunchConfig:
+        return launch_config(n)
+
+    def launch_elementwise(self, name: str, *tensors, alpha: float = 0.0):
+        from ..ops import elementwise
+        if name in self.BINARY and len(tensors) == 2:
+            return elementwise.binary(tensors[0], tensors[1], name)
+        if name in self.UNARY and len(tensors) == 1:
+            return elementwise.unary(tensors[0], name, alpha)
+        raise KernelNotFound(f"{name} with {len(tensors)} operands")
+
+
 def gpu_count() -> int:
     """Devices over all GPU backends (backends/mod.rs:266-291): the CUDA devices here."""
     return torch.cuda.device_count() if torch.cuda.is_available() else 0

@@ -864,3 +864,26 @@ def test_vocab_parallel_cross_entropy_kernels_on_two_slices(dtype, kernel_status
     tol = 1e-6 if dtype == torch.float32 else 2e-4
     close(full[:, :V], ref_in.grad, tol, 2e-2)
     assert bool((full[:, V:] == 0).all())                       # padded columns get a zero gradient
+
+
+@pytest.mark.gpu
+def test_cuda_kernels_facade_and_device_queries():
+    from axonml_b200 import core
+    from axonml_b200.core import backends as B
+    assert B.is_available() and B.device_count() >= 1 and B.is_device_available(0) and not B.is_device_available(64)
+    caps = B.get_capabilities(0)
+    assert caps.sm_count > 0 and caps.total_memory > 0 and caps.supports_bf16
+    k = core.CudaKernels.load(0)
+    assert k.has("ax_norm_bwd_noalloc") and not k.has("ax_no_such_entry") and k.launch_config(1000).grid_dim == (4, 1, 1)
+    x = torch.linspace(-2, 2, 4096, device="cuda")
+    assert torch.allclose(k.launch_elementwise("relu", x), torch.relu(x))
+    assert torch.allclose(k.launch_elementwise("add", x, x), 2 * x)
+    with pytest.raises(core.CudaError):
+        k.launch_elementwise("conv9d", x)
+    with pytest.raises(core.CudaError):
+        core.CudaKernels.load(64)
+    mem = core.GpuMemory.of(x)
+    assert mem.backend_type() is core.BackendType.Cuda and mem.size() == 4096 * 4
+    s = core.GpuStream.current(0)
+    assert s.backend_type() is core.BackendType.Cuda
+    s.synchronize()
