@@ -7,6 +7,7 @@ import torch
 from .. import nn
 from ..ops.attention import sdpa
 from .config import BertConfig
+from ._api import ModelApi
 from .hf_loader import LoadStateDict
 
 
@@ -105,43 +106,89 @@ class BertLMPredictionHead(nn.Module):
         return torch.nn.functional.linear(h, self._tied[0].to(h.dtype), self.bias.to(h.dtype))
 
 
-class Bert(nn.Module, LoadStateDict):
-    def __init__(self, cfg: BertConfig):
+def _bert_config_from_json(j: dict) -> BertConfig:
+    d = BertConfig()
+    g = lambda k, cast: cast(j.get(k, getattr(d, k)))
+    return BertConfig(vocab_size=g("vocab_size", int), hidden_size=g("hidden_size", int), num_hidden_layers=g("num_hidden_layers", int),
+                      num_attention_heads=g("num_attention_heads", int), intermediate_size=g("intermediate_size", int),
+                      max_position_embeddings=g("max_position_embeddings", int), type_vocab_size=g("type_vocab_size", int),
+                      layer_norm_eps=g("layer_norm_eps", float), hidden_dropout_prob=g("hidden_dropout_prob", float),
+                      attention_probs_dropout_prob=g("attention_probs_dropout_prob", float))
+
+
+class Bert(nn.Module, LoadStateDict, ModelApi):
+    ARCH = "bert"
+    _config_from_json = staticmethod(_bert_config_from_json)
+
+    def __init__(self, cfg: BertConfig, add_pooler: bool = True):
         super().__init__()
         self.cfg = cfg
         self.embeddings = BertEmbeddings(cfg)
         self.layers = nn.ModuleList([BertLayer(cfg) for _ in range(cfg.num_hidden_layers)])
-        self.pooler = BertPooler(cfg.hidden_size)
+        self.pooler = BertPooler(cfg.hidden_size) if add_pooler else None
 
     @classmethod
     def new(cls, cfg): return cls(cfg)
 
-    def forward(self, ids, token_type_ids=None, attention_mask=None):
+    @classmethod
+    def with_pooler(cls, cfg, add_pooler: bool = True):
+        """Encoder with (``True``) or without the pooling layer over the first token (bert.rs ``with_pooler``)."""
+        return cls(cfg, add_pooler)
+
+    def encode(self, ids, token_type_ids=None, attention_mask=None):
+        """Hidden states [batch, seq, hidden] of the last layer."""
         h = self.embeddings(ids, token_type_ids)
         for l in self.layers:
             h = l(h, attention_mask)
-        return h, self.pooler(h)
+        return h
+
+    def forward(self, ids, token_type_ids=None, attention_mask=None):
+        h = self.encode(ids, token_type_ids, attention_mask)
+        return h, (self.pooler(h) if self.pooler is not None else None)
+
+    def forward_with_pooling(self, ids, token_type_ids=None, attention_mask=None):
+        """``(hidden states, pooled first-token vector)``; an encoder built without a pooler raises."""
+        if self.pooler is None:
+            raise ValueError("this encoder was built without a pooler")
+        return self.forward(ids, token_type_ids, attention_mask)
+
+    def forward_ids(self, ids, token_type_ids=None, attention_mask=None):
+        """Hidden states for integer (or float-typed) token ids."""
+        ids = torch.as_tensor(ids)
+        return self.encode((ids.unsqueeze(0) if ids.dim() == 1 else ids).long(), token_type_ids, attention_mask)
 
 
-class BertForSequenceClassification(nn.Module, LoadStateDict):
+class BertForSequenceClassification(nn.Module, LoadStateDict, ModelApi):
+    ARCH = "bert"
+    _config_from_json = staticmethod(_bert_config_from_json)
+
     def __init__(self, cfg: BertConfig, num_labels: int = 2):
         super().__init__()
+        self.cfg = cfg
         self.bert, self.dropout = Bert(cfg), nn.Dropout(cfg.hidden_dropout_prob)
         self.classifier = nn.Linear(cfg.hidden_size, num_labels)
 
     def forward(self, ids, token_type_ids=None, attention_mask=None):
         return self.classifier(self.dropout(self.bert(ids, token_type_ids, attention_mask)[1]))
 
+    forward_classification = forward
 
-class BertForMaskedLM(nn.Module, LoadStateDict):
+
+class BertForMaskedLM(nn.Module, LoadStateDict, ModelApi):
+    ARCH = "bert"
+    _config_from_json = staticmethod(_bert_config_from_json)
+
     def __init__(self, cfg: BertConfig):
         super().__init__()
+        self.cfg = cfg
         self.bert = Bert(cfg)
         self.cls = BertLMPredictionHead(cfg.hidden_size, cfg.vocab_size, cfg.layer_norm_eps, getattr(cfg, "hidden_act", "gelu"),
                                         tied_weight=self.bert.embeddings.word_embeddings.weight)
 
     def forward(self, ids, token_type_ids=None, attention_mask=None):
         return self.cls(self.bert(ids, token_type_ids, attention_mask)[0])
+
+    forward_mlm = forward
 
 
 _BERT_RENAMES = (("attention.self.query", "query"), ("attention.self.key", "key"), ("attention.self.value", "value"),

@@ -86,6 +86,12 @@ class MistralConfig(LLaMAConfig):
     def mistral_7b(cls): return cls(vocab_size=32000, intermediate_size=14336, num_key_value_heads=8,
                                     max_position_embeddings=32768, rope_theta=10000.0, sliding_window=4096)
     @classmethod
+    def mistral_7b_instruct(cls):
+        """Mistral-7B-Instruct v0.2: the 7B architecture without a sliding window and with rope theta 1e6."""
+        return cls(vocab_size=32000, intermediate_size=14336, num_key_value_heads=8, max_position_embeddings=32768, rope_theta=1e6,
+                   sliding_window=None)
+
+    @classmethod
     def mixtral_8x7b(cls): return cls(vocab_size=32000, intermediate_size=14336, num_key_value_heads=8,
                                       max_position_embeddings=32768, rope_theta=1e6, sliding_window=None)
     @classmethod
@@ -121,6 +127,10 @@ class PhiConfig:
                               num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=128)
 
     def head_dim(self) -> int: return self.hidden_size // self.num_attention_heads
+
+    def rotary_dim(self) -> int:
+        """Leading features of each head that are rotated (an even number)."""
+        return int(self.head_dim() * self.partial_rotary_factor) // 2 * 2
 
 
 @dataclasses.dataclass

@@ -37,6 +37,19 @@ class GenerationConfig:
     def beam_search(cls, max_new_tokens: int, num_beams: int):
         return cls(max_new_tokens=max_new_tokens, num_beams=num_beams, do_sample=False)
 
+    # chainable setters (generation.rs:105-121)
+    def with_max_tokens(self, max_new_tokens: int):
+        self.max_new_tokens = int(max_new_tokens)
+        return self
+
+    def with_eos_token(self, eos_token_id: int):
+        self.eos_token_ids = list(self.eos_token_ids) + [int(eos_token_id)]
+        return self
+
+    def with_repetition_penalty(self, penalty: float):
+        self.repetition_penalty = float(penalty)
+        return self
+
 
 class TextGenerator:
     def __init__(self, config: GenerationConfig | None = None):
@@ -45,26 +58,61 @@ class TextGenerator:
     @classmethod
     def new(cls, config): return cls(config)
 
+    # ---- the steps of the pipeline, each on ``logits [B, V]`` (or ``[V]``), returning new logits
+    def apply_repetition_penalty(self, logits: torch.Tensor, generated) -> torch.Tensor:
+        """Scores of tokens already generated are divided by the penalty when positive and
+        multiplied when negative (generation.rs:145-158)."""
+        pen = self.config.repetition_penalty
+        if pen == 1.0 or generated is None:
+            return logits
+        gen = torch.as_tensor(generated, device=logits.device).long()
+        if gen.numel() == 0:
+            return logits
+        flat = logits.dim() == 1
+        lg = (logits.unsqueeze(0) if flat else logits).clone()
+        gen = gen.reshape(lg.shape[0], -1)
+        score = torch.gather(lg, 1, gen)
+        lg.scatter_(1, gen, torch.where(score > 0, score / pen, score * pen))
+        return lg[0] if flat else lg
+
+    def apply_temperature(self, logits: torch.Tensor) -> torch.Tensor:
+        t = self.config.temperature
+        return logits / t if t != 1.0 and t > 0 else logits
+
+    def apply_top_k(self, logits: torch.Tensor) -> torch.Tensor:
+        """Everything below the k-th largest logit becomes -inf."""
+        k = self.config.top_k
+        if k is None or not 0 < k < logits.shape[-1]:
+            return logits
+        kth = torch.topk(logits, k, dim=-1).values[..., -1:]
+        return logits.masked_fill(logits < kth, float("-inf"))
+
+    def apply_top_p(self, logits: torch.Tensor) -> torch.Tensor:
+        """Keeps the smallest set of most likely tokens whose probabilities sum to at least p."""
+        p = self.config.top_p
+        if p is None or not 0.0 < p < 1.0:
+            return logits
+        sl, si = torch.sort(logits, descending=True, dim=-1)
+        probs = torch.softmax(sl, -1)
+        sl = sl.masked_fill(probs.cumsum(-1) - probs > p, float("-inf"))
+        return torch.full_like(logits, float("-inf")).scatter(-1, si, sl)
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        return logits.argmax(-1)
+
     def process_logits(self, logits: torch.Tensor, generated: torch.Tensor | None = None) -> torch.Tensor:
-        """``logits [B, V]`` -> filtered logits (fp32)."""
-        c = self.config
-        logits = logits.float().clone()
-        if c.repetition_penalty != 1.0 and generated is not None and generated.numel():
-            score = torch.gather(logits, 1, generated)
-            score = torch.where(score > 0, score / c.repetition_penalty, score * c.repetition_penalty)
-            logits.scatter_(1, generated, score)
-        if c.temperature != 1.0 and c.temperature > 0:
-            logits = logits / c.temperature
-        if c.top_k is not None and 0 < c.top_k < logits.shape[-1]:
-            kth = torch.topk(logits, c.top_k, dim=-1).values[..., -1:]
-            logits = logits.masked_fill(logits < kth, float("-inf"))
-        if c.top_p is not None and 0.0 < c.top_p < 1.0:
-            sl, si = torch.sort(logits, descending=True, dim=-1)
-            cum = torch.softmax(sl, -1).cumsum(-1)
-            remove = cum - torch.softmax(sl, -1) > c.top_p
-            sl = sl.masked_fill(remove, float("-inf"))
-            logits = torch.full_like(logits, float("-inf")).scatter(1, si, sl)
-        return logits
+        """Repetition penalty -> temperature -> top-k -> top-p on fp32 logits (generation.rs:258-270)."""
+        logits = self.apply_repetition_penalty(logits.float(), generated)
+        return self.apply_top_p(self.apply_top_k(self.apply_temperature(logits)))
+
+    def get_next_token(self, logits, generated=None):
+        """Next token for one sequence: ``logits [V]`` and the tokens generated so far -> int."""
+        lg = torch.as_tensor(logits, dtype=torch.float32).reshape(1, -1)
+        gen = None if generated is None else torch.as_tensor(generated).reshape(1, -1)
+        return int(self.sample(lg, gen)[0])
+
+    def should_stop(self, token: int) -> bool:
+        return int(token) in self.config.eos_token_ids
 
     def sample(self, logits: torch.Tensor, generated=None) -> torch.Tensor:
         logits = self.process_logits(logits, generated)

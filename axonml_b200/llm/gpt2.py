@@ -19,6 +19,7 @@ from ..ops import misc as Mi
 from ..ops.attention import sdpa, sdpa_packed
 from ..ops.linear import linear
 from .config import GPT2Config
+from ._api import ModelApi
 from .hf_loader import LoadStateDict
 
 
@@ -41,6 +42,11 @@ class GPT2Embedding(nn.Module):
         B, S = ids.shape
         x = Mi.embedding(ids, self.wte.weight, pos_weight=self.wpe.weight, seq_len=S, pos0=pos0)
         return self.drop(x)
+
+    def forward_ids(self, input_ids, pos0: int = 0):
+        """Token + position embeddings of integer (or float-typed) ids."""
+        ids = torch.as_tensor(input_ids)
+        return self.forward((ids.unsqueeze(0) if ids.dim() == 1 else ids).long(), pos0)
 
 
 class CausalSelfAttention(nn.Module):
@@ -73,6 +79,19 @@ class CausalSelfAttention(nn.Module):
             k, v = kv_cache.update(k, v)
             o = sdpa(q, k, v, causal=True, dropout_p=drop)
         return self.resid_drop(self.c_proj(o.reshape(B, S, E)))
+
+    def create_causal_mask(self, seq_len: int, device=None) -> torch.Tensor:
+        """Additive mask [seq, seq]: 0 where query i may see key j (j <= i), -inf elsewhere."""
+        m = torch.full((seq_len, seq_len), float("-inf"), device=device)
+        return torch.triu(m, diagonal=1)
+
+    def forward_causal(self, x):
+        """Causal self-attention over a whole sequence (no cache)."""
+        return self.forward(x, None)
+
+    def forward_with_cache(self, x, kv_cache):
+        """Attention of the new positions ``x`` over everything in ``kv_cache`` plus themselves."""
+        return self.forward(x, kv_cache)
 
 
 class FeedForward(nn.Module):
@@ -108,7 +127,24 @@ class TransformerBlock(nn.Module):
         return self.ffn(m), residual
 
 
-class GPT2(nn.Module):
+class _Presets:
+    """``Model.small()`` ... ``Model.tiny()``: the model built from the configuration preset of that name."""
+
+    @classmethod
+    def small(cls): return cls(GPT2Config.small())
+    @classmethod
+    def medium(cls): return cls(GPT2Config.medium())
+    @classmethod
+    def large(cls): return cls(GPT2Config.large())
+    @classmethod
+    def xl(cls): return cls(GPT2Config.xl())
+    @classmethod
+    def tiny(cls): return cls(GPT2Config.tiny())
+
+
+class GPT2(nn.Module, ModelApi, _Presets):
+    ARCH = "gpt2"
+
     def __init__(self, cfg: GPT2Config, device=None, dtype=None):
         super().__init__()
         self.cfg = cfg
@@ -144,8 +180,33 @@ class GPT2(nn.Module):
         h, _ = self.ln_f(delta, residual=residual)
         return h
 
+    def create_kv_cache(self, batch: int, max_seq_len: int | None = None):
+        from .attention import LayerKVCache
+        p = next(self.parameters())
+        return LayerKVCache(self.cfg.n_layer, batch, max_seq_len or self.cfg.n_ctx, self.cfg.n_head, self.cfg.head_dim(),
+                            device=p.device, dtype=p.dtype)
 
-class GPT2LMHead(nn.Module, LoadStateDict):
+    def forward_with_past(self, ids, past=None):
+        """``(hidden states, cache)``: runs ``ids`` after whatever ``past`` (a cache from an earlier
+        call, or ``None`` to start one) already holds."""
+        ids = torch.as_tensor(ids).long()
+        ids = ids.unsqueeze(0) if ids.dim() == 1 else ids
+        if past is None:
+            past = self.create_kv_cache(ids.shape[0])
+        return self.forward(ids, past, past.seq_len()), past
+
+    @classmethod
+    def _config_from_json(cls, j):
+        d = GPT2Config()
+        return GPT2Config(vocab_size=int(j.get("vocab_size", d.vocab_size)), n_ctx=int(j.get("n_positions", j.get("n_ctx", d.n_ctx))),
+                          n_embd=int(j.get("n_embd", d.n_embd)), n_layer=int(j.get("n_layer", d.n_layer)), n_head=int(j.get("n_head", d.n_head)),
+                          layer_norm_eps=float(j.get("layer_norm_epsilon", d.layer_norm_eps)))
+
+
+class GPT2LMHead(nn.Module, LoadStateDict, ModelApi, _Presets):
+    ARCH = "gpt2"
+    _config_from_json = GPT2._config_from_json
+
     """Language-model head tied to the token embedding (``lm_head.weight`` is ``wte``)."""
 
     def __init__(self, cfg: GPT2Config, device=None, dtype=None):
@@ -165,8 +226,14 @@ class GPT2LMHead(nn.Module, LoadStateDict):
         return self
 
     def forward_ids(self, ids, kv_caches=None, pos0: int = 0):
+        """Logits over the padded vocabulary (``forward`` cuts them to ``vocab_size``)."""
+        ids = torch.as_tensor(ids)
+        ids = (ids.unsqueeze(0) if ids.dim() == 1 else ids).long()
         h = self.transformer(ids, kv_caches, pos0)
         return linear(h, self.lm_head_weight)
+
+    def create_kv_cache(self, batch: int, max_seq_len: int | None = None):
+        return self.transformer.create_kv_cache(batch, max_seq_len)
 
     def forward(self, ids, kv_caches=None, pos0: int = 0):
         return self.forward_ids(ids, kv_caches, pos0)[..., : self.cfg.vocab_size]

@@ -96,6 +96,24 @@ class HFLoader:
             self._tensors = out
         return self._tensors
 
+    def cache_dir(self) -> str:
+        """Directory the model's files are (or will be) in."""
+        return self.path
+
+    @property
+    def tensors(self) -> dict:
+        """``{name: tensor}`` of everything loaded so far (empty before ``load_tensors``)."""
+        return self._tensors or {}
+
+    def print_tensor_info(self, limit: int | None = None) -> None:
+        """One line per tensor: name, stored dtype, shape, element count."""
+        names = self.tensor_names()
+        for n in names[:limit]:
+            i = self.tensor_info(n)
+            print(f"{n:60s} {i.dtype:5s} {str(i.shape):24s} {i.numel():>12,d}")
+        total = sum(t.numel() for t in self.load_tensors().values())
+        print(f"{len(names)} tensors, {total:,d} elements")
+
     def tensor_names(self): return list(self.load_tensors())
     def get_tensor(self, name: str): return self.load_tensors().get(name)
 

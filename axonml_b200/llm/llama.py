@@ -23,6 +23,7 @@ from ..ops.attention import sdpa, sdpa_packed
 from ..ops.linear import linear
 from .attention import LayerKVCache
 from .config import LLaMAConfig
+from ._api import ModelApi
 from .hf_loader import LoadStateDict
 
 
@@ -101,6 +102,11 @@ class LLaMAAttention(nn.Module):
         return self.o_proj(o.reshape(B, S, self.nh * self.hd))
 
 
+    def forward_with_cache(self, x, kv_cache, pos0: int | None = None):
+        """Attention over ``x`` appended to ``kv_cache``; positions continue from the cache."""
+        return self.forward(x, kv_cache, kv_cache.seq_len if pos0 is None and kv_cache is not None else (pos0 or 0))
+
+
 class LLaMAMLP(nn.Module):
     def __init__(self, cfg: LLaMAConfig, device=None, dtype=None):
         super().__init__()
@@ -131,8 +137,16 @@ class LLaMADecoderLayer(nn.Module):
         m, residual = self.post_attention_layernorm(attn, residual=residual)
         return self.mlp(m), residual
 
+    def forward_with_cache(self, x, kv_cache, pos0: int | None = None):
+        """The whole layer on a hidden state ``x`` (residual connections included), appending to ``kv_cache``."""
+        p = kv_cache.seq_len if pos0 is None and kv_cache is not None else (pos0 or 0)
+        delta, residual = self.forward(x, None, kv_cache, p)
+        return delta + residual
 
-class LLaMA(nn.Module):
+
+class LLaMA(nn.Module, ModelApi):
+    ARCH = "llama"
+
     def __init__(self, cfg: LLaMAConfig, device=None, dtype=None):
         super().__init__()
         self.cfg = cfg
@@ -162,10 +176,20 @@ class LLaMA(nn.Module):
         h, _ = self.norm(delta, residual=residual)
         return h
 
-    forward_with_cache = forward
+    def create_kv_cache(self, batch: int, max_seq_len: int | None = None):
+        p = next(self.parameters())
+        return LayerKVCache(self.cfg.num_hidden_layers, batch, max_seq_len or self.cfg.max_position_embeddings,
+                            self.cfg.num_key_value_heads, self.cfg.head_dim(), device=p.device, dtype=p.dtype)
+
+    @classmethod
+    def _config_from_json(cls, j):
+        from .hf_loader import parse_llama_config_from_json
+        return parse_llama_config_from_json(j)
 
 
-class LLaMAForCausalLM(nn.Module, LoadStateDict):
+class LLaMAForCausalLM(nn.Module, LoadStateDict, ModelApi):
+    ARCH = "llama"
+
     def __init__(self, cfg: LLaMAConfig, tie_word_embeddings: bool = False, device=None, dtype=None):
         super().__init__()
         self.cfg = cfg
@@ -194,7 +218,10 @@ class LLaMAForCausalLM(nn.Module, LoadStateDict):
     def forward(self, ids, kv_caches=None, pos0: int = 0):
         return linear(self.model(ids, kv_caches, pos0), self.head_weight())
 
-    forward_with_cache = forward
+    @classmethod
+    def _config_from_json(cls, j):
+        from .hf_loader import parse_llama_config_from_json
+        return parse_llama_config_from_json(j)
 
     def enable_context_parallel(self, process_group, form: str = "ulysses"):
         """Shards the sequence over ``process_group``: ``forward_with_loss`` then takes the whole

@@ -10,6 +10,7 @@ from ..ops.attention import sdpa
 from ..ops.linear import linear
 from .attention import LayerKVCache
 from .config import MistralConfig, PhiConfig
+from ._api import ModelApi
 from .hf_loader import LoadStateDict
 from .llama import LLaMAForCausalLM
 
@@ -17,11 +18,18 @@ from .llama import LLaMAForCausalLM
 class MistralForCausalLM(LLaMAForCausalLM):
     """Same decoder as LLaMA; ``cfg.sliding_window`` limits every query to the last W keys."""
 
+    ARCH = "mistral"
+
     def __init__(self, cfg: MistralConfig, **kw):
         super().__init__(cfg, **kw)
 
     @classmethod
     def new(cls, cfg): return cls(cfg)
+
+    @classmethod
+    def _config_from_json(cls, j):
+        from .hf_loader import parse_mistral_config
+        return parse_mistral_config(j)
 
 
 Mistral = MistralForCausalLM
@@ -59,6 +67,9 @@ class PhiAttention(nn.Module):
             k, v = kv_cache.update(k, v)
         return self.dense(sdpa(q, k, v, causal=True).reshape(B, S, self.nh * self.hd))
 
+    def forward_with_cache(self, x, kv_cache, pos0: int | None = None):
+        return self.forward(x, kv_cache, kv_cache.seq_len if pos0 is None and kv_cache is not None else (pos0 or 0))
+
 
 class PhiMLP(nn.Module):
     """fc1 -> GELU -> fc2 (phi.rs ``PhiMLP``); the activation runs in the first GEMM's epilogue."""
@@ -89,8 +100,13 @@ class PhiDecoderLayer(nn.Module):
         x = x + a
         return x + self.mlp(self.post_layernorm(x))
 
+    def forward_with_cache(self, x, kv_cache, pos0: int | None = None):
+        return self.forward(x, kv_cache, kv_cache.seq_len if pos0 is None and kv_cache is not None else (pos0 or 0))
 
-class PhiForCausalLM(nn.Module, LoadStateDict):
+
+class PhiForCausalLM(nn.Module, LoadStateDict, ModelApi):
+    ARCH = "phi"
+
     def __init__(self, cfg: PhiConfig):
         super().__init__()
         self.cfg = cfg
@@ -112,6 +128,25 @@ class PhiForCausalLM(nn.Module, LoadStateDict):
         for i, l in enumerate(self.layers):
             h = l(h, kv_caches[i] if kv_caches is not None else None, pos0)
         return self.lm_head(self.final_layernorm(h))
+
+    @classmethod
+    def with_parallel_attn(cls, cfg: PhiConfig, parallel: bool = True):
+        """Model whose blocks run attention and MLP side by side on the same normalised input
+        (``parallel=True``, Phi-1 / Phi-2) or one after the other."""
+        import dataclasses
+        return cls(dataclasses.replace(cfg, parallel_attn=parallel))
+
+    @classmethod
+    def _config_from_json(cls, j):
+        d = PhiConfig()
+        head = int(j.get("num_attention_heads", d.num_attention_heads))
+        return PhiConfig(vocab_size=int(j.get("vocab_size", d.vocab_size)), hidden_size=int(j.get("hidden_size", d.hidden_size)),
+                         intermediate_size=int(j.get("intermediate_size", d.intermediate_size)),
+                         num_hidden_layers=int(j.get("num_hidden_layers", d.num_hidden_layers)), num_attention_heads=head,
+                         num_key_value_heads=int(j.get("num_key_value_heads") or head),
+                         max_position_embeddings=int(j.get("max_position_embeddings", d.max_position_embeddings)),
+                         layer_norm_eps=float(j.get("layer_norm_eps", d.layer_norm_eps)), rope_theta=float(j.get("rope_theta", d.rope_theta)),
+                         partial_rotary_factor=float(j.get("partial_rotary_factor", d.partial_rotary_factor)))
 
 
 Phi = PhiForCausalLM

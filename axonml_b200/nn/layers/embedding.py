@@ -38,3 +38,11 @@ class Embedding(Module):
             idx = idx.long()
         return _misc.embedding(idx, self.weight,
                                padding_idx=-1 if self.padding_idx is None else self.padding_idx)
+
+    def lookup(self, indices: torch.Tensor) -> torch.Tensor:
+        """``forward`` under the reference's name (embedding.rs:103-150).  An index outside the
+        table raises ``IndexError`` (the reference clamps it to row 0 with a warning)."""
+        idx = indices.long() if indices.is_floating_point() else indices
+        if idx.numel() and (int(idx.max()) >= self.num_embeddings or int(idx.min()) < 0):
+            raise IndexError(f"index out of range for a table of {self.num_embeddings} rows")
+        return self.forward(idx)

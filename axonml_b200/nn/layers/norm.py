@@ -121,6 +121,14 @@ class RMSNorm(Module):
     def forward(self, x, residual=None):
         return _norm.rms_norm(x, self.weight, self.eps, residual=residual)
 
+    def load_weight(self, weight) -> None:
+        """Replaces the scale vector (llama.rs ``RMSNorm::load_weight``)."""
+        w = torch.as_tensor(weight)
+        if w.shape != self.weight.shape:
+            raise ValueError(f"expected shape {tuple(self.weight.shape)}, got {tuple(w.shape)}")
+        with torch.no_grad():
+            self.weight.copy_(w.to(self.weight.dtype))
+
 
 class GroupNorm(Module):
     def __init__(self, num_groups: int, num_channels: int, eps: float = 1e-5, affine: bool = True):

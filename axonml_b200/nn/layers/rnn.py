@@ -30,6 +30,13 @@ class _Cell(Module):
     def _gates(self, x, h):
         return _linear(x, self.weight_ih, self.bias_ih), _linear(h, self.weight_hh, self.bias_hh)
 
+    def forward_step(self, input, hidden):
+        """One time step with an explicit previous state (rnn.rs ``forward_step``): a tensor for
+        RNN / GRU cells, an ``(h, c)`` pair for the LSTM cell.  The feature size is checked."""
+        if input.shape[-1] != self.input_size:
+            raise ValueError(f"{type(self).__name__}: expected input size {self.input_size}, got {input.shape[-1]}")
+        return self.forward(input, hidden)
+
 
 class RNNCell(_Cell):
     GATES = 1

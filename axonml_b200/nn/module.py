@@ -83,6 +83,26 @@ class Module(torch.nn.Module):
     def parameters_list(self) -> list:
         return list(self.parameters())
 
+    def load_weights(self, weights: dict, prefix: str = "") -> int:
+        """Copies ``weights[prefix + name]`` into every parameter and buffer of this module that
+        has an entry (the per-layer ``load_weights`` of the reference's LLaMA blocks,
+        crates/axonml-llm/src/llama.rs).  Returns how many tensors were loaded; a shape that does
+        not match raises ``ValueError`` naming the tensor."""
+        n = 0
+        own = dict(self.named_parameters())
+        own.update(dict(self.named_buffers()))
+        with torch.no_grad():
+            for name, dst in own.items():
+                src = weights.get(prefix + name)
+                if src is None:
+                    continue
+                src = torch.as_tensor(src)
+                if src.shape != dst.shape:
+                    raise ValueError(f"{prefix + name}: expected shape {tuple(dst.shape)}, got {tuple(src.shape)}")
+                dst.copy_(src.to(dst.dtype))
+                n += 1
+        return n
+
 
 class Sequential(torch.nn.Sequential, Module):
     """Ordered container; ``add``/``push`` append with automatic names "0", "1", ..."""
@@ -105,6 +125,9 @@ class Sequential(torch.nn.Sequential, Module):
     def push_named(self, name: str, module: torch.nn.Module) -> None:
         self.add_named(name, module)
 
+    def len(self) -> int:
+        return len(self)
+
     def iter(self) -> Iterator[torch.nn.Module]:
         return iter(self)
 
@@ -126,6 +149,13 @@ class ModuleList(torch.nn.ModuleList, Module):
 
     def get(self, index: int):
         return self[index] if -len(self) <= index < len(self) else None
+
+    def len(self) -> int:
+        return len(self)
+
+    def iter_mut(self):
+        """Modules are mutable objects here: the same iterator as ``iter``."""
+        return iter(self)
 
     def iter(self):
         return iter(self)

@@ -584,3 +584,153 @@ def test_weight_mappers_cover_what_the_models_expect(tmp_path):
     assert llm.MistralAttention is llm.LLaMAAttention and llm.MistralMLP is llm.LLaMAMLP and llm.MistralDecoderLayer is llm.LLaMADecoderLayer
     with pytest.raises(NotImplementedError):
         llm.WeightMapper(1).map_name("x")
+
+
+def test_text_generator_steps():
+    cfg = llm.GenerationConfig.greedy(10).with_max_tokens(7).with_eos_token(2).with_eos_token(9).with_repetition_penalty(2.0)
+    assert (cfg.max_new_tokens, cfg.eos_token_ids, cfg.repetition_penalty, cfg.do_sample) == (7, [2, 9], 2.0, False)
+    g = llm.TextGenerator(cfg)
+    lg = torch.tensor([2.0, -1.0, 4.0, 0.5])
+    out = g.apply_repetition_penalty(lg, [0, 1])
+    assert out.tolist() == [1.0, -2.0, 4.0, 0.5] and lg.tolist() == [2.0, -1.0, 4.0, 0.5]                # the input is left alone
+    assert g.apply_repetition_penalty(lg, []).tolist() == lg.tolist() and g.apply_repetition_penalty(lg, None) is lg
+    assert g.should_stop(9) and not g.should_stop(3) and int(g.argmax(lg)) == 2
+    assert g.get_next_token([1.0, 5.0, 4.0], [1]) == 2                                                  # 5 / 2 < 4
+    t = llm.TextGenerator(llm.GenerationConfig(temperature=0.5, top_k=2, top_p=None))
+    assert t.apply_temperature(lg).tolist() == [4.0, -2.0, 8.0, 1.0]
+    assert t.apply_top_k(lg).tolist() == [2.0, float("-inf"), 4.0, float("-inf")]
+    batch = torch.stack([lg, lg.flip(0)])
+    assert t.apply_top_k(batch).isinf().sum().item() == 4
+    probs = torch.tensor([0.5, 0.3, 0.15, 0.05])
+    p = llm.TextGenerator(llm.GenerationConfig(top_p=0.7))
+    kept = p.apply_top_p(torch.log(probs))
+    assert kept[:2].tolist() == pytest.approx(torch.log(probs[:2]).tolist()) and kept[2:].isinf().all()  # 0.5 + 0.3 reaches 0.7
+    assert not llm.TextGenerator(llm.GenerationConfig(top_p=0.81)).apply_top_p(torch.log(probs))[2].isinf()
+    full = t.process_logits(lg.unsqueeze(0))
+    assert full.shape == (1, 4) and full[0].tolist() == [4.0, float("-inf"), 8.0, float("-inf")]
+    torch.manual_seed(0)
+    s = llm.TextGenerator(llm.GenerationConfig(top_k=1))
+    assert {s.get_next_token([0.1, 3.0, 0.2]) for _ in range(5)} == {1}                                   # sampling from one candidate
+
+
+def test_model_api_methods(tmp_path):
+    torch.manual_seed(0)
+    cfg, ref = _tiny_llama_dir(str(tmp_path / "ck"), dtype=torch.float32)
+    model = llm.LLaMAForCausalLM.from_pretrained(str(tmp_path / "ck"), strict=True)
+    assert model.config() == cfg and not model.training
+    ids = torch.randint(0, cfg.vocab_size, (1, 10))
+    with torch.no_grad():
+        full = model(ids)
+        assert torch.allclose(full, ref.eval()(ids), atol=1e-5)
+        assert torch.equal(model.forward_ids(ids[0].float()), full)                          # 1-D float ids, as the reference passes them
+        cache = model.create_kv_cache(1, 16)
+        a = model.forward_with_cache(ids[:, :6], cache)
+        b = model.forward_with_cache(ids[:, 6:], cache)                                      # positions continue from the cache
+        assert cache.seq_len() == 10 and torch.allclose(torch.cat([a, b], 1), full, atol=1e-4)
+        out = model.generate_greedy(ids[:, :4], max_new_tokens=5)
+        nocache = ids[:, :4]
+        for _ in range(5):
+            nocache = torch.cat([nocache, model(nocache)[:, -1].argmax(-1, keepdim=True)], 1)
+        assert torch.equal(out, nocache)
+        bare = llm.LLaMA.from_pretrained(str(tmp_path / "ck"))
+        assert isinstance(bare, llm.LLaMA) and torch.allclose(bare.forward_ids(ids), model.model(ids), atol=1e-6)
+        layer = model.model.layers[0]
+        x = torch.randn(1, 5, cfg.hidden_size)
+        lc = llm.KVCache(1, 8, cfg.num_key_value_heads, cfg.head_dim())
+        whole = layer.forward_with_cache(x, None)
+        step = torch.cat([layer.forward_with_cache(x[:, :3], lc), layer.forward_with_cache(x[:, 3:], lc)], 1)
+        assert torch.allclose(whole, step, atol=1e-5) and lc.seq_len == 5
+        ac = llm.KVCache(1, 8, cfg.num_key_value_heads, cfg.head_dim())
+        att = layer.self_attn
+        assert torch.allclose(torch.cat([att.forward_with_cache(x[:, :2], ac), att.forward_with_cache(x[:, 2:], ac)], 1), att(x), atol=1e-5)
+    w = {"pre.weight": torch.full((cfg.hidden_size,), 3.0), "other": torch.zeros(1)}
+    assert layer.input_layernorm.load_weights(w, "pre.") == 1 and torch.all(layer.input_layernorm.weight == 3.0)
+    layer.input_layernorm.load_weight(torch.ones(cfg.hidden_size))
+    assert torch.all(layer.input_layernorm.weight == 1.0)
+    with pytest.raises(ValueError):
+        layer.input_layernorm.load_weight(torch.ones(3))
+    src = {f"layers.1.{k}": v.detach().clone() for k, v in model.model.layers[1].named_parameters()}
+    assert layer.load_weights(src, "layers.1.") == 9 and torch.equal(layer.mlp.up_proj.weight, model.model.layers[1].mlp.up_proj.weight)
+    with pytest.raises(ValueError, match="layers.1.mlp.up_proj.weight"):
+        layer.load_weights({"layers.1.mlp.up_proj.weight": torch.zeros(2, 2)}, "layers.1.")
+    m = llm.MistralConfig.mistral_7b_instruct()
+    assert m.sliding_window is None and m.rope_theta == 1e6 and llm.PhiConfig.phi2().rotary_dim() == 32 and llm.PhiConfig.phi1().rotary_dim() == 32
+    pc = llm.PhiConfig.tiny()
+    assert not llm.PhiForCausalLM.with_parallel_attn(pc, False).layers[0].parallel and llm.PhiForCausalLM.with_parallel_attn(pc).layers[0].parallel
+    phi = llm.PhiForCausalLM(pc).eval()
+    pids = torch.randint(0, pc.vocab_size, (1, 8))
+    with torch.no_grad():
+        cache = phi.create_kv_cache(1, 16)
+        stepwise = torch.cat([phi.forward_with_cache(pids[:, :5], cache), phi.forward_with_cache(pids[:, 5:], cache)], 1)
+        assert torch.allclose(stepwise, phi.forward_ids(pids), atol=1e-4)
+
+
+def test_gpt2_and_bert_api_methods():
+    torch.manual_seed(0)
+    tiny = llm.GPT2LMHead.tiny().eval()
+    assert tiny.config() == llm.GPT2Config.tiny() and isinstance(llm.GPT2.tiny(), llm.GPT2) and callable(llm.GPT2.small) and callable(llm.GPT2LMHead.xl)
+    ids = torch.randint(0, tiny.cfg.vocab_size, (1, 9))
+    with torch.no_grad():
+        full = tiny(ids)
+        h1, past = tiny.transformer.forward_with_past(ids[:, :4])
+        h2, past = tiny.transformer.forward_with_past(ids[:, 4:], past)
+        assert past.seq_len() == 9 and torch.allclose(torch.cat([h1, h2], 1), tiny.transformer(ids), atol=1e-4)
+        cache = tiny.create_kv_cache(1, 16)
+        stepwise = torch.cat([tiny.forward_with_cache(ids[:, :5], cache), tiny.forward_with_cache(ids[:, 5:], cache)], 1)
+        assert torch.allclose(stepwise, full, atol=1e-4)
+        greedy = tiny.generate_greedy(ids[:, :3], 4)
+        ref = ids[:, :3]
+        for _ in range(4):
+            ref = torch.cat([ref, tiny(ref)[:, -1].argmax(-1, keepdim=True)], 1)
+        assert torch.equal(greedy, ref)
+        emb = tiny.transformer.wte
+        assert torch.equal(emb.forward_ids(ids[0].float()), emb(ids))
+        att = tiny.transformer.blocks[0].attention
+        x = torch.randn(1, 6, tiny.cfg.n_embd)
+        kc = llm.KVCache(1, 8, tiny.cfg.n_head, tiny.cfg.head_dim())
+        parts = torch.cat([att.forward_with_cache(x[:, :4], kc), att.forward_with_cache(x[:, 4:], kc)], 1)
+        assert torch.allclose(parts, att.forward_causal(x), atol=1e-5)
+        m = att.create_causal_mask(4)
+        assert m.shape == (4, 4) and torch.all(m.tril() == 0) and torch.isinf(m[0, 1]) and m[0, 1] < 0
+    cfg = llm.BertConfig(vocab_size=40, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, intermediate_size=32,
+                         max_position_embeddings=12, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    bert = llm.Bert(cfg).eval()
+    bids = torch.randint(0, 40, (2, 5))
+    with torch.no_grad():
+        seq, pooled = bert.forward_with_pooling(bids)
+        assert seq.shape == (2, 5, 16) and pooled.shape == (2, 16) and torch.equal(bert.forward_ids(bids.float()), seq)
+        nop = llm.Bert.with_pooler(cfg, False)
+        assert nop.pooler is None and nop(bids)[1] is None and not any("pooler" in k for k, _ in nop.named_parameters())
+        with pytest.raises(ValueError):
+            nop.forward_with_pooling(bids)
+        clf = llm.BertForSequenceClassification(cfg, 3).eval()
+        assert torch.equal(clf.forward_classification(bids), clf(bids)) and clf(bids).shape == (2, 3)
+        mlm = llm.BertForMaskedLM(cfg).eval()
+        assert torch.equal(mlm.forward_mlm(bids), mlm(bids)) and mlm.config() is cfg
+
+
+def test_loader_reports_and_embedding_lookup(tmp_path, capsys):
+    cfg, _ = _tiny_llama_dir(str(tmp_path / "ck"), dtype=torch.float16)
+    loader = llm.HFLoader.from_local(str(tmp_path / "ck"))
+    assert loader.cache_dir() == str(tmp_path / "ck") and loader.tensors == {}
+    loader.load_tensors()
+    assert len(loader.tensors) == 22
+    loader.print_tensor_info(limit=2)
+    out = capsys.readouterr().out.splitlines()
+    assert len(out) == 3 and "F16" in out[0] and out[2].startswith("22 tensors, ")
+    from axonml_b200 import nn
+    e = nn.Embedding(10, 4)
+    assert torch.equal(e.lookup(torch.tensor([[1.0, 2.0]])), e(torch.tensor([[1, 2]])))
+    with pytest.raises(IndexError):
+        e.lookup(torch.tensor([10]))
+    cell = nn.GRUCell(3, 5)
+    h = torch.zeros(2, 5)
+    assert torch.equal(cell.forward_step(torch.ones(2, 3), h), cell(torch.ones(2, 3), h))
+    with pytest.raises(ValueError, match="expected input size 3, got 4"):
+        cell.forward_step(torch.ones(2, 4), h)
+    lc = nn.LSTMCell(3, 5)
+    hh, cc = lc.forward_step(torch.ones(2, 3), (h, h))
+    assert hh.shape == cc.shape == (2, 5)
+    seq = nn.Sequential(nn.Linear(2, 2), nn.ReLU())
+    ml = nn.ModuleList([nn.Linear(2, 2)])
+    assert seq.len() == 2 and ml.len() == 1 and list(ml.iter_mut())[0] is ml[0]
