@@ -16,6 +16,13 @@ class _Synthetic(Dataset):
 
     def len(self) -> int: return self.n
     def num_classes(self) -> int: return self.classes
+    def sample_rate(self) -> int: return self.sr
+
+    @classmethod
+    def new(cls, num_samples, sample_rate, duration, num_classes):
+        """The reference's argument order: size, sample rate, seconds per clip, classes."""
+        return cls(num_samples, num_classes, sample_rate, duration)
+
     def _wave(self, label, g): raise NotImplementedError
 
     def get(self, i: int):
@@ -28,6 +35,14 @@ class SyntheticCommandDataset(_Synthetic):
     def __init__(self, num_samples=1000, num_classes=10, sample_rate=16000, duration=1.0, seed=42):
         super().__init__(num_samples, num_classes, sample_rate, duration, seed)
 
+    # sizes of the reference's presets (datasets.rs:105-119)
+    @classmethod
+    def small(cls): return cls.new(100, 16000, 0.5, 10)
+    @classmethod
+    def medium(cls): return cls.new(1000, 16000, 0.5, 10)
+    @classmethod
+    def large(cls): return cls.new(10000, 16000, 0.5, 35)
+
     def _wave(self, label, g):
         t = torch.arange(self.len_s) / self.sr
         f = 200.0 + 80.0 * label
@@ -39,6 +54,12 @@ class SyntheticMusicDataset(_Synthetic):
     def __init__(self, num_samples=500, num_classes=5, sample_rate=22050, duration=1.0, seed=42):
         super().__init__(num_samples, num_classes, sample_rate, duration, seed)
 
+    @classmethod
+    def small(cls): return cls.new(100, 22050, 1.0, 5)
+    @classmethod
+    def medium(cls): return cls.new(500, 22050, 2.0, 10)
+    def num_genres(self) -> int: return self.classes
+
     def _wave(self, label, g):
         t = torch.arange(self.len_s) / self.sr
         base = 110.0 * (1 + label)
@@ -48,7 +69,13 @@ class SyntheticMusicDataset(_Synthetic):
 
 class SyntheticSpeakerDataset(_Synthetic):
     def __init__(self, num_samples=500, num_speakers=8, sample_rate=16000, duration=1.0, seed=42):
-        super().__init__(num_samples, num_speakers, sample_rate, duration, seed)
+        super().__init__(num_samples, max(num_speakers, 2), sample_rate, duration, seed)
+
+    @classmethod
+    def small(cls): return cls.new(100, 16000, 0.5, 5)
+    @classmethod
+    def medium(cls): return cls.new(500, 16000, 1.0, 20)
+    def num_speakers(self) -> int: return self.classes
 
     def _wave(self, label, g):
         t = torch.arange(self.len_s) / self.sr

@@ -99,7 +99,13 @@ class NormalizeAudio(Transform):
 
 
 class TrimSilence(Transform):
-    def __init__(self, threshold_db: float = -40.0): self.thr = 10 ** (threshold_db / 20.0)
+    def __init__(self, threshold_db: float = -40.0): self.threshold_db, self.thr = threshold_db, 10 ** (threshold_db / 20.0)
+    @classmethod
+    def new(cls, threshold_db: float): return cls(threshold_db)
+    @classmethod
+    def default_threshold(cls):
+        """-60 dB below the clip's peak."""
+        return cls(-60.0)
     def apply(self, x):
         idx = (x.abs() > self.thr * x.abs().max().clamp_min(1e-12)).nonzero()
         if idx.numel() == 0:

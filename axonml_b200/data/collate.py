@@ -28,4 +28,8 @@ class DefaultCollate(Collate):
 
 class StackCollate(Collate):
     def __init__(self, dim: int = 0): self.dim = dim
+    @classmethod
+    def new(cls): return cls(0)
+    @classmethod
+    def with_dim(cls, dim: int): return cls(dim)
     def collate(self, samples): return torch.stack(list(samples), self.dim)

@@ -20,6 +20,10 @@ class Batch:
     targets: torch.Tensor
     size: int
 
+    def len(self) -> int: return self.size
+    def __len__(self) -> int: return self.size
+    def is_empty(self) -> bool: return self.size == 0
+
     def to(self, device, non_blocking: bool = True) -> "Batch":
         return Batch(self.data.to(device, non_blocking=non_blocking),
                      self.targets.to(device, non_blocking=non_blocking), self.size)
@@ -47,6 +51,8 @@ class DataLoader:
         return n // self.batch_size if self._drop_last else (n + self.batch_size - 1) // self.batch_size
 
     def len(self) -> int: return len(self)
+    def is_empty(self) -> bool: return len(self) == 0
+    def dataset_len(self) -> int: return self.dataset.len()
 
     def _batches(self):
         base = self._sampler or (RandomSampler(self.dataset.len()) if self._shuffle else SequentialSampler(self.dataset.len()))

@@ -21,6 +21,12 @@ class TensorDataset(Dataset):
 
     @classmethod
     def new(cls, data, targets): return cls(data, targets)
+
+    @classmethod
+    def from_data(cls, data: torch.Tensor):
+        """Unlabelled data: every target is 0 (dataset.rs:66-70)."""
+        return cls(data, torch.zeros(data.shape[0]))
+
     def len(self) -> int: return self.data.shape[0]
     def get(self, index: int): return self.data[index], self.targets[index]
 

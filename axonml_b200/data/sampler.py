@@ -91,6 +91,9 @@ class BatchSampler(Sampler):
         n = len(self.sampler)
         return n // self.batch_size if self.drop_last else math.ceil(n / self.batch_size)
 
+    def len(self) -> int: return len(self)
+    def is_empty(self) -> bool: return len(self) == 0
+
 
 class DistributedSampler(Sampler):
     def __init__(self, n: int, world_size: int, rank: int, shuffle: bool = True, seed: int = 0,

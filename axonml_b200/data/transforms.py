@@ -13,7 +13,11 @@ class Compose(Transform):
     def __init__(self, transforms): self.transforms = list(transforms)
     @classmethod
     def new(cls, transforms): return cls(transforms)
+    @classmethod
+    def empty(cls): return cls([])
     def add(self, t): self.transforms.append(t); return self
+    def len(self) -> int: return len(self.transforms)
+    def is_empty(self) -> bool: return not self.transforms
     def apply(self, x):
         for t in self.transforms:
             x = t(x)
@@ -30,6 +34,10 @@ class Normalize(Transform):
     def new(cls, mean, std): return cls(mean, std)
     @classmethod
     def standard(cls): return cls(0.0, 1.0)
+    @classmethod
+    def zero_centered(cls):
+        """[0, 1] -> [-1, 1]: mean 0.5, std 0.5."""
+        return cls(0.5, 0.5)
     def apply(self, x):
         m, s = self.mean, self.std
         if isinstance(m, (list, tuple)):        # per-channel statistics: broadcast over [C, H, W]
@@ -46,6 +54,10 @@ class RandomNoise(Transform):
 
 class RandomCrop(Transform):
     def __init__(self, size): self.size = (size, size) if isinstance(size, int) else tuple(size)
+    @classmethod
+    def new(cls, size): return cls(size)
+    @classmethod
+    def new_2d(cls, height: int, width: int): return cls((height, width))
     def apply(self, x):
         h, w = x.shape[-2:]
         th, tw = self.size
@@ -56,6 +68,16 @@ class RandomCrop(Transform):
 
 class RandomFlip(Transform):
     def __init__(self, dim: int = -1, p: float = 0.5): self.dim, self.p = dim, p
+    @classmethod
+    def new(cls, dim: int, probability: float): return cls(dim, probability)
+    @classmethod
+    def horizontal(cls):
+        """Mirror left-right (the last dimension) half of the time."""
+        return cls(-1, 0.5)
+    @classmethod
+    def vertical(cls):
+        """Mirror top-bottom (the second to last dimension) half of the time."""
+        return cls(-2, 0.5)
     def apply(self, x): return x.flip(self.dim) if float(torch.rand(())) < self.p else x
 
 
@@ -66,6 +88,12 @@ class Scale(Transform):
 
 class Clamp(Transform):
     def __init__(self, lo: float, hi: float): self.lo, self.hi = lo, hi
+    @classmethod
+    def new(cls, lo: float, hi: float): return cls(lo, hi)
+    @classmethod
+    def zero_one(cls): return cls(0.0, 1.0)
+    @classmethod
+    def symmetric(cls): return cls(-1.0, 1.0)
     def apply(self, x): return x.clamp(self.lo, self.hi)
 
 

@@ -14,7 +14,21 @@ class TextDataset(Dataset):
 
     @classmethod
     def new(cls, texts, labels, vocab, tokenizer, max_len): return cls(texts, labels, vocab, tokenizer, max_len)
+
+    @classmethod
+    def from_samples(cls, samples, tokenizer, min_freq: int = 1, max_length: int = 64):
+        """Dataset from ``(text, label)`` pairs: the vocabulary holds the special tokens and then
+        every token seen at least ``min_freq`` times, most frequent first (ties alphabetically)."""
+        import collections
+        freq = collections.Counter(t for text, _ in samples for t in tokenizer(text))
+        vocab = Vocab.with_special_tokens()
+        for tok, _ in sorted(((t, c) for t, c in freq.items() if c >= min_freq), key=lambda tc: (-tc[1], tc[0])):
+            vocab.add_token(tok)
+        return cls([t for t, _ in samples], [l for _, l in samples], vocab, tokenizer, max_length)
+
     def len(self) -> int: return len(self.texts)
+    def num_classes(self) -> int: return (max(self.labels) + 1) if self.labels else 0
+    def max_length(self) -> int: return self.max_len
 
     def get(self, i: int):
         ids = self.vocab.encode(self.tokenizer(self.texts[i]))[: self.max_len]
@@ -31,7 +45,13 @@ class LanguageModelDataset(Dataset):
 
     @classmethod
     def from_text(cls, text: str, vocab: Vocab, tokenizer, seq_len: int):
-        return cls(vocab.encode(tokenizer(text)), seq_len)
+        ds = cls(vocab.encode(tokenizer(text)), seq_len)
+        ds._vocab = vocab
+        return ds
+
+    def vocab(self):
+        """The vocabulary the token stream was encoded with (``None`` for a dataset built from ids)."""
+        return getattr(self, "_vocab", None)
 
     def len(self) -> int: return max(0, (self.tokens.numel() - self.seq_len - 1) // self.stride + 1)
 
@@ -52,6 +72,13 @@ class SyntheticSentimentDataset(Dataset):
 
     @classmethod
     def new(cls, num_samples, seq_len, vocab_size): return cls(num_samples, seq_len, vocab_size)
+    # sizes of the reference's presets (datasets/mod.rs:234-248)
+    @classmethod
+    def small(cls): return cls(100, 32, 1000)
+    @classmethod
+    def train(cls): return cls(10000, 64, 10000)
+    @classmethod
+    def test(cls): return cls(2000, 64, 10000)
     def len(self) -> int: return self.data.shape[0]
     def get(self, i): return self.data[i], self.labels[i]
 

@@ -12,24 +12,34 @@ class Tokenizer:
 
 
 class WhitespaceTokenizer(Tokenizer):
-    def __init__(self, lowercase: bool = False): self.lowercase = lowercase
+    def __init__(self, lowercase: bool = False): self._lowercase = lowercase
     @classmethod
     def new(cls): return cls()
-    def tokenize(self, text): return (text.lower() if self.lowercase else text).split()
+    @classmethod
+    def lowercase(cls):
+        """Tokenizer that lower-cases its input first."""
+        return cls(True)
+    def tokenize(self, text): return (text.lower() if self._lowercase else text).split()
 
 
 class CharTokenizer(Tokenizer):
     def __init__(self, include_whitespace: bool = True): self.include_whitespace = include_whitespace
     @classmethod
     def new(cls): return cls()
+    @classmethod
+    def no_whitespace(cls):
+        """Tokenizer that drops blanks instead of emitting them as tokens."""
+        return cls(False)
     def tokenize(self, text): return [c for c in text if self.include_whitespace or not c.isspace()]
 
 
 class WordPunctTokenizer(Tokenizer):
-    def __init__(self, lowercase: bool = False): self.lowercase = lowercase
+    def __init__(self, lowercase: bool = False): self._lowercase = lowercase
     @classmethod
     def new(cls): return cls()
-    def tokenize(self, text): return re.findall(r"\w+|[^\w\s]", text.lower() if self.lowercase else text)
+    @classmethod
+    def lowercase(cls): return cls(True)
+    def tokenize(self, text): return re.findall(r"\w+|[^\w\s]", text.lower() if self._lowercase else text)
 
 
 class NGramTokenizer(Tokenizer):
@@ -76,6 +86,10 @@ class BasicBPETokenizer(Tokenizer):
         toks = {t for w in words for t in w}
         self.vocab = {t: i for i, t in enumerate(sorted(toks))}
 
+    def get_vocab(self) -> list:
+        """The learned symbols in index order."""
+        return sorted(self.vocab, key=self.vocab.get)
+
     @staticmethod
     def _merge(w, pair):
         out, i = [], 0
@@ -104,6 +118,10 @@ class UnigramTokenizer(Tokenizer):
     def __init__(self, vocab: dict | None = None): self.vocab = dict(vocab or {})
     @classmethod
     def new(cls, vocab): return cls(vocab)
+    @classmethod
+    def from_tokens(cls, tokens):
+        """Vocabulary of the given pieces, all with the same score."""
+        return cls({t: 1.0 for t in tokens})
 
     def train(self, corpus, vocab_size: int) -> None:
         c = collections.Counter()

@@ -48,6 +48,21 @@ class Vocab:
             self.idx_to_token.append(token)
         return self.token_to_idx[token]
 
+    def add_special_tokens(self, tokens) -> None:
+        for t in tokens:
+            self.add_token(t)
+
+    def set_unk_token(self, token: str) -> None:
+        """Adds ``token`` (if new) and makes it what unknown words map to."""
+        self.unk_index = self.add_token(token)
+        self.unk_token = token
+
+    def set_pad_token(self, token: str) -> None:
+        self.add_token(token)
+        self.pad_token = token
+
+    def tokens(self) -> list: return list(self.idx_to_token)
+    def is_empty(self) -> bool: return not self.idx_to_token
     def len(self) -> int: return len(self.idx_to_token)
     def __len__(self) -> int: return len(self.idx_to_token)
     def contains(self, token: str) -> bool: return token in self.token_to_idx
@@ -58,7 +73,7 @@ class Vocab:
     def encode(self, tokens) -> list: return [self.token_to_index(t) for t in tokens]
     def decode(self, indices) -> list: return [self.index_to_token(int(i)) for i in indices]
     def encode_tensor(self, tokens) -> torch.Tensor: return torch.tensor(self.encode(tokens), dtype=torch.long)
-    def pad_index(self): return self.token_to_idx.get(PAD)
+    def pad_index(self): return self.token_to_idx.get(getattr(self, "pad_token", PAD))
     def unk_index_(self): return self.unk_index
     def bos_index(self): return self.token_to_idx.get(BOS)
     def eos_index(self): return self.token_to_idx.get(EOS)

@@ -34,11 +34,19 @@ class MNIST(Dataset):
             raise FileNotFoundError(os.path.join(root, n))
         self.images = torch.from_numpy(read_idx(find(img)).copy()).float().div_(255.0).unsqueeze(1)
         self.labels = torch.from_numpy(read_idx(find(lab)).copy()).long()
+        self.train = train
+
+    CLASSES = [str(d) for d in range(10)]
 
     @classmethod
     def new(cls, root, train=True): return cls(root, train)
     def len(self) -> int: return self.images.shape[0]
     def get(self, i): return self.images[i], self.labels[i]
+    def is_train(self) -> bool: return self.train
+    def num_classes(self) -> int: return 10
+    def image_size(self) -> tuple: return (28, 28)
+    @classmethod
+    def class_names(cls) -> list: return list(cls.CLASSES)
 
 
 class FashionMNIST(MNIST):
@@ -53,9 +61,19 @@ class CIFAR10(Dataset):
         raw = np.concatenate([np.fromfile(os.path.join(root, f), dtype=np.uint8) for f in files]).reshape(-1, self.REC)
         self.labels = torch.from_numpy(raw[:, self.REC - 3073].astype(np.int64))
         self.images = torch.from_numpy(raw[:, -3072:].copy()).float().div_(255.0).view(-1, 3, 32, 32)
+        self.train = train
 
+    CLASSES = ["airplane", "automobile", "bird", "cat", "deer", "dog", "frog", "horse", "ship", "truck"]
+
+    @classmethod
+    def new(cls, root, train=True): return cls(root, train)
     def len(self) -> int: return self.images.shape[0]
     def get(self, i): return self.images[i], self.labels[i]
+    def is_train(self) -> bool: return self.train
+    def num_classes(self) -> int: return self.NUM_FINE
+    def image_size(self) -> tuple: return (3, 32, 32)
+    @classmethod
+    def class_names(cls) -> list: return list(cls.CLASSES)
 
 
 class CIFAR100(CIFAR10):
@@ -63,8 +81,23 @@ class CIFAR100(CIFAR10):
 
     def __init__(self, root: str, train: bool = True):
         raw = np.fromfile(os.path.join(root, "train.bin" if train else "test.bin"), dtype=np.uint8).reshape(-1, self.REC)
+        self.coarse_labels = torch.from_numpy(raw[:, 0].astype(np.int64))        # the 20 superclasses
         self.labels = torch.from_numpy(raw[:, 1].astype(np.int64))
         self.images = torch.from_numpy(raw[:, 2:].copy()).float().div_(255.0).view(-1, 3, 32, 32)
+        self.train = train
+
+    CLASSES = None                                    # the 100 fine names are not part of the binary files
+
+    @classmethod
+    def class_names(cls): return None
+    def num_fine_classes(self) -> int: return 100
+    def num_coarse_classes(self) -> int: return 20
+
+    def get_with_coarse(self, i: int):
+        """``(image, fine label, coarse label)``, or ``None`` past the end."""
+        if not 0 <= i < self.len():
+            return None
+        return self.images[i], self.labels[i], self.coarse_labels[i]
 
 
 class _SyntheticImages(Dataset):
@@ -88,12 +121,32 @@ class SyntheticMNIST(_SyntheticImages):
     def __init__(self, num_samples: int = 1000, seed: int = 42): super().__init__(num_samples, (1, 28, 28), 10, seed)
     @classmethod
     def new(cls, num_samples=1000): return cls(num_samples)
+    # sizes of the reference's presets (mnist.rs:285-299)
+    @classmethod
+    def small(cls): return cls(100)
+    @classmethod
+    def train(cls): return cls(60000)
+    @classmethod
+    def test(cls): return cls(10000)
 
 
 class SyntheticCIFAR(_SyntheticImages):
     def __init__(self, num_samples: int = 1000, num_classes: int = 10, seed: int = 42): super().__init__(num_samples, (3, 32, 32), num_classes, seed)
     @classmethod
     def new(cls, num_samples=1000): return cls(num_samples)
+    @classmethod
+    def cifar10(cls, size: int): return cls(size, 10)
+    @classmethod
+    def cifar100(cls, size: int): return cls(size, 100)
+    @classmethod
+    def small(cls): return cls(100, 10)
+    @classmethod
+    def train(cls): return cls(50000, 10)
+    @classmethod
+    def test(cls): return cls(10000, 10)
+    def class_names(self):
+        """The CIFAR-10 names for a ten-class set, ``None`` otherwise."""
+        return CIFAR10.class_names() if self.classes == 10 else None
 
 
 class SyntheticImageNet(_SyntheticImages):

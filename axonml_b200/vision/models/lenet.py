@@ -47,6 +47,10 @@ class SimpleCNN(nn.Module):
         side = input_size // 4
         self.fc1 = nn.Linear(64 * side * side, 128)
         self.fc2 = nn.Linear(128, num_classes)
+        self._in_channels, self._num_classes = in_channels, num_classes
+
+    def input_channels(self) -> int: return self._in_channels
+    def num_classes(self) -> int: return self._num_classes
 
     @classmethod
     def new(cls, in_channels=1, num_classes=10): return cls(in_channels, num_classes)

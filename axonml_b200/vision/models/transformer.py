@@ -17,11 +17,12 @@ class _MHA(nn.Module):
         self.q_proj, self.k_proj = nn.Linear(d_model, d_model), nn.Linear(d_model, d_model)
         self.v_proj, self.out_proj = nn.Linear(d_model, d_model), nn.Linear(d_model, d_model)
 
-    def forward(self, q, k, v, causal=False):
+    def forward(self, q, k, v, causal=False, mask=None):
+        """``mask``: attend where non-zero / True; broadcasts against [batch, heads, query, key]."""
         B, Sq, E = q.shape
         Sk = k.shape[1]
         o = sdpa(self.q_proj(q).view(B, Sq, self.h, self.hd), self.k_proj(k).view(B, Sk, self.h, self.hd),
-                 self.v_proj(v).view(B, Sk, self.h, self.hd), causal=causal)
+                 self.v_proj(v).view(B, Sk, self.h, self.hd), mask=mask, causal=causal)
         return self.out_proj(o.reshape(B, Sq, E))
 
 
@@ -60,11 +61,18 @@ class TransformerEncoderLayer(nn.Module):
         self.fc1 = nn.Linear(d_model, dim_feedforward, activation=activation)
         self.fc2 = nn.Linear(dim_feedforward, d_model)
         self.drop = nn.Dropout(dropout)
+        self._d_model = d_model
+
+    def d_model(self) -> int: return self._d_model
+
+    def forward_with_mask(self, x, src_mask=None):
+        """The layer with an attention mask over the keys (non-zero = may be attended)."""
+        h = self.norm1(x)
+        x = x + self.drop(self.attn(h, h, h, mask=src_mask))
+        return x + self.drop(self.fc2(self.fc1(self.norm2(x))))
 
     def forward(self, x):
-        h = self.norm1(x)
-        x = x + self.drop(self.attn(h, h, h))
-        return x + self.drop(self.fc2(self.fc1(self.norm2(x))))
+        return self.forward_with_mask(x, None)
 
 
 class TransformerDecoderLayer(nn.Module):
@@ -76,11 +84,16 @@ class TransformerDecoderLayer(nn.Module):
         self.fc2 = nn.Linear(dim_feedforward, d_model)
         self.drop = nn.Dropout(dropout)
 
-    def forward(self, x, memory):
+    def forward_with_memory(self, x, memory, tgt_mask=None, memory_mask=None):
+        """Decoder layer with explicit masks: ``tgt_mask`` over the target's own positions (causal
+        when ``None``), ``memory_mask`` over the encoder output."""
         h = self.norm1(x)
-        x = x + self.drop(self.self_attn(h, h, h, causal=True))
-        x = x + self.drop(self.cross_attn(self.norm2(x), memory, memory))
+        x = x + self.drop(self.self_attn(h, h, h, causal=tgt_mask is None, mask=tgt_mask))
+        x = x + self.drop(self.cross_attn(self.norm2(x), memory, memory, mask=memory_mask))
         return x + self.drop(self.fc2(self.fc1(self.norm3(x))))
+
+    def forward(self, x, memory):
+        return self.forward_with_memory(x, memory)
 
 
 class TransformerEncoder(nn.Module):
@@ -89,10 +102,13 @@ class TransformerEncoder(nn.Module):
         self.layers = nn.ModuleList([TransformerEncoderLayer(d_model, nhead, dim_feedforward, dropout) for _ in range(num_layers)])
         self.norm = nn.LayerNorm(d_model)
 
-    def forward(self, x):
+    def forward_with_mask(self, x, mask=None):
         for l in self.layers:
-            x = l(x)
+            x = l.forward_with_mask(x, mask)
         return self.norm(x)
+
+    def forward(self, x):
+        return self.forward_with_mask(x, None)
 
 
 class TransformerDecoder(nn.Module):
@@ -101,10 +117,13 @@ class TransformerDecoder(nn.Module):
         self.layers = nn.ModuleList([TransformerDecoderLayer(d_model, nhead, dim_feedforward, dropout) for _ in range(num_layers)])
         self.norm = nn.LayerNorm(d_model)
 
-    def forward(self, x, memory):
+    def forward_with_memory(self, x, memory, tgt_mask=None, memory_mask=None):
         for l in self.layers:
-            x = l(x, memory)
+            x = l.forward_with_memory(x, memory, tgt_mask, memory_mask)
         return self.norm(x)
+
+    def forward(self, x, memory):
+        return self.forward_with_memory(x, memory)
 
 
 class Transformer(nn.Module):
@@ -113,7 +132,16 @@ class Transformer(nn.Module):
         self.encoder = TransformerEncoder(d_model, nhead, num_encoder_layers, dim_feedforward, dropout)
         self.decoder = TransformerDecoder(d_model, nhead, num_decoder_layers, dim_feedforward, dropout)
 
-    def forward(self, src, tgt): return self.decoder(tgt, self.encoder(src))
+        self._d_model = d_model
+
+    def d_model(self) -> int: return self._d_model
+
+    def forward_full(self, src, tgt, src_mask=None, tgt_mask=None, memory_mask=None):
+        """Encoder then decoder with every mask explicit (transformer.rs:482-493)."""
+        memory = self.encoder.forward_with_mask(src, src_mask)
+        return self.decoder.forward_with_memory(tgt, memory, tgt_mask, memory_mask)
+
+    def forward(self, src, tgt): return self.forward_full(src, tgt)
 
 
 class VisionTransformer(nn.Module):

@@ -66,6 +66,11 @@ class VggClassifier(nn.Sequential):
     @classmethod
     def new(cls, num_classes: int): return cls(num_classes)
 
+    @classmethod
+    def with_input_size(cls, input_features: int, num_classes: int):
+        """Classifier for a trunk whose flattened output has ``input_features`` values."""
+        return cls(num_classes, input_features)
+
 
 class VGG(nn.Module):
     def __init__(self, depth: int = 16, num_classes: int = 1000, batch_norm: bool = False, in_channels: int = 3):
@@ -76,6 +81,12 @@ class VGG(nn.Module):
 
     def forward(self, x):
         return self.classifier(self.avgpool(self.features(x)).flatten(1))
+
+
+# the constructors under the class as well (vgg.rs ``VGG::vgg11`` ... ``VGG::vgg19_bn``)
+for _depth in (11, 13, 16, 19):
+    setattr(VGG, f"vgg{_depth}", classmethod(lambda cls, num_classes=1000, _d=_depth: cls(_d, num_classes)))
+    setattr(VGG, f"vgg{_depth}_bn", classmethod(lambda cls, num_classes=1000, _d=_depth: cls(_d, num_classes, True)))
 
 
 def vgg11(num_classes=1000): return VGG(11, num_classes)

@@ -15,14 +15,24 @@ def _u(x, s): return x.squeeze(0) if s else x
 
 
 class Resize(Transform):
-    def __init__(self, size): self.size = (size, size) if isinstance(size, int) else tuple(size)
+    def __init__(self, size, width: int | None = None):
+        self.size = (size, width) if width is not None else (size, size) if isinstance(size, int) else tuple(size)
+    @classmethod
+    def new(cls, height: int, width: int): return cls((height, width))
+    @classmethod
+    def square(cls, size: int): return cls((size, size))
     def apply(self, x):
         y, s = _b(x)
         return _u(F.interpolate(y.float(), size=self.size, mode="bilinear", align_corners=False), s)
 
 
 class CenterCrop(Transform):
-    def __init__(self, size): self.size = (size, size) if isinstance(size, int) else tuple(size)
+    def __init__(self, size, width: int | None = None):
+        self.size = (size, width) if width is not None else (size, size) if isinstance(size, int) else tuple(size)
+    @classmethod
+    def new(cls, height: int, width: int): return cls((height, width))
+    @classmethod
+    def square(cls, size: int): return cls((size, size))
     def apply(self, x):
         h, w = x.shape[-2:]
         th, tw = self.size
@@ -31,18 +41,49 @@ class CenterCrop(Transform):
 
 
 class RandomHorizontalFlip(Transform):
-    def __init__(self, p: float = 0.5): self.p = p
+    def __init__(self, p: float = 0.5): self.p = min(max(float(p), 0.0), 1.0)
+    @classmethod
+    def new(cls): return cls(0.5)
+    @classmethod
+    def with_probability(cls, probability: float):
+        """Flip with this probability (clamped to [0, 1])."""
+        return cls(probability)
     def apply(self, x): return x.flip(-1) if float(torch.rand(())) < self.p else x
 
 
 class RandomVerticalFlip(Transform):
-    def __init__(self, p: float = 0.5): self.p = p
+    def __init__(self, p: float = 0.5): self.p = min(max(float(p), 0.0), 1.0)
+    @classmethod
+    def new(cls): return cls(0.5)
+    @classmethod
+    def with_probability(cls, probability: float):
+        """Flip with this probability (clamped to [0, 1])."""
+        return cls(probability)
     def apply(self, x): return x.flip(-2) if float(torch.rand(())) < self.p else x
 
 
 class RandomRotation(Transform):
-    def __init__(self, degrees: float): self.degrees = degrees
+    """Two forms: ``RandomRotation(degrees)`` turns by a uniformly drawn angle in [-degrees, degrees]
+    (bilinear resampling); ``RandomRotation.new()`` / ``with_angles([...])`` picks one of the
+    quarter turns 0 / 90 / 180 / 270 and rotates exactly, as the reference does
+    (transforms.rs:391-470)."""
+
+    def __init__(self, degrees: float = 0.0, angles=None):
+        self.degrees, self.angles = degrees, angles
+
+    @classmethod
+    def new(cls): return cls(0.0, [0, 90, 180, 270])
+
+    @classmethod
+    def with_angles(cls, angles):
+        """Quarter turns to choose from; anything else in the list is dropped (an empty choice means no rotation)."""
+        valid = [int(a) for a in angles if int(a) in (0, 90, 180, 270)]
+        return cls(0.0, valid or [0])
+
     def apply(self, x):
+        if self.angles is not None:
+            a = self.angles[int(torch.randint(0, len(self.angles), ()))]
+            return torch.rot90(x, a // 90, dims=(-2, -1)) if a else x
         a = math.radians((float(torch.rand(())) * 2 - 1) * self.degrees)
         y, s = _b(x)
         theta = torch.tensor([[math.cos(a), -math.sin(a), 0.0], [math.sin(a), math.cos(a), 0.0]]).repeat(y.shape[0], 1, 1)
@@ -63,7 +104,13 @@ class ColorJitter(Transform):
 
 
 class Grayscale(Transform):
-    def __init__(self, num_output_channels: int = 1): self.n = num_output_channels
+    def __init__(self, num_output_channels: int = 1): self.n = max(int(num_output_channels), 1)
+    @classmethod
+    def new(cls): return cls(1)
+    @classmethod
+    def with_channels(cls, num_output_channels: int):
+        """Grey image repeated over this many channels (at least one)."""
+        return cls(num_output_channels)
     def apply(self, x):
         w = torch.tensor([0.299, 0.587, 0.114], device=x.device).view(3, 1, 1)
         g = (x * w).sum(-3, keepdim=True)
@@ -77,12 +124,28 @@ class ImageNormalize(Transform):
     def imagenet(cls): return cls([0.485, 0.456, 0.406], [0.229, 0.224, 0.225])
     @classmethod
     def mnist(cls): return cls([0.1307], [0.3081])
+    @classmethod
+    def cifar10(cls): return cls([0.4914, 0.4822, 0.4465], [0.2470, 0.2435, 0.2616])
     def apply(self, x): return (x - self.mean.to(x.device)) / self.std.to(x.device)
 
 
 class Pad(Transform):
-    def __init__(self, padding: int, value: float = 0.0): self.p, self.v = padding, value
-    def apply(self, x): return F.pad(x, (self.p,) * 4, value=self.v)
+    """Constant padding of the last two dimensions; ``padding`` = one width for every side or
+    ``(left, right, top, bottom)``."""
+
+    def __init__(self, padding, value: float = 0.0):
+        self.padding = (padding,) * 4 if isinstance(padding, int) else tuple(int(p) for p in padding)
+        if len(self.padding) != 4:
+            raise ValueError("padding is one int or (left, right, top, bottom)")
+        self.p, self.v = self.padding[0], value
+    @classmethod
+    def new(cls, padding: int): return cls(padding)
+    @classmethod
+    def asymmetric(cls, left: int, right: int, top: int, bottom: int): return cls((left, right, top, bottom))
+    def with_fill(self, value: float):
+        self.v = float(value)
+        return self
+    def apply(self, x): return F.pad(x, self.padding, value=self.v)
 
 
 class ToTensorImage(Transform):

@@ -647,3 +647,98 @@ def test_backend_handles_launch_config_and_storage_guards():
     w = s.write(timeout=1.0)
     assert isinstance(w, core.StorageWriteGuard)
     w.drop()
+
+
+def test_transform_and_loader_conveniences():
+    from axonml_b200 import data, vision
+    c = data.Compose.empty()
+    assert c.is_empty() and c.add(data.Scale(2.0)).add(data.Clamp.zero_one()).len() == 2 and c(torch.tensor([0.2, 0.9])).tolist() == pytest.approx([0.4, 1.0])
+    assert data.Normalize.zero_centered()(torch.tensor([0.0, 0.5, 1.0])).tolist() == [-1.0, 0.0, 1.0]
+    assert data.Clamp.symmetric()(torch.tensor([-3.0, 0.5, 3.0])).tolist() == [-1.0, 0.5, 1.0]
+    assert data.RandomCrop.new_2d(2, 3)(torch.zeros(1, 5, 5)).shape == (1, 2, 3)
+    img = torch.arange(6.0).view(1, 2, 3)
+    h, v = data.RandomFlip.horizontal(), data.RandomFlip.vertical()
+    assert (h.dim, h.p, v.dim, v.p) == (-1, 0.5, -2, 0.5)
+    assert torch.equal(data.RandomFlip.new(-1, 1.0)(img), img.flip(-1)) and torch.equal(data.RandomFlip.new(-2, 0.0)(img), img)
+    assert data.StackCollate.with_dim(1).collate([torch.zeros(2), torch.ones(2)]).shape == (2, 2) and data.StackCollate.new().dim == 0
+    ds = data.TensorDataset.from_data(torch.randn(5, 2))
+    assert ds.len() == 5 and ds.get(3)[1] == 0
+    dl = data.DataLoader(ds, 2)
+    assert dl.dataset_len() == 5 and not dl.is_empty() and dl.batch_size == 2 and data.DataLoader(data.TensorDataset.from_data(torch.zeros(0, 2)), 2).is_empty()
+    b = next(iter(dl))
+    assert b.len() == len(b) == 2 and not b.is_empty()
+    bs = data.BatchSampler(data.SequentialSampler(0), 2)
+    assert bs.is_empty() and bs.len() == 0
+
+    x = torch.rand(3, 8, 6)
+    assert vision.Resize.square(4)(x).shape == (3, 4, 4) and vision.Resize.new(2, 5)(x).shape == (3, 2, 5) and vision.Resize(4, 2)(x).shape == (3, 4, 2)
+    assert vision.CenterCrop.square(4)(x).shape == (3, 4, 4) and torch.equal(vision.CenterCrop.new(2, 2)(x), x[:, 3:5, 2:4])
+    assert torch.equal(vision.RandomHorizontalFlip.with_probability(7.0)(x), x.flip(-1)) and torch.equal(vision.RandomVerticalFlip.with_probability(-1.0)(x), x)
+    assert vision.RandomHorizontalFlip.new().p == 0.5
+    quarter = vision.RandomRotation.with_angles([90, 45])
+    assert quarter.angles == [90] and torch.equal(quarter(x), torch.rot90(x, 1, (-2, -1))) and quarter(x).shape == (3, 6, 8)
+    assert vision.RandomRotation.with_angles([13]).angles == [0] and torch.equal(vision.RandomRotation.with_angles([13])(x), x)
+    assert vision.RandomRotation.new().angles == [0, 90, 180, 270] and vision.RandomRotation(0.0)(x).shape == x.shape
+    g = vision.Grayscale.with_channels(3)(x)
+    assert g.shape == (3, 8, 6) and torch.equal(g[0], g[2]) and vision.Grayscale.with_channels(0).n == 1 and vision.Grayscale.new()(x).shape == (1, 8, 6)
+    n = vision.ImageNormalize.cifar10()
+    assert n.mean.flatten().tolist() == pytest.approx([0.4914, 0.4822, 0.4465]) and n.std.flatten().tolist() == pytest.approx([0.2470, 0.2435, 0.2616])
+    p = vision.Pad.asymmetric(1, 2, 3, 4).with_fill(-1.0)(torch.zeros(1, 2, 2))
+    assert p.shape == (1, 9, 5) and p[0, 0, 0] == -1.0 and p[0, 3, 1] == 0.0 and vision.Pad.new(2)(torch.zeros(1, 2, 2)).shape == (1, 6, 6)
+    with pytest.raises(ValueError):
+        vision.Pad((1, 2))
+
+
+def test_vision_dataset_and_model_accessors(tmp_path):
+    import numpy as np
+    from axonml_b200 import vision
+    sm = vision.SyntheticMNIST.small()
+    assert sm.len() == 100 and vision.SyntheticMNIST.train().len() == 60000 and vision.SyntheticMNIST.test().len() == 10000
+    sc = vision.SyntheticCIFAR.small()
+    assert sc.len() == 100 and sc.class_names()[0] == "airplane" and vision.SyntheticCIFAR.cifar100(7).class_names() is None
+    assert vision.SyntheticCIFAR.cifar100(7).num_classes() == 100 and vision.SyntheticCIFAR.train().len() == 50000 and vision.SyntheticCIFAR.test().len() == 10000
+    assert vision.CIFAR10.class_names() == ["airplane", "automobile", "bird", "cat", "deer", "dog", "frog", "horse", "ship", "truck"]
+    assert vision.FashionMNIST.class_names()[9] == "Ankle boot" and vision.MNIST.class_names() == [str(d) for d in range(10)]
+    rec = np.zeros((4, 3074), dtype=np.uint8)
+    rec[:, 0], rec[:, 1], rec[:, 2:] = [3, 3, 7, 19], [10, 11, 70, 99], 128
+    rec.tofile(tmp_path / "test.bin")
+    c100 = vision.CIFAR100(str(tmp_path), train=False)
+    img, fine, coarse = c100.get_with_coarse(2)
+    assert (int(fine), int(coarse)) == (70, 7) and img.shape == (3, 32, 32) and c100.get_with_coarse(4) is None
+    assert (c100.num_fine_classes(), c100.num_coarse_classes(), c100.num_classes(), c100.is_train(), c100.image_size()) == (100, 20, 100, False, (3, 32, 32))
+    assert int(c100.get(3)[1]) == 99 and c100.class_names() is None
+    r10 = np.zeros((2, 3073), dtype=np.uint8)
+    r10[:, 0] = [4, 9]
+    r10.tofile(tmp_path / "test_batch.bin")
+    c10 = vision.CIFAR10.new(str(tmp_path), False)
+    assert (c10.num_classes(), c10.is_train(), c10.image_size(), int(c10.get(1)[1])) == (10, False, (3, 32, 32), 9)
+    cnn = vision.SimpleCNN(3, 7, 32)
+    assert cnn.input_channels() == 3 and cnn.num_classes() == 7
+    assert isinstance(vision.VGG.vgg13_bn(5), vision.VGG) and any("BatchNorm" in type(m).__name__ for m in vision.VGG.vgg11_bn(5).features)
+    assert not any("BatchNorm" in type(m).__name__ for m in vision.VGG.vgg11(5).features)
+    head = vision.VggClassifier.with_input_size(32, 3)
+    assert head[0].weight.shape == (4096, 32) and head[6].weight.shape == (3, 4096)
+
+    torch.manual_seed(0)
+    tr = vision.Transformer(16, 2, 1, 1, 32, 0.0).eval()
+    src, tgt = torch.randn(2, 5, 16), torch.randn(2, 4, 16)
+    with torch.no_grad():
+        assert tr.d_model() == 16 and tr.encoder.layers[0].d_model() == 16
+        base = tr(src, tgt)
+        assert torch.allclose(tr.forward_full(src, tgt), base)
+        keep = torch.ones(2, 1, 1, 5, dtype=torch.bool)
+        keep[..., 3:] = False                                              # the last two source positions are padding
+        masked = tr.forward_full(src, tgt, src_mask=keep, memory_mask=keep)
+        src2 = src.clone()
+        src2[:, 3:] += 5.0
+        assert torch.allclose(tr.forward_full(src2, tgt, src_mask=keep, memory_mask=keep), masked, atol=1e-5)        # masked inputs have no effect
+        mem = tr.encoder.forward_with_mask(src, keep)
+        mem2 = tr.encoder.forward_with_mask(src2, keep)
+        assert torch.allclose(mem[:, :3], mem2[:, :3], atol=1e-5)           # visible positions ignore what is masked
+        out = tr.decoder.forward_with_memory(tgt, mem, None, keep)
+        out2 = tr.decoder.forward_with_memory(tgt, mem2, None, keep)
+        assert torch.allclose(out, out2, atol=1e-5)
+        causal = torch.ones(4, 4, dtype=torch.bool).tril()
+        assert torch.allclose(tr.decoder.forward_with_memory(tgt, mem, causal, keep), out, atol=1e-5)      # the default target mask is causal
+        full = torch.ones(4, 4, dtype=torch.bool)
+        assert not torch.allclose(tr.decoder.forward_with_memory(tgt, mem, full, keep), out, atol=1e-5)

@@ -458,3 +458,44 @@ def test_bottleneck_severities_summaries_and_guards():
     assert isinstance(st, fusion.OptimizationStats) and st.fusions_applied == 3 and st.ops_eliminated == 5
     assert st.patterns == [[P.MatMulBiasRelu, 2], [P.ConvBatchNorm, 1]]
     assert st.estimated_speedup == pytest.approx(P.MatMulBiasRelu.estimated_speedup() ** 2 * P.ConvBatchNorm.estimated_speedup())
+
+
+def test_text_and_audio_conveniences():
+    assert text.WhitespaceTokenizer.lowercase().tokenize("Hello World") == ["hello", "world"] and text.WhitespaceTokenizer().tokenize("Hi There") == ["Hi", "There"]
+    assert text.WordPunctTokenizer.lowercase().tokenize("Hi, You!") == ["hi", ",", "you", "!"]
+    assert text.CharTokenizer.no_whitespace().tokenize("a b\tc") == ["a", "b", "c"]
+    bpe = text.BasicBPETokenizer()
+    bpe.train("low lower lowest low low", 6)
+    gv = bpe.get_vocab()
+    assert gv == sorted(gv) and all(isinstance(t, str) for t in gv) and set(bpe.tokenize("low")) <= set(gv)
+    uni = text.UnigramTokenizer.from_tokens(["un", "break", "able"])
+    assert uni.tokenize("unbreakable") == ["un", "break", "able"] and uni.vocab["un"] == 1.0
+    v = text.Vocab.new()
+    assert v.is_empty()
+    v.add_special_tokens(["<s>", "</s>"])
+    v.set_unk_token("<?>")
+    v.set_pad_token("<_>")
+    v.add_token("cat")
+    assert v.tokens() == ["<s>", "</s>", "<?>", "<_>", "cat"] and not v.is_empty() and v.token_to_index("dog") == 2 and v.pad_index() == 3
+    samples = [("the cat sat", 0), ("the dog sat", 1), ("the cat ran", 2)]
+    ds = text.TextDataset.from_samples(samples, text.WhitespaceTokenizer(), min_freq=2, max_length=5)
+    toks = ds.vocab.tokens()
+    assert toks[5:] == ["the", "cat", "sat"] and (ds.num_classes(), ds.max_length(), ds.len()) == (3, 5, 3)        # by count, ties alphabetically
+    x, y = ds.get(1)
+    assert x.tolist() == [5, ds.vocab.unk_index, 7, 0, 0] and int(y) == 1
+    lm = text.LanguageModelDataset.from_text("a b c d e f g h", text.Vocab.from_text("a b c d e f g h"), text.WhitespaceTokenizer(), 3)
+    assert lm.vocab() is not None and text.LanguageModelDataset(list(range(9)), 4).vocab() is None
+    s = text.SyntheticSentimentDataset.small()
+    assert s.len() == 100 and s.get(0)[0].shape == (32,) and text.SyntheticSentimentDataset.test().len() == 2000
+    c = audio.SyntheticCommandDataset.small()
+    assert (c.len(), c.sample_rate(), c.num_classes(), c.get(0)[0].numel()) == (100, 16000, 10, 8000)
+    assert audio.SyntheticCommandDataset.large().num_classes() == 35 and audio.SyntheticCommandDataset.medium().len() == 1000
+    m = audio.SyntheticMusicDataset.medium()
+    assert (m.len(), m.sample_rate(), m.num_genres(), m.get(1)[0].numel()) == (500, 22050, 10, 44100) and audio.SyntheticMusicDataset.small().num_genres() == 5
+    sp = audio.SyntheticSpeakerDataset.medium()
+    assert (sp.len(), sp.num_speakers(), sp.sample_rate()) == (500, 20, 16000) and audio.SyntheticSpeakerDataset.small().num_speakers() == 5
+    assert audio.SyntheticSpeakerDataset(10, 1).num_speakers() == 2                       # at least two speakers
+    t = audio.TrimSilence.default_threshold()
+    assert t.threshold_db == -60.0 and t.thr == pytest.approx(1e-3)
+    w = torch.cat([torch.zeros(100), torch.ones(50), torch.zeros(30)])
+    assert t(w).numel() == 50 and audio.TrimSilence.new(-20.0).threshold_db == -20.0
