@@ -135,6 +135,10 @@ class ComputationGraph:
         self._nodes.clear()
         self._next_id = 0
 
+    def reset_id_counter(self) -> None:
+        """Node ids start again from 0 for nodes registered from now on (ids are per graph here)."""
+        self._next_id = 0
+
     def op_counts(self) -> dict:
         out: dict[str, int] = {}
         for n in self.operations():

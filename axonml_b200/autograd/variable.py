@@ -73,6 +73,34 @@ class Variable:
     def slice(self, ranges): return self._w(self.tensor[tuple(slice(a, b) for a, b in ranges)])
     def expand(self, *shape): return self._w(self.tensor.expand(*shape))
     def mse_loss(self, target): return self._w(F.mse_loss(self.tensor, self._u(target)))
+    def binary_cross_entropy(self, target): return self._w(F.binary_cross_entropy(self.tensor, self._u(target)))
+    def sub_scalar(self, s): return self._w(self.tensor - s)
+    def div_scalar(self, s): return self._w(self.tensor / s)
+    # operator forms under the reference's short names
+    def add(self, o): return self.add_var(o)
+    def sub(self, o): return self.sub_var(o)
+    def mul(self, o): return self.mul_var(o)
+    def div(self, o): return self.div_var(o)
+    def ndim(self) -> int: return self.tensor.dim()
+
+    @classmethod
+    def from_tensor_with_grad(cls, t, requires_grad: bool = True): return cls(t, requires_grad)
+
+    def clone_var(self):
+        """A new leaf with a copy of the data and the same ``requires_grad``."""
+        return Variable(self.tensor.detach().clone(), self.tensor.requires_grad)
+
+    def requires_grad_(self, flag: bool = True):
+        self.tensor.requires_grad_(flag)
+        return self
+
+    def set_grad(self, grad) -> None:
+        self.tensor.grad = None if grad is None else torch.as_tensor(grad, dtype=self.tensor.dtype).reshape(self.tensor.shape).clone()
+
+    def accumulate_grad(self, grad) -> None:
+        """Adds ``grad`` to the stored gradient (sets it when there is none)."""
+        g = torch.as_tensor(grad, dtype=self.tensor.dtype).reshape(self.tensor.shape)
+        self.tensor.grad = g.clone() if self.tensor.grad is None else self.tensor.grad + g
 
     __add__ = add_var
     __sub__ = sub_var

@@ -199,6 +199,12 @@ class CudaKernels:
     def launch_config(self, n: int) -> LaunchConfig:
         return launch_config(n)
 
+    def get(self, entry_point: str):
+        """The library's callable for ``entry_point``; ``KernelNotFound`` when it has none (mod.rs ``get``)."""
+        if not self.has(entry_point):
+            raise KernelNotFound(entry_point)
+        return getattr(self._lib, entry_point)
+
     def launch_elementwise(self, name: str, *tensors, alpha: float = 0.0):
         from ..ops import elementwise
         if name in self.BINARY and len(tensors) == 2:
@@ -290,6 +296,42 @@ class CpuBackend(Backend):
         return c
 
     @staticmethod
+    def sgemm(c, a, b, m: int, n: int, k: int, alpha: float = 1.0, beta: float = 0.0):
+        """C[m, n] = alpha * A[m, k] B[k, n] + beta * C, in place on the fp32 tensor ``c`` (cpu.rs:566-600)."""
+        prod = CpuBackend.matmul(a.reshape(m, k), b.reshape(k, n))
+        out = c.view(m, n)
+        out.copy_(alpha * prod + (beta * out if beta != 0.0 else 0.0))
+        return c
+
+    @staticmethod
+    def dgemm(c, a, b, m: int, n: int, k: int, alpha: float = 1.0, beta: float = 0.0):
+        """The fp64 form of ``sgemm`` (cpu.rs:603-636)."""
+        prod = a.reshape(m, k).double() @ b.reshape(k, n).double()
+        out = c.view(m, n)
+        out.copy_(alpha * prod + (beta * out if beta != 0.0 else 0.0))
+        return c
+
+    @staticmethod
+    def matmul_f32(c, a, b, m: int, n: int, k: int): return CpuBackend.sgemm(c, a, b, m, n, k, 1.0, 0.0)
+    @staticmethod
+    def matmul_f64(c, a, b, m: int, n: int, k: int): return CpuBackend.dgemm(c, a, b, m, n, k, 1.0, 0.0)
+
+    @staticmethod
+    def fill(dst, value):
+        dst.fill_(value)
+        return dst
+
+    @staticmethod
+    def fill_zeros(dst): return CpuBackend.fill(dst, 0)
+
+    @staticmethod
+    def copy(dst, src):
+        if dst.numel() != src.numel():
+            raise ValueError(f"copy of {src.numel()} elements into {dst.numel()}")
+        dst.view(-1).copy_(src.reshape(-1))
+        return dst
+
+    @staticmethod
     def transpose(x):
         x = _f(x)
         y = torch.empty(x.shape[1], x.shape[0])
@@ -362,6 +404,27 @@ class CudaBackend(Backend):
     def synchronize(self) -> None: torch.cuda.synchronize(self.index)
     def stream_synchronize(self) -> None: torch.cuda.current_stream(self.index).synchronize()
     def mem_get_info(self): return torch.cuda.mem_get_info(self.index)
+    def device_index(self) -> int: return self.index
+
+    def blas(self):
+        """Handle of the library GEMM context of this device (the reference exposes its cuBLAS
+        handle); plain library GEMMs here go through torch, so this is torch's handle."""
+        with torch.cuda.device(self.index):
+            return torch.cuda.current_blas_handle()
+
+    def alloc(self, count: int, dtype=torch.float32) -> torch.Tensor:
+        """``count`` zeroed elements on the device (cuda.rs ``alloc``)."""
+        return torch.zeros(count, dtype=dtype, device=f"cuda:{self.index}")
+
+    def alloc_uninit(self, count: int, dtype=torch.float32) -> torch.Tensor:
+        return torch.empty(count, dtype=dtype, device=f"cuda:{self.index}")
+
+    def htod_copy(self, host, non_blocking: bool = False) -> torch.Tensor:
+        """Host data (tensor, list or array) -> a new device tensor."""
+        return torch.as_tensor(host).to(f"cuda:{self.index}", non_blocking=non_blocking)
+
+    def dtoh_copy(self, dev: torch.Tensor) -> torch.Tensor:
+        return dev.detach().cpu()
 
     def _e(self):
         from ..ops import elementwise

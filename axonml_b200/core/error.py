@@ -86,3 +86,13 @@ class InternalError(AxonmlError):
 
 
 Error = AxonmlError
+
+
+# constructor helpers of the reference's ``Error`` (error.rs ``Error::shape_mismatch`` ...)
+def _as_static(fn):
+    return staticmethod(fn)
+
+
+AxonmlError.shape_mismatch = _as_static(lambda expected, actual: ShapeMismatch(expected, actual))
+AxonmlError.invalid_operation = _as_static(lambda message: InvalidOperation(message))
+AxonmlError.internal = _as_static(lambda message: InternalError(message))

@@ -26,20 +26,57 @@ class GpuTestResult:
     passed: bool
     max_error: float = 0.0
     message: str = ""
+    throughput_gbps: float | None = None
+    latency_us: float | None = None
+
+    # the reference's builders (gpu_tests.rs:79-113); ``pass`` is a keyword, hence the underscore
+    @classmethod
+    def pass_(cls, name: str): return cls(name, True)
+    @classmethod
+    def fail(cls, name: str, error: str): return cls(name, False, 0.0, error)
+
+    def with_error(self, max_abs_error: float):
+        self.max_error = float(max_abs_error)
+        return self
+
+    def with_perf(self, throughput_gbps: float, latency_us: float):
+        self.throughput_gbps, self.latency_us = float(throughput_gbps), float(latency_us)
+        return self
+
+    @property
+    def error(self): return self.message or None
+    @property
+    def max_abs_error(self): return self.max_error
 
 
 @dataclasses.dataclass
 class GpuTestReport:
     results: list = dataclasses.field(default_factory=list)
+    backend: str = "cuda"
+    capabilities: object = None
+
+    @classmethod
+    def new(cls, backend: str): return cls([], backend)
+
+    def with_capabilities(self, caps):
+        self.capabilities = caps
+        return self
 
     def add(self, r: GpuTestResult) -> None: self.results.append(r)
+    add_result = add
     def passed(self) -> int: return sum(r.passed for r in self.results)
     def failed(self) -> int: return sum(not r.passed for r in self.results)
+    passed_count, failed_count = passed, failed
     def all_passed(self) -> bool: return self.failed() == 0
 
     def print_summary(self) -> None:
+        print(f"GPU Test Report: {self.backend}")
+        if self.capabilities is not None:
+            c = self.capabilities
+            print(f"Device: {c.name}  memory {c.total_memory / 2 ** 30:.1f} GiB  SMs {getattr(c, 'sm_count', 0)}")
         for r in self.results:
-            print(f"[{'PASS' if r.passed else 'FAIL'}] {r.name} max_err={r.max_error:.3e} {r.message}")
+            perf = f" {r.throughput_gbps:.1f} GB/s {r.latency_us:.1f} us" if r.throughput_gbps is not None else ""
+            print(f"[{'PASS' if r.passed else 'FAIL'}] {r.name} max_err={r.max_error:.3e}{perf} {r.message}")
         print(f"{self.passed()} passed, {self.failed()} failed")
 
 

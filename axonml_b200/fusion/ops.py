@@ -41,6 +41,7 @@ class TensorError(FusionError):
 
 class FusedOp:
     def execute(self, x: torch.Tensor) -> torch.Tensor: raise NotImplementedError
+    def forward(self, x: torch.Tensor) -> torch.Tensor: return self.execute(x)
     def name(self) -> str: return type(self).__name__
     def num_ops(self) -> int: return 1
     def __call__(self, x): return self.execute(x)
@@ -93,6 +94,27 @@ class ElementwiseOp(enum.Enum):
     Clamp = "clamp"
     Neg = "neg"
     Abs = "abs"
+
+    def apply(self, x, *args):
+        """The operation on a number or a tensor; ``args`` are its constants (the addend, the
+        factor, the slope, the clamp bounds)."""
+        t = torch.is_tensor(x)
+        v = x if t else torch.tensor(float(x))
+        k = self.value
+        if k == "add": r = v + args[0]
+        elif k == "mul": r = v * args[0]
+        elif k == "relu": r = v.clamp_min(0)
+        elif k == "leaky_relu": r = torch.where(v > 0, v, v * (args[0] if args else 0.01))
+        elif k == "sigmoid": r = torch.sigmoid(v)
+        elif k == "tanh": r = torch.tanh(v)
+        elif k == "exp": r = torch.exp(v)
+        elif k == "log": r = torch.log(v)
+        elif k == "sqrt": r = torch.sqrt(v)
+        elif k == "square": r = v * v
+        elif k == "clamp": r = v.clamp(args[0], args[1])
+        elif k == "neg": r = -v
+        else: r = v.abs()
+        return r if t else float(r)
 
 
 class FusedElementwise(FusedOp):

@@ -52,6 +52,10 @@ class FusionPattern(enum.Enum):
                 FusionPattern.MatMulBias: 1.2, FusionPattern.Softmax: 1.2, FusionPattern.LayerNorm: 1.2,
                 FusionPattern.GeluApprox: 1.2}[self]
 
+    def is_memory_bound(self) -> bool:
+        """Patterns whose cost is memory traffic, where fusing saves whole passes over the data."""
+        return self in (FusionPattern.ElementwiseChain, FusionPattern.AddRelu, FusionPattern.MulAdd)
+
     def num_ops(self) -> int:
         return {FusionPattern.MatMulBias: 2, FusionPattern.MatMulBiasRelu: 3, FusionPattern.MatMulBiasGelu: 3,
                 FusionPattern.ConvBatchNorm: 2, FusionPattern.ConvBatchNormRelu: 3, FusionPattern.AddRelu: 2,
@@ -97,6 +101,10 @@ class FusionConfig:
 
     @classmethod
     def new(cls): return cls()
+    @classmethod
+    def all_enabled(cls):
+        """Every fusion on, chains from two operations, aggressive mode."""
+        return cls(True, True, True, 2, True)
     @classmethod
     def conservative(cls): return cls(min_chain_length=3)
     @classmethod
@@ -159,6 +167,15 @@ class FusionOptimizer:
         return pats
 
     def stats(self) -> FusionStats: return self._stats
+
+    def apply_fusions(self, patterns) -> None:
+        """Counts ``(pattern, start, length)`` entries into ``optimization_stats`` (optimizer.rs:159-163)."""
+        for p, _, n in patterns:
+            self.optimization_stats.add_fusion(p, n)
+
+    def reset_stats(self) -> None:
+        self._stats = FusionStats()
+        self.optimization_stats = OptimizationStats()
 
 
 def estimate_speedup(ops, patterns) -> float:

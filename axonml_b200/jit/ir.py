@@ -65,6 +65,9 @@ class DataType(enum.Enum):
     I64 = "i64"
     Bool = "bool"
 
+    def size_bytes(self) -> int:
+        return {"f32": 4, "i32": 4, "f64": 8, "i64": 8, "bool": 1}[self.value]
+
 
 UNARY = ("Neg", "Abs", "Sqrt", "Exp", "Log", "Sin", "Cos", "Tanh", "Relu", "Sigmoid", "Gelu", "Silu", "Contiguous")
 BINARY = ("Add", "Sub", "Mul", "Div", "Pow", "Max", "Min", "Gt", "Lt", "Eq")
@@ -124,6 +127,22 @@ class Graph:
         if op.kind == "Output":
             self.outputs[op.attr("name")] = nid
         return nid
+
+    def register_input(self, name: str, nid: int) -> None:
+        """Names node ``nid`` as the graph input ``name`` (``add_node`` does this for Input nodes)."""
+        self.inputs[name] = NodeId(nid)
+
+    def register_output(self, name: str, nid: int) -> None:
+        self.outputs[name] = NodeId(nid)
+
+    def input(self, name: str): return self.inputs.get(name)
+    def output(self, name: str): return self.outputs.get(name)
+    def node_mut(self, nid: int) -> Node: return self.nodes[nid]          # nodes are mutable objects
+
+    def topological_order(self) -> list:
+        """Node ids with every node after its inputs: nodes can only refer to earlier ones, so
+        this is the order of insertion."""
+        return [n.id for n in self.nodes]
 
     def node(self, nid: int) -> Node: return self.nodes[nid]
     def len(self) -> int: return len(self.nodes)

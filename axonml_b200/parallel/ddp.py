@@ -53,6 +53,7 @@ class GradientBucket:
     def is_empty(self) -> bool: return self._size == 0
     def num_tensors(self) -> int: return len(self.shapes)
     def data(self) -> torch.Tensor: return self.buffer[:self._size]
+    def data_mut(self) -> torch.Tensor: return self.buffer[:self._size]        # a view: writes land in the bucket
 
     def reserve(self, shape) -> torch.Tensor:
         n = 1
@@ -181,6 +182,7 @@ class DistributedDataParallel(Module):
         return self
 
     def module(self): return self._module
+    def module_mut(self): return self._module
     def process_group(self) -> ProcessGroup: return self.pg
     def attach_scaler(self, scaler) -> None: self._scaler = scaler
     def num_buckets(self) -> int: return len(self._buckets)

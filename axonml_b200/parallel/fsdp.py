@@ -65,6 +65,15 @@ class FSDPMemoryStats:
     local_param_memory: int
     local_optimizer_memory: int
     savings_factor: float
+    world_size: int = 1
+
+    def total_memory_mb(self) -> float:
+        """Parameters (with their fp32 masters) plus optimizer state held by this rank, in MiB."""
+        return (self.local_param_memory + self.local_optimizer_memory) / (1024.0 * 1024.0)
+
+    def memory_savings(self) -> float:
+        """Fraction of the unsharded footprint this rank no longer holds: 1 - 1 / world size."""
+        return 1.0 - 1.0 / self.world_size if self.world_size > 1 else 0.0
 
 
 class _Buffer:
@@ -709,7 +718,14 @@ class FullyShardedDataParallel(Module):
         local = sum(u.shard for u in self.units)
         bpe = torch.empty((), dtype=self.param_dtype).element_size()
         return FSDPMemoryStats(total, total * bpe, local, local * (bpe + 4), local * 8,
-                               total / max(local, 1))
+                               total / max(local, 1), self.world)
+
+    def module_mut(self):
+        """The wrapped module (modules are mutable objects: the same object as ``.module``)."""
+        return self.module
+
+    def process_group(self):
+        return self.pg
 
     # ------------------------------------------------------------------ state (sharded checkpoints)
     def full_state_dict(self) -> dict:

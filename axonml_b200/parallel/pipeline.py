@@ -35,6 +35,11 @@ class PipelineStage:
     stage_id: int
     device_rank: int
 
+    def forward(self, x):
+        return self.module(x)
+
+    __call__ = forward
+
 
 @dataclasses.dataclass
 class PipelineMemoryStats:
@@ -42,6 +47,16 @@ class PipelineMemoryStats:
     num_microbatches: int
     peak_activations_per_stage: int
     schedule: PipelineSchedule
+
+    @staticmethod
+    def gpipe_peak_activations(num_stages: int, num_microbatches: int) -> int:
+        """GPipe keeps every microbatch's activations on every stage until the backward pass."""
+        return num_stages * num_microbatches
+
+    @staticmethod
+    def one_f_one_b_peak_activations(num_stages: int, num_microbatches: int) -> int:
+        """1F1B holds at most as many microbatches in flight as there are stages."""
+        return min(num_stages, num_microbatches)
 
 
 def build_schedule(num_stages: int, world: int, num_microbatches: int, in_flight_limit=None):

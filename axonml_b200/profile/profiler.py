@@ -363,6 +363,19 @@ class Profiler:
     def enable(self) -> None: self.enabled = True
     def disable(self) -> None: self.enabled = False
     def is_enabled(self) -> bool: return self.enabled
+    def set_enabled(self, enabled: bool) -> None: self.enabled = bool(enabled)
+    def peak_memory(self) -> int: return self.memory.peak_usage()
+    def current_memory(self) -> int: return self.memory.current_usage()
+    def total_time(self, name: str) -> float: return self.compute.total_time(name)
+    def avg_time(self, name: str) -> float: return self.compute.avg_time(name)
+
+    def summary(self):
+        """The report of everything recorded so far (``print_summary`` prints it)."""
+        return self.report()
+
+    def analyze_bottlenecks(self) -> list:
+        from .bottleneck import BottleneckAnalyzer
+        return BottleneckAnalyzer().analyze(self)
 
     def start(self, name: str) -> None:
         if not self.enabled:

@@ -102,6 +102,13 @@ class ProfileReport:
                 "<table border=1><tr><th>operation</th><th>calls</th><th>total ms</th><th>avg us</th>"
                 f"<th>GFLOPS</th><th>GB/s</th></tr>{rows}</table></body></html>")
 
+    def export(self, path, fmt: ReportFormat | None = None) -> None:
+        """Writes the report; the format follows the file extension unless given (report.rs ``export``)."""
+        self.save(path, fmt)
+
+    def __str__(self) -> str:
+        return self.to_text()
+
     def save(self, path, fmt: ReportFormat | None = None) -> None:
         if fmt is None:
             ext = str(path).rsplit(".", 1)[-1].lower()

@@ -78,23 +78,56 @@ def transpose_linear_weights(sd: StateDict) -> StateDict:
 
 
 class OnnxOpType(enum.Enum):
-    Gemm = "Gemm"
+    """ONNX operator names the converters know (convert.rs:93-245)."""
+    Add = "Add"
+    Sub = "Sub"
+    Mul = "Mul"
+    Div = "Div"
     MatMul = "MatMul"
-    Conv = "Conv"
+    Gemm = "Gemm"
     Relu = "Relu"
     Sigmoid = "Sigmoid"
     Tanh = "Tanh"
     Softmax = "Softmax"
-    BatchNormalization = "BatchNormalization"
+    Gelu = "Gelu"
+    Conv = "Conv"
+    ConvTranspose = "ConvTranspose"
     MaxPool = "MaxPool"
     AveragePool = "AveragePool"
+    GlobalAveragePool = "GlobalAveragePool"
+    BatchNormalization = "BatchNormalization"
+    LayerNormalization = "LayerNormalization"
+    Reshape = "Reshape"
+    Transpose = "Transpose"
     Flatten = "Flatten"
-    Add = "Add"
+    Squeeze = "Squeeze"
+    Unsqueeze = "Unsqueeze"
+    Concat = "Concat"
+    ReduceSum = "ReduceSum"
+    ReduceMean = "ReduceMean"
+    ReduceMax = "ReduceMax"
+    ReduceMin = "ReduceMin"
     Dropout = "Dropout"
+    Constant = "Constant"
+    Identity = "Identity"
+    Unknown = "Unknown"
 
     @staticmethod
     def from_layer(name: str):
         return {"Linear": OnnxOpType.Gemm, "Conv2d": OnnxOpType.Conv, "ReLU": OnnxOpType.Relu,
-                "Sigmoid": OnnxOpType.Sigmoid, "Tanh": OnnxOpType.Tanh, "Softmax": OnnxOpType.Softmax,
-                "BatchNorm2d": OnnxOpType.BatchNormalization, "MaxPool2d": OnnxOpType.MaxPool,
-                "AvgPool2d": OnnxOpType.AveragePool, "Dropout": OnnxOpType.Dropout}.get(name)
+                "Sigmoid": OnnxOpType.Sigmoid, "Tanh": OnnxOpType.Tanh, "Softmax": OnnxOpType.Softmax, "GELU": OnnxOpType.Gelu,
+                "BatchNorm2d": OnnxOpType.BatchNormalization, "LayerNorm": OnnxOpType.LayerNormalization,
+                "MaxPool2d": OnnxOpType.MaxPool, "AvgPool2d": OnnxOpType.AveragePool,
+                "AdaptiveAvgPool2d": OnnxOpType.GlobalAveragePool, "Dropout": OnnxOpType.Dropout, "Identity": OnnxOpType.Identity}.get(name)
+
+    @staticmethod
+    def from_str(name: str) -> "OnnxOpType":
+        """Member with this ONNX name; ``Unknown`` for anything else."""
+        try:
+            return OnnxOpType(name)
+        except ValueError:
+            return OnnxOpType.Unknown
+
+    def as_str(self) -> str:
+        """The operator's ONNX name."""
+        return self.value

@@ -21,6 +21,11 @@ class SparseCOO:
     def from_triplets(cls, rows, cols, values, shape):
         return cls(torch.tensor([rows, cols]), torch.as_tensor(values, dtype=torch.float32), shape)
 
+    @classmethod
+    def from_coo_2d(cls, rows, cols, values, shape):
+        """Matrix from parallel row / column / value lists (sparse.rs ``from_coo_2d``)."""
+        return cls.from_triplets(rows, cols, values, shape)
+
     def nnz(self) -> int: return self.values.numel()
     def density(self) -> float:
         n = 1
@@ -57,6 +62,12 @@ class SparseCSR:
         return SparseCOO.from_dense(dense, threshold).to_csr()
 
     def nnz(self) -> int: return self.values.numel()
+    def nrows(self) -> int: return self.shape[0]
+    def ncols(self) -> int: return self.shape[1]
+
+    def density(self) -> float:
+        n = self.shape[0] * self.shape[1]
+        return self.nnz() / n if n else 0.0
 
     def _t(self):
         return torch.sparse_csr_tensor(self.crow, self.cols, self.values, self.shape)

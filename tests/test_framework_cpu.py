@@ -742,3 +742,101 @@ def test_vision_dataset_and_model_accessors(tmp_path):
         assert torch.allclose(tr.decoder.forward_with_memory(tgt, mem, causal, keep), out, atol=1e-5)      # the default target mask is causal
         full = torch.ones(4, 4, dtype=torch.bool)
         assert not torch.allclose(tr.decoder.forward_with_memory(tgt, mem, full, keep), out, atol=1e-5)
+
+
+def test_remaining_reference_method_names():
+    """Small methods the reference's types answer: one behavioural check each."""
+    from axonml_b200 import autograd as ag, core, fusion, jit, parallel, profile, serialize, tensor
+    from axonml_b200.core import gpu_tests as GT
+    from axonml_b200.core.error import InternalError, InvalidOperation, ShapeMismatch
+    assert isinstance(core.Error.shape_mismatch((2,), (3,)), ShapeMismatch) and isinstance(core.Error.invalid_operation("x"), InvalidOperation)
+    assert isinstance(core.Error.internal("x"), InternalError)
+    r = GT.GpuTestResult.pass_("add").with_error(1e-6).with_perf(900.0, 3.5)
+    assert r.passed and r.max_abs_error == 1e-6 and (r.throughput_gbps, r.latency_us, r.error) == (900.0, 3.5, None)
+    f = GT.GpuTestResult.fail("mul", "mismatch")
+    rep = GT.GpuTestReport.new("cuda").with_capabilities(core.Device.Cpu().capabilities())
+    rep.add_result(r); rep.add_result(f)
+    assert (rep.passed_count(), rep.failed_count(), f.error, rep.backend) == (1, 1, "mismatch", "cuda") and not rep.all_passed()
+    a, b = torch.randn(3, 4), torch.randn(4, 2)
+    c = torch.ones(3, 2)
+    core.CpuBackend.sgemm(c, a, b, 3, 2, 4, 2.0, 0.5)
+    assert torch.allclose(c, 2.0 * a @ b + 0.5, atol=1e-5)
+    c64 = torch.zeros(3, 2, dtype=torch.float64)
+    core.CpuBackend.matmul_f64(c64, a.double(), b.double(), 3, 2, 4)
+    assert torch.allclose(c64, a.double() @ b.double()) and torch.allclose(core.CpuBackend.matmul_f32(torch.empty(6), a.flatten(), b.flatten(), 3, 2, 4).view(3, 2), a @ b, atol=1e-5)
+    buf = torch.empty(5)
+    assert core.CpuBackend.fill(buf, 2.5).tolist() == [2.5] * 5 and core.CpuBackend.fill_zeros(buf).sum() == 0
+    assert core.CpuBackend.copy(buf, torch.arange(5.0)).tolist() == [0.0, 1.0, 2.0, 3.0, 4.0]
+    with pytest.raises(ValueError):
+        core.CpuBackend.copy(buf, torch.zeros(4))
+    assert core.CudaBackend(2).device_index() == 2
+
+    v = ag.Variable(torch.tensor([1.0, 2.0]), True)
+    assert v.ndim() == 1 and v.add(v).to_vec() == [2.0, 4.0] and v.sub(1.0).to_vec() == [0.0, 1.0] and v.mul(v).to_vec() == [1.0, 4.0] and v.div(2.0).to_vec() == [0.5, 1.0]
+    assert v.sub_scalar(1.0).to_vec() == [0.0, 1.0] and v.div_scalar(4.0).to_vec() == [0.25, 0.5]
+    v.set_grad([1.0, 1.0]); v.accumulate_grad(torch.tensor([0.5, 2.0]))
+    assert v.grad().tolist() == [1.5, 3.0]
+    v.set_grad(None)
+    assert v.grad() is None
+    v.accumulate_grad([1.0, 1.0])
+    assert v.grad().tolist() == [1.0, 1.0]
+    cl = v.clone_var()
+    assert cl.requires_grad() and cl.is_leaf() and cl.tensor.data_ptr() != v.tensor.data_ptr()
+    assert not ag.Variable(torch.zeros(1)).requires_grad() and ag.Variable(torch.zeros(1)).requires_grad_().requires_grad()
+    assert ag.Variable.from_tensor_with_grad(torch.zeros(2)).requires_grad()
+    p = ag.Variable(torch.tensor([0.8, 0.3]), True)
+    p.binary_cross_entropy(torch.tensor([1.0, 0.0])).backward()
+    assert p.grad() is not None
+    g = ag.ComputationGraph()
+    g.register_leaf(True); g.register_leaf(True)
+    g.reset_id_counter()
+    assert g.register_leaf(False).id == 0
+
+    s = tensor.SparseCOO.from_coo_2d([0, 2], [1, 0], [5.0, 6.0], (3, 2)).to_csr()
+    assert (s.nrows(), s.ncols(), s.nnz()) == (3, 2, 2) and s.density() == pytest.approx(1 / 3)
+    assert serialize.OnnxOpType.Gelu.as_str() == "Gelu" and serialize.OnnxOpType.from_str("ReduceMin") is serialize.OnnxOpType.ReduceMin
+    assert serialize.OnnxOpType.from_str("Einsum") is serialize.OnnxOpType.Unknown and len(serialize.OnnxOpType) == 32
+    assert serialize.OnnxOpType.from_layer("LayerNorm") is serialize.OnnxOpType.LayerNormalization
+
+    E = fusion.ElementwiseOp
+    assert E.Relu.apply(-2.0) == 0.0 and E.Add.apply(1.0, 2.5) == 3.5 and E.Clamp.apply(5.0, 0.0, 1.0) == 1.0 and E.LeakyRelu.apply(-2.0, 0.1) == pytest.approx(-0.2)
+    assert E.Square.apply(torch.tensor([2.0, -3.0])).tolist() == [4.0, 9.0] and E.Sigmoid.apply(0.0) == 0.5
+    w = torch.randn(3, 2)
+    assert torch.allclose(fusion.fuse_matmul_bias(w, torch.zeros(3)).forward(torch.ones(1, 2)), w.sum(1)[None], atol=1e-5)
+    assert torch.equal(fusion.fused_add_relu(1.0).forward(torch.tensor([-2.0, 0.5])), torch.tensor([0.0, 1.5]))
+    fc = fusion.FusionConfig.all_enabled()
+    assert fc.aggressive and fc.fuse_conv and fc.min_chain_length == 2
+    P = fusion.FusionPattern
+    assert P.AddRelu.is_memory_bound() and P.ElementwiseChain.is_memory_bound() and not P.MatMulBiasRelu.is_memory_bound()
+    opt = fusion.FusionOptimizer()
+    opt.apply_fusions([(P.AddRelu, 0, 2), (P.MatMulBias, 2, 2)])
+    assert opt.optimization_stats.fusions_applied == 2 and opt.optimization_stats.ops_eliminated == 2
+    opt.reset_stats()
+    assert opt.optimization_stats.fusions_applied == 0 and opt.optimization_stats.estimated_speedup == 1.0
+
+    assert [d.size_bytes() for d in jit.DataType] == [4, 8, 4, 8, 1]
+    gr = jit.Graph()
+    i0 = gr.add_node(jit.Op.make("Constant", value=1.0), jit.DataType.F32, [2])
+    n1 = gr.add_node(jit.Op.make("Neg", [i0]), jit.DataType.F32, [2])
+    gr.register_input("x", i0); gr.register_output("y", n1)
+    assert gr.input("x") == 0 and gr.output("y") == 1 and gr.input("z") is None and gr.topological_order() == [0, 1]
+    gr.node_mut(1).shape = jit.Shape([2])
+    assert gr.inputs == {"x": 0} and isinstance(gr.input("x"), jit.NodeId)
+
+    pr = profile.Profiler()
+    pr.set_enabled(False)
+    pr.start("x"); pr.stop("x")
+    assert not pr.is_enabled() and pr.compute.get_stats("x") is None
+    pr.set_enabled(True)
+    pr.compute.record("step", 4e6); pr.compute.record("step", 2e6)
+    pr.record_alloc("buf", 64)
+    assert pr.peak_memory() == 64 and pr.current_memory() == 64 and pr.total_time("step") == pytest.approx(6e-3) and pr.avg_time("step") == pytest.approx(3e-3)
+    assert "step" in str(pr.summary()) and any(b.kind is profile.BottleneckType.SlowOperation for b in pr.analyze_bottlenecks())
+    st = parallel.fsdp.FSDPMemoryStats(100, 400, 25, 200, 200, 4.0, 4)
+    assert st.memory_savings() == 0.75 and st.total_memory_mb() == pytest.approx(400 / 2 ** 20) and parallel.fsdp.FSDPMemoryStats(1, 4, 1, 8, 8, 1.0).memory_savings() == 0.0
+    PM = parallel.pipeline.PipelineMemoryStats
+    assert PM.gpipe_peak_activations(4, 8) == 32 and PM.one_f_one_b_peak_activations(4, 8) == 4 and PM.one_f_one_b_peak_activations(4, 2) == 2
+    stage = parallel.pipeline.PipelineStage(torch.nn.Linear(2, 3), 1, 0)
+    assert stage.forward(torch.zeros(1, 2)).shape == (1, 3) and stage(torch.zeros(1, 2)).shape == (1, 3)
+    gb = parallel.GradientBucket(8)
+    assert gb.data_mut().numel() == 0
