@@ -174,6 +174,7 @@ def _session() -> dict | None:
 
 
 def cmd_login(a) -> None:
+    a.username = getattr(a, "username_opt", None) or a.username or os.environ.get("AXONML_USER") or input("user (e-mail): ")
     server = (a.server or "http://localhost:3021").rstrip("/")
     password = a.password or os.environ.get("AXONML_PASSWORD") or getpass.getpass("password: ")
     code, j = _http("POST", server + "/api/auth/login", {"email": a.username, "password": password})
@@ -279,6 +280,7 @@ def cmd_kaggle(a) -> None:
     k = KaggleClient()
     try:
         if a.action == "login":
+            a.username = getattr(a, "username_opt", None) or a.username or os.environ.get("KAGGLE_USERNAME") or input("Kaggle user name: ")
             key = a.key or os.environ.get("KAGGLE_KEY") or getpass.getpass("Kaggle API key: ")
             print(f"saved to {k.save_credentials(a.username, key)}")
         elif a.action == "status":
@@ -339,51 +341,52 @@ def add_parsers(sub) -> None:
     p = sub.add_parser("start", help="start the API server and dashboard")
     p.add_argument("--server", action="store_true"); p.add_argument("--dashboard", action="store_true")
     p.add_argument("--port", type=int, default=3021); p.add_argument("--dashboard-port", type=int, default=8080)
-    p.add_argument("--host", default="127.0.0.1"); p.add_argument("--foreground", action="store_true"); p.add_argument("--config")
+    p.add_argument("--host", default="127.0.0.1"); p.add_argument("-f", "--foreground", action="store_true"); p.add_argument("-c", "--config")
     p.set_defaults(fn=cmd_start)
     p = sub.add_parser("stop"); p.add_argument("--server", action="store_true"); p.add_argument("--dashboard", action="store_true")
-    p.add_argument("--force", action="store_true"); p.set_defaults(fn=cmd_stop)
-    p = sub.add_parser("status"); p.add_argument("--detailed", action="store_true")
-    p.add_argument("--format", default="text", choices=["text", "json"]); p.set_defaults(fn=cmd_status)
+    p.add_argument("-f", "--force", action="store_true"); p.set_defaults(fn=cmd_stop)
+    p = sub.add_parser("status"); p.add_argument("-d", "--detailed", action="store_true")
+    p.add_argument("-f", "--format", default="text", choices=["text", "json"]); p.set_defaults(fn=cmd_status)
     p = sub.add_parser("logs"); p.add_argument("--server", action="store_true"); p.add_argument("--dashboard", action="store_true")
-    p.add_argument("--lines", "-n", type=int, default=50); p.add_argument("--follow", "-f", action="store_true"); p.add_argument("--level")
+    p.add_argument("--lines", "-n", "-l", type=int, default=50); p.add_argument("--follow", "-f", action="store_true"); p.add_argument("--level")
     p.set_defaults(fn=cmd_logs)
-    p = sub.add_parser("login"); p.add_argument("username"); p.add_argument("--password"); p.add_argument("--server")
+    p = sub.add_parser("login"); p.add_argument("username", nargs="?"); p.add_argument("-u", "--username", dest="username_opt")
+    p.add_argument("-p", "--password"); p.add_argument("-s", "--server")
     p.set_defaults(fn=cmd_login)
     p = sub.add_parser("logout"); p.set_defaults(fn=cmd_logout)
-    p = sub.add_parser("sync"); p.add_argument("--check", action="store_true"); p.add_argument("--force", action="store_true")
+    p = sub.add_parser("sync"); p.add_argument("--status", "--check", dest="check", action="store_true"); p.add_argument("--force", action="store_true")
     p.set_defaults(fn=cmd_sync)
 
     p = sub.add_parser("wandb", help="Weights & Biases settings")
     s = p.add_subparsers(dest="action", required=True)
     for name in ("login", "logout", "status", "enable", "disable"):
         s.add_parser(name)
-    q = s.add_parser("config"); q.add_argument("--api-key", dest="api_key"); q.add_argument("--entity"); q.add_argument("--project")
+    q = s.add_parser("config"); q.add_argument("--api-key", dest="api_key"); q.add_argument("-e", "--entity"); q.add_argument("-p", "--project")
     q.add_argument("--base-url", dest="base_url"); q.add_argument("--log-frequency", dest="log_frequency", type=int)
     q.add_argument("--log-checkpoints", dest="log_checkpoints", type=lambda v: v.lower() in ("1", "true", "yes"), default=None)
-    q.add_argument("--log-system", dest="log_system", type=lambda v: v.lower() in ("1", "true", "yes"), default=None)
+    q.add_argument("--log-system-metrics", "--log-system", dest="log_system", type=lambda v: v.lower() in ("1", "true", "yes"), default=None)
     p.set_defaults(fn=cmd_wandb)
 
     p = sub.add_parser("kaggle", help="Kaggle datasets")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("login"); q.add_argument("username"); q.add_argument("--key")
+    q = s.add_parser("login"); q.add_argument("username", nargs="?"); q.add_argument("-u", "--username", dest="username_opt"); q.add_argument("-k", "--key")
     s.add_parser("status"); s.add_parser("list")
-    q = s.add_parser("search"); q.add_argument("query"); q.add_argument("--limit", type=int, default=10)
-    q = s.add_parser("download"); q.add_argument("dataset"); q.add_argument("--output")
+    q = s.add_parser("search"); q.add_argument("query"); q.add_argument("-l", "--limit", type=int, default=10)
+    q = s.add_parser("download"); q.add_argument("dataset"); q.add_argument("-o", "--output")
     p.set_defaults(fn=cmd_kaggle)
 
     p = sub.add_parser("dataset", help="dataset catalogue")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("list"); q.add_argument("--source")
+    q = s.add_parser("list"); q.add_argument("-s", "--source")
     q = s.add_parser("info"); q.add_argument("id")
-    q = s.add_parser("search"); q.add_argument("query"); q.add_argument("--source"); q.add_argument("--limit", type=int, default=10)
-    q = s.add_parser("download"); q.add_argument("id"); q.add_argument("--output")
+    q = s.add_parser("search"); q.add_argument("query"); q.add_argument("-s", "--source"); q.add_argument("-l", "--limit", type=int, default=10)
+    q = s.add_parser("download"); q.add_argument("id"); q.add_argument("-o", "--output")
     s.add_parser("sources")
     p.set_defaults(fn=cmd_dataset)
 
     from . import tui
     p = sub.add_parser("tui", help="terminal user interface")
-    p.add_argument("--model"); p.add_argument("--data")
+    p.add_argument("-m", "--model"); p.add_argument("-d", "--data")
     p.add_argument("--watch", help="training log (JSON lines) to follow in the Training and Graphs views")
     p.add_argument("--once", action="store_true", help="render every view once and exit")
     p.set_defaults(fn=tui.cmd_tui)

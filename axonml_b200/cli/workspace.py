@@ -41,13 +41,8 @@ def model_summary(path: str) -> dict:
         from ..quant.gguf import read_gguf
         g = read_gguf(path)
         for name in g.tensor_names():
-            info = g.tensors[name]
-            shape = list(info["shape"]) if isinstance(info, dict) else list(getattr(info, "shape", []))
-            kind = info.get("type") if isinstance(info, dict) else getattr(info, "type", "")
-            n = 1
-            for s in shape:
-                n *= s
-            rows.append({"name": name, "shape": shape, "dtype": str(kind), "numel": n})
+            info = g.tensor_info(name)
+            rows.append({"name": name, "shape": info["shape"], "dtype": info["type"], "numel": info["numel"]})
     elif fmt == "onnx":
         from ..onnx import load_onnx
         m = load_onnx(path)
@@ -305,6 +300,10 @@ def cmd_scaffold(a) -> None:
     cfg = ProjectConfig()
     cfg.project.name = a.name
     cfg.model.architecture = a.arch
+    if getattr(a, "model", None):
+        cfg.model.path = a.model
+    if getattr(a, "data", None):
+        cfg.data.train_path = a.data
     cfg.data.format = "synthetic-mnist"
     with open(os.path.join(root, "axonml.toml"), "w") as f:
         f.write(cfg.to_toml())
@@ -334,6 +333,9 @@ def cmd_scaffold(a) -> None:
 # ----------------------------------------------------------------------------- zip bundles
 def cmd_zip(a) -> None:
     if a.action == "create":
+        a.output = getattr(a, "output_opt", None) or a.output
+        if not a.output:
+            raise SystemExit("zip create needs an output file (-o bundle.zip)")
         if os.path.exists(a.output) and not a.overwrite:
             raise SystemExit(f"{a.output} exists (use --overwrite)")
         if not (a.model or a.data):
@@ -458,13 +460,13 @@ def cmd_analyze(a) -> None:
     ws = _ws_load()
 
     def model_path():
-        p = getattr(a, "path", None) or (ws["model"]["path"] if ws.get("model") else None)
+        p = getattr(a, "path_opt", None) or getattr(a, "path", None) or (ws["model"]["path"] if ws.get("model") else None)
         if not p:
             raise SystemExit("no model given and none loaded (axonml load model <path>)")
         return p
 
     def data_path():
-        p = getattr(a, "path", None) or (ws["dataset"]["path"] if ws.get("dataset") else None)
+        p = getattr(a, "path_opt", None) or getattr(a, "path", None) or (ws["dataset"]["path"] if ws.get("dataset") else None)
         if not p:
             raise SystemExit("no dataset given and none loaded (axonml load data <path>)")
         return p
@@ -504,21 +506,21 @@ def cmd_analyze(a) -> None:
 # ----------------------------------------------------------------------------- parser wiring
 def add_parsers(sub) -> None:
     p = sub.add_parser("upload", help="copy a model file into the workspace's model directory")
-    p.add_argument("path"); p.add_argument("--name"); p.add_argument("--description"); p.add_argument("--format")
-    p.add_argument("--version"); p.add_argument("--dest"); p.add_argument("--validate", action="store_true")
-    p.add_argument("--overwrite", action="store_true"); p.add_argument("--info", action="store_true")
+    p.add_argument("path"); p.add_argument("-n", "--name"); p.add_argument("-d", "--description"); p.add_argument("-f", "--format")
+    p.add_argument("--version"); p.add_argument("-o", "--output", "--dest", dest="dest"); p.add_argument("--validate", action="store_true")
+    p.add_argument("--overwrite", action="store_true"); p.add_argument("--inspect", "--info", dest="info", action="store_true")
     p.set_defaults(fn=cmd_upload)
 
     p = sub.add_parser("data", help="upload, analyse, list, preview and validate datasets")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("upload"); q.add_argument("path"); q.add_argument("--name"); q.add_argument("--type"); q.add_argument("--task")
-    q.add_argument("--dest"); q.add_argument("--split", default="0.8,0.1,0.1"); q.add_argument("--analyze", action="store_true")
-    q = s.add_parser("analyze"); q.add_argument("path"); q.add_argument("--type"); q.add_argument("--max-samples", type=int, default=10000)
-    q.add_argument("--format", default="text", choices=["text", "json"]); q.add_argument("--output")
+    q = s.add_parser("upload"); q.add_argument("path"); q.add_argument("-n", "--name"); q.add_argument("-t", "--data-type", "--type", dest="type"); q.add_argument("--task")
+    q.add_argument("-o", "--output", "--dest", dest="dest"); q.add_argument("--split", default="0.8,0.1,0.1"); q.add_argument("--analyze", action="store_true")
+    q = s.add_parser("analyze"); q.add_argument("path"); q.add_argument("-t", "--data-type", "--type", dest="type"); q.add_argument("--max-samples", type=int, default=10000)
+    q.add_argument("-f", "--format", default="text", choices=["text", "json"]); q.add_argument("-o", "--output")
     q.add_argument("--detailed", action="store_true"); q.add_argument("--recommend", action="store_true")
-    q = s.add_parser("list"); q.add_argument("--path"); q.add_argument("--detailed", action="store_true")
-    q = s.add_parser("config"); q.add_argument("path"); q.add_argument("--output"); q.add_argument("--format", default="toml")
-    q = s.add_parser("preview"); q.add_argument("path"); q.add_argument("--num-samples", type=int, default=5)
+    q = s.add_parser("list"); q.add_argument("-p", "--path"); q.add_argument("-d", "--detailed", action="store_true")
+    q = s.add_parser("config"); q.add_argument("path"); q.add_argument("-o", "--output"); q.add_argument("-f", "--format", default="toml")
+    q = s.add_parser("preview"); q.add_argument("path"); q.add_argument("-n", "--num-samples", type=int, default=5)
     q.add_argument("--random", action="store_true")
     q = s.add_parser("validate"); q.add_argument("path"); q.add_argument("--num-classes", type=int); q.add_argument("--input-shape")
     q.add_argument("--check-missing", action="store_true", default=True); q.add_argument("--check-balance", action="store_true", default=True)
@@ -526,43 +528,44 @@ def add_parsers(sub) -> None:
 
     p = sub.add_parser("scaffold", help="generate a training project")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("generate"); q.add_argument("name"); q.add_argument("--output"); q.add_argument("--template", default="training")
-    q.add_argument("--task", default="classification"); q.add_argument("--arch", default="mlp")
-    q.add_argument("--wandb", action="store_true"); q.add_argument("--augment", action="store_true")
+    q = s.add_parser("generate"); q.add_argument("name"); q.add_argument("-o", "--output"); q.add_argument("-t", "--template", default="training")
+    q.add_argument("--task", default="classification"); q.add_argument("--architecture", "--arch", dest="arch", default="mlp")
+    q.add_argument("-m", "--model", help="model file the generated project starts from"); q.add_argument("-d", "--data", help="dataset path written into the project file")
+    q.add_argument("--wandb", action="store_true"); q.add_argument("--augmentation", "--augment", dest="augment", action="store_true")
     q.add_argument("--overwrite", action="store_true")
-    q = s.add_parser("templates"); q.add_argument("--detailed", action="store_true")
+    q = s.add_parser("templates"); q.add_argument("-d", "--detailed", action="store_true")
     p.set_defaults(fn=cmd_scaffold)
 
     p = sub.add_parser("zip", help="model/dataset bundles")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("create"); q.add_argument("output"); q.add_argument("--model"); q.add_argument("--data")
+    q = s.add_parser("create"); q.add_argument("output", nargs="?"); q.add_argument("-o", "--output", dest="output_opt"); q.add_argument("-m", "--model"); q.add_argument("-d", "--data")
     q.add_argument("--include-config", action="store_true"); q.add_argument("--overwrite", action="store_true")
-    q = s.add_parser("extract"); q.add_argument("input"); q.add_argument("--output"); q.add_argument("--verbose", action="store_true")
-    q = s.add_parser("list"); q.add_argument("input"); q.add_argument("--detailed", action="store_true")
+    q = s.add_parser("extract"); q.add_argument("input"); q.add_argument("-o", "--output"); q.add_argument("-v", "--verbose", action="store_true")
+    q = s.add_parser("list"); q.add_argument("input"); q.add_argument("-d", "--detailed", action="store_true")
     p.set_defaults(fn=cmd_zip)
 
     p = sub.add_parser("rename", help="rename a model file or a dataset")
     s = p.add_subparsers(dest="kind", required=True)
     for kind in ("model", "data"):
-        q = s.add_parser(kind); q.add_argument("path"); q.add_argument("new_name"); q.add_argument("--force", action="store_true")
+        q = s.add_parser(kind); q.add_argument("path"); q.add_argument("new_name"); q.add_argument("-f", "--force", action="store_true")
     p.set_defaults(fn=cmd_rename)
 
     p = sub.add_parser("load", help="load a model and/or dataset into the workspace")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("model"); q.add_argument("path"); q.add_argument("--name"); q.add_argument("--format")
-    q = s.add_parser("data"); q.add_argument("path"); q.add_argument("--name"); q.add_argument("--type")
-    q = s.add_parser("both"); q.add_argument("--model", required=True); q.add_argument("--data", required=True)
+    q = s.add_parser("model"); q.add_argument("path"); q.add_argument("-n", "--name"); q.add_argument("-f", "--format")
+    q = s.add_parser("data"); q.add_argument("path"); q.add_argument("-n", "--name"); q.add_argument("-t", "--data-type", "--type", dest="type")
+    q = s.add_parser("both"); q.add_argument("-m", "--model", required=True); q.add_argument("-d", "--data", required=True)
     s.add_parser("status"); s.add_parser("clear")
     p.set_defaults(fn=cmd_load)
 
     p = sub.add_parser("analyze", help="analyse the loaded (or a given) model / dataset")
     s = p.add_subparsers(dest="action", required=True)
-    q = s.add_parser("model"); q.add_argument("path", nargs="?"); q.add_argument("--detailed", action="store_true")
-    q.add_argument("--output"); q.add_argument("--format", default="text", choices=["text", "json"])
-    q = s.add_parser("data"); q.add_argument("path", nargs="?"); q.add_argument("--detailed", action="store_true")
-    q.add_argument("--max-samples", type=int, default=10000); q.add_argument("--output")
-    q.add_argument("--format", default="text", choices=["text", "json"])
-    q = s.add_parser("both"); q.add_argument("--output")
-    q = s.add_parser("report"); q.add_argument("--output"); q.add_argument("--format", default="text", choices=["html", "json", "md", "text"])
-    q.add_argument("--visualizations", action="store_true")
+    q = s.add_parser("model"); q.add_argument("path", nargs="?"); q.add_argument("-p", "--path", dest="path_opt"); q.add_argument("-d", "--detailed", action="store_true")
+    q.add_argument("-o", "--output"); q.add_argument("-f", "--format", default="text", choices=["text", "json"])
+    q = s.add_parser("data"); q.add_argument("path", nargs="?"); q.add_argument("-p", "--path", dest="path_opt"); q.add_argument("-d", "--detailed", action="store_true")
+    q.add_argument("--max-samples", type=int, default=10000); q.add_argument("-o", "--output")
+    q.add_argument("-f", "--format", default="text", choices=["text", "json"])
+    q = s.add_parser("both"); q.add_argument("-o", "--output")
+    q = s.add_parser("report"); q.add_argument("-o", "--output"); q.add_argument("-f", "--format", default="text", choices=["html", "json", "md", "text"])
+    q.add_argument("--visualize", "--visualizations", dest="visualizations", action="store_true")
     p.set_defaults(fn=cmd_analyze)

@@ -167,6 +167,14 @@ class GGUFFile:
 
     def tensor_names(self): return list(self.tensors)
 
+    def tensor_info(self, name: str) -> dict:
+        """``{"shape", "type" (storage type name), "numel", "nbytes"}`` of one tensor."""
+        shape, qt, _, nbytes = self.tensors[name]
+        n = 1
+        for d in shape:
+            n *= d
+        return {"shape": list(shape), "type": qt.value, "numel": n, "nbytes": nbytes}
+
     def quantized(self, name: str, device=None) -> QuantizedTensor:
         shape, qt, off, nbytes = self.tensors[name]
         import warnings
