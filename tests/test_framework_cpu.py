@@ -840,3 +840,18 @@ def test_remaining_reference_method_names():
     assert stage.forward(torch.zeros(1, 2)).shape == (1, 3) and stage(torch.zeros(1, 2)).shape == (1, 3)
     gb = parallel.GradientBucket(8)
     assert gb.data_mut().numel() == 0
+
+
+def test_tensor_module_functions_named_after_the_reference_methods():
+    import axonml_b200.tensor as T
+    from axonml_b200.core import Storage
+    x = T.from_slice(range(12), [3, 4])
+    assert T.slice(x, [(1, 3), (0, 2)]).tolist() == [[4, 5], [8, 9]]
+    assert T.get(x, [2, 3]) == 11 and T.to_vec(T.slice_dim0(x, 0, 1)) == [0, 1, 2, 3]
+    with pytest.raises(IndexError):
+        T.get(x, [1])
+    assert T.strides(x.t()) == [1, 4] and T.clone_deep(x.t()).is_contiguous()
+    assert T.is_scalar(T.scalar(1.0)) and T.is_empty(T.zeros([0])) and not T.is_empty(x)
+    assert T.mean_dim(x, 1).tolist() == [1.5, 5.5, 9.5]
+    assert T.from_storage(Storage(torch.arange(6.0)), [2, 3]).tolist() == [[0, 1, 2], [3, 4, 5]]
+    assert T.to_device(x, "cpu").shape == (3, 4)
