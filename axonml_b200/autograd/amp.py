@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import contextlib
 import enum
+import threading
 
 import torch
 
@@ -21,7 +22,14 @@ def _device_type() -> str:
     return "cuda" if torch.cuda.is_available() else "cpu"
 
 
-_STACK: list = []          # dtypes of the enabled autocast regions this thread is inside
+_TLS = threading.local()    # .stack: dtypes of the enabled autocast regions this thread is inside
+
+
+def _stack() -> list:
+    st = getattr(_TLS, "stack", None)
+    if st is None:
+        st = _TLS.stack = []
+    return st
 
 
 @contextlib.contextmanager
@@ -29,26 +37,26 @@ def autocast(dtype=torch.bfloat16, enabled: bool = True, device_type: str | None
     td = as_torch_dtype(dtype)
     with torch.autocast(device_type or _device_type(), dtype=td, enabled=enabled):
         if enabled:
-            _STACK.append(td)
+            _stack().append(td)
         try:
             yield
         finally:
             if enabled:
-                _STACK.pop()
+                _stack().pop()
 
 
 def autocast_dtype(device_type: str | None = None):
     """Compute dtype of the innermost autocast region as a ``DType`` (meaningful only while
     ``is_autocast_enabled()``; amp.rs:49-54)."""
     from ..core.dtype import DType
-    if _STACK:
-        return DType.from_torch(_STACK[-1])
+    if _stack():
+        return DType.from_torch(_stack()[-1])
     return DType.from_torch(torch.get_autocast_dtype(device_type or _device_type()))
 
 
 def autocast_depth() -> int:
     """How many enabled ``autocast`` regions are open (amp.rs:56-60)."""
-    return len(_STACK)
+    return len(_stack())
 
 
 @contextlib.contextmanager
