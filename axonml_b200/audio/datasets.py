@@ -26,6 +26,8 @@ class _Synthetic(Dataset):
     def _wave(self, label, g): raise NotImplementedError
 
     def get(self, i: int):
+        if not 0 <= i < self.n:
+            raise IndexError(f"index {i} out of range for a dataset of {self.n} samples")
         g = torch.Generator().manual_seed(self.seed + i)
         label = i % self.classes
         return self._wave(label, g), torch.tensor(label, dtype=torch.long)

@@ -78,12 +78,53 @@ class TimeStretch(Transform):
         return F.interpolate(x.reshape(1, 1, -1).float(), size=n, mode="linear", align_corners=False).reshape(*x.shape[:-1], n)
 
 
+def _phase_vocoder(x: torch.Tensor, stretch: float, n_fft: int) -> torch.Tensor:
+    """``x`` made ``stretch`` times longer at the same pitch: short-time spectra re-spaced in time,
+    magnitudes interpolated between neighbouring frames, phases advanced by each bin's measured
+    instantaneous frequency."""
+    hop = n_fft // 4
+    win = torch.hann_window(n_fft, dtype=torch.float32)
+    spec = torch.stft(x.float(), n_fft, hop, window=win, return_complex=True, pad_mode="constant")           # [bins, frames]
+    frames = spec.shape[1]
+    steps = torch.arange(0, frames - 1, 1.0 / stretch) if frames > 1 else torch.zeros(1)
+    k0 = steps.floor().long().clamp_max(frames - 1)
+    k1 = (k0 + 1).clamp_max(frames - 1)
+    frac = (steps - k0).unsqueeze(0)
+    mag = spec.abs()
+    mag_t = mag[:, k0] * (1 - frac) + mag[:, k1] * frac
+    omega = (2 * math.pi * hop * torch.arange(spec.shape[0]) / n_fft).unsqueeze(1)          # expected advance per hop
+    ang = spec.angle()
+    dphi = ang[:, k1] - ang[:, k0] - omega
+    dphi = dphi - 2 * math.pi * torch.round(dphi / (2 * math.pi)) + omega
+    phase = torch.cat([ang[:, :1], ang[:, :1] + dphi[:, :-1].cumsum(1)], 1)
+    out = torch.istft(torch.polar(mag_t, phase), n_fft, hop, window=win, length=int(round(x.shape[-1] * stretch)))
+    return out
+
+
 class PitchShift(Transform):
+    """Pitch moved by ``semitones`` at the same length (transforms.rs:300-340): the clip is made
+    ``2^(semitones/12)`` times longer at constant pitch by a phase vocoder and then played back at
+    that speed (linear resampling to the original length), then scaled to the input's RMS level.
+    Clips shorter than 64 samples come back unchanged."""
+
     def __init__(self, semitones: float): self.semitones = semitones
+    @classmethod
+    def new(cls, semitones: float): return cls(semitones)
+
     def apply(self, x):
         rate = 2.0 ** (self.semitones / 12.0)
-        y = TimeStretch(rate)(x)                       # changes pitch and duration ...
-        return F.interpolate(y.reshape(1, 1, -1), size=x.shape[-1], mode="linear", align_corners=False).reshape(x.shape)
+        n = x.shape[-1]
+        if n < 64 or abs(rate - 1.0) < 1e-9:
+            return x
+        n_fft = 1024 if n >= 4096 else 1 << max(5, (n // 4).bit_length() - 1)
+        flat = x.reshape(-1, n)
+        out = []
+        for row in flat:
+            long_ = _phase_vocoder(row, rate, n_fft)
+            y = F.interpolate(long_.reshape(1, 1, -1), size=n, mode="linear", align_corners=False).reshape(n)
+            gain = row.float().pow(2).mean().sqrt() / y.pow(2).mean().sqrt().clamp_min(1e-12)     # same loudness as the input
+            out.append(y * gain)
+        return torch.stack(out).reshape(x.shape).to(x.dtype)
 
 
 class AddNoise(Transform):

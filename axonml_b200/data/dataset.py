@@ -9,7 +9,17 @@ class Dataset:
     def len(self) -> int: raise NotImplementedError
     def get(self, index: int): raise NotImplementedError
     def __len__(self) -> int: return self.len()
-    def __getitem__(self, index: int): return self.get(index)
+
+    def __getitem__(self, index: int):
+        """``dataset[i]`` with Python's conventions: negative positions count from the end and a
+        position past the end raises ``IndexError`` (which also ends ``for sample in dataset``)."""
+        n = self.len()
+        if index < 0:
+            index += n
+        if not 0 <= index < n:
+            raise IndexError(f"index {index} out of range for a dataset of {n} samples")
+        return self.get(index)
+
     def is_empty(self) -> bool: return self.len() == 0
 
 

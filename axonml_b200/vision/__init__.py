@@ -10,6 +10,6 @@ from .models import (VGG, PositionalEncoding, Transformer, TransformerDecoder, T
 from .transforms import (CenterCrop, ColorJitter, Grayscale, ImageNormalize, Pad, RandomHorizontalFlip,
                          RandomRotation, RandomVerticalFlip, Resize, ToTensorImage)
 from . import hub
-from .hub import (HubError, PretrainedModel, cache_dir, download_weights, is_cached, list_models, load_state_dict, model_info,
-                  model_registry)
+from .hub import (HubError, PretrainedModel, cache_dir, cached_path, download_weights, is_cached, list_models,
+                  load_state_dict, model_info, model_registry, save_state_dict)
 from ..serialize.state_dict import StateDict

@@ -108,6 +108,8 @@ class _SyntheticImages(Dataset):
     def num_classes(self) -> int: return self.classes
 
     def get(self, i):
+        if not 0 <= i < self.n:
+            raise IndexError(f"index {i} out of range for a dataset of {self.n} samples")
         g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
         label = i % self.classes
         img = torch.rand(self.shape, generator=g) * 0.3
@@ -155,6 +157,8 @@ class SyntheticImageNet(_SyntheticImages):
     def __init__(self, num_samples: int = 1024, seed: int = 0): super().__init__(num_samples, (3, 224, 224), 1000, seed)
 
     def get(self, i):
+        if not 0 <= i < self.n:
+            raise IndexError(f"index {i} out of range for a dataset of {self.n} samples")
         g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
         return torch.randn(self.shape, generator=g), torch.randint(0, 1000, (), generator=g)
 
