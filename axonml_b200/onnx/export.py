@@ -73,7 +73,10 @@ class OnnxExporter:
         m += P.enc_bytes(7, g) + P.enc_bytes(8, P.enc_str(1, "") + P.enc_varint(2, OPSET))
         return m
 
-    to_proto = to_bytes
+    def to_proto(self):
+        """The model as a ``ModelProto`` message object (export.rs: ``OnnxExporter::to_proto``)."""
+        from .messages import ModelProto
+        return ModelProto.from_bytes(self.to_bytes())
 
     def export(self, path) -> None:
         with open(path, "wb") as f:
