@@ -167,8 +167,8 @@ class PlatformServer:
         self.revoked: set[str] = set()
         self.started = time.time()
         self.router = Router()
-        from . import routes_assets, routes_auth, routes_misc, routes_training
-        for mod in (routes_auth, routes_training, routes_assets, routes_misc):
+        from . import routes_assets, routes_auth, routes_misc, routes_tools, routes_training
+        for mod in (routes_auth, routes_training, routes_tools, routes_assets, routes_misc):
             mod.register(self)
         if self.users.count() == 0 and admin_password:
             self.create_user(admin_email, "admin", admin_password, role="admin")
@@ -242,6 +242,8 @@ class PlatformServer:
             return 409, {"error": f"already exists: {e}"}
         except A.AuthError as e:
             return e.status, {"error": str(e)}
+        except PermissionError as e:                  # e.g. a service whose credentials are not configured
+            return 403, {"error": str(e)}
         except (ValueError, KeyError) as e:
             return 400, {"error": f"{type(e).__name__}: {e}"}
 
@@ -310,6 +312,8 @@ def _make_handler(app: PlatformServer):
                 self._respond(409, {"error": f"already exists: {e}"}); ok = False
             except A.AuthError as e:
                 self._respond(e.status, {"error": str(e)}); ok = False
+            except PermissionError as e:              # e.g. a service whose credentials are not configured
+                self._respond(403, {"error": str(e)}); ok = False
             except (ValueError, KeyError) as e:
                 self._respond(400, {"error": f"{type(e).__name__}: {e}"}); ok = False
             except Exception as e:  # noqa: BLE001 - the server must answer

@@ -82,8 +82,10 @@ class JwtAuth:
 
     def _token(self, user_id, email, role, ttl, token_type, mfa_verified=False) -> str:
         now = int(time.time())
+        # jti: two tokens issued to one user within the same second must differ, or revoking one
+        # session (logout) would revoke the other too
         return self._encode({"sub": user_id, "email": email, "role": role, "exp": now + ttl, "iat": now,
-                             "token_type": token_type, "mfa_verified": mfa_verified})
+                             "token_type": token_type, "mfa_verified": mfa_verified, "jti": secrets.token_hex(8)})
 
     def create_access_token(self, user_id, email, role, mfa_verified=False) -> str:
         return self._token(user_id, email, role, self.access_expiry_s, "access", mfa_verified)

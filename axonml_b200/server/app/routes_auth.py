@@ -260,6 +260,8 @@ def register(app) -> None:
         (collection,) = req.need("collection")
         if collection == "users":
             raise HttpError(403, "the users collection is not exposed through the query endpoint")
+        if collection not in app.store.COLLECTIONS:
+            raise HttpError(404, f"no collection named {collection!r} (one of {', '.join(sorted(app.store.COLLECTIONS))})")
         return app.store.query(collection, req.json.get("filter"), limit=req.json.get("limit"),
                                sort=req.json.get("sort"), descending=bool(req.json.get("descending")))
 
